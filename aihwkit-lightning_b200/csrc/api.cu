@@ -1,0 +1,413 @@
+// extern "C" entry points of libanalog_b200.so (declared in include/analog_b200.h): argument
+// checking, narrowing of the configuration scalars, and the launch sequence of one forward /
+// backward call.  No device memory is allocated here and nothing synchronises the stream.
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "analog_math.cuh"
+#include "internal.h"
+
+namespace al {
+
+static thread_local char g_last_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return AL_ERR_CUDA;
+  }
+  return AL_OK;
+}
+
+static int make_tile_table(const int32_t* ends, int T, int K, TileTable* tt) {
+  if (ends == nullptr || T < 1) {
+    set_error("tile table missing (T=%d)", T);
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  if (T > kMaxTiles) {
+    set_error("T=%d exceeds the maximum of %d analog tiles", T, kMaxTiles);
+    return AL_ERR_TOO_LARGE;
+  }
+  int prev = 0;
+  for (int t = 0; t < T; ++t) {
+    if (ends[t] <= prev) {
+      set_error("tile ends must be strictly increasing (tile %d: %d after %d)", t, ends[t], prev);
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    tt->ends[t] = ends[t];
+    prev = ends[t];
+  }
+  if (prev != K) {
+    set_error("last tile end %d != K=%d", prev, K);
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  tt->T = T;
+  return AL_OK;
+}
+
+static int check_dtype(int dtype) {
+  if (dtype != AL_F32 && dtype != AL_BF16) {
+    set_error("unknown dtype %d", dtype);
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  return AL_OK;
+}
+
+static int derive(const AlDesc& d, Derived* o) {
+  memset(o, 0, sizeof(*o));
+  if (d.M < 1 || d.K < 1 || d.N < 1) {
+    set_error("non-positive size M=%d K=%d N=%d", d.M, d.K, d.N);
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  if (check_dtype(d.dtype)) return AL_ERR_BAD_ARGUMENT;
+  if (d.ir_mode < AL_IR_OFF || d.ir_mode > AL_IR_DYNAMIC) {
+    set_error("unknown input-range mode %d", d.ir_mode);
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  if (d.clip_type == AL_CLIP_LEARNABLE_PER_CHANNEL) {
+    set_error("learnable per-channel weight clipping is not implemented");
+    return AL_ERR_UNSUPPORTED;
+  }
+  o->has_dac = d.inp_res > 0;
+  if (o->has_dac && d.ir_mode == AL_IR_OFF) {
+    set_error("inp_res > 0 needs an input range");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  o->has_adc = d.out_res > 0;
+  o->has_bound = d.out_bound > 0;
+  if (o->has_adc && (!o->has_bound || d.ir_mode == AL_IR_OFF)) {
+    set_error("out_res > 0 needs out_bound > 0 and an input range");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  if (o->has_bound && d.ir_mode == AL_IR_OFF) {
+    set_error("out_bound > 0 needs an input range");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  o->has_noise = d.training && d.out_noise > 0;
+  if (o->has_noise && d.ir_mode == AL_IR_OFF) {
+    set_error("out_noise > 0 needs an input range");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  o->inp_res = (float)d.inp_res;
+  o->out_res = (float)d.out_res;
+  o->out_bound = (float)d.out_bound;
+  o->noise_coef = (float)(d.out_noise / sqrt((double)d.T));
+  o->std_dev = (float)d.std_dev;
+  o->decay = (float)d.decay;
+  o->input_min_percentage = (float)d.input_min_percentage;
+  o->init_std_alpha = (float)d.init_std_alpha;
+  o->weight_quant = d.quant_type;
+  o->weight_noise = d.training ? d.noise_type : AL_NOISE_NONE;
+  if (o->weight_quant != AL_QUANT_NONE) {
+    if (!(d.mod_res > 0)) {
+      set_error("weight discretisation needs modifier.res > 0");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    double n_states = d.mod_res > 1.0 / d.mod_res ? d.mod_res : 1.0 / d.mod_res;
+    o->n_states = (float)n_states;
+    o->max_state = (float)(n_states / 2.0);
+  }
+  o->bound_pc = d.clip_type == AL_CLIP_LAYER_GAUSSIAN_PER_CHANNEL ||
+                d.clip_type == AL_CLIP_LEARNABLE_PER_CHANNEL;
+  o->noise_pc = d.out_noise_per_channel != 0;
+  o->round_dt = (d.dtype == AL_BF16 && d.ref_rounding) ? AL_BF16 : AL_F32;
+  return AL_OK;
+}
+
+static bool needs_wmax(const Derived& dv) {
+  return dv.has_adc || dv.has_bound || dv.has_noise || dv.weight_noise != AL_NOISE_NONE ||
+         dv.weight_quant != AL_QUANT_NONE;
+}
+
+static bool pick_tc(const AlDesc& d, const TileTable& tt, bool backward) {
+  if (d.engine == AL_ENGINE_SIMT) return false;
+  return backward ? tc_backward_supported(d, tt) : tc_forward_supported(d, tt);
+}
+
+}  // namespace al
+
+using namespace al;
+
+extern "C" {
+
+int al_version(void) { return 1; }
+
+const char* al_last_error(void) { return g_last_error; }
+
+const char* al_status_str(int status) {
+  switch (status) {
+    case AL_OK: return "ok";
+    case AL_ERR_BAD_ARGUMENT: return "bad argument";
+    case AL_ERR_UNSUPPORTED: return "unsupported configuration";
+    case AL_ERR_CUDA: return "CUDA error";
+    case AL_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+    case AL_ERR_TOO_LARGE: return "size beyond the stated maximum";
+    default: return "unknown status";
+  }
+}
+
+int al_abs_max_tiles(int32_t dtype, const void* a, int32_t rows, int32_t K,
+                     const int32_t* tile_ends_host, int32_t T, void* out, void* stream) {
+  if (check_dtype(dtype)) return AL_ERR_BAD_ARGUMENT;
+  if (!a || !out || rows < 1 || K < 1) {
+    set_error("al_abs_max_tiles: null pointer or empty matrix");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  TileTable tt;
+  int rc = make_tile_table(tile_ends_host, T, K, &tt);
+  if (rc) return rc;
+  return launch_abs_max_tiles(dtype, a, rows, K, tt, out, (cudaStream_t)stream);
+}
+
+int64_t al_std_scratch_floats(int32_t rows, int32_t T) { return 2 * (int64_t)rows * T + T + 4; }
+
+int al_std_tiles(int32_t dtype, const void* a, int32_t rows, int32_t K,
+                 const int32_t* tile_ends_host, int32_t T, float* out, float* scratch,
+                 void* stream) {
+  if (check_dtype(dtype)) return AL_ERR_BAD_ARGUMENT;
+  if (!a || !out || !scratch || rows < 1 || K < 1) {
+    set_error("al_std_tiles: null pointer or empty matrix");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  TileTable tt;
+  int rc = make_tile_table(tile_ends_host, T, K, &tt);
+  if (rc) return rc;
+  return launch_std_tiles(dtype, a, rows, K, tt, out, scratch, (cudaStream_t)stream);
+}
+
+int al_uses_tcgen05(const AlDesc* desc, const int32_t* tile_ends_host) {
+  if (!desc) return 0;
+  TileTable tt;
+  if (make_tile_table(tile_ends_host, desc->T, desc->K, &tt)) return 0;
+  return pick_tc(*desc, tt, false) ? 1 : 0;
+}
+
+int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
+  if (!desc || !a) {
+    set_error("al_forward: null descriptor");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  const AlDesc& d = *desc;
+  Derived dv;
+  int rc = derive(d, &dv);
+  if (rc) return rc;
+  TileTable tt;
+  rc = make_tile_table(a->tile_ends, d.T, d.K, &tt);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (!a->x || !a->w || !a->out) {
+    set_error("al_forward: x, w and out must be given");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+
+  // 1. input range (static mode): optional init-from-data update, then copy the ranges used
+  const void* ir_static = nullptr;
+  if (d.ir_mode == AL_IR_STATIC) {
+    if (!a->input_range || !a->input_range_update_idx || !a->ir_rows) {
+      set_error("static input range needs input_range, input_range_update_idx and ir_rows");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    int do_update = d.training && d.init_from_data > 0;
+    if (do_update) {
+      if (!a->std_scratch) {
+        set_error("init_from_data > 0 needs std_scratch");
+        return AL_ERR_BAD_ARGUMENT;
+      }
+      float* std_out = a->std_scratch + 2 * (int64_t)d.M * d.T;
+      rc = launch_std_tiles(d.dtype, a->x, d.M, d.K, tt, std_out, a->std_scratch, s);
+      if (rc) return rc;
+      rc = launch_ir_update(d.dtype, a->input_range, a->input_range_update_idx, std_out, d.T,
+                            d.init_from_data, dv.init_std_alpha, 1, a->ir_rows, s);
+    } else {
+      rc = launch_ir_update(d.dtype, a->input_range, a->input_range_update_idx, nullptr, d.T, 0,
+                            0.0f, 0, a->ir_rows, s);
+    }
+    if (rc) return rc;
+    ir_static = a->ir_rows;
+  }
+
+  // 2. DAC: x -> xq (+ per-row ranges in dynamic mode)
+  const void* xq = a->x;
+  if (d.ir_mode != AL_IR_OFF) {
+    if (!a->xq || (d.ir_mode == AL_IR_DYNAMIC && !a->ir_rows)) {
+      set_error("al_forward: xq / ir_rows workspace missing");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    rc = launch_dac(d.dtype, a->x, d.M, d.K, tt, d.ir_mode, ir_static, dv.has_dac ? dv.inp_res : -1.0f,
+                    d.no_rounding, a->xq, a->ir_rows, a->codes, s);
+    if (rc) return rc;
+    xq = a->xq;
+  }
+
+  // 3. weight statistics and modifier
+  const void* w_mod = a->w;
+  float* tile_max = nullptr;
+  if (needs_wmax(dv)) {
+    if (!a->w_amax || !a->w_tile_max) {
+      set_error("al_forward: w_amax / w_tile_max workspace missing");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    tile_max = (float*)a->w_tile_max;
+    int32_t* flags = (int32_t*)(tile_max + d.T);
+    rc = launch_abs_max_tiles(d.dtype, a->w, d.N, d.K, tt, a->w_amax, s);
+    if (rc) return rc;
+    rc = launch_tile_max(d.dtype, a->w_amax, d.N, tt, dv.weight_quant, dv.n_states, tile_max, flags, s);
+    if (rc) return rc;
+    if (dv.weight_quant != AL_QUANT_NONE || dv.weight_noise != AL_NOISE_NONE) {
+      if (!a->w_mod || a->w_mod == a->w) {
+        set_error("al_forward: w_mod workspace missing (the modifier never writes into w)");
+        return AL_ERR_BAD_ARGUMENT;
+      }
+      rc = launch_weight_modify(d.dtype, a->w, d.N, d.K, tt, a->w_amax, tile_max, flags,
+                                dv.weight_quant, dv.n_states, dv.max_state, dv.weight_noise,
+                                dv.std_dev, a->w_noise, a->seed, a->offset, d.no_rounding, a->w_mod, s);
+      if (rc) return rc;
+      w_mod = a->w_mod;
+    }
+  }
+
+  // 4. tiled GEMM with the per-tile output stage
+  FwdEpilogueParams ep;
+  memset(&ep, 0, sizeof(ep));
+  ep.M = d.M; ep.N = d.N; ep.T = d.T;
+  ep.ir_mode = d.ir_mode;
+  ep.ir_rows = a->ir_rows;
+  ep.w_amax = a->w_amax;
+  ep.w_tile_max = tile_max;
+  ep.bias = a->bias;
+  ep.out_noise = a->out_noise;
+  ep.mask_words = (d.N + 31) / 32;
+  ep.keep_mask = (dv.has_bound && d.save_for_backward) ? a->keep_mask : nullptr;
+  if (dv.has_bound && d.save_for_backward && !a->keep_mask) {
+    set_error("al_forward: keep_mask workspace missing");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  ep.has_noise = dv.has_noise; ep.has_bound = dv.has_bound; ep.has_adc = dv.has_adc;
+  ep.bound_pc = dv.bound_pc; ep.noise_pc = dv.noise_pc; ep.no_rounding = d.no_rounding;
+  ep.noise_coef = dv.noise_coef; ep.out_bound = dv.out_bound; ep.out_res = dv.out_res;
+  ep.seed = a->seed; ep.offset = a->offset;
+
+  if (d.engine == AL_ENGINE_TCGEN05 && !tc_forward_supported(d, tt)) {
+    set_error("tcgen05 engine requested but the problem does not qualify (bf16, 16-byte aligned tiles)");
+    return AL_ERR_UNSUPPORTED;
+  }
+  if (pick_tc(d, tt, false)) return launch_fwd_tc(dv.round_dt, xq, w_mod, d.K, tt, ep, a->out, s);
+  return launch_fwd_simt(d.dtype, dv.round_dt, xq, w_mod, d.K, tt, ep, a->out, s);
+}
+
+int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T) {
+  (void)K;
+  return 256 * (int64_t)N + 3 * (int64_t)T * M + 16;
+}
+
+int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
+  if (!desc || !a) {
+    set_error("al_backward: null descriptor");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  const AlDesc& d = *desc;
+  Derived dv;
+  int rc = derive(d, &dv);
+  if (rc) return rc;
+  TileTable tt;
+  rc = make_tile_table(a->tile_ends, d.T, d.K, &tt);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (!a->grad_out) {
+    set_error("al_backward: grad_out missing");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  const uint32_t* mask = dv.has_bound ? a->keep_mask : nullptr;
+  if (dv.has_bound && !mask) {
+    set_error("al_backward: keep_mask missing although out_bound > 0");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  int mask_words = (d.N + 31) / 32;
+  // Without a clamp mask every tile sees the same gradient: one GEMM over the whole K range.
+  TileTable one;
+  one.T = 1;
+  one.ends[0] = d.K;
+  const TileTable& gt = mask ? tt : one;
+  if (d.engine == AL_ENGINE_TCGEN05 && !tc_backward_supported(d, tt)) {
+    set_error("tcgen05 engine requested but the problem does not qualify");
+    return AL_ERR_UNSUPPORTED;
+  }
+  bool tc = pick_tc(d, tt, true);
+
+  if (a->grad_x) {
+    if (!a->w_mod) {
+      set_error("al_backward: w_mod missing");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    rc = tc ? launch_dgrad_tc(a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, a->grad_x, s)
+            : launch_dgrad_simt(d.dtype, a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, a->grad_x, s);
+    if (rc) return rc;
+    if (d.ir_mode == AL_IR_STATIC) {
+      if (!a->x || !a->ir_rows || !a->reduce_scratch) {
+        set_error("al_backward: static input range needs x, ir_rows and reduce_scratch");
+        return AL_ERR_BAD_ARGUMENT;
+      }
+      rc = launch_static_ir_backward(d.dtype, a->x, a->ir_rows, a->grad_x, d.M, d.K, tt, dv.decay,
+                                     dv.input_min_percentage, a->grad_input_range,
+                                     a->reduce_scratch + 256 * (int64_t)d.N, s);
+      if (rc) return rc;
+    }
+  } else if (a->grad_input_range) {
+    set_error("al_backward: grad_input_range needs grad_x");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  if (a->grad_w) {
+    if (!a->xq) {
+      set_error("al_backward: xq missing");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    rc = tc ? launch_wgrad_tc(a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt, a->grad_w, s)
+            : launch_wgrad_simt(d.dtype, a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt, a->grad_w, s);
+    if (rc) return rc;
+  }
+  if (a->grad_bias) {
+    if (!a->reduce_scratch) {
+      set_error("al_backward: reduce_scratch missing");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    rc = launch_bias_grad(d.dtype, a->grad_out, d.M, d.N, a->grad_bias, a->reduce_scratch, s);
+    if (rc) return rc;
+  }
+  return AL_OK;
+}
+
+int al_clip_weights(int32_t dtype, void* w, int32_t rows, int32_t cols, int32_t clip_type,
+                    float sigma, float* scratch, void* stream) {
+  if (check_dtype(dtype)) return AL_ERR_BAD_ARGUMENT;
+  if (clip_type == AL_CLIP_NONE || clip_type == AL_CLIP_LEARNABLE_PER_CHANNEL) return AL_OK;
+  if (!w || rows < 1 || cols < 1 || !scratch) {
+    set_error("al_clip_weights: null pointer or empty matrix");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  if (!(sigma > 0)) {
+    set_error("Clip sigma must be greater than 0");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  if (clip_type != AL_CLIP_LAYER_GAUSSIAN && clip_type != AL_CLIP_LAYER_GAUSSIAN_PER_CHANNEL) {
+    set_error("Unknown clip type %d", clip_type);
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  return launch_clip_weights(dtype, w, rows, cols, clip_type, sigma, scratch, (cudaStream_t)stream);
+}
+
+int al_read_device_error(void* stream, uint32_t* out_code) {
+  if (!out_code) return AL_ERR_BAD_ARGUMENT;
+  return tc_read_device_error((cudaStream_t)stream, out_code);
+}
+
+}  // extern "C"

@@ -1,0 +1,105 @@
+// Internal declarations shared by the translation units of libanalog_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/analog_b200.h"
+
+namespace al {
+
+constexpr int kMaxTiles = 256;
+
+// Tile boundaries travel to the kernels by value (kernel parameter space), so that no device
+// allocation or copy is needed for them.
+struct TileTable {
+  int32_t T;
+  int32_t ends[kMaxTiles];  // cumulative, ends[T-1] == K
+  __host__ __device__ int lo(int t) const { return t == 0 ? 0 : ends[t - 1]; }
+  __host__ __device__ int hi(int t) const { return ends[t]; }
+};
+
+// Host-side derived constants of a forward/backward call (double -> float narrowing happens
+// here, once, the way the Python reference narrows its scalars).
+struct Derived {
+  float inp_res, out_res, out_bound, noise_coef, std_dev, n_states, max_state;
+  float decay, input_min_percentage, init_std_alpha;
+  int has_dac, has_noise, has_bound, has_adc, bound_pc, noise_pc;
+  int weight_noise;   // noise type active in this call (training only)
+  int weight_quant;   // quant type
+  int round_dt;       // dtype intermediate results are rounded to
+};
+
+// Everything the per-tile output stage of a forward GEMM kernel needs.
+struct FwdEpilogueParams {
+  int32_t M, N, T;
+  int32_t ir_mode;
+  const void* ir_rows;       // [T,M] (dynamic) or [T] (static), dtype
+  const void* w_amax;        // [T,N] dtype
+  const float* w_tile_max;   // [T]
+  const void* bias;          // [N] dtype or null
+  const void* out_noise;     // [T,M,N] dtype or null (replay)
+  uint32_t* keep_mask;       // [T,M,mask_words] or null
+  int32_t mask_words;
+  int32_t has_noise, has_bound, has_adc, bound_pc, noise_pc, no_rounding;
+  float noise_coef, out_bound, out_res;
+  uint64_t seed, offset;
+};
+
+void set_error(const char* fmt, ...);
+int check_launch(const char* what);
+
+// ---- reductions (reduce_kernels.cu) -------------------------------------------------------
+int launch_abs_max_tiles(int dtype, const void* a, int rows, int K, const TileTable& tt,
+                         void* out, cudaStream_t s);
+int launch_tile_max(int dtype, const void* amax, int rows, const TileTable& tt, int quant_type,
+                    float n_states, float* tile_max, int32_t* flags, cudaStream_t s);
+int launch_std_tiles(int dtype, const void* a, int rows, int K, const TileTable& tt, float* out,
+                     float* scratch, cudaStream_t s);
+int launch_ir_update(int dtype, void* input_range, void* update_idx, const float* std, int T,
+                     int init_from_data, float init_std_alpha, int do_update, void* ir_used,
+                     cudaStream_t s);
+int launch_clip_weights(int dtype, void* w, int rows, int cols, int clip_type, float sigma,
+                        float* scratch, cudaStream_t s);
+
+// ---- operand pre-passes (prepass_kernels.cu) ----------------------------------------------
+int launch_dac(int dtype, const void* x, int M, int K, const TileTable& tt, int ir_mode,
+               const void* ir_static, float inp_res, int no_rounding, void* xq, void* ir_rows,
+               void* codes, cudaStream_t s);
+int launch_weight_modify(int dtype, const void* w, int N, int K, const TileTable& tt,
+                         const void* w_amax, const float* tile_max, const int32_t* flags,
+                         int quant_type, float n_states, float max_state, int noise_type,
+                         float std_dev, const void* w_noise, uint64_t seed, uint64_t offset,
+                         int no_rounding, void* w_mod, cudaStream_t s);
+
+// ---- SIMT GEMMs (gemm_simt.cu) ------------------------------------------------------------
+int launch_fwd_simt(int dtype, int round_dt, const void* xq, const void* w_mod, int K,
+                    const TileTable& tt, const FwdEpilogueParams& ep, void* out, cudaStream_t s);
+// grad_x[:, tile] = (g * keep_t) @ w_mod[:, tile]
+int launch_dgrad_simt(int dtype, const void* g, const void* w_mod, const uint32_t* keep_mask,
+                      int mask_words, int M, int K, int N, const TileTable& tt, void* grad_x,
+                      cudaStream_t s);
+// grad_w[:, tile] = (g * keep_t)^T @ xq[:, tile]
+int launch_wgrad_simt(int dtype, const void* g, const void* xq, const uint32_t* keep_mask,
+                      int mask_words, int M, int K, int N, const TileTable& tt, void* grad_w,
+                      cudaStream_t s);
+
+// ---- backward element-wise parts (backward_kernels.cu) ------------------------------------
+int launch_bias_grad(int dtype, const void* g, int M, int N, void* grad_bias, float* scratch,
+                     cudaStream_t s);
+int launch_static_ir_backward(int dtype, const void* x, const void* ir_used, void* grad_x, int M,
+                              int K, const TileTable& tt, float decay, float input_min_percentage,
+                              void* grad_ir, float* scratch, cudaStream_t s);
+
+// ---- tcgen05 GEMMs (gemm_tcgen05.cu) ------------------------------------------------------
+bool tc_forward_supported(const AlDesc& d, const TileTable& tt);
+int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const TileTable& tt,
+                  const FwdEpilogueParams& ep, void* out, cudaStream_t s);
+bool tc_backward_supported(const AlDesc& d, const TileTable& tt);
+int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask, int mask_words,
+                    int M, int K, int N, const TileTable& tt, void* grad_x, cudaStream_t s);
+int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, int mask_words,
+                    int M, int K, int N, const TileTable& tt, void* grad_w, cudaStream_t s);
+int tc_read_device_error(cudaStream_t s, uint32_t* code);
+
+}  // namespace al

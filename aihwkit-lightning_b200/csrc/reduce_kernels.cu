@@ -1,0 +1,313 @@
+// Reductions of the analog linear path: per-(row, tile) abs-max, per-tile abs-max over rows,
+// per-tile standard deviation over all rows, the predicated input-range update and the
+// Gaussian weight clipping.  All are HBM-bound scans: one warp per (row, tile) segment,
+// 128-bit loads on the aligned body of the segment, warp-shuffle reductions, and a fixed
+// merge order (no floating-point atomics), so results are bitwise repeatable.
+#include "analog_math.cuh"
+#include "internal.h"
+
+namespace al {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+template <int DT>
+struct Vec;  // 16-byte vector of DT elements
+template <>
+struct Vec<kF32> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const void* p, float v[4]) {
+    float4 q = *reinterpret_cast<const float4*>(p);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  }
+};
+template <>
+struct Vec<kBF16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const void* p, float v[8]) {
+    uint4 q = *reinterpret_cast<const uint4*>(p);
+    uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+
+// Calls f(value) for every element of the segment [start, start+len) of a DT array, spreading
+// the elements over the 32 lanes of the calling warp: scalar head up to the first 16-byte
+// boundary, vector body, scalar tail.
+template <int DT, class F>
+__device__ __forceinline__ void warp_scan_segment(const void* base, int64_t start, int len,
+                                                  int lane, F f) {
+  constexpr int VN = Vec<DT>::N;
+  constexpr int ES = 16 / VN;
+  const char* p = reinterpret_cast<const char*>(base) + start * ES;
+  int mis = (int)((reinterpret_cast<uintptr_t>(p) & 15) / ES);
+  int head = mis == 0 ? 0 : VN - mis;
+  if (head > len) head = len;
+  if (lane < head) f(Elem<DT>::load(p, lane));
+  int nvec = (len - head) / VN;
+  const char* body = p + (int64_t)head * ES;
+  for (int v = lane; v < nvec; v += 32) {
+    float x[VN];
+    Vec<DT>::load(body + (int64_t)v * 16, x);
+#pragma unroll
+    for (int i = 0; i < VN; ++i) f(x[i]);
+  }
+  int done = head + nvec * VN;
+  for (int i = done + lane; i < len; i += 32) f(Elem<DT>::load(p, i));
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// out[t, r] = max |a[r, tile t]|
+template <int DT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+abs_max_tiles_kernel(const void* __restrict__ a, int rows, int K, TileTable tt,
+                     void* __restrict__ out) {
+  int64_t seg = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
+  if (seg >= (int64_t)rows * tt.T) return;
+  int r = (int)(seg / tt.T), t = (int)(seg % tt.T);
+  int lo = tt.lo(t), hi = tt.hi(t);
+  float m = 0.0f;
+  warp_scan_segment<DT>(a, (int64_t)r * K + lo, hi - lo, lane, [&](float v) { m = fmaxf(m, fabsf(v)); });
+  m = warp_max(m);
+  if (lane == 0) Elem<DT>::store(out, (int64_t)t * rows + r, m);
+}
+
+// tile_max[t] = max_r amax[t, r]; flags[t] = the "(res > 1).all()" switch of the weight
+// discretiser for that tile.
+template <int DT>
+__global__ void tile_max_kernel(const void* __restrict__ amax, int rows, int quant_type,
+                                float n_states, float* __restrict__ tile_max,
+                                int32_t* __restrict__ flags) {
+  __shared__ float s_max[256];
+  __shared__ int s_all[256];
+  int t = blockIdx.x;
+  float m = 0.0f;
+  int all = 1;
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+    float v = Elem<DT>::load(amax, (int64_t)t * rows + r);
+    m = fmaxf(m, v);
+    if (quant_type == AL_QUANT_DISCRETIZE_PER_CHANNEL) all &= discretize_scale_gt1<DT>(v, n_states) ? 1 : 0;
+  }
+  s_max[threadIdx.x] = m;
+  s_all[threadIdx.x] = all;
+  __syncthreads();
+  for (int o = blockDim.x / 2; o > 0; o >>= 1) {
+    if (threadIdx.x < o) {
+      s_max[threadIdx.x] = fmaxf(s_max[threadIdx.x], s_max[threadIdx.x + o]);
+      s_all[threadIdx.x] &= s_all[threadIdx.x + o];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    tile_max[t] = s_max[0];
+    int f = 0;
+    if (quant_type == AL_QUANT_DISCRETIZE) f = discretize_scale_gt1<DT>(s_max[0], n_states) ? 1 : 0;
+    if (quant_type == AL_QUANT_DISCRETIZE_PER_CHANNEL) f = s_all[0];
+    flags[t] = f;
+  }
+}
+
+// Stage 1 of the per-tile std: (mean, M2) of every (row, tile) segment, two passes over the
+// segment (the second one is served by L1/L2).
+template <int DT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+segment_moments_kernel(const void* __restrict__ a, int rows, int K, TileTable tt,
+                       float* __restrict__ partial) {
+  int64_t seg = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
+  if (seg >= (int64_t)rows * tt.T) return;
+  int r = (int)(seg / tt.T), t = (int)(seg % tt.T);
+  int lo = tt.lo(t), len = tt.hi(t) - lo;
+  float s = 0.0f;
+  warp_scan_segment<DT>(a, (int64_t)r * K + lo, len, lane, [&](float v) { s += v; });
+  float mean = warp_sum(s) / (float)len;
+  float m2 = 0.0f;
+  warp_scan_segment<DT>(a, (int64_t)r * K + lo, len, lane, [&](float v) {
+    float d = v - mean;
+    m2 = fmaf(d, d, m2);
+  });
+  m2 = warp_sum(m2);
+  if (lane == 0) {
+    partial[((int64_t)t * rows + r) * 2] = mean;
+    partial[((int64_t)t * rows + r) * 2 + 1] = m2;
+  }
+}
+
+struct Moments {
+  double n, mean, m2;
+};
+__device__ __forceinline__ Moments merge(const Moments& a, const Moments& b) {
+  if (b.n == 0.0) return a;
+  if (a.n == 0.0) return b;
+  Moments o;
+  o.n = a.n + b.n;
+  double d = b.mean - a.mean;
+  o.mean = a.mean + d * (b.n / o.n);
+  o.m2 = a.m2 + b.m2 + d * d * (a.n * b.n / o.n);
+  return o;
+}
+
+// Stage 2: pairwise merge (Chan et al.) of the row partials of one tile in double, fixed order.
+template <int DT>
+__global__ void merge_moments_kernel(const float* __restrict__ partial, int rows, TileTable tt,
+                                     float* __restrict__ out) {
+  __shared__ Moments sm[256];
+  int t = blockIdx.x;
+  double width = (double)(tt.hi(t) - tt.lo(t));
+  Moments acc = {0.0, 0.0, 0.0};
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+    Moments p = {width, (double)partial[((int64_t)t * rows + r) * 2],
+                 (double)partial[((int64_t)t * rows + r) * 2 + 1]};
+    acc = merge(acc, p);
+  }
+  sm[threadIdx.x] = acc;
+  __syncthreads();
+  for (int o = blockDim.x / 2; o > 0; o >>= 1) {
+    if (threadIdx.x < o) sm[threadIdx.x] = merge(sm[threadIdx.x], sm[threadIdx.x + o]);
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    double var = sm[0].m2 / (sm[0].n - 1.0);
+    out[t] = rnd<DT>((float)sqrt(var));
+  }
+}
+
+// Running mean of init_std_alpha*std over the first init_from_data training calls, on the
+// device (no host read of the counter), then the ranges used by this call are copied out.
+template <int DT>
+__global__ void ir_update_kernel(void* input_range, void* update_idx, const float* std, int T,
+                                 int init_from_data, float init_std_alpha, int do_update,
+                                 void* ir_used) {
+  for (int t = threadIdx.x; t < T; t += blockDim.x) {
+    float ir = Elem<DT>::load(input_range, t);
+    if (do_update) {
+      float idx = Elem<DT>::load(update_idx, t);
+      if (idx < (float)init_from_data) {
+        float sd = std[t];
+        if (sd > 0.0f) {
+          float idx1 = rnd<DT>(fadd(idx, 1.0f));
+          float v = fdiv(fadd(fmul(ir, idx), fmul(init_std_alpha, sd)), idx1);
+          ir = rnd<DT>(v);
+          Elem<DT>::store(update_idx, t, idx1);
+        }
+        ir = fabsf(ir);
+        Elem<DT>::store(input_range, t, ir);
+      }
+    }
+    Elem<DT>::store(ir_used, t, ir);
+  }
+}
+
+// Per-row Gaussian clipping: w[r,:] <- clamp(w[r,:], +-sigma*std(w[r,:])).
+template <int DT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+clip_rows_kernel(void* w, int rows, int cols, float sigma) {
+  int r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  float s = 0.0f;
+  warp_scan_segment<DT>(w, (int64_t)r * cols, cols, lane, [&](float v) { s += v; });
+  float mean = warp_sum(s) / (float)cols;
+  float m2 = 0.0f;
+  warp_scan_segment<DT>(w, (int64_t)r * cols, cols, lane, [&](float v) {
+    float d = v - mean;
+    m2 = fmaf(d, d, m2);
+  });
+  m2 = warp_sum(m2);
+  float sd = rnd<DT>(sqrtf(m2 / (float)(cols - 1)));
+  float lim = rnd<DT>(fmul(sigma, sd));
+  for (int c = lane; c < cols; c += 32) {
+    float v = Elem<DT>::load(w, (int64_t)r * cols + c);
+    Elem<DT>::store(w, (int64_t)r * cols + c, fminf(fmaxf(v, -lim), lim));
+  }
+}
+
+template <int DT>
+__global__ void clip_all_kernel(void* w, int64_t n, float sigma, const float* std_scalar) {
+  float lim = rnd<DT>(fmul(sigma, std_scalar[0]));
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float v = Elem<DT>::load(w, i);
+    Elem<DT>::store(w, i, fminf(fmaxf(v, -lim), lim));
+  }
+}
+
+inline unsigned seg_blocks(int64_t segs) { return (unsigned)((segs + kWarpsPerBlock - 1) / kWarpsPerBlock); }
+
+}  // namespace
+
+#define AL_DISPATCH_DT(dtype, ...)            \
+  if ((dtype) == AL_F32) {                    \
+    constexpr int DT = kF32;                  \
+    __VA_ARGS__;                              \
+  } else {                                    \
+    constexpr int DT = kBF16;                 \
+    __VA_ARGS__;                              \
+  }
+
+int launch_abs_max_tiles(int dtype, const void* a, int rows, int K, const TileTable& tt,
+                         void* out, cudaStream_t s) {
+  int64_t segs = (int64_t)rows * tt.T;
+  AL_DISPATCH_DT(dtype, (abs_max_tiles_kernel<DT><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(a, rows, K, tt, out)));
+  return check_launch("abs_max_tiles");
+}
+
+int launch_tile_max(int dtype, const void* amax, int rows, const TileTable& tt, int quant_type,
+                    float n_states, float* tile_max, int32_t* flags, cudaStream_t s) {
+  AL_DISPATCH_DT(dtype, (tile_max_kernel<DT><<<tt.T, 256, 0, s>>>(amax, rows, quant_type, n_states, tile_max, flags)));
+  return check_launch("tile_max");
+}
+
+int launch_std_tiles(int dtype, const void* a, int rows, int K, const TileTable& tt, float* out,
+                     float* scratch, cudaStream_t s) {
+  int64_t segs = (int64_t)rows * tt.T;
+  AL_DISPATCH_DT(dtype, (segment_moments_kernel<DT><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(a, rows, K, tt, scratch)));
+  int rc = check_launch("segment_moments");
+  if (rc) return rc;
+  AL_DISPATCH_DT(dtype, (merge_moments_kernel<DT><<<tt.T, 256, 0, s>>>(scratch, rows, tt, out)));
+  return check_launch("merge_moments");
+}
+
+int launch_ir_update(int dtype, void* input_range, void* update_idx, const float* std, int T,
+                     int init_from_data, float init_std_alpha, int do_update, void* ir_used,
+                     cudaStream_t s) {
+  AL_DISPATCH_DT(dtype, (ir_update_kernel<DT><<<1, 256, 0, s>>>(input_range, update_idx, std, T, init_from_data, init_std_alpha, do_update, ir_used)));
+  return check_launch("ir_update");
+}
+
+int launch_clip_weights(int dtype, void* w, int rows, int cols, int clip_type, float sigma,
+                        float* scratch, cudaStream_t s) {
+  if (clip_type == AL_CLIP_LAYER_GAUSSIAN_PER_CHANNEL) {
+    AL_DISPATCH_DT(dtype, (clip_rows_kernel<DT><<<seg_blocks(rows), kWarpsPerBlock * 32, 0, s>>>(w, rows, cols, sigma)));
+    return check_launch("clip_rows");
+  }
+  TileTable tt;
+  tt.T = 1;
+  tt.ends[0] = cols;
+  // scratch: [0, 2*rows) row partials, then 1 float for the std
+  int rc = launch_std_tiles(dtype, w, rows, cols, tt, scratch + 2 * (int64_t)rows, scratch, s);
+  if (rc) return rc;
+  int64_t n = (int64_t)rows * cols;
+  unsigned blocks = (unsigned)((n + 1023) / 1024);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  AL_DISPATCH_DT(dtype, (clip_all_kernel<DT><<<blocks, 256, 0, s>>>(w, n, sigma, scratch + 2 * (int64_t)rows)));
+  return check_launch("clip_all");
+}
+
+}  // namespace al

@@ -1,0 +1,184 @@
+/*
+ * analog_b200.h -- C ABI of libanalog_b200.so: the noisy, quantised, input-tiled analog
+ * linear forward/backward for NVIDIA B200 (sm_100a).
+ *
+ * The reference (IBM/aihwkit-lightning) is pure Python: it has no native library and no FFI
+ * for this path.  The functions below therefore replace *Python* call sites of the reference;
+ * each one cites the call site it stands in for (paths inside the reference project,
+ * `P = src/aihwkit_lightning/nn/modules`).
+ *
+ * Conventions
+ *  - every pointer is a device pointer on the current CUDA device unless stated otherwise;
+ *    the caller owns all memory, the library allocates nothing on the device;
+ *  - `stream` is a `cudaStream_t` passed as `void*`; all work is enqueued on it and the
+ *    functions return without synchronising;
+ *  - matrices are row-major and contiguous: x [M,K], w [N,K], out [M,N];
+ *  - "dtype" tensors have the layer's element type (AL_F32 or AL_BF16);
+ *  - return value 0 = success, anything else is an `AlStatus` (see al_status_str);
+ *  - functions are re-entrant; the only process-wide state is a cache of TMA tensor maps.
+ */
+#ifndef ANALOG_B200_H_
+#define ANALOG_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum AlDtype { AL_F32 = 0, AL_BF16 = 1 };
+
+enum AlStatus {
+  AL_OK = 0,
+  AL_ERR_BAD_ARGUMENT = 1,   /* null pointer, non-positive size, inconsistent tile table   */
+  AL_ERR_UNSUPPORTED = 2,    /* configuration outside what the kernels implement           */
+  AL_ERR_CUDA = 3,           /* a CUDA runtime / driver call failed (launch, tensor map)    */
+  AL_ERR_DEVICE_TIMEOUT = 4, /* a bounded device-side wait gave up (al_read_device_error)   */
+  AL_ERR_TOO_LARGE = 5       /* size beyond a stated maximum                               */
+};
+
+/* reference enums, `simulator/parameters/enums.py:46-90` */
+enum AlNoiseType { AL_NOISE_NONE = 0, AL_NOISE_ADD_NORMAL = 1, AL_NOISE_ADD_NORMAL_PER_CHANNEL = 2 };
+enum AlQuantType { AL_QUANT_NONE = 0, AL_QUANT_DISCRETIZE = 1, AL_QUANT_DISCRETIZE_PER_CHANNEL = 2 };
+enum AlClipType {
+  AL_CLIP_NONE = 0,
+  AL_CLIP_LAYER_GAUSSIAN = 1,
+  AL_CLIP_LAYER_GAUSSIAN_PER_CHANNEL = 2,
+  AL_CLIP_LEARNABLE_PER_CHANNEL = 3
+};
+enum AlInputRangeMode { AL_IR_OFF = 0, AL_IR_STATIC = 1, AL_IR_DYNAMIC = 2 };
+
+/* GEMM engine selection.  AUTO picks the tcgen05/TMA kernels whenever dtype and alignment
+ * allow and the SIMT kernels otherwise; the other two force one of them (tests). */
+enum AlEngine { AL_ENGINE_AUTO = 0, AL_ENGINE_SIMT = 1, AL_ENGINE_TCGEN05 = 2 };
+
+/*
+ * Flattened `TorchInferenceRPUConfig` (`simulator/configs/configs.py:27-88`) plus the problem
+ * size.  Field meaning is the reference's; see `simulator/parameters/{io,inference,mapping,
+ * pre_post}.py`.
+ */
+/* Python floats of the configuration are carried as doubles so that derived constants
+ * (out_noise/sqrt(T), max(res, 1/res), ...) are evaluated in double and narrowed to float
+ * once, exactly like the Python reference does. */
+typedef struct AlDesc {
+  int32_t M, K, N, T;        /* rows, in_features, out_features, number of analog tiles     */
+  int32_t dtype;             /* AlDtype                                                     */
+  int32_t training;          /* module.training                                            */
+  int32_t ir_mode;           /* AlInputRangeMode                                           */
+  int32_t init_from_data;    /* InputRangeParameter.init_from_data                         */
+  double init_std_alpha;      /* InputRangeParameter.init_std_alpha                         */
+  double decay;               /* InputRangeParameter.decay                                  */
+  double input_min_percentage;
+  double inp_res;             /* IOParameters.inp_res  (<=0: DAC off)                        */
+  double out_res;             /* IOParameters.out_res  (<=0: ADC quantisation off)           */
+  double out_bound;           /* IOParameters.out_bound (<=0: no clipping)                   */
+  double out_noise;           /* IOParameters.out_noise                                     */
+  int32_t out_noise_per_channel;
+  int32_t noise_type;        /* AlNoiseType                                                 */
+  int32_t quant_type;        /* AlQuantType                                                 */
+  double std_dev;             /* WeightModifierParameter.std_dev                            */
+  double mod_res;             /* WeightModifierParameter.res                                */
+  int32_t clip_type;         /* AlClipType (selects per-channel ADC bounds)                 */
+  int32_t no_rounding;       /* skip rint in every quantiser (`quant_utils.py:60,88`)       */
+  int32_t ref_rounding;      /* bf16: round to bf16 after every op like the reference does */
+  int32_t engine;            /* AlEngine                                                    */
+  int32_t save_for_backward; /* write `keep_mask` (forward) so that al_backward can run     */
+} AlDesc;
+
+/*
+ * Buffers of one forward call.  Nullable entries say so.  Sizes in elements.
+ */
+typedef struct AlForwardArgs {
+  const void* x;             /* [M,K] dtype                                                 */
+  const void* w;             /* [N,K] dtype                                                 */
+  const void* bias;          /* [N] dtype, nullable                                         */
+  void* input_range;         /* [T] dtype, static mode: read, and updated while
+                                 init_from_data is active; null otherwise                  */
+  void* input_range_update_idx; /* [T] dtype, static mode                                   */
+  const int32_t* tile_ends;  /* HOST pointer, [T] cumulative tile ends (last == K)         */
+  void* out;                 /* [M,N] dtype                                                 */
+  /* saved for backward / intermediates (caller-allocated workspace) */
+  void* xq;                  /* [M,K] dtype: DAC output fed to the GEMM. May equal x when
+                                 the input range and the DAC are both off                  */
+  void* ir_rows;             /* [T,M] dtype (dynamic mode) or [T] dtype (static mode: the
+                                 ranges actually used by this call)                        */
+  void* w_amax;              /* [T,N] dtype per-tile per-channel abs-max of w               */
+  void* w_tile_max;          /* [T] float  per-tile abs-max of w + [T] int32 flags behind it */
+  void* w_mod;               /* [N,K] dtype modified weights; may equal w when the modifier
+                                 does nothing in this call                                  */
+  uint32_t* keep_mask;       /* [T, M, ceil(N/32)] bit n%32 of word n/32 = 1 where the ADC
+                                 clamp passes the gradient; nullable if out_bound <= 0     */
+  float* std_scratch;        /* >= al_std_scratch_floats(M, T) floats, static mode with
+                                 init_from_data > 0 in training; nullable otherwise        */
+  /* shared-noise parity mode: standard normals to use instead of the internal generator */
+  const void* w_noise;       /* [N,K] dtype, nullable                                       */
+  const void* out_noise;     /* [T,M,N] dtype, nullable                                     */
+  /* optional debug output */
+  void* codes;               /* [M,K] dtype integer DAC codes, nullable                     */
+  uint64_t seed, offset;     /* counter-based generator: (seed, call counter)              */
+} AlForwardArgs;
+
+typedef struct AlBackwardArgs {
+  const void* grad_out;      /* [M,N] dtype                                                 */
+  const void* x;             /* [M,K] dtype (static mode: clip positions)                   */
+  const void* xq;            /* [M,K] dtype from the forward                                */
+  const void* w_mod;         /* [N,K] dtype from the forward                                */
+  const void* ir_rows;       /* as written by the forward                                   */
+  const uint32_t* keep_mask; /* as written by the forward, nullable if out_bound <= 0      */
+  const int32_t* tile_ends;  /* HOST pointer                                                */
+  void* grad_x;              /* [M,K] dtype, nullable                                       */
+  void* grad_w;              /* [N,K] dtype, nullable                                       */
+  void* grad_bias;           /* [N] dtype, nullable                                         */
+  void* grad_input_range;    /* [T] dtype, nullable (static mode, learn_input_range)       */
+  float* reduce_scratch;     /* >= al_backward_scratch_floats(M,K,N,T) floats               */
+} AlBackwardArgs;
+
+/* Per-tile, per-row abs-max: out[t, r] = max_k |a[r, k]|, k in tile t.  a is [rows, K] dtype,
+ * out [T, rows] dtype.  Replaces `sliced_abs_max` (P/torch_utils/torch_abs_max.py:17-39), the
+ * in-loop `abs().amax(-1)` (P/torch_utils/torch_linear.py:220), the dynamic input range
+ * `abs().max(-1)` (torch_linear.py:156) and the Triton `sliced_fast_abs_max`
+ * (P/triton_utils/triton_abs_max.py:273-327). */
+int al_abs_max_tiles(int32_t dtype, const void* a, int32_t rows, int32_t K,
+                     const int32_t* tile_ends_host, int32_t T, void* out, void* stream);
+
+/* Per-tile unbiased standard deviation over all rows: out[t] = std(a[:, tile t]) as float.
+ * Replaces `values.std()` of the init-from-data update (torch_linear.py:342) and the Triton
+ * `sliced_fast_std` (P/triton_utils/triton_std.py:184-245).  scratch: al_std_scratch_floats. */
+int al_std_tiles(int32_t dtype, const void* a, int32_t rows, int32_t K,
+                 const int32_t* tile_ends_host, int32_t T, float* out, float* scratch,
+                 void* stream);
+int64_t al_std_scratch_floats(int32_t rows, int32_t T);
+
+/* Whole forward of one analog layer.  Replaces `TorchLinear.linear`
+ * (P/torch_utils/torch_linear.py:116-314) and `TritonLinear.forward`
+ * (P/triton_utils/triton_linear.py:446-690). */
+int al_forward(const AlDesc* desc, const AlForwardArgs* args, void* stream);
+
+/* Whole backward.  Replaces what autograd derives from `TorchLinear.linear` (custom pieces:
+ * torch_linear.py:44-54, 81-108; quant_utils.py:113-156) and `TritonLinear.backward`
+ * (triton_linear.py:695-764). */
+int al_backward(const AlDesc* desc, const AlBackwardArgs* args, void* stream);
+int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T);
+
+/* In-place weight clipping w <- clamp(w, +-sigma*std(w)), std over the whole tensor
+ * (AL_CLIP_LAYER_GAUSSIAN) or per row (AL_CLIP_LAYER_GAUSSIAN_PER_CHANNEL).  Replaces
+ * `AnalogLinear.clip_weights` (P/linear.py:269-283) / `_AnalogConvNd.clip_weights`
+ * (P/conv.py:647-663).  scratch: >= 2*rows + 4 floats. */
+int al_clip_weights(int32_t dtype, void* w, int32_t rows, int32_t cols, int32_t clip_type,
+                    float sigma, float* scratch, void* stream);
+
+/* Device-side error word of the tcgen05 kernels (a bounded wait that gave up).  Reads and
+ * clears it; synchronises `stream`.  0 = no error. */
+int al_read_device_error(void* stream, uint32_t* out_code);
+
+/* 1 if the given problem would run on the tcgen05/TMA kernels under AL_ENGINE_AUTO. */
+int al_uses_tcgen05(const AlDesc* desc, const int32_t* tile_ends_host);
+
+const char* al_status_str(int status);
+const char* al_last_error(void); /* thread-local detail of the last non-zero status */
+int al_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ANALOG_B200_H_ */
