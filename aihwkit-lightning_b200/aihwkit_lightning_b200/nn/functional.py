@@ -1,0 +1,304 @@
+"""The analog linear operator: one ``torch.autograd.Function`` around the C-ABI calls.
+
+It stands where the reference has ``TorchLinear.linear`` / ``TritonLinear.apply``
+(`nn/modules/torch_utils/torch_linear.py:116-129`, `nn/modules/triton_utils/triton_linear.py:446-456`):
+same arguments, same results, same in-place update of ``input_range`` /
+``input_range_update_idx`` during the init-from-data phase.  PyTorch only supplies device
+memory and the current stream here.
+"""
+from contextlib import contextmanager
+from typing import List, Optional
+
+import torch
+from torch import Tensor
+
+from .. import _lib
+from ..exceptions import ConfigError
+from ..simulator.enums import WeightClipType, WeightNoiseInjectionType, WeightQuantizationType
+
+_NOISE = {
+    WeightNoiseInjectionType.NONE: 0,
+    WeightNoiseInjectionType.ADD_NORMAL: 1,
+    WeightNoiseInjectionType.ADD_NORMAL_PER_CHANNEL: 2,
+}
+_QUANT = {
+    WeightQuantizationType.NONE: 0,
+    WeightQuantizationType.DISCRETIZE: 1,
+    WeightQuantizationType.DISCRETIZE_PER_CHANNEL: 2,
+}
+_CLIP = {
+    WeightClipType.NONE: 0,
+    WeightClipType.LAYER_GAUSSIAN: 1,
+    WeightClipType.LAYER_GAUSSIAN_PER_CHANNEL: 2,
+    WeightClipType.LEARNABLE_PER_CHANNEL: 3,
+}
+_DTYPE = {torch.float32: _lib.AL_F32, torch.bfloat16: _lib.AL_BF16}
+_ENGINE = {"auto": _lib.AL_ENGINE_AUTO, "simt": _lib.AL_ENGINE_SIMT, "tcgen05": _lib.AL_ENGINE_TCGEN05}
+
+
+class _Settings:
+    """Process-wide switches of the operator (debug and parity aids)."""
+
+    engine = "auto"
+    reference_rounding = True  # bf16: round after every op like the reference's torch path
+    no_rounding = False  # the reference's `_AIHWKIT_NO_ROUNDING` test switch (`quant_utils.py:60`)
+    w_noise: Optional[Tensor] = None  # shared-noise parity mode: [N,K] standard normals
+    out_noise: Optional[Tensor] = None  # [T,M,N] standard normals
+    capture: Optional[dict] = None  # when a dict: filled with the intermediates of each call
+
+
+settings = _Settings()
+
+
+@contextmanager
+def operator_settings(**kwargs):
+    """Temporarily override fields of ``settings`` (engine, reference_rounding, no_rounding,
+    w_noise, out_noise, capture)."""
+    old = {k: getattr(settings, k) for k in kwargs}
+    for k, v in kwargs.items():
+        if not hasattr(_Settings, k):
+            raise AttributeError(k)
+        setattr(settings, k, v)
+    try:
+        yield settings
+    finally:
+        for k, v in old.items():
+            setattr(settings, k, v)
+
+
+def _ptr(t: Optional[Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _next_seed(device):
+    """(seed, offset) from torch's CUDA generator so that ``torch.manual_seed`` governs the
+    analog noise; advances the generator like a kernel drawing 4 values per thread would."""
+    gen = torch.cuda.default_generators[device.index if device.index is not None else torch.cuda.current_device()]
+    seed, offset = gen.initial_seed(), gen.get_offset()
+    gen.set_offset(offset + 4)
+    return seed & 0xFFFFFFFFFFFFFFFF, offset
+
+
+def make_desc(rpu_config, m: int, k: int, n: int, t: int, dtype, training: bool) -> "_lib.AlDesc":
+    fwd, mod, clip = rpu_config.forward, rpu_config.modifier, rpu_config.clip
+    irp = rpu_config.pre_post.input_range
+    if dtype not in _DTYPE:
+        raise ConfigError(f"analog layers run in float32 or bfloat16, got {dtype}")
+    if irp.enable and irp.fast_mode:
+        raise ConfigError("input_range.fast_mode is not implemented by the CUDA path")
+    d = _lib.AlDesc()
+    d.M, d.K, d.N, d.T = m, k, n, t
+    d.dtype = _DTYPE[dtype]
+    d.training = int(training)
+    d.ir_mode = _lib.AL_IR_OFF if not irp.enable else (_lib.AL_IR_DYNAMIC if irp.dynamic else _lib.AL_IR_STATIC)
+    d.init_from_data = int(irp.init_from_data)
+    d.init_std_alpha = float(irp.init_std_alpha)
+    d.decay = float(irp.decay)
+    d.input_min_percentage = float(irp.input_min_percentage)
+    d.inp_res = float(fwd.inp_res)
+    d.out_res = float(fwd.out_res)
+    d.out_bound = float(fwd.out_bound)
+    d.out_noise = float(fwd.out_noise)
+    d.out_noise_per_channel = int(bool(fwd.out_noise_per_channel))
+    d.noise_type = _NOISE[mod.noise_type]
+    d.quant_type = _QUANT[mod.quantization_type]
+    d.std_dev = float(mod.std_dev)
+    d.mod_res = float(mod.res)
+    d.clip_type = _CLIP[clip.type]
+    d.no_rounding = int(settings.no_rounding)
+    d.ref_rounding = int(settings.reference_rounding)
+    d.engine = _ENGINE[settings.engine]
+    d.save_for_backward = 0
+    return d
+
+
+class AnalogLinearFunction(torch.autograd.Function):
+    """out = analog_linear(x, weight, bias) with the noisy / quantised tile model."""
+
+    @staticmethod
+    def forward(ctx, inp, weight, bias, input_range, input_range_update_idx, in_sizes, training,
+                rpu_config):  # type: ignore[override]
+        lib = _lib.load()
+        if not inp.is_cuda or not weight.is_cuda:
+            raise ValueError(
+                "analog layers of this package run on CUDA tensors only (no CPU fallback): "
+                f"input on {inp.device}, weight on {weight.device}"
+            )
+        if inp.dtype != weight.dtype:
+            raise RuntimeError(f"input dtype {inp.dtype} and weight dtype {weight.dtype} differ")
+        n, k = weight.shape
+        if inp.shape[-1] != k:
+            raise RuntimeError(f"input has {inp.shape[-1]} features, the layer expects {k}")
+        x2d = inp.reshape(-1, k).contiguous()
+        m = x2d.shape[0]
+        w = weight.contiguous()
+        t = len(in_sizes)
+        dev, dtype = inp.device, inp.dtype
+        needs_grad = any(ctx.needs_input_grad[:4])
+        desc = make_desc(rpu_config, m, k, n, t, dtype, training)
+        desc.save_for_backward = int(needs_grad)
+        ends = _lib.tile_ends_array(in_sizes)
+        static = desc.ir_mode == _lib.AL_IR_STATIC
+        if static:
+            assert input_range is not None, "Input range must be provided"
+            assert input_range_update_idx is not None, "Input range update index must be provided"
+        if m == 0:
+            ctx.empty = True
+            return inp.new_zeros(*inp.shape[:-1], n) + (bias if bias is not None else 0)
+        ctx.empty = False
+
+        with torch.cuda.device(dev):
+            out = torch.empty(m, n, device=dev, dtype=dtype)
+            args = _lib.AlForwardArgs()
+            args.x, args.w, args.bias, args.out = _ptr(x2d), _ptr(w), _ptr(bias), _ptr(out)
+            args.tile_ends = ends
+            ir_data = iridx_data = None
+            if static:
+                ir_data = input_range.data if input_range.is_contiguous() else input_range.data.contiguous()
+                iridx_data = input_range_update_idx
+                args.input_range, args.input_range_update_idx = _ptr(ir_data), _ptr(iridx_data)
+            xq = x2d
+            ir_rows = None
+            if desc.ir_mode != _lib.AL_IR_OFF:
+                xq = torch.empty_like(x2d)
+                ir_rows = torch.empty((t, m) if not static else (t,), device=dev, dtype=dtype)
+            args.xq, args.ir_rows = _ptr(xq), _ptr(ir_rows)
+            w_amax = torch.empty(t, n, device=dev, dtype=dtype)
+            w_tile_max = torch.empty(2 * t, device=dev, dtype=torch.float32)
+            args.w_amax, args.w_tile_max = _ptr(w_amax), _ptr(w_tile_max)
+            modifies = desc.quant_type != 0 or (training and desc.noise_type != 0)
+            w_mod = torch.empty_like(w) if modifies else w
+            args.w_mod = _ptr(w_mod)
+            keep_mask = None
+            if desc.out_bound > 0 and needs_grad:
+                keep_mask = torch.empty(t, m, (n + 31) // 32, device=dev, dtype=torch.int32)
+            args.keep_mask = _ptr(keep_mask)
+            std_scratch = None
+            if static and training and desc.init_from_data > 0:
+                std_scratch = torch.empty(lib.al_std_scratch_floats(m, t), device=dev, dtype=torch.float32)
+            args.std_scratch = _ptr(std_scratch)
+            w_noise, out_noise = settings.w_noise, settings.out_noise
+            if w_noise is not None:
+                w_noise = w_noise.to(device=dev, dtype=dtype).contiguous()
+                assert w_noise.shape == w.shape, "replayed weight noise must be [N,K]"
+            if out_noise is not None:
+                out_noise = out_noise.to(device=dev, dtype=dtype).contiguous()
+                assert out_noise.numel() == t * m * n, "replayed output noise must be [T,M,N]"
+            args.w_noise, args.out_noise = _ptr(w_noise), _ptr(out_noise)
+            codes = None
+            if settings.capture is not None and desc.ir_mode != _lib.AL_IR_OFF:
+                codes = torch.empty_like(x2d)
+            args.codes = _ptr(codes)
+            if training and (desc.noise_type != 0 or desc.out_noise > 0):
+                args.seed, args.offset = _next_seed(dev)
+            _lib.check(lib.al_forward(desc, args, _stream(dev)))
+            if static and ir_data is not input_range.data:
+                input_range.data.copy_(ir_data)
+
+        if settings.capture is not None:
+            settings.capture.update(
+                codes=codes, xq=xq, ir_rows=ir_rows, w_amax=w_amax, w_tile_max=w_tile_max[:t],
+                w_mod=w_mod, keep_mask=keep_mask,
+                uses_tcgen05=bool(lib.al_uses_tcgen05(desc, ends)),
+            )
+        ctx.desc, ctx.in_sizes = desc, list(in_sizes)
+        ctx.shape = tuple(inp.shape)
+        ctx.has_bias = bias is not None
+        ctx.ir_needs_grad = static and input_range is not None and input_range.requires_grad
+        if needs_grad:
+            ctx.save_for_backward(x2d if static else None, xq, w_mod, ir_rows, keep_mask)
+        return out.view(*inp.shape[:-1], n)
+
+    @staticmethod
+    def backward(ctx, grad_out):  # type: ignore[override]
+        if ctx.empty:
+            return (None,) * 8
+        lib = _lib.load()
+        x2d, xq, w_mod, ir_rows, keep_mask = ctx.saved_tensors
+        desc = ctx.desc
+        m, k, n, t = desc.M, desc.K, desc.N, desc.T
+        dev, dtype = grad_out.device, xq.dtype
+        g = grad_out.reshape(m, n).to(dtype).contiguous()
+        need_x, need_w, need_b, need_ir = ctx.needs_input_grad[:4]
+        need_b = need_b and ctx.has_bias
+        need_ir = need_ir and ctx.ir_needs_grad
+        with torch.cuda.device(dev):
+            args = _lib.AlBackwardArgs()
+            ends = _lib.tile_ends_array(ctx.in_sizes)
+            args.tile_ends = ends
+            args.grad_out, args.x, args.xq, args.w_mod = _ptr(g), _ptr(x2d), _ptr(xq), _ptr(w_mod)
+            args.ir_rows, args.keep_mask = _ptr(ir_rows), _ptr(keep_mask)
+            grad_x = torch.empty(m, k, device=dev, dtype=dtype) if (need_x or need_ir) else None
+            grad_w = torch.empty(n, k, device=dev, dtype=dtype) if need_w else None
+            grad_b = torch.empty(n, device=dev, dtype=dtype) if need_b else None
+            grad_ir = torch.empty(t, device=dev, dtype=dtype) if need_ir else None
+            scratch = torch.empty(lib.al_backward_scratch_floats(m, k, n, t), device=dev, dtype=torch.float32)
+            args.grad_x, args.grad_w, args.grad_bias = _ptr(grad_x), _ptr(grad_w), _ptr(grad_b)
+            args.grad_input_range, args.reduce_scratch = _ptr(grad_ir), _ptr(scratch)
+            _lib.check(lib.al_backward(desc, args, _stream(dev)))
+        if grad_x is not None:
+            grad_x = grad_x.view(ctx.shape) if need_x else None
+        return grad_x, grad_w, grad_b, grad_ir, None, None, None, None
+
+
+def analog_linear(inp: Tensor, weight: Tensor, bias: Optional[Tensor], input_range: Optional[Tensor],
+                  input_range_update_idx: Optional[Tensor], in_sizes: List[int], training: bool,
+                  rpu_config) -> Tensor:
+    """Functional form used by ``AnalogLinear`` and ``AnalogConv2d``."""
+    return AnalogLinearFunction.apply(inp, weight, bias, input_range, input_range_update_idx,
+                                      in_sizes, training, rpu_config)
+
+
+def sliced_abs_max(in_sizes: List[int], weights: Tensor) -> Tensor:
+    """Per-tile, per-row abs-max ``[T, rows]`` of a 2-D CUDA tensor
+    (`nn/modules/torch_utils/torch_abs_max.py:17-39`)."""
+    lib = _lib.load()
+    assert weights.ndim == 2, "Weight must be 2D"
+    if not weights.is_cuda:
+        raise ValueError("sliced_abs_max runs on CUDA tensors only")
+    w = weights.detach().contiguous()
+    out = torch.empty(len(in_sizes), w.shape[0], device=w.device, dtype=w.dtype)
+    with torch.cuda.device(w.device):
+        _lib.check(lib.al_abs_max_tiles(_DTYPE[w.dtype], w.data_ptr(), w.shape[0], w.shape[1],
+                                        _lib.tile_ends_array(in_sizes), len(in_sizes), out.data_ptr(),
+                                        _stream(w.device)))
+    return out
+
+
+def sliced_std(in_sizes: List[int], values: Tensor) -> Tensor:
+    """Per-tile unbiased std over all rows ``[T]`` (float32) of a 2-D CUDA tensor."""
+    lib = _lib.load()
+    assert values.ndim == 2, "values must be 2D"
+    v = values.detach().contiguous()
+    t = len(in_sizes)
+    out = torch.empty(t, device=v.device, dtype=torch.float32)
+    scratch = torch.empty(lib.al_std_scratch_floats(v.shape[0], t), device=v.device, dtype=torch.float32)
+    with torch.cuda.device(v.device):
+        _lib.check(lib.al_std_tiles(_DTYPE[v.dtype], v.data_ptr(), v.shape[0], v.shape[1],
+                                    _lib.tile_ends_array(in_sizes), t, out.data_ptr(), scratch.data_ptr(),
+                                    _stream(v.device)))
+    return out
+
+
+def clip_weights_(weight: Tensor, clip_type: WeightClipType, sigma: float) -> None:
+    """In-place Gaussian weight clipping of a CUDA parameter (`nn/modules/linear.py:269-283`)."""
+    if clip_type in (WeightClipType.NONE, WeightClipType.LEARNABLE_PER_CHANNEL):
+        return
+    assert sigma > 0, "Clip sigma must be greater than 0"
+    if clip_type not in (WeightClipType.LAYER_GAUSSIAN, WeightClipType.LAYER_GAUSSIAN_PER_CHANNEL):
+        raise ValueError(f"Unknown clip type {clip_type}")
+    lib = _lib.load()
+    if not weight.is_cuda:
+        raise ValueError("clip_weights runs on CUDA tensors only")
+    w = weight.data
+    assert w.is_contiguous(), "weight must be contiguous"
+    rows = w.shape[0]
+    cols = w.numel() // rows
+    scratch = torch.empty(2 * rows + 8, device=w.device, dtype=torch.float32)
+    with torch.cuda.device(w.device):
+        _lib.check(lib.al_clip_weights(_DTYPE[w.dtype], w.data_ptr(), rows, cols, _CLIP[clip_type],
+                                       float(sigma), scratch.data_ptr(), _stream(w.device)))

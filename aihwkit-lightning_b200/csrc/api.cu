@@ -411,3 +411,87 @@ int al_read_device_error(void* stream, uint32_t* out_code) {
 }
 
 }  // extern "C"
+
+// ---- launch accounting / per-kernel event timing ------------------------------------------
+#include <mutex>
+#include <vector>
+
+namespace al {
+namespace {
+struct EventPair {
+  cudaEvent_t start, stop;
+  int cls;
+};
+std::mutex g_prof_mu;
+bool g_prof_on = false;
+AlProfileEntry g_prof[AL_K_COUNT];
+std::vector<EventPair*> g_pending, g_free;
+}  // namespace
+
+ProfScope::ProfScope(int kernel_class, cudaStream_t s, int launches)
+    : cls(kernel_class), stream(s), slot(nullptr) {
+  std::lock_guard<std::mutex> lock(g_prof_mu);
+  g_prof[cls].launches += launches;
+  if (!g_prof_on) return;
+  EventPair* ep = nullptr;
+  if (!g_free.empty()) {
+    ep = g_free.back();
+    g_free.pop_back();
+  } else {
+    ep = new EventPair();
+    if (cudaEventCreate(&ep->start) != cudaSuccess || cudaEventCreate(&ep->stop) != cudaSuccess) {
+      delete ep;
+      cudaGetLastError();
+      return;
+    }
+  }
+  ep->cls = cls;
+  cudaEventRecord(ep->start, stream);
+  slot = ep;
+}
+
+ProfScope::~ProfScope() {
+  if (!slot) return;
+  EventPair* ep = static_cast<EventPair*>(slot);
+  cudaEventRecord(ep->stop, stream);
+  std::lock_guard<std::mutex> lock(g_prof_mu);
+  g_pending.push_back(ep);
+}
+}  // namespace al
+
+extern "C" {
+
+int al_profile_enable(int on) {
+  std::lock_guard<std::mutex> lock(g_prof_mu);
+  g_prof_on = on != 0;
+  return AL_OK;
+}
+
+int al_profile_read(AlProfileEntry* out, int reset) {
+  if (!out) return AL_ERR_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lock(g_prof_mu);
+  for (EventPair* ep : g_pending) {
+    float ms = 0.0f;
+    if (cudaEventSynchronize(ep->stop) == cudaSuccess &&
+        cudaEventElapsedTime(&ms, ep->start, ep->stop) == cudaSuccess) {
+      g_prof[ep->cls].timed += 1;
+      g_prof[ep->cls].total_ms += ms;
+    } else {
+      cudaGetLastError();
+    }
+    g_free.push_back(ep);
+  }
+  g_pending.clear();
+  memcpy(out, g_prof, sizeof(g_prof));
+  if (reset) memset(g_prof, 0, sizeof(g_prof));
+  return AL_OK;
+}
+
+const char* al_kernel_class_name(int k) {
+  static const char* names[AL_K_COUNT] = {
+      "abs_max_tiles", "tile_max", "std_tiles", "ir_update", "dac", "weight_modify",
+      "fwd_gemm", "dgrad_gemm", "wgrad_gemm", "bias_grad", "ir_backward", "clip_weights"};
+  return (k >= 0 && k < AL_K_COUNT) ? names[k] : "?";
+}
+
+}  // extern "C"

@@ -119,6 +119,7 @@ __global__ void static_ir_final_kernel(const float* __restrict__ partial,
 
 int launch_bias_grad(int dtype, const void* g, int M, int N, void* grad_bias, float* scratch,
                      cudaStream_t s) {
+  ProfScope prof(AL_K_BIAS_GRAD, s, 2);
   int chunks = M < kBiasChunks ? M : kBiasChunks;
   int rows_per_chunk = (M + chunks - 1) / chunks;
   chunks = (M + rows_per_chunk - 1) / rows_per_chunk;
@@ -136,6 +137,7 @@ int launch_bias_grad(int dtype, const void* g, int M, int N, void* grad_bias, fl
 int launch_static_ir_backward(int dtype, const void* x, const void* ir_used, void* grad_x, int M,
                               int K, const TileTable& tt, float decay, float input_min_percentage,
                               void* grad_ir, float* scratch, cudaStream_t s) {
+  ProfScope prof(AL_K_IR_BACKWARD, s, grad_ir ? 2 : 1);
   int64_t segs = (int64_t)M * tt.T;
   unsigned blocks = (unsigned)((segs + 7) / 8);
   if (dtype == AL_F32) {

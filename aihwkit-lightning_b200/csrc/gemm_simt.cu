@@ -216,6 +216,7 @@ inline int max_tile_width(const TileTable& tt) {
 
 int launch_fwd_simt(int dtype, int round_dt, const void* xq, const void* w_mod, int K,
                     const TileTable& tt, const FwdEpilogueParams& ep, void* out, cudaStream_t s) {
+  ProfScope prof(AL_K_FWD_GEMM, s);
   dim3 grid((ep.N + BN - 1) / BN, (ep.M + BM - 1) / BM);
   if (dtype == AL_F32)
     fwd_simt_kernel<kF32, kF32><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out);
@@ -229,6 +230,7 @@ int launch_fwd_simt(int dtype, int round_dt, const void* xq, const void* w_mod, 
 int launch_dgrad_simt(int dtype, const void* g, const void* w_mod, const uint32_t* keep_mask,
                       int mask_words, int M, int K, int N, const TileTable& tt, void* grad_x,
                       cudaStream_t s) {
+  ProfScope prof(AL_K_DGRAD_GEMM, s);
   dim3 grid((max_tile_width(tt) + BN - 1) / BN, (M + BM - 1) / BM, tt.T);
   if (dtype == AL_F32)
     bwd_simt_kernel<kF32, false><<<grid, kThreads, 0, s>>>(g, w_mod, keep_mask, mask_words, M, K, N, tt, grad_x);
@@ -240,6 +242,7 @@ int launch_dgrad_simt(int dtype, const void* g, const void* w_mod, const uint32_
 int launch_wgrad_simt(int dtype, const void* g, const void* xq, const uint32_t* keep_mask,
                       int mask_words, int M, int K, int N, const TileTable& tt, void* grad_w,
                       cudaStream_t s) {
+  ProfScope prof(AL_K_WGRAD_GEMM, s);
   dim3 grid((max_tile_width(tt) + BN - 1) / BN, (N + BM - 1) / BM, tt.T);
   if (dtype == AL_F32)
     bwd_simt_kernel<kF32, true><<<grid, kThreads, 0, s>>>(g, xq, keep_mask, mask_words, M, K, N, tt, grad_w);

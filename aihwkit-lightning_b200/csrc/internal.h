@@ -47,6 +47,17 @@ struct FwdEpilogueParams {
 };
 
 void set_error(const char* fmt, ...);
+
+// Launch accounting: every launch_* function opens one scope.  Launch counts are always kept;
+// when profiling is enabled (al_profile_enable) the scope also brackets the launches with CUDA
+// events on the launching stream.
+struct ProfScope {
+  ProfScope(int kernel_class, cudaStream_t s, int launches = 1);
+  ~ProfScope();
+  int cls;
+  cudaStream_t stream;
+  void* slot;
+};
 int check_launch(const char* what);
 
 // ---- reductions (reduce_kernels.cu) -------------------------------------------------------

@@ -179,6 +179,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 int launch_dac(int dtype, const void* x, int M, int K, const TileTable& tt, int ir_mode,
                const void* ir_static, float inp_res, int no_rounding, void* xq, void* ir_rows,
                void* codes, cudaStream_t s) {
+  ProfScope prof(AL_K_DAC, s);
   int64_t segs = (int64_t)M * tt.T;
   int aligned = aligned16(x) && aligned16(xq);
   if (dtype == AL_F32)
@@ -193,6 +194,7 @@ int launch_weight_modify(int dtype, const void* w, int N, int K, const TileTable
                          int quant_type, float n_states, float max_state, int noise_type,
                          float std_dev, const void* w_noise, uint64_t seed, uint64_t offset,
                          int no_rounding, void* w_mod, cudaStream_t s) {
+  ProfScope prof(AL_K_WEIGHT_MODIFY, s);
   int64_t segs = (int64_t)N * tt.T;
   if (dtype == AL_F32)
     weight_modify_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, flags, quant_type, n_states, max_state, noise_type, std_dev, w_noise, seed, offset, no_rounding, w_mod);

@@ -263,6 +263,7 @@ inline unsigned seg_blocks(int64_t segs) { return (unsigned)((segs + kWarpsPerBl
 
 int launch_abs_max_tiles(int dtype, const void* a, int rows, int K, const TileTable& tt,
                          void* out, cudaStream_t s) {
+  ProfScope prof(AL_K_ABS_MAX, s);
   int64_t segs = (int64_t)rows * tt.T;
   AL_DISPATCH_DT(dtype, (abs_max_tiles_kernel<DT><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(a, rows, K, tt, out)));
   return check_launch("abs_max_tiles");
@@ -270,12 +271,14 @@ int launch_abs_max_tiles(int dtype, const void* a, int rows, int K, const TileTa
 
 int launch_tile_max(int dtype, const void* amax, int rows, const TileTable& tt, int quant_type,
                     float n_states, float* tile_max, int32_t* flags, cudaStream_t s) {
+  ProfScope prof(AL_K_TILE_MAX, s);
   AL_DISPATCH_DT(dtype, (tile_max_kernel<DT><<<tt.T, 256, 0, s>>>(amax, rows, quant_type, n_states, tile_max, flags)));
   return check_launch("tile_max");
 }
 
 int launch_std_tiles(int dtype, const void* a, int rows, int K, const TileTable& tt, float* out,
                      float* scratch, cudaStream_t s) {
+  ProfScope prof(AL_K_STD, s, 2);
   int64_t segs = (int64_t)rows * tt.T;
   AL_DISPATCH_DT(dtype, (segment_moments_kernel<DT><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(a, rows, K, tt, scratch)));
   int rc = check_launch("segment_moments");
@@ -287,12 +290,14 @@ int launch_std_tiles(int dtype, const void* a, int rows, int K, const TileTable&
 int launch_ir_update(int dtype, void* input_range, void* update_idx, const float* std, int T,
                      int init_from_data, float init_std_alpha, int do_update, void* ir_used,
                      cudaStream_t s) {
+  ProfScope prof(AL_K_IR_UPDATE, s);
   AL_DISPATCH_DT(dtype, (ir_update_kernel<DT><<<1, 256, 0, s>>>(input_range, update_idx, std, T, init_from_data, init_std_alpha, do_update, ir_used)));
   return check_launch("ir_update");
 }
 
 int launch_clip_weights(int dtype, void* w, int rows, int cols, int clip_type, float sigma,
                         float* scratch, cudaStream_t s) {
+  ProfScope prof(AL_K_CLIP, s);
   if (clip_type == AL_CLIP_LAYER_GAUSSIAN_PER_CHANNEL) {
     AL_DISPATCH_DT(dtype, (clip_rows_kernel<DT><<<seg_blocks(rows), kWarpsPerBlock * 32, 0, s>>>(w, rows, cols, sigma)));
     return check_launch("clip_rows");

@@ -174,6 +174,26 @@ int al_read_device_error(void* stream, uint32_t* out_code);
 /* 1 if the given problem would run on the tcgen05/TMA kernels under AL_ENGINE_AUTO. */
 int al_uses_tcgen05(const AlDesc* desc, const int32_t* tile_ends_host);
 
+/* Launch accounting and optional per-kernel timing (no counterpart in the reference, whose
+ * only timing aids are ad-hoc `triton.testing.do_bench` scripts, P/triton_utils/triton_abs_max.py:358-404).
+ * Launch counts are always kept.  With profiling enabled every launch is bracketed by CUDA
+ * events on its stream; al_profile_read waits for the recorded events (host-side wait only),
+ * adds their elapsed times to the totals, copies AL_K_COUNT entries to `out` and optionally
+ * resets the totals. */
+enum AlKernelClass {
+  AL_K_ABS_MAX = 0, AL_K_TILE_MAX, AL_K_STD, AL_K_IR_UPDATE, AL_K_DAC, AL_K_WEIGHT_MODIFY,
+  AL_K_FWD_GEMM, AL_K_DGRAD_GEMM, AL_K_WGRAD_GEMM, AL_K_BIAS_GRAD, AL_K_IR_BACKWARD, AL_K_CLIP,
+  AL_K_COUNT
+};
+typedef struct AlProfileEntry {
+  int64_t launches;   /* kernel launches issued for this class                              */
+  int64_t timed;      /* scopes that were timed with events                                 */
+  double total_ms;    /* summed event time of the timed scopes                              */
+} AlProfileEntry;
+int al_profile_enable(int on);
+int al_profile_read(AlProfileEntry* out, int reset);
+const char* al_kernel_class_name(int kernel_class);
+
 const char* al_status_str(int status);
 const char* al_last_error(void); /* thread-local detail of the last non-zero status */
 int al_version(void);

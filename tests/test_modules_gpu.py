@@ -1,0 +1,140 @@
+"""Module-level behaviour on the GPU: API surface, conv path, optimizer hook, checkpoints,
+internal noise generator statistics."""
+import math
+
+import pytest
+import torch
+
+import analog_oracle as O
+import cases as C
+from util import NS
+
+pytestmark = pytest.mark.gpu
+
+
+def make_cfg(**kw):
+    case = dict(C.DEFAULTS)
+    case.update(kw)
+    return C.build_rpu_config(NS, case), case
+
+
+def test_cpu_tensor_is_rejected():
+    from aihwkit_lightning_b200.nn import AnalogLinear
+
+    rpu, _ = make_cfg()
+    layer = AnalogLinear(8, 4, rpu_config=rpu)
+    with pytest.raises(ValueError):
+        layer(torch.randn(2, 8))
+
+
+def test_missing_rpu_config():
+    from aihwkit_lightning_b200.nn import AnalogLinear
+
+    with pytest.raises(ValueError):
+        AnalogLinear(8, 4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_conv2d_matches_oracle_on_unfolded_patches(dtype):
+    from aihwkit_lightning_b200.nn import AnalogConv2d
+
+    rpu, case = make_cfg(ir_dynamic=True, max_input_size=10, out_bound=4.0, out_res=254.0, training=False)
+    torch.manual_seed(0)
+    conv = AnalogConv2d(4, 6, 3, padding=1, rpu_config=rpu).to(device="cuda", dtype=dtype).eval()
+    x = torch.randn(2, 4, 9, 9).to(dtype)
+    got = conv(x.cuda())
+    patches = torch.nn.functional.unfold(x.float(), 3, padding=1).transpose(1, 2).to(dtype)
+    rec = O.forward(patches, conv.weight.detach().cpu().view(6, -1), conv.bias.detach().cpu(), None, None,
+                    None, None, conv.in_sizes, False, rpu)
+    want = rec.out.transpose(1, 2).reshape(2, 6, 9, 9)
+    if dtype == torch.float32:
+        assert torch.allclose(got.cpu(), want, rtol=1e-5, atol=1e-5)
+    else:
+        assert (got.cpu().float() - want.float()).norm() <= 1e-2 * want.float().norm()
+
+
+def test_conv2d_backward_runs_and_matches_fp32():
+    from aihwkit_lightning_b200.nn import AnalogConv2d
+
+    rpu, _ = make_cfg(ir_enable=False, inp_res=-1.0, max_input_size=-1)
+    torch.manual_seed(0)
+    conv = AnalogConv2d(3, 5, 3, stride=2, padding=1, rpu_config=rpu).cuda()
+    ref = AnalogConv2d.to_digital(conv)
+    x = torch.randn(4, 3, 8, 8, device="cuda", requires_grad=True)
+    x2 = x.detach().clone().requires_grad_(True)
+    conv(x).square().sum().backward()
+    ref(x2).square().sum().backward()
+    assert torch.allclose(x.grad, x2.grad, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(conv.weight.grad, ref.weight.grad, rtol=1e-4, atol=1e-4)
+
+
+def test_optimizer_hook_clips_weights():
+    from aihwkit_lightning_b200.nn import AnalogLinear
+    from aihwkit_lightning_b200.optim import AnalogOptimizer
+
+    rpu, _ = make_cfg(clip_type="LayerGaussian", clip_sigma=1.0, ir_dynamic=True)
+    layer = AnalogLinear(64, 32, rpu_config=rpu).cuda()
+    opt = AnalogOptimizer(torch.optim.SGD, layer.analog_layers, layer.parameters(), lr=0.0)
+    before = layer.weight.detach().clone()
+    layer(torch.randn(4, 64, device="cuda")).sum().backward()
+    opt.step()
+    lim = before.std().item()
+    assert layer.weight.abs().max().item() <= lim * (1 + 1e-5)
+    assert torch.equal(layer.weight.detach().cpu(), O.clip_weights(before.cpu(), "LayerGaussian", 1.0))
+
+
+def test_state_dict_round_trip_and_reference_key_names(tmp_path):
+    from aihwkit_lightning_b200.nn import AnalogLinear
+
+    rpu, _ = make_cfg()
+    layer = AnalogLinear(40, 24, rpu_config=rpu).cuda()
+    assert list(layer.state_dict().keys()) == [
+        "weight", "bias", "input_range", "input_range_update_idx", "x_min", "x_max"]
+    path = tmp_path / "ckpt.pt"
+    torch.save(layer.state_dict(), path)
+    other = AnalogLinear(40, 24, rpu_config=make_cfg()[0]).cuda()
+    other.load_state_dict(torch.load(path, weights_only=False))
+    x = torch.randn(3, 40, device="cuda")
+    layer.eval(), other.eval()
+    assert torch.equal(layer(x), other(x))
+
+
+def test_internal_generator_noise_moments():
+    """Noise from the library's own counter-based generator: statistics as in the reference's
+    test of its Triton noise (`tests/test_correctness_triton_mode.py:192-218`)."""
+    from aihwkit_lightning_b200.nn import AnalogLinear
+
+    rpu, _ = make_cfg(ir_dynamic=True, out_noise=0.1, max_input_size=128, inp_res=254.0)
+    torch.manual_seed(0)
+    layer = AnalogLinear(256, 512, bias=False, rpu_config=rpu).cuda()
+    x = torch.randn(512, 256, device="cuda")
+    layer.eval()
+    clean = layer(x)
+    layer.train()
+    noisy1, noisy2 = layer(x), layer(x)
+    delta = (noisy1 - clean).cpu()
+    assert not torch.equal(noisy1, noisy2)
+    # expected per-element std: sqrt(sum_t (wmax_t * out_noise/sqrt(T) * ir_t[m])^2)
+    w, xs = layer.weight.detach().cpu(), x.cpu()
+    var = torch.zeros(512)
+    for t in range(2):
+        wmax = w[:, 128 * t:128 * (t + 1)].abs().max()
+        ir = xs[:, 128 * t:128 * (t + 1)].abs().amax(1)
+        var += (wmax * 0.1 / math.sqrt(2) * ir) ** 2
+    z = delta / var.sqrt()[:, None]
+    assert abs(z.mean().item()) < 0.01
+    assert abs(z.std().item() - 1.0) < 0.01
+
+    rpu2, _ = make_cfg(ir_dynamic=True, noise_type="AddNormalPerChannel", std_dev=0.1, max_input_size=128)
+    layer2 = AnalogLinear(256, 512, bias=False, rpu_config=rpu2).cuda().train()
+    from aihwkit_lightning_b200.nn import functional as F
+    cap = {}
+    with F.operator_settings(capture=cap):
+        layer2(x)
+    dw = (cap["w_mod"] - layer2.weight.detach()).cpu()
+    w2 = layer2.weight.detach().cpu()
+    scale = torch.cat([w2[:, :128].abs().amax(1, keepdim=True).expand(-1, 128),
+                       w2[:, 128:].abs().amax(1, keepdim=True).expand(-1, 128)], 1) * 0.1
+    z = dw / scale
+    assert abs(z.mean().item()) < 0.01
+    assert abs(z.std().item() - 1.0) < 0.01
