@@ -55,6 +55,7 @@ class AlBackwardArgs(Structure):
 
 
 AL_K_COUNT = 12
+AL_STD_STATIC_MAX_SEGMENTS = 262144
 
 
 class AlProfileEntry(Structure):
@@ -66,6 +67,7 @@ SYMBOLS = {
     "al_abs_max_tiles": (c_int32, [c_int32, c_void_p, c_int32, c_int32, POINTER(c_int32), c_int32, c_void_p, c_void_p]),
     "al_std_tiles": (c_int32, [c_int32, c_void_p, c_int32, c_int32, POINTER(c_int32), c_int32, c_void_p, c_void_p, c_void_p]),
     "al_std_scratch_floats": (c_int64, [c_int32, c_int32]),
+    "al_std_tiles_static": (c_int32, [c_int32, c_void_p, c_int32, c_int32, POINTER(c_int32), c_int32, c_void_p, c_void_p]),
     "al_forward": (c_int32, [POINTER(AlDesc), POINTER(AlForwardArgs), c_void_p]),
     "al_backward": (c_int32, [POINTER(AlDesc), POINTER(AlBackwardArgs), c_void_p]),
     "al_backward_scratch_floats": (c_int64, [c_int32, c_int32, c_int32, c_int32]),

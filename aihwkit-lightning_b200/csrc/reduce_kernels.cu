@@ -3,6 +3,8 @@
 // Gaussian weight clipping.  All are HBM-bound scans: one warp per (row, tile) segment,
 // 128-bit loads on the aligned body of the segment, warp-shuffle reductions, and a fixed
 // merge order (no floating-point atomics), so results are bitwise repeatable.
+#include <mutex>
+
 #include "analog_math.cuh"
 #include "internal.h"
 
@@ -316,3 +318,86 @@ int launch_clip_weights(int dtype, void* w, int rows, int cols, int clip_type, f
 }
 
 }  // namespace al
+
+// ---- per-tile std without a caller-supplied scratch buffer ---------------------------------
+//
+// al_std_tiles needs 2 floats of scratch per (row, tile) segment for its stage-1 partials and
+// asks the caller to bring that buffer.  Some hosts of this library cannot produce one at the
+// point where they want the statistic: an inference server that hands each plugin a fixed
+// device arena at start-up and forbids later cudaMalloc calls (they synchronise the whole
+// device and would stall its other streams), or a calibration hook that runs inside someone
+// else's forward pass and owns no allocator at all.  For them the partials live in the array
+// below, which is part of the library image: every GPU that loads the library holds these
+// 2 MiB until the process exits, whether the entry point is used or not.
+//
+// All calls on a device share the array and it keeps whatever the previous call left in it.
+// Nothing in it has to start at zero: stage 1 overwrites every slot stage 2 reads.  Two calls
+// whose kernels overlap on the GPU (different streams, or different host threads on
+// different streams) would overwrite each other's partials -- serialise them.
+static __device__ __align__(256) float g_std_static_scratch[2 * AL_STD_STATIC_MAX_SEGMENTS];
+
+namespace al {
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+float* g_static_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
+}  // namespace
+}  // namespace al
+
+extern "C" int al_std_tiles_static(int32_t dtype, const void* a, int32_t rows, int32_t K,
+                                   const int32_t* tile_ends_host, int32_t T, float* out,
+                                   void* stream) {
+  using namespace al;
+  if (dtype != AL_F32 && dtype != AL_BF16) {
+    set_error("al_std_tiles_static: unknown dtype %d", dtype);
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  if (!a || !out || !tile_ends_host || rows < 1 || K < 1 || T < 1) {
+    set_error("al_std_tiles_static: null pointer or empty matrix");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  if (T > kMaxTiles || (int64_t)rows * T > (int64_t)AL_STD_STATIC_MAX_SEGMENTS) {
+    set_error("al_std_tiles_static: rows*T = %lld exceeds the built-in scratch of %d segments "
+              "(use al_std_tiles with your own scratch buffer)",
+              (long long)rows * T, (int)AL_STD_STATIC_MAX_SEGMENTS);
+    return AL_ERR_TOO_LARGE;
+  }
+  TileTable tt;
+  tt.T = T;
+  int prev = 0;
+  for (int t = 0; t < T; ++t) {
+    if (tile_ends_host[t] <= prev) {
+      set_error("al_std_tiles_static: tile ends must be strictly increasing");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    tt.ends[t] = prev = tile_ends_host[t];
+  }
+  if (prev != K) {
+    set_error("al_std_tiles_static: last tile end %d != K=%d", prev, K);
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  // Set-up, once per device, with that device current: host code cannot use the array's name as
+  // a device address, it has to ask the runtime for it.
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_error("al_std_tiles_static: cannot identify the current device");
+    cudaGetLastError();
+    return AL_ERR_CUDA;
+  }
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, g_std_static_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        set_error("al_std_tiles_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        cudaGetLastError();
+        return AL_ERR_CUDA;
+      }
+      g_static_ptr[dev] = static_cast<float*>(p);
+    }
+    scratch = g_static_ptr[dev];
+  }
+  return launch_std_tiles(dtype, a, rows, K, tt, out, scratch, (cudaStream_t)stream);
+}

@@ -149,6 +149,22 @@ int al_std_tiles(int32_t dtype, const void* a, int32_t rows, int32_t K,
                  void* stream);
 int64_t al_std_scratch_floats(int32_t rows, int32_t T);
 
+/* Same result as al_std_tiles, for callers that have no way to hand over a scratch buffer.
+ * This entry point has no counterpart in the reference.  It is meant for hosts that must not
+ * (or cannot) allocate device memory when they need the statistic -- a serving process whose
+ * device arena is fixed at start-up and where a later cudaMalloc would stall every stream of
+ * the device, or a hook running inside another component's forward pass that owns no
+ * allocator.  The stage-1 partials go to a 2 MiB array built into the library image (resident
+ * on every GPU that loads the library, until the process exits), so the problem is limited
+ * to rows*T <= AL_STD_STATIC_MAX_SEGMENTS; larger ones return AL_ERR_TOO_LARGE.  The call
+ * allocates nothing.  The first call on each device looks the array's device address up
+ * (with that device current); make that first call outside of any stream capture.  All calls
+ * on a device share the array: calls whose kernels may overlap on the GPU race and must be
+ * serialised by the caller.  `a` and `out` are the caller's, as for al_std_tiles. */
+#define AL_STD_STATIC_MAX_SEGMENTS 262144
+int al_std_tiles_static(int32_t dtype, const void* a, int32_t rows, int32_t K,
+                        const int32_t* tile_ends_host, int32_t T, float* out, void* stream);
+
 /* Whole forward of one analog layer.  Replaces `TorchLinear.linear`
  * (P/torch_utils/torch_linear.py:116-314) and `TritonLinear.forward`
  * (P/triton_utils/triton_linear.py:446-690). */
