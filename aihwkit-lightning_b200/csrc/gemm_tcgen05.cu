@@ -1,10 +1,946 @@
-// placeholder, replaced by the tcgen05 kernels
+// bf16 GEMMs of the analog linear path on the Blackwell tensor cores (sm_100a): operands are
+// brought into shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), multiplied by
+// tcgen05.mma with fp32 accumulators in tensor memory (TMEM), and drained by tcgen05.ld.
+//
+// Two persistent, warp-specialised kernels (one CTA per SM):
+//
+//  * fwd_tc_kernel   out[m,n] = sum_t stage_t( xq[m, tile t] . w_mod[n, tile t] ) + bias[n]
+//      128x128 output block per CTA iteration.  The K loop is cut at the analog-tile
+//      boundaries; each analog tile accumulates into one of two TMEM accumulators, and while
+//      the tensor core works on tile t+1 eight epilogue warps run tile t's output stage
+//      (rounding, output noise, ADC quantisation, clamp, clamp-mask bits) and add it to a
+//      running sum that also lives in TMEM.
+//  * bwd_tc_kernel   C[i, lo_t + j] = sum_l (g * keep_t)(i,l) * B(l, lo_t + j)
+//      dgrad (C = grad_x, A = g, B = w_mod) and wgrad (C = grad_w, A = g^T, B = xq) in one
+//      template: 128x256 output block, the operands that are contiguous along the output
+//      dimension are fed as MN-major tiles, and four warps apply the ADC clamp mask of the
+//      analog tile to the staged gradient tile before the MMA reads it.
+//
+// Every wait on an mbarrier is bounded (wall-clock limit); a wait that gives up raises a
+// device error word, makes the CTA drain its copies in flight, free its TMEM and return.
+// No TMA multicast and no thread-block clusters are used.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "analog_math.cuh"
 #include "internal.h"
+
 namespace al {
-bool tc_forward_supported(const AlDesc&, const TileTable&) { return false; }
-bool tc_backward_supported(const AlDesc&, const TileTable&) { return false; }
-int launch_fwd_tc(int, const void*, const void*, int, const TileTable&, const FwdEpilogueParams&, void*, cudaStream_t) { return AL_ERR_UNSUPPORTED; }
-int launch_dgrad_tc(const void*, const void*, const uint32_t*, int, int, int, int, const TileTable&, void*, cudaStream_t) { return AL_ERR_UNSUPPORTED; }
-int launch_wgrad_tc(const void*, const void*, const uint32_t*, int, int, int, int, const TileTable&, void*, cudaStream_t) { return AL_ERR_UNSUPPORTED; }
-int tc_read_device_error(cudaStream_t, uint32_t* code) { *code = 0; return AL_OK; }
+
+__device__ uint32_t g_tc_error_word = 0;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle span
+constexpr int kThreads = 384;          // 12 warps
+constexpr uint64_t kTimeoutNs = 2000000000ull;
+
+// forward kernel
+constexpr int F_BN = 128;
+constexpr int F_STAGES = 6;
+constexpr int F_A_BYTES = BM * BK * 2;     // 16 KiB
+constexpr int F_B_BYTES = F_BN * BK * 2;   // 16 KiB
+constexpr int F_STAGE_BYTES = F_A_BYTES + F_B_BYTES;
+constexpr int F_EPI_WARPS = 8;
+// backward kernel
+constexpr int B_BN = 256;
+constexpr int B_STAGES = 4;
+constexpr int B_A_BYTES = BM * BK * 2;     // 16 KiB
+constexpr int B_B_BYTES = B_BN * BK * 2;   // 32 KiB
+constexpr int B_STAGE_BYTES = B_A_BYTES + B_B_BYTES;
+constexpr int B_BOX_BYTES = 64 * BK * 2;   // one 64x64 MN-major box: 8 KiB
+constexpr int B_EPI_WARPS = 4;
+constexpr int B_XFORM_THREADS = 128;
+
+constexpr int kTmemCols = 512;
+
+enum ErrCode : uint32_t {
+  kErrProducer = 1u, kErrMma = 2u, kErrEpilogue = 4u, kErrTransform = 8u, kErrDrain = 16u
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the wait gave up (time limit, or another role aborted).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    if (mbar_try(bar, parity)) return true;
+    if ((spin & 31u) == 31u) {
+      if (*abort_flag) return false;
+      uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kTimeoutNs) return false;
+    }
+  }
+}
+__device__ __forceinline__ void raise_error(uint32_t code, volatile uint32_t* abort_flag) {
+  *abort_flag = 1u;
+  atomicOr(&g_tc_error_word, code);
+}
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// tensor memory
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], bf16 inputs, fp32 accumulate, issued by one thread
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+#define AL_TMEM_REGS32(r)                                                                                   \
+  r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7], r[8], r[9], r[10], r[11], r[12], r[13], r[14], r[15],     \
+      r[16], r[17], r[18], r[19], r[20], r[21], r[22], r[23], r[24], r[25], r[26], r[27], r[28], r[29],     \
+      r[30], r[31]
+// 32 lanes x 32 columns of 32-bit: thread i of the warp gets lane (base lane + i), 32 columns
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t r[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
+        "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptors (128-byte swizzle, descriptor version 1 of sm_100).
+// K-major: rows of 128 bytes (64 bf16 along K), 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// MN-major: rows of 128 bytes hold 64 consecutive M/N elements of one k; 8-k groups are 1024
+// bytes apart (stride offset) and the next 64 M/N elements start `lbo_bytes` further (leading
+// offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr, uint32_t lbo_bytes) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
+         ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of tcgen05.mma.kind::f16: fp32 accumulator, bf16 A and B.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int a_mn_major, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
+}
+
+struct Barriers {
+  uint64_t full[8];
+  uint64_t ready[8];
+  uint64_t empty[8];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint64_t mma_done;
+  uint32_t tmem_slot;
+  uint32_t abort_flag;
+};
+
+__device__ __forceinline__ uint8_t* align_1024(uint8_t* p) {
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------------
+struct FwdTcParams {
+  int32_t tile_w;      // width of every analog tile (all equal on this path)
+  int32_t ksteps;      // ceil(tile_w / 64)
+  int32_t num_mb, num_nb;
+  FwdEpilogueParams ep;
+  void* out;
+};
+
+template <int RD>
+__global__ void __launch_bounds__(kThreads, 1)
+fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+              const FwdTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* stage_base = align_1024(smem_raw);
+  Barriers* bars = reinterpret_cast<Barriers*>(stage_base + F_STAGES * F_STAGE_BYTES);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const FwdEpilogueParams& ep = p.ep;
+  const int T = ep.T;
+  const int num_tiles = p.num_mb * p.num_nb;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < F_STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], F_EPI_WARPS);
+    }
+    mbar_init(&bars->mma_done, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc(&bars->tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer ------------------------------------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int mb = tile / p.num_nb, nb = tile % p.num_nb;
+        for (int t = 0; t < T && ok; ++t) {
+          for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
+            const int s = it % F_STAGES;
+            const uint32_t ph = (it / F_STAGES) & 1u;
+            if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag)) {
+              raise_error(kErrProducer, abort_flag);
+              ok = false;
+              break;
+            }
+            uint8_t* sa = stage_base + s * F_STAGE_BYTES;
+            mbar_expect_tx(&bars->full[s], F_STAGE_BYTES);
+            tma_load_3d(sa, &map_a, &bars->full[s], ks * BK, t, mb * BM);
+            tma_load_3d(sa + F_A_BYTES, &map_b, &bars->full[s], ks * BK, t, nb * F_BN);
+          }
+        }
+      }
+      // drain: the last copies issued must have landed before the CTA may exit
+      const uint32_t n_back = it < (uint32_t)F_STAGES ? it : (uint32_t)F_STAGES;
+      for (uint32_t j = it - n_back; j < it; ++j) {
+        const int s = j % F_STAGES;
+        const uint32_t ph = (j / F_STAGES) & 1u;
+        uint64_t t0 = globaltimer_ns();
+        while (!mbar_try(&bars->full[s], ph)) {
+          if (globaltimer_ns() - t0 > kTimeoutNs) {
+            raise_error(kErrDrain, abort_flag);
+            break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer --------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, F_BN, 0, 0);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int t = 0; t < T && ok; ++t, ++acc_it) {
+          const int b = acc_it & 1u;
+          const uint32_t aph = (acc_it >> 1) & 1u;
+          if (!mbar_wait(&bars->acc_empty[b], aph ^ 1u, abort_flag)) {
+            raise_error(kErrMma, abort_flag);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(b * F_BN);
+          for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
+            const int s = it % F_STAGES;
+            const uint32_t ph = (it / F_STAGES) & 1u;
+            if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
+              raise_error(kErrMma, abort_flag);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(stage_base + s * F_STAGE_BYTES);
+            const uint64_t da = desc_k_major(sa), db = desc_k_major(sa + F_A_BYTES);
+#pragma unroll
+            for (int k4 = 0; k4 < BK / 16; ++k4)
+              umma_bf16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (ks | k4) != 0 ? 1u : 0u);
+            umma_commit(&bars->empty[s]);
+          }
+          if (ok) umma_commit(&bars->acc_full[b]);
+        }
+      }
+      // all MMAs issued by this thread must have retired before TMEM is freed
+      umma_commit(&bars->mma_done);
+      uint64_t t0 = globaltimer_ns();
+      while (!mbar_try(&bars->mma_done, 0)) {
+        if (globaltimer_ns() - t0 > kTimeoutNs) {
+          raise_error(kErrDrain, abort_flag);
+          break;
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ---- epilogue: per-tile output stage, running sum in TMEM ---------------------------
+    const int ew = warp - 4;
+    const int quad = warp & 3;           // TMEM lane quadrant this warp may access
+    const int half = ew >> 2;            // which 64 of the 128 columns
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    TileEpilogueCfg cfg;
+    cfg.has_noise = ep.has_noise; cfg.has_bound = ep.has_bound; cfg.has_adc = ep.has_adc;
+    cfg.no_rounding = ep.no_rounding; cfg.noise_coef = ep.noise_coef; cfg.out_bound = ep.out_bound;
+    cfg.out_res = ep.out_res;
+    const int M = ep.M, N = ep.N;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int mb = tile / p.num_nb, nb = tile % p.num_nb;
+      const int m = mb * BM + quad * 32 + lane;
+      const bool row_ok = m < M;
+      for (int t = 0; t < T && ok; ++t, ++acc_it) {
+        const int b = acc_it & 1u;
+        const uint32_t aph = (acc_it >> 1) & 1u;
+        if (!mbar_wait(&bars->acc_full[b], aph, abort_flag)) {
+          if (lane == 0) raise_error(kErrEpilogue, abort_flag);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        float ir = 0.0f;
+        if (row_ok) {
+          if (ep.ir_mode == AL_IR_DYNAMIC) ir = Elem<kBF16>::load(ep.ir_rows, (int64_t)t * M + m);
+          else if (ep.ir_mode == AL_IR_STATIC) ir = Elem<kBF16>::load(ep.ir_rows, t);
+        }
+        const float t_max = ep.w_tile_max ? ep.w_tile_max[t] : 0.0f;
+        const bool col_scale = ep.w_amax != nullptr && (ep.noise_pc || ep.bound_pc);
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          const int col0 = half * 64 + c * 32;
+          const int n0 = nb * F_BN + col0;
+          uint32_t accr[32], sumr[32];
+          tmem_ld32(tmem_base + lane_base + (uint32_t)(b * F_BN + col0), accr);
+          if (t > 0) tmem_ld32(tmem_base + lane_base + (uint32_t)(2 * F_BN + col0), sumr);
+          tmem_wait_ld();
+          uint32_t keep_bits = 0;
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            float z[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const int nq = n0 + j4 * 4;
+            if (ep.has_noise && row_ok && nq < N) {
+              const uint64_t idx = ((uint64_t)t * M + m) * N + nq;
+              if (ep.out_noise) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) z[q] = Elem<kBF16>::load(ep.out_noise, (int64_t)(idx + q));
+              } else {
+                normal4(ep.seed, ep.offset, 1u, idx >> 2, z);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) z[q] = rnd<RD>(z[q]);
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int j = j4 * 4 + q;
+              const int n = n0 + j;
+              float cmax = 0.0f;
+              if (col_scale && n < N) cmax = Elem<kBF16>::load(ep.w_amax, (int64_t)t * N + n);
+              const float s_noise = ep.noise_pc ? cmax : t_max;
+              const float s_bound = ep.bound_pc ? cmax : t_max;
+              bool keep;
+              const float o = tile_epilogue<RD>(__uint_as_float(accr[j]), ir, s_noise, s_bound, z[q], cfg, &keep);
+              const float prev = __uint_as_float(sumr[j]);
+              sumr[j] = __float_as_uint(t == 0 ? fadd(0.0f, o) : rnd<RD>(fadd(prev, o)));
+              keep_bits |= (keep ? 1u : 0u) << j;
+            }
+          }
+          if (ep.keep_mask != nullptr && row_ok && (n0 >> 5) < ep.mask_words)
+            ep.keep_mask[((int64_t)t * M + m) * ep.mask_words + (n0 >> 5)] = keep_bits;
+          if (t < T - 1) {
+            tmem_st32(tmem_base + lane_base + (uint32_t)(2 * F_BN + col0), sumr);
+          } else if (row_ok) {
+            // final: bias, convert, store 32 bf16 = 64 bytes of this row
+            uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + (int64_t)m * N + n0;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (n0 + v * 8 < N) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  f[e] = __uint_as_float(sumr[v * 8 + e]);
+                  if (ep.bias) f[e] = fadd(rnd<RD>(f[e]), Elem<kBF16>::load(ep.bias, n0 + v * 8 + e));
+                }
+                uint4 pk = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                                      pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+                *reinterpret_cast<uint4*>(dst + v * 8) = pk;
+              }
+            }
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->acc_empty[b]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward (dgrad / wgrad)
+// ---------------------------------------------------------------------------------------------
+struct BwdTcParams {
+  int32_t I;           // rows of C (M for dgrad, N for wgrad)
+  int32_t L;           // reduction length (N for dgrad, M for wgrad)
+  int32_t K;           // row stride of C
+  int32_t M;           // rows of the mask
+  int32_t T;           // analog tiles that carry their own mask (1 when there is no mask)
+  int32_t tile_w;      // width of a tile (K when there is no mask)
+  int32_t num_ib, num_jb, lsteps;
+  const uint32_t* keep_mask;
+  int32_t mask_words;
+  void* c_out;
+};
+
+template <bool WGRAD>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+              const BwdTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* stage_base = align_1024(smem_raw);
+  Barriers* bars = reinterpret_cast<Barriers*>(stage_base + B_STAGES * B_STAGE_BYTES);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool masked = p.keep_mask != nullptr;
+  const int num_work = p.num_ib * p.T * p.num_jb;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < B_STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->ready[s], B_XFORM_THREADS);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], B_EPI_WARPS);
+    }
+    mbar_init(&bars->mma_done, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc(&bars->tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer ------------------------------------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const int ib = w / (p.T * p.num_jb);
+        const int rem = w % (p.T * p.num_jb);
+        const int t = rem / p.num_jb, jb = rem % p.num_jb;
+        const int j0 = t * p.tile_w + jb * B_BN;
+        for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+          const int s = it % B_STAGES;
+          const uint32_t ph = (it / B_STAGES) & 1u;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag)) {
+            raise_error(kErrProducer, abort_flag);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = stage_base + s * B_STAGE_BYTES;
+          uint8_t* sb = sa + B_A_BYTES;
+          const int l0 = ls * BK;
+          mbar_expect_tx(&bars->full[s], B_STAGE_BYTES);
+          if (WGRAD) {
+            // A = g^T: two MN-major boxes [64 rows of m] x [64 n]
+            tma_load_2d(sa, &map_a, &bars->full[s], ib * BM, l0);
+            tma_load_2d(sa + B_BOX_BYTES, &map_a, &bars->full[s], ib * BM + 64, l0);
+          } else {
+            // A = g: K-major [128 rows of m] x [64 n]
+            tma_load_2d(sa, &map_a, &bars->full[s], l0, ib * BM);
+          }
+#pragma unroll
+          for (int c = 0; c < B_BN / 64; ++c)
+            tma_load_2d(sb + c * B_BOX_BYTES, &map_b, &bars->full[s], j0 + c * 64, l0);
+        }
+      }
+      const uint32_t n_back = it < (uint32_t)B_STAGES ? it : (uint32_t)B_STAGES;
+      for (uint32_t j = it - n_back; j < it; ++j) {
+        const int s = j % B_STAGES;
+        const uint32_t ph = (j / B_STAGES) & 1u;
+        uint64_t t0 = globaltimer_ns();
+        while (!mbar_try(&bars->full[s], ph)) {
+          if (globaltimer_ns() - t0 > kTimeoutNs) {
+            raise_error(kErrDrain, abort_flag);
+            break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer --------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, B_BN, WGRAD ? 1 : 0, 1);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++acc_it) {
+        const int b = acc_it & 1u;
+        const uint32_t aph = (acc_it >> 1) & 1u;
+        if (!mbar_wait(&bars->acc_empty[b], aph ^ 1u, abort_flag)) {
+          raise_error(kErrMma, abort_flag);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * B_BN);
+        for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+          const int s = it % B_STAGES;
+          const uint32_t ph = (it / B_STAGES) & 1u;
+          uint64_t* wait_on = masked ? &bars->ready[s] : &bars->full[s];
+          if (!mbar_wait(wait_on, ph, abort_flag)) {
+            raise_error(kErrMma, abort_flag);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stage_base + s * B_STAGE_BYTES);
+          const uint32_t sb = sa + B_A_BYTES;
+          const uint64_t da = WGRAD ? desc_mn_major(sa, B_BOX_BYTES) : desc_k_major(sa);
+          const uint64_t db = desc_mn_major(sb, B_BOX_BYTES);
+          // one MMA consumes 16 k: 32 bytes along a K-major row, 16 rows (2048 bytes) of an MN-major box
+          constexpr uint64_t a_step = WGRAD ? (2048u >> 4) : (32u >> 4);
+          constexpr uint64_t b_step = 2048u >> 4;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4)
+            umma_bf16(d_tmem, da + a_step * k4, db + b_step * k4, idesc, (ls | k4) != 0 ? 1u : 0u);
+          umma_commit(&bars->empty[s]);
+        }
+        if (ok) umma_commit(&bars->acc_full[b]);
+      }
+      umma_commit(&bars->mma_done);
+      uint64_t t0 = globaltimer_ns();
+      while (!mbar_try(&bars->mma_done, 0)) {
+        if (globaltimer_ns() - t0 > kTimeoutNs) {
+          raise_error(kErrDrain, abort_flag);
+          break;
+        }
+      }
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ---- epilogue: TMEM -> bf16 -> global ------------------------------------------------
+    const int quad = warp & 3;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++acc_it) {
+      const int ib = w / (p.T * p.num_jb);
+      const int rem = w % (p.T * p.num_jb);
+      const int t = rem / p.num_jb, jb = rem % p.num_jb;
+      const int j0 = t * p.tile_w + jb * B_BN;
+      const int j_end = min((t + 1) * p.tile_w, p.K);
+      const int i = ib * BM + quad * 32 + lane;
+      const int b = acc_it & 1u;
+      const uint32_t aph = (acc_it >> 1) & 1u;
+      if (!mbar_wait(&bars->acc_full[b], aph, abort_flag)) {
+        if (lane == 0) raise_error(kErrEpilogue, abort_flag);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint16_t* dst_row = reinterpret_cast<uint16_t*>(p.c_out) + (int64_t)i * p.K;
+#pragma unroll 1
+      for (int c = 0; c < B_BN / 32; ++c) {
+        const int jc = j0 + c * 32;
+        if (jc >= j_end) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(tmem_base + lane_base + (uint32_t)(b * B_BN + c * 32), r);
+        tmem_wait_ld();
+        if (i < p.I) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (jc + v * 8 < j_end) {
+              uint4 pk = make_uint4(
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1])),
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3])),
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5])),
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7])));
+              *reinterpret_cast<uint4*>(dst_row + jc + v * 8) = pk;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty[b]);
+    }
+  } else if (warp >= 8 && masked) {
+    // ---- mask transform: zero the gradient entries the tile's ADC clamp blocked ---------
+    const int r = threadIdx.x - 8 * 32;  // 0..127: one 128-byte row of the staged A tile
+    uint32_t it = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      const int ib = w / (p.T * p.num_jb);
+      const int rem = w % (p.T * p.num_jb);
+      const int t = rem / p.num_jb;
+      for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+        const int s = it % B_STAGES;
+        const uint32_t ph = (it / B_STAGES) & 1u;
+        if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
+          raise_error(kErrTransform, abort_flag);
+          ok = false;
+          break;
+        }
+        const int l0 = ls * BK;
+        // row r of the staged tile: which (m, n0..n0+63) of g does it hold?
+        int m, n0;
+        uint8_t* row_ptr;
+        if (WGRAD) {
+          m = l0 + (r & 63);
+          n0 = ib * BM + (r >> 6) * 64;
+          row_ptr = stage_base + s * B_STAGE_BYTES + (r >> 6) * B_BOX_BYTES + (r & 63) * 128;
+        } else {
+          m = ib * BM + r;
+          n0 = l0;
+          row_ptr = stage_base + s * B_STAGE_BYTES + r * 128;
+        }
+        if (m < p.M) {
+          const uint32_t* mrow = p.keep_mask + ((int64_t)t * p.M + m) * p.mask_words;
+          const int w0 = n0 >> 5;
+          const uint32_t lo = w0 < p.mask_words ? mrow[w0] : 0xffffffffu;
+          const uint32_t hi = w0 + 1 < p.mask_words ? mrow[w0 + 1] : 0xffffffffu;
+          if ((lo & hi) != 0xffffffffu) {
+            const uint64_t bits = (uint64_t)lo | ((uint64_t)hi << 32);
+            const int sw = r & 7;  // 128-byte swizzle: 16-byte chunk index is XORed with row % 8
+#pragma unroll 1
+            for (int c = 0; c < 8; ++c) {
+              const uint32_t byte = (uint32_t)(bits >> (8 * c)) & 0xffu;
+              if (byte == 0xffu) continue;
+              uint4* chunk = reinterpret_cast<uint4*>(row_ptr + ((c ^ sw) << 4));
+              uint4 v = *chunk;
+              uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const uint32_t keep_lo = (byte >> (2 * e)) & 1u, keep_hi = (byte >> (2 * e + 1)) & 1u;
+                wv[e] &= (keep_lo ? 0x0000ffffu : 0u) | (keep_hi ? 0xffff0000u : 0u);
+              }
+              *chunk = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&bars->ready[s]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// bf16 tensor map with 128-byte swizzle.  dims/strides innermost first; strides in bytes for
+// dims 1.. (the innermost stride is the element size).
+int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+             const uint32_t* box) {
+  PFN_cuTensorMapEncodeTiled_v12000 fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return AL_ERR_CUDA;
+  }
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[5];
+  cuuint32_t bdim[5], estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    estr[i] = 1;
+  }
+  for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr,
+                  bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return AL_ERR_CUDA;
+  }
+  return AL_OK;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+constexpr int F_SMEM = F_STAGES * F_STAGE_BYTES + (int)sizeof(Barriers) + 1024;
+constexpr int B_SMEM = B_STAGES * B_STAGE_BYTES + (int)sizeof(Barriers) + 1024;
+
+template <class Kernel>
+int ensure_smem(Kernel k, int bytes) {
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(%d bytes): %s", bytes, cudaGetErrorString(e));
+    return AL_ERR_CUDA;
+  }
+  return AL_OK;
+}
+
+bool uniform_tiles(const TileTable& tt, int* width) {
+  int w = tt.hi(0);
+  for (int t = 1; t < tt.T; ++t)
+    if (tt.hi(t) - tt.lo(t) != w) return false;
+  *width = w;
+  return true;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+// bf16, all analog tiles equally wide, every row pitch and tile offset a multiple of 16 bytes
+static bool tc_shape_ok(const AlDesc& d, const TileTable& tt) {
+  int w = 0;
+  if (d.dtype != AL_BF16) return false;
+  if (!uniform_tiles(tt, &w)) return false;
+  if (w % 8 != 0 || d.K % 8 != 0 || d.N % 8 != 0) return false;
+  return true;
+}
+bool tc_forward_supported(const AlDesc& d, const TileTable& tt) { return tc_shape_ok(d, tt); }
+bool tc_backward_supported(const AlDesc& d, const TileTable& tt) { return tc_shape_ok(d, tt); }
+
+int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const TileTable& tt,
+                  const FwdEpilogueParams& ep, void* out, cudaStream_t s) {
+  ProfScope prof(AL_K_FWD_GEMM, s);
+  int w = 0;
+  if (!uniform_tiles(tt, &w) || !aligned16(xq) || !aligned16(w_mod) || !aligned16(out)) {
+    set_error("fwd_tc: operands must be 16-byte aligned with equally wide tiles");
+    return AL_ERR_UNSUPPORTED;
+  }
+  FwdTcParams p;
+  p.tile_w = w;
+  p.ksteps = (w + BK - 1) / BK;
+  p.num_mb = (ep.M + BM - 1) / BM;
+  p.num_nb = (ep.N + F_BN - 1) / F_BN;
+  p.ep = ep;
+  p.out = out;
+  // The runtime call below also binds the device's primary context to the calling thread
+  // (autograd runs backward on its own threads); the driver entry point that encodes the
+  // tensor maps needs a current context.
+  int rc = round_dt == AL_BF16 ? ensure_smem(fwd_tc_kernel<kBF16>, F_SMEM) : ensure_smem(fwd_tc_kernel<kF32>, F_SMEM);
+  if (rc) return rc;
+  CUtensorMap map_a, map_b;
+  {
+    uint64_t dims[3] = {(uint64_t)w, (uint64_t)tt.T, (uint64_t)ep.M};
+    uint64_t strides[2] = {(uint64_t)w * 2, (uint64_t)K * 2};
+    uint32_t box[3] = {BK, 1, BM};
+    rc = make_map(&map_a, xq, 3, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)w, (uint64_t)tt.T, (uint64_t)ep.N};
+    uint64_t strides[2] = {(uint64_t)w * 2, (uint64_t)K * 2};
+    uint32_t box[3] = {BK, 1, F_BN};
+    rc = make_map(&map_b, w_mod, 3, dims, strides, box);
+    if (rc) return rc;
+  }
+  int tiles = p.num_mb * p.num_nb;
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (round_dt == AL_BF16)
+    fwd_tc_kernel<kBF16><<<grid, kThreads, F_SMEM, s>>>(map_a, map_b, p);
+  else
+    fwd_tc_kernel<kF32><<<grid, kThreads, F_SMEM, s>>>(map_a, map_b, p);
+  return check_launch("fwd_tc");
+}
+
+static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint32_t* keep_mask,
+                         int mask_words, int M, int K, int N, const TileTable& tt, void* c_out,
+                         cudaStream_t s) {
+  int w = 0;
+  if (!uniform_tiles(tt, &w) || !aligned16(g) || !aligned16(b_op) || !aligned16(c_out)) {
+    set_error("bwd_tc: operands must be 16-byte aligned with equally wide tiles");
+    return AL_ERR_UNSUPPORTED;
+  }
+  BwdTcParams p;
+  p.I = wgrad ? N : M;
+  p.L = wgrad ? M : N;
+  p.K = K;
+  p.M = M;
+  p.T = tt.T;
+  p.tile_w = w;
+  p.num_ib = (p.I + BM - 1) / BM;
+  p.num_jb = (w + B_BN - 1) / B_BN;
+  p.lsteps = (p.L + BK - 1) / BK;
+  p.keep_mask = keep_mask;
+  p.mask_words = mask_words;
+  p.c_out = c_out;
+  int rc = wgrad ? ensure_smem(bwd_tc_kernel<true>, B_SMEM) : ensure_smem(bwd_tc_kernel<false>, B_SMEM);
+  if (rc) return rc;
+  CUtensorMap map_a, map_b;
+  {
+    // g [M,N]: dims innermost first {N, M}
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+    uint64_t strides[1] = {(uint64_t)N * 2};
+    uint32_t box_k[2] = {BK, BM};   // dgrad: 64 n (reduction) x 128 m
+    uint32_t box_mn[2] = {64, BK};  // wgrad: 64 n (MMA-M) x 64 m (reduction)
+    rc = make_map(&map_a, g, 2, dims, strides, wgrad ? box_mn : box_k);
+    if (rc) return rc;
+  }
+  {
+    // B operand [L, K] row-major (w_mod [N,K] for dgrad, xq [M,K] for wgrad): {K, L}
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)p.L};
+    uint64_t strides[1] = {(uint64_t)K * 2};
+    uint32_t box[2] = {64, BK};
+    rc = make_map(&map_b, b_op, 2, dims, strides, box);
+    if (rc) return rc;
+  }
+  int work = p.num_ib * p.T * p.num_jb;
+  int grid = work < sm_count() ? work : sm_count();
+  if (wgrad)
+    bwd_tc_kernel<true><<<grid, kThreads, B_SMEM, s>>>(map_a, map_b, p);
+  else
+    bwd_tc_kernel<false><<<grid, kThreads, B_SMEM, s>>>(map_a, map_b, p);
+  return check_launch(wgrad ? "wgrad_tc" : "dgrad_tc");
+}
+
+int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask, int mask_words,
+                    int M, int K, int N, const TileTable& tt, void* grad_x, cudaStream_t s) {
+  ProfScope prof(AL_K_DGRAD_GEMM, s);
+  return launch_bwd_tc(false, g, w_mod, keep_mask, mask_words, M, K, N, tt, grad_x, s);
+}
+
+int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, int mask_words,
+                    int M, int K, int N, const TileTable& tt, void* grad_w, cudaStream_t s) {
+  ProfScope prof(AL_K_WGRAD_GEMM, s);
+  return launch_bwd_tc(true, g, xq, keep_mask, mask_words, M, K, N, tt, grad_w, s);
+}
+
+int tc_read_device_error(cudaStream_t s, uint32_t* code) {
+  cudaError_t e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) {
+    set_error("al_read_device_error: %s", cudaGetErrorString(e));
+    return AL_ERR_CUDA;
+  }
+  uint32_t zero = 0;
+  e = cudaMemcpyFromSymbol(code, g_tc_error_word, sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_tc_error_word, &zero, sizeof(uint32_t));
+  if (e != cudaSuccess) {
+    set_error("al_read_device_error: %s", cudaGetErrorString(e));
+    return AL_ERR_CUDA;
+  }
+  if (*code != 0) {
+    set_error("a device-side wait of the tcgen05 kernels gave up (role mask 0x%x)", *code);
+    return AL_ERR_DEVICE_TIMEOUT;
+  }
+  return AL_OK;
+}
+
+}  // namespace al
