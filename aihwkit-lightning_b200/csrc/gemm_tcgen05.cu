@@ -7,7 +7,7 @@
 //  * fwd_tc_kernel   out[m,n] = sum_t stage_t( xq[m, tile t] . w_mod[n, tile t] ) + bias[n]
 //      128x128 output block per CTA iteration.  The K loop is cut at the analog-tile
 //      boundaries; each analog tile accumulates into one of two TMEM accumulators, and while
-//      the tensor core works on tile t+1 eight epilogue warps run tile t's output stage
+//      the tensor core works on tile t+1 sixteen epilogue warps run tile t's output stage
 //      (rounding, output noise, ADC quantisation, clamp, clamp-mask bits) and add it to a
 //      running sum that also lives in TMEM.
 //  * bwd_tc_kernel   C[i, lo_t + j] = sum_l (g * keep_t)(i,l) * B(l, lo_t + j)
@@ -42,7 +42,8 @@ constexpr int F_STAGES = 6;
 constexpr int F_A_BYTES = BM * BK * 2;     // 16 KiB
 constexpr int F_B_BYTES = F_BN * BK * 2;   // 16 KiB
 constexpr int F_STAGE_BYTES = F_A_BYTES + F_B_BYTES;
-constexpr int F_EPI_WARPS = 8;
+constexpr int F_EPI_WARPS = 16;
+constexpr int kFwdThreads = (4 + F_EPI_WARPS) * 32;  // producer, MMA, two idle, 16 epilogue warps
 // backward kernel
 constexpr int B_BN = 256;
 constexpr int B_STAGES = 4;
@@ -209,6 +210,69 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
 }
 
+// 16-column variants of the TMEM load / store
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t r[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t r[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(taddr)
+      : "memory");
+}
+
+// Round-to-nearest-even to bf16 precision on the integer ALU.  The cvt.rn.bf16.f32 instruction
+// runs on the quarter-rate conversion pipe, which the per-tile output stage (six roundings per
+// element in reference-rounding mode) would saturate.  Same result as the cvt for every finite
+// value and for infinities; NaNs are patched by the caller.
+template <int RD>
+__device__ __forceinline__ float rnd_alu(float v) {
+  if (RD == kBF16) {
+    uint32_t u = __float_as_uint(v);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return __uint_as_float(u & 0xffff0000u);
+  }
+  return v;
+}
+// round-half-even to an integer with two additions (exact for |x| < 2^22)
+__device__ __forceinline__ float rint_magic(float x) {
+  const float r = __fsub_rn(__fadd_rn(x, 12582912.0f), 12582912.0f);
+  return fabsf(x) < 4194304.0f ? r : x;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+// Four standard normals of group `group` (same counter layout as al::normal4), with the
+// uniform->float conversions done by bit manipulation and approximate transcendentals.
+__device__ __forceinline__ void box_muller_fast(uint32_t a, uint32_t b, float* z0, float* z1) {
+  const float u1 = 2.0f - __uint_as_float(0x3f800000u | (a >> 9));  // (0, 1]
+  const float u2 = __uint_as_float(0x3f800000u | (b >> 9)) - 1.0f;  // [0, 1)
+  float r;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(-1.3862943611198906f * __log2f(u1)));
+  float s, c;
+  __sincosf(6.283185307179586f * u2, &s, &c);
+  *z0 = r * c;
+  *z1 = r * s;
+}
+__device__ __forceinline__ void normal4_fast(uint64_t seed, uint64_t offset, uint32_t stream, uint64_t group,
+                                             float z[4]) {
+  Philox4 p = philox4x32_10((uint32_t)group, (uint32_t)(group >> 32), (uint32_t)offset,
+                            (uint32_t)(offset >> 32) ^ (stream * 0x85EBCA6Bu), (uint32_t)seed,
+                            (uint32_t)(seed >> 32));
+  box_muller_fast(p.v[0], p.v[1], &z[0], &z[1]);
+  box_muller_fast(p.v[2], p.v[3], &z[2], &z[3]);
+}
+
 struct Barriers {
   uint64_t full[8];
   uint64_t ready[8];
@@ -236,7 +300,7 @@ struct FwdTcParams {
 };
 
 template <int RD>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
               const FwdTcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -355,21 +419,23 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     }
   } else if (warp >= 4) {
     // ---- epilogue: per-tile output stage, running sum in TMEM ---------------------------
-    const int ew = warp - 4;
-    const int quad = warp & 3;           // TMEM lane quadrant this warp may access
-    const int half = ew >> 2;            // which 64 of the 128 columns
+    // 16 warps: warp & 3 selects the TMEM lane quadrant (rows), (warp - 4) >> 2 the 32 columns.
+    const int quad = warp & 3;
+    const int col0 = ((warp - 4) >> 2) * 32;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    const int M = ep.M, N = ep.N;
+    const bool per_channel = ep.w_amax != nullptr && (ep.noise_pc || ep.bound_pc);
     TileEpilogueCfg cfg;
     cfg.has_noise = ep.has_noise; cfg.has_bound = ep.has_bound; cfg.has_adc = ep.has_adc;
     cfg.no_rounding = ep.no_rounding; cfg.noise_coef = ep.noise_coef; cfg.out_bound = ep.out_bound;
     cfg.out_res = ep.out_res;
-    const int M = ep.M, N = ep.N;
     uint32_t acc_it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int mb = tile / p.num_nb, nb = tile % p.num_nb;
       const int m = mb * BM + quad * 32 + lane;
       const bool row_ok = m < M;
+      const int n0 = nb * F_BN + col0;
       for (int t = 0; t < T && ok; ++t, ++acc_it) {
         const int b = acc_it & 1u;
         const uint32_t aph = (acc_it >> 1) & 1u;
@@ -379,75 +445,105 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           break;
         }
         tc_fence_after();
+        // constants of this (row, analog tile)
         float ir = 0.0f;
         if (row_ok) {
           if (ep.ir_mode == AL_IR_DYNAMIC) ir = Elem<kBF16>::load(ep.ir_rows, (int64_t)t * M + m);
           else if (ep.ir_mode == AL_IR_STATIC) ir = Elem<kBF16>::load(ep.ir_rows, t);
         }
         const float t_max = ep.w_tile_max ? ep.w_tile_max[t] : 0.0f;
-        const bool col_scale = ep.w_amax != nullptr && (ep.noise_pc || ep.bound_pc);
+        const float sc = rnd<RD>(fmul(t_max, rnd<RD>(fmul(ep.noise_coef, ir))));
+        const float bound = rnd<RD>(fmul(rnd<RD>(fmul(ir, ep.out_bound)), t_max));
+        const float step = ep.has_adc ? quant_step<RD>(bound, ep.out_res) : 1.0f;
+        const float stepc = step < kTiny ? kTiny : step;
+        const float rstep = __frcp_rn(stepc);
+        uint32_t keep_bits = 0;
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          const int col0 = half * 64 + c * 32;
-          const int n0 = nb * F_BN + col0;
-          uint32_t accr[32], sumr[32];
-          tmem_ld32(tmem_base + lane_base + (uint32_t)(b * F_BN + col0), accr);
-          if (t > 0) tmem_ld32(tmem_base + lane_base + (uint32_t)(2 * F_BN + col0), sumr);
+        for (int h = 0; h < 2; ++h) {
+          const int cc = col0 + h * 16;
+          const int nh = n0 + h * 16;
+          uint32_t accr[16], sumr[16];
+          tmem_ld16(tmem_base + lane_base + (uint32_t)(b * F_BN + cc), accr);
+          if (t > 0) tmem_ld16(tmem_base + lane_base + (uint32_t)(2 * F_BN + cc), sumr);
           tmem_wait_ld();
-          uint32_t keep_bits = 0;
+          float z[16];
+          if (ep.has_noise) {
 #pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            float z[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const int nq = n0 + j4 * 4;
-            if (ep.has_noise && row_ok && nq < N) {
-              const uint64_t idx = ((uint64_t)t * M + m) * N + nq;
+            for (int g4 = 0; g4 < 4; ++g4) {
+              const int nq = nh + g4 * 4;
+              const uint64_t idx = ((uint64_t)t * M + (row_ok ? m : 0)) * N + (nq < N ? nq : 0);
               if (ep.out_noise) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) z[q] = Elem<kBF16>::load(ep.out_noise, (int64_t)(idx + q));
+                const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(ep.out_noise) + idx);
+                z[g4 * 4 + 0] = __uint_as_float(raw.x << 16);
+                z[g4 * 4 + 1] = __uint_as_float(raw.x & 0xffff0000u);
+                z[g4 * 4 + 2] = __uint_as_float(raw.y << 16);
+                z[g4 * 4 + 3] = __uint_as_float(raw.y & 0xffff0000u);
               } else {
-                normal4(ep.seed, ep.offset, 1u, idx >> 2, z);
+                normal4_fast(ep.seed, ep.offset, 1u, idx >> 2, &z[g4 * 4]);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) z[q] = rnd<RD>(z[q]);
+                for (int q = 0; q < 4; ++q) z[g4 * 4 + q] = rnd_alu<RD>(z[g4 * 4 + q]);
               }
             }
+          }
+          if (!per_channel) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int j = j4 * 4 + q;
-              const int n = n0 + j;
-              float cmax = 0.0f;
-              if (col_scale && n < N) cmax = Elem<kBF16>::load(ep.w_amax, (int64_t)t * N + n);
-              const float s_noise = ep.noise_pc ? cmax : t_max;
-              const float s_bound = ep.bound_pc ? cmax : t_max;
+            for (int j = 0; j < 16; ++j) {
+              const float acc = __uint_as_float(accr[j]);
+              float o = rnd_alu<RD>(acc);
+              if (ep.has_noise) o = rnd_alu<RD>(fadd(o, rnd_alu<RD>(fmul(sc, z[j]))));
+              bool keep = true;
+              if (ep.has_adc) {
+                // o / stepc, correctly rounded from the correctly rounded reciprocal
+                const float q0 = fmul(o, rstep);
+                const float q = fmaf(fmaf(-q0, stepc, o), rstep, q0);
+                float code = rnd_alu<RD>(q);
+                if (!ep.no_rounding) code = rint_magic(code);
+                o = rnd_alu<RD>(fmul(code, step));
+              }
+              if (ep.has_bound) {
+                keep = fabsf(o) <= bound;
+                o = fminf(fmaxf(o, -bound), bound);
+              }
+              float sum = t == 0 ? fadd(0.0f, o) : rnd_alu<RD>(fadd(__uint_as_float(sumr[j]), o));
+              if (acc != acc) sum = acc;  // the integer rounding above does not preserve NaN
+              sumr[j] = __float_as_uint(sum);
+              keep_bits |= (keep ? 1u : 0u) << (h * 16 + j);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int n = nh + j;
+              const float cmax = n < N ? Elem<kBF16>::load(ep.w_amax, (int64_t)t * N + n) : 0.0f;
               bool keep;
-              const float o = tile_epilogue<RD>(__uint_as_float(accr[j]), ir, s_noise, s_bound, z[q], cfg, &keep);
-              const float prev = __uint_as_float(sumr[j]);
-              sumr[j] = __float_as_uint(t == 0 ? fadd(0.0f, o) : rnd<RD>(fadd(prev, o)));
-              keep_bits |= (keep ? 1u : 0u) << j;
+              const float o = tile_epilogue<RD>(__uint_as_float(accr[j]), ir, ep.noise_pc ? cmax : t_max,
+                                                ep.bound_pc ? cmax : t_max, ep.has_noise ? z[j] : 0.0f, cfg, &keep);
+              sumr[j] = __float_as_uint(t == 0 ? fadd(0.0f, o) : rnd<RD>(fadd(__uint_as_float(sumr[j]), o)));
+              keep_bits |= (keep ? 1u : 0u) << (h * 16 + j);
             }
           }
-          if (ep.keep_mask != nullptr && row_ok && (n0 >> 5) < ep.mask_words)
-            ep.keep_mask[((int64_t)t * M + m) * ep.mask_words + (n0 >> 5)] = keep_bits;
           if (t < T - 1) {
-            tmem_st32(tmem_base + lane_base + (uint32_t)(2 * F_BN + col0), sumr);
+            tmem_st16(tmem_base + lane_base + (uint32_t)(2 * F_BN + cc), sumr);
           } else if (row_ok) {
-            // final: bias, convert, store 32 bf16 = 64 bytes of this row
-            uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + (int64_t)m * N + n0;
+            // final: bias, convert, store 16 bf16 = 32 bytes of this row
+            uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + (int64_t)m * N + nh;
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (n0 + v * 8 < N) {
+            for (int v = 0; v < 2; ++v) {
+              if (nh + v * 8 < N) {
                 float f[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                   f[e] = __uint_as_float(sumr[v * 8 + e]);
-                  if (ep.bias) f[e] = fadd(rnd<RD>(f[e]), Elem<kBF16>::load(ep.bias, n0 + v * 8 + e));
+                  if (ep.bias) f[e] = fadd(rnd<RD>(f[e]), Elem<kBF16>::load(ep.bias, nh + v * 8 + e));
                 }
-                uint4 pk = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
-                                      pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
-                *reinterpret_cast<uint4*>(dst + v * 8) = pk;
+                *reinterpret_cast<uint4*>(dst + v * 8) =
+                    make_uint4(pack_bf16x2_rn(f[0], f[1]), pack_bf16x2_rn(f[2], f[3]),
+                               pack_bf16x2_rn(f[4], f[5]), pack_bf16x2_rn(f[6], f[7]));
               }
             }
           }
         }
+        if (ep.keep_mask != nullptr && row_ok && (n0 >> 5) < ep.mask_words)
+          ep.keep_mask[((int64_t)t * M + m) * ep.mask_words + (n0 >> 5)] = keep_bits;
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -659,61 +755,71 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     }
   } else if (warp >= 8 && masked) {
     // ---- mask transform: zero the gradient entries the tile's ADC clamp blocked ---------
-    const int r = threadIdx.x - 8 * 32;  // 0..127: one 128-byte row of the staged A tile
-    uint32_t it = 0;
-    bool ok = true;
-    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-      const int ib = w / (p.T * p.num_jb);
-      const int rem = w % (p.T * p.num_jb);
-      const int t = rem / p.num_jb;
-      for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
-        const int s = it % B_STAGES;
-        const uint32_t ph = (it / B_STAGES) & 1u;
-        if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
-          raise_error(kErrTransform, abort_flag);
-          ok = false;
-          break;
-        }
-        const int l0 = ls * BK;
-        // row r of the staged tile: which (m, n0..n0+63) of g does it hold?
-        int m, n0;
-        uint8_t* row_ptr;
-        if (WGRAD) {
-          m = l0 + (r & 63);
-          n0 = ib * BM + (r >> 6) * 64;
-          row_ptr = stage_base + s * B_STAGE_BYTES + (r >> 6) * B_BOX_BYTES + (r & 63) * 128;
-        } else {
-          m = ib * BM + r;
-          n0 = l0;
-          row_ptr = stage_base + s * B_STAGE_BYTES + r * 128;
-        }
+    // Thread r owns one 128-byte row of the staged A tile.  The two mask words of that row are
+    // fetched two stages ahead, so that their L2 latency is off the TMA -> MMA critical path.
+    const int r = threadIdx.x - 8 * 32;  // 0..127
+    const int row_in_box = WGRAD ? (r & 63) : r;
+    const int box = WGRAD ? (r >> 6) : 0;
+    const int total = ((num_work - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * p.lsteps;
+    // cursor of the prefetch (runs two stage-iterations ahead of the consumer)
+    int pf_w = blockIdx.x, pf_ls = 0, pf_count = 0;
+    auto fetch = [&](uint32_t* lo, uint32_t* hi) {
+      *lo = 0xffffffffu;
+      *hi = 0xffffffffu;
+      if (pf_count < total) {
+        const int ib = pf_w / (p.T * p.num_jb);
+        const int t = (pf_w % (p.T * p.num_jb)) / p.num_jb;
+        const int l0 = pf_ls * BK;
+        const int m = WGRAD ? l0 + row_in_box : ib * BM + r;
+        const int n0 = WGRAD ? ib * BM + box * 64 : l0;
         if (m < p.M) {
           const uint32_t* mrow = p.keep_mask + ((int64_t)t * p.M + m) * p.mask_words;
           const int w0 = n0 >> 5;
-          const uint32_t lo = w0 < p.mask_words ? mrow[w0] : 0xffffffffu;
-          const uint32_t hi = w0 + 1 < p.mask_words ? mrow[w0 + 1] : 0xffffffffu;
-          if ((lo & hi) != 0xffffffffu) {
-            const uint64_t bits = (uint64_t)lo | ((uint64_t)hi << 32);
-            const int sw = r & 7;  // 128-byte swizzle: 16-byte chunk index is XORed with row % 8
+          if (w0 < p.mask_words) *lo = mrow[w0];
+          if (w0 + 1 < p.mask_words) *hi = mrow[w0 + 1];
+        }
+      }
+      ++pf_count;
+      if (++pf_ls == p.lsteps) {
+        pf_ls = 0;
+        pf_w += gridDim.x;
+      }
+    };
+    uint32_t lo0, hi0, lo1, hi1, lo2, hi2;
+    fetch(&lo0, &hi0);
+    fetch(&lo1, &hi1);
+    uint8_t* const row_base = stage_base + box * B_BOX_BYTES + row_in_box * 128;
+    const int sw = r & 7;  // 128-byte swizzle: 16-byte chunk index is XORed with row % 8
+    for (int it = 0; it < total; ++it) {
+      fetch(&lo2, &hi2);
+      const int s = it % B_STAGES;
+      const uint32_t ph = ((uint32_t)it / B_STAGES) & 1u;
+      if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
+        raise_error(kErrTransform, abort_flag);
+        break;
+      }
+      if ((lo0 & hi0) != 0xffffffffu) {
+        uint8_t* row_ptr = row_base + s * B_STAGE_BYTES;
+        const uint64_t bits = (uint64_t)lo0 | ((uint64_t)hi0 << 32);
 #pragma unroll 1
-            for (int c = 0; c < 8; ++c) {
-              const uint32_t byte = (uint32_t)(bits >> (8 * c)) & 0xffu;
-              if (byte == 0xffu) continue;
-              uint4* chunk = reinterpret_cast<uint4*>(row_ptr + ((c ^ sw) << 4));
-              uint4 v = *chunk;
-              uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t byte = (uint32_t)(bits >> (8 * c)) & 0xffu;
+          if (byte == 0xffu) continue;
+          uint4* chunk = reinterpret_cast<uint4*>(row_ptr + ((c ^ sw) << 4));
+          uint4 v = *chunk;
+          uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const uint32_t keep_lo = (byte >> (2 * e)) & 1u, keep_hi = (byte >> (2 * e + 1)) & 1u;
-                wv[e] &= (keep_lo ? 0x0000ffffu : 0u) | (keep_hi ? 0xffff0000u : 0u);
-              }
-              *chunk = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-            }
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t keep_lo = (byte >> (2 * e)) & 1u, keep_hi = (byte >> (2 * e + 1)) & 1u;
+            wv[e] &= (keep_lo ? 0x0000ffffu : 0u) | (keep_hi ? 0xffff0000u : 0u);
           }
+          *chunk = make_uint4(wv[0], wv[1], wv[2], wv[3]);
         }
         fence_proxy_async_smem();
-        mbar_arrive(&bars->ready[s]);
       }
+      mbar_arrive(&bars->ready[s]);
+      lo0 = lo1; hi0 = hi1;
+      lo1 = lo2; hi1 = hi2;
     }
   }
 
@@ -855,9 +961,9 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
   int tiles = p.num_mb * p.num_nb;
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (round_dt == AL_BF16)
-    fwd_tc_kernel<kBF16><<<grid, kThreads, F_SMEM, s>>>(map_a, map_b, p);
+    fwd_tc_kernel<kBF16><<<grid, kFwdThreads, F_SMEM, s>>>(map_a, map_b, p);
   else
-    fwd_tc_kernel<kF32><<<grid, kThreads, F_SMEM, s>>>(map_a, map_b, p);
+    fwd_tc_kernel<kF32><<<grid, kFwdThreads, F_SMEM, s>>>(map_a, map_b, p);
   return check_launch("fwd_tc");
 }
 
