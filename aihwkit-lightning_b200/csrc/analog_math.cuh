@@ -153,6 +153,83 @@ AL_HD float dac(float x, float ir, float inp_res, bool static_clamp, bool no_rou
   return rnd<DT>(fmul(c, step));
 }
 
+// ---- same results, fewer instructions: what the streaming kernels actually execute --------
+// Rounding to bf16 precision with integer adds (the cvt instruction is quarter rate).  Equal to
+// rnd<DT> for every finite value and for infinities; NaN inputs must be patched by the caller.
+template <int DT>
+AL_HD float rnd_int(float v) {
+  if (DT == kBF16) {
+    uint32_t u = f2u(v);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return u2f(u & 0xffff0000u);
+  }
+  return v;
+}
+AL_HD float ffma(float a, float b, float c) {
+#if defined(__CUDA_ARCH__)
+  return __fmaf_rn(a, b, c);
+#else
+  return fmaf(a, b, c);
+#endif
+}
+AL_HD float frcp(float b) {
+#if defined(__CUDA_ARCH__)
+  return __frcp_rn(b);
+#else
+  return 1.0f / b;
+#endif
+}
+// a / b from y = RN(1/b): q = RN(a*y), r = a - b*q (exact in one FMA), RN(q + r*y).  With a
+// correctly rounded reciprocal this is the correctly rounded quotient (Markstein), as long as
+// no intermediate over/underflows; the CPU test-suite compares it with the true division.
+AL_HD float fdiv_rcp(float a, float b, float y) {
+  float q = fmul(a, y);
+  return ffma(ffma(-q, b, a), y, q);
+}
+// round-half-even to an integer with two additions, exact for |x| < 2^22
+AL_HD float frint_add(float x) {
+  float r = fsub(fadd(x, 12582912.0f), 12582912.0f);
+  return fabsf(x) < 4194304.0f ? r : frint(x);
+}
+
+// Quantiser constants of one (row, tile) segment, hoisted out of the element loop.
+struct QuantSeg {
+  float bound;   // clamp range (input range for the DAC)
+  float step;    // quantisation step (0 for an all-zero row)
+  float stepc;   // max(step, tiny): the divisor
+  float rstep;   // RN(1 / stepc)
+  int clampit;   // clamp to +-bound first
+  int quantise;  // resolution given
+  int no_rounding;
+};
+template <int DT>
+AL_HD QuantSeg dac_prepare(float ir, float inp_res, bool static_clamp, bool no_rounding) {
+  QuantSeg q;
+  q.bound = ir;
+  q.clampit = static_clamp ? 1 : 0;
+  q.quantise = inp_res > 0.0f ? 1 : 0;
+  q.no_rounding = no_rounding ? 1 : 0;
+  q.step = q.quantise ? quant_step<DT>(ir, inp_res) : 1.0f;
+  q.stepc = q.step < kTiny ? kTiny : q.step;
+  q.rstep = frcp(q.stepc);
+  return q;
+}
+// Same value as dac<DT>(x, ...) for every non-NaN x; NaN passes through unchanged.
+template <int DT>
+AL_HD float dac_apply(const QuantSeg& q, float x, float* code_out) {
+  float v = x;
+  if (q.clampit) v = fminf(fmaxf(v, -q.bound), q.bound);
+  float c = v;
+  if (q.quantise) {
+    c = rnd_int<DT>(fdiv_rcp(v, q.stepc, q.rstep));
+    if (!q.no_rounding) c = frint_add(c);
+    v = rnd_int<DT>(fmul(c, q.step));
+  }
+  if (x != x) { v = x; c = x; }
+  if (code_out) *code_out = c;
+  return v;
+}
+
 // Weight discretisation of one element.  `scale` = tile abs-max or channel abs-max (already a
 // DT value), n_states = float(max(res, 1/res)) and max_state = float(n_states/2) evaluated in
 // double by the host like the Python reference does, all_gt1 = whether every scale/n_states
@@ -173,6 +250,48 @@ AL_HD float discretize(float w, float scale, float n_states, float max_state, bo
 template <int DT>
 AL_HD bool discretize_scale_gt1(float scale, float n_states) {
   return rnd<DT>(fdiv(scale, n_states)) > 1.0f;
+}
+
+// Weight-modifier constants of one (channel, tile) segment, hoisted out of the element loop.
+struct WeightSeg {
+  int quant, noise, no_rounding;
+  float res, resc, rres, max_state;  // discretiser: step, max(step, tiny), RN(1/.), clamp
+  float amp;                         // noise amplitude rnd(std_dev * scale)
+};
+template <int DT>
+AL_HD WeightSeg weight_prepare(int quant_type, float q_scale, float n_states, float max_state,
+                               bool all_gt1, int noise_type, float std_dev, float n_scale,
+                               bool no_rounding) {
+  WeightSeg s;
+  s.quant = quant_type != 0;
+  s.noise = noise_type != 0;
+  s.no_rounding = no_rounding ? 1 : 0;
+  s.res = 1.0f;
+  if (s.quant) {
+    float res = rnd<DT>(fdiv(q_scale, n_states));
+    res = all_gt1 ? rnd<DT>(fdiv(2.0f, res)) : rnd<DT>(fmul(2.0f, res));
+    if (res == 0.0f) res = 1.0f;
+    s.res = res;
+  }
+  s.resc = s.res < kTiny ? kTiny : s.res;
+  s.rres = frcp(s.resc);
+  s.max_state = rnd<DT>(max_state);
+  s.amp = rnd<DT>(fmul(std_dev, n_scale));
+  return s;
+}
+// Same value as discretize<DT> followed by add_weight_noise<DT> for non-NaN weights.
+template <int DT>
+AL_HD float weight_apply(const WeightSeg& s, float w, float xi) {
+  float v = w;
+  if (s.quant) {
+    v = rnd_int<DT>(fdiv_rcp(v, s.resc, s.rres));
+    v = fminf(fmaxf(v, -s.max_state), s.max_state);
+    if (!s.no_rounding) v = frint_add(v);
+    v = rnd_int<DT>(fmul(v, s.res));
+  }
+  if (s.noise) v = rnd_int<DT>(fadd(v, rnd_int<DT>(fmul(s.amp, xi))));
+  if (w != w) v = w;
+  return v;
 }
 
 // Additive weight noise: w + (std_dev * s) * xi.

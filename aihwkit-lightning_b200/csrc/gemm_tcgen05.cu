@@ -52,7 +52,9 @@ constexpr int B_B_BYTES = B_BN * BK * 2;   // 32 KiB
 constexpr int B_STAGE_BYTES = B_A_BYTES + B_B_BYTES;
 constexpr int B_BOX_BYTES = 64 * BK * 2;   // one 64x64 MN-major box: 8 KiB
 constexpr int B_EPI_WARPS = 4;
-constexpr int B_XFORM_THREADS = 128;
+constexpr int B_XFORM_THREADS = 128;   // per group; each group handles one stage at a time
+constexpr int B_XFORM_GROUPS = 2;
+constexpr int kBwdThreads = (8 + 4 * B_XFORM_GROUPS) * 32;
 
 constexpr int kTmemCols = 512;
 
@@ -575,7 +577,7 @@ struct BwdTcParams {
 };
 
 template <bool WGRAD>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
               const BwdTcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -590,7 +592,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
   if (threadIdx.x == 0) {
     for (int s = 0; s < B_STAGES; ++s) {
       mbar_init(&bars->full[s], 1);
-      mbar_init(&bars->ready[s], B_XFORM_THREADS);
+      mbar_init(&bars->ready[s], B_XFORM_THREADS / 32);
       mbar_init(&bars->empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -755,21 +757,23 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     }
   } else if (warp >= 8 && masked) {
     // ---- mask transform: zero the gradient entries the tile's ADC clamp blocked ---------
-    // Thread r owns one 128-byte row of the staged A tile.  The two mask words of that row are
-    // fetched two stages ahead, so that their L2 latency is off the TMA -> MMA critical path.
-    const int r = threadIdx.x - 8 * 32;  // 0..127
+    // B_XFORM_GROUPS groups of 128 threads take the stage-iterations round robin, so that
+    // the fix-up of consecutive stages overlaps.  Within a group thread r owns one 128-byte
+    // row of the staged A tile; the two mask words of that row are fetched one turn ahead so
+    // that their L2 latency is off the TMA -> MMA critical path.
+    const int grp = (warp - 8) >> 2;
+    const int r = threadIdx.x - (8 + 4 * grp) * 32;  // 0..127
     const int row_in_box = WGRAD ? (r & 63) : r;
     const int box = WGRAD ? (r >> 6) : 0;
     const int total = ((num_work - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * p.lsteps;
-    // cursor of the prefetch (runs two stage-iterations ahead of the consumer)
-    int pf_w = blockIdx.x, pf_ls = 0, pf_count = 0;
-    auto fetch = [&](uint32_t* lo, uint32_t* hi) {
+    auto fetch = [&](int it, uint32_t* lo, uint32_t* hi) {
       *lo = 0xffffffffu;
       *hi = 0xffffffffu;
-      if (pf_count < total) {
-        const int ib = pf_w / (p.T * p.num_jb);
-        const int t = (pf_w % (p.T * p.num_jb)) / p.num_jb;
-        const int l0 = pf_ls * BK;
+      if (it < total) {
+        const int w = blockIdx.x + (it / p.lsteps) * gridDim.x;
+        const int l0 = (it % p.lsteps) * BK;
+        const int ib = w / (p.T * p.num_jb);
+        const int t = (w % (p.T * p.num_jb)) / p.num_jb;
         const int m = WGRAD ? l0 + row_in_box : ib * BM + r;
         const int n0 = WGRAD ? ib * BM + box * 64 : l0;
         if (m < p.M) {
@@ -779,47 +783,36 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           if (w0 + 1 < p.mask_words) *hi = mrow[w0 + 1];
         }
       }
-      ++pf_count;
-      if (++pf_ls == p.lsteps) {
-        pf_ls = 0;
-        pf_w += gridDim.x;
-      }
     };
-    uint32_t lo0, hi0, lo1, hi1, lo2, hi2;
-    fetch(&lo0, &hi0);
-    fetch(&lo1, &hi1);
+    uint32_t lo0, hi0, lo1, hi1;
+    fetch(grp, &lo0, &hi0);
     uint8_t* const row_base = stage_base + box * B_BOX_BYTES + row_in_box * 128;
     const int sw = r & 7;  // 128-byte swizzle: 16-byte chunk index is XORed with row % 8
-    for (int it = 0; it < total; ++it) {
-      fetch(&lo2, &hi2);
+    for (int it = grp; it < total; it += B_XFORM_GROUPS) {
+      fetch(it + B_XFORM_GROUPS, &lo1, &hi1);
       const int s = it % B_STAGES;
       const uint32_t ph = ((uint32_t)it / B_STAGES) & 1u;
       if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
         raise_error(kErrTransform, abort_flag);
         break;
       }
-      if ((lo0 & hi0) != 0xffffffffu) {
-        uint8_t* row_ptr = row_base + s * B_STAGE_BYTES;
-        const uint64_t bits = (uint64_t)lo0 | ((uint64_t)hi0 << 32);
-#pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
-          const uint32_t byte = (uint32_t)(bits >> (8 * c)) & 0xffu;
-          if (byte == 0xffu) continue;
-          uint4* chunk = reinterpret_cast<uint4*>(row_ptr + ((c ^ sw) << 4));
-          uint4 v = *chunk;
-          uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const uint32_t keep_lo = (byte >> (2 * e)) & 1u, keep_hi = (byte >> (2 * e + 1)) & 1u;
-            wv[e] &= (keep_lo ? 0x0000ffffu : 0u) | (keep_hi ? 0xffff0000u : 0u);
-          }
-          *chunk = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+      uint64_t zeros = ~((uint64_t)lo0 | ((uint64_t)hi0 << 32));
+      if (zeros != 0ull) {
+        // one 2-byte store of zero per blocked element (typically one or two per row)
+        const uint32_t row_addr = smem_u32(row_base + s * B_STAGE_BYTES);
+        while (zeros != 0ull) {
+          const int pos = __ffsll((long long)zeros) - 1;  // n - n0 of the blocked element
+          zeros &= zeros - 1ull;
+          const uint32_t addr = row_addr + (uint32_t)((((pos >> 3) ^ sw) << 4) + ((pos & 7) << 1));
+          asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)0) : "memory");
         }
         fence_proxy_async_smem();
       }
-      mbar_arrive(&bars->ready[s]);
-      lo0 = lo1; hi0 = hi1;
-      lo1 = lo2; hi1 = hi2;
+      // one arrival per warp: 128 arrivals on one mbarrier would serialise in shared memory
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->ready[s]);
+      lo0 = lo1;
+      hi0 = hi1;
     }
   }
 
@@ -1011,9 +1004,9 @@ static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint
   int work = p.num_ib * p.T * p.num_jb;
   int grid = work < sm_count() ? work : sm_count();
   if (wgrad)
-    bwd_tc_kernel<true><<<grid, kThreads, B_SMEM, s>>>(map_a, map_b, p);
+    bwd_tc_kernel<true><<<grid, kBwdThreads, B_SMEM, s>>>(map_a, map_b, p);
   else
-    bwd_tc_kernel<false><<<grid, kThreads, B_SMEM, s>>>(map_a, map_b, p);
+    bwd_tc_kernel<false><<<grid, kBwdThreads, B_SMEM, s>>>(map_a, map_b, p);
   return check_launch(wgrad ? "wgrad_tc" : "dgrad_tc");
 }
 

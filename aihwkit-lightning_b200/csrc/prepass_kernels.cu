@@ -1,7 +1,8 @@
 // Operand pre-passes of the analog GEMM: the DAC (input range + input quantisation) that
 // turns x into the GEMM's A operand, and the weight modifier (discretisation + additive
 // Gaussian noise) that turns w into the B operand.  Both stream their operand once: one warp
-// per (row, tile) segment, 128-bit loads/stores on the aligned body.
+// per (row, tile) segment, 128-bit loads/stores on the aligned body, per-segment constants
+// (quantisation step, its reciprocal, noise amplitude) computed once per warp.
 #include "analog_math.cuh"
 #include "internal.h"
 
@@ -36,26 +37,33 @@ struct Pack<kBF16> {
       v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
   }
+  // values are already exactly representable in bf16: packing is a pure bit move
   static __device__ __forceinline__ void store(void* p, const float v[8]) {
     uint32_t w[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
-      w[i] = (uint32_t)f32_to_bf16_bits(v[2 * i]) | ((uint32_t)f32_to_bf16_bits(v[2 * i + 1]) << 16);
+      w[i] = (__float_as_uint(v[2 * i]) >> 16) | (__float_as_uint(v[2 * i + 1]) & 0xffff0000u);
     *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 };
 
 // Geometry of one segment as seen by a warp: scalar head, vector body, scalar tail.  All
-// arrays that are walked together (input, output, optional extras) share the element offset,
-// so they share the alignment as long as their base pointers are 16-byte aligned.
+// arrays that are walked together (input, output, noise) share the element offset, so they
+// share the alignment as long as their base pointers are 16-byte aligned.
 struct SegPlan {
   int head, nvec, done;
 };
 template <int DT>
-__device__ __forceinline__ SegPlan plan_segment(int64_t start, int len) {
+__device__ __forceinline__ SegPlan plan_segment(int64_t start, int len, bool aligned_base) {
   constexpr int VN = Pack<DT>::N;
-  int mis = (int)(start % VN);
   SegPlan p;
+  if (!aligned_base) {  // everything through the scalar path
+    p.head = len;
+    p.nvec = 0;
+    p.done = len;
+    return p;
+  }
+  int mis = (int)(start % VN);
   p.head = mis == 0 ? 0 : VN - mis;
   if (p.head > len) p.head = len;
   p.nvec = (len - p.head) / VN;
@@ -65,24 +73,19 @@ __device__ __forceinline__ SegPlan plan_segment(int64_t start, int len) {
 
 template <int DT>
 __device__ __forceinline__ float warp_abs_max(const void* a, int64_t start, int len, int lane,
-                                              bool aligned_base) {
+                                              const SegPlan& p) {
   constexpr int VN = Pack<DT>::N;
   constexpr int ES = 16 / VN;
   float m = 0.0f;
-  if (aligned_base) {
-    SegPlan p = plan_segment<DT>(start, len);
-    if (lane < p.head) m = fabsf(Elem<DT>::load(a, start + lane));
-    const char* body = reinterpret_cast<const char*>(a) + (start + p.head) * ES;
-    for (int v = lane; v < p.nvec; v += 32) {
-      float x[VN];
-      Pack<DT>::load(body + (int64_t)v * 16, x);
+  for (int i = lane; i < p.head; i += 32) m = fmaxf(m, fabsf(Elem<DT>::load(a, start + i)));
+  const char* body = reinterpret_cast<const char*>(a) + (start + p.head) * ES;
+  for (int v = lane; v < p.nvec; v += 32) {
+    float x[VN];
+    Pack<DT>::load(body + (int64_t)v * 16, x);
 #pragma unroll
-      for (int i = 0; i < VN; ++i) m = fmaxf(m, fabsf(x[i]));
-    }
-    for (int i = p.done + lane; i < len; i += 32) m = fmaxf(m, fabsf(Elem<DT>::load(a, start + i)));
-  } else {
-    for (int i = lane; i < len; i += 32) m = fmaxf(m, fabsf(Elem<DT>::load(a, start + i)));
+    for (int i = 0; i < VN; ++i) m = fmaxf(m, fabsf(x[i]));
   }
+  for (int i = p.done + lane; i < len; i += 32) m = fmaxf(m, fabsf(Elem<DT>::load(a, start + i)));
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   return m;
@@ -103,39 +106,33 @@ dac_kernel(const void* __restrict__ x, int M, int K, TileTable tt, int ir_mode,
   int m = (int)(seg / tt.T), t = (int)(seg % tt.T);
   int lo = tt.lo(t), len = tt.hi(t) - lo;
   int64_t start = (int64_t)m * K + lo;
+  const SegPlan p = plan_segment<DT>(start, len, aligned_base != 0 && codes == nullptr);
   float ir = 0.0f;
   bool clampit = false;
   if (ir_mode == AL_IR_DYNAMIC) {
-    ir = warp_abs_max<DT>(x, start, len, lane, aligned_base != 0);
+    ir = warp_abs_max<DT>(x, start, len, lane, p);
     if (lane == 0) Elem<DT>::store(ir_rows, (int64_t)t * M + m, ir);
   } else if (ir_mode == AL_IR_STATIC) {
     ir = Elem<DT>::load(ir_static, t);
     clampit = true;
   }
-  const bool nr = no_rounding != 0;
-  if (aligned_base && codes == nullptr) {
-    SegPlan p = plan_segment<DT>(start, len);
-    if (lane < p.head)
-      Elem<DT>::store(xq, start + lane, dac<DT>(Elem<DT>::load(x, start + lane), ir, inp_res, clampit, nr, nullptr));
-    const char* src = reinterpret_cast<const char*>(x) + (start + p.head) * ES;
-    char* dst = reinterpret_cast<char*>(xq) + (start + p.head) * ES;
-    for (int v = lane; v < p.nvec; v += 32) {
-      float a[VN];
-      Pack<DT>::load(src + (int64_t)v * 16, a);
-#pragma unroll
-      for (int i = 0; i < VN; ++i) a[i] = dac<DT>(a[i], ir, inp_res, clampit, nr, nullptr);
-      Pack<DT>::store(dst + (int64_t)v * 16, a);
-    }
-    for (int i = p.done + lane; i < len; i += 32)
-      Elem<DT>::store(xq, start + i, dac<DT>(Elem<DT>::load(x, start + i), ir, inp_res, clampit, nr, nullptr));
-  } else {
-    for (int i = lane; i < len; i += 32) {
-      float c;
-      float q = dac<DT>(Elem<DT>::load(x, start + i), ir, inp_res, clampit, nr, &c);
-      Elem<DT>::store(xq, start + i, q);
-      if (codes) Elem<DT>::store(codes, start + i, c);
-    }
+  const QuantSeg q = dac_prepare<DT>(ir, inp_res, clampit, no_rounding != 0);
+  for (int i = lane; i < p.head; i += 32) {
+    float c;
+    Elem<DT>::store(xq, start + i, dac_apply<DT>(q, Elem<DT>::load(x, start + i), &c));
+    if (codes) Elem<DT>::store(codes, start + i, c);
   }
+  const char* src = reinterpret_cast<const char*>(x) + (start + p.head) * ES;
+  char* dst = reinterpret_cast<char*>(xq) + (start + p.head) * ES;
+  for (int v = lane; v < p.nvec; v += 32) {
+    float a[VN];
+    Pack<DT>::load(src + (int64_t)v * 16, a);
+#pragma unroll
+    for (int i = 0; i < VN; ++i) a[i] = dac_apply<DT>(q, a[i], nullptr);
+    Pack<DT>::store(dst + (int64_t)v * 16, a);
+  }
+  for (int i = p.done + lane; i < len; i += 32)
+    Elem<DT>::store(xq, start + i, dac_apply<DT>(q, Elem<DT>::load(x, start + i), nullptr));
 }
 
 // w_mod[n, tile] = noise(discretise(w[n, tile]))
@@ -146,7 +143,9 @@ weight_modify_kernel(const void* __restrict__ w, int N, int K, TileTable tt,
                      const int32_t* __restrict__ flags, int quant_type, float n_states,
                      float max_state, int noise_type, float std_dev,
                      const void* __restrict__ w_noise, uint64_t seed, uint64_t offset,
-                     int no_rounding, void* __restrict__ w_mod) {
+                     int no_rounding, void* __restrict__ w_mod, int aligned_base) {
+  constexpr int VN = Pack<DT>::N;
+  constexpr int ES = 16 / VN;
   int64_t seg = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   int lane = threadIdx.x & 31;
   if (seg >= (int64_t)N * tt.T) return;
@@ -155,20 +154,47 @@ weight_modify_kernel(const void* __restrict__ w, int N, int K, TileTable tt,
   int64_t start = (int64_t)n * K + lo;
   float row_max = Elem<DT>::load(w_amax, (int64_t)t * N + n);
   float t_max = rnd<DT>(tile_max[t]);
-  float q_scale = quant_type == AL_QUANT_DISCRETIZE ? t_max : row_max;
-  float n_scale = noise_type == AL_NOISE_ADD_NORMAL ? t_max : row_max;
-  bool gt1 = flags[t] != 0;
-  const bool nr = no_rounding != 0;
-  for (int i = lane; i < len; i += 32) {
-    float v = Elem<DT>::load(w, start + i);
-    if (quant_type != AL_QUANT_NONE) v = discretize<DT>(v, q_scale, n_states, max_state, gt1, nr);
-    if (noise_type != AL_NOISE_NONE) {
-      float xi = w_noise ? Elem<DT>::load(w_noise, start + i)
-                         : rnd<DT>(normal1(seed, offset, 0u, (uint64_t)(start + i)));
-      v = add_weight_noise<DT>(v, std_dev, n_scale, xi);
+  const WeightSeg ws = weight_prepare<DT>(
+      quant_type, quant_type == AL_QUANT_DISCRETIZE ? t_max : row_max, n_states, max_state,
+      flags[t] != 0, noise_type, std_dev, noise_type == AL_NOISE_ADD_NORMAL ? t_max : row_max,
+      no_rounding != 0);
+  const SegPlan p = plan_segment<DT>(start, len, aligned_base != 0);
+  auto one = [&](int i) {
+    float xi = 0.0f;
+    if (ws.noise)
+      xi = w_noise ? Elem<DT>::load(w_noise, start + i)
+                   : rnd<DT>(normal1(seed, offset, 0u, (uint64_t)(start + i)));
+    Elem<DT>::store(w_mod, start + i, weight_apply<DT>(ws, Elem<DT>::load(w, start + i), xi));
+  };
+  for (int i = lane; i < p.head; i += 32) one(i);
+  const char* src = reinterpret_cast<const char*>(w) + (start + p.head) * ES;
+  const char* nsrc = reinterpret_cast<const char*>(w_noise) + (start + p.head) * ES;
+  char* dst = reinterpret_cast<char*>(w_mod) + (start + p.head) * ES;
+  for (int v = lane; v < p.nvec; v += 32) {
+    float a[VN], xi[VN];
+    Pack<DT>::load(src + (int64_t)v * 16, a);
+    if (ws.noise) {
+      if (w_noise) {
+        Pack<DT>::load(nsrc + (int64_t)v * 16, xi);
+      } else {
+        // the vector starts at a multiple of VN elements, i.e. on a group-of-four boundary
+        const uint64_t g0 = (uint64_t)(start + p.head + (int64_t)v * VN) >> 2;
+#pragma unroll
+        for (int g = 0; g < VN / 4; ++g) {
+          normal4(seed, offset, 0u, g0 + g, &xi[4 * g]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) xi[4 * g + e] = rnd_int<DT>(xi[4 * g + e]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < VN; ++i) xi[i] = 0.0f;
     }
-    Elem<DT>::store(w_mod, start + i, v);
+#pragma unroll
+    for (int i = 0; i < VN; ++i) a[i] = weight_apply<DT>(ws, a[i], xi[i]);
+    Pack<DT>::store(dst + (int64_t)v * 16, a);
   }
+  for (int i = p.done + lane; i < len; i += 32) one(i);
 }
 
 inline unsigned seg_blocks(int64_t segs) { return (unsigned)((segs + kWarpsPerBlock - 1) / kWarpsPerBlock); }
@@ -196,10 +222,11 @@ int launch_weight_modify(int dtype, const void* w, int N, int K, const TileTable
                          int no_rounding, void* w_mod, cudaStream_t s) {
   ProfScope prof(AL_K_WEIGHT_MODIFY, s);
   int64_t segs = (int64_t)N * tt.T;
+  int aligned = aligned16(w) && aligned16(w_mod) && (w_noise == nullptr || aligned16(w_noise));
   if (dtype == AL_F32)
-    weight_modify_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, flags, quant_type, n_states, max_state, noise_type, std_dev, w_noise, seed, offset, no_rounding, w_mod);
+    weight_modify_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, flags, quant_type, n_states, max_state, noise_type, std_dev, w_noise, seed, offset, no_rounding, w_mod, aligned);
   else
-    weight_modify_kernel<kBF16><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, flags, quant_type, n_states, max_state, noise_type, std_dev, w_noise, seed, offset, no_rounding, w_mod);
+    weight_modify_kernel<kBF16><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, flags, quant_type, n_states, max_state, noise_type, std_dev, w_noise, seed, offset, no_rounding, w_mod, aligned);
   return check_launch("weight_modify");
 }
 

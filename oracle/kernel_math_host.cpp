@@ -26,9 +26,10 @@ static void dac_rows(const void* x, int M, int K, const int* ends, int T, int ir
         ir = Elem<DT>::load(ir_static, t);
         clampit = true;
       }
+      const QuantSeg seg = dac_prepare<DT>(ir, inp_res, clampit, no_rounding != 0);
       for (int k = lo; k < hi; ++k) {
         float c;
-        float q = dac<DT>(Elem<DT>::load(x, (int64_t)m * K + k), ir, inp_res, clampit, no_rounding != 0, &c);
+        float q = dac_apply<DT>(seg, Elem<DT>::load(x, (int64_t)m * K + k), &c);
         Elem<DT>::store(xq, (int64_t)m * K + k, q);
         if (codes) Elem<DT>::store(codes, (int64_t)m * K + k, c);
       }
@@ -55,11 +56,13 @@ static void weight_modify_rows(const void* w, int N, int K, const int* ends, int
     if (quant_type == 0) all_gt1 = false;
     for (int n = 0; n < N; ++n) {
       float r = Elem<DT>::load(amax_out, (int64_t)t * N + n);
+      const WeightSeg ws = weight_prepare<DT>(quant_type, quant_type == 1 ? t_max : r, n_states, max_state,
+                                              all_gt1, noise_type, std_dev, noise_type == 1 ? t_max : r,
+                                              no_rounding != 0);
       for (int k = lo; k < hi; ++k) {
         float v = Elem<DT>::load(w, (int64_t)n * K + k);
-        if (quant_type) v = discretize<DT>(v, quant_type == 1 ? t_max : r, n_states, max_state, all_gt1, no_rounding != 0);
-        if (noise_type) v = add_weight_noise<DT>(v, std_dev, noise_type == 1 ? t_max : r, Elem<DT>::load(w_noise, (int64_t)n * K + k));
-        Elem<DT>::store(w_mod, (int64_t)n * K + k, v);
+        float xi = noise_type ? Elem<DT>::load(w_noise, (int64_t)n * K + k) : 0.0f;
+        Elem<DT>::store(w_mod, (int64_t)n * K + k, weight_apply<DT>(ws, v, xi));
       }
     }
   }
@@ -112,6 +115,28 @@ void km_tile_stage(int dtype, const float* acc, int M, int N, const void* ir, in
   cfg.out_res = out_res;
   if (dtype == kF32) tile_stage<kF32>(acc, M, N, ir, ir_per_row, s_noise, s_noise_per_col, s_bound, s_bound_per_col, xi, &cfg, out, keep);
   else tile_stage<kBF16>(acc, M, N, ir, ir_per_row, s_noise, s_noise_per_col, s_bound, s_bound_per_col, xi, &cfg, out, keep);
+}
+
+// Reciprocal-based division and add-based rint against the plain operations: returns the
+// number of mismatches over n pairs drawn from a xorshift stream (exponents in [-20, 20]).
+long long km_check_fast_ops(long long n, unsigned long long seed) {
+  unsigned long long s = seed ? seed : 88172645463325252ull;
+  long long bad = 0;
+  for (long long i = 0; i < n; ++i) {
+    uint32_t bits[2];
+    for (int j = 0; j < 2; ++j) {
+      s ^= s << 13; s ^= s >> 7; s ^= s << 17;
+      uint32_t m = (uint32_t)s & 0x7fffffu;
+      int e = (int)((s >> 23) % 41) - 20;
+      bits[j] = ((uint32_t)(s >> 63) << 31) | ((uint32_t)(e + 127) << 23) | m;
+    }
+    float a = u2f(bits[0]), b = fabsf(u2f(bits[1]));
+    if (fdiv_rcp(a, b, frcp(b)) != fdiv(a, b)) ++bad;
+    float x = a * 64.0f;
+    if (frint_add(x) != frint(x)) ++bad;
+    if (rnd_int<kBF16>(a) != rnd<kBF16>(a)) ++bad;
+  }
+  return bad;
 }
 
 // n standard normals of stream `stream` of call (seed, offset), element indices [0, n)

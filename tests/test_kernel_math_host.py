@@ -29,7 +29,7 @@ def km():
     hdr = os.path.join(ROOT, "aihwkit-lightning_b200", "csrc", "analog_math.cuh")
     if not os.path.exists(lib) or os.path.getmtime(lib) < max(os.path.getmtime(src), os.path.getmtime(hdr)):
         subprocess.check_call(
-            ["g++", "-O2", "-ffp-contract=off", "-shared", "-fPIC", "-x", "c++", src, "-o", lib]
+            ["g++", "-O2", "-mfma", "-ffp-contract=off", "-shared", "-fPIC", "-x", "c++", src, "-o", lib]
         )
     return ctypes.CDLL(lib)
 
@@ -114,6 +114,14 @@ def test_host_build_of_kernel_math_matches_golden(km, name):
                          ctypes.c_float(noise_coef), ctypes.c_float(case["out_bound"]),
                          ctypes.c_float(case["out_res"]), ptr(out), ptr(keep))
         assert same(out, tr["out_t"].reshape(m, n)), f"tile output {t}"
+
+
+def test_fast_division_rint_and_rounding_are_exact(km):
+    """The streaming kernels divide through a correctly rounded reciprocal (Markstein), round to
+    integers with two additions and round to bf16 with integer adds; all three must agree with
+    the plain operations bit for bit."""
+    km.km_check_fast_ops.restype = ctypes.c_longlong
+    assert km.km_check_fast_ops(ctypes.c_longlong(20_000_000), ctypes.c_ulonglong(12345)) == 0
 
 
 def test_generator_moments(km):
