@@ -353,11 +353,11 @@ AL_HD uint32_t mulhi32(uint32_t a, uint32_t b) {
   return (uint32_t)(((uint64_t)a * (uint64_t)b) >> 32);
 #endif
 }
-AL_HD Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
-                            uint32_t k1) {
+template <int ROUNDS>
+AL_HD Philox4 philox4x32(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1) {
   const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
 #pragma unroll
-  for (int r = 0; r < 10; ++r) {
+  for (int r = 0; r < ROUNDS; ++r) {
     uint32_t hi0 = mulhi32(M0, c0), lo0 = M0 * c0;
     uint32_t hi1 = mulhi32(M1, c2), lo1 = M1 * c2;
     uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
@@ -367,6 +367,10 @@ AL_HD Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, 
   Philox4 out;
   out.v[0] = c0; out.v[1] = c1; out.v[2] = c2; out.v[3] = c3;
   return out;
+}
+AL_HD Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
+                            uint32_t k1) {
+  return philox4x32<10>(c0, c1, c2, c3, k0, k1);
 }
 
 // Two standard normals from two 32-bit words (Box-Muller).

@@ -254,11 +254,15 @@ __device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-// Four standard normals of group `group` (same counter layout as al::normal4), with the
-// uniform->float conversions done by bit manipulation and approximate transcendentals.
-__device__ __forceinline__ void box_muller_fast(uint32_t a, uint32_t b, float* z0, float* z1) {
-  const float u1 = 2.0f - __uint_as_float(0x3f800000u | (a >> 9));  // (0, 1]
-  const float u2 = __uint_as_float(0x3f800000u | (b >> 9)) - 1.0f;  // [0, 1)
+// Output-noise generator of the forward epilogue: one Philox4x32-7 call (seven rounds are the
+// fewest that pass BigCrush in Salmon et al.) yields eight 16-bit uniforms, i.e. four
+// Box-Muller pairs = eight standard normals for eight consecutive columns.  Uniforms are turned
+// into floats by bit manipulation; logarithm, square root and sine/cosine use the approximate
+// hardware functions.  The 16-bit radius limits a draw to |z| < 4.71.
+__device__ __forceinline__ void box_muller16(uint32_t ab, float* z0, float* z1) {
+  // low 16 bits -> radius, high 16 bits -> angle
+  const float u1 = 2.0f - __uint_as_float(0x3f800000u | ((ab & 0xffffu) << 7));   // (0, 1], step 2^-16
+  const float u2 = __uint_as_float(0x3f800000u | ((ab >> 16) << 7)) - 1.0f;       // [0, 1)
   float r;
   asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(-1.3862943611198906f * __log2f(u1)));
   float s, c;
@@ -266,14 +270,28 @@ __device__ __forceinline__ void box_muller_fast(uint32_t a, uint32_t b, float* z
   *z0 = r * c;
   *z1 = r * s;
 }
-__device__ __forceinline__ void normal4_fast(uint64_t seed, uint64_t offset, uint32_t stream, uint64_t group,
-                                             float z[4]) {
-  Philox4 p = philox4x32_10((uint32_t)group, (uint32_t)(group >> 32), (uint32_t)offset,
-                            (uint32_t)(offset >> 32) ^ (stream * 0x85EBCA6Bu), (uint32_t)seed,
-                            (uint32_t)(seed >> 32));
-  box_muller_fast(p.v[0], p.v[1], &z[0], &z[1]);
-  box_muller_fast(p.v[2], p.v[3], &z[2], &z[3]);
+__device__ __forceinline__ void normal8_fast(uint64_t seed, uint64_t offset, uint32_t stream, uint64_t group8,
+                                             float z[8]) {
+  const Philox4 p = philox4x32<7>((uint32_t)group8, (uint32_t)(group8 >> 32), (uint32_t)offset,
+                                  (uint32_t)(offset >> 32) ^ (stream * 0x85EBCA6Bu) ^ 0x5bd1e995u,
+                                  (uint32_t)seed, (uint32_t)(seed >> 32));
+#pragma unroll
+  for (int i = 0; i < 4; ++i) box_muller16(p.v[i], &z[2 * i], &z[2 * i + 1]);
 }
+// 8-column (packed bf16x2 running sum) variants of the TMEM load / store
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t r[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t r[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
+               ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
+__device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 h) { return *reinterpret_cast<uint32_t*>(&h); }
 
 struct Barriers {
   uint64_t full[8];
@@ -460,45 +478,80 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const float stepc = step < kTiny ? kTiny : step;
         const float rstep = __frcp_rn(stepc);
         uint32_t keep_bits = 0;
+        const bool packed = RD == kBF16 && !per_channel;  // bf16x2 arithmetic, bf16x2 running sum
+        const __nv_bfloat162 sc2 = __float2bfloat162_rn(sc), step2 = __float2bfloat162_rn(step);
+        const __nv_bfloat162 bound2 = __float2bfloat162_rn(bound), nbound2 = __float2bfloat162_rn(-bound);
+        const __nv_bfloat162 zero2 = __float2bfloat162_rn(0.0f);
 #pragma unroll 1
         for (int h = 0; h < 2; ++h) {
           const int cc = col0 + h * 16;
           const int nh = n0 + h * 16;
           uint32_t accr[16], sumr[16];
           tmem_ld16(tmem_base + lane_base + (uint32_t)(b * F_BN + cc), accr);
-          if (t > 0) tmem_ld16(tmem_base + lane_base + (uint32_t)(2 * F_BN + cc), sumr);
+          if (t > 0) {
+            if (packed) tmem_ld8(tmem_base + lane_base + (uint32_t)(2 * F_BN + (cc >> 1)), sumr);
+            else tmem_ld16(tmem_base + lane_base + (uint32_t)(2 * F_BN + cc), sumr);
+          }
           tmem_wait_ld();
           float z[16];
           if (ep.has_noise) {
 #pragma unroll
-            for (int g4 = 0; g4 < 4; ++g4) {
-              const int nq = nh + g4 * 4;
+            for (int g8 = 0; g8 < 2; ++g8) {
+              const int nq = nh + g8 * 8;
               const uint64_t idx = ((uint64_t)t * M + (row_ok ? m : 0)) * N + (nq < N ? nq : 0);
               if (ep.out_noise) {
-                const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(ep.out_noise) + idx);
-                z[g4 * 4 + 0] = __uint_as_float(raw.x << 16);
-                z[g4 * 4 + 1] = __uint_as_float(raw.x & 0xffff0000u);
-                z[g4 * 4 + 2] = __uint_as_float(raw.y << 16);
-                z[g4 * 4 + 3] = __uint_as_float(raw.y & 0xffff0000u);
-              } else {
-                normal4_fast(ep.seed, ep.offset, 1u, idx >> 2, &z[g4 * 4]);
+                const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(ep.out_noise) + idx);
+                const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                for (int q = 0; q < 4; ++q) z[g4 * 4 + q] = rnd_alu<RD>(z[g4 * 4 + q]);
+                for (int q = 0; q < 4; ++q) {
+                  z[g8 * 8 + 2 * q] = __uint_as_float(rw[q] << 16);
+                  z[g8 * 8 + 2 * q + 1] = __uint_as_float(rw[q] & 0xffff0000u);
+                }
+              } else {
+                normal8_fast(ep.seed, ep.offset, 1u, idx >> 3, &z[g8 * 8]);
               }
             }
           }
-          if (!per_channel) {
+          if (packed) {
+#pragma unroll
+            for (int pr = 0; pr < 8; ++pr) {
+              // element 2*pr in the low half, 2*pr+1 in the high half
+              __nv_bfloat162 o2 = __floats2bfloat162_rn(__uint_as_float(accr[2 * pr]), __uint_as_float(accr[2 * pr + 1]));
+              if (ep.has_noise) {
+                const __nv_bfloat162 z2 = __floats2bfloat162_rn(z[2 * pr], z[2 * pr + 1]);
+                o2 = __hadd2_rn(o2, __hmul2_rn(sc2, z2));
+              }
+              if (ep.has_adc) {
+                const float q_lo = fdiv_rcp(__low2float(o2), stepc, rstep);
+                const float q_hi = fdiv_rcp(__high2float(o2), stepc, rstep);
+                const __nv_bfloat162 q2 = __floats2bfloat162_rn(q_lo, q_hi);
+                float c_lo = __low2float(q2), c_hi = __high2float(q2);
+                if (!ep.no_rounding) {
+                  c_lo = rint_magic(c_lo);
+                  c_hi = rint_magic(c_hi);
+                }
+                // an integer-rounded bf16 value is a bf16 value: packing is a bit move
+                const uint32_t c2 = (__float_as_uint(c_lo) >> 16) | (__float_as_uint(c_hi) & 0xffff0000u);
+                o2 = __hmul2_rn(as_bf162(c2), step2);
+              }
+              uint32_t keep2 = 3u;
+              if (ep.has_bound) {
+                const uint32_t msk = __hle2_mask(__habs2(o2), bound2);
+                keep2 = (msk & 1u) | ((msk >> 15) & 2u);
+                o2 = __hmin2_nan(__hmax2_nan(o2, nbound2), bound2);
+              }
+              keep_bits |= keep2 << (h * 16 + 2 * pr);
+              sumr[pr] = as_u32(__hadd2_rn(t == 0 ? zero2 : as_bf162(sumr[pr]), o2));
+            }
+          } else if (!per_channel) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const float acc = __uint_as_float(accr[j]);
               float o = rnd_alu<RD>(acc);
-              if (ep.has_noise) o = rnd_alu<RD>(fadd(o, rnd_alu<RD>(fmul(sc, z[j]))));
+              if (ep.has_noise) o = rnd_alu<RD>(fadd(o, rnd_alu<RD>(fmul(sc, rnd_alu<RD>(z[j])))));
               bool keep = true;
               if (ep.has_adc) {
-                // o / stepc, correctly rounded from the correctly rounded reciprocal
-                const float q0 = fmul(o, rstep);
-                const float q = fmaf(fmaf(-q0, stepc, o), rstep, q0);
-                float code = rnd_alu<RD>(q);
+                float code = rnd_alu<RD>(fdiv_rcp(o, stepc, rstep));
                 if (!ep.no_rounding) code = rint_magic(code);
                 o = rnd_alu<RD>(fmul(code, step));
               }
@@ -518,28 +571,44 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
               const float cmax = n < N ? Elem<kBF16>::load(ep.w_amax, (int64_t)t * N + n) : 0.0f;
               bool keep;
               const float o = tile_epilogue<RD>(__uint_as_float(accr[j]), ir, ep.noise_pc ? cmax : t_max,
-                                                ep.bound_pc ? cmax : t_max, ep.has_noise ? z[j] : 0.0f, cfg, &keep);
+                                                ep.bound_pc ? cmax : t_max, ep.has_noise ? rnd<RD>(z[j]) : 0.0f,
+                                                cfg, &keep);
               sumr[j] = __float_as_uint(t == 0 ? fadd(0.0f, o) : rnd<RD>(fadd(__uint_as_float(sumr[j]), o)));
               keep_bits |= (keep ? 1u : 0u) << (h * 16 + j);
             }
           }
           if (t < T - 1) {
-            tmem_st16(tmem_base + lane_base + (uint32_t)(2 * F_BN + cc), sumr);
+            if (packed) tmem_st8(tmem_base + lane_base + (uint32_t)(2 * F_BN + (cc >> 1)), sumr);
+            else tmem_st16(tmem_base + lane_base + (uint32_t)(2 * F_BN + cc), sumr);
           } else if (row_ok) {
             // final: bias, convert, store 16 bf16 = 32 bytes of this row
             uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + (int64_t)m * N + nh;
 #pragma unroll
             for (int v = 0; v < 2; ++v) {
               if (nh + v * 8 < N) {
-                float f[8];
+                uint32_t w4[4];
+                if (packed) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  f[e] = __uint_as_float(sumr[v * 8 + e]);
-                  if (ep.bias) f[e] = fadd(rnd<RD>(f[e]), Elem<kBF16>::load(ep.bias, nh + v * 8 + e));
+                  for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 s2 = as_bf162(sumr[v * 4 + e]);
+                    if (ep.bias) {
+                      const uint32_t b2 = *reinterpret_cast<const uint32_t*>(
+                          reinterpret_cast<const uint16_t*>(ep.bias) + nh + v * 8 + 2 * e);
+                      s2 = __hadd2_rn(s2, as_bf162(b2));
+                    }
+                    w4[e] = as_u32(s2);
+                  }
+                } else {
+                  float f[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    f[e] = __uint_as_float(sumr[v * 8 + e]);
+                    if (ep.bias) f[e] = fadd(rnd<RD>(f[e]), Elem<kBF16>::load(ep.bias, nh + v * 8 + e));
+                  }
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) w4[e] = pack_bf16x2_rn(f[2 * e], f[2 * e + 1]);
                 }
-                *reinterpret_cast<uint4*>(dst + v * 8) =
-                    make_uint4(pack_bf16x2_rn(f[0], f[1]), pack_bf16x2_rn(f[2], f[3]),
-                               pack_bf16x2_rn(f[4], f[5]), pack_bf16x2_rn(f[6], f[7]));
+                *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
               }
             }
           }

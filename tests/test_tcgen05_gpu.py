@@ -104,3 +104,70 @@ def test_tcgen05_internal_noise_statistics():
     z = delta / var.sqrt()[:, None]
     assert abs(z.mean().item()) < 0.02
     assert abs(z.std().item() - 1.0) < 0.03
+
+
+def _dyadic_problem(m, k, n, tile, seed=0):
+    """Inputs for which every product and partial sum of the GEMM is exact in fp32, so that the
+    result does not depend on the accumulation order: per (row, tile) the inputs are integers
+    with abs-max exactly 127 (dynamic range -> DAC step exactly 1, codes = inputs), weights are
+    multiples of 1/64 in [-1, 1]."""
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randint(-126, 127, (m, k), generator=gen).float()
+    for t in range(k // tile):
+        x[:, t * tile] = 127.0 * (1 - 2 * torch.randint(0, 2, (m,), generator=gen)).float()
+    w = torch.randint(-64, 65, (n, k), generator=gen).float() / 64.0
+    w[:, ::tile] = 1.0  # abs-max of every (channel, tile) exactly 1
+    g = torch.randint(-8, 9, (m, n), generator=gen).float() / 8.0
+    return x.bfloat16(), w.bfloat16(), g.bfloat16()
+
+
+@pytest.mark.parametrize("variant", ["adc_noise", "noise_only", "adc_eval", "static_adc_noise"])
+def test_order_independent_problem_is_bit_exact(variant):
+    """With an order-independent GEMM the whole per-tile chain (bf16 rounding after every op,
+    replayed noise, ADC division / rint / clamp, running sum) must equal the CPU oracle bit for
+    bit on both engines, and the clamp masks must make the backward GEMMs agree exactly too."""
+    from aihwkit_lightning_b200.nn import AnalogLinear
+    from aihwkit_lightning_b200.nn import functional as F
+    import analog_oracle as O
+    from util import NS
+
+    m, k, n, tile = 256, 512, 384, 128
+    x, w, g = _dyadic_problem(m, k, n, tile)
+    case = dict(C.DEFAULTS)
+    case.update(dtype="bf16", max_input_size=tile, ir_dynamic=True, bias=False, inp_res=254.0)
+    if variant in ("adc_noise", "static_adc_noise"):
+        case.update(out_bound=12.0, out_res=254.0, out_noise=0.05)
+    elif variant == "noise_only":
+        case.update(out_noise=0.05)
+    else:
+        case.update(out_bound=12.0, out_res=254.0, training=False)
+    if variant == "static_adc_noise":
+        case.update(ir_dynamic=False, ir_init_value=127.0, ir_decay=0.0)
+    rpu = C.build_rpu_config(NS, case)
+    gen = torch.Generator().manual_seed(5)
+    t_count = k // tile
+    out_noise = torch.randn(t_count, m, n, generator=gen).bfloat16()
+    in_sizes = [tile] * t_count
+    ir = idx = None
+    if not case["ir_dynamic"]:
+        ir = torch.full((t_count,), 127.0, dtype=torch.bfloat16)
+        idx = torch.zeros(t_count, dtype=torch.bfloat16)
+    rec = O.forward(x, w, None, ir, idx, None, None, in_sizes, case["training"], rpu,
+                    O.NoiseReplay(None, out_noise))
+    grads = O.backward(rec, g, w, False, ir, rpu)
+    clipped = sum(int(((tr.pre_clamp < -tr.bound) | (tr.pre_clamp > tr.bound)).sum()) for tr in rec.tiles
+                  if tr.pre_clamp is not None)
+    if case["out_bound"] > 0:
+        assert clipped > 0, "the test problem should exercise the ADC clamp"
+    for engine in ("tcgen05", "simt"):
+        layer = AnalogLinear(k, n, bias=False, rpu_config=rpu).to(device="cuda", dtype=torch.bfloat16)
+        layer.set_weights(w.cuda())
+        layer.train(case["training"])
+        xin = x.cuda().requires_grad_(True)
+        with F.operator_settings(engine=engine, out_noise=out_noise):
+            out = layer(xin)
+        out.backward(g.cuda())
+        assert device_error() == (0, 0)
+        assert torch.equal(out.detach().cpu(), rec.out), f"{engine}: forward differs"
+        assert torch.equal(xin.grad.cpu(), grads["grad_x"]), f"{engine}: grad_x differs"
+        assert torch.equal(layer.weight.grad.cpu(), grads["grad_w"]), f"{engine}: grad_w differs"
