@@ -259,21 +259,29 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     }
     tile_max = (float*)a->w_tile_max;
     int32_t* flags = (int32_t*)(tile_max + d.T);
-    rc = launch_abs_max_tiles(d.dtype, a->w, d.N, d.K, tt, a->w_amax, s);
-    if (rc) return rc;
-    rc = launch_tile_max(d.dtype, a->w_amax, d.N, tt, dv.weight_quant, dv.n_states, tile_max, flags, s);
-    if (rc) return rc;
-    if (dv.weight_quant != AL_QUANT_NONE || dv.weight_noise != AL_NOISE_NONE) {
-      if (!a->w_mod || a->w_mod == a->w) {
-        set_error("al_forward: w_mod workspace missing (the modifier never writes into w)");
-        return AL_ERR_BAD_ARGUMENT;
-      }
-      rc = launch_weight_modify(d.dtype, a->w, d.N, d.K, tt, a->w_amax, tile_max, flags,
-                                dv.weight_quant, dv.n_states, dv.max_state, dv.weight_noise,
-                                dv.std_dev, a->w_noise, a->seed, a->offset, d.no_rounding, a->w_mod, s);
-      if (rc) return rc;
-      w_mod = a->w_mod;
+    const bool modifies = dv.weight_quant != AL_QUANT_NONE || dv.weight_noise != AL_NOISE_NONE;
+    if (modifies && (!a->w_mod || a->w_mod == a->w)) {
+      set_error("al_forward: w_mod workspace missing (the modifier never writes into w)");
+      return AL_ERR_BAD_ARGUMENT;
     }
+    if (dv.weight_quant == AL_QUANT_NONE && dv.weight_noise != AL_NOISE_ADD_NORMAL) {
+      // every scale the modifier needs is the segment's own abs-max: one sweep over w
+      rc = launch_weight_fused(d.dtype, a->w, d.N, d.K, tt, a->w_amax, tile_max, dv.weight_noise,
+                               dv.std_dev, a->w_noise, a->seed, a->offset, modifies ? a->w_mod : nullptr, s);
+      if (rc) return rc;
+    } else {
+      rc = launch_abs_max_tiles(d.dtype, a->w, d.N, d.K, tt, a->w_amax, s);
+      if (rc) return rc;
+      rc = launch_tile_max(d.dtype, a->w_amax, d.N, tt, dv.weight_quant, dv.n_states, tile_max, flags, s);
+      if (rc) return rc;
+      if (modifies) {
+        rc = launch_weight_modify(d.dtype, a->w, d.N, d.K, tt, a->w_amax, tile_max, flags,
+                                  dv.weight_quant, dv.n_states, dv.max_state, dv.weight_noise,
+                                  dv.std_dev, a->w_noise, a->seed, a->offset, d.no_rounding, a->w_mod, s);
+        if (rc) return rc;
+      }
+    }
+    if (modifies) w_mod = a->w_mod;
   }
 
   // 4. tiled GEMM with the per-tile output stage

@@ -23,6 +23,7 @@
 #include <cudaTypedefs.h>
 
 #include "analog_math.cuh"
+#include "device_fast.cuh"
 #include "internal.h"
 
 namespace al {
@@ -254,30 +255,6 @@ __device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-// Output-noise generator of the forward epilogue: one Philox4x32-7 call (seven rounds are the
-// fewest that pass BigCrush in Salmon et al.) yields eight 16-bit uniforms, i.e. four
-// Box-Muller pairs = eight standard normals for eight consecutive columns.  Uniforms are turned
-// into floats by bit manipulation; logarithm, square root and sine/cosine use the approximate
-// hardware functions.  The 16-bit radius limits a draw to |z| < 4.71.
-__device__ __forceinline__ void box_muller16(uint32_t ab, float* z0, float* z1) {
-  // low 16 bits -> radius, high 16 bits -> angle
-  const float u1 = 2.0f - __uint_as_float(0x3f800000u | ((ab & 0xffffu) << 7));   // (0, 1], step 2^-16
-  const float u2 = __uint_as_float(0x3f800000u | ((ab >> 16) << 7)) - 1.0f;       // [0, 1)
-  float r;
-  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(-1.3862943611198906f * __log2f(u1)));
-  float s, c;
-  __sincosf(6.283185307179586f * u2, &s, &c);
-  *z0 = r * c;
-  *z1 = r * s;
-}
-__device__ __forceinline__ void normal8_fast(uint64_t seed, uint64_t offset, uint32_t stream, uint64_t group8,
-                                             float z[8]) {
-  const Philox4 p = philox4x32<7>((uint32_t)group8, (uint32_t)(group8 >> 32), (uint32_t)offset,
-                                  (uint32_t)(offset >> 32) ^ (stream * 0x85EBCA6Bu) ^ 0x5bd1e995u,
-                                  (uint32_t)seed, (uint32_t)(seed >> 32));
-#pragma unroll
-  for (int i = 0; i < 4; ++i) box_muller16(p.v[i], &z[2 * i], &z[2 * i + 1]);
-}
 // 8-column (packed bf16x2 running sum) variants of the TMEM load / store
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t r[8]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
@@ -290,8 +267,6 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t r[8]) {
                ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(taddr)
                : "memory");
 }
-__device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
-__device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 h) { return *reinterpret_cast<uint32_t*>(&h); }
 
 struct Barriers {
   uint64_t full[8];

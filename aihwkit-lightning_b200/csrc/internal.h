@@ -83,6 +83,11 @@ int launch_weight_modify(int dtype, const void* w, int N, int K, const TileTable
                          float std_dev, const void* w_noise, uint64_t seed, uint64_t offset,
                          int no_rounding, void* w_mod, cudaStream_t s);
 
+// abs-max + tile max + (per-channel-scaled) noise in one sweep; w_mod may be null when noise is off
+int launch_weight_fused(int dtype, const void* w, int N, int K, const TileTable& tt, void* w_amax,
+                        float* tile_max, int noise_type, float std_dev, const void* w_noise,
+                        uint64_t seed, uint64_t offset, void* w_mod, cudaStream_t s);
+
 // ---- SIMT GEMMs (gemm_simt.cu) ------------------------------------------------------------
 int launch_fwd_simt(int dtype, int round_dt, const void* xq, const void* w_mod, int K,
                     const TileTable& tt, const FwdEpilogueParams& ep, void* out, cudaStream_t s);

@@ -4,6 +4,7 @@
 // per (row, tile) segment, 128-bit loads/stores on the aligned body, per-segment constants
 // (quantisation step, its reciprocal, noise amplitude) computed once per warp.
 #include "analog_math.cuh"
+#include "device_fast.cuh"
 #include "internal.h"
 
 namespace al {
@@ -79,11 +80,24 @@ __device__ __forceinline__ float warp_abs_max(const void* a, int64_t start, int 
   float m = 0.0f;
   for (int i = lane; i < p.head; i += 32) m = fmaxf(m, fabsf(Elem<DT>::load(a, start + i)));
   const char* body = reinterpret_cast<const char*>(a) + (start + p.head) * ES;
-  for (int v = lane; v < p.nvec; v += 32) {
-    float x[VN];
-    Pack<DT>::load(body + (int64_t)v * 16, x);
+  if (DT == kBF16) {
+    // packed: |x| and max on two bf16 at a time
+    __nv_bfloat162 m2 = __float2bfloat162_rn(0.0f);
+    for (int v = lane; v < p.nvec; v += 32) {
+      const uint4 q = *reinterpret_cast<const uint4*>(body + (int64_t)v * 16);
+      m2 = __hmax2(m2, __habs2(as_bf162(q.x)));
+      m2 = __hmax2(m2, __habs2(as_bf162(q.y)));
+      m2 = __hmax2(m2, __habs2(as_bf162(q.z)));
+      m2 = __hmax2(m2, __habs2(as_bf162(q.w)));
+    }
+    m = fmaxf(m, fmaxf(__low2float(m2), __high2float(m2)));
+  } else {
+    for (int v = lane; v < p.nvec; v += 32) {
+      float x[VN];
+      Pack<DT>::load(body + (int64_t)v * 16, x);
 #pragma unroll
-    for (int i = 0; i < VN; ++i) m = fmaxf(m, fabsf(x[i]));
+      for (int i = 0; i < VN; ++i) m = fmaxf(m, fabsf(x[i]));
+    }
   }
   for (int i = p.done + lane; i < len; i += 32) m = fmaxf(m, fabsf(Elem<DT>::load(a, start + i)));
 #pragma unroll
@@ -97,7 +111,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 dac_kernel(const void* __restrict__ x, int M, int K, TileTable tt, int ir_mode,
            const void* __restrict__ ir_static, float inp_res, int no_rounding,
            void* __restrict__ xq, void* __restrict__ ir_rows, void* __restrict__ codes,
-           int aligned_base) {
+           int aligned_base, int small_codes) {
   constexpr int VN = Pack<DT>::N;
   constexpr int ES = 16 / VN;
   int64_t seg = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
@@ -124,12 +138,43 @@ dac_kernel(const void* __restrict__ x, int M, int K, TileTable tt, int ir_mode,
   }
   const char* src = reinterpret_cast<const char*>(x) + (start + p.head) * ES;
   char* dst = reinterpret_cast<char*>(xq) + (start + p.head) * ES;
-  for (int v = lane; v < p.nvec; v += 32) {
-    float a[VN];
-    Pack<DT>::load(src + (int64_t)v * 16, a);
+  if (DT == kBF16) {
+    // bf16x2 arithmetic: a correctly rounded bf16 multiply equals "fp32 multiply, round to
+    // bf16" for bf16 operands (the fp32 product is exact), the same holds for clamp; the
+    // quotient goes through fp32 (reciprocal-based exact division) and one packed conversion
+    const __nv_bfloat162 b2 = __float2bfloat162_rn(q.bound), nb2 = __float2bfloat162_rn(-q.bound);
+    const __nv_bfloat162 step2 = __float2bfloat162_rn(q.step);
+    for (int v = lane; v < p.nvec; v += 32) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + (int64_t)v * 16);
+      uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int i = 0; i < VN; ++i) a[i] = dac_apply<DT>(q, a[i], nullptr);
-    Pack<DT>::store(dst + (int64_t)v * 16, a);
+      for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 x2 = as_bf162(w[i]);
+        if (q.clampit) x2 = __hmin2_nan(__hmax2_nan(x2, nb2), b2);
+        if (q.quantise) {
+          const __nv_bfloat162 q2 = __floats2bfloat162_rn(fdiv_rcp(__low2float(x2), q.stepc, q.rstep),
+                                                          fdiv_rcp(__high2float(x2), q.stepc, q.rstep));
+          float c_lo = __low2float(q2), c_hi = __high2float(q2);
+          if (!q.no_rounding) {
+            c_lo = small_codes ? rint_small(c_lo) : frint_add(c_lo);
+            c_hi = small_codes ? rint_small(c_hi) : frint_add(c_hi);
+          }
+          // an integer-rounded (or already bf16) value packs by a bit move
+          const uint32_t c2 = (__float_as_uint(c_lo) >> 16) | (__float_as_uint(c_hi) & 0xffff0000u);
+          x2 = __hmul2_rn(as_bf162(c2), step2);
+        }
+        w[i] = as_u32(x2);
+      }
+      *reinterpret_cast<uint4*>(dst + (int64_t)v * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  } else {
+    for (int v = lane; v < p.nvec; v += 32) {
+      float a[VN];
+      Pack<DT>::load(src + (int64_t)v * 16, a);
+#pragma unroll
+      for (int i = 0; i < VN; ++i) a[i] = dac_apply<DT>(q, a[i], nullptr);
+      Pack<DT>::store(dst + (int64_t)v * 16, a);
+    }
   }
   for (int i = p.done + lane; i < len; i += 32)
     Elem<DT>::store(xq, start + i, dac_apply<DT>(q, Elem<DT>::load(x, start + i), nullptr));
@@ -197,6 +242,78 @@ weight_modify_kernel(const void* __restrict__ w, int N, int K, TileTable tt,
   for (int i = p.done + lane; i < len; i += 32) one(i);
 }
 
+// Weight pre-pass in one sweep, for modifiers whose scale is the segment's own abs-max (or
+// that do nothing): per (channel, tile) segment the warp computes the abs-max, stores it,
+// folds it into the tile's abs-max with an integer atomicMax (exact and order independent for
+// non-negative floats) and, if weight noise is on, writes w + (std_dev * abs-max) * xi.
+template <int DT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+weight_fused_kernel(const void* __restrict__ w, int N, int K, TileTable tt, void* __restrict__ w_amax,
+                    float* __restrict__ tile_max, int noise_type, float std_dev,
+                    const void* __restrict__ w_noise, uint64_t seed, uint64_t offset,
+                    void* __restrict__ w_mod, int aligned_base) {
+  constexpr int VN = Pack<DT>::N;
+  constexpr int ES = 16 / VN;
+  int64_t seg = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
+  if (seg >= (int64_t)N * tt.T) return;
+  int n = (int)(seg / tt.T), t = (int)(seg % tt.T);
+  int lo = tt.lo(t), len = tt.hi(t) - lo;
+  int64_t start = (int64_t)n * K + lo;
+  const SegPlan p = plan_segment<DT>(start, len, aligned_base != 0);
+  const float row_max = warp_abs_max<DT>(w, start, len, lane, p);
+  if (lane == 0) {
+    Elem<DT>::store(w_amax, (int64_t)t * N + n, row_max);
+    atomicMax(reinterpret_cast<unsigned int*>(tile_max) + t, __float_as_uint(row_max));
+  }
+  if (noise_type == AL_NOISE_NONE) return;
+  const WeightSeg ws = weight_prepare<DT>(AL_QUANT_NONE, row_max, 1.0f, 1.0f, false, noise_type, std_dev,
+                                          row_max, false);
+  auto one = [&](int i) {
+    float xi = w_noise ? Elem<DT>::load(w_noise, start + i)
+                       : rnd<DT>(normal1(seed, offset, 0u, (uint64_t)(start + i)));
+    Elem<DT>::store(w_mod, start + i, weight_apply<DT>(ws, Elem<DT>::load(w, start + i), xi));
+  };
+  for (int i = lane; i < p.head; i += 32) one(i);
+  const char* src = reinterpret_cast<const char*>(w) + (start + p.head) * ES;
+  const char* nsrc = reinterpret_cast<const char*>(w_noise) + (start + p.head) * ES;
+  char* dst = reinterpret_cast<char*>(w_mod) + (start + p.head) * ES;
+  for (int v = lane; v < p.nvec; v += 32) {
+    float xi[8];
+    if (w_noise) {
+      float tmp[VN];
+      Pack<DT>::load(nsrc + (int64_t)v * 16, tmp);
+#pragma unroll
+      for (int i = 0; i < VN; ++i) xi[i] = tmp[i];
+    } else {
+      // VN == 8: one group of eight; VN == 4: the half of the group this vector covers
+      const uint64_t e0 = (uint64_t)(start + p.head + (int64_t)v * VN);
+      float z[8];
+      normal8_fast(seed, offset, 0u, e0 >> 3, z);
+#pragma unroll
+      for (int i = 0; i < VN; ++i) xi[i] = z[(VN == 8 ? 0 : (int)(e0 & 4)) + i];
+    }
+    if (DT == kBF16) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + (int64_t)v * 16);
+      uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+      const __nv_bfloat162 amp2 = __float2bfloat162_rn(ws.amp);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 z2 = __floats2bfloat162_rn(xi[2 * i], xi[2 * i + 1]);
+        wv[i] = as_u32(__hadd2_rn(as_bf162(wv[i]), __hmul2_rn(amp2, z2)));
+      }
+      *reinterpret_cast<uint4*>(dst + (int64_t)v * 16) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+    } else {
+      float a[VN];
+      Pack<DT>::load(src + (int64_t)v * 16, a);
+#pragma unroll
+      for (int i = 0; i < VN; ++i) a[i] = weight_apply<DT>(ws, a[i], xi[i]);
+      Pack<DT>::store(dst + (int64_t)v * 16, a);
+    }
+  }
+  for (int i = p.done + lane; i < len; i += 32) one(i);
+}
+
 inline unsigned seg_blocks(int64_t segs) { return (unsigned)((segs + kWarpsPerBlock - 1) / kWarpsPerBlock); }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -208,10 +325,13 @@ int launch_dac(int dtype, const void* x, int M, int K, const TileTable& tt, int 
   ProfScope prof(AL_K_DAC, s);
   int64_t segs = (int64_t)M * tt.T;
   int aligned = aligned16(x) && aligned16(xq);
+  // |code| <= max(inp_res, 1/inp_res)/2 + 1: the guard-free rint needs that below 2^22
+  float states = inp_res > 0.0f ? (inp_res > 1.0f ? inp_res : 1.0f / inp_res) : 0.0f;
+  int small_codes = states < 4.0e6f;
   if (dtype == AL_F32)
-    dac_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(x, M, K, tt, ir_mode, ir_static, inp_res, no_rounding, xq, ir_rows, codes, aligned);
+    dac_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(x, M, K, tt, ir_mode, ir_static, inp_res, no_rounding, xq, ir_rows, codes, aligned, small_codes);
   else
-    dac_kernel<kBF16><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(x, M, K, tt, ir_mode, ir_static, inp_res, no_rounding, xq, ir_rows, codes, aligned);
+    dac_kernel<kBF16><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(x, M, K, tt, ir_mode, ir_static, inp_res, no_rounding, xq, ir_rows, codes, aligned, small_codes);
   return check_launch("dac");
 }
 
@@ -228,6 +348,25 @@ int launch_weight_modify(int dtype, const void* w, int N, int K, const TileTable
   else
     weight_modify_kernel<kBF16><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, flags, quant_type, n_states, max_state, noise_type, std_dev, w_noise, seed, offset, no_rounding, w_mod, aligned);
   return check_launch("weight_modify");
+}
+
+int launch_weight_fused(int dtype, const void* w, int N, int K, const TileTable& tt, void* w_amax,
+                        float* tile_max, int noise_type, float std_dev, const void* w_noise,
+                        uint64_t seed, uint64_t offset, void* w_mod, cudaStream_t s) {
+  ProfScope prof(AL_K_WEIGHT_MODIFY, s);
+  // tile_max[T] floats followed by T int32 flags (zero: the discretiser is off on this path)
+  cudaError_t e = cudaMemsetAsync(tile_max, 0, 2 * sizeof(float) * tt.T, s);
+  if (e != cudaSuccess) {
+    set_error("weight_fused: memset: %s", cudaGetErrorString(e));
+    return AL_ERR_CUDA;
+  }
+  int64_t segs = (int64_t)N * tt.T;
+  int aligned = aligned16(w) && (w_mod == nullptr || aligned16(w_mod)) && (w_noise == nullptr || aligned16(w_noise));
+  if (dtype == AL_F32)
+    weight_fused_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, noise_type, std_dev, w_noise, seed, offset, w_mod, aligned);
+  else
+    weight_fused_kernel<kBF16><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, noise_type, std_dev, w_noise, seed, offset, w_mod, aligned);
+  return check_launch("weight_fused");
 }
 
 }  // namespace al
