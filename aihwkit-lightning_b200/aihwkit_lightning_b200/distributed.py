@@ -1,0 +1,114 @@
+"""Data-parallel plumbing of the analog layers: one process per GPU, rows (tokens) sharded
+across ranks, gradients summed with one collective per bucket.
+
+Every per-row quantity of the analog linear path (dynamic input range, DAC codes, ADC bound,
+output noise) is row-local, so a batch splits across ranks without any exchange inside the
+forward or backward kernels; the only exchange step of a training step is the all-reduce of
+the parameter gradients (weights, biases, learned input ranges).  The reference has no
+distributed code of its own -- its examples delegate to DeepSpeed / Accelerate
+(`examples/deepspeed_cifar10/cifar10_deepspeed.py:210-268`) -- so this module mirrors what
+those do for this path: flat gradient buckets, asynchronous all-reduce on the process group's
+stream while the rest of backward runs, averaging by the world size.
+
+Works with any ``torch.distributed`` backend (NCCL on GPUs, gloo in the CPU tests).
+"""
+from typing import Iterable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_rows(total_rows: int, rank: int, world_size: int) -> Tuple[int, int]:
+    """Half-open row range of ``rank`` when ``total_rows`` rows are split as evenly as possible
+    (the first ``total_rows % world_size`` ranks get one row more)."""
+    if not 0 <= rank < world_size:
+        raise ValueError(f"rank {rank} outside world of size {world_size}")
+    base, extra = divmod(total_rows, world_size)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def rank_seed(seed: int, rank: int) -> int:
+    """Per-rank generator seed: replicas must draw independent analog noise."""
+    return (seed * 1_000_003 + 7919 * (rank + 1)) & 0x7FFFFFFFFFFFFFFF
+
+
+class GradientBuckets:
+    """Flat-bucket gradient all-reduce for a fixed list of parameters.
+
+    ``reduce_async`` copies the gradients of one bucket into a flat buffer and launches one
+    all-reduce for it; ``finish`` waits for all launched buckets, divides by the world size
+    and copies the results back into ``param.grad``.  Buckets follow the reverse parameter
+    order (the order backward produces gradients in), capped at ``bucket_bytes``.
+    """
+
+    def __init__(self, params: Iterable[torch.nn.Parameter], bucket_bytes: int = 64 << 20,
+                 group: Optional[dist.ProcessGroup] = None, average: bool = True):
+        self.params: List[torch.nn.Parameter] = [p for p in params if p.requires_grad]
+        self.group = group
+        self.average = average
+        self.buckets: List[List[torch.nn.Parameter]] = []
+        current: List[torch.nn.Parameter] = []
+        size = 0
+        for p in reversed(self.params):
+            nbytes = p.numel() * p.element_size()
+            if current and (size + nbytes > bucket_bytes or p.dtype != current[0].dtype
+                            or p.device != current[0].device):
+                self.buckets.append(current)
+                current, size = [], 0
+            current.append(p)
+            size += nbytes
+        if current:
+            self.buckets.append(current)
+        self._flat: List[Optional[torch.Tensor]] = [None] * len(self.buckets)
+        self._pending: List[Tuple[int, "dist.Work"]] = []
+
+    def bucket_sizes(self) -> List[int]:
+        return [sum(p.numel() for p in b) for b in self.buckets]
+
+    def reduce_async(self, index: int) -> None:
+        bucket = self.buckets[index]
+        total = sum(p.numel() for p in bucket)
+        flat = self._flat[index]
+        if flat is None or flat.numel() != total:
+            flat = torch.empty(total, dtype=bucket[0].dtype, device=bucket[0].device)
+            self._flat[index] = flat
+        offset = 0
+        for p in bucket:
+            n = p.numel()
+            if p.grad is None:
+                flat[offset:offset + n].zero_()
+            else:
+                flat[offset:offset + n].copy_(p.grad.reshape(-1))
+            offset += n
+        work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        self._pending.append((index, work))
+
+    def reduce_all_async(self) -> None:
+        for i in range(len(self.buckets)):
+            self.reduce_async(i)
+
+    def finish(self) -> None:
+        world = dist.get_world_size(self.group)
+        for index, work in self._pending:
+            work.wait()
+            flat = self._flat[index]
+            if self.average:
+                flat.div_(world)
+            offset = 0
+            for p in self.buckets[index]:
+                n = p.numel()
+                if p.grad is None:
+                    p.grad = flat[offset:offset + n].reshape(p.shape).clone()
+                else:
+                    p.grad.copy_(flat[offset:offset + n].reshape(p.shape))
+                offset += n
+        self._pending.clear()
+
+
+def all_reduce_gradients(params: Sequence[torch.nn.Parameter], group: Optional[dist.ProcessGroup] = None,
+                         bucket_bytes: int = 64 << 20) -> None:
+    """One-shot helper: average the gradients of ``params`` over the group."""
+    buckets = GradientBuckets(params, bucket_bytes=bucket_bytes, group=group)
+    buckets.reduce_all_async()
+    buckets.finish()

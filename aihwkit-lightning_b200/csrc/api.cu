@@ -70,6 +70,10 @@ static int derive(const AlDesc& d, Derived* o) {
     return AL_ERR_BAD_ARGUMENT;
   }
   if (check_dtype(d.dtype)) return AL_ERR_BAD_ARGUMENT;
+  if ((int64_t)(d.M > d.N ? d.M : d.N) * (int64_t)(d.T > 0 ? d.T : 1) >= (1ll << 31)) {
+    set_error("rows * tiles = %lld exceeds 2^31 - 1 segments", (long long)(d.M > d.N ? d.M : d.N) * d.T);
+    return AL_ERR_TOO_LARGE;
+  }
   if (d.ir_mode < AL_IR_OFF || d.ir_mode > AL_IR_DYNAMIC) {
     set_error("unknown input-range mode %d", d.ir_mode);
     return AL_ERR_BAD_ARGUMENT;
@@ -163,6 +167,10 @@ int al_abs_max_tiles(int32_t dtype, const void* a, int32_t rows, int32_t K,
     set_error("al_abs_max_tiles: null pointer or empty matrix");
     return AL_ERR_BAD_ARGUMENT;
   }
+  if ((int64_t)rows * (int64_t)(T > 0 ? T : 1) >= (1ll << 31)) {
+    set_error("al_abs_max_tiles: rows * tiles exceeds 2^31 - 1 segments");
+    return AL_ERR_TOO_LARGE;
+  }
   TileTable tt;
   int rc = make_tile_table(tile_ends_host, T, K, &tt);
   if (rc) return rc;
@@ -178,6 +186,10 @@ int al_std_tiles(int32_t dtype, const void* a, int32_t rows, int32_t K,
   if (!a || !out || !scratch || rows < 1 || K < 1) {
     set_error("al_std_tiles: null pointer or empty matrix");
     return AL_ERR_BAD_ARGUMENT;
+  }
+  if ((int64_t)rows * (int64_t)(T > 0 ? T : 1) >= (1ll << 31)) {
+    set_error("al_std_tiles: rows * tiles exceeds 2^31 - 1 segments");
+    return AL_ERR_TOO_LARGE;
   }
   TileTable tt;
   int rc = make_tile_table(tile_ends_host, T, K, &tt);

@@ -40,10 +40,10 @@ __global__ void __launch_bounds__(256)
 static_ir_partial_kernel(const void* __restrict__ x, const void* __restrict__ ir_used,
                          void* __restrict__ grad_x, int M, int K, TileTable tt,
                          float* __restrict__ partial) {
-  int64_t seg = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const unsigned seg = blockIdx.x * 8 + (threadIdx.x >> 5);  // rows * T < 2^31 (checked by the host)
   int lane = threadIdx.x & 31;
-  if (seg >= (int64_t)M * tt.T) return;
-  int m = (int)(seg / tt.T), t = (int)(seg % tt.T);
+  if (seg >= (unsigned)M * (unsigned)tt.T) return;
+  const int m = (int)(seg / (unsigned)tt.T), t = (int)(seg - (unsigned)m * (unsigned)tt.T);
   int lo = tt.lo(t), len = tt.hi(t) - lo;
   int64_t start = (int64_t)m * K + lo;
   float ir = Elem<DT>::load(ir_used, t);

@@ -114,10 +114,10 @@ dac_kernel(const void* __restrict__ x, int M, int K, TileTable tt, int ir_mode,
            int aligned_base, int small_codes) {
   constexpr int VN = Pack<DT>::N;
   constexpr int ES = 16 / VN;
-  int64_t seg = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const unsigned seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);  // rows * T < 2^31 (checked by the host)
   int lane = threadIdx.x & 31;
-  if (seg >= (int64_t)M * tt.T) return;
-  int m = (int)(seg / tt.T), t = (int)(seg % tt.T);
+  if (seg >= (unsigned)M * (unsigned)tt.T) return;
+  const int m = (int)(seg / (unsigned)tt.T), t = (int)(seg - (unsigned)m * (unsigned)tt.T);
   int lo = tt.lo(t), len = tt.hi(t) - lo;
   int64_t start = (int64_t)m * K + lo;
   const SegPlan p = plan_segment<DT>(start, len, aligned_base != 0 && codes == nullptr);
@@ -191,10 +191,10 @@ weight_modify_kernel(const void* __restrict__ w, int N, int K, TileTable tt,
                      int no_rounding, void* __restrict__ w_mod, int aligned_base) {
   constexpr int VN = Pack<DT>::N;
   constexpr int ES = 16 / VN;
-  int64_t seg = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const unsigned seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);  // rows * T < 2^31 (checked by the host)
   int lane = threadIdx.x & 31;
-  if (seg >= (int64_t)N * tt.T) return;
-  int n = (int)(seg / tt.T), t = (int)(seg % tt.T);
+  if (seg >= (unsigned)N * (unsigned)tt.T) return;
+  const int n = (int)(seg / (unsigned)tt.T), t = (int)(seg - (unsigned)n * (unsigned)tt.T);
   int lo = tt.lo(t), len = tt.hi(t) - lo;
   int64_t start = (int64_t)n * K + lo;
   float row_max = Elem<DT>::load(w_amax, (int64_t)t * N + n);
@@ -254,10 +254,10 @@ weight_fused_kernel(const void* __restrict__ w, int N, int K, TileTable tt, void
                     void* __restrict__ w_mod, int aligned_base) {
   constexpr int VN = Pack<DT>::N;
   constexpr int ES = 16 / VN;
-  int64_t seg = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const unsigned seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);  // rows * T < 2^31 (checked by the host)
   int lane = threadIdx.x & 31;
-  if (seg >= (int64_t)N * tt.T) return;
-  int n = (int)(seg / tt.T), t = (int)(seg % tt.T);
+  if (seg >= (unsigned)N * (unsigned)tt.T) return;
+  const int n = (int)(seg / (unsigned)tt.T), t = (int)(seg - (unsigned)n * (unsigned)tt.T);
   int lo = tt.lo(t), len = tt.hi(t) - lo;
   int64_t start = (int64_t)n * K + lo;
   const SegPlan p = plan_segment<DT>(start, len, aligned_base != 0);

@@ -79,10 +79,10 @@ template <int DT>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 abs_max_tiles_kernel(const void* __restrict__ a, int rows, int K, TileTable tt,
                      void* __restrict__ out) {
-  int64_t seg = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const unsigned seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);  // rows * T < 2^31 (checked by the host)
   int lane = threadIdx.x & 31;
-  if (seg >= (int64_t)rows * tt.T) return;
-  int r = (int)(seg / tt.T), t = (int)(seg % tt.T);
+  if (seg >= (unsigned)rows * (unsigned)tt.T) return;
+  const int r = (int)(seg / (unsigned)tt.T), t = (int)(seg - (unsigned)r * (unsigned)tt.T);
   int lo = tt.lo(t), hi = tt.hi(t);
   float m = 0.0f;
   warp_scan_segment<DT>(a, (int64_t)r * K + lo, hi - lo, lane, [&](float v) { m = fmaxf(m, fabsf(v)); });
@@ -131,10 +131,10 @@ template <int DT>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 segment_moments_kernel(const void* __restrict__ a, int rows, int K, TileTable tt,
                        float* __restrict__ partial) {
-  int64_t seg = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const unsigned seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);  // rows * T < 2^31 (checked by the host)
   int lane = threadIdx.x & 31;
-  if (seg >= (int64_t)rows * tt.T) return;
-  int r = (int)(seg / tt.T), t = (int)(seg % tt.T);
+  if (seg >= (unsigned)rows * (unsigned)tt.T) return;
+  const int r = (int)(seg / (unsigned)tt.T), t = (int)(seg - (unsigned)r * (unsigned)tt.T);
   int lo = tt.lo(t), len = tt.hi(t) - lo;
   float s = 0.0f;
   warp_scan_segment<DT>(a, (int64_t)r * K + lo, len, lane, [&](float v) { s += v; });

@@ -11,7 +11,8 @@ algorithmic TFLOP/s = 6*M*K*N / time.
 
 * ``value``: inputs resident in HBM, CUDA-event timing over exactly K steps (max over ranks).
 * ``e2e``: the same step through the public ``AnalogLinear`` call with the batch in pinned
-  host memory: host->device copy of the inputs and a device->host read of the loss inside
+  host memory: every step uploads its batch (double-buffered on a copy stream, so the upload
+  of the next batch overlaps the current step) and reads the loss back to the host, all inside
   the timed region.
 * ``roofline``: the dominant kernel, timed live with CUDA events by the library's launch
   accounting, against the measured bf16 tensor peak.
@@ -78,7 +79,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -128,6 +129,14 @@ def cpu_reference_run(steps: int, warmup: int, rows: int):
     w = lin.weight.detach().bfloat16().requires_grad_(True)
     g = torch.randn(rows, N, generator=gen).bfloat16()
     in_sizes = O.split_sizes(K, MAX_IN)
+    # bound the whole run to a few minutes: time one step, then shrink the row sample if needed
+    t0 = time.perf_counter()
+    O.linear_autograd(x.clone().requires_grad_(True), w, None, None, None, in_sizes, True, rpu).backward(g)
+    first = time.perf_counter() - t0
+    budget_s = 150.0
+    if first * (warmup + steps) > budget_s:
+        rows = max(128, int(rows * budget_s / (first * (warmup + steps))) // 128 * 128)
+        x, g = x[:rows].contiguous(), g[:rows].contiguous()
     times = []
     for it in range(warmup + steps):
         xin = x.clone().requires_grad_(True)
@@ -186,8 +195,8 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -205,6 +214,7 @@ def main():
     import torch.distributed as dist
 
     from aihwkit_lightning_b200 import _lib
+    from aihwkit_lightning_b200.distributed import GradientBuckets, rank_seed
     from aihwkit_lightning_b200.nn import AnalogLinear
     from aihwkit_lightning_b200.nn import functional as F
     from aihwkit_lightning_b200.simulator import configs as cfg
@@ -221,37 +231,60 @@ def main():
     gen = torch.Generator().manual_seed(rank)
     x_host = torch.randn(M, K, generator=gen).bfloat16().pin_memory()
     g = torch.randn(M, N, generator=gen).bfloat16().to(dev)
-    torch.manual_seed(0)
+    torch.manual_seed(0)  # identical weights on every replica
     layer = AnalogLinear(K, N, bias=False, rpu_config=make_rpu_config(cfg)).to(device=dev, dtype=torch.bfloat16)
     layer.train()
+    torch.cuda.manual_seed(rank_seed(0, rank))  # independent analog noise per replica
+    buckets = GradientBuckets(layer.parameters()) if world > 1 else None
     x_dev = x_host.to(dev).requires_grad_(True)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev)
-
-    pending = []
 
     def step_resident():
         layer.weight.grad = None
         x_dev.grad = None
         out = layer(x_dev)
         out.backward(g)
-        if world > 1:
-            pending.append(dist.all_reduce(layer.weight.grad, async_op=True))
-            while len(pending) > 1:
-                pending.pop(0).wait()
+        if buckets is not None:
+            # the only exchange step of data-parallel training: sum the weight gradient over ranks
+            buckets.finish()  # previous step's all-reduce (overlapped with this step's kernels)
+            buckets.reduce_all_async()
 
     def drain():
-        while pending:
-            pending.pop(0).wait()
+        if buckets is not None:
+            buckets.finish()
+
+    # end to end: the batch lives in pinned host memory; the upload of batch i+1 is enqueued on
+    # a copy stream before step i runs (double buffering), every step reads its loss back.
+    copy_stream = torch.cuda.Stream(dev)
+    slots = [torch.empty(M, K, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    state = {"i": 0}
+
+    def upload(slot):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[slot])
+            slots[slot].copy_(x_host, non_blocking=True)
+            ready[slot].record(copy_stream)
 
     def step_e2e():
+        i = state["i"]
+        slot = i & 1
+        if i == 0:
+            upload(0)
+        upload(slot ^ 1)  # next batch, overlaps this step's kernels
+        stream.wait_event(ready[slot])
         layer.weight.grad = None
-        x = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        x = slots[slot].detach().requires_grad_(True)
         out = layer(x)
         loss = (out * g).sum(dtype=torch.float32)
         loss.backward()
-        if world > 1:
-            dist.all_reduce(layer.weight.grad)
+        consumed[slot].record(stream)
+        if buckets is not None:
+            buckets.reduce_all_async()
+            buckets.finish()
+        state["i"] = i + 1
         return float(loss.item())
 
     def timed(fn, steps, between=None):
@@ -300,6 +333,8 @@ def main():
     value = FLOP_PER_STEP * world / (ms_per_step * 1e-3) / 1e12
 
     # ---- end to end through the public API, batch in pinned host memory -------------------
+    for slot in range(2):
+        consumed[slot].record(stream)
     for _ in range(3):
         step_e2e()
     barrier()

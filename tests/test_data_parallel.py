@@ -1,0 +1,90 @@
+"""Host logic of the data-parallel path with two gloo ranks on the CPU: row sharding covers the
+batch exactly once, bucketed gradient all-reduce equals the mean of the per-rank gradients and
+leaves every replica with identical values, per-rank noise seeds differ."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from aihwkit_lightning_b200.distributed import GradientBuckets, all_reduce_gradients, rank_seed, shard_rows
+
+
+def test_shard_rows_partition():
+    for total, world in ((8192, 8), (10, 4), (3, 8), (0, 2), (17, 1)):
+        seen = []
+        for rank in range(world):
+            lo, hi = shard_rows(total, rank, world)
+            assert 0 <= lo <= hi <= total
+            seen.extend(range(lo, hi))
+        assert seen == list(range(total))
+        sizes = [shard_rows(total, r, world)[1] - shard_rows(total, r, world)[0] for r in range(world)]
+        assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        shard_rows(10, 4, 4)
+
+
+def test_rank_seeds_are_distinct():
+    assert len({rank_seed(0, r) for r in range(8)}) == 8
+    assert rank_seed(1, 0) != rank_seed(0, 0)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)  # identical parameters on every replica
+        shapes = [(24, 40), (24,), (3,), (9, 40), (9,), (5, 5)]
+        params = [torch.nn.Parameter(torch.randn(s)) for s in shapes]
+        params[3].requires_grad_(False)  # a frozen parameter must be skipped
+        gen = torch.Generator().manual_seed(100 + rank)  # per-rank gradients
+        for p in params:
+            if p.requires_grad:
+                p.grad = torch.randn(p.shape, generator=gen)
+        params[5].grad = None  # a parameter that received no gradient on this rank counts as zero
+        local = [None if p.grad is None else p.grad.clone() for p in params]
+
+        buckets = GradientBuckets(params, bucket_bytes=24 * 40 * 4 + 100)  # forces several buckets
+        assert len(buckets.buckets) >= 2
+        assert sum(buckets.bucket_sizes()) == sum(p.numel() for p in params if p.requires_grad)
+        buckets.reduce_all_async()
+        buckets.finish()
+
+        gathered = [None] * world
+        dist.all_gather_object(gathered, local)
+        for i, p in enumerate(params):
+            if not p.requires_grad:
+                assert p.grad is None
+                continue
+            want = sum((g[i] if g[i] is not None else torch.zeros(p.shape)) for g in gathered) / world
+            assert torch.allclose(p.grad, want, rtol=1e-6, atol=1e-7), i
+
+        # one-shot helper gives the same result
+        for p, g in zip(params, local):
+            if p.requires_grad:
+                p.grad = None if g is None else g.clone()
+        all_reduce_gradients(params)
+        torch.save([None if p.grad is None else p.grad for p in params], os.path.join(out_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_bucketed_all_reduce_two_gloo_ranks(tmp_path):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    a = torch.load(tmp_path / "r0.pt")
+    b = torch.load(tmp_path / "r1.pt")
+    for x, y in zip(a, b):
+        if x is None:
+            assert y is None
+        else:
+            assert torch.equal(x, y)  # replicas hold bit-identical averaged gradients
