@@ -287,6 +287,7 @@ __device__ __forceinline__ uint8_t* align_1024(uint8_t* p) {
 // forward
 // ---------------------------------------------------------------------------------------------
 struct FwdTcParams {
+  int32_t small_adc_codes;  // |ADC code| provably below 2^38: unguarded add-based rint is exact
   int32_t tile_w;      // width of every analog tile (all equal on this path)
   int32_t ksteps;      // ceil(tile_w / 64)
   int32_t num_mb, num_nb;
@@ -294,7 +295,10 @@ struct FwdTcParams {
   void* out;
 };
 
-template <int RD>
+// MODE >= 0: the output stage is fixed at compile time (bit 0 output noise from the internal
+// generator, bit 1 ADC quantisation, bit 2 clamp; reference rounding, per-tile scalar scales,
+// rounding on, small ADC codes).  MODE < 0: every switch is read at run time.
+template <int RD, int MODE>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
               const FwdTcParams p) {
@@ -419,7 +423,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     const int col0 = ((warp - 4) >> 2) * 32;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     const int M = ep.M, N = ep.N;
-    const bool per_channel = ep.w_amax != nullptr && (ep.noise_pc || ep.bound_pc);
+    constexpr bool kFixed = MODE >= 0;
+    const bool has_noise = kFixed ? (MODE & 1) != 0 : ep.has_noise != 0;
+    const bool has_adc = kFixed ? (MODE & 2) != 0 : ep.has_adc != 0;
+    const bool has_bound = kFixed ? (MODE & 4) != 0 : ep.has_bound != 0;
+    const bool replay = kFixed ? false : ep.out_noise != nullptr;
+    const bool no_round = kFixed ? false : ep.no_rounding != 0;
+    const bool small_codes = kFixed ? true : p.small_adc_codes != 0;
+    const bool per_channel = kFixed ? false : (ep.w_amax != nullptr && (ep.noise_pc || ep.bound_pc));
     TileEpilogueCfg cfg;
     cfg.has_noise = ep.has_noise; cfg.has_bound = ep.has_bound; cfg.has_adc = ep.has_adc;
     cfg.no_rounding = ep.no_rounding; cfg.noise_coef = ep.noise_coef; cfg.out_bound = ep.out_bound;
@@ -449,7 +460,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const float t_max = ep.w_tile_max ? ep.w_tile_max[t] : 0.0f;
         const float sc = rnd<RD>(fmul(t_max, rnd<RD>(fmul(ep.noise_coef, ir))));
         const float bound = rnd<RD>(fmul(rnd<RD>(fmul(ir, ep.out_bound)), t_max));
-        const float step = ep.has_adc ? quant_step<RD>(bound, ep.out_res) : 1.0f;
+        const float step = has_adc ? quant_step<RD>(bound, ep.out_res) : 1.0f;
         const float stepc = step < kTiny ? kTiny : step;
         const float rstep = __frcp_rn(stepc);
         uint32_t keep_bits = 0;
@@ -469,12 +480,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           }
           tmem_wait_ld();
           float z[16];
-          if (ep.has_noise) {
+          if (has_noise) {
 #pragma unroll
             for (int g8 = 0; g8 < 2; ++g8) {
               const int nq = nh + g8 * 8;
               const uint64_t idx = ((uint64_t)t * M + (row_ok ? m : 0)) * N + (nq < N ? nq : 0);
-              if (ep.out_noise) {
+              if (replay) {
                 const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(ep.out_noise) + idx);
                 const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -488,49 +499,53 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             }
           }
           if (packed) {
+            uint32_t kept = 0;  // bit 2*pr (low half) and bit 16 + 2*pr + 1 (high half): element kept
 #pragma unroll
             for (int pr = 0; pr < 8; ++pr) {
               // element 2*pr in the low half, 2*pr+1 in the high half
               __nv_bfloat162 o2 = __floats2bfloat162_rn(__uint_as_float(accr[2 * pr]), __uint_as_float(accr[2 * pr + 1]));
-              if (ep.has_noise) {
+              if (has_noise) {
                 const __nv_bfloat162 z2 = __floats2bfloat162_rn(z[2 * pr], z[2 * pr + 1]);
                 o2 = __hadd2_rn(o2, __hmul2_rn(sc2, z2));
               }
-              if (ep.has_adc) {
+              if (has_adc) {
                 const float q_lo = fdiv_rcp(__low2float(o2), stepc, rstep);
                 const float q_hi = fdiv_rcp(__high2float(o2), stepc, rstep);
                 const __nv_bfloat162 q2 = __floats2bfloat162_rn(q_lo, q_hi);
                 float c_lo = __low2float(q2), c_hi = __high2float(q2);
-                if (!ep.no_rounding) {
-                  c_lo = rint_magic(c_lo);
-                  c_hi = rint_magic(c_hi);
+                if (!no_round) {
+                  // bf16-valued codes: the unguarded add-based rint is exact below 2^38
+                  c_lo = small_codes ? rint_small(c_lo) : rint_magic(c_lo);
+                  c_hi = small_codes ? rint_small(c_hi) : rint_magic(c_hi);
                 }
                 // an integer-rounded bf16 value is a bf16 value: packing is a bit move
                 const uint32_t c2 = (__float_as_uint(c_lo) >> 16) | (__float_as_uint(c_hi) & 0xffff0000u);
                 o2 = __hmul2_rn(as_bf162(c2), step2);
               }
-              uint32_t keep2 = 3u;
-              if (ep.has_bound) {
-                const uint32_t msk = __hle2_mask(__habs2(o2), bound2);
-                keep2 = (msk & 1u) | ((msk >> 15) & 2u);
-                o2 = __hmin2_nan(__hmax2_nan(o2, nbound2), bound2);
+              if (has_bound) {
+                // kept <=> the clamp leaves the value unchanged (false for NaN, like the reference's
+                // -bound <= o <= bound)
+                const __nv_bfloat162 c2 = __hmin2_nan(__hmax2_nan(o2, nbound2), bound2);
+                kept |= __heq2_mask(c2, o2) & ((1u << (2 * pr)) | (1u << (17 + 2 * pr)));
+                o2 = c2;
               }
-              keep_bits |= keep2 << (h * 16 + 2 * pr);
               sumr[pr] = as_u32(__hadd2_rn(t == 0 ? zero2 : as_bf162(sumr[pr]), o2));
             }
+            if (!has_bound) kept = 0xffffffffu;
+            keep_bits |= ((kept | (kept >> 16)) & 0xffffu) << (h * 16);
           } else if (!per_channel) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const float acc = __uint_as_float(accr[j]);
               float o = rnd_alu<RD>(acc);
-              if (ep.has_noise) o = rnd_alu<RD>(fadd(o, rnd_alu<RD>(fmul(sc, rnd_alu<RD>(z[j])))));
+              if (has_noise) o = rnd_alu<RD>(fadd(o, rnd_alu<RD>(fmul(sc, rnd_alu<RD>(z[j])))));
               bool keep = true;
-              if (ep.has_adc) {
+              if (has_adc) {
                 float code = rnd_alu<RD>(fdiv_rcp(o, stepc, rstep));
-                if (!ep.no_rounding) code = rint_magic(code);
+                if (!no_round) code = rint_magic(code);
                 o = rnd_alu<RD>(fmul(code, step));
               }
-              if (ep.has_bound) {
+              if (has_bound) {
                 keep = fabsf(o) <= bound;
                 o = fminf(fmaxf(o, -bound), bound);
               }
@@ -546,7 +561,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
               const float cmax = n < N ? Elem<kBF16>::load(ep.w_amax, (int64_t)t * N + n) : 0.0f;
               bool keep;
               const float o = tile_epilogue<RD>(__uint_as_float(accr[j]), ir, ep.noise_pc ? cmax : t_max,
-                                                ep.bound_pc ? cmax : t_max, ep.has_noise ? rnd<RD>(z[j]) : 0.0f,
+                                                ep.bound_pc ? cmax : t_max, has_noise ? rnd<RD>(z[j]) : 0.0f,
                                                 cfg, &keep);
               sumr[j] = __float_as_uint(t == 0 ? fadd(0.0f, o) : rnd<RD>(fadd(__uint_as_float(sumr[j]), o)));
               keep_bits |= (keep ? 1u : 0u) << (h * 16 + j);
@@ -975,10 +990,32 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
   p.num_nb = (ep.N + F_BN - 1) / F_BN;
   p.ep = ep;
   p.out = out;
-  // The runtime call below also binds the device's primary context to the calling thread
+  {
+    // |o| <= tile_w * ir * wmax * (1 + noise) and step = 2 * out_bound * ir * wmax / states
+    double states = ep.out_res > 1.0f ? ep.out_res : (ep.out_res > 0.0f ? 1.0 / ep.out_res : 1.0);
+    double max_code = 8.0 * (double)w * states / (2.0 * (ep.out_bound > 0.0f ? ep.out_bound : 1.0));
+    p.small_adc_codes = max_code < 274877906944.0 ? 1 : 0;  // 2^38
+  }
+  const bool per_channel = ep.w_amax != nullptr && (ep.noise_pc || ep.bound_pc);
+  const bool fixed = round_dt == AL_BF16 && !per_channel && ep.out_noise == nullptr && !ep.no_rounding &&
+                     p.small_adc_codes;
+  const int mode = fixed ? ((ep.has_noise ? 1 : 0) | (ep.has_adc ? 2 : 0) | (ep.has_bound ? 4 : 0)) : -1;
+  // The runtime calls below also bind the device's primary context to the calling thread
   // (autograd runs backward on its own threads); the driver entry point that encodes the
   // tensor maps needs a current context.
-  int rc = round_dt == AL_BF16 ? ensure_smem(fwd_tc_kernel<kBF16>, F_SMEM) : ensure_smem(fwd_tc_kernel<kF32>, F_SMEM);
+  void (*kernel)(const CUtensorMap, const CUtensorMap, const FwdTcParams) = nullptr;
+  switch (mode) {
+    case 0: kernel = fwd_tc_kernel<kBF16, 0>; break;
+    case 1: kernel = fwd_tc_kernel<kBF16, 1>; break;
+    case 2: kernel = fwd_tc_kernel<kBF16, 2>; break;
+    case 3: kernel = fwd_tc_kernel<kBF16, 3>; break;
+    case 4: kernel = fwd_tc_kernel<kBF16, 4>; break;
+    case 5: kernel = fwd_tc_kernel<kBF16, 5>; break;
+    case 6: kernel = fwd_tc_kernel<kBF16, 6>; break;
+    case 7: kernel = fwd_tc_kernel<kBF16, 7>; break;
+    default: kernel = round_dt == AL_BF16 ? fwd_tc_kernel<kBF16, -1> : fwd_tc_kernel<kF32, -1>; break;
+  }
+  int rc = ensure_smem(kernel, F_SMEM);
   if (rc) return rc;
   CUtensorMap map_a, map_b;
   {
@@ -997,10 +1034,7 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
   }
   int tiles = p.num_mb * p.num_nb;
   int grid = tiles < sm_count() ? tiles : sm_count();
-  if (round_dt == AL_BF16)
-    fwd_tc_kernel<kBF16><<<grid, kFwdThreads, F_SMEM, s>>>(map_a, map_b, p);
-  else
-    fwd_tc_kernel<kF32><<<grid, kFwdThreads, F_SMEM, s>>>(map_a, map_b, p);
+  kernel<<<grid, kFwdThreads, F_SMEM, s>>>(map_a, map_b, p);
   return check_launch("fwd_tc");
 }
 

@@ -138,32 +138,28 @@ dac_kernel(const void* __restrict__ x, int M, int K, TileTable tt, int ir_mode,
   }
   const char* src = reinterpret_cast<const char*>(x) + (start + p.head) * ES;
   char* dst = reinterpret_cast<char*>(xq) + (start + p.head) * ES;
-  if (DT == kBF16) {
-    // bf16x2 arithmetic: a correctly rounded bf16 multiply equals "fp32 multiply, round to
-    // bf16" for bf16 operands (the fp32 product is exact), the same holds for clamp; the
-    // quotient goes through fp32 (reciprocal-based exact division) and one packed conversion
+  if (DT == kBF16 && q.quantise && !q.no_rounding && small_codes) {
+    // The common case in bf16x2 arithmetic: a correctly rounded bf16 multiply equals "fp32
+    // multiply, round to bf16" for bf16 operands (the fp32 product is exact), the same holds
+    // for the clamp; the quotient goes through fp32 (reciprocal-based exact division), one
+    // packed conversion and an add-based rint (codes are far below 2^22 here).
     const __nv_bfloat162 b2 = __float2bfloat162_rn(q.bound), nb2 = __float2bfloat162_rn(-q.bound);
     const __nv_bfloat162 step2 = __float2bfloat162_rn(q.step);
+    const float stepc = q.stepc, rstep = q.rstep;
+    const bool clamp_first = q.clampit != 0;
     for (int v = lane; v < p.nvec; v += 32) {
       const uint4 raw = *reinterpret_cast<const uint4*>(src + (int64_t)v * 16);
       uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         __nv_bfloat162 x2 = as_bf162(w[i]);
-        if (q.clampit) x2 = __hmin2_nan(__hmax2_nan(x2, nb2), b2);
-        if (q.quantise) {
-          const __nv_bfloat162 q2 = __floats2bfloat162_rn(fdiv_rcp(__low2float(x2), q.stepc, q.rstep),
-                                                          fdiv_rcp(__high2float(x2), q.stepc, q.rstep));
-          float c_lo = __low2float(q2), c_hi = __high2float(q2);
-          if (!q.no_rounding) {
-            c_lo = small_codes ? rint_small(c_lo) : frint_add(c_lo);
-            c_hi = small_codes ? rint_small(c_hi) : frint_add(c_hi);
-          }
-          // an integer-rounded (or already bf16) value packs by a bit move
-          const uint32_t c2 = (__float_as_uint(c_lo) >> 16) | (__float_as_uint(c_hi) & 0xffff0000u);
-          x2 = __hmul2_rn(as_bf162(c2), step2);
-        }
-        w[i] = as_u32(x2);
+        if (clamp_first) x2 = __hmin2_nan(__hmax2_nan(x2, nb2), b2);
+        const __nv_bfloat162 q2 = __floats2bfloat162_rn(fdiv_rcp(__low2float(x2), stepc, rstep),
+                                                        fdiv_rcp(__high2float(x2), stepc, rstep));
+        const float c_lo = rint_small(__low2float(q2)), c_hi = rint_small(__high2float(q2));
+        // an integer of at most 8 significant bits is a bf16 value: packing is a bit move
+        const uint32_t c2 = (__float_as_uint(c_lo) >> 16) | (__float_as_uint(c_hi) & 0xffff0000u);
+        w[i] = as_u32(__hmul2_rn(as_bf162(c2), step2));
       }
       *reinterpret_cast<uint4*>(dst + (int64_t)v * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
