@@ -17,22 +17,44 @@ __device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 h) { return *reinterpr
 // manipulation; logarithm, square root and sine/cosine use the approximate hardware
 // functions.  The 16-bit radius limits a draw to |z| < 4.71.
 __device__ __forceinline__ void box_muller16(uint32_t ab, float* z0, float* z1) {
-  // low 16 bits -> radius, high 16 bits -> angle
-  const float u1 = 2.0f - __uint_as_float(0x3f800000u | ((ab & 0xffffu) << 7));  // (0, 1], step 2^-16
-  const float u2 = __uint_as_float(0x3f800000u | ((ab >> 16) << 7)) - 1.0f;      // [0, 1)
-  float r;
-  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(-1.3862943611198906f * __log2f(u1)));
-  float s, c;
-  __sincosf(6.283185307179586f * u2, &s, &c);
+  // low 16 bits -> radius, high 16 bits -> angle.  0x4b000000 | k is the float 2^23 + k, so one
+  // byte permute and one subtraction turn a 16-bit integer into a float without a conversion.
+  const float k1 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7610)) - 8388608.0f;  // 0 .. 65535
+  const float k2 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7632)) - 8388608.0f;
+  const float u1 = fmaf(k1, -1.52587890625e-05f, 1.0f);  // (0, 1], step 2^-16: never denormal
+  // .ftz forms: single MUFU instructions (the default forms wrap them in denormal handling)
+  float lg, r, s, c;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(u1));
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(-1.3862943611198906f * lg));
+  const float phi = 9.587379924285257e-05f * k2;  // 2*pi * k2 / 65536
+  asm("sin.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(phi));
+  asm("cos.approx.ftz.f32 %0, %1;" : "=f"(c) : "f"(phi));
   *z0 = r * c;
   *z1 = r * s;
+}
+// Philox4x32 with the two 32x32 -> 64 bit products written as 64-bit multiplies (one wide
+// multiply-add instruction each instead of separate high and low halves).
+template <int ROUNDS>
+__device__ __forceinline__ Philox4 philox4x32_wide(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
+                                                   uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < ROUNDS; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ (k0 + (uint32_t)r * 0x9E3779B9u);
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ (k1 + (uint32_t)r * 0xBB67AE85u);
+    c0 = n0; c1 = (uint32_t)p1; c2 = n2; c3 = (uint32_t)p0;
+  }
+  Philox4 out;
+  out.v[0] = c0; out.v[1] = c1; out.v[2] = c2; out.v[3] = c3;
+  return out;
 }
 // Eight normals for elements [8*group8, 8*group8 + 8) of stream `stream` of call (seed, offset).
 __device__ __forceinline__ void normal8_fast(uint64_t seed, uint64_t offset, uint32_t stream, uint64_t group8,
                                              float z[8]) {
-  const Philox4 p = philox4x32<7>((uint32_t)group8, (uint32_t)(group8 >> 32), (uint32_t)offset,
-                                  (uint32_t)(offset >> 32) ^ (stream * 0x85EBCA6Bu) ^ 0x5bd1e995u,
-                                  (uint32_t)seed, (uint32_t)(seed >> 32));
+  const Philox4 p = philox4x32_wide<7>((uint32_t)group8, (uint32_t)(group8 >> 32), (uint32_t)offset,
+                                       (uint32_t)(offset >> 32) ^ (stream * 0x85EBCA6Bu) ^ 0x5bd1e995u,
+                                       (uint32_t)seed, (uint32_t)(seed >> 32));
 #pragma unroll
   for (int i = 0; i < 4; ++i) box_muller16(p.v[i], &z[2 * i], &z[2 * i + 1]);
 }

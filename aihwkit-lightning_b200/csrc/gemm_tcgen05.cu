@@ -445,13 +445,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       for (int t = 0; t < T && ok; ++t, ++acc_it) {
         const int b = acc_it & 1u;
         const uint32_t aph = (acc_it >> 1) & 1u;
-        if (!mbar_wait(&bars->acc_full[b], aph, abort_flag)) {
-          if (lane == 0) raise_error(kErrEpilogue, abort_flag);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        // constants of this (row, analog tile)
+        // constants of this (row, analog tile): fetched and derived before waiting for the
+        // accumulator, so that the load latency and the division overlap the tile's MMAs
         float ir = 0.0f;
         if (row_ok) {
           if (ep.ir_mode == AL_IR_DYNAMIC) ir = Elem<kBF16>::load(ep.ir_rows, (int64_t)t * M + m);
@@ -463,6 +458,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const float step = has_adc ? quant_step<RD>(bound, ep.out_res) : 1.0f;
         const float stepc = step < kTiny ? kTiny : step;
         const float rstep = __frcp_rn(stepc);
+        if (!mbar_wait(&bars->acc_full[b], aph, abort_flag)) {
+          if (lane == 0) raise_error(kErrEpilogue, abort_flag);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
         uint32_t keep_bits = 0;
         const bool packed = RD == kBF16 && !per_channel;  // bf16x2 arithmetic, bf16x2 running sum
         const __nv_bfloat162 sc2 = __float2bfloat162_rn(sc), step2 = __float2bfloat162_rn(step);
@@ -499,6 +500,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             }
           }
           if (packed) {
+            if (t == 0) {
+#pragma unroll
+              for (int pr = 0; pr < 8; ++pr) sumr[pr] = 0u;  // +0.0 in both halves
+            }
             uint32_t kept = 0;  // bit 2*pr (low half) and bit 16 + 2*pr + 1 (high half): element kept
 #pragma unroll
             for (int pr = 0; pr < 8; ++pr) {
@@ -519,7 +524,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                   c_hi = small_codes ? rint_small(c_hi) : rint_magic(c_hi);
                 }
                 // an integer-rounded bf16 value is a bf16 value: packing is a bit move
-                const uint32_t c2 = (__float_as_uint(c_lo) >> 16) | (__float_as_uint(c_hi) & 0xffff0000u);
+                const uint32_t c2 = __byte_perm(__float_as_uint(c_lo), __float_as_uint(c_hi), 0x7632);
                 o2 = __hmul2_rn(as_bf162(c2), step2);
               }
               if (has_bound) {
@@ -529,7 +534,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 kept |= __heq2_mask(c2, o2) & ((1u << (2 * pr)) | (1u << (17 + 2 * pr)));
                 o2 = c2;
               }
-              sumr[pr] = as_u32(__hadd2_rn(t == 0 ? zero2 : as_bf162(sumr[pr]), o2));
+              sumr[pr] = as_u32(__hadd2_rn(as_bf162(sumr[pr]), o2));
             }
             if (!has_bound) kept = 0xffffffffu;
             keep_bits |= ((kept | (kept >> 16)) & 0xffffu) << (h * 16);
