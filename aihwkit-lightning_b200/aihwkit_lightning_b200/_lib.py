@@ -54,7 +54,7 @@ class AlBackwardArgs(Structure):
     ]
 
 
-AL_K_COUNT = 12
+AL_K_COUNT = 14
 AL_STD_STATIC_MAX_SEGMENTS = 262144
 
 
@@ -72,6 +72,8 @@ SYMBOLS = {
     "al_backward": (c_int32, [POINTER(AlDesc), POINTER(AlBackwardArgs), c_void_p]),
     "al_backward_scratch_floats": (c_int64, [c_int32, c_int32, c_int32, c_int32]),
     "al_clip_weights": (c_int32, [c_int32, c_void_p, c_int32, c_int32, c_int32, c_float, c_void_p, c_void_p]),
+    "al_unfold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
+    "al_fold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
     "al_read_device_error": (c_int32, [c_void_p, POINTER(c_uint32)]),
     "al_uses_tcgen05": (c_int32, [POINTER(AlDesc), POINTER(c_int32)]),
     "al_profile_enable": (c_int32, [c_int32]),

@@ -302,3 +302,45 @@ def clip_weights_(weight: Tensor, clip_type: WeightClipType, sigma: float) -> No
     with torch.cuda.device(w.device):
         _lib.check(lib.al_clip_weights(_DTYPE[w.dtype], w.data_ptr(), rows, cols, _CLIP[clip_type],
                                        float(sigma), scratch.data_ptr(), _stream(w.device)))
+
+
+class Unfold2dFunction(torch.autograd.Function):
+    """Patch matrix ``[B, L, C*kh*kw]`` of a ``[B, C, H, W]`` CUDA tensor; the same values as
+    ``unfold(x, ...).transpose(-1, -2).contiguous()`` in the reference's conv forward
+    (`nn/modules/conv.py:312-322`), produced and differentiated by the library's kernels."""
+
+    @staticmethod
+    def forward(ctx, x, kernel_size, dilation, padding, stride):  # type: ignore[override]
+        lib = _lib.load()
+        if not x.is_cuda:
+            raise ValueError("analog convolutions of this package run on CUDA tensors only")
+        if x.dtype not in _DTYPE:
+            raise ConfigError(f"analog layers run in float32 or bfloat16, got {x.dtype}")
+        xc = x.contiguous()
+        b, c, h, w = xc.shape
+        (kh, kw), (dh, dw), (ph, pw), (sh, sw) = kernel_size, dilation, padding, stride
+        ho = (h + 2 * ph - dh * (kh - 1) - 1) // sh + 1
+        wo = (w + 2 * pw - dw * (kw - 1) - 1) // sw + 1
+        out = torch.empty(b, max(ho, 0) * max(wo, 0), c * kh * kw, device=x.device, dtype=x.dtype)
+        geom = (b, c, h, w, kh, kw, sh, sw, ph, pw, dh, dw)
+        with torch.cuda.device(x.device):
+            _lib.check(lib.al_unfold2d(_DTYPE[x.dtype], xc.data_ptr(), *geom, out.data_ptr(), _stream(x.device)))
+        ctx.geom, ctx.dtype_code = geom, _DTYPE[x.dtype]
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_patches):  # type: ignore[override]
+        lib = _lib.load()
+        gp = grad_patches.contiguous()
+        b, c, h, w = ctx.geom[:4]
+        gx = torch.empty(b, c, h, w, device=gp.device, dtype=gp.dtype)
+        with torch.cuda.device(gp.device):
+            _lib.check(lib.al_fold2d(ctx.dtype_code, gp.data_ptr(), *ctx.geom, gx.data_ptr(), _stream(gp.device)))
+        return gx, None, None, None, None
+
+
+def unfold2d(x: Tensor, kernel_size, dilation, padding, stride) -> Tensor:
+    """``[B, C, H, W]`` (or ``[C, H, W]``) -> ``[B, L, C*kh*kw]`` (or ``[L, C*kh*kw]``)."""
+    if x.dim() == 3:
+        return Unfold2dFunction.apply(x.unsqueeze(0), kernel_size, dilation, padding, stride).squeeze(0)
+    return Unfold2dFunction.apply(x, kernel_size, dilation, padding, stride)

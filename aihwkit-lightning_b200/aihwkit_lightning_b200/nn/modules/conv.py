@@ -10,7 +10,6 @@ from typing import Optional, Tuple, Union
 
 import torch
 from torch import Tensor
-from torch.nn.functional import unfold
 from torch.nn.modules.conv import _ConvNd
 from torch.nn.modules.utils import _pair
 
@@ -92,8 +91,7 @@ class _AnalogConvNd(AnalogLayerBase, _ConvNd):
         self._check_forward_config()
         im_shape = inp.shape
         assert isinstance(self.padding, tuple), "Padding must be a tuple"
-        patches = unfold(inp, kernel_size=self.kernel_size, dilation=self.dilation,
-                         padding=self.padding, stride=self.stride).transpose(-1, -2).contiguous()
+        patches = F.unfold2d(inp, self.kernel_size, self.dilation, self.padding, self.stride)
         out = F.analog_linear(patches, self.weight.view(self.out_channels, -1), self.bias,
                               self.input_range, self.input_range_update_idx, self.in_sizes,
                               self.training, self.rpu_config)

@@ -20,6 +20,7 @@ SOURCES = [
     "gemm_simt.cu",
     "gemm_tcgen05.cu",
     "backward_kernels.cu",
+    "conv_kernels.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

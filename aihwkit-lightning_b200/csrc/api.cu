@@ -510,7 +510,8 @@ int al_profile_read(AlProfileEntry* out, int reset) {
 const char* al_kernel_class_name(int k) {
   static const char* names[AL_K_COUNT] = {
       "abs_max_tiles", "tile_max", "std_tiles", "ir_update", "dac", "weight_modify",
-      "fwd_gemm", "dgrad_gemm", "wgrad_gemm", "bias_grad", "ir_backward", "clip_weights"};
+      "fwd_gemm", "dgrad_gemm", "wgrad_gemm", "bias_grad", "ir_backward", "clip_weights",
+      "unfold2d", "fold2d"};
   return (k >= 0 && k < AL_K_COUNT) ? names[k] : "?";
 }
 

@@ -183,6 +183,17 @@ int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T);
 int al_clip_weights(int32_t dtype, void* w, int32_t rows, int32_t cols, int32_t clip_type,
                     float sigma, float* scratch, void* stream);
 
+/* Patch matrix of a 2-D convolution: out[b, l, c*kh*kw + i*kw + j] = x[b, c, oh*sh - ph + i*dh,
+ * ow*sw - pw + j*dw] (zero outside the image), l = oh*Wo + ow.  x is [B,C,H,W] contiguous, out
+ * [B, Ho*Wo, C*kh*kw].  Replaces `unfold(...).transpose(-1, -2).contiguous()` in
+ * `_AnalogConvNd.forward` (P/conv.py:312-322).  al_fold2d is its adjoint (the backward of that
+ * expression): grad_x[b,c,h,w] = sum of grad_patches over every patch position that read x[b,c,h,w]. */
+int al_unfold2d(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh, int32_t kw,
+                int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw, void* out, void* stream);
+int al_fold2d(int32_t dtype, const void* grad_patches, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh,
+              int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw, void* grad_x,
+              void* stream);
+
 /* Device-side error word of the tcgen05 kernels (a bounded wait that gave up).  Reads and
  * clears it; synchronises `stream`.  0 = no error. */
 int al_read_device_error(void* stream, uint32_t* out_code);
@@ -199,6 +210,7 @@ int al_uses_tcgen05(const AlDesc* desc, const int32_t* tile_ends_host);
 enum AlKernelClass {
   AL_K_ABS_MAX = 0, AL_K_TILE_MAX, AL_K_STD, AL_K_IR_UPDATE, AL_K_DAC, AL_K_WEIGHT_MODIFY,
   AL_K_FWD_GEMM, AL_K_DGRAD_GEMM, AL_K_WGRAD_GEMM, AL_K_BIAS_GRAD, AL_K_IR_BACKWARD, AL_K_CLIP,
+  AL_K_UNFOLD, AL_K_FOLD,
   AL_K_COUNT
 };
 typedef struct AlProfileEntry {

@@ -138,3 +138,31 @@ def test_internal_generator_noise_moments():
     z = dw / scale
     assert abs(z.mean().item()) < 0.01
     assert abs(z.std().item() - 1.0) < 0.01
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("geom", [
+    dict(c=3, h=32, w=32, k=(3, 3), s=(1, 1), p=(1, 1), d=(1, 1)),
+    dict(c=16, h=9, w=11, k=(3, 2), s=(2, 1), p=(0, 2), d=(1, 2)),
+    dict(c=5, h=7, w=7, k=(1, 1), s=(2, 2), p=(0, 0), d=(1, 1)),
+])
+def test_unfold2d_and_its_adjoint_match_torch(dtype, geom):
+    """The patch-extraction kernel is a pure copy (bit-equal to F.unfold + transpose); its
+    backward is the gather form of col2im."""
+    from aihwkit_lightning_b200.nn import functional as F
+
+    torch.manual_seed(0)
+    x = torch.randn(4, geom["c"], geom["h"], geom["w"], device="cuda").to(dtype).requires_grad_(True)
+    x2 = x.detach().clone().requires_grad_(True)
+    got = F.unfold2d(x, geom["k"], geom["d"], geom["p"], geom["s"])
+    want = torch.nn.functional.unfold(x2.float(), geom["k"], dilation=geom["d"], padding=geom["p"],
+                                      stride=geom["s"]).transpose(-1, -2)
+    assert torch.equal(got.float(), want)
+    g = torch.randn_like(got)
+    got.backward(g)
+    want.backward(g.float())
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(x.grad.float(), x2.grad.float(), rtol=tol, atol=tol)
+    # 3-D input (single image), as the reference accepts
+    one = F.unfold2d(x.detach()[0], geom["k"], geom["d"], geom["p"], geom["s"])
+    assert torch.equal(one, got.detach()[0])
