@@ -260,7 +260,11 @@ weight_fused_kernel(const void* __restrict__ w, int N, int K, TileTable tt, void
   const float row_max = warp_abs_max<DT>(w, start, len, lane, p);
   if (lane == 0) {
     Elem<DT>::store(w_amax, (int64_t)t * N + n, row_max);
-    atomicMax(reinterpret_cast<unsigned int*>(tile_max) + t, __float_as_uint(row_max));
+    // the running maximum only grows: a plain read first keeps all but a few warps off the
+    // atomic unit (tens of thousands of atomics on T addresses would serialise)
+    unsigned int* slot = reinterpret_cast<unsigned int*>(tile_max) + t;
+    const unsigned int bits = __float_as_uint(row_max);
+    if (bits > *reinterpret_cast<volatile unsigned int*>(slot)) atomicMax(slot, bits);
   }
   if (noise_type == AL_NOISE_NONE) return;
   const WeightSeg ws = weight_prepare<DT>(AL_QUANT_NONE, row_max, 1.0f, 1.0f, false, noise_type, std_dev,
