@@ -12,8 +12,8 @@ algorithmic TFLOP/s = 6*M*K*N / time.
 * ``value``: inputs resident in HBM, CUDA-event timing over exactly K steps (max over ranks).
 * ``e2e``: the same step through the public ``AnalogLinear`` call with the batch in pinned
   host memory: every step uploads its batch (double-buffered on a copy stream, so the upload
-  of the next batch overlaps the current step) and reads the loss back to the host, all inside
-  the timed region.
+  of the next batch overlaps the current step) and copies its loss back to pinned host memory,
+  where the host reads it one step later; all inside the timed region.
 * ``roofline``: the dominant kernel, timed live with CUDA events by the library's launch
   accounting, against the measured bf16 tensor peak.
 * ``cpu_baseline`` / ``--impl reference``: the CPU restatement of the reference's torch path
@@ -260,7 +260,9 @@ def main():
     slots = [torch.empty(M, K, dtype=torch.bfloat16, device=dev) for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
-    state = {"i": 0}
+    loss_host = [torch.empty(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+    loss_done = [torch.cuda.Event() for _ in range(2)]
+    state = {"i": 0, "losses": []}
 
     def upload(slot):
         with torch.cuda.stream(copy_stream):
@@ -284,8 +286,14 @@ def main():
         if buckets is not None:
             buckets.reduce_all_async()
             buckets.finish()
+        # device -> host read of this step's loss: copied to pinned memory on the compute stream
+        # and picked up by the host one step later, so the host can already enqueue the next step
+        loss_host[slot].copy_(loss.detach().reshape(1), non_blocking=True)
+        loss_done[slot].record(stream)
+        if i > 0:
+            loss_done[slot ^ 1].synchronize()
+            state["losses"].append(float(loss_host[slot ^ 1][0]))
         state["i"] = i + 1
-        return float(loss.item())
 
     def timed(fn, steps, between=None):
         """CUDA-event time of exactly `steps` calls; the L2 flush between steps is excluded."""
