@@ -38,6 +38,7 @@ M, K, N, MAX_IN = 8192, 4096, 4096, 512
 CPU_SAMPLE_ROWS = 1024
 FLOP_PER_STEP = 6.0 * M * K * N
 L2_FLUSH_BYTES = 256 << 20
+FWD_KERNEL_DRAM_BYTES = 101.7e6 + 77.3e6
 
 
 def make_rpu_config(ns):
@@ -379,7 +380,9 @@ def main():
                          "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_sustained"],
                          "peak_source": f"{peaks['source']} (sustained; burst {peaks['bf16']})",
-                         "traffic": None},
+                         # DRAM bytes (read + write) of one fwd_tc_kernel launch on this workload,
+                         # from the ncu capture summarised in profiles/fwd_tc_kernel_c2.md
+                         "traffic": FWD_KERNEL_DRAM_BYTES if dominant == "fwd_gemm" else None},
             "kernels": kernels,
             "engine": {"requested": args.engine,
                        "tcgen05": bool(lib.al_uses_tcgen05(
