@@ -12,7 +12,7 @@ from .exceptions import ConfigError, KernelError
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libanalog_b200.so")
 
 AL_F32, AL_BF16 = 0, 1
-AL_IR_OFF, AL_IR_STATIC, AL_IR_DYNAMIC = 0, 1, 2
+AL_IR_OFF, AL_IR_STATIC, AL_IR_DYNAMIC, AL_IR_FAST = 0, 1, 2, 3
 AL_ENGINE_AUTO, AL_ENGINE_SIMT, AL_ENGINE_TCGEN05 = 0, 1, 2
 (AL_OK, AL_ERR_BAD_ARGUMENT, AL_ERR_UNSUPPORTED, AL_ERR_CUDA, AL_ERR_DEVICE_TIMEOUT,
  AL_ERR_TOO_LARGE) = range(6)
@@ -24,6 +24,7 @@ class AlDesc(Structure):
         ("dtype", c_int32), ("training", c_int32), ("ir_mode", c_int32),
         ("init_from_data", c_int32),
         ("init_std_alpha", c_double), ("decay", c_double), ("input_min_percentage", c_double),
+        ("act_range_momentum", c_double),
         ("inp_res", c_double), ("out_res", c_double), ("out_bound", c_double),
         ("out_noise", c_double),
         ("out_noise_per_channel", c_int32), ("noise_type", c_int32), ("quant_type", c_int32),
@@ -37,6 +38,7 @@ class AlForwardArgs(Structure):
     _fields_ = [
         ("x", c_void_p), ("w", c_void_p), ("bias", c_void_p),
         ("input_range", c_void_p), ("input_range_update_idx", c_void_p),
+        ("x_min", c_void_p), ("x_max", c_void_p),
         ("tile_ends", POINTER(c_int32)),
         ("out", c_void_p), ("xq", c_void_p), ("ir_rows", c_void_p), ("w_amax", c_void_p),
         ("w_tile_max", c_void_p), ("w_mod", c_void_p), ("keep_mask", c_void_p),

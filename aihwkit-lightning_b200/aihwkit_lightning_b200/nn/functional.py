@@ -88,17 +88,21 @@ def make_desc(rpu_config, m: int, k: int, n: int, t: int, dtype, training: bool)
     irp = rpu_config.pre_post.input_range
     if dtype not in _DTYPE:
         raise ConfigError(f"analog layers run in float32 or bfloat16, got {dtype}")
-    if irp.enable and irp.fast_mode:
-        raise ConfigError("input_range.fast_mode is not implemented by the CUDA path")
     d = _lib.AlDesc()
     d.M, d.K, d.N, d.T = m, k, n, t
     d.dtype = _DTYPE[dtype]
     d.training = int(training)
-    d.ir_mode = _lib.AL_IR_OFF if not irp.enable else (_lib.AL_IR_DYNAMIC if irp.dynamic else _lib.AL_IR_STATIC)
+    if not irp.enable:
+        d.ir_mode = _lib.AL_IR_OFF
+    elif irp.fast_mode:
+        d.ir_mode = _lib.AL_IR_FAST
+    else:
+        d.ir_mode = _lib.AL_IR_DYNAMIC if irp.dynamic else _lib.AL_IR_STATIC
     d.init_from_data = int(irp.init_from_data)
     d.init_std_alpha = float(irp.init_std_alpha)
     d.decay = float(irp.decay)
     d.input_min_percentage = float(irp.input_min_percentage)
+    d.act_range_momentum = float(irp.act_range_momentum)
     d.inp_res = float(fwd.inp_res)
     d.out_res = float(fwd.out_res)
     d.out_bound = float(fwd.out_bound)
@@ -121,7 +125,7 @@ class AnalogLinearFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, inp, weight, bias, input_range, input_range_update_idx, in_sizes, training,
-                rpu_config):  # type: ignore[override]
+                rpu_config, x_min=None, x_max=None):  # type: ignore[override]
         lib = _lib.load()
         if not inp.is_cuda or not weight.is_cuda:
             raise ValueError(
@@ -142,7 +146,7 @@ class AnalogLinearFunction(torch.autograd.Function):
         desc = make_desc(rpu_config, m, k, n, t, dtype, training)
         desc.save_for_backward = int(needs_grad)
         ends = _lib.tile_ends_array(in_sizes)
-        static = desc.ir_mode == _lib.AL_IR_STATIC
+        static = desc.ir_mode in (_lib.AL_IR_STATIC, _lib.AL_IR_FAST)  # one stored range per tile
         if static:
             assert input_range is not None, "Input range must be provided"
             assert input_range_update_idx is not None, "Input range update index must be provided"
@@ -161,6 +165,9 @@ class AnalogLinearFunction(torch.autograd.Function):
                 ir_data = input_range.data if input_range.is_contiguous() else input_range.data.contiguous()
                 iridx_data = input_range_update_idx
                 args.input_range, args.input_range_update_idx = _ptr(ir_data), _ptr(iridx_data)
+                if desc.ir_mode == _lib.AL_IR_FAST:
+                    assert x_min is not None and x_max is not None, "x_min and x_max must be provided"
+                    args.x_min, args.x_max = _ptr(x_min), _ptr(x_max)
             xq = x2d
             ir_rows = None
             if desc.ir_mode != _lib.AL_IR_OFF:
@@ -216,7 +223,7 @@ class AnalogLinearFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):  # type: ignore[override]
         if ctx.empty:
-            return (None,) * 8
+            return (None,) * 10
         lib = _lib.load()
         x2d, xq, w_mod, ir_rows, keep_mask = ctx.saved_tensors
         desc = ctx.desc
@@ -242,15 +249,15 @@ class AnalogLinearFunction(torch.autograd.Function):
             _lib.check(lib.al_backward(desc, args, _stream(dev)))
         if grad_x is not None:
             grad_x = grad_x.view(ctx.shape) if need_x else None
-        return grad_x, grad_w, grad_b, grad_ir, None, None, None, None
+        return grad_x, grad_w, grad_b, grad_ir, None, None, None, None, None, None
 
 
 def analog_linear(inp: Tensor, weight: Tensor, bias: Optional[Tensor], input_range: Optional[Tensor],
                   input_range_update_idx: Optional[Tensor], in_sizes: List[int], training: bool,
-                  rpu_config) -> Tensor:
+                  rpu_config, x_min: Optional[Tensor] = None, x_max: Optional[Tensor] = None) -> Tensor:
     """Functional form used by ``AnalogLinear`` and ``AnalogConv2d``."""
     return AnalogLinearFunction.apply(inp, weight, bias, input_range, input_range_update_idx,
-                                      in_sizes, training, rpu_config)
+                                      in_sizes, training, rpu_config, x_min, x_max)
 
 
 def sliced_abs_max(in_sizes: List[int], weights: Tensor) -> Tensor:

@@ -94,7 +94,7 @@ class _AnalogConvNd(AnalogLayerBase, _ConvNd):
         patches = F.unfold2d(inp, self.kernel_size, self.dilation, self.padding, self.stride)
         out = F.analog_linear(patches, self.weight.view(self.out_channels, -1), self.bias,
                               self.input_range, self.input_range_update_idx, self.in_sizes,
-                              self.training, self.rpu_config)
+                              self.training, self.rpu_config, self.x_min, self.x_max)
         out = out.transpose(-1, -2).contiguous()
         out_size = (im_shape[-2] + 2 * self.padding[0] - self.dilation[0] * (self.kernel_size[0] - 1) - 1
                     ) // self.stride[0] + 1

@@ -46,7 +46,7 @@ class AnalogLinear(Linear, AnalogLayerBase):
         self._check_forward_config()
         return F.analog_linear(inp, self.weight, self.bias, self.input_range,
                                self.input_range_update_idx, self.in_sizes, self.training,
-                               self.rpu_config)
+                               self.rpu_config, self.x_min, self.x_max)
 
     @classmethod
     def from_digital(cls, module: Linear, rpu_config: TorchInferenceRPUConfig) -> "AnalogLinear":

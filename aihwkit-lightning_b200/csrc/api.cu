@@ -74,7 +74,7 @@ static int derive(const AlDesc& d, Derived* o) {
     set_error("rows * tiles = %lld exceeds 2^31 - 1 segments", (long long)(d.M > d.N ? d.M : d.N) * d.T);
     return AL_ERR_TOO_LARGE;
   }
-  if (d.ir_mode < AL_IR_OFF || d.ir_mode > AL_IR_DYNAMIC) {
+  if (d.ir_mode < AL_IR_OFF || d.ir_mode > AL_IR_FAST) {
     set_error("unknown input-range mode %d", d.ir_mode);
     return AL_ERR_BAD_ARGUMENT;
   }
@@ -224,6 +224,23 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
 
   // 1. input range (static mode): optional init-from-data update, then copy the ranges used
   const void* ir_static = nullptr;
+  if (d.ir_mode == AL_IR_FAST) {
+    if (!a->input_range || !a->input_range_update_idx || !a->x_min || !a->x_max || !a->ir_rows) {
+      set_error("fast input-range mode needs input_range, input_range_update_idx, x_min, x_max and ir_rows");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    int do_update = d.training && d.init_from_data > 0;
+    if (do_update && !a->std_scratch) {
+      set_error("init_from_data > 0 needs std_scratch");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    rc = launch_ir_fast_update(d.dtype, a->x, d.M, d.K, tt, a->input_range, a->input_range_update_idx,
+                               a->x_min, a->x_max, d.init_from_data, (float)d.act_range_momentum,
+                               (float)(1.0 - d.act_range_momentum), d.act_range_momentum == -1.0, do_update,
+                               a->std_scratch, a->ir_rows, s);
+    if (rc) return rc;
+    ir_static = a->ir_rows;
+  }
   if (d.ir_mode == AL_IR_STATIC) {
     if (!a->input_range || !a->input_range_update_idx || !a->ir_rows) {
       set_error("static input range needs input_range, input_range_update_idx and ir_rows");
@@ -255,7 +272,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
       set_error("al_forward: xq / ir_rows workspace missing");
       return AL_ERR_BAD_ARGUMENT;
     }
-    rc = launch_dac(d.dtype, a->x, d.M, d.K, tt, d.ir_mode, ir_static, dv.has_dac ? dv.inp_res : -1.0f,
+    rc = launch_dac(d.dtype, a->x, d.M, d.K, tt, d.ir_mode == AL_IR_FAST ? AL_IR_STATIC : d.ir_mode, ir_static, dv.has_dac ? dv.inp_res : -1.0f,
                     d.no_rounding, a->xq, a->ir_rows, a->codes, s);
     if (rc) return rc;
     xq = a->xq;
@@ -300,7 +317,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
   FwdEpilogueParams ep;
   memset(&ep, 0, sizeof(ep));
   ep.M = d.M; ep.N = d.N; ep.T = d.T;
-  ep.ir_mode = d.ir_mode;
+  ep.ir_mode = d.ir_mode == AL_IR_FAST ? AL_IR_STATIC : d.ir_mode;  // one range per tile either way
   ep.ir_rows = a->ir_rows;
   ep.w_amax = a->w_amax;
   ep.w_tile_max = tile_max;
@@ -372,14 +389,14 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
     rc = tc ? launch_dgrad_tc(a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, a->grad_x, s)
             : launch_dgrad_simt(d.dtype, a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, a->grad_x, s);
     if (rc) return rc;
-    if (d.ir_mode == AL_IR_STATIC) {
+    if (d.ir_mode == AL_IR_STATIC || d.ir_mode == AL_IR_FAST) {
       if (!a->x || !a->ir_rows || !a->reduce_scratch) {
         set_error("al_backward: static input range needs x, ir_rows and reduce_scratch");
         return AL_ERR_BAD_ARGUMENT;
       }
       rc = launch_static_ir_backward(d.dtype, a->x, a->ir_rows, a->grad_x, d.M, d.K, tt, dv.decay,
                                      dv.input_min_percentage, a->grad_input_range,
-                                     a->reduce_scratch + 256 * (int64_t)d.N, s);
+                                     a->reduce_scratch + 256 * (int64_t)d.N, d.ir_mode == AL_IR_FAST, s);
       if (rc) return rc;
     }
   } else if (a->grad_input_range) {

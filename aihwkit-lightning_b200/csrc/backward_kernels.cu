@@ -39,7 +39,7 @@ template <int DT>
 __global__ void __launch_bounds__(256)
 static_ir_partial_kernel(const void* __restrict__ x, const void* __restrict__ ir_used,
                          void* __restrict__ grad_x, int M, int K, TileTable tt,
-                         float* __restrict__ partial) {
+                         float* __restrict__ partial, int fast_mode) {
   const unsigned seg = blockIdx.x * 8 + (threadIdx.x >> 5);  // rows * T < 2^31 (checked by the host)
   int lane = threadIdx.x & 31;
   if (seg >= (unsigned)M * (unsigned)tt.T) return;
@@ -51,6 +51,14 @@ static_ir_partial_kernel(const void* __restrict__ x, const void* __restrict__ ir
   for (int i = lane; i < len; i += 32) {
     float xv = Elem<DT>::load(x, start + i);
     float gv = Elem<DT>::load(grad_x, start + i);
+    if (fast_mode) {
+      // plain clamp with tensor bounds: the bounds collect the gradient outside [-ir, ir]
+      bool up = xv > ir, dn = xv < -ir;
+      if (up) s_up += gv;
+      if (dn) s_lo += gv;
+      if (up || dn) Elem<DT>::store(grad_x, start + i, 0.0f);
+      continue;
+    }
     bool up = xv >= ir, dn = xv <= -ir;
     if (up) s_up += fminf(gv, 0.0f);
     if (dn) s_lo += fmaxf(gv, 0.0f);
@@ -77,7 +85,7 @@ template <int DT>
 __global__ void static_ir_final_kernel(const float* __restrict__ partial,
                                        const void* __restrict__ ir_used, int M, TileTable tt,
                                        float decay, float input_min_percentage,
-                                       void* __restrict__ grad_ir) {
+                                       void* __restrict__ grad_ir, int fast_mode) {
   __shared__ double sm[3][256];
   int t = blockIdx.x;
   double a = 0.0, b = 0.0, c = 0.0;
@@ -103,6 +111,10 @@ __global__ void static_ir_final_kernel(const float* __restrict__ partial,
     float ir = Elem<DT>::load(ir_used, t);
     float acc = rnd<DT>(fadd(0.0f, rnd<DT>((float)sm[0][0])));
     acc = rnd<DT>(fsub(acc, rnd<DT>((float)sm[1][0])));
+    if (fast_mode) {
+      Elem<DT>::store(grad_ir, t, acc);
+      return;
+    }
     acc = rnd<DT>(fmul(acc, ir));
     if (decay > 0.0f) {
       float numel = (float)((double)M * (double)(tt.hi(t) - tt.lo(t)));
@@ -136,16 +148,16 @@ int launch_bias_grad(int dtype, const void* g, int M, int N, void* grad_bias, fl
 
 int launch_static_ir_backward(int dtype, const void* x, const void* ir_used, void* grad_x, int M,
                               int K, const TileTable& tt, float decay, float input_min_percentage,
-                              void* grad_ir, float* scratch, cudaStream_t s) {
+                              void* grad_ir, float* scratch, int fast_mode, cudaStream_t s) {
   ProfScope prof(AL_K_IR_BACKWARD, s, grad_ir ? 2 : 1);
   int64_t segs = (int64_t)M * tt.T;
   unsigned blocks = (unsigned)((segs + 7) / 8);
   if (dtype == AL_F32) {
-    static_ir_partial_kernel<kF32><<<blocks, 256, 0, s>>>(x, ir_used, grad_x, M, K, tt, scratch);
-    if (grad_ir) static_ir_final_kernel<kF32><<<tt.T, 256, 0, s>>>(scratch, ir_used, M, tt, decay, input_min_percentage, grad_ir);
+    static_ir_partial_kernel<kF32><<<blocks, 256, 0, s>>>(x, ir_used, grad_x, M, K, tt, scratch, fast_mode);
+    if (grad_ir) static_ir_final_kernel<kF32><<<tt.T, 256, 0, s>>>(scratch, ir_used, M, tt, decay, input_min_percentage, grad_ir, fast_mode);
   } else {
-    static_ir_partial_kernel<kBF16><<<blocks, 256, 0, s>>>(x, ir_used, grad_x, M, K, tt, scratch);
-    if (grad_ir) static_ir_final_kernel<kBF16><<<tt.T, 256, 0, s>>>(scratch, ir_used, M, tt, decay, input_min_percentage, grad_ir);
+    static_ir_partial_kernel<kBF16><<<blocks, 256, 0, s>>>(x, ir_used, grad_x, M, K, tt, scratch, fast_mode);
+    if (grad_ir) static_ir_final_kernel<kBF16><<<tt.T, 256, 0, s>>>(scratch, ir_used, M, tt, decay, input_min_percentage, grad_ir, fast_mode);
   }
   return check_launch("static_ir_backward");
 }

@@ -70,6 +70,12 @@ int launch_std_tiles(int dtype, const void* a, int rows, int K, const TileTable&
 int launch_ir_update(int dtype, void* input_range, void* update_idx, const float* std, int T,
                      int init_from_data, float init_std_alpha, int do_update, void* ir_used,
                      cudaStream_t s);
+// fast mode: per-tile min / max over all rows and the momentum update of x_min, x_max, the
+// range and its counter, all on the device; ir_used receives the ranges of this call
+int launch_ir_fast_update(int dtype, const void* x, int M, int K, const TileTable& tt, void* input_range,
+                          void* update_idx, void* x_min, void* x_max, int init_from_data, float momentum,
+                          float one_minus_momentum, int minmax_mode, int do_update, float* scratch,
+                          void* ir_used, cudaStream_t s);
 int launch_clip_weights(int dtype, void* w, int rows, int cols, int clip_type, float sigma,
                         float* scratch, cudaStream_t s);
 
@@ -105,7 +111,7 @@ int launch_bias_grad(int dtype, const void* g, int M, int N, void* grad_bias, fl
                      cudaStream_t s);
 int launch_static_ir_backward(int dtype, const void* x, const void* ir_used, void* grad_x, int M,
                               int K, const TileTable& tt, float decay, float input_min_percentage,
-                              void* grad_ir, float* scratch, cudaStream_t s);
+                              void* grad_ir, float* scratch, int fast_mode, cudaStream_t s);
 
 // ---- tcgen05 GEMMs (gemm_tcgen05.cu) ------------------------------------------------------
 bool tc_forward_supported(const AlDesc& d, const TileTable& tt);

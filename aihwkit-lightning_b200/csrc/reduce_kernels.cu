@@ -319,6 +319,108 @@ int launch_clip_weights(int dtype, void* w, int rows, int cols, int clip_type, f
 
 }  // namespace al
 
+namespace al {
+namespace {
+
+// fast mode, stage 1: (min, max) of every (row, tile) segment; skipped for tiles whose update
+// counter already reached init_from_data
+template <int DT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+segment_minmax_kernel(const void* __restrict__ a, int rows, int K, TileTable tt,
+                      const void* __restrict__ update_idx, int init_from_data,
+                      float* __restrict__ partial) {
+  const unsigned seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
+  if (seg >= (unsigned)rows * (unsigned)tt.T) return;
+  const int r = (int)(seg / (unsigned)tt.T), t = (int)(seg - (unsigned)r * (unsigned)tt.T);
+  if (!(Elem<DT>::load(update_idx, t) < (float)init_from_data)) return;
+  int lo = tt.lo(t), len = tt.hi(t) - lo;
+  float mn = INFINITY, mx = -INFINITY;
+  warp_scan_segment<DT>(a, (int64_t)r * K + lo, len, lane, [&](float v) {
+    mn = fminf(mn, v);
+    mx = fmaxf(mx, v);
+  });
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if (lane == 0) {
+    partial[((int64_t)t * rows + r) * 2] = mn;
+    partial[((int64_t)t * rows + r) * 2 + 1] = mx;
+  }
+}
+
+// fast mode, stage 2: one block per tile reduces the row partials and applies the update of
+// `apply_input_range_fast` (reference torch_linear.py:386-420), every op rounded to DT
+template <int DT>
+__global__ void ir_fast_update_kernel(const float* __restrict__ partial, int rows, void* input_range,
+                                      void* update_idx, void* x_min, void* x_max, int init_from_data,
+                                      float momentum, float one_minus_momentum, int minmax_mode,
+                                      int do_update, void* ir_used) {
+  __shared__ float s_mn[256], s_mx[256];
+  const int t = blockIdx.x;
+  float ir = Elem<DT>::load(input_range, t);
+  const float idx = Elem<DT>::load(update_idx, t);
+  const bool update = do_update && idx < (float)init_from_data;  // uniform over the block
+  if (update) {
+    float mn = INFINITY, mx = -INFINITY;
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+      mn = fminf(mn, partial[((int64_t)t * rows + r) * 2]);
+      mx = fmaxf(mx, partial[((int64_t)t * rows + r) * 2 + 1]);
+    }
+    s_mn[threadIdx.x] = mn;
+    s_mx[threadIdx.x] = mx;
+    __syncthreads();
+    for (int o = blockDim.x / 2; o > 0; o >>= 1) {
+      if (threadIdx.x < o) {
+        s_mn[threadIdx.x] = fminf(s_mn[threadIdx.x], s_mn[threadIdx.x + o]);
+        s_mx[threadIdx.x] = fmaxf(s_mx[threadIdx.x], s_mx[threadIdx.x + o]);
+      }
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+      const float act_min = s_mn[0], act_max = s_mx[0];
+      float xmin = Elem<DT>::load(x_min, t), xmax = Elem<DT>::load(x_max, t);
+      if (xmin > -1.1e-5f && xmax < 1.1e-5f) {  // first update: start from the observed range
+        xmin = rnd<DT>(fadd(xmin, act_min));
+        xmax = rnd<DT>(fadd(xmax, act_max));
+      } else if (minmax_mode) {  // act_range_momentum == -1: running extrema
+        xmin = fminf(xmin, act_min);
+        xmax = fmaxf(xmax, act_max);
+      } else {
+        xmin = rnd<DT>(fadd(rnd<DT>(fmul(xmin, momentum)), rnd<DT>(fmul(act_min, one_minus_momentum))));
+        xmax = rnd<DT>(fadd(rnd<DT>(fmul(xmax, momentum)), rnd<DT>(fmul(act_max, one_minus_momentum))));
+      }
+      Elem<DT>::store(x_min, t, xmin);
+      Elem<DT>::store(x_max, t, xmax);
+      Elem<DT>::store(update_idx, t, rnd<DT>(fadd(idx, 1.0f)));
+      ir = fmaxf(fabsf(xmin), fabsf(xmax));
+      Elem<DT>::store(input_range, t, ir);
+    }
+  }
+  if (threadIdx.x == 0) Elem<DT>::store(ir_used, t, ir);
+}
+
+}  // namespace
+
+int launch_ir_fast_update(int dtype, const void* x, int M, int K, const TileTable& tt, void* input_range,
+                          void* update_idx, void* x_min, void* x_max, int init_from_data, float momentum,
+                          float one_minus_momentum, int minmax_mode, int do_update, float* scratch,
+                          void* ir_used, cudaStream_t s) {
+  ProfScope prof(AL_K_IR_UPDATE, s, do_update ? 2 : 1);
+  if (do_update) {
+    int64_t segs = (int64_t)M * tt.T;
+    AL_DISPATCH_DT(dtype, (segment_minmax_kernel<DT><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(x, M, K, tt, update_idx, init_from_data, scratch)));
+    int rc = check_launch("segment_minmax");
+    if (rc) return rc;
+  }
+  AL_DISPATCH_DT(dtype, (ir_fast_update_kernel<DT><<<tt.T, 256, 0, s>>>(scratch, M, input_range, update_idx, x_min, x_max, init_from_data, momentum, one_minus_momentum, minmax_mode, do_update, ir_used)));
+  return check_launch("ir_fast_update");
+}
+
+}  // namespace al
+
 // ---- per-tile std without a caller-supplied scratch buffer ---------------------------------
 //
 // al_std_tiles needs 2 floats of scratch per (row, tile) segment for its stage-1 partials and

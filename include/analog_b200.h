@@ -46,7 +46,9 @@ enum AlClipType {
   AL_CLIP_LAYER_GAUSSIAN_PER_CHANNEL = 2,
   AL_CLIP_LEARNABLE_PER_CHANNEL = 3
 };
-enum AlInputRangeMode { AL_IR_OFF = 0, AL_IR_STATIC = 1, AL_IR_DYNAMIC = 2 };
+/* STATIC: learned / fixed range with init-from-data (std based); DYNAMIC: per-row abs-max;
+ * FAST: the reference's fast_mode (min/max tracking, plain clamp, `torch_linear.py:361-423`) */
+enum AlInputRangeMode { AL_IR_OFF = 0, AL_IR_STATIC = 1, AL_IR_DYNAMIC = 2, AL_IR_FAST = 3 };
 
 /* GEMM engine selection.  AUTO picks the tcgen05/TMA kernels whenever dtype and alignment
  * allow and the SIMT kernels otherwise; the other two force one of them (tests). */
@@ -69,6 +71,7 @@ typedef struct AlDesc {
   double init_std_alpha;      /* InputRangeParameter.init_std_alpha                         */
   double decay;               /* InputRangeParameter.decay                                  */
   double input_min_percentage;
+  double act_range_momentum;  /* InputRangeParameter.act_range_momentum (fast mode)          */
   double inp_res;             /* IOParameters.inp_res  (<=0: DAC off)                        */
   double out_res;             /* IOParameters.out_res  (<=0: ADC quantisation off)           */
   double out_bound;           /* IOParameters.out_bound (<=0: no clipping)                   */
@@ -95,6 +98,8 @@ typedef struct AlForwardArgs {
   void* input_range;         /* [T] dtype, static mode: read, and updated while
                                  init_from_data is active; null otherwise                  */
   void* input_range_update_idx; /* [T] dtype, static mode                                   */
+  void* x_min;               /* [T] dtype, fast mode: running minimum (updated)             */
+  void* x_max;               /* [T] dtype, fast mode: running maximum (updated)             */
   const int32_t* tile_ends;  /* HOST pointer, [T] cumulative tile ends (last == K)         */
   void* out;                 /* [M,N] dtype                                                 */
   /* saved for backward / intermediates (caller-allocated workspace) */

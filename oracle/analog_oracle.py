@@ -253,7 +253,7 @@ def forward(
                     update_input_range_fast(
                         x_t, t, irp, input_range, input_range_update_idx, x_min, x_max
                     )
-                ir = input_range[t]
+                ir = input_range[t].detach().clone()
                 x_t = torch.clamp(x_t, min=-ir, max=ir)
             elif irp.dynamic:
                 ir = x_t.abs().max(dim=-1, keepdim=True)[0]
@@ -349,7 +349,7 @@ def backward(
     grad_w = torch.zeros_like(weights)
     static_ir = irp.enable and not irp.dynamic and not irp.fast_mode
     fast_ir = irp.enable and irp.fast_mode
-    grad_ir = torch.zeros_like(input_range) if (static_ir and input_range is not None) else None
+    grad_ir = torch.zeros_like(input_range) if ((static_ir or fast_ir) and input_range is not None) else None
     for t, tr in enumerate(rec.tiles):
         g_t = g
         if tr.pre_clamp is not None:
@@ -372,7 +372,16 @@ def backward(
             gx = gx.clone()
             gx[zero] = 0.0
         elif fast_ir:
+            # plain torch.clamp with tensor bounds (`torch_linear.py:422`): the gradient passes
+            # inside [-ir, ir]; the upper bound receives the gradient mass above it, the lower
+            # bound (= -ir) the mass below it
             ir = tr.ir
+            if grad_ir is not None:
+                acc = torch.zeros_like(ir)
+                zero = torch.zeros((), dtype=gx.dtype)
+                acc = acc + torch.where(x_t > ir, gx, zero).sum()
+                acc = acc + (-torch.where(x_t < -ir, gx, zero).sum())
+                grad_ir[t] = acc
             gx = gx * ((x_t >= -ir) & (x_t <= ir))
         grad_x[:, tr.lo : tr.hi] = gx
     return {

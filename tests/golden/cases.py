@@ -23,6 +23,8 @@ DEFAULTS = dict(
     ir_init_std_alpha=3.0,
     ir_decay=0.001,
     ir_min_pct=0.95,
+    ir_fast_mode=False,
+    ir_momentum=0.95,
     inp_res=254.0,
     out_noise=0.0,
     out_noise_per_channel=False,
@@ -87,6 +89,12 @@ CASES = [
     _c("bf16_discretize", dtype="bf16", quant_type="DiscretizePerChannel", mod_res=254.0,
        ir_dynamic=True),
     _c("bf16_init_from_data", dtype="bf16", ir_init_from_data=2, steps=3, ir_init_value=3.0),
+    # fast mode: min/max tracking of the first calls, plain clamp afterwards
+    _c("fast_mode_momentum", ir_fast_mode=True, ir_init_from_data=2, steps=4, out_noise=0.04),
+    _c("fast_mode_minmax", ir_fast_mode=True, ir_momentum=-1, ir_init_from_data=3, steps=3,
+       out_bound=3.0, out_res=254.0),
+    _c("fast_mode_fixed", ir_fast_mode=True, ir_init_from_data=0, ir_init_value=0.9),
+    _c("bf16_fast_mode", dtype="bf16", ir_fast_mode=True, ir_init_from_data=2, steps=3),
 ]
 
 CASES_BY_NAME = {c["name"]: c for c in CASES}
@@ -112,6 +120,8 @@ def build_rpu_config(ns, case):
     ir.init_std_alpha = case["ir_init_std_alpha"]
     ir.decay = case["ir_decay"]
     ir.input_min_percentage = case["ir_min_pct"]
+    ir.fast_mode = case["ir_fast_mode"]
+    ir.act_range_momentum = case["ir_momentum"]
     rpu.modifier.noise_type = ns.WeightNoiseInjectionType(case["noise_type"])
     rpu.modifier.quantization_type = ns.WeightQuantizationType(case["quant_type"])
     rpu.modifier.std_dev = case["std_dev"]

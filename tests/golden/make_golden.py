@@ -77,6 +77,8 @@ def run_reference(ref, case, data):
         input_range_update_idx=None
         if layer.input_range_update_idx is None
         else layer.input_range_update_idx.clone(),
+        x_min=None if getattr(layer, "x_min", None) is None else layer.x_min.clone(),
+        x_max=None if getattr(layer, "x_max", None) is None else layer.x_max.clone(),
         in_sizes=list(layer.in_sizes),
     )
 
@@ -85,20 +87,22 @@ def run_oracle(ns, case, data):
     rpu = C.build_rpu_config(ns, case)
     in_sizes = O.split_sizes(data["k"], case["max_input_size"])
     static = case["ir_enable"] and not case["ir_dynamic"]
-    ir = idx = None
+    ir = idx = x_min = x_max = None
     if static:
         ir = torch.full((len(in_sizes),), case["ir_init_value"], dtype=data["dtype"])
         idx = torch.zeros(len(in_sizes), dtype=data["dtype"])
+        x_min = torch.zeros(len(in_sizes), dtype=data["dtype"]) - 1e-5
+        x_max = torch.zeros(len(in_sizes), dtype=data["dtype"]) + 1e-5
     for step in range(case["steps"]):
         rec = O.forward(
-            data["xs"][step], data["w"], data["b"], ir, idx, None, None, in_sizes,
+            data["xs"][step], data["w"], data["b"], ir, idx, x_min, x_max, in_sizes,
             case["training"], rpu,
             O.NoiseReplay(data["w_noise"][step], data["out_noise"][step]),
         )
     grads = O.backward(rec, data["g"], data["w"], case["bias"], ir, rpu)
     if static and not case["ir_learn"]:
         grads["grad_ir"] = None
-    return rec, grads, ir, idx
+    return rec, grads, ir, idx, x_min, x_max
 
 
 def main():
@@ -118,7 +122,7 @@ def main():
     for case in C.CASES:
         data = C.make_inputs(case)
         want = run_reference(ref, case, data)
-        rec, grads, ir, idx = run_oracle(ref, case, data)
+        rec, grads, ir, idx, x_min, x_max = run_oracle(ref, case, data)
         checks = dict(
             out=same(want["out"], rec.out),
             grad_x=same(want["grad_x"], grads["grad_x"]),
@@ -127,6 +131,8 @@ def main():
             grad_ir=same(want["grad_ir"], grads["grad_ir"]),
             input_range=same(want["input_range"], ir),
             update_idx=same(want["input_range_update_idx"], idx),
+            x_min=same(want["x_min"], x_min),
+            x_max=same(want["x_max"], x_max),
         )
         bad = [k for k, ok in checks.items() if not ok]
         assert not bad, f"oracle differs from the reference in case {case['name']}: {bad}"

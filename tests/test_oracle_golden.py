@@ -33,19 +33,21 @@ def run_oracle(case, data):
     rpu = C.build_rpu_config(NS, case)
     in_sizes = O.split_sizes(data["k"], case["max_input_size"])
     static = case["ir_enable"] and not case["ir_dynamic"]
-    ir = idx = None
+    ir = idx = x_min = x_max = None
     if static:
         ir = torch.full((len(in_sizes),), case["ir_init_value"], dtype=data["dtype"])
         idx = torch.zeros(len(in_sizes), dtype=data["dtype"])
+        x_min = torch.zeros(len(in_sizes), dtype=data["dtype"]) - 1e-5
+        x_max = torch.zeros(len(in_sizes), dtype=data["dtype"]) + 1e-5
     for step in range(case["steps"]):
         rec = O.forward(
-            data["xs"][step], data["w"], data["b"], ir, idx, None, None, in_sizes,
+            data["xs"][step], data["w"], data["b"], ir, idx, x_min, x_max, in_sizes,
             case["training"], rpu, O.NoiseReplay(data["w_noise"][step], data["out_noise"][step]),
         )
     grads = O.backward(rec, data["g"], data["w"], case["bias"], ir, rpu)
     if static and not case["ir_learn"]:
         grads["grad_ir"] = None
-    return rec, grads, ir, idx
+    return rec, grads, ir, idx, x_min, x_max
 
 
 @pytest.mark.parametrize("name", [c["name"] for c in C.CASES])
@@ -54,12 +56,13 @@ def test_oracle_reproduces_reference(name):
     want = torch.load(os.path.join(GOLDEN, name + ".pt"), weights_only=False)
     assert want["case"] == case, "golden file is stale: re-run tests/golden/make_golden.py"
     data = C.make_inputs(case)
-    rec, grads, ir, idx = run_oracle(case, data)
+    rec, grads, ir, idx, x_min, x_max = run_oracle(case, data)
     assert same(want["out"], rec.out)
     for key in ("grad_x", "grad_w", "grad_bias", "grad_ir"):
         assert same(want[key], grads[key]), key
     assert same(want["input_range"], ir)
     assert same(want["input_range_update_idx"], idx)
+    assert same(want["x_min"], x_min) and same(want["x_max"], x_max)
     assert want["in_sizes"] == O.split_sizes(data["k"], case["max_input_size"])
 
 

@@ -72,6 +72,10 @@ def test_golden_case(name):
     if want["input_range"] is not None:
         check_close("input_range", layer.input_range.detach(), want["input_range"], dtype, case)
         assert torch.equal(layer.input_range_update_idx.cpu(), want["input_range_update_idx"])
+        # min/max tracking is exact arithmetic on exact extrema: bit-identical state
+        assert torch.equal(layer.x_min.cpu(), want["x_min"]) and torch.equal(layer.x_max.cpu(), want["x_max"])
+        if case["ir_fast_mode"]:
+            assert torch.equal(layer.input_range.detach().cpu(), want["input_range"])
 
 
 @pytest.mark.parametrize("name", ["bf16_dynamic_adc_noise", "bf16_static_noise", "bf16_static_adc",

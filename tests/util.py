@@ -65,11 +65,13 @@ def oracle_run(case, data, x=None, w=None, b=None, g=None, w_noise=None, out_noi
     training = case["training"] if training is None else training
     in_sizes = O.split_sizes(x.shape[-1], case["max_input_size"])
     static = case["ir_enable"] and not case["ir_dynamic"]
-    ir = idx = None
+    ir = idx = x_min = x_max = None
     if static:
         ir = torch.full((len(in_sizes),), case["ir_init_value"], dtype=x.dtype)
         idx = torch.zeros(len(in_sizes), dtype=x.dtype)
-    rec = O.forward(x, w, b, ir, idx, None, None, in_sizes, training, rpu,
+        x_min = torch.zeros(len(in_sizes), dtype=x.dtype) - 1e-5
+        x_max = torch.zeros(len(in_sizes), dtype=x.dtype) + 1e-5
+    rec = O.forward(x, w, b, ir, idx, x_min, x_max, in_sizes, training, rpu,
                     O.NoiseReplay(w_noise, out_noise))
     grads = O.backward(rec, g, w, b is not None, ir, rpu)
     return rec, grads
