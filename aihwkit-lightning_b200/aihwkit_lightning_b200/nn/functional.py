@@ -182,7 +182,7 @@ class AnalogLinearFunction(torch.autograd.Function):
             args.w_mod = _ptr(w_mod)
             keep_mask = None
             if desc.out_bound > 0 and needs_grad:
-                keep_mask = torch.empty(t, m, (n + 31) // 32, device=dev, dtype=torch.int32)
+                keep_mask = torch.empty(t, (n + 31) // 32, m, device=dev, dtype=torch.int32)
             args.keep_mask = _ptr(keep_mask)
             std_scratch = None
             if static and training and desc.init_from_data > 0:

@@ -129,9 +129,9 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
         int sh = lane == 0 ? 0 : 16;
         uint32_t w0 = ((bal[0] >> sh) & 0xffffu) | (((bal[1] >> sh) & 0xffffu) << 16);
         uint32_t w1 = ((bal[2] >> sh) & 0xffffu) | (((bal[3] >> sh) & 0xffffu) << 16);
-        int64_t base = ((int64_t)t * M + m) * ep.mask_words + n0 / 32;
+        int64_t base = ((int64_t)t * ep.mask_words + n0 / 32) * M + m;
         if (n0 / 32 < ep.mask_words) ep.keep_mask[base] = w0;
-        if (n0 / 32 + 1 < ep.mask_words) ep.keep_mask[base + 1] = w1;
+        if (n0 / 32 + 1 < ep.mask_words) ep.keep_mask[base + M] = w1;
       }
     }
   }
@@ -186,7 +186,7 @@ bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
         int gi = i0 + i, gl = l0 + l;
         if (gi < I && gl < L) {
           int m = WGRAD ? gl : gi, n = WGRAD ? gi : gl;
-          uint32_t word = keep_mask[((int64_t)t * M + m) * mask_words + (n >> 5)];
+          uint32_t word = keep_mask[((int64_t)t * mask_words + (n >> 5)) * M + m];
           if (((word >> (n & 31)) & 1u) == 0u) As[l][i] = 0.0f;
         }
       }

@@ -609,7 +609,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           }
         }
         if (ep.keep_mask != nullptr && row_ok && (n0 >> 5) < ep.mask_words)
-          ep.keep_mask[((int64_t)t * M + m) * ep.mask_words + (n0 >> 5)] = keep_bits;
+          ep.keep_mask[((int64_t)t * ep.mask_words + (n0 >> 5)) * M + m] = keep_bits;  // lanes = consecutive rows
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -742,8 +742,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
           const int s = it % B_STAGES;
           const uint32_t ph = (it / B_STAGES) & 1u;
-          uint64_t* wait_on = masked ? &bars->ready[s] : &bars->full[s];
-          if (!mbar_wait(wait_on, ph, abort_flag)) {
+          // the transform warps vouch for a stage on `ready` before its copy has landed when
+          // the stage has nothing to zero, so both barriers gate the MMA
+          if (!mbar_wait(&bars->full[s], ph, abort_flag) ||
+              (masked && !mbar_wait(&bars->ready[s], ph, abort_flag))) {
             raise_error(kErrMma, abort_flag);
             ok = false;
             break;
@@ -841,10 +843,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const int m = WGRAD ? l0 + row_in_box : ib * BM + r;
         const int n0 = WGRAD ? ib * BM + box * 64 : l0;
         if (m < p.M) {
-          const uint32_t* mrow = p.keep_mask + ((int64_t)t * p.M + m) * p.mask_words;
+          // word-major layout: the threads of a warp (consecutive rows) read consecutive words
           const int w0 = n0 >> 5;
-          if (w0 < p.mask_words) *lo = mrow[w0];
-          if (w0 + 1 < p.mask_words) *hi = mrow[w0 + 1];
+          const uint32_t* mcol = p.keep_mask + ((int64_t)t * p.mask_words + w0) * p.M + m;
+          if (w0 < p.mask_words) *lo = mcol[0];
+          if (w0 + 1 < p.mask_words) *hi = mcol[p.M];
         }
       }
     };
@@ -856,11 +859,27 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       fetch(it + B_XFORM_GROUPS, &lo1, &hi1);
       const int s = it % B_STAGES;
       const uint32_t ph = ((uint32_t)it / B_STAGES) & 1u;
+      uint64_t zeros = ~((uint64_t)lo0 | ((uint64_t)hi0 << 32));
+      if (!__any_sync(0xffffffffu, zeros != 0ull)) {
+        // Nothing to zero in this warp's rows (the common case: a clamp that fires is rare).
+        // The warp's arrival must still land in the right phase of `ready`, so it waits for
+        // the stage's previous use to be consumed -- long before the copy lands, which takes
+        // this hand-off off the TMA -> MMA critical path.
+        bool okw = true;
+        if (lane == 0) {
+          okw = mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag);
+          if (okw) mbar_arrive(&bars->ready[s]);
+          else raise_error(kErrTransform, abort_flag);
+        }
+        if (!__shfl_sync(0xffffffffu, okw, 0)) break;
+        lo0 = lo1;
+        hi0 = hi1;
+        continue;
+      }
       if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
         raise_error(kErrTransform, abort_flag);
         break;
       }
-      uint64_t zeros = ~((uint64_t)lo0 | ((uint64_t)hi0 << 32));
       if (zeros != 0ull) {
         // one 2-byte store of zero per blocked element (typically one or two per row)
         const uint32_t row_addr = smem_u32(row_base + s * B_STAGE_BYTES);

@@ -39,7 +39,7 @@ struct FwdEpilogueParams {
   const float* w_tile_max;   // [T]
   const void* bias;          // [N] dtype or null
   const void* out_noise;     // [T,M,N] dtype or null (replay)
-  uint32_t* keep_mask;       // [T,M,mask_words] or null
+  uint32_t* keep_mask;       // [T,mask_words,M] or null
   int32_t mask_words;
   int32_t has_noise, has_bound, has_adc, bound_pc, noise_pc, no_rounding;
   float noise_coef, out_bound, out_res;

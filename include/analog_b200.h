@@ -111,8 +111,9 @@ typedef struct AlForwardArgs {
   void* w_tile_max;          /* [T] float  per-tile abs-max of w + [T] int32 flags behind it */
   void* w_mod;               /* [N,K] dtype modified weights; may equal w when the modifier
                                  does nothing in this call                                  */
-  uint32_t* keep_mask;       /* [T, M, ceil(N/32)] bit n%32 of word n/32 = 1 where the ADC
-                                 clamp passes the gradient; nullable if out_bound <= 0     */
+  uint32_t* keep_mask;       /* [T, ceil(N/32), M] word (t, n/32, m), bit n%32 = 1 where the
+                                 ADC clamp of tile t passes the gradient of out[m, n];
+                                 nullable if out_bound <= 0                                 */
   float* std_scratch;        /* >= al_std_scratch_floats(M, T) floats, static mode with
                                  init_from_data > 0 in training; nullable otherwise        */
   /* shared-noise parity mode: standard normals to use instead of the internal generator */

@@ -73,7 +73,7 @@ def test_config2_training_step_at_full_size():
     gg = g.cuda().float()
     bits = torch.arange(32, device="cuda", dtype=torch.int32)
     for t in (0, t_count - 1):
-        keep = ((mask[t].unsqueeze(-1) >> bits) & 1).reshape(m, -1)[:, :n].float()
+        keep = ((mask[t].T.unsqueeze(-1) >> bits) & 1).reshape(m, -1)[:, :n].float()  # mask is [T, N/32, M]
         g_t = gg * keep
         want_w = g_t.T @ xq[:, t * tile:(t + 1) * tile]
         want_x = g_t @ w_mod[:, t * tile:(t + 1) * tile]
