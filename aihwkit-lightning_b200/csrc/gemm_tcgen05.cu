@@ -57,6 +57,15 @@ constexpr int B_XFORM_THREADS = 128;   // per group; each group handles one stag
 constexpr int B_XFORM_GROUPS = 2;
 constexpr int kBwdThreads = (8 + 4 * B_XFORM_GROUPS) * 32;
 
+// backward kernel on CTA pairs: a 256 x 256 tile per pair, each CTA stages its 128 rows of A and
+// its 128 columns of B, so a stage is 32 KiB and six of them fit
+constexpr int P_BN = 256;
+constexpr int P_BN_CTA = 128;
+constexpr int P_STAGES = 6;
+constexpr int P_A_BYTES = BM * BK * 2;         // 16 KiB
+constexpr int P_B_BYTES = P_BN_CTA * BK * 2;   // 16 KiB
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+
 constexpr int kTmemCols = 512;
 
 enum ErrCode : uint32_t {
@@ -83,6 +92,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Arrival that publishes nothing: the caller wrote no data the waiter reads.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
@@ -155,6 +168,73 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster drive one 256-row MMA ------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `saddr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrival on an mbarrier of any CTA of the cluster (address from mapa_u32)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// wait side of a barrier that CTAs of the whole cluster arrive on
+__device__ __forceinline__ bool mbar_try_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// TMA tile load of a CTA pair: lands in this CTA's shared memory, completes bytes on the
+// mbarrier at `bar_cluster_addr`, which may live in either CTA of the pair.  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// commit of the pair's MMAs: one arrival on the barrier at this offset in every CTA of cta_mask
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(cta_mask)
+      : "memory");
+}
+// D[tmem of both CTAs] (+)= A[256 rows, 128 per CTA] * B[256 columns, 128 per CTA]
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -640,6 +720,27 @@ struct BwdTcParams {
   void* c_out;
 };
 
+// A heavily clamped 128-byte row of a staged A tile: rewrite its 16-byte chunks under the
+// expanded keep mask (bit j = keep element j).
+__device__ __forceinline__ void rewrite_row_masked(uint32_t row_addr, int sw, uint64_t keep) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint32_t kb = (uint32_t)(keep >> (8 * c)) & 0xffu;
+    if (kb == 0xffu) continue;
+    const uint32_t addr = row_addr + (uint32_t)((c ^ sw) << 4);
+    uint32_t v[4];
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr) : "memory");
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t two = (kb >> (2 * j)) & 3u;
+      v[j] &= (two & 1u) * 0x0000ffffu + (two >> 1) * 0xffff0000u;
+    }
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                 "r"(v[3]) : "memory");
+  }
+}
+
 template <bool WGRAD>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -821,81 +922,120 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->acc_empty[b]);
     }
-  } else if (warp >= 8 && masked) {
+  } else if (warp >= 8 && masked && (int)blockIdx.x < num_work) {
     // ---- mask transform: zero the gradient entries the tile's ADC clamp blocked ---------
     // B_XFORM_GROUPS groups of 128 threads take the stage-iterations round robin, so that
     // the fix-up of consecutive stages overlaps.  Within a group thread r owns one 128-byte
-    // row of the staged A tile; the two mask words of that row are fetched one turn ahead so
-    // that their L2 latency is off the TMA -> MMA critical path.
+    // row of the staged A tile and the two mask words that cover it.
     const int grp = (warp - 8) >> 2;
     const int r = threadIdx.x - (8 + 4 * grp) * 32;  // 0..127
     const int row_in_box = WGRAD ? (r & 63) : r;
     const int box = WGRAD ? (r >> 6) : 0;
     const int total = ((num_work - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * p.lsteps;
-    auto fetch = [&](int it, uint32_t* lo, uint32_t* hi) {
-      *lo = 0xffffffffu;
-      *hi = 0xffffffffu;
-      if (it < total) {
-        const int w = blockIdx.x + (it / p.lsteps) * gridDim.x;
-        const int l0 = (it % p.lsteps) * BK;
-        const int ib = w / (p.T * p.num_jb);
-        const int t = (w % (p.T * p.num_jb)) / p.num_jb;
-        const int m = WGRAD ? l0 + row_in_box : ib * BM + r;
-        const int n0 = WGRAD ? ib * BM + box * 64 : l0;
-        if (m < p.M) {
-          // word-major layout: the threads of a warp (consecutive rows) read consecutive words
-          const int w0 = n0 >> 5;
-          const uint32_t* mcol = p.keep_mask + ((int64_t)t * p.mask_words + w0) * p.M + m;
-          if (w0 < p.mask_words) *lo = mcol[0];
-          if (w0 + 1 < p.mask_words) *hi = mcol[p.M];
-        }
+    // Mask words are [T][word][M].  The fetch stream walks (work item, l-step) with a cursor
+    // instead of dividing per turn, and its loads are unconditional: indices past an edge
+    // are clamped to the last valid row / word.  What a clamped word may zero lies in rows or
+    // columns that the TMA copy filled with zeros anyway, and a load that nothing selects on
+    // does not stall the warp at the point of issue.
+    const int m_last = p.M - 1, w_last = p.mask_words - 1;
+    int f_w = (int)blockIdx.x + (grp / p.lsteps) * (int)gridDim.x, f_ls = grp % p.lsteps;
+    const uint32_t* f_lo = p.keep_mask;  // dgrad: word 0 of (t, row); wgrad: row 0 of (t, word)
+    const uint32_t* f_hi = p.keep_mask;
+    auto seek_item = [&]() {
+      if (f_w >= num_work) return;  // past the end: keep pointing at valid memory
+      const int ib = f_w / (p.T * p.num_jb);
+      const int t = (f_w % (p.T * p.num_jb)) / p.num_jb;
+      const uint32_t* tile = p.keep_mask + (int64_t)t * p.mask_words * p.M;
+      if (WGRAD) {
+        const int w0 = (ib * BM + box * 64) >> 5;
+        f_lo = tile + (int64_t)min(w0, w_last) * p.M;
+        f_hi = tile + (int64_t)min(w0 + 1, w_last) * p.M;
+      } else {
+        f_lo = tile + min(ib * BM + r, m_last);
+        f_hi = f_lo;
       }
     };
-    uint32_t lo0, hi0, lo1, hi1;
-    fetch(grp, &lo0, &hi0);
+    seek_item();
+    auto fetch = [&](uint32_t* lo, uint32_t* hi) {
+      if (WGRAD) {
+        const int m = min(f_ls * BK + row_in_box, m_last);
+        *lo = f_lo[m];
+        *hi = f_hi[m];
+      } else {
+        *lo = f_lo[(int64_t)min(2 * f_ls, w_last) * p.M];
+        *hi = f_hi[(int64_t)min(2 * f_ls + 1, w_last) * p.M];
+      }
+      f_ls += B_XFORM_GROUPS;
+      if (f_ls >= p.lsteps) {
+        do {
+          f_ls -= p.lsteps;
+          f_w += (int)gridDim.x;
+        } while (f_ls >= p.lsteps);
+        seek_item();
+      }
+    };
+    constexpr int kScanLimit = 6;  // blocked entries per row up to which single stores beat a rewrite
     uint8_t* const row_base = stage_base + box * B_BOX_BYTES + row_in_box * 128;
     const int sw = r & 7;  // 128-byte swizzle: 16-byte chunk index is XORed with row % 8
-    for (int it = grp; it < total; it += B_XFORM_GROUPS) {
-      fetch(it + B_XFORM_GROUPS, &lo1, &hi1);
+    // one stage-iteration of this thread's row; false = the wait gave up
+    auto process = [&](int it, uint32_t lo, uint32_t hi) -> bool {
       const int s = it % B_STAGES;
       const uint32_t ph = ((uint32_t)it / B_STAGES) & 1u;
-      uint64_t zeros = ~((uint64_t)lo0 | ((uint64_t)hi0 << 32));
+      uint64_t zeros = ~((uint64_t)lo | ((uint64_t)hi << 32));
       if (!__any_sync(0xffffffffu, zeros != 0ull)) {
-        // Nothing to zero in this warp's rows (the common case: a clamp that fires is rare).
-        // The warp's arrival must still land in the right phase of `ready`, so it waits for
-        // the stage's previous use to be consumed -- long before the copy lands, which takes
-        // this hand-off off the TMA -> MMA critical path.
+        // Nothing to zero in this warp's rows.  The warp's arrival must still land in the
+        // right phase of `ready`, so it waits for the stage's previous use to be consumed --
+        // long before the copy lands, which takes this hand-off off the TMA -> MMA critical
+        // path -- and it publishes no data, so the arrival is a relaxed one.
         bool okw = true;
         if (lane == 0) {
           okw = mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag);
-          if (okw) mbar_arrive(&bars->ready[s]);
+          if (okw) mbar_arrive_relaxed(&bars->ready[s]);
           else raise_error(kErrTransform, abort_flag);
         }
-        if (!__shfl_sync(0xffffffffu, okw, 0)) break;
-        lo0 = lo1;
-        hi0 = hi1;
-        continue;
+        return __shfl_sync(0xffffffffu, okw, 0);
       }
       if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
         raise_error(kErrTransform, abort_flag);
-        break;
+        return false;
       }
       if (zeros != 0ull) {
-        // one 2-byte store of zero per blocked element (typically one or two per row)
         const uint32_t row_addr = smem_u32(row_base + s * B_STAGE_BYTES);
-        while (zeros != 0ull) {
-          const int pos = __ffsll((long long)zeros) - 1;  // n - n0 of the blocked element
-          zeros &= zeros - 1ull;
-          const uint32_t addr = row_addr + (uint32_t)((((pos >> 3) ^ sw) << 4) + ((pos & 7) << 1));
-          asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)0) : "memory");
+        if (__popcll(zeros) <= kScanLimit) {
+          // one 2-byte store of zero per blocked element (typically one or two per row)
+          while (zeros != 0ull) {
+            const int pos = __ffsll((long long)zeros) - 1;  // n - n0 of the blocked element
+            zeros &= zeros - 1ull;
+            const uint32_t addr = row_addr + (uint32_t)((((pos >> 3) ^ sw) << 4) + ((pos & 7) << 1));
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)0) : "memory");
+          }
+        } else {
+          rewrite_row_masked(row_addr, sw, ~zeros);
         }
         fence_proxy_async_smem();
       }
       // one arrival per warp: 128 arrivals on one mbarrier would serialise in shared memory
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->ready[s]);
-      lo0 = lo1;
-      hi0 = hi1;
+      return true;
+    };
+    // The mask words run kAhead turns ahead of their use in a ring of registers (the loop is
+    // unrolled by the ring size so that every slot is a fixed register): a turn never waits
+    // for a load it issued itself.
+    constexpr int kRing = 4, kAhead = 3;
+    uint32_t lo[kRing], hi[kRing];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) fetch(&lo[u], &hi[u]);
+    bool ok = true;
+    for (int base = grp; base < total && ok; base += kRing * B_XFORM_GROUPS) {
+#pragma unroll
+      for (int u = 0; u < kRing; ++u) {
+        const int it = base + u * B_XFORM_GROUPS;
+        if (it < total && ok) {
+          fetch(&lo[(u + kAhead) % kRing], &hi[(u + kAhead) % kRing]);
+          ok = process(it, lo[u], hi[u]);
+        }
+      }
     }
   }
 
@@ -903,6 +1043,329 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward (dgrad / wgrad) on CTA pairs
+// ---------------------------------------------------------------------------------------------
+// Same GEMM as bwd_tc_kernel with one tcgen05.mma.cta_group::2 of 256 x 256 x 16 per k-step.
+// CTA `rank` of the pair owns rows [256 ib + 128 rank, +128) of C: it stages those rows of A and
+// columns [128 rank, +128) of the B block, holds its half of the accumulator in its own tensor
+// memory and writes its rows of C.  Each CTA therefore stages 32 KiB per 64-deep k-step instead of
+// 48 KiB, which buys two more pipeline stages and takes a third off the L2 -> shared-memory
+// traffic per flop.
+//
+// Barriers.  `empty`, `acc_full`: one copy per CTA, signalled in both by the leader's multicast
+// commit.  `acc_empty`, `ready`, `mma_done`: used in the leader (rank 0) only; the other CTA
+// arrives on them through the cluster address.  `full`: without a mask the leader's barrier
+// collects the bytes of both CTAs' copies and gates the MMA; with a mask each CTA's copies
+// complete on its own barrier, its transform warps fix the A tile up and then vouch for the
+// stage on the leader's `ready`, which gates the MMA.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    if (mbar_try_cluster(bar, parity)) return true;
+    if ((spin & 31u) == 31u) {
+      if (*abort_flag) return false;
+      uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kTimeoutNs) return false;
+    }
+  }
+}
+
+template <bool WGRAD>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kBwdThreads, 1)
+bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const BwdTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* stage_base = align_1024(smem_raw);
+  Barriers* bars = reinterpret_cast<Barriers*>(stage_base + P_STAGES * P_STAGE_BYTES);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const bool masked = p.keep_mask != nullptr;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int num_work = p.num_ib * p.T * p.num_jb;  // num_ib counts 256-row blocks here
+  const int row_off = (int)rank * BM;               // this CTA's rows inside the pair's block
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->ready[s], 2 * (B_XFORM_THREADS / 32));
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], 2 * B_EPI_WARPS);
+    }
+    mbar_init(&bars->mma_done, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc_pair(&bars->tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer (both CTAs) --------------------------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = pair; w < num_work && ok; w += n_pairs) {
+        const int ib = w / (p.T * p.num_jb);
+        const int rem = w % (p.T * p.num_jb);
+        const int t = rem / p.num_jb, jb = rem % p.num_jb;
+        const int i0 = ib * (2 * BM) + row_off;
+        const int j0 = t * p.tile_w + jb * P_BN + (int)rank * P_BN_CTA;
+        for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+          const int s = it % P_STAGES;
+          const uint32_t ph = (it / P_STAGES) & 1u;
+          if (!mbar_wait_cluster(&bars->empty[s], ph ^ 1u, abort_flag)) {
+            raise_error(kErrProducer, abort_flag);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = stage_base + s * P_STAGE_BYTES;
+          uint8_t* sb = sa + P_A_BYTES;
+          const int l0 = ls * BK;
+          uint32_t bar;
+          if (masked) {
+            mbar_expect_tx(&bars->full[s], P_STAGE_BYTES);
+            bar = smem_u32(&bars->full[s]);
+          } else {
+            if (leader) mbar_expect_tx(&bars->full[s], 2 * P_STAGE_BYTES);
+            bar = mapa_u32(smem_u32(&bars->full[s]), 0);
+          }
+          if (WGRAD) {
+            tma_load_2d_pair(sa, &map_a, bar, i0, l0);
+            tma_load_2d_pair(sa + B_BOX_BYTES, &map_a, bar, i0 + 64, l0);
+          } else {
+            tma_load_2d_pair(sa, &map_a, bar, l0, i0);
+          }
+#pragma unroll
+          for (int c = 0; c < P_BN_CTA / 64; ++c)
+            tma_load_2d_pair(sb + c * B_BOX_BYTES, &map_b, bar, j0 + c * 64, l0);
+        }
+      }
+      // drain: copies that complete on this CTA's own barrier must have landed before it exits;
+      // copies that complete on the leader's barrier are covered by the leader's drain and the
+      // cluster barrier at the end
+      if (masked || leader) {
+        const uint32_t n_back = it < (uint32_t)P_STAGES ? it : (uint32_t)P_STAGES;
+        for (uint32_t j = it - n_back; j < it; ++j) {
+          const int s = j % P_STAGES;
+          const uint32_t ph = (j / P_STAGES) & 1u;
+          uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_cluster(&bars->full[s], ph)) {
+            if (globaltimer_ns() - t0 > kTimeoutNs) {
+              raise_error(kErrDrain, abort_flag);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer (leader only) --------------------------------------------------------
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc(2 * BM, P_BN, WGRAD ? 1 : 0, 1);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int w = pair; w < num_work && ok; w += n_pairs, ++acc_it) {
+        const int b = acc_it & 1u;
+        const uint32_t aph = (acc_it >> 1) & 1u;
+        if (!mbar_wait_cluster(&bars->acc_empty[b], aph ^ 1u, abort_flag)) {
+          raise_error(kErrMma, abort_flag);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * P_BN);
+        for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+          const int s = it % P_STAGES;
+          const uint32_t ph = (it / P_STAGES) & 1u;
+          if (!mbar_wait_cluster(masked ? &bars->ready[s] : &bars->full[s], ph, abort_flag)) {
+            raise_error(kErrMma, abort_flag);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stage_base + s * P_STAGE_BYTES);
+          const uint32_t sb = sa + P_A_BYTES;
+          const uint64_t da = WGRAD ? desc_mn_major(sa, B_BOX_BYTES) : desc_k_major(sa);
+          const uint64_t db = desc_mn_major(sb, B_BOX_BYTES);
+          constexpr uint64_t a_step = WGRAD ? (2048u >> 4) : (32u >> 4);
+          constexpr uint64_t b_step = 2048u >> 4;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4)
+            umma_bf16_pair(d_tmem, da + a_step * k4, db + b_step * k4, idesc, (ls | k4) != 0 ? 1u : 0u);
+          umma_commit_pair(&bars->empty[s], 3);  // frees the stage in both CTAs
+        }
+        if (ok) umma_commit_pair(&bars->acc_full[b], 3);
+      }
+      umma_commit_pair(&bars->mma_done, 1);
+      uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_cluster(&bars->mma_done, 0)) {
+        if (globaltimer_ns() - t0 > kTimeoutNs) {
+          raise_error(kErrDrain, abort_flag);
+          break;
+        }
+      }
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ---- epilogue (both CTAs): own half of the accumulator -> bf16 -> own rows of C --------
+    const int quad = warp & 3;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int w = pair; w < num_work && ok; w += n_pairs, ++acc_it) {
+      const int ib = w / (p.T * p.num_jb);
+      const int rem = w % (p.T * p.num_jb);
+      const int t = rem / p.num_jb, jb = rem % p.num_jb;
+      const int j0 = t * p.tile_w + jb * P_BN;
+      const int j_end = min((t + 1) * p.tile_w, p.K);
+      const int i = ib * (2 * BM) + row_off + quad * 32 + lane;
+      const int b = acc_it & 1u;
+      const uint32_t aph = (acc_it >> 1) & 1u;
+      if (!mbar_wait_cluster(&bars->acc_full[b], aph, abort_flag)) {
+        if (lane == 0) raise_error(kErrEpilogue, abort_flag);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint16_t* dst_row = reinterpret_cast<uint16_t*>(p.c_out) + (int64_t)i * p.K;
+#pragma unroll 1
+      for (int c = 0; c < P_BN / 32; ++c) {
+        const int jc = j0 + c * 32;
+        if (jc >= j_end) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(tmem_base + lane_base + (uint32_t)(b * P_BN + c * 32), r);
+        tmem_wait_ld();
+        if (i < p.I) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (jc + v * 8 < j_end) {
+              uint4 pk = make_uint4(
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1])),
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3])),
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5])),
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7])));
+              *reinterpret_cast<uint4*>(dst_row + jc + v * 8) = pk;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->acc_empty[b]), 0));
+    }
+  } else if (warp >= 8 && masked && pair < num_work) {
+    // ---- mask transform (both CTAs, own A tile): see bwd_tc_kernel -------------------------
+    const int grp = (warp - 8) >> 2;
+    const int r = threadIdx.x - (8 + 4 * grp) * 32;  // 0..127
+    const int row_in_box = WGRAD ? (r & 63) : r;
+    const int box = WGRAD ? (r >> 6) : 0;
+    const int total = ((num_work - pair + n_pairs - 1) / n_pairs) * p.lsteps;
+    const int m_last = p.M - 1, w_last = p.mask_words - 1;
+    int f_w = pair + (grp / p.lsteps) * n_pairs, f_ls = grp % p.lsteps;
+    const uint32_t* f_lo = p.keep_mask;
+    const uint32_t* f_hi = p.keep_mask;
+    auto seek_item = [&]() {
+      if (f_w >= num_work) return;
+      const int ib = f_w / (p.T * p.num_jb);
+      const int t = (f_w % (p.T * p.num_jb)) / p.num_jb;
+      const int i0 = ib * (2 * BM) + row_off;
+      const uint32_t* tile = p.keep_mask + (int64_t)t * p.mask_words * p.M;
+      if (WGRAD) {
+        const int w0 = (i0 + box * 64) >> 5;
+        f_lo = tile + (int64_t)min(w0, w_last) * p.M;
+        f_hi = tile + (int64_t)min(w0 + 1, w_last) * p.M;
+      } else {
+        f_lo = tile + min(i0 + r, m_last);
+        f_hi = f_lo;
+      }
+    };
+    seek_item();
+    auto fetch = [&](uint32_t* lo, uint32_t* hi) {
+      if (WGRAD) {
+        const int m = min(f_ls * BK + row_in_box, m_last);
+        *lo = f_lo[m];
+        *hi = f_hi[m];
+      } else {
+        *lo = f_lo[(int64_t)min(2 * f_ls, w_last) * p.M];
+        *hi = f_hi[(int64_t)min(2 * f_ls + 1, w_last) * p.M];
+      }
+      f_ls += B_XFORM_GROUPS;
+      if (f_ls >= p.lsteps) {
+        do {
+          f_ls -= p.lsteps;
+          f_w += n_pairs;
+        } while (f_ls >= p.lsteps);
+        seek_item();
+      }
+    };
+    constexpr int kScanLimit = 6;
+    uint8_t* const row_base = stage_base + box * B_BOX_BYTES + row_in_box * 128;
+    const int sw = r & 7;
+    auto process = [&](int it, uint32_t lo, uint32_t hi) -> bool {
+      const int s = it % P_STAGES;
+      const uint32_t ph = ((uint32_t)it / P_STAGES) & 1u;
+      // the MMA waits on `ready` alone, so every warp waits for its CTA's copy before it vouches
+      if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
+        raise_error(kErrTransform, abort_flag);
+        return false;
+      }
+      uint64_t zeros = ~((uint64_t)lo | ((uint64_t)hi << 32));
+      if (zeros != 0ull) {
+        const uint32_t row_addr = smem_u32(row_base + s * P_STAGE_BYTES);
+        if (__popcll(zeros) <= kScanLimit) {
+          while (zeros != 0ull) {
+            const int pos = __ffsll((long long)zeros) - 1;
+            zeros &= zeros - 1ull;
+            const uint32_t addr = row_addr + (uint32_t)((((pos >> 3) ^ sw) << 4) + ((pos & 7) << 1));
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)0) : "memory");
+          }
+        } else {
+          rewrite_row_masked(row_addr, sw, ~zeros);
+        }
+        fence_proxy_async_smem();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->ready[s]), 0));
+      return true;
+    };
+    constexpr int kRing = 4, kAhead = 3;
+    uint32_t lo[kRing], hi[kRing];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) fetch(&lo[u], &hi[u]);
+    bool ok = true;
+    for (int base = grp; base < total && ok; base += kRing * B_XFORM_GROUPS) {
+#pragma unroll
+      for (int u = 0; u < kRing; ++u) {
+        const int it = base + u * B_XFORM_GROUPS;
+        if (it < total && ok) {
+          fetch(&lo[(u + kAhead) % kRing], &hi[(u + kAhead) % kRing]);
+          ok = process(it, lo[u], hi[u]);
+        }
+      }
+    }
+  }
+
+  // nothing of this CTA's shared or tensor memory may go while the peer can still signal or
+  // read it: both CTAs meet before the pair's tensor memory is released
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -965,6 +1428,7 @@ int sm_count() {
 
 constexpr int F_SMEM = F_STAGES * F_STAGE_BYTES + (int)sizeof(Barriers) + 1024;
 constexpr int B_SMEM = B_STAGES * B_STAGE_BYTES + (int)sizeof(Barriers) + 1024;
+constexpr int P_SMEM = P_STAGES * P_STAGE_BYTES + (int)sizeof(Barriers) + 1024;
 
 template <class Kernel>
 int ensure_smem(Kernel k, int bytes) {
@@ -1062,6 +1526,47 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
   return check_launch("fwd_tc");
 }
 
+// How many 2-CTA clusters of the pair kernel the device runs at once (0: cannot run them).
+static int max_pairs(bool wgrad) {
+  static int cached[2] = {-1, -1};
+  int& n = cached[wgrad ? 1 : 0];
+  if (n >= 0) return n;
+  n = 0;
+  if ((wgrad ? ensure_smem(bwd_tc_pair_kernel<true>, P_SMEM) : ensure_smem(bwd_tc_pair_kernel<false>, P_SMEM)) != AL_OK)
+    return n;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * sm_count());
+  cfg.blockDim = dim3(kBwdThreads);
+  cfg.dynamicSmemBytes = P_SMEM;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  cudaError_t e = wgrad ? cudaOccupancyMaxActiveClusters(&clusters, bwd_tc_pair_kernel<true>, &cfg)
+                        : cudaOccupancyMaxActiveClusters(&clusters, bwd_tc_pair_kernel<false>, &cfg);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return n;
+  }
+  n = clusters;
+  return n;
+}
+// AL_BWD_PAIR=0 keeps the backward GEMMs on single CTAs, AL_BWD_PAIR=2 sends every problem to
+// the CTA-pair kernel (tests use it to cover that kernel at small sizes); otherwise pairs are
+// used when there is at least one 256 x 256 block per pair of SMs.
+static int pair_kernel_mode() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("AL_BWD_PAIR");
+    v = (e && e[0] == '0') ? 0 : (e && e[0] == '2') ? 2 : 1;
+  }
+  return v;
+}
+
 static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint32_t* keep_mask,
                          int mask_words, int M, int K, int N, const TileTable& tt, void* c_out,
                          cudaStream_t s) {
@@ -1102,6 +1607,21 @@ static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint
     uint32_t box[2] = {64, BK};
     rc = make_map(&map_b, b_op, 2, dims, strides, box);
     if (rc) return rc;
+  }
+  // CTA pairs (256-row blocks) when they fill the machine; single CTAs for smaller problems
+  const int pair_work = ((p.I + 2 * BM - 1) / (2 * BM)) * p.T * p.num_jb;
+  const int pairs = max_pairs(wgrad);
+  const int mode = pair_kernel_mode();
+  if (pairs > 0 && mode != 0 && (pair_work >= pairs || mode == 2)) {
+    p.num_ib = (p.I + 2 * BM - 1) / (2 * BM);
+    rc = wgrad ? ensure_smem(bwd_tc_pair_kernel<true>, P_SMEM) : ensure_smem(bwd_tc_pair_kernel<false>, P_SMEM);
+    if (rc) return rc;
+    const int grid = 2 * (pair_work < pairs ? pair_work : pairs);
+    if (wgrad)
+      bwd_tc_pair_kernel<true><<<grid, kBwdThreads, P_SMEM, s>>>(map_a, map_b, p);
+    else
+      bwd_tc_pair_kernel<false><<<grid, kBwdThreads, P_SMEM, s>>>(map_a, map_b, p);
+    return check_launch(wgrad ? "wgrad_tc_pair" : "dgrad_tc_pair");
   }
   int work = p.num_ib * p.T * p.num_jb;
   int grid = work < sm_count() ? work : sm_count();
