@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "liba
 
 AL_F32, AL_BF16 = 0, 1
 AL_IR_OFF, AL_IR_STATIC, AL_IR_DYNAMIC, AL_IR_FAST = 0, 1, 2, 3
-AL_ENGINE_AUTO, AL_ENGINE_SIMT, AL_ENGINE_TCGEN05 = 0, 1, 2
+AL_ENGINE_AUTO, AL_ENGINE_SIMT, AL_ENGINE_TCGEN05, AL_ENGINE_TCGEN05_PAIR, AL_ENGINE_TCGEN05_SINGLE = 0, 1, 2, 3, 4
 (AL_OK, AL_ERR_BAD_ARGUMENT, AL_ERR_UNSUPPORTED, AL_ERR_CUDA, AL_ERR_DEVICE_TIMEOUT,
  AL_ERR_TOO_LARGE) = range(6)
 

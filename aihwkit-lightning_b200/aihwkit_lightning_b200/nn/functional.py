@@ -33,7 +33,8 @@ _CLIP = {
     WeightClipType.LEARNABLE_PER_CHANNEL: 3,
 }
 _DTYPE = {torch.float32: _lib.AL_F32, torch.bfloat16: _lib.AL_BF16}
-_ENGINE = {"auto": _lib.AL_ENGINE_AUTO, "simt": _lib.AL_ENGINE_SIMT, "tcgen05": _lib.AL_ENGINE_TCGEN05}
+_ENGINE = {"auto": _lib.AL_ENGINE_AUTO, "simt": _lib.AL_ENGINE_SIMT, "tcgen05": _lib.AL_ENGINE_TCGEN05,
+           "tcgen05_pair": _lib.AL_ENGINE_TCGEN05_PAIR, "tcgen05_single": _lib.AL_ENGINE_TCGEN05_SINGLE}
 
 
 class _Settings:

@@ -334,7 +334,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
   ep.noise_coef = dv.noise_coef; ep.out_bound = dv.out_bound; ep.out_res = dv.out_res;
   ep.seed = a->seed; ep.offset = a->offset;
 
-  if (d.engine == AL_ENGINE_TCGEN05 && !tc_forward_supported(d, tt)) {
+  if (d.engine >= AL_ENGINE_TCGEN05 && !tc_forward_supported(d, tt)) {
     set_error("tcgen05 engine requested but the problem does not qualify (bf16, 16-byte aligned tiles)");
     return AL_ERR_UNSUPPORTED;
   }
@@ -375,7 +375,8 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
   one.T = 1;
   one.ends[0] = d.K;
   const TileTable& gt = mask ? tt : one;
-  if (d.engine == AL_ENGINE_TCGEN05 && !tc_backward_supported(d, tt)) {
+  const int pairing = d.engine == AL_ENGINE_TCGEN05_PAIR ? 1 : d.engine == AL_ENGINE_TCGEN05_SINGLE ? -1 : 0;
+  if (d.engine >= AL_ENGINE_TCGEN05 && !tc_backward_supported(d, tt)) {
     set_error("tcgen05 engine requested but the problem does not qualify");
     return AL_ERR_UNSUPPORTED;
   }
@@ -386,7 +387,7 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
       set_error("al_backward: w_mod missing");
       return AL_ERR_BAD_ARGUMENT;
     }
-    rc = tc ? launch_dgrad_tc(a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, a->grad_x, s)
+    rc = tc ? launch_dgrad_tc(a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, pairing, a->grad_x, s)
             : launch_dgrad_simt(d.dtype, a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, a->grad_x, s);
     if (rc) return rc;
     if (d.ir_mode == AL_IR_STATIC || d.ir_mode == AL_IR_FAST) {
@@ -408,7 +409,7 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
       set_error("al_backward: xq missing");
       return AL_ERR_BAD_ARGUMENT;
     }
-    rc = tc ? launch_wgrad_tc(a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt, a->grad_w, s)
+    rc = tc ? launch_wgrad_tc(a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt, pairing, a->grad_w, s)
             : launch_wgrad_simt(d.dtype, a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt, a->grad_w, s);
     if (rc) return rc;
   }

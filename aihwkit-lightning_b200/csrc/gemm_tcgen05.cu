@@ -1555,20 +1555,8 @@ static int max_pairs(bool wgrad) {
   n = clusters;
   return n;
 }
-// AL_BWD_PAIR=0 keeps the backward GEMMs on single CTAs, AL_BWD_PAIR=2 sends every problem to
-// the CTA-pair kernel (tests use it to cover that kernel at small sizes); otherwise pairs are
-// used when there is at least one 256 x 256 block per pair of SMs.
-static int pair_kernel_mode() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("AL_BWD_PAIR");
-    v = (e && e[0] == '0') ? 0 : (e && e[0] == '2') ? 2 : 1;
-  }
-  return v;
-}
-
 static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint32_t* keep_mask,
-                         int mask_words, int M, int K, int N, const TileTable& tt, void* c_out,
+                         int mask_words, int M, int K, int N, const TileTable& tt, int pairing, void* c_out,
                          cudaStream_t s) {
   int w = 0;
   if (!uniform_tiles(tt, &w) || !aligned16(g) || !aligned16(b_op) || !aligned16(c_out)) {
@@ -1611,8 +1599,7 @@ static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint
   // CTA pairs (256-row blocks) when they fill the machine; single CTAs for smaller problems
   const int pair_work = ((p.I + 2 * BM - 1) / (2 * BM)) * p.T * p.num_jb;
   const int pairs = max_pairs(wgrad);
-  const int mode = pair_kernel_mode();
-  if (pairs > 0 && mode != 0 && (pair_work >= pairs || mode == 2)) {
+  if (pairs > 0 && pairing >= 0 && (pair_work >= pairs || pairing > 0)) {
     p.num_ib = (p.I + 2 * BM - 1) / (2 * BM);
     rc = wgrad ? ensure_smem(bwd_tc_pair_kernel<true>, P_SMEM) : ensure_smem(bwd_tc_pair_kernel<false>, P_SMEM);
     if (rc) return rc;
@@ -1633,15 +1620,15 @@ static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint
 }
 
 int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask, int mask_words,
-                    int M, int K, int N, const TileTable& tt, void* grad_x, cudaStream_t s) {
+                    int M, int K, int N, const TileTable& tt, int pairing, void* grad_x, cudaStream_t s) {
   ProfScope prof(AL_K_DGRAD_GEMM, s);
-  return launch_bwd_tc(false, g, w_mod, keep_mask, mask_words, M, K, N, tt, grad_x, s);
+  return launch_bwd_tc(false, g, w_mod, keep_mask, mask_words, M, K, N, tt, pairing, grad_x, s);
 }
 
 int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, int mask_words,
-                    int M, int K, int N, const TileTable& tt, void* grad_w, cudaStream_t s) {
+                    int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s) {
   ProfScope prof(AL_K_WGRAD_GEMM, s);
-  return launch_bwd_tc(true, g, xq, keep_mask, mask_words, M, K, N, tt, grad_w, s);
+  return launch_bwd_tc(true, g, xq, keep_mask, mask_words, M, K, N, tt, pairing, grad_w, s);
 }
 
 int tc_read_device_error(cudaStream_t s, uint32_t* code) {

@@ -118,10 +118,12 @@ bool tc_forward_supported(const AlDesc& d, const TileTable& tt);
 int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const TileTable& tt,
                   const FwdEpilogueParams& ep, void* out, cudaStream_t s);
 bool tc_backward_supported(const AlDesc& d, const TileTable& tt);
+// pairing: 0 = CTA pairs when they fill the machine, 1 = always pairs, -1 = never
+// pairing: 0 = CTA pairs when they fill the machine, 1 = always pairs, -1 = never
 int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask, int mask_words,
-                    int M, int K, int N, const TileTable& tt, void* grad_x, cudaStream_t s);
+                    int M, int K, int N, const TileTable& tt, int pairing, void* grad_x, cudaStream_t s);
 int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, int mask_words,
-                    int M, int K, int N, const TileTable& tt, void* grad_w, cudaStream_t s);
+                    int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s);
 int tc_read_device_error(cudaStream_t s, uint32_t* code);
 
 }  // namespace al

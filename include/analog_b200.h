@@ -51,8 +51,14 @@ enum AlClipType {
 enum AlInputRangeMode { AL_IR_OFF = 0, AL_IR_STATIC = 1, AL_IR_DYNAMIC = 2, AL_IR_FAST = 3 };
 
 /* GEMM engine selection.  AUTO picks the tcgen05/TMA kernels whenever dtype and alignment
- * allow and the SIMT kernels otherwise; the other two force one of them (tests). */
-enum AlEngine { AL_ENGINE_AUTO = 0, AL_ENGINE_SIMT = 1, AL_ENGINE_TCGEN05 = 2 };
+ * allow and the SIMT kernels otherwise; SIMT and TCGEN05 force one of them (tests).  The
+ * tcgen05 backward GEMMs run on CTA pairs (cta_group::2) when the problem has a 256 x 256 block
+ * per pair of SMs and on single CTAs otherwise; TCGEN05_PAIR / TCGEN05_SINGLE force that choice
+ * as well (tests, comparisons). */
+enum AlEngine {
+  AL_ENGINE_AUTO = 0, AL_ENGINE_SIMT = 1, AL_ENGINE_TCGEN05 = 2,
+  AL_ENGINE_TCGEN05_PAIR = 3, AL_ENGINE_TCGEN05_SINGLE = 4
+};
 
 /*
  * Flattened `TorchInferenceRPUConfig` (`simulator/configs/configs.py:27-88`) plus the problem

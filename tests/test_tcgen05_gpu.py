@@ -47,14 +47,16 @@ def device_error():
 
 
 @pytest.mark.parametrize("base,over", SHAPES, ids=[f"{b}-{'x'.join(map(str, o['in_shape']))}x{o['out_features']}" for b, o in SHAPES])
-def test_tcgen05_engine_matches_oracle_and_simt(base, over):
+@pytest.mark.parametrize("engine", ["tcgen05_single", "tcgen05_pair"])
+def test_tcgen05_engine_matches_oracle_and_simt(base, over, engine):
+    """``engine`` picks the backward GEMM kernel: single CTAs or CTA pairs (cta_group::2)."""
     case = dict(C.CASES_BY_NAME[base])
     case.update(over)
     case["weight_scale"] = 0.05
     data = C.make_inputs(case)
     rec, grads = oracle_run(case, data, w_noise=data["w_noise"][-1], out_noise=data["out_noise"][-1])
     cap = {}
-    layer, x, out = run_product_layer(case, data, engine="tcgen05", capture=cap)
+    layer, x, out = run_product_layer(case, data, engine=engine, capture=cap)
     assert cap["uses_tcgen05"]
     assert device_error() == (0, 0)
     layer2, x2, out2 = run_product_layer(case, data, engine="simt")
