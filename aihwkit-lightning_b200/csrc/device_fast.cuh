@@ -17,16 +17,19 @@ __device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 h) { return *reinterpr
 // manipulation; logarithm, square root and sine/cosine use the approximate hardware
 // functions.  The 16-bit radius limits a draw to |z| < 4.71.
 __device__ __forceinline__ void box_muller16(uint32_t ab, float* z0, float* z1) {
-  // low 16 bits -> radius, high 16 bits -> angle.  0x4b000000 | k is the float 2^23 + k, so one
-  // byte permute and one subtraction turn a 16-bit integer into a float without a conversion.
-  const float k1 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7610)) - 8388608.0f;  // 0 .. 65535
-  const float k2 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7632)) - 8388608.0f;
-  const float u1 = fmaf(k1, -1.52587890625e-05f, 1.0f);  // (0, 1], step 2^-16: never denormal
+  // low 16 bits -> radius, high 16 bits -> angle.  0x4b000000 | k is the float 2^23 + k, so a
+  // byte permute turns a 16-bit integer k into the float f = 2^23 + k without a conversion; the
+  // 2^23 is folded into the constant of the multiply-add that consumes f.
+  const float f1 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7610));  // 2^23 + (0 .. 65535)
+  const float f2 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7632));
+  const float u1 = fmaf(f1, -1.52587890625e-05f, 129.0f);  // 1 - k1 / 65536, exact: (0, 1], never denormal
   // .ftz forms: single MUFU instructions (the default forms wrap them in denormal handling)
   float lg, r, s, c;
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(u1));
   asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(-1.3862943611198906f * lg));
-  const float phi = 9.587379924285257e-05f * k2;  // 2*pi * k2 / 65536
+  // 2*pi * k2 / 65536 up to a constant offset below 4e-5 (the rounding of the folded constant),
+  // which a uniform angle does not notice
+  const float phi = fmaf(f2, 9.587379924285257e-05f, -804.24771931898713f);
   asm("sin.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(phi));
   asm("cos.approx.ftz.f32 %0, %1;" : "=f"(c) : "f"(phi));
   *z0 = r * c;
@@ -48,6 +51,40 @@ __device__ __forceinline__ Philox4 philox4x32_wide(uint32_t c0, uint32_t c1, uin
   Philox4 out;
   out.v[0] = c0; out.v[1] = c1; out.v[2] = c2; out.v[3] = c3;
   return out;
+}
+// The same generator with everything that depends only on (seed, offset, stream) prepared on the
+// host: the fourteen round keys and the two fixed counter words.  Passed inside a kernel's
+// parameter block they are constant-bank operands of the XORs, so a round costs two wide
+// multiplies and two three-input XORs.
+struct NoiseKeys {
+  uint32_t k[14];  // k[2r] = seed.lo + r * 0x9E3779B9, k[2r+1] = seed.hi + r * 0xBB67AE85
+  uint32_t c2, c3;
+};
+__host__ __device__ inline NoiseKeys make_noise_keys(uint64_t seed, uint64_t offset, uint32_t stream) {
+  NoiseKeys nk;
+  for (int r = 0; r < 7; ++r) {
+    nk.k[2 * r] = (uint32_t)seed + (uint32_t)r * 0x9E3779B9u;
+    nk.k[2 * r + 1] = (uint32_t)(seed >> 32) + (uint32_t)r * 0xBB67AE85u;
+  }
+  nk.c2 = (uint32_t)offset;
+  nk.c3 = (uint32_t)(offset >> 32) ^ (stream * 0x85EBCA6Bu) ^ 0x5bd1e995u;
+  return nk;
+}
+// same values as normal8_fast(seed, offset, stream, group8, z)
+__device__ __forceinline__ void normal8_keyed(const NoiseKeys& nk, uint64_t group8, float z[8]) {
+  uint32_t c0 = (uint32_t)group8, c1 = (uint32_t)(group8 >> 32), c2 = nk.c2, c3 = nk.c3;
+#pragma unroll
+  for (int r = 0; r < 7; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ nk.k[2 * r];
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ nk.k[2 * r + 1];
+    c0 = n0; c1 = (uint32_t)p1; c2 = n2; c3 = (uint32_t)p0;
+  }
+  box_muller16(c0, &z[0], &z[1]);
+  box_muller16(c1, &z[2], &z[3]);
+  box_muller16(c2, &z[4], &z[5]);
+  box_muller16(c3, &z[6], &z[7]);
 }
 // Eight normals for elements [8*group8, 8*group8 + 8) of stream `stream` of call (seed, offset).
 __device__ __forceinline__ void normal8_fast(uint64_t seed, uint64_t offset, uint32_t stream, uint64_t group8,

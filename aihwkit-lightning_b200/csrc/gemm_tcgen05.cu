@@ -372,6 +372,7 @@ struct FwdTcParams {
   int32_t ksteps;      // ceil(tile_w / 64)
   int32_t num_mb, num_nb;
   FwdEpilogueParams ep;
+  NoiseKeys noise;     // output-noise stream of this call, prepared on the host
   void* out;
 };
 
@@ -545,6 +546,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         }
         tc_fence_after();
         uint32_t keep_bits = 0;
+        // eight consecutive elements share one generator call (N is a multiple of 8 on this path)
+        const uint64_t row_group8 = (((uint64_t)t * M + (row_ok ? m : 0)) * N) >> 3;
         const bool packed = RD == kBF16 && !per_channel;  // bf16x2 arithmetic, bf16x2 running sum
         const __nv_bfloat162 sc2 = __float2bfloat162_rn(sc), step2 = __float2bfloat162_rn(step);
         const __nv_bfloat162 bound2 = __float2bfloat162_rn(bound), nbound2 = __float2bfloat162_rn(-bound);
@@ -565,8 +568,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 #pragma unroll
             for (int g8 = 0; g8 < 2; ++g8) {
               const int nq = nh + g8 * 8;
-              const uint64_t idx = ((uint64_t)t * M + (row_ok ? m : 0)) * N + (nq < N ? nq : 0);
               if (replay) {
+                const uint64_t idx = ((uint64_t)t * M + (row_ok ? m : 0)) * N + (nq < N ? nq : 0);
                 const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(ep.out_noise) + idx);
                 const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -575,7 +578,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                   z[g8 * 8 + 2 * q + 1] = __uint_as_float(rw[q] & 0xffff0000u);
                 }
               } else {
-                normal8_fast(ep.seed, ep.offset, 1u, idx >> 3, &z[g8 * 8]);
+                normal8_keyed(p.noise, row_group8 + (uint32_t)((nq < N ? nq : 0) >> 3), &z[g8 * 8]);
               }
             }
           }
@@ -1477,6 +1480,7 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
   p.num_mb = (ep.M + BM - 1) / BM;
   p.num_nb = (ep.N + F_BN - 1) / F_BN;
   p.ep = ep;
+  p.noise = make_noise_keys(ep.seed, ep.offset, 1u);
   p.out = out;
   {
     // |o| <= tile_w * ir * wmax * (1 + noise) and step = 2 * out_bound * ir * wmax / states
