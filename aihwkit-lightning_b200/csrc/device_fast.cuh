@@ -96,6 +96,37 @@ __device__ __forceinline__ void normal8_fast(uint64_t seed, uint64_t offset, uin
   for (int i = 0; i < 4; ++i) box_muller16(p.v[i], &z[2 * i], &z[2 * i + 1]);
 }
 
+// Two fp32 lanes in one 64-bit register: sm_100 executes fma / mul / add on such a pair as one
+// instruction with the same per-lane IEEE rounding as the scalar forms.
+__device__ __forceinline__ uint64_t f32x2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f32x2_unpack(uint64_t v, float* lo, float* hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(*lo), "=f"(*hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f32x2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f32x2_mul(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t f32x2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// fdiv_rcp on both lanes: y2 = (1/b, 1/b) correctly rounded, nb2 = (-b, -b)
+__device__ __forceinline__ uint64_t f32x2_div_rcp(uint64_t a, uint64_t nb2, uint64_t y2) {
+  const uint64_t q = f32x2_mul(a, y2);
+  return f32x2_fma(f32x2_fma(q, nb2, a), y2, q);
+}
+
 // round-half-even with two additions, without a range guard: only for |x| < 2^22, which holds
 // for DAC codes (|x| <= input range  =>  |x / step| <= inp_res / 2 + 1)
 __device__ __forceinline__ float rint_small(float x) {

@@ -552,6 +552,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const __nv_bfloat162 sc2 = __float2bfloat162_rn(sc), step2 = __float2bfloat162_rn(step);
         const __nv_bfloat162 bound2 = __float2bfloat162_rn(bound), nbound2 = __float2bfloat162_rn(-bound);
         const __nv_bfloat162 zero2 = __float2bfloat162_rn(0.0f);
+        const uint64_t nstepc2 = f32x2_pack(-stepc, -stepc), rstep2 = f32x2_pack(rstep, rstep);
+        const uint64_t magic2 = f32x2_pack(12582912.0f, 12582912.0f), nmagic2 = f32x2_pack(-12582912.0f, -12582912.0f);
 #pragma unroll 1
         for (int h = 0; h < 2; ++h) {
           const int cc = col0 + h * 16;
@@ -597,14 +599,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 o2 = __hadd2_rn(o2, __hmul2_rn(sc2, z2));
               }
               if (has_adc) {
-                const float q_lo = fdiv_rcp(__low2float(o2), stepc, rstep);
-                const float q_hi = fdiv_rcp(__high2float(o2), stepc, rstep);
+                // both elements of the pair side by side in fp32x2 arithmetic
+                float q_lo, q_hi;
+                f32x2_unpack(f32x2_div_rcp(f32x2_pack(__low2float(o2), __high2float(o2)), nstepc2, rstep2), &q_lo, &q_hi);
                 const __nv_bfloat162 q2 = __floats2bfloat162_rn(q_lo, q_hi);
                 float c_lo = __low2float(q2), c_hi = __high2float(q2);
                 if (!no_round) {
                   // bf16-valued codes: the unguarded add-based rint is exact below 2^38
-                  c_lo = small_codes ? rint_small(c_lo) : rint_magic(c_lo);
-                  c_hi = small_codes ? rint_small(c_hi) : rint_magic(c_hi);
+                  if (small_codes) {
+                    f32x2_unpack(f32x2_add(f32x2_add(f32x2_pack(c_lo, c_hi), magic2), nmagic2), &c_lo, &c_hi);
+                  } else {
+                    c_lo = rint_magic(c_lo);
+                    c_hi = rint_magic(c_hi);
+                  }
                 }
                 // an integer-rounded bf16 value is a bf16 value: packing is a bit move
                 const uint32_t c2 = __byte_perm(__float_as_uint(c_lo), __float_as_uint(c_hi), 0x7632);
