@@ -338,7 +338,8 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     set_error("tcgen05 engine requested but the problem does not qualify (bf16, 16-byte aligned tiles)");
     return AL_ERR_UNSUPPORTED;
   }
-  if (pick_tc(d, tt, false)) return launch_fwd_tc(dv.round_dt, xq, w_mod, d.K, tt, ep, a->out, s);
+  const int pairing = d.engine == AL_ENGINE_TCGEN05_PAIR ? 1 : d.engine == AL_ENGINE_TCGEN05_SINGLE ? -1 : 0;
+  if (pick_tc(d, tt, false)) return launch_fwd_tc(dv.round_dt, xq, w_mod, d.K, tt, ep, pairing, a->out, s);
   return launch_fwd_simt(d.dtype, dv.round_dt, xq, w_mod, d.K, tt, ep, a->out, s);
 }
 

@@ -40,6 +40,8 @@ constexpr uint64_t kTimeoutNs = 2000000000ull;
 // forward kernel
 constexpr int F_BN = 128;
 constexpr int F_STAGES = 6;
+constexpr int FP_STAGES = 5;   // CTA pairs: 64 KiB of shared memory hold the running sum
+constexpr int FP_SUM_BYTES = BM * 2 * F_BN * 2;
 constexpr int F_A_BYTES = BM * BK * 2;     // 16 KiB
 constexpr int F_B_BYTES = F_BN * BK * 2;   // 16 KiB
 constexpr int F_STAGE_BYTES = F_A_BYTES + F_B_BYTES;
@@ -213,6 +215,14 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
                : "memory");
@@ -379,36 +389,64 @@ struct FwdTcParams {
 // MODE >= 0: the output stage is fixed at compile time (bit 0 output noise from the internal
 // generator, bit 1 ADC quantisation, bit 2 clamp; reference rounding, per-tile scalar scales,
 // rounding on, small ADC codes).  MODE < 0: every switch is read at run time.
-template <int RD, int MODE>
+//
+// PAIR: launched as clusters of two CTAs that share one tcgen05.mma.cta_group::2 of 256 x 256
+// per k-step (an MMA that is 256 columns wide runs the tensor cores at their full rate, one of
+// 128 columns does not).  CTA `rank` owns rows [256 mb + 128 rank, +128) of the block: it stages
+// those rows of the inputs and 128 of the block's 256 weight rows, holds its 128 x 256 half of
+// the accumulator and runs the output stage on it.  The two accumulator buffers fill the tensor
+// memory, so the running sum over the analog tiles (bf16x2) lives in shared memory, which leaves
+// five pipeline stages.  Only the packed bf16 output stage exists in this form (the host sends
+// per-channel scales and fp32 rounding to single CTAs).  The leader (rank 0) issues the MMAs;
+// `full` collects both CTAs' copies in the leader, `empty` and `acc_full` are signalled in both
+// CTAs by the leader's multicast commits, `acc_empty` collects both CTAs' epilogue warps in the
+// leader.
+template <int RD, int MODE, bool PAIR>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
               const FwdTcParams p) {
+  constexpr int kStages = PAIR ? FP_STAGES : F_STAGES;
+  constexpr int kBRows = F_BN;                                 // weight rows this CTA stages
+  constexpr int kStageBytes = F_STAGE_BYTES;
+  constexpr int kBlockRows = PAIR ? 2 * BM : BM;               // rows of the outputs per work item
+  constexpr int kBN = PAIR ? 2 * F_BN : F_BN;                  // columns of the outputs per work item
+  constexpr int kSumBytes = PAIR ? FP_SUM_BYTES : 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* stage_base = align_1024(smem_raw);
-  Barriers* bars = reinterpret_cast<Barriers*>(stage_base + F_STAGES * F_STAGE_BYTES);
+  uint8_t* sum_base = stage_base + kStages * kStageBytes;      // PAIR: [128 rows][256 bf16], 16-byte chunks swizzled
+  Barriers* bars = reinterpret_cast<Barriers*>(sum_base + kSumBytes);
   volatile uint32_t* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const FwdEpilogueParams& ep = p.ep;
   const int T = ep.T;
-  const int num_tiles = p.num_mb * p.num_nb;
+  const int num_tiles = p.num_mb * p.num_nb;  // num_mb counts blocks of kBlockRows rows
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int n_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int row_off = (int)rank * BM;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < F_STAGES; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->acc_full[b], 1);
-      mbar_init(&bars->acc_empty[b], F_EPI_WARPS);
+      mbar_init(&bars->acc_empty[b], PAIR ? 2 * F_EPI_WARPS : F_EPI_WARPS);
     }
     mbar_init(&bars->mma_done, 1);
     bars->abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 1) tmem_alloc(&bars->tmem_slot, kTmemCols);
+  if (warp == 1) {
+    if (PAIR) tmem_alloc_pair(&bars->tmem_slot, kTmemCols);
+    else tmem_alloc(&bars->tmem_slot, kTmemCols);
+  }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_slot;
 
@@ -419,45 +457,56 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       tma_prefetch_desc(&map_b);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = worker; tile < num_tiles && ok; tile += n_workers) {
         const int mb = tile / p.num_nb, nb = tile % p.num_nb;
         for (int t = 0; t < T && ok; ++t) {
           for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
-            const int s = it % F_STAGES;
-            const uint32_t ph = (it / F_STAGES) & 1u;
+            const int s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1u;
             if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag)) {
               raise_error(kErrProducer, abort_flag);
               ok = false;
               break;
             }
-            uint8_t* sa = stage_base + s * F_STAGE_BYTES;
-            mbar_expect_tx(&bars->full[s], F_STAGE_BYTES);
-            tma_load_3d(sa, &map_a, &bars->full[s], ks * BK, t, mb * BM);
-            tma_load_3d(sa + F_A_BYTES, &map_b, &bars->full[s], ks * BK, t, nb * F_BN);
+            uint8_t* sa = stage_base + s * kStageBytes;
+            if (PAIR) {
+              // both CTAs' copies complete on the leader's barrier
+              if (leader) mbar_expect_tx(&bars->full[s], 2 * kStageBytes);
+              const uint32_t bar = mapa_u32(smem_u32(&bars->full[s]), 0);
+              tma_load_3d_pair(sa, &map_a, bar, ks * BK, t, mb * kBlockRows + row_off);
+              tma_load_3d_pair(sa + F_A_BYTES, &map_b, bar, ks * BK, t, nb * kBN + (int)rank * kBRows);
+            } else {
+              mbar_expect_tx(&bars->full[s], kStageBytes);
+              tma_load_3d(sa, &map_a, &bars->full[s], ks * BK, t, mb * BM);
+              tma_load_3d(sa + F_A_BYTES, &map_b, &bars->full[s], ks * BK, t, nb * F_BN);
+            }
           }
         }
       }
-      // drain: the last copies issued must have landed before the CTA may exit
-      const uint32_t n_back = it < (uint32_t)F_STAGES ? it : (uint32_t)F_STAGES;
-      for (uint32_t j = it - n_back; j < it; ++j) {
-        const int s = j % F_STAGES;
-        const uint32_t ph = (j / F_STAGES) & 1u;
-        uint64_t t0 = globaltimer_ns();
-        while (!mbar_try(&bars->full[s], ph)) {
-          if (globaltimer_ns() - t0 > kTimeoutNs) {
-            raise_error(kErrDrain, abort_flag);
-            break;
+      // drain: the last copies issued must have landed before the CTA may exit (the leader's
+      // barrier covers its peer's copies; both CTAs meet at the end of the kernel)
+      if (leader) {
+        const uint32_t n_back = it < (uint32_t)kStages ? it : (uint32_t)kStages;
+        for (uint32_t j = it - n_back; j < it; ++j) {
+          const int s = j % kStages;
+          const uint32_t ph = (j / kStages) & 1u;
+          uint64_t t0 = globaltimer_ns();
+          while (!mbar_try(&bars->full[s], ph)) {
+            if (globaltimer_ns() - t0 > kTimeoutNs) {
+              raise_error(kErrDrain, abort_flag);
+              break;
+            }
           }
         }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer --------------------------------------------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, F_BN, 0, 0);
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc(kBlockRows, kBN, 0, 0);
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = worker; tile < num_tiles && ok; tile += n_workers) {
         for (int t = 0; t < T && ok; ++t, ++acc_it) {
           const int b = acc_it & 1u;
           const uint32_t aph = (acc_it >> 1) & 1u;
@@ -467,28 +516,35 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             break;
           }
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + (uint32_t)(b * F_BN);
+          const uint32_t d_tmem = tmem_base + (uint32_t)(b * kBN);
           for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
-            const int s = it % F_STAGES;
-            const uint32_t ph = (it / F_STAGES) & 1u;
+            const int s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1u;
             if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
               raise_error(kErrMma, abort_flag);
               ok = false;
               break;
             }
             tc_fence_after();
-            const uint32_t sa = smem_u32(stage_base + s * F_STAGE_BYTES);
+            const uint32_t sa = smem_u32(stage_base + s * kStageBytes);
             const uint64_t da = desc_k_major(sa), db = desc_k_major(sa + F_A_BYTES);
 #pragma unroll
-            for (int k4 = 0; k4 < BK / 16; ++k4)
-              umma_bf16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (ks | k4) != 0 ? 1u : 0u);
-            umma_commit(&bars->empty[s]);
+            for (int k4 = 0; k4 < BK / 16; ++k4) {
+              if (PAIR) umma_bf16_pair(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (ks | k4) != 0 ? 1u : 0u);
+              else umma_bf16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (ks | k4) != 0 ? 1u : 0u);
+            }
+            if (PAIR) umma_commit_pair(&bars->empty[s], 3);  // frees the stage in both CTAs
+            else umma_commit(&bars->empty[s]);
           }
-          if (ok) umma_commit(&bars->acc_full[b]);
+          if (ok) {
+            if (PAIR) umma_commit_pair(&bars->acc_full[b], 3);
+            else umma_commit(&bars->acc_full[b]);
+          }
         }
       }
       // all MMAs issued by this thread must have retired before TMEM is freed
-      umma_commit(&bars->mma_done);
+      if (PAIR) umma_commit_pair(&bars->mma_done, 1);
+      else umma_commit(&bars->mma_done);
       uint64_t t0 = globaltimer_ns();
       while (!mbar_try(&bars->mma_done, 0)) {
         if (globaltimer_ns() - t0 > kTimeoutNs) {
@@ -499,9 +555,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     }
   } else if (warp >= 4) {
     // ---- epilogue: per-tile output stage, running sum in TMEM ---------------------------
-    // 16 warps: warp & 3 selects the TMEM lane quadrant (rows), (warp - 4) >> 2 the 32 columns.
+    // 16 warps: warp & 3 selects the TMEM lane quadrant (rows), (warp - 4) >> 2 the kCols columns.
+    constexpr int kCols = kBN / 4;
     const int quad = warp & 3;
-    const int col0 = ((warp - 4) >> 2) * 32;
+    const int col0 = ((warp - 4) >> 2) * kCols;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     const int M = ep.M, N = ep.N;
     constexpr bool kFixed = MODE >= 0;
@@ -518,11 +575,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     cfg.out_res = ep.out_res;
     uint32_t acc_it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int tile = worker; tile < num_tiles && ok; tile += n_workers) {
       const int mb = tile / p.num_nb, nb = tile % p.num_nb;
-      const int m = mb * BM + quad * 32 + lane;
+      const int m = mb * kBlockRows + row_off + quad * 32 + lane;
       const bool row_ok = m < M;
-      const int n0 = nb * F_BN + col0;
+      const int n_first = nb * kBN + col0;
       for (int t = 0; t < T && ok; ++t, ++acc_it) {
         const int b = acc_it & 1u;
         const uint32_t aph = (acc_it >> 1) & 1u;
@@ -554,15 +611,32 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const __nv_bfloat162 zero2 = __float2bfloat162_rn(0.0f);
         const uint64_t nstepc2 = f32x2_pack(-stepc, -stepc), rstep2 = f32x2_pack(rstep, rstep);
         const uint64_t magic2 = f32x2_pack(12582912.0f, 12582912.0f), nmagic2 = f32x2_pack(-12582912.0f, -12582912.0f);
+        // this thread's row of the shared-memory running sum (PAIR): chunk c of 8 columns sits at
+        // 16 * (c ^ (row & 7)), so the eight rows a quarter-warp reads hit distinct banks
+        const int srow = quad * 32 + lane;
+        const uint32_t sum_row = smem_u32(sum_base) + (uint32_t)srow * (uint32_t)(kBN * 2);
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < kCols / 16; ++h) {
           const int cc = col0 + h * 16;
-          const int nh = n0 + h * 16;
+          const int nh = n_first + h * 16;
+          const int n0 = n_first + (h >> 1) * 32;  // the 32 columns whose mask word this half belongs to
+          if ((h & 1) == 0) keep_bits = 0;
           uint32_t accr[16], sumr[16];
-          tmem_ld16(tmem_base + lane_base + (uint32_t)(b * F_BN + cc), accr);
+          tmem_ld16(tmem_base + lane_base + (uint32_t)(b * kBN + cc), accr);
           if (t > 0) {
-            if (packed) tmem_ld8(tmem_base + lane_base + (uint32_t)(2 * F_BN + (cc >> 1)), sumr);
-            else tmem_ld16(tmem_base + lane_base + (uint32_t)(2 * F_BN + cc), sumr);
+            if (PAIR) {
+#pragma unroll
+              for (int v = 0; v < 2; ++v) {
+                const uint32_t addr = sum_row + (uint32_t)((((cc >> 3) + v) ^ (srow & 7)) << 4);
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(sumr[4 * v]), "=r"(sumr[4 * v + 1]), "=r"(sumr[4 * v + 2]), "=r"(sumr[4 * v + 3])
+                             : "r"(addr) : "memory");
+              }
+            } else if (packed) {
+              tmem_ld8(tmem_base + lane_base + (uint32_t)(2 * F_BN + (cc >> 1)), sumr);
+            } else {
+              tmem_ld16(tmem_base + lane_base + (uint32_t)(2 * F_BN + cc), sumr);
+            }
           }
           tmem_wait_ld();
           float z[16];
@@ -627,7 +701,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
               sumr[pr] = as_u32(__hadd2_rn(as_bf162(sumr[pr]), o2));
             }
             if (!has_bound) kept = 0xffffffffu;
-            keep_bits |= ((kept | (kept >> 16)) & 0xffffu) << (h * 16);
+            keep_bits |= ((kept | (kept >> 16)) & 0xffffu) << ((h & 1) * 16);
           } else if (!per_channel) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -647,7 +721,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
               float sum = t == 0 ? fadd(0.0f, o) : rnd_alu<RD>(fadd(__uint_as_float(sumr[j]), o));
               if (acc != acc) sum = acc;  // the integer rounding above does not preserve NaN
               sumr[j] = __float_as_uint(sum);
-              keep_bits |= (keep ? 1u : 0u) << (h * 16 + j);
+              keep_bits |= (keep ? 1u : 0u) << ((h & 1) * 16 + j);
             }
           } else {
 #pragma unroll
@@ -659,12 +733,22 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                                                 ep.bound_pc ? cmax : t_max, has_noise ? rnd<RD>(z[j]) : 0.0f,
                                                 cfg, &keep);
               sumr[j] = __float_as_uint(t == 0 ? fadd(0.0f, o) : rnd<RD>(fadd(__uint_as_float(sumr[j]), o)));
-              keep_bits |= (keep ? 1u : 0u) << (h * 16 + j);
+              keep_bits |= (keep ? 1u : 0u) << ((h & 1) * 16 + j);
             }
           }
           if (t < T - 1) {
-            if (packed) tmem_st8(tmem_base + lane_base + (uint32_t)(2 * F_BN + (cc >> 1)), sumr);
-            else tmem_st16(tmem_base + lane_base + (uint32_t)(2 * F_BN + cc), sumr);
+            if (PAIR) {
+#pragma unroll
+              for (int v = 0; v < 2; ++v) {
+                const uint32_t addr = sum_row + (uint32_t)((((cc >> 3) + v) ^ (srow & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(sumr[4 * v]),
+                             "r"(sumr[4 * v + 1]), "r"(sumr[4 * v + 2]), "r"(sumr[4 * v + 3]) : "memory");
+              }
+            } else if (packed) {
+              tmem_st8(tmem_base + lane_base + (uint32_t)(2 * F_BN + (cc >> 1)), sumr);
+            } else {
+              tmem_st16(tmem_base + lane_base + (uint32_t)(2 * F_BN + cc), sumr);
+            }
           } else if (row_ok) {
             // final: bias, convert, store 16 bf16 = 32 bytes of this row
             uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + (int64_t)m * N + nh;
@@ -697,21 +781,30 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
               }
             }
           }
+          if ((h & 1) && ep.keep_mask != nullptr && row_ok && (n0 >> 5) < ep.mask_words)
+            ep.keep_mask[((int64_t)t * ep.mask_words + (n0 >> 5)) * M + m] = keep_bits;  // lanes = consecutive rows
         }
-        if (ep.keep_mask != nullptr && row_ok && (n0 >> 5) < ep.mask_words)
-          ep.keep_mask[((int64_t)t * ep.mask_words + (n0 >> 5)) * M + m] = keep_bits;  // lanes = consecutive rows
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->acc_empty[b]);
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->acc_empty[b]), 0));
+          else mbar_arrive(&bars->acc_empty[b]);
+        }
       }
     }
   }
 
+  // (pairs) nothing of this CTA's shared or tensor memory may go while the peer can still signal
+  // or use it: both CTAs meet before the tensor memory is released
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();
   tc_fence_after();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 1) {
+    if (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1439,6 +1532,7 @@ int sm_count() {
 constexpr int F_SMEM = F_STAGES * F_STAGE_BYTES + (int)sizeof(Barriers) + 1024;
 constexpr int B_SMEM = B_STAGES * B_STAGE_BYTES + (int)sizeof(Barriers) + 1024;
 constexpr int P_SMEM = P_STAGES * P_STAGE_BYTES + (int)sizeof(Barriers) + 1024;
+constexpr int FP_SMEM = FP_STAGES * F_STAGE_BYTES + FP_SUM_BYTES + (int)sizeof(Barriers) + 1024;
 
 template <class Kernel>
 int ensure_smem(Kernel k, int bytes) {
@@ -1473,8 +1567,64 @@ static bool tc_shape_ok(const AlDesc& d, const TileTable& tt) {
 bool tc_forward_supported(const AlDesc& d, const TileTable& tt) { return tc_shape_ok(d, tt); }
 bool tc_backward_supported(const AlDesc& d, const TileTable& tt) { return tc_shape_ok(d, tt); }
 
+using FwdKernel = void (*)(const CUtensorMap, const CUtensorMap, const FwdTcParams);
+template <bool PAIR>
+static FwdKernel pick_fwd_kernel(int mode, int round_dt) {
+  switch (mode) {
+    case 0: return fwd_tc_kernel<kBF16, 0, PAIR>;
+    case 1: return fwd_tc_kernel<kBF16, 1, PAIR>;
+    case 2: return fwd_tc_kernel<kBF16, 2, PAIR>;
+    case 3: return fwd_tc_kernel<kBF16, 3, PAIR>;
+    case 4: return fwd_tc_kernel<kBF16, 4, PAIR>;
+    case 5: return fwd_tc_kernel<kBF16, 5, PAIR>;
+    case 6: return fwd_tc_kernel<kBF16, 6, PAIR>;
+    case 7: return fwd_tc_kernel<kBF16, 7, PAIR>;
+    default:
+      // CTA pairs exist for bf16 rounding only
+      if (PAIR) return fwd_tc_kernel<kBF16, -1, PAIR>;
+      return round_dt == AL_BF16 ? fwd_tc_kernel<kBF16, -1, false> : fwd_tc_kernel<kF32, -1, false>;
+  }
+}
+// launch configuration of a kernel that runs as clusters of two CTAs
+struct PairLaunch {
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr;
+  PairLaunch(int grid, int threads, int smem, cudaStream_t s) {
+    cfg = cudaLaunchConfig_t{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+};
+// how many CTA pairs of the forward kernel the device runs at once (0: it cannot)
+static int max_fwd_pairs(FwdKernel kernel) {
+  static FwdKernel seen[24];
+  static int count[24];
+  static int n_seen = 0;
+  for (int i = 0; i < n_seen; ++i)
+    if (seen[i] == kernel) return count[i];
+  int clusters = 0;
+  PairLaunch pl(2 * sm_count(), kFwdThreads, FP_SMEM, nullptr);
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &pl.cfg) != cudaSuccess) {
+    cudaGetLastError();
+    clusters = 0;
+  }
+  if (n_seen < 24) {
+    seen[n_seen] = kernel;
+    count[n_seen++] = clusters;
+  }
+  return clusters;
+}
+
 int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const TileTable& tt,
-                  const FwdEpilogueParams& ep, void* out, cudaStream_t s) {
+                  const FwdEpilogueParams& ep, int pairing, void* out, cudaStream_t s) {
   ProfScope prof(AL_K_FWD_GEMM, s);
   int w = 0;
   if (!uniform_tiles(tt, &w) || !aligned16(xq) || !aligned16(w_mod) || !aligned16(out)) {
@@ -1499,23 +1649,30 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
   const bool fixed = round_dt == AL_BF16 && !per_channel && ep.out_noise == nullptr && !ep.no_rounding &&
                      p.small_adc_codes;
   const int mode = fixed ? ((ep.has_noise ? 1 : 0) | (ep.has_adc ? 2 : 0) | (ep.has_bound ? 4 : 0)) : -1;
+  // CTA pairs (256 x 256 blocks, packed bf16 output stage only) when there is a block per pair
+  // of SMs; single CTAs (128 x 128) otherwise.
   // The runtime calls below also bind the device's primary context to the calling thread
   // (autograd runs backward on its own threads); the driver entry point that encodes the
   // tensor maps needs a current context.
-  void (*kernel)(const CUtensorMap, const CUtensorMap, const FwdTcParams) = nullptr;
-  switch (mode) {
-    case 0: kernel = fwd_tc_kernel<kBF16, 0>; break;
-    case 1: kernel = fwd_tc_kernel<kBF16, 1>; break;
-    case 2: kernel = fwd_tc_kernel<kBF16, 2>; break;
-    case 3: kernel = fwd_tc_kernel<kBF16, 3>; break;
-    case 4: kernel = fwd_tc_kernel<kBF16, 4>; break;
-    case 5: kernel = fwd_tc_kernel<kBF16, 5>; break;
-    case 6: kernel = fwd_tc_kernel<kBF16, 6>; break;
-    case 7: kernel = fwd_tc_kernel<kBF16, 7>; break;
-    default: kernel = round_dt == AL_BF16 ? fwd_tc_kernel<kBF16, -1> : fwd_tc_kernel<kF32, -1>; break;
+  const bool pair_ok = pairing >= 0 && round_dt == AL_BF16 && !per_channel;
+  const int pair_tiles = ((ep.M + 2 * BM - 1) / (2 * BM)) * ((ep.N + 2 * F_BN - 1) / (2 * F_BN));
+  FwdKernel kernel = nullptr;
+  int rc = AL_OK, pairs = 0;
+  if (pair_ok) {
+    kernel = pick_fwd_kernel<true>(mode, round_dt);
+    rc = ensure_smem(kernel, FP_SMEM);
+    if (rc) return rc;
+    pairs = max_fwd_pairs(kernel);
   }
-  int rc = ensure_smem(kernel, F_SMEM);
-  if (rc) return rc;
+  const bool pair = pairs > 0 && (pair_tiles >= pairs || pairing > 0);
+  if (!pair) {
+    kernel = pick_fwd_kernel<false>(mode, round_dt);
+    rc = ensure_smem(kernel, F_SMEM);
+    if (rc) return rc;
+  } else {
+    p.num_mb = (ep.M + 2 * BM - 1) / (2 * BM);
+    p.num_nb = (ep.N + 2 * F_BN - 1) / (2 * F_BN);
+  }
   CUtensorMap map_a, map_b;
   {
     uint64_t dims[3] = {(uint64_t)w, (uint64_t)tt.T, (uint64_t)ep.M};
@@ -1530,6 +1687,15 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
     uint32_t box[3] = {BK, 1, F_BN};
     rc = make_map(&map_b, w_mod, 3, dims, strides, box);
     if (rc) return rc;
+  }
+  if (pair) {
+    PairLaunch pl(2 * (pair_tiles < pairs ? pair_tiles : pairs), kFwdThreads, FP_SMEM, s);
+    cudaError_t e = cudaLaunchKernelEx(&pl.cfg, kernel, map_a, map_b, p);
+    if (e != cudaSuccess) {
+      set_error("fwd_tc (pairs): %s", cudaGetErrorString(e));
+      return AL_ERR_CUDA;
+    }
+    return check_launch("fwd_tc_pair");
   }
   int tiles = p.num_mb * p.num_nb;
   int grid = tiles < sm_count() ? tiles : sm_count();
