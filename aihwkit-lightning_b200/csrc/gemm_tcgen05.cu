@@ -56,7 +56,7 @@ constexpr int B_STAGE_BYTES = B_A_BYTES + B_B_BYTES;
 constexpr int B_BOX_BYTES = 64 * BK * 2;   // one 64x64 MN-major box: 8 KiB
 constexpr int B_EPI_WARPS = 4;
 constexpr int B_XFORM_THREADS = 128;   // per group; each group handles one stage at a time
-constexpr int B_XFORM_GROUPS = 2;
+constexpr int B_XFORM_GROUPS = 4;
 constexpr int kBwdThreads = (8 + 4 * B_XFORM_GROUPS) * 32;
 
 // backward kernel on CTA pairs: a 256 x 256 tile per pair, each CTA stages its 128 rows of A and
