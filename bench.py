@@ -38,7 +38,7 @@ M, K, N, MAX_IN = 8192, 4096, 4096, 512
 CPU_SAMPLE_ROWS = 1024
 FLOP_PER_STEP = 6.0 * M * K * N
 L2_FLUSH_BYTES = 256 << 20
-FWD_KERNEL_DRAM_BYTES = 101.7e6 + 77.3e6
+FWD_KERNEL_DRAM_BYTES = 120.1e6 + 76.4e6
 
 
 def make_rpu_config(ns):
