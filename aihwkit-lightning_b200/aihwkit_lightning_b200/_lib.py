@@ -38,7 +38,7 @@ class AlForwardArgs(Structure):
     _fields_ = [
         ("x", c_void_p), ("w", c_void_p), ("bias", c_void_p),
         ("input_range", c_void_p), ("input_range_update_idx", c_void_p),
-        ("x_min", c_void_p), ("x_max", c_void_p),
+        ("x_min", c_void_p), ("x_max", c_void_p), ("learnable_weight_clip", c_void_p),
         ("tile_ends", POINTER(c_int32)),
         ("out", c_void_p), ("xq", c_void_p), ("ir_rows", c_void_p), ("w_amax", c_void_p),
         ("w_tile_max", c_void_p), ("w_mod", c_void_p), ("keep_mask", c_void_p),
@@ -53,6 +53,7 @@ class AlBackwardArgs(Structure):
         ("ir_rows", c_void_p), ("keep_mask", c_void_p), ("tile_ends", POINTER(c_int32)),
         ("grad_x", c_void_p), ("grad_w", c_void_p), ("grad_bias", c_void_p),
         ("grad_input_range", c_void_p), ("reduce_scratch", c_void_p),
+        ("w", c_void_p), ("learnable_weight_clip", c_void_p), ("grad_weight_clip", c_void_p),
     ]
 
 

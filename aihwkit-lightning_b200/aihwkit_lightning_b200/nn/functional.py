@@ -126,7 +126,7 @@ class AnalogLinearFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, inp, weight, bias, input_range, input_range_update_idx, in_sizes, training,
-                rpu_config, x_min=None, x_max=None):  # type: ignore[override]
+                rpu_config, x_min=None, x_max=None, learnable_weight_clip=None):  # type: ignore[override]
         lib = _lib.load()
         if not inp.is_cuda or not weight.is_cuda:
             raise ValueError(
@@ -143,7 +143,7 @@ class AnalogLinearFunction(torch.autograd.Function):
         w = weight.contiguous()
         t = len(in_sizes)
         dev, dtype = inp.device, inp.dtype
-        needs_grad = any(ctx.needs_input_grad[:4])
+        needs_grad = any(ctx.needs_input_grad[:4]) or ctx.needs_input_grad[10]
         desc = make_desc(rpu_config, m, k, n, t, dtype, training)
         desc.save_for_backward = int(needs_grad)
         ends = _lib.tile_ends_array(in_sizes)
@@ -178,7 +178,14 @@ class AnalogLinearFunction(torch.autograd.Function):
             w_amax = torch.empty(t, n, device=dev, dtype=dtype)
             w_tile_max = torch.empty(2 * t, device=dev, dtype=torch.float32)
             args.w_amax, args.w_tile_max = _ptr(w_amax), _ptr(w_tile_max)
-            modifies = desc.quant_type != 0 or (training and desc.noise_type != 0)
+            learn_clip = desc.clip_type == _CLIP[WeightClipType.LEARNABLE_PER_CHANNEL]
+            lwc = None
+            if learn_clip:
+                assert learnable_weight_clip is not None, "learnable_weight_clip should not be None"
+                assert tuple(learnable_weight_clip.shape) == (t, n), f"learnable_weight_clip.shape must be ({t}, {n})"
+                lwc = learnable_weight_clip.detach().to(dtype).contiguous()
+                args.learnable_weight_clip = _ptr(lwc)
+            modifies = desc.quant_type != 0 or (training and desc.noise_type != 0) or learn_clip
             w_mod = torch.empty_like(w) if modifies else w
             args.w_mod = _ptr(w_mod)
             keep_mask = None
@@ -217,16 +224,18 @@ class AnalogLinearFunction(torch.autograd.Function):
         ctx.shape = tuple(inp.shape)
         ctx.has_bias = bias is not None
         ctx.ir_needs_grad = static and input_range is not None and input_range.requires_grad
+        ctx.learn_clip = learn_clip
         if needs_grad:
-            ctx.save_for_backward(x2d if static else None, xq, w_mod, ir_rows, keep_mask)
+            ctx.save_for_backward(x2d if static else None, xq, w_mod, ir_rows, keep_mask,
+                                  w if learn_clip else None, lwc)
         return out.view(*inp.shape[:-1], n)
 
     @staticmethod
     def backward(ctx, grad_out):  # type: ignore[override]
         if ctx.empty:
-            return (None,) * 10
+            return (None,) * 11
         lib = _lib.load()
-        x2d, xq, w_mod, ir_rows, keep_mask = ctx.saved_tensors
+        x2d, xq, w_mod, ir_rows, keep_mask, w_saved, lwc = ctx.saved_tensors
         desc = ctx.desc
         m, k, n, t = desc.M, desc.K, desc.N, desc.T
         dev, dtype = grad_out.device, xq.dtype
@@ -234,6 +243,8 @@ class AnalogLinearFunction(torch.autograd.Function):
         need_x, need_w, need_b, need_ir = ctx.needs_input_grad[:4]
         need_b = need_b and ctx.has_bias
         need_ir = need_ir and ctx.ir_needs_grad
+        need_clip = ctx.learn_clip and (ctx.needs_input_grad[10] or need_w)
+        need_w = need_w or need_clip
         with torch.cuda.device(dev):
             args = _lib.AlBackwardArgs()
             ends = _lib.tile_ends_array(ctx.in_sizes)
@@ -247,18 +258,28 @@ class AnalogLinearFunction(torch.autograd.Function):
             scratch = torch.empty(lib.al_backward_scratch_floats(m, k, n, t), device=dev, dtype=torch.float32)
             args.grad_x, args.grad_w, args.grad_bias = _ptr(grad_x), _ptr(grad_w), _ptr(grad_b)
             args.grad_input_range, args.reduce_scratch = _ptr(grad_ir), _ptr(scratch)
+            grad_clip = None
+            if need_clip:
+                grad_clip = torch.empty(t, n, device=dev, dtype=dtype)
+                args.w, args.learnable_weight_clip = _ptr(w_saved), _ptr(lwc)
+                args.grad_weight_clip = _ptr(grad_clip)
             _lib.check(lib.al_backward(desc, args, _stream(dev)))
         if grad_x is not None:
             grad_x = grad_x.view(ctx.shape) if need_x else None
-        return grad_x, grad_w, grad_b, grad_ir, None, None, None, None, None, None
+        if not ctx.needs_input_grad[1]:
+            grad_w = None
+        if not ctx.needs_input_grad[10]:
+            grad_clip = None
+        return grad_x, grad_w, grad_b, grad_ir, None, None, None, None, None, None, grad_clip
 
 
 def analog_linear(inp: Tensor, weight: Tensor, bias: Optional[Tensor], input_range: Optional[Tensor],
                   input_range_update_idx: Optional[Tensor], in_sizes: List[int], training: bool,
-                  rpu_config, x_min: Optional[Tensor] = None, x_max: Optional[Tensor] = None) -> Tensor:
+                  rpu_config, x_min: Optional[Tensor] = None, x_max: Optional[Tensor] = None,
+                  learnable_weight_clip: Optional[Tensor] = None) -> Tensor:
     """Functional form used by ``AnalogLinear`` and ``AnalogConv2d``."""
     return AnalogLinearFunction.apply(inp, weight, bias, input_range, input_range_update_idx,
-                                      in_sizes, training, rpu_config, x_min, x_max)
+                                      in_sizes, training, rpu_config, x_min, x_max, learnable_weight_clip)
 
 
 def sliced_abs_max(in_sizes: List[int], weights: Tensor) -> Tensor:

@@ -80,9 +80,8 @@ class _AnalogConvNd(AnalogLayerBase, _ConvNd):
 
     @torch.no_grad()
     def quantize_weights(self) -> None:
-        if self.rpu_config.modifier.quantization_type != WeightQuantizationType.NONE:
-            if self.rpu_config.clip.type == WeightClipType.LEARNABLE_PER_CHANNEL:
-                raise NotImplementedError("learnable weight clipping is not implemented")
+        if (self.rpu_config.modifier.quantization_type != WeightQuantizationType.NONE
+                or self.rpu_config.clip.type == WeightClipType.LEARNABLE_PER_CHANNEL):
             w2d = self.weight.data.reshape(self.out_channels, -1).contiguous()
             self.weight.data = _modified_weights(self, w2d).view_as(self.weight)
         AnalogLayerBase.quantize_weights(self)
@@ -94,7 +93,8 @@ class _AnalogConvNd(AnalogLayerBase, _ConvNd):
         patches = F.unfold2d(inp, self.kernel_size, self.dilation, self.padding, self.stride)
         out = F.analog_linear(patches, self.weight.view(self.out_channels, -1), self.bias,
                               self.input_range, self.input_range_update_idx, self.in_sizes,
-                              self.training, self.rpu_config, self.x_min, self.x_max)
+                              self.training, self.rpu_config, self.x_min, self.x_max,
+                              self.learnable_weight_clip)
         out = out.transpose(-1, -2).contiguous()
         out_size = (im_shape[-2] + 2 * self.padding[0] - self.dilation[0] * (self.kernel_size[0] - 1) - 1
                     ) // self.stride[0] + 1

@@ -46,7 +46,7 @@ class AnalogLinear(Linear, AnalogLayerBase):
         self._check_forward_config()
         return F.analog_linear(inp, self.weight, self.bias, self.input_range,
                                self.input_range_update_idx, self.in_sizes, self.training,
-                               self.rpu_config, self.x_min, self.x_max)
+                               self.rpu_config, self.x_min, self.x_max, self.learnable_weight_clip)
 
     @classmethod
     def from_digital(cls, module: Linear, rpu_config: TorchInferenceRPUConfig) -> "AnalogLinear":
@@ -91,9 +91,8 @@ class AnalogLinear(Linear, AnalogLayerBase):
     @torch.no_grad()
     def quantize_weights(self) -> None:
         """Bake the configured weight discretisation into ``weight`` and switch it off."""
-        if self.rpu_config.modifier.quantization_type != WeightQuantizationType.NONE:
-            if self.rpu_config.clip.type == WeightClipType.LEARNABLE_PER_CHANNEL:
-                raise NotImplementedError("learnable weight clipping is not implemented")
+        if (self.rpu_config.modifier.quantization_type != WeightQuantizationType.NONE
+                or self.rpu_config.clip.type == WeightClipType.LEARNABLE_PER_CHANNEL):
             self.weight.data = _modified_weights(self, self.weight.data)
         AnalogLayerBase.quantize_weights(self)
 
@@ -118,8 +117,12 @@ def _modified_weights(layer, weight2d: Tensor) -> Tensor:
     cfg.modifier.quantization_type = layer.rpu_config.modifier.quantization_type
     cfg.modifier.res = layer.rpu_config.modifier.res
     cfg.mapping.max_input_size = layer.rpu_config.mapping.max_input_size
+    lwc = None
+    if layer.rpu_config.clip.type == WeightClipType.LEARNABLE_PER_CHANNEL:
+        cfg.clip.type = WeightClipType.LEARNABLE_PER_CHANNEL
+        lwc = layer.learnable_weight_clip
     capture: dict = {}
     probe = torch.zeros(1, weight2d.shape[1], device=weight2d.device, dtype=weight2d.dtype)
     with F.operator_settings(capture=capture):
-        F.analog_linear(probe, weight2d, None, None, None, layer.in_sizes, False, cfg)
+        F.analog_linear(probe, weight2d, None, None, None, layer.in_sizes, False, cfg, None, None, lwc)
     return capture["w_mod"].clone()

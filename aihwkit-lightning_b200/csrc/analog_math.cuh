@@ -279,6 +279,26 @@ AL_HD WeightSeg weight_prepare(int quant_type, float q_scale, float n_states, fl
   s.amp = rnd<DT>(fmul(std_dev, n_scale));
   return s;
 }
+// LEARNABLE_PER_CHANNEL clipping without discretisation (`quant_utils.py:190-197`): the quantiser
+// is entered with res = the learned range as a tensor, bound = 0.5 (alpha = 1), max state 1 and
+// no rounding, i.e. w / range, clamp to +-1, times range -- with the same `(res > 1).all()`
+// switch and zero guard as the discretiser.
+template <int DT>
+AL_HD WeightSeg weight_prepare_learn_clamp(float clip, bool all_gt1, int noise_type, float std_dev,
+                                           float n_scale) {
+  WeightSeg s;
+  s.quant = 1;
+  s.noise = noise_type != 0;
+  s.no_rounding = 1;
+  float res = all_gt1 ? rnd<DT>(fdiv(1.0f, clip)) : clip;
+  if (res == 0.0f) res = 1.0f;
+  s.res = res;
+  s.resc = s.res < kTiny ? kTiny : s.res;
+  s.rres = frcp(s.resc);
+  s.max_state = 1.0f;
+  s.amp = rnd<DT>(fmul(std_dev, n_scale));
+  return s;
+}
 // Same value as discretize<DT> followed by add_weight_noise<DT> for non-NaN weights.
 template <int DT>
 AL_HD float weight_apply(const WeightSeg& s, float w, float xi) {

@@ -78,9 +78,10 @@ static int derive(const AlDesc& d, Derived* o) {
     set_error("unknown input-range mode %d", d.ir_mode);
     return AL_ERR_BAD_ARGUMENT;
   }
-  if (d.clip_type == AL_CLIP_LEARNABLE_PER_CHANNEL) {
-    set_error("learnable per-channel weight clipping is not implemented");
-    return AL_ERR_UNSUPPORTED;
+  if (d.clip_type == AL_CLIP_LEARNABLE_PER_CHANNEL && d.quant_type != AL_QUANT_NONE &&
+      d.quant_type != AL_QUANT_DISCRETIZE_PER_CHANNEL) {
+    set_error("You can't learn weight ranges per column but quantize per tensor");
+    return AL_ERR_BAD_ARGUMENT;
   }
   o->has_dac = d.inp_res > 0;
   if (o->has_dac && d.ir_mode == AL_IR_OFF) {
@@ -132,6 +133,7 @@ static bool needs_wmax(const Derived& dv) {
   return dv.has_adc || dv.has_bound || dv.has_noise || dv.weight_noise != AL_NOISE_NONE ||
          dv.weight_quant != AL_QUANT_NONE;
 }
+static size_t elem_size(int dtype) { return dtype == AL_BF16 ? 2 : 4; }
 
 static bool pick_tc(const AlDesc& d, const TileTable& tt, bool backward) {
   if (d.engine == AL_ENGINE_SIMT) return false;
@@ -281,7 +283,32 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
   // 3. weight statistics and modifier
   const void* w_mod = a->w;
   float* tile_max = nullptr;
-  if (needs_wmax(dv)) {
+  const bool learn_clip = d.clip_type == AL_CLIP_LEARNABLE_PER_CHANNEL;
+  if (learn_clip) {
+    // `quant_utils.py:184-233`, `torch_linear.py:236-246`: the weights are clamped to (or
+    // discretised on the scale of) the learned ranges, which then stand in for the per-channel
+    // abs-max everywhere downstream
+    if (!a->learnable_weight_clip || !a->w_amax || !a->w_tile_max || !a->w_mod || a->w_mod == a->w) {
+      set_error("al_forward: learnable_weight_clip, w_amax, w_tile_max and a separate w_mod are needed");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    cudaError_t e = cudaMemcpyAsync(a->w_amax, a->learnable_weight_clip, elem_size(d.dtype) * d.T * d.N,
+                                    cudaMemcpyDeviceToDevice, s);
+    if (e != cudaSuccess) {
+      set_error("al_forward: copying the learned weight ranges: %s", cudaGetErrorString(e));
+      return AL_ERR_CUDA;
+    }
+    tile_max = (float*)a->w_tile_max;
+    int32_t* flags = (int32_t*)(tile_max + d.T);
+    const int quant = dv.weight_quant == AL_QUANT_NONE ? kQuantLearnClamp : dv.weight_quant;
+    rc = launch_tile_max(d.dtype, a->w_amax, d.N, tt, quant, dv.n_states, tile_max, flags, s);
+    if (rc) return rc;
+    rc = launch_weight_modify(d.dtype, a->w, d.N, d.K, tt, a->w_amax, tile_max, flags, quant, dv.n_states,
+                              dv.max_state, dv.weight_noise, dv.std_dev, a->w_noise, a->seed, a->offset,
+                              d.no_rounding, a->w_mod, s);
+    if (rc) return rc;
+    w_mod = a->w_mod;
+  } else if (needs_wmax(dv)) {
     if (!a->w_amax || !a->w_tile_max) {
       set_error("al_forward: w_amax / w_tile_max workspace missing");
       return AL_ERR_BAD_ARGUMENT;
@@ -345,7 +372,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
 
 int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T) {
   (void)K;
-  return 256 * (int64_t)N + 3 * (int64_t)T * M + 16;
+  return 256 * (int64_t)N + 3 * (int64_t)T * M + 16 + 2 * (int64_t)T + 16;
 }
 
 int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
@@ -412,6 +439,24 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
     }
     rc = tc ? launch_wgrad_tc(a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt, pairing, a->grad_w, s)
             : launch_wgrad_simt(d.dtype, a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt, a->grad_w, s);
+    if (rc) return rc;
+  }
+  if (d.clip_type == AL_CLIP_LEARNABLE_PER_CHANNEL && (a->grad_w || a->grad_weight_clip)) {
+    // `quant_utils.py:125-151`: straight-through inside the learned range, range gradient outside
+    if (!a->grad_w || !a->grad_weight_clip || !a->w || !a->learnable_weight_clip || !a->reduce_scratch) {
+      set_error("al_backward: learnable weight ranges need grad_w, grad_weight_clip, w, learnable_weight_clip "
+                "and reduce_scratch");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    float* tile_max = a->reduce_scratch + 256 * (int64_t)d.N + 3 * (int64_t)d.T * d.M + 16;
+    int32_t* flags = (int32_t*)(tile_max + d.T);
+    const int discretize = dv.weight_quant == AL_QUANT_DISCRETIZE_PER_CHANNEL;
+    rc = launch_tile_max(d.dtype, a->learnable_weight_clip, d.N, tt, discretize ? dv.weight_quant : kQuantLearnClamp,
+                         dv.n_states, tile_max, flags, s);
+    if (rc) return rc;
+    const double n_states_d = d.mod_res > 0 ? (d.mod_res > 1.0 / d.mod_res ? d.mod_res : 1.0 / d.mod_res) : 1.0;
+    rc = launch_learn_clip_backward(d.dtype, a->w, a->learnable_weight_clip, flags, d.N, d.K, tt, discretize,
+                                    dv.n_states, n_states_d / 2.0, d.no_rounding, a->grad_w, a->grad_weight_clip, s);
     if (rc) return rc;
   }
   if (a->grad_bias) {

@@ -127,7 +127,78 @@ __global__ void static_ir_final_kernel(const float* __restrict__ partial,
   }
 }
 
+// Backward of the learned per-channel weight range (`quant_utils.py:125-151`, learn_res branch).
+// One warp per (channel, tile) segment.  grad_w arrives as the gradient of the clipped /
+// discretised weights and leaves as the gradient of the weights themselves (zero outside the
+// range); grad_clip[t, n] is the fp32 row sum of (-Q | +Q | round(q) - q) * grad_w * grad_scale
+// (below, above, inside the range), rounded to the layer dtype, and divided by n_states when the
+// range entered the quantiser as range / n_states.  The reference builds its indicator tensors in
+// fp32, so products and the row sum are fp32; the order of the row sum is this warp's.
+template <int DT>
+__global__ void __launch_bounds__(256)
+learn_clip_backward_kernel(const void* __restrict__ w, const void* __restrict__ clip,
+                           const int32_t* __restrict__ all_gt1, int N, int K, TileTable tt, int discretize,
+                           float n_states, double max_state_d, int no_rounding,
+                           void* __restrict__ grad_w, void* __restrict__ grad_clip) {
+  const unsigned seg = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (seg >= (unsigned)N * (unsigned)tt.T) return;
+  const int n = (int)(seg / (unsigned)tt.T), t = (int)(seg - (unsigned)n * (unsigned)tt.T);
+  const int lo = tt.lo(t), len = tt.hi(t) - lo;
+  const int64_t start = (int64_t)n * K + lo;
+  const float c = Elem<DT>::load(clip, (int64_t)t * N + n);
+  float res;
+  if (discretize) {
+    const float arg = rnd<DT>(fdiv(c, n_states));
+    res = all_gt1[t] ? rnd<DT>(fdiv(2.0f, arg)) : rnd<DT>(fmul(2.0f, arg));
+  } else {
+    res = all_gt1[t] ? rnd<DT>(fdiv(1.0f, c)) : c;
+  }
+  if (res == 0.0f) res = 1.0f;
+  const float resc = res < kTiny ? kTiny : res;
+  const float q_max = discretize ? (float)max_state_d : 1.0f;  // as a Python float in the products
+  const float q_cmp = rnd<DT>(q_max);                  // as the layer dtype in the comparisons
+  const bool skip = !discretize || no_rounding != 0;
+  // 1 / sqrt(numel) without rounding, 2 * sqrt(max_state / numel) with it, evaluated in double
+  // like the Python expression and then used as an fp32 scalar (`quant_utils.py:103-106`)
+  const double numel = (double)N * (double)len;
+  const float grad_scale = (float)(skip ? 1.0 / sqrt(numel) : 2.0 * sqrt(max_state_d / numel));
+  float acc = 0.0f;
+  for (int i = lane; i < len; i += 32) {
+    const float wv = Elem<DT>::load(w, start + i);
+    const float g = Elem<DT>::load(grad_w, start + i);
+    const float q = rnd<DT>(fdiv(wv, resc));
+    const bool small = q < -q_cmp, big = q > q_cmp;
+    float a;
+    if (small) a = -q_max;
+    else if (big) a = q_max;
+    else a = skip ? 0.0f : rnd<DT>(fadd(-q, rnd<DT>(frint(q))));
+    acc = fadd(acc, fmul(fmul(a, g), grad_scale));
+    if (small || big) Elem<DT>::store(grad_w, start + i, 0.0f);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc = fadd(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+  if (lane == 0) {
+    float r = rnd<DT>(acc);
+    if (discretize) r = rnd<DT>(fdiv(r, n_states));
+    Elem<DT>::store(grad_clip, (int64_t)t * N + n, r);
+  }
+}
+
 }  // namespace
+
+int launch_learn_clip_backward(int dtype, const void* w, const void* clip, const int32_t* all_gt1, int N,
+                               int K, const TileTable& tt, int discretize, float n_states, double max_state,
+                               int no_rounding, void* grad_w, void* grad_clip, cudaStream_t s) {
+  ProfScope prof(AL_K_CLIP, s);
+  int64_t segs = (int64_t)N * tt.T;
+  unsigned blocks = (unsigned)((segs + 7) / 8);
+  if (dtype == AL_F32)
+    learn_clip_backward_kernel<kF32><<<blocks, 256, 0, s>>>(w, clip, all_gt1, N, K, tt, discretize, n_states, max_state, no_rounding, grad_w, grad_clip);
+  else
+    learn_clip_backward_kernel<kBF16><<<blocks, 256, 0, s>>>(w, clip, all_gt1, N, K, tt, discretize, n_states, max_state, no_rounding, grad_w, grad_clip);
+  return check_launch("learn_clip_backward");
+}
 
 int launch_bias_grad(int dtype, const void* g, int M, int N, void* grad_bias, float* scratch,
                      cudaStream_t s) {

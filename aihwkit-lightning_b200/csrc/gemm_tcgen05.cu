@@ -1085,18 +1085,22 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       const int s = it % B_STAGES;
       const uint32_t ph = ((uint32_t)it / B_STAGES) & 1u;
       uint64_t zeros = ~((uint64_t)lo | ((uint64_t)hi << 32));
+      // A parity wait tells phases apart only one phase deep, and a warp that had nothing to
+      // zero on the stage's previous use never looked at `full` then: first wait until that
+      // previous use has been consumed (normally long past), which puts `full` and `ready`
+      // of this stage in the phase of this use.
+      bool okw = true;
+      if (lane == 0) {
+        okw = mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag);
+        if (!okw) raise_error(kErrTransform, abort_flag);
+      }
+      if (!__shfl_sync(0xffffffffu, okw, 0)) return false;
       if (!__any_sync(0xffffffffu, zeros != 0ull)) {
-        // Nothing to zero in this warp's rows.  The warp's arrival must still land in the
-        // right phase of `ready`, so it waits for the stage's previous use to be consumed --
-        // long before the copy lands, which takes this hand-off off the TMA -> MMA critical
-        // path -- and it publishes no data, so the arrival is a relaxed one.
-        bool okw = true;
-        if (lane == 0) {
-          okw = mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag);
-          if (okw) mbar_arrive_relaxed(&bars->ready[s]);
-          else raise_error(kErrTransform, abort_flag);
-        }
-        return __shfl_sync(0xffffffffu, okw, 0);
+        // Nothing to zero in this warp's rows: it vouches for the stage before the copy has
+        // landed, which takes this hand-off off the TMA -> MMA critical path, and it
+        // publishes no data, so the arrival is a relaxed one.
+        if (lane == 0) mbar_arrive_relaxed(&bars->ready[s]);
+        return true;
       }
       if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
         raise_error(kErrTransform, abort_flag);

@@ -46,6 +46,10 @@ struct FwdEpilogueParams {
   uint64_t seed, offset;
 };
 
+// Internal weight-quantiser mode next to AlQuantType: the learned per-channel range used as a
+// clamp only (LEARNABLE_PER_CHANNEL clipping without discretisation, `quant_utils.py:184-201`).
+constexpr int kQuantLearnClamp = 100;
+
 void set_error(const char* fmt, ...);
 
 // Launch accounting: every launch_* function opens one scope.  Launch counts are always kept;
@@ -109,6 +113,11 @@ int launch_wgrad_simt(int dtype, const void* g, const void* xq, const uint32_t* 
 // ---- backward element-wise parts (backward_kernels.cu) ------------------------------------
 int launch_bias_grad(int dtype, const void* g, int M, int N, void* grad_bias, float* scratch,
                      cudaStream_t s);
+// learned per-channel weight ranges: grad_w -> gradient of the unclipped weights (in place),
+// grad_clip [T,N]; all_gt1 = the per-tile flags launch_tile_max wrote for the ranges
+int launch_learn_clip_backward(int dtype, const void* w, const void* clip, const int32_t* all_gt1, int N,
+                               int K, const TileTable& tt, int discretize, float n_states, double max_state,
+                               int no_rounding, void* grad_w, void* grad_clip, cudaStream_t s);
 int launch_static_ir_backward(int dtype, const void* x, const void* ir_used, void* grad_x, int M,
                               int K, const TileTable& tt, float decay, float input_min_percentage,
                               void* grad_ir, float* scratch, int fast_mode, cudaStream_t s);

@@ -195,10 +195,12 @@ weight_modify_kernel(const void* __restrict__ w, int N, int K, TileTable tt,
   int64_t start = (int64_t)n * K + lo;
   float row_max = Elem<DT>::load(w_amax, (int64_t)t * N + n);
   float t_max = rnd<DT>(tile_max[t]);
-  const WeightSeg ws = weight_prepare<DT>(
-      quant_type, quant_type == AL_QUANT_DISCRETIZE ? t_max : row_max, n_states, max_state,
-      flags[t] != 0, noise_type, std_dev, noise_type == AL_NOISE_ADD_NORMAL ? t_max : row_max,
-      no_rounding != 0);
+  const float n_scale = noise_type == AL_NOISE_ADD_NORMAL ? t_max : row_max;
+  const WeightSeg ws =
+      quant_type == kQuantLearnClamp
+          ? weight_prepare_learn_clamp<DT>(row_max, flags[t] != 0, noise_type, std_dev, n_scale)
+          : weight_prepare<DT>(quant_type, quant_type == AL_QUANT_DISCRETIZE ? t_max : row_max, n_states,
+                               max_state, flags[t] != 0, noise_type, std_dev, n_scale, no_rounding != 0);
   const SegPlan p = plan_segment<DT>(start, len, aligned_base != 0);
   auto one = [&](int i) {
     float xi = 0.0f;

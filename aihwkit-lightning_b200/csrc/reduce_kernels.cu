@@ -105,6 +105,7 @@ __global__ void tile_max_kernel(const void* __restrict__ amax, int rows, int qua
     float v = Elem<DT>::load(amax, (int64_t)t * rows + r);
     m = fmaxf(m, v);
     if (quant_type == AL_QUANT_DISCRETIZE_PER_CHANNEL) all &= discretize_scale_gt1<DT>(v, n_states) ? 1 : 0;
+    if (quant_type == kQuantLearnClamp) all &= v > 1.0f ? 1 : 0;
   }
   s_max[threadIdx.x] = m;
   s_all[threadIdx.x] = all;
@@ -120,7 +121,7 @@ __global__ void tile_max_kernel(const void* __restrict__ amax, int rows, int qua
     tile_max[t] = s_max[0];
     int f = 0;
     if (quant_type == AL_QUANT_DISCRETIZE) f = discretize_scale_gt1<DT>(s_max[0], n_states) ? 1 : 0;
-    if (quant_type == AL_QUANT_DISCRETIZE_PER_CHANNEL) f = s_all[0];
+    if (quant_type == AL_QUANT_DISCRETIZE_PER_CHANNEL || quant_type == kQuantLearnClamp) f = s_all[0];
     flags[t] = f;
   }
 }

@@ -106,6 +106,8 @@ typedef struct AlForwardArgs {
   void* input_range_update_idx; /* [T] dtype, static mode                                   */
   void* x_min;               /* [T] dtype, fast mode: running minimum (updated)             */
   void* x_max;               /* [T] dtype, fast mode: running maximum (updated)             */
+  const void* learnable_weight_clip; /* [T,N] dtype, clip type LEARNABLE_PER_CHANNEL: the learned
+                                 per-tile per-channel weight ranges; null otherwise        */
   const int32_t* tile_ends;  /* HOST pointer, [T] cumulative tile ends (last == K)         */
   void* out;                 /* [M,N] dtype                                                 */
   /* saved for backward / intermediates (caller-allocated workspace) */
@@ -143,6 +145,11 @@ typedef struct AlBackwardArgs {
   void* grad_bias;           /* [N] dtype, nullable                                         */
   void* grad_input_range;    /* [T] dtype, nullable (static mode, learn_input_range)       */
   float* reduce_scratch;     /* >= al_backward_scratch_floats(M,K,N,T) floats               */
+  /* clip type LEARNABLE_PER_CHANNEL (`quant_utils.py:125-151`): grad_w becomes the gradient of
+   * the unclipped weights and grad_weight_clip that of the learned ranges; null otherwise */
+  const void* w;             /* [N,K] dtype weights of the forward                          */
+  const void* learnable_weight_clip; /* [T,N] dtype                                         */
+  void* grad_weight_clip;    /* [T,N] dtype                                                 */
 } AlBackwardArgs;
 
 /* Per-tile, per-row abs-max: out[t, r] = max_k |a[r, k]|, k in tile t.  a is [rows, K] dtype,

@@ -115,6 +115,25 @@ def discretize_weight(w_t: Tensor, scale: Tensor, mod_res: float, no_rounding: b
     return out
 
 
+def learnable_quantize(w_t: Tensor, res_arg: Tensor, bound: float, max_state: float, skip_rounding: bool):
+    """``UniformQuantize.forward`` with ``learn_res=True`` (`quant_utils.py:63-109`) as
+    `clip_and_quantize` enters it for LEARNABLE_PER_CHANNEL clipping (`quant_utils.py:184-233`):
+    ``res_arg`` is the ``[N,1]`` tensor handed in as ``res`` (the clip values, or clip / n_states
+    when the weights are also discretised).  Returns the output and the clamped step that the
+    backward divides by."""
+    alpha = 2 * bound
+    res = alpha / res_arg if bool((res_arg > 1.0).all()) else alpha * res_arg
+    res = res.clone()
+    res[res == 0.0] = 1.0
+    clamped = res.clamp_min(torch.finfo(w_t.dtype).tiny)
+    out = w_t / clamped
+    out = torch.clamp(out, min=-max_state, max=max_state)
+    if not skip_rounding:
+        out = out.round()
+    out = out * res
+    return out, clamped
+
+
 @dataclass
 class TileRecord:
     """Everything the backward and the parity tests want to see of one tile."""
@@ -131,6 +150,7 @@ class TileRecord:
     bound: Optional[Tensor] = None  # ADC bound, broadcastable to [M,N]
     pre_clamp: Optional[Tensor] = None  # ADC-quantised tile output before the clamp
     out_t: Optional[Tensor] = None  # tile contribution after everything
+    learn: Optional[dict] = None  # learnable weight clip: what its backward needs
 
 
 @dataclass
@@ -223,14 +243,21 @@ def forward(
     rpu_config,
     noise: Optional[NoiseReplay] = None,
     no_rounding: bool = False,
+    learnable_weight_clip: Optional[Tensor] = None,
 ) -> ForwardRecord:
     """Restated ``TorchLinear.linear`` (`torch_linear.py:116-314`) that also records every
-    intermediate.  ``LEARNABLE_PER_CHANNEL`` clipping is not restated (outside the path)."""
+    intermediate.  ``learnable_weight_clip`` is the ``[T, N]`` parameter of LEARNABLE_PER_CHANNEL
+    clipping (`base.py:104-118`)."""
     noise = noise or NoiseReplay(None, None)
     fwd, mod, clip = rpu_config.forward, rpu_config.modifier, rpu_config.clip
     irp = rpu_config.pre_post.input_range
     noise_type, quant_type, clip_type = _ev(mod.noise_type), _ev(mod.quantization_type), _ev(clip.type)
-    assert clip_type != CLIP_LEARN_PC, "learnable weight clipping is not restated by this oracle"
+    learnable = clip_type == CLIP_LEARN_PC
+    if learnable:
+        assert learnable_weight_clip is not None, "learnable_weight_clip should not be None"
+        assert quant_type in (QUANT_NONE, QUANT_DISC_PC), (
+            "You can't learn weight ranges per column but quantize per tensor"
+        )
     apply_out_quant = fwd.out_res > 0
     if apply_out_quant:
         assert fwd.out_bound > 0, "Out quant. without a bound."
@@ -284,13 +311,32 @@ def forward(
             or (training and fwd.out_noise > 0)
             or (training and noise_type in (NOISE_ADD, NOISE_ADD_PC))
             or quant_type in (QUANT_DISC, QUANT_DISC_PC)
+            or learnable
         )
         amax_rows = w_t.abs().amax(dim=-1, keepdim=True) if need_wmax else None
-        tr.amax_rows = amax_rows
 
-        if quant_type in (QUANT_DISC, QUANT_DISC_PC):
+        if learnable:
+            # `quant_utils.py:184-233`: clamp to the learned range (no rounding), or discretise with
+            # the learned range as the scale; afterwards the learned range stands in for the
+            # abs-max everywhere (`torch_linear.py:236-246`)
+            lwc_t = learnable_weight_clip[t].detach().unsqueeze(-1)
+            numel = w_t.numel()
+            if quant_type == QUANT_NONE:
+                w_q, clamped = learnable_quantize(w_t, lwc_t, 0.5, 1.0, True)
+                tr.learn = dict(w=w_t, res=clamped, qmax=1.0, skip=True, grad_scale=1 / sqrt(numel), n_states=None)
+            else:
+                n_states = max(mod.res, 1 / mod.res)
+                qmax = n_states / 2
+                skip = bool(no_rounding)
+                w_q, clamped = learnable_quantize(w_t, lwc_t / n_states, 1.0, qmax, skip)
+                tr.learn = dict(w=w_t, res=clamped, qmax=qmax, skip=skip, n_states=n_states,
+                                grad_scale=1 / sqrt(numel) if skip else 2 * sqrt(qmax / numel))
+            w_t = w_q
+            amax_rows = lwc_t.view_as(amax_rows)
+        elif quant_type in (QUANT_DISC, QUANT_DISC_PC):
             scale = amax_rows.max() if quant_type == QUANT_DISC else amax_rows
             w_t = discretize_weight(w_t, scale, mod.res, no_rounding)
+        tr.amax_rows = amax_rows
 
         if training and noise_type != NOISE_NONE:
             s = amax_rows.max() if noise_type == NOISE_ADD else amax_rows
@@ -350,12 +396,34 @@ def backward(
     static_ir = irp.enable and not irp.dynamic and not irp.fast_mode
     fast_ir = irp.enable and irp.fast_mode
     grad_ir = torch.zeros_like(input_range) if ((static_ir or fast_ir) and input_range is not None) else None
+    grad_clip = None
+    if rec.tiles and rec.tiles[0].learn is not None:
+        grad_clip = torch.zeros(len(rec.tiles), weights.shape[0], dtype=weights.dtype)
     for t, tr in enumerate(rec.tiles):
         g_t = g
         if tr.pre_clamp is not None:
             keep = (tr.pre_clamp >= -tr.bound) & (tr.pre_clamp <= tr.bound)
             g_t = g * keep
-        grad_w[:, tr.lo : tr.hi] = g_t.T @ tr.q
+        gw_t = g_t.T @ tr.q
+        if tr.learn is not None:
+            # `UniformQuantize.backward`, learn_res branch (`quant_utils.py:125-151`): indicator
+            # tensors are fp32 (`.float()`), which promotes the products and the row sum to fp32;
+            # autograd then casts both gradients back to the dtype of their inputs
+            L = tr.learn
+            q_w = L["w"] / L["res"]
+            small = (q_w < -L["qmax"]).float()
+            big = (q_w > L["qmax"]).float()
+            middle = 1.0 - small - big
+            if L["skip"]:
+                g_res = (small * (-L["qmax"]) + big * L["qmax"]) * gw_t * L["grad_scale"]
+            else:
+                g_res = (small * (-L["qmax"]) + big * L["qmax"] + middle * (-q_w + q_w.round())) * gw_t * L["grad_scale"]
+            g_res = g_res.sum(dim=-1, keepdim=True).to(weights.dtype)
+            if L["n_states"] is not None:
+                g_res = g_res / L["n_states"]  # res argument was clip / n_states
+            grad_clip[t] = g_res.view(-1)
+            gw_t = (middle * gw_t).to(weights.dtype)
+        grad_w[:, tr.lo : tr.hi] = gw_t
         gx = g_t @ tr.w_mod
         x_t = x2d[:, tr.lo : tr.hi]
         if static_ir:
@@ -389,6 +457,7 @@ def backward(
         "grad_w": grad_w,
         "grad_bias": g.sum(0) if has_bias else None,
         "grad_ir": grad_ir,
+        "grad_clip": grad_clip,
     }
 
 

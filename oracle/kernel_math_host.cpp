@@ -40,25 +40,33 @@ static void dac_rows(const void* x, int M, int K, const int* ends, int T, int ir
 template <int DT>
 static void weight_modify_rows(const void* w, int N, int K, const int* ends, int T, int quant_type,
                                float n_states, float max_state, int noise_type, float std_dev,
-                               const void* w_noise, int no_rounding, void* w_mod, void* amax_out) {
+                               const void* w_noise, int no_rounding, void* w_mod, void* amax_out,
+                               const void* clip) {
+  // clip != null: learned per-channel ranges [T,N] stand in for the abs-max; without a
+  // discretiser they only clamp
+  const bool learn_clamp = clip != nullptr && quant_type == 0;
   for (int t = 0; t < T; ++t) {
     int lo = t ? ends[t - 1] : 0, hi = ends[t];
     float t_max = 0.0f;
     bool all_gt1 = true;
     for (int n = 0; n < N; ++n) {
       float r = 0.0f;
-      for (int k = lo; k < hi; ++k) r = fmaxf(r, fabsf(Elem<DT>::load(w, (int64_t)n * K + k)));
+      if (clip) r = Elem<DT>::load(clip, (int64_t)t * N + n);
+      else for (int k = lo; k < hi; ++k) r = fmaxf(r, fabsf(Elem<DT>::load(w, (int64_t)n * K + k)));
       Elem<DT>::store(amax_out, (int64_t)t * N + n, r);
       t_max = fmaxf(t_max, r);
       if (quant_type == 2) all_gt1 = all_gt1 && discretize_scale_gt1<DT>(r, n_states);
+      if (learn_clamp) all_gt1 = all_gt1 && r > 1.0f;
     }
     if (quant_type == 1) all_gt1 = discretize_scale_gt1<DT>(t_max, n_states);
-    if (quant_type == 0) all_gt1 = false;
+    if (quant_type == 0 && !learn_clamp) all_gt1 = false;
     for (int n = 0; n < N; ++n) {
       float r = Elem<DT>::load(amax_out, (int64_t)t * N + n);
-      const WeightSeg ws = weight_prepare<DT>(quant_type, quant_type == 1 ? t_max : r, n_states, max_state,
-                                              all_gt1, noise_type, std_dev, noise_type == 1 ? t_max : r,
-                                              no_rounding != 0);
+      const float n_scale = noise_type == 1 ? t_max : r;
+      const WeightSeg ws =
+          learn_clamp ? weight_prepare_learn_clamp<DT>(r, all_gt1, noise_type, std_dev, n_scale)
+                      : weight_prepare<DT>(quant_type, quant_type == 1 ? t_max : r, n_states, max_state, all_gt1,
+                                           noise_type, std_dev, n_scale, no_rounding != 0);
       for (int k = lo; k < hi; ++k) {
         float v = Elem<DT>::load(w, (int64_t)n * K + k);
         float xi = noise_type ? Elem<DT>::load(w_noise, (int64_t)n * K + k) : 0.0f;
@@ -99,9 +107,9 @@ void km_dac(int dtype, const void* x, int M, int K, const int* ends, int T, int 
 void km_weight_modify(int dtype, const void* w, int N, int K, const int* ends, int T,
                       int quant_type, float n_states, float max_state, int noise_type,
                       float std_dev, const void* w_noise, int no_rounding, void* w_mod,
-                      void* amax_out) {
-  if (dtype == kF32) weight_modify_rows<kF32>(w, N, K, ends, T, quant_type, n_states, max_state, noise_type, std_dev, w_noise, no_rounding, w_mod, amax_out);
-  else weight_modify_rows<kBF16>(w, N, K, ends, T, quant_type, n_states, max_state, noise_type, std_dev, w_noise, no_rounding, w_mod, amax_out);
+                      void* amax_out, const void* clip) {
+  if (dtype == kF32) weight_modify_rows<kF32>(w, N, K, ends, T, quant_type, n_states, max_state, noise_type, std_dev, w_noise, no_rounding, w_mod, amax_out, clip);
+  else weight_modify_rows<kBF16>(w, N, K, ends, T, quant_type, n_states, max_state, noise_type, std_dev, w_noise, no_rounding, w_mod, amax_out, clip);
 }
 
 void km_tile_stage(int dtype, const float* acc, int M, int N, const void* ir, int ir_per_row,

@@ -36,6 +36,7 @@ DEFAULTS = dict(
     mod_res=0.0,
     clip_type="None",
     clip_sigma=-1.0,
+    lwc_scale=1.0,  # LearnablePerChannel: the learned ranges are the per-tile abs-max times this
     weight_scale=0.3,
     seed=0,
     steps=1,  # number of forward calls (exercises init-from-data)
@@ -95,6 +96,19 @@ CASES = [
        out_bound=3.0, out_res=254.0),
     _c("fast_mode_fixed", ir_fast_mode=True, ir_init_from_data=0, ir_init_value=0.9),
     _c("bf16_fast_mode", dtype="bf16", ir_fast_mode=True, ir_init_from_data=2, steps=3),
+    # learnable per-channel weight ranges: clamp only, and as the scale of the discretiser
+    _c("learnable_clip", clip_type="LearnablePerChannel", lwc_scale=0.6, out_bound=3.0, out_res=254.0,
+       out_noise=0.04, noise_type="AddNormalPerChannel", std_dev=0.02),
+    _c("learnable_clip_eval", clip_type="LearnablePerChannel", lwc_scale=0.8, training=False,
+       ir_dynamic=True, out_bound=2.0),
+    _c("learnable_clip_discretize", clip_type="LearnablePerChannel", lwc_scale=0.8,
+       quant_type="DiscretizePerChannel", mod_res=30.0, ir_dynamic=True, noise_type="AddNormal", std_dev=0.02),
+    _c("learnable_clip_wide", clip_type="LearnablePerChannel", lwc_scale=1.0, weight_scale=6.0,
+       in_shape=(6, 32), out_features=8, ir_dynamic=True),
+    _c("bf16_learnable_clip", dtype="bf16", clip_type="LearnablePerChannel", lwc_scale=0.7,
+       ir_dynamic=True, out_bound=3.0, out_res=254.0, noise_type="AddNormalPerChannel", std_dev=0.02),
+    _c("bf16_learnable_clip_discretize", dtype="bf16", clip_type="LearnablePerChannel", lwc_scale=0.9,
+       quant_type="DiscretizePerChannel", mod_res=254.0, ir_dynamic=True),
 ]
 
 CASES_BY_NAME = {c["name"]: c for c in CASES}

@@ -42,6 +42,8 @@ def run_reference(ref, case, data):
     layer = layer.to(dtype=data["dtype"])
     layer.set_weights_and_biases(data["w"], data["b"])
     layer.train(case["training"])
+    if layer.learnable_weight_clip is not None:
+        layer.learnable_weight_clip.data.mul_(case["lwc_scale"])
 
     queue = []
     original = TL.randn_like
@@ -73,6 +75,9 @@ def run_reference(ref, case, data):
         grad_w=layer.weight.grad,
         grad_bias=None if layer.bias is None else layer.bias.grad,
         grad_ir=None if layer.input_range is None else layer.input_range.grad,
+        grad_clip=None if layer.learnable_weight_clip is None else layer.learnable_weight_clip.grad,
+        learnable_weight_clip=None if layer.learnable_weight_clip is None
+        else layer.learnable_weight_clip.detach().clone(),
         input_range=None if layer.input_range is None else layer.input_range.detach().clone(),
         input_range_update_idx=None
         if layer.input_range_update_idx is None
@@ -93,11 +98,15 @@ def run_oracle(ns, case, data):
         idx = torch.zeros(len(in_sizes), dtype=data["dtype"])
         x_min = torch.zeros(len(in_sizes), dtype=data["dtype"]) - 1e-5
         x_max = torch.zeros(len(in_sizes), dtype=data["dtype"]) + 1e-5
+    lwc = None
+    if case["clip_type"] == "LearnablePerChannel":
+        lwc = O.sliced_abs_max(in_sizes, data["w"]) * case["lwc_scale"]
     for step in range(case["steps"]):
         rec = O.forward(
             data["xs"][step], data["w"], data["b"], ir, idx, x_min, x_max, in_sizes,
             case["training"], rpu,
             O.NoiseReplay(data["w_noise"][step], data["out_noise"][step]),
+            learnable_weight_clip=lwc,
         )
     grads = O.backward(rec, data["g"], data["w"], case["bias"], ir, rpu)
     if static and not case["ir_learn"]:
@@ -129,6 +138,7 @@ def main():
             grad_w=same(want["grad_w"], grads["grad_w"]),
             grad_bias=same(want["grad_bias"], grads["grad_bias"]),
             grad_ir=same(want["grad_ir"], grads["grad_ir"]),
+            grad_clip=same(want["grad_clip"], grads["grad_clip"]),
             input_range=same(want["input_range"], ir),
             update_idx=same(want["input_range_update_idx"], idx),
             x_min=same(want["x_min"], x_min),

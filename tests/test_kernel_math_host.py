@@ -83,9 +83,12 @@ def test_host_build_of_kernel_math_matches_golden(km, name):
     n_states = max(case["mod_res"], 1 / case["mod_res"]) if quant_type else 0.0
     w_mod = torch.empty_like(w)
     amax = torch.empty(T, n, dtype=w.dtype)
+    clip = None
+    if case["clip_type"] == "LearnablePerChannel":
+        clip = want["learnable_weight_clip"].contiguous()
     km.km_weight_modify(dt, ptr(w), n, k, ptr(ends), T, quant_type, ctypes.c_float(n_states),
                         ctypes.c_float(n_states / 2), noise_type, ctypes.c_float(case["std_dev"]),
-                        ptr(data["w_noise"][-1].contiguous()), 0, ptr(w_mod), ptr(amax))
+                        ptr(data["w_noise"][-1].contiguous()), 0, ptr(w_mod), ptr(amax), ptr(clip))
     lo = 0
     for t, size in enumerate(want["in_sizes"]):
         assert same(w_mod[:, lo:lo + size], tiles[t]["w_mod"]), f"w_mod tile {t}"

@@ -39,10 +39,14 @@ def run_oracle(case, data):
         idx = torch.zeros(len(in_sizes), dtype=data["dtype"])
         x_min = torch.zeros(len(in_sizes), dtype=data["dtype"]) - 1e-5
         x_max = torch.zeros(len(in_sizes), dtype=data["dtype"]) + 1e-5
+    lwc = None
+    if case["clip_type"] == "LearnablePerChannel":
+        lwc = O.sliced_abs_max(in_sizes, data["w"]) * case["lwc_scale"]
     for step in range(case["steps"]):
         rec = O.forward(
             data["xs"][step], data["w"], data["b"], ir, idx, x_min, x_max, in_sizes,
             case["training"], rpu, O.NoiseReplay(data["w_noise"][step], data["out_noise"][step]),
+            learnable_weight_clip=lwc,
         )
     grads = O.backward(rec, data["g"], data["w"], case["bias"], ir, rpu)
     if static and not case["ir_learn"]:
@@ -58,7 +62,7 @@ def test_oracle_reproduces_reference(name):
     data = C.make_inputs(case)
     rec, grads, ir, idx, x_min, x_max = run_oracle(case, data)
     assert same(want["out"], rec.out)
-    for key in ("grad_x", "grad_w", "grad_bias", "grad_ir"):
+    for key in ("grad_x", "grad_w", "grad_bias", "grad_ir", "grad_clip"):
         assert same(want[key], grads[key]), key
     assert same(want["input_range"], ir)
     assert same(want["input_range_update_idx"], idx)

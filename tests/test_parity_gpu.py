@@ -69,6 +69,8 @@ def test_golden_case(name):
     check_close("grad_bias", None if layer.bias is None else layer.bias.grad, want["grad_bias"], dtype, case)
     got_ir_grad = None if layer.input_range is None else layer.input_range.grad
     check_close("grad_ir", got_ir_grad, want["grad_ir"], dtype, case)
+    got_clip_grad = None if layer.learnable_weight_clip is None else layer.learnable_weight_clip.grad
+    check_close("grad_clip", got_clip_grad, want["grad_clip"], dtype, case)
     if want["input_range"] is not None:
         check_close("input_range", layer.input_range.detach(), want["input_range"], dtype, case)
         assert torch.equal(layer.input_range_update_idx.cpu(), want["input_range_update_idx"])

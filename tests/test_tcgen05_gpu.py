@@ -30,6 +30,11 @@ SHAPES = [
     ("bf16_discretize", dict(in_shape=(128, 256), out_features=128, max_input_size=64)),
     ("bf16_static_noise", dict(in_shape=(64, 320), out_features=72, max_input_size=-1, ir_enable=False,
                                inp_res=-1.0, out_noise=0.0, noise_type="AddNormal", std_dev=0.02)),
+    # a clamp that rarely fires and a long reduction on a single CTA: stages are reused by transform
+    # warps that had nothing to zero on the previous use
+    ("bf16_dynamic_adc_noise", dict(in_shape=(128, 256), out_features=768, max_input_size=128, out_bound=10.0)),
+    ("bf16_dynamic_adc_noise", dict(in_shape=(128, 256), out_features=1024, max_input_size=128, out_bound=10.0,
+                                    out_noise=0.0, noise_type="None")),
     # heavy ADC clamping: most rows of the staged gradient blocks have many blocked entries
     ("bf16_dynamic_adc_noise", dict(in_shape=(384, 512), out_features=392, max_input_size=128, out_bound=0.3)),
     ("bf16_static_adc", dict(in_shape=(200, 512), out_features=264, max_input_size=256, ir_init_value=2.0,
@@ -73,7 +78,7 @@ def test_tcgen05_engine_matches_oracle_and_simt(base, over, engine):
     # with the reference's rounding chain emulated the two engines and the oracle agree on
     # almost every bf16 value of the forward output
     assert frac_equal(got["out"], want["out"]) >= 0.95
-    if "out_bound" in over:
+    if over.get("out_bound", 10.0) < 1.0:
         blocked = sum(int(((tr.pre_clamp < -tr.bound) | (tr.pre_clamp > tr.bound)).sum()) for tr in rec.tiles)
         assert blocked > 0.05 * rec.out.numel() * len(rec.tiles), "this case is meant to clamp heavily"
     if grads["grad_ir"] is not None and case["ir_learn"]:

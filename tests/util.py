@@ -44,6 +44,8 @@ def run_product_layer(case, data, device="cuda", engine="auto", capture=None):
     layer = layer.to(device=device, dtype=data["dtype"])
     layer.set_weights_and_biases(data["w"].to(device), None if data["b"] is None else data["b"].to(device))
     layer.train(case["training"])
+    if layer.learnable_weight_clip is not None:
+        layer.learnable_weight_clip.data.mul_(case["lwc_scale"])
     for step in range(case["steps"]):
         x = data["xs"][step].to(device).clone().requires_grad_(True)
         layer.zero_grad()
@@ -71,7 +73,10 @@ def oracle_run(case, data, x=None, w=None, b=None, g=None, w_noise=None, out_noi
         idx = torch.zeros(len(in_sizes), dtype=x.dtype)
         x_min = torch.zeros(len(in_sizes), dtype=x.dtype) - 1e-5
         x_max = torch.zeros(len(in_sizes), dtype=x.dtype) + 1e-5
+    lwc = None
+    if case["clip_type"] == "LearnablePerChannel":
+        lwc = O.sliced_abs_max(in_sizes, w) * case["lwc_scale"]
     rec = O.forward(x, w, b, ir, idx, x_min, x_max, in_sizes, training, rpu,
-                    O.NoiseReplay(w_noise, out_noise))
+                    O.NoiseReplay(w_noise, out_noise), learnable_weight_clip=lwc)
     grads = O.backward(rec, g, w, b is not None, ir, rpu)
     return rec, grads
