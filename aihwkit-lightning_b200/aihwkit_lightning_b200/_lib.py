@@ -42,7 +42,7 @@ class AlForwardArgs(Structure):
         ("tile_ends", POINTER(c_int32)),
         ("out", c_void_p), ("xq", c_void_p), ("ir_rows", c_void_p), ("w_amax", c_void_p),
         ("w_tile_max", c_void_p), ("w_mod", c_void_p), ("keep_mask", c_void_p),
-        ("std_scratch", c_void_p), ("w_noise", c_void_p), ("out_noise", c_void_p),
+        ("std_scratch", c_void_p), ("smallm_scratch", c_void_p), ("w_noise", c_void_p), ("out_noise", c_void_p),
         ("codes", c_void_p), ("seed", c_uint64), ("offset", c_uint64),
     ]
 
@@ -74,6 +74,7 @@ SYMBOLS = {
     "al_forward": (c_int32, [POINTER(AlDesc), POINTER(AlForwardArgs), c_void_p]),
     "al_backward": (c_int32, [POINTER(AlDesc), POINTER(AlBackwardArgs), c_void_p]),
     "al_backward_scratch_floats": (c_int64, [c_int32, c_int32, c_int32, c_int32]),
+    "al_smallm_scratch_floats": (c_int64, [c_int32, c_int32, c_int32]),
     "al_clip_weights": (c_int32, [c_int32, c_void_p, c_int32, c_int32, c_int32, c_float, c_void_p, c_void_p]),
     "al_unfold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
     "al_fold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),

@@ -126,7 +126,8 @@ class AnalogLinearFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, inp, weight, bias, input_range, input_range_update_idx, in_sizes, training,
-                rpu_config, x_min=None, x_max=None, learnable_weight_clip=None):  # type: ignore[override]
+                rpu_config, x_min=None, x_max=None, learnable_weight_clip=None,
+                grad_enabled=True):  # type: ignore[override]
         lib = _lib.load()
         if not inp.is_cuda or not weight.is_cuda:
             raise ValueError(
@@ -143,7 +144,9 @@ class AnalogLinearFunction(torch.autograd.Function):
         w = weight.contiguous()
         t = len(in_sizes)
         dev, dtype = inp.device, inp.dtype
-        needs_grad = any(ctx.needs_input_grad[:4]) or ctx.needs_input_grad[10]
+        # needs_input_grad mirrors requires_grad of the inputs even under torch.no_grad(); the
+        # caller's grad mode arrives as an argument (inside forward it is always off)
+        needs_grad = grad_enabled and (any(ctx.needs_input_grad[:4]) or ctx.needs_input_grad[10])
         desc = make_desc(rpu_config, m, k, n, t, dtype, training)
         desc.save_for_backward = int(needs_grad)
         ends = _lib.tile_ends_array(in_sizes)
@@ -196,6 +199,10 @@ class AnalogLinearFunction(torch.autograd.Function):
             if static and training and desc.init_from_data > 0:
                 std_scratch = torch.empty(lib.al_std_scratch_floats(m, t), device=dev, dtype=torch.float32)
             args.std_scratch = _ptr(std_scratch)
+            smallm_scratch = None
+            if m <= 16 and not needs_grad and dtype == torch.bfloat16 and settings.capture is None:
+                smallm_scratch = torch.empty(lib.al_smallm_scratch_floats(m, n, t), device=dev, dtype=torch.float32)
+            args.smallm_scratch = _ptr(smallm_scratch)
             w_noise, out_noise = settings.w_noise, settings.out_noise
             if w_noise is not None:
                 w_noise = w_noise.to(device=dev, dtype=dtype).contiguous()
@@ -233,7 +240,7 @@ class AnalogLinearFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):  # type: ignore[override]
         if ctx.empty:
-            return (None,) * 11
+            return (None,) * 12
         lib = _lib.load()
         x2d, xq, w_mod, ir_rows, keep_mask, w_saved, lwc = ctx.saved_tensors
         desc = ctx.desc
@@ -270,7 +277,7 @@ class AnalogLinearFunction(torch.autograd.Function):
             grad_w = None
         if not ctx.needs_input_grad[10]:
             grad_clip = None
-        return grad_x, grad_w, grad_b, grad_ir, None, None, None, None, None, None, grad_clip
+        return grad_x, grad_w, grad_b, grad_ir, None, None, None, None, None, None, grad_clip, None
 
 
 def analog_linear(inp: Tensor, weight: Tensor, bias: Optional[Tensor], input_range: Optional[Tensor],
@@ -279,7 +286,8 @@ def analog_linear(inp: Tensor, weight: Tensor, bias: Optional[Tensor], input_ran
                   learnable_weight_clip: Optional[Tensor] = None) -> Tensor:
     """Functional form used by ``AnalogLinear`` and ``AnalogConv2d``."""
     return AnalogLinearFunction.apply(inp, weight, bias, input_range, input_range_update_idx,
-                                      in_sizes, training, rpu_config, x_min, x_max, learnable_weight_clip)
+                                      in_sizes, training, rpu_config, x_min, x_max, learnable_weight_clip,
+                                      torch.is_grad_enabled())
 
 
 def sliced_abs_max(in_sizes: List[int], weights: Tensor) -> Tensor:

@@ -19,6 +19,7 @@ SOURCES = [
     "prepass_kernels.cu",
     "gemm_simt.cu",
     "gemm_tcgen05.cu",
+    "gemm_smallm.cu",
     "backward_kernels.cu",
     "conv_kernels.cu",
 ]

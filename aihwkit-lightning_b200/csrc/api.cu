@@ -280,6 +280,25 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     xq = a->xq;
   }
 
+  // 2b. a handful of rows, nothing to modify in the weights, no backward to prepare: the layer is
+  // bound by streaming W once; one kernel takes abs-max and tile products from the same read
+  if (a->smallm_scratch && d.dtype == AL_BF16 && d.engine == AL_ENGINE_AUTO && !dv.has_noise &&
+      dv.weight_quant == AL_QUANT_NONE && dv.weight_noise == AL_NOISE_NONE &&
+      d.clip_type != AL_CLIP_LEARNABLE_PER_CHANNEL && !d.save_for_backward && a->w_amax && a->w_tile_max &&
+      smallm_forward_supported(d.M, d.K, d.N, tt) && ((uintptr_t)xq % 16) == 0 && ((uintptr_t)a->w % 16) == 0) {
+    FwdEpilogueParams ep;
+    memset(&ep, 0, sizeof(ep));
+    ep.M = d.M; ep.N = d.N; ep.T = d.T;
+    ep.ir_mode = d.ir_mode == AL_IR_FAST ? AL_IR_STATIC : d.ir_mode;
+    ep.ir_rows = a->ir_rows;
+    ep.bias = a->bias;
+    ep.has_bound = dv.has_bound; ep.has_adc = dv.has_adc;
+    ep.bound_pc = dv.bound_pc; ep.noise_pc = dv.noise_pc; ep.no_rounding = d.no_rounding;
+    ep.noise_coef = dv.noise_coef; ep.out_bound = dv.out_bound; ep.out_res = dv.out_res;
+    return launch_fwd_smallm(dv.round_dt, xq, a->w, d.K, tt, ep, a->w_amax, (float*)a->w_tile_max,
+                             a->smallm_scratch, a->out, s);
+  }
+
   // 3. weight statistics and modifier
   const void* w_mod = a->w;
   float* tile_max = nullptr;
@@ -368,6 +387,12 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
   const int pairing = d.engine == AL_ENGINE_TCGEN05_PAIR ? 1 : d.engine == AL_ENGINE_TCGEN05_SINGLE ? -1 : 0;
   if (pick_tc(d, tt, false)) return launch_fwd_tc(dv.round_dt, xq, w_mod, d.K, tt, ep, pairing, a->out, s);
   return launch_fwd_simt(d.dtype, dv.round_dt, xq, w_mod, d.K, tt, ep, a->out, s);
+}
+
+int64_t al_smallm_scratch_floats(int32_t M, int32_t N, int32_t T) {
+  // 0: the problem does not take the few-rows path (more than 16 rows), no scratch needed
+  if (M < 1 || M > 16 || N < 1 || T < 1) return 0;
+  return smallm_scratch_floats(N, T);
 }
 
 int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T) {

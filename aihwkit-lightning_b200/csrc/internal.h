@@ -122,6 +122,13 @@ int launch_static_ir_backward(int dtype, const void* x, const void* ir_used, voi
                               int K, const TileTable& tt, float decay, float input_min_percentage,
                               void* grad_ir, float* scratch, int fast_mode, cudaStream_t s);
 
+// ---- few-rows forward (gemm_smallm.cu): M <= 16, bf16, unmodified weights, no output noise ----
+int64_t smallm_scratch_floats(int N, int T);
+bool smallm_forward_supported(int M, int K, int N, const TileTable& tt);
+int launch_fwd_smallm(int round_dt, const void* xq, const void* w, int K, const TileTable& tt,
+                      const FwdEpilogueParams& ep, void* w_amax, float* tile_max, float* scratch, void* out,
+                      cudaStream_t s);
+
 // ---- tcgen05 GEMMs (gemm_tcgen05.cu) ------------------------------------------------------
 bool tc_forward_supported(const AlDesc& d, const TileTable& tt);
 // pairing: 0 = CTA pairs when they fill the machine, 1 = always pairs, -1 = never

@@ -124,6 +124,10 @@ typedef struct AlForwardArgs {
                                  nullable if out_bound <= 0                                 */
   float* std_scratch;        /* >= al_std_scratch_floats(M, T) floats, static mode with
                                  init_from_data > 0 in training; nullable otherwise        */
+  float* smallm_scratch;     /* >= al_smallm_scratch_floats(M, N, T) floats, nullable: lets a
+                                 call with M <= 16 rows that modifies no weights and prepares
+                                 no backward stream the weights once (abs-max and tile
+                                 products from the same read)                               */
   /* shared-noise parity mode: standard normals to use instead of the internal generator */
   const void* w_noise;       /* [N,K] dtype, nullable                                       */
   const void* out_noise;     /* [T,M,N] dtype, nullable                                     */
@@ -194,6 +198,8 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* args, void* stream);
  * (triton_linear.py:695-764). */
 int al_backward(const AlDesc* desc, const AlBackwardArgs* args, void* stream);
 int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T);
+/* floats of AlForwardArgs.smallm_scratch; 0 when the problem has more than 16 rows */
+int64_t al_smallm_scratch_floats(int32_t M, int32_t N, int32_t T);
 
 /* In-place weight clipping w <- clamp(w, +-sigma*std(w)), std over the whole tensor
  * (AL_CLIP_LAYER_GAUSSIAN) or per row (AL_CLIP_LAYER_GAUSSIAN_PER_CHANNEL).  Replaces
