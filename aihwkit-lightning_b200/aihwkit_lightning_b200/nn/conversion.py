@@ -1,18 +1,19 @@
-"""Swap ``nn.Linear`` / ``nn.Conv2d`` for their analog counterparts and back.
+"""Swap ``nn.Linear`` / ``nn.Conv1d`` / ``nn.Conv2d`` / ``nn.Conv3d`` for their analog counterparts and back.
 
 Covers what the benchmark models need of the reference's ``convert_to_analog`` /
-``convert_to_digital`` (`nn/conversion.py:71-295`): same arguments for the Linear/Conv2d
+``convert_to_digital`` (`nn/conversion.py:71-295`): same arguments for the Linear/ConvNd
 entries of the conversion map, recursion over children, ``exclude_modules`` by name suffix.
 """
 from copy import deepcopy
 from typing import Dict, List, Optional, Type
 
-from torch.nn import Conv2d, Linear, Module
+from torch.nn import Conv1d, Conv2d, Conv3d, Linear, Module
 
-from .modules import AnalogConv2d, AnalogLayerBase, AnalogLinear
+from .modules import AnalogConv1d, AnalogConv2d, AnalogConv3d, AnalogLayerBase, AnalogLinear
 
-_DEFAULT_CONVERSION_MAP: Dict[Type, Type] = {Linear: AnalogLinear, Conv2d: AnalogConv2d}
-_DEFAULT_DIGITAL_CONVERSION_SET = {AnalogLinear, AnalogConv2d}
+_DEFAULT_CONVERSION_MAP: Dict[Type, Type] = {Linear: AnalogLinear, Conv1d: AnalogConv1d, Conv2d: AnalogConv2d,
+                                             Conv3d: AnalogConv3d}
+_DEFAULT_DIGITAL_CONVERSION_SET = {AnalogLinear, AnalogConv1d, AnalogConv2d, AnalogConv3d}
 
 
 def convert_to_analog(module: Module, rpu_config, conversion_map: Optional[Dict] = None,

@@ -1,8 +1,12 @@
-"""``AnalogConv2d``: drop-in for the reference layer (`nn/modules/conv.py:123-360,516-677`).
+"""``AnalogConv1d`` / ``AnalogConv2d`` / ``AnalogConv3d``: drop-ins for the reference layers
+(`nn/modules/conv.py:123-360, 363-513, 516-677, 680-941`).
 
 The convolution is evaluated as the analog linear operator on unfolded patches: the patch
-axis is ordered (channel, kernel row, kernel column) like ``torch.nn.functional.unfold``, and
-analog tiles are cut along that axis, exactly as the reference does.
+axis is ordered (channel, kernel depth, kernel row, kernel column) like
+``torch.nn.functional.unfold``, and analog tiles are cut along that axis, exactly as the
+reference does.  2-D (and 1-D, which is 2-D with one row) patches come from the library's own
+unfold kernel; 3-D patches are strided views of the padded input (PyTorch plumbing, off the
+benchmarked path).
 """
 from copy import deepcopy
 from functools import reduce
@@ -11,7 +15,7 @@ from typing import Optional, Tuple, Union
 import torch
 from torch import Tensor
 from torch.nn.modules.conv import _ConvNd
-from torch.nn.modules.utils import _pair
+from torch.nn.modules.utils import _pair, _single, _triple
 
 from ...simulator.configs import TorchInferenceRPUConfig
 from ...simulator.enums import WeightClipType, WeightQuantizationType
@@ -21,7 +25,7 @@ from .linear import _modified_weights
 
 
 class _AnalogConvNd(AnalogLayerBase, _ConvNd):
-    """Shared base of the analog convolutions (only 2-D is provided)."""
+    """Shared base of the analog convolutions."""
 
     def __init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, transposed,
                  output_padding, groups, bias, padding_mode, device=None, dtype=None,
@@ -137,6 +141,124 @@ class AnalogConv2d(_AnalogConvNd):
     @classmethod
     def to_digital(cls, module: "AnalogConv2d") -> torch.nn.Conv2d:
         digital = torch.nn.Conv2d(module.in_channels, module.out_channels, module.kernel_size,
+                                  module.stride, module.padding, module.dilation, module.groups,
+                                  module.bias is not None, module.padding_mode)
+        digital.weight.data = module.weight.data.detach().clone()
+        if module.bias is not None:
+            digital.bias.data = module.bias.data.detach().clone()
+        return digital.to(device=module.weight.device, dtype=module.weight.dtype)
+
+
+class AnalogConv1d(_AnalogConvNd):
+    """1-D convolution on analog tiles; same signature as ``torch.nn.Conv1d`` plus ``rpu_config``.
+
+    Held as a 2-D convolution over images of one row (`nn/modules/conv.py:394-436`): the weight
+    parameter is ``[out, in, 1, k]`` and is squeezed to PyTorch's ``[out, in, k]`` in state dicts."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size: Union[int, Tuple], stride=1,
+                 padding=0, dilation=1, groups: int = 1, bias: bool = True, padding_mode: str = "zeros",
+                 device=None, dtype=None, rpu_config: Optional[TorchInferenceRPUConfig] = None):
+        kernel_size, stride = _single(kernel_size), _single(stride)
+        padding, dilation = _single(padding), _single(dilation)
+        if dilation != _single(1):
+            raise ValueError("Only dilation = 1 is supported")
+        super().__init__(in_channels, out_channels, (1, kernel_size[0]), (1, stride[0]), (0, padding[0]),
+                         (1, dilation[0]), False, _pair(0), groups, bias, padding_mode, device, dtype,
+                         rpu_config)
+        self._register_load_state_dict_pre_hook(self._unsqueeze_loaded_weight)
+        self._register_state_dict_hook(self._squeeze_saved_weight)
+
+    def forward(self, inp: Tensor) -> Tensor:
+        return super().forward(inp.unsqueeze(-2)).squeeze(-2)
+
+    @classmethod
+    def from_digital(cls, module: torch.nn.Conv1d, rpu_config: TorchInferenceRPUConfig) -> "AnalogConv1d":
+        layer = cls(module.in_channels, module.out_channels, module.kernel_size, module.stride,
+                    module.padding, module.dilation, module.groups, module.bias is not None,
+                    module.padding_mode, device=module.weight.device, dtype=module.weight.dtype,
+                    rpu_config=rpu_config)
+        layer.set_weights_and_biases(module.weight.data.unsqueeze(-2),
+                                     None if module.bias is None else module.bias.data)
+        return layer
+
+    @classmethod
+    def to_digital(cls, module: "AnalogConv1d") -> torch.nn.Conv1d:
+        digital = torch.nn.Conv1d(module.in_channels, module.out_channels, module.kernel_size[1],
+                                  module.stride[1], module.padding[1], module.dilation[1], module.groups,
+                                  module.bias is not None, module.padding_mode)
+        digital.weight.data = module.weight.data.detach().clone().squeeze(-2)
+        if module.bias is not None:
+            digital.bias.data = module.bias.data.detach().clone()
+        return digital.to(device=module.weight.device, dtype=module.weight.dtype)
+
+    @staticmethod
+    def _unsqueeze_loaded_weight(state_dict, prefix, *args, **kwargs):  # pylint: disable=unused-argument
+        key = prefix + "weight"
+        if key in state_dict and state_dict[key].ndim == 3:
+            state_dict[key] = state_dict[key].unsqueeze(-2)
+
+    @staticmethod
+    def _squeeze_saved_weight(module, state_dict, prefix, local_metadata):  # pylint: disable=unused-argument
+        key = prefix + "weight"
+        if key in state_dict and state_dict[key].ndim == 4:
+            state_dict[key] = state_dict[key].squeeze(-2)
+
+
+def unfold3d(inp: Tensor, kernel_size, padding, stride) -> Tensor:
+    """Patches of a ``[B, C, D, H, W]`` (or unbatched ``[C, D, H, W]``) volume as
+    ``[B, patches, C * kD * kH * kW]``: rows are output positions (depth-major), the patch axis is
+    ordered (channel, kernel depth, kernel row, kernel column) (`nn/modules/conv.py:42-104`,
+    transposed here because the linear operator wants patches as rows)."""
+    batched = inp.ndim == 5
+    vol = inp if batched else inp.unsqueeze(0)
+    vol = torch.nn.functional.pad(vol, (padding[2], padding[2], padding[1], padding[1], padding[0], padding[0]))
+    views = vol.unfold(2, kernel_size[0], stride[0]).unfold(3, kernel_size[1], stride[1])
+    views = views.unfold(4, kernel_size[2], stride[2])          # [B, C, nD, nH, nW, kD, kH, kW]
+    views = views.permute(0, 2, 3, 4, 1, 5, 6, 7)               # [B, nD, nH, nW, C, kD, kH, kW]
+    patches = views.reshape(views.shape[0], views.shape[1] * views.shape[2] * views.shape[3], -1)
+    return patches if batched else patches.squeeze(0)
+
+
+class AnalogConv3d(_AnalogConvNd):
+    """3-D convolution on analog tiles; same signature as ``torch.nn.Conv3d`` plus ``rpu_config``
+    (`nn/modules/conv.py:680-941`; dilation 1 only, like the reference)."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size: Union[int, Tuple], stride=1,
+                 padding=0, dilation=1, groups: int = 1, bias: bool = True, padding_mode: str = "zeros",
+                 device=None, dtype=None, rpu_config: Optional[TorchInferenceRPUConfig] = None):
+        if _triple(dilation) != _triple(1):
+            raise ValueError("Only dilation = 1 is supported")
+        super().__init__(in_channels, out_channels, _triple(kernel_size), _triple(stride), _triple(padding),
+                         _triple(dilation), False, _triple(0), groups, bias, padding_mode, device, dtype,
+                         rpu_config)
+
+    def forward(self, inp: Tensor) -> Tensor:
+        self._check_forward_config()
+        assert isinstance(self.padding, tuple), "Padding must be a tuple"
+        patches = unfold3d(inp, self.kernel_size, self.padding, self.stride)
+        out = F.analog_linear(patches, self.weight.view(self.out_channels, -1), self.bias,
+                              self.input_range, self.input_range_update_idx, self.in_sizes,
+                              self.training, self.rpu_config, self.x_min, self.x_max,
+                              self.learnable_weight_clip)
+        sizes = [(inp.shape[-3 + i] + 2 * self.padding[i] - (self.kernel_size[i] - 1) - 1) // self.stride[i] + 1
+                 for i in range(3)]
+        out = out.transpose(-1, -2).contiguous()
+        if inp.ndim == 4:
+            return out.view(self.out_channels, *sizes)
+        return out.view(inp.shape[0], self.out_channels, *sizes)
+
+    @classmethod
+    def from_digital(cls, module: torch.nn.Conv3d, rpu_config: TorchInferenceRPUConfig) -> "AnalogConv3d":
+        layer = cls(module.in_channels, module.out_channels, module.kernel_size, module.stride,
+                    module.padding, module.dilation, module.groups, module.bias is not None,
+                    module.padding_mode, device=module.weight.device, dtype=module.weight.dtype,
+                    rpu_config=rpu_config)
+        layer.set_weights_and_biases(module.weight.data, None if module.bias is None else module.bias.data)
+        return layer
+
+    @classmethod
+    def to_digital(cls, module: "AnalogConv3d") -> torch.nn.Conv3d:
+        digital = torch.nn.Conv3d(module.in_channels, module.out_channels, module.kernel_size,
                                   module.stride, module.padding, module.dilation, module.groups,
                                   module.bias is not None, module.padding_mode)
         digital.weight.data = module.weight.data.detach().clone()

@@ -166,3 +166,77 @@ def test_unfold2d_and_its_adjoint_match_torch(dtype, geom):
     # 3-D input (single image), as the reference accepts
     one = F.unfold2d(x.detach()[0], geom["k"], geom["d"], geom["p"], geom["s"])
     assert torch.equal(one, got.detach()[0])
+
+
+@pytest.mark.parametrize("dims", [1, 3])
+def test_conv1d_and_conv3d_match_their_digital_twins(dims):
+    """With input range, DAC and modifier off the analog layer is the plain convolution: forward
+    and all gradients against ``to_digital`` of the same layer."""
+    from aihwkit_lightning_b200.nn import AnalogConv1d, AnalogConv3d
+
+    rpu, _ = make_cfg(ir_enable=False, inp_res=-1.0, max_input_size=16)
+    torch.manual_seed(0)
+    torch.backends.cudnn.allow_tf32 = False  # the digital twin must compute in fp32 to be a yardstick
+    if dims == 1:
+        conv = AnalogConv1d(3, 5, 4, stride=2, padding=1, rpu_config=rpu).cuda()
+        x = torch.randn(4, 3, 19, device="cuda", requires_grad=True)
+        assert conv.weight.shape == (5, 3, 1, 4)
+    else:
+        conv = AnalogConv3d(2, 4, (2, 3, 2), stride=(1, 2, 1), padding=(1, 0, 1), rpu_config=rpu).cuda()
+        x = torch.randn(2, 2, 5, 6, 7, device="cuda", requires_grad=True)
+    ref = type(conv).to_digital(conv)
+    x2 = x.detach().clone().requires_grad_(True)
+    out, want = conv(x), ref(x2)
+    assert out.shape == want.shape
+    assert torch.allclose(out, want, rtol=1e-4, atol=1e-4)
+    out.square().sum().backward()
+    want.square().sum().backward()
+    assert torch.allclose(x.grad, x2.grad, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(conv.weight.grad.reshape(ref.weight.shape), ref.weight.grad, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(conv.bias.grad, ref.bias.grad, rtol=1e-4, atol=1e-4)
+    # unbatched input
+    assert torch.allclose(conv(x.detach()[0]), ref(x2.detach()[0]), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("dims", [1, 3])
+def test_conv1d_and_conv3d_match_oracle_on_patches(dims):
+    from aihwkit_lightning_b200.nn import AnalogConv1d, AnalogConv3d
+    from aihwkit_lightning_b200.nn.modules.conv import unfold3d
+
+    rpu, _ = make_cfg(ir_dynamic=True, max_input_size=10, out_bound=4.0, out_res=254.0, training=False)
+    torch.manual_seed(0)
+    if dims == 1:
+        conv = AnalogConv1d(4, 6, 5, padding=2, rpu_config=rpu).cuda().eval()
+        x = torch.randn(3, 4, 21)
+        patches = torch.nn.functional.unfold(x.unsqueeze(-2), (1, 5), padding=(0, 2)).transpose(1, 2)
+    else:
+        conv = AnalogConv3d(2, 5, 2, padding=1, rpu_config=rpu).cuda().eval()
+        x = torch.randn(2, 2, 4, 5, 6)
+        patches = unfold3d(x, (2, 2, 2), (1, 1, 1), (1, 1, 1))
+    got = conv(x.cuda())
+    rec = O.forward(patches, conv.weight.detach().cpu().view(conv.out_channels, -1), conv.bias.detach().cpu(),
+                    None, None, None, None, conv.in_sizes, False, rpu)
+    want = rec.out.transpose(1, 2).reshape(got.shape)
+    assert torch.allclose(got.cpu(), want, rtol=1e-5, atol=1e-5)
+
+
+def test_conv1d_conversion_and_checkpoint_use_pytorch_weight_shape():
+    from aihwkit_lightning_b200.nn import AnalogConv1d, AnalogConv3d, convert_to_analog, convert_to_digital
+
+    rpu, _ = make_cfg(ir_dynamic=True)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Conv1d(3, 4, 3), torch.nn.Flatten(), torch.nn.Linear(4 * 6, 2))
+    analog = convert_to_analog(model, rpu).cuda()
+    assert isinstance(analog[0], AnalogConv1d)
+    state = analog.state_dict()
+    assert state["0.weight"].shape == (4, 3, 3)            # squeezed like torch.nn.Conv1d
+    twin = convert_to_analog(model, rpu).cuda()
+    twin.load_state_dict(state)
+    assert twin[0].weight.shape == (4, 3, 1, 3)
+    x = torch.randn(5, 3, 8, device="cuda")
+    assert torch.equal(analog.eval()(x), twin.eval()(x))
+    digital = convert_to_digital(analog)
+    assert isinstance(digital[0], torch.nn.Conv1d) and digital[0].weight.shape == (4, 3, 3)
+    assert isinstance(convert_to_analog(torch.nn.Conv3d(1, 2, 3), rpu), AnalogConv3d)
+    with pytest.raises(ValueError):
+        AnalogConv1d(3, 4, 3, dilation=2, rpu_config=rpu)
