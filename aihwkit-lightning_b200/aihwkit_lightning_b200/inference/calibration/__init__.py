@@ -1,0 +1,4 @@
+"""Input-range calibration."""
+from .calibration import InputRangeCalibrationType, calibrate_input_ranges
+
+__all__ = ["InputRangeCalibrationType", "calibrate_input_ranges"]
