@@ -41,6 +41,7 @@ class _Settings:
     """Process-wide switches of the operator (debug and parity aids)."""
 
     engine = "auto"
+    capture_codes = True       # with ``capture``: also ask for the integer DAC codes (debug output)
     reference_rounding = True  # bf16: round after every op like the reference's torch path
     no_rounding = False  # the reference's `_AIHWKIT_NO_ROUNDING` test switch (`quant_utils.py:60`)
     w_noise: Optional[Tensor] = None  # shared-noise parity mode: [N,K] standard normals
@@ -212,7 +213,7 @@ class AnalogLinearFunction(torch.autograd.Function):
                 assert out_noise.numel() == t * m * n, "replayed output noise must be [T,M,N]"
             args.w_noise, args.out_noise = _ptr(w_noise), _ptr(out_noise)
             codes = None
-            if settings.capture is not None and desc.ir_mode != _lib.AL_IR_OFF:
+            if settings.capture is not None and settings.capture_codes and desc.ir_mode != _lib.AL_IR_OFF:
                 codes = torch.empty_like(x2d)
             args.codes = _ptr(codes)
             if training and (desc.noise_type != 0 or desc.out_noise > 0):

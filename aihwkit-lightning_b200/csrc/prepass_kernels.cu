@@ -319,6 +319,98 @@ weight_fused_kernel(const void* __restrict__ w, int N, int K, TileTable tt, void
 inline unsigned seg_blocks(int64_t segs) { return (unsigned)((segs + kWarpsPerBlock - 1) / kWarpsPerBlock); }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+
+// ---- batched bf16 fast path of the DAC ------------------------------------------------------------------
+// A warp that handles one 1 KiB segment has 1 KiB of loads in flight and then a chain of
+// dependent steps (reduce, constants, arithmetic, store): the DAC kernel above is bound by that
+// latency, not by HBM.  When every analog tile is 256 * Q elements wide (Q = 1, 2, 4, 8)
+// and 16-byte aligned, a warp takes 8 / Q consecutive tiles of one row instead: all eight 16-byte
+// vectors of a lane are loaded up front (4 KiB in flight per warp), the per-tile abs-max comes
+// from the registers, and the same registers are transformed and stored.
+constexpr int kBatchVecs = 8;
+
+__device__ __forceinline__ float vecs_abs_max(const uint4* v, int count) {
+  __nv_bfloat162 m2 = __float2bfloat162_rn(0.0f);
+  for (int j = 0; j < count; ++j) {
+    m2 = __hmax2(m2, __habs2(as_bf162(v[j].x)));
+    m2 = __hmax2(m2, __habs2(as_bf162(v[j].y)));
+    m2 = __hmax2(m2, __habs2(as_bf162(v[j].z)));
+    m2 = __hmax2(m2, __habs2(as_bf162(v[j].w)));
+  }
+  float m = fmaxf(__low2float(m2), __high2float(m2));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  return m;
+}
+
+template <int Q>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+dac_batched_kernel(const uint16_t* __restrict__ x, int M, int K, int T, int ir_mode,
+                   const uint16_t* __restrict__ ir_static, float inp_res, uint16_t* __restrict__ xq,
+                   uint16_t* __restrict__ ir_rows) {
+  constexpr int kTiles = kBatchVecs / Q;  // tiles per warp
+  constexpr int kTileW = 256 * Q;
+  const int batches = (T + kTiles - 1) / kTiles;
+  const unsigned wid = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (unsigned)M * (unsigned)batches) return;
+  const int m = (int)(wid / (unsigned)batches), t0 = (int)(wid - (unsigned)m * (unsigned)batches) * kTiles;
+  const int64_t row = (int64_t)m * K;
+  uint4 v[kBatchVecs];
+#pragma unroll
+  for (int j = 0; j < kBatchVecs; ++j) {
+    const int t = t0 + j / Q;
+    v[j] = t < T ? __ldg(reinterpret_cast<const uint4*>(x + row + (int64_t)t * kTileW + ((j % Q) * 32 + lane) * 8))
+                 : make_uint4(0u, 0u, 0u, 0u);
+  }
+  const uint64_t magic2 = f32x2_pack(12582912.0f, 12582912.0f), nmagic2 = f32x2_pack(-12582912.0f, -12582912.0f);
+#pragma unroll
+  for (int i = 0; i < kTiles; ++i) {
+    const int t = t0 + i;
+    if (t >= T) break;
+    float ir;
+    bool clampit = false;
+    if (ir_mode == AL_IR_DYNAMIC) {
+      ir = vecs_abs_max(&v[i * Q], Q);
+      if (lane == 0) ir_rows[(int64_t)t * M + m] = f32_to_bf16_bits(ir);
+    } else {
+      ir = Elem<kBF16>::load(ir_static, t);
+      clampit = true;
+    }
+    const QuantSeg q = dac_prepare<kBF16>(ir, inp_res, clampit, false);
+    const __nv_bfloat162 b2 = __float2bfloat162_rn(q.bound), nb2 = __float2bfloat162_rn(-q.bound);
+    const __nv_bfloat162 step2 = __float2bfloat162_rn(q.step);
+    const uint64_t nstepc2 = f32x2_pack(-q.stepc, -q.stepc), rstep2 = f32x2_pack(q.rstep, q.rstep);
+#pragma unroll
+    for (int jj = 0; jj < Q; ++jj) {
+      uint32_t w[4] = {v[i * Q + jj].x, v[i * Q + jj].y, v[i * Q + jj].z, v[i * Q + jj].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        __nv_bfloat162 x2 = as_bf162(w[e]);
+        if (clampit) x2 = __hmin2_nan(__hmax2_nan(x2, nb2), b2);
+        float q_lo, q_hi, c_lo, c_hi;
+        f32x2_unpack(f32x2_div_rcp(f32x2_pack(__low2float(x2), __high2float(x2)), nstepc2, rstep2), &q_lo, &q_hi);
+        const __nv_bfloat162 q2 = __floats2bfloat162_rn(q_lo, q_hi);
+        f32x2_unpack(f32x2_add(f32x2_add(f32x2_pack(__low2float(q2), __high2float(q2)), magic2), nmagic2), &c_lo, &c_hi);
+        // an integer of at most 8 significant bits is a bf16 value: packing is a bit move
+        const uint32_t c2 = __byte_perm(__float_as_uint(c_lo), __float_as_uint(c_hi), 0x7632);
+        w[e] = as_u32(__hmul2_rn(as_bf162(c2), step2));
+      }
+      *reinterpret_cast<uint4*>(xq + row + (int64_t)t * kTileW + (jj * 32 + lane) * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+// Q for a tiling the batched kernels take (0: use the general kernels)
+int batched_q(const TileTable& tt, int K) {
+  const int w = tt.hi(0);
+  if (w != 256 && w != 512 && w != 1024 && w != 2048) return 0;
+  for (int t = 1; t < tt.T; ++t)
+    if (tt.hi(t) - tt.lo(t) != w) return 0;
+  if ((int64_t)tt.T * w != K) return 0;
+  return w / 256;
+}
+
 }  // namespace
 
 int launch_dac(int dtype, const void* x, int M, int K, const TileTable& tt, int ir_mode,
@@ -330,6 +422,23 @@ int launch_dac(int dtype, const void* x, int M, int K, const TileTable& tt, int 
   // |code| <= max(inp_res, 1/inp_res)/2 + 1: the guard-free rint needs that below 2^22
   float states = inp_res > 0.0f ? (inp_res > 1.0f ? inp_res : 1.0f / inp_res) : 0.0f;
   int small_codes = states < 4.0e6f;
+  const int q = batched_q(tt, K);
+  if (dtype == AL_BF16 && q > 0 && aligned && codes == nullptr && inp_res > 0.0f && !no_rounding && small_codes &&
+      (ir_mode == AL_IR_DYNAMIC || ir_mode == AL_IR_STATIC) && aligned16(ir_rows)) {
+    const int64_t warps = (int64_t)M * ((tt.T + kBatchVecs / q - 1) / (kBatchVecs / q));
+    const unsigned blocks = seg_blocks(warps);
+    const uint16_t* xs = reinterpret_cast<const uint16_t*>(x);
+    const uint16_t* irs = reinterpret_cast<const uint16_t*>(ir_static);
+    uint16_t* xqs = reinterpret_cast<uint16_t*>(xq);
+    uint16_t* irr = reinterpret_cast<uint16_t*>(ir_rows);
+    switch (q) {
+      case 1: dac_batched_kernel<1><<<blocks, kWarpsPerBlock * 32, 0, s>>>(xs, M, K, tt.T, ir_mode, irs, inp_res, xqs, irr); break;
+      case 2: dac_batched_kernel<2><<<blocks, kWarpsPerBlock * 32, 0, s>>>(xs, M, K, tt.T, ir_mode, irs, inp_res, xqs, irr); break;
+      case 4: dac_batched_kernel<4><<<blocks, kWarpsPerBlock * 32, 0, s>>>(xs, M, K, tt.T, ir_mode, irs, inp_res, xqs, irr); break;
+      default: dac_batched_kernel<8><<<blocks, kWarpsPerBlock * 32, 0, s>>>(xs, M, K, tt.T, ir_mode, irs, inp_res, xqs, irr); break;
+    }
+    return check_launch("dac_batched");
+  }
   if (dtype == AL_F32)
     dac_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(x, M, K, tt, ir_mode, ir_static, inp_res, no_rounding, xq, ir_rows, codes, aligned, small_codes);
   else
@@ -356,14 +465,14 @@ int launch_weight_fused(int dtype, const void* w, int N, int K, const TileTable&
                         float* tile_max, int noise_type, float std_dev, const void* w_noise,
                         uint64_t seed, uint64_t offset, void* w_mod, cudaStream_t s) {
   ProfScope prof(AL_K_WEIGHT_MODIFY, s);
+  int64_t segs = (int64_t)N * tt.T;
+  int aligned = aligned16(w) && (w_mod == nullptr || aligned16(w_mod)) && (w_noise == nullptr || aligned16(w_noise));
   // tile_max[T] floats followed by T int32 flags (zero: the discretiser is off on this path)
   cudaError_t e = cudaMemsetAsync(tile_max, 0, 2 * sizeof(float) * tt.T, s);
   if (e != cudaSuccess) {
     set_error("weight_fused: memset: %s", cudaGetErrorString(e));
     return AL_ERR_CUDA;
   }
-  int64_t segs = (int64_t)N * tt.T;
-  int aligned = aligned16(w) && (w_mod == nullptr || aligned16(w_mod)) && (w_noise == nullptr || aligned16(w_noise));
   if (dtype == AL_F32)
     weight_fused_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, noise_type, std_dev, w_noise, seed, offset, w_mod, aligned);
   else
