@@ -134,9 +134,9 @@ def cpu_reference_run(steps: int, warmup: int, rows: int):
     t0 = time.perf_counter()
     O.linear_autograd(x.clone().requires_grad_(True), w, None, None, None, in_sizes, True, rpu).backward(g)
     first = time.perf_counter() - t0
-    budget_s = 150.0
-    if first * (warmup + steps) > budget_s:
-        rows = max(128, int(rows * budget_s / (first * (warmup + steps))) // 128 * 128)
+    limit_s = 150.0
+    if first * (warmup + steps) > limit_s:
+        rows = max(128, int(rows * limit_s / (first * (warmup + steps))) // 128 * 128)
         x, g = x[:rows].contiguous(), g[:rows].contiguous()
     times = []
     for it in range(warmup + steps):

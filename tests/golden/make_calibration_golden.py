@@ -2,7 +2,7 @@
 calibrated ranges next to the seeds that reproduce models and batches.
 
 Usage (needs the reference tree, which the test machines do not have):
-    python tests/golden/make_calibration_golden.py [/root/reference/src]
+    python tests/golden/make_calibration_golden.py <path to the reference's src directory>
 """
 import os
 import sys
@@ -15,7 +15,9 @@ import calibration_cases as CC  # noqa: E402
 
 
 def main():
-    ref_src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_calibration_golden.py <path to the reference's src directory>")
+    ref_src = sys.argv[1]
     sys.path.insert(0, ref_src)
     from aihwkit_lightning.inference import InputRangeCalibrationType, calibrate_input_ranges
     from aihwkit_lightning.nn.conversion import convert_to_analog

@@ -115,7 +115,9 @@ def run_oracle(ns, case, data):
 
 
 def main():
-    ref_src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path to the reference's src directory>")
+    ref_src = sys.argv[1]
     sys.path.insert(0, ref_src)
     import aihwkit_lightning.nn as ref_nn
     import aihwkit_lightning.simulator.configs as ref_cfg
