@@ -569,6 +569,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     const bool no_round = kFixed ? false : ep.no_rounding != 0;
     const bool small_codes = kFixed ? true : p.small_adc_codes != 0;
     const bool per_channel = kFixed ? false : (ep.w_amax != nullptr && (ep.noise_pc || ep.bound_pc));
+    // Output noise with nothing non-linear between the tiles (no ADC, no clamp): the T independent
+    // Gaussian terms s_t * xi_t of an output add up to one Gaussian of variance sum_t s_t^2, so
+    // one draw per output at the last tile replaces T draws -- same distribution up to the bf16
+    // rounding of the partial sums, an eighth of the generator work on an 8-tile layer.  Replayed
+    // noise (parity runs) never takes this route: it is applied tile by tile as given.
+    constexpr bool kMergedNoise = kFixed && MODE == 1;
+    float noise_var = 0.0f;
     TileEpilogueCfg cfg;
     cfg.has_noise = ep.has_noise; cfg.has_bound = ep.has_bound; cfg.has_adc = ep.has_adc;
     cfg.no_rounding = ep.no_rounding; cfg.noise_coef = ep.noise_coef; cfg.out_bound = ep.out_bound;
@@ -591,7 +598,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           else if (ep.ir_mode == AL_IR_STATIC) ir = Elem<kBF16>::load(ep.ir_rows, t);
         }
         const float t_max = ep.w_tile_max ? ep.w_tile_max[t] : 0.0f;
-        const float sc = rnd<RD>(fmul(t_max, rnd<RD>(fmul(ep.noise_coef, ir))));
+        float sc = rnd<RD>(fmul(t_max, rnd<RD>(fmul(ep.noise_coef, ir))));
+        bool noise_now = has_noise;
+        if (kMergedNoise) {
+          noise_var = t == 0 ? sc * sc : fmaf(sc, sc, noise_var);
+          noise_now = t == T - 1;
+          sc = sqrtf(noise_var);
+        }
         const float bound = rnd<RD>(fmul(rnd<RD>(fmul(ir, ep.out_bound)), t_max));
         const float step = has_adc ? quant_step<RD>(bound, ep.out_res) : 1.0f;
         const float stepc = step < kTiny ? kTiny : step;
@@ -640,7 +653,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           }
           tmem_wait_ld();
           float z[16];
-          if (has_noise) {
+          if (noise_now) {
 #pragma unroll
             for (int g8 = 0; g8 < 2; ++g8) {
               const int nq = nh + g8 * 8;
@@ -668,7 +681,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             for (int pr = 0; pr < 8; ++pr) {
               // element 2*pr in the low half, 2*pr+1 in the high half
               __nv_bfloat162 o2 = __floats2bfloat162_rn(__uint_as_float(accr[2 * pr]), __uint_as_float(accr[2 * pr + 1]));
-              if (has_noise) {
+              if (noise_now) {
                 const __nv_bfloat162 z2 = __floats2bfloat162_rn(z[2 * pr], z[2 * pr + 1]);
                 o2 = __hadd2_rn(o2, __hmul2_rn(sc2, z2));
               }

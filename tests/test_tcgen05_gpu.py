@@ -183,3 +183,45 @@ def test_order_independent_problem_is_bit_exact(variant):
         assert torch.equal(out.detach().cpu(), rec.out), f"{engine}: forward differs"
         assert torch.equal(xin.grad.cpu(), grads["grad_x"]), f"{engine}: grad_x differs"
         assert torch.equal(layer.weight.grad.cpu(), grads["grad_w"]), f"{engine}: grad_w differs"
+
+
+@pytest.mark.parametrize("engine", ["tcgen05_single", "tcgen05_pair"])
+def test_output_noise_without_adc_is_one_gaussian_per_output(engine):
+    """No ADC and no clamp: the tile terms s_t * xi_t of an output are drawn as one Gaussian of the
+    summed variance.  Mean, variance (per row: it depends on the row's input ranges), Gaussian shape
+    and independence across neighbouring outputs and across calls."""
+    import math
+
+    from aihwkit_lightning_b200.nn import AnalogLinear
+    from aihwkit_lightning_b200.nn import functional as F
+    from util import NS
+
+    case = dict(C.DEFAULTS)
+    case.update(ir_dynamic=True, out_noise=0.1, max_input_size=128, inp_res=254.0)
+    rpu = C.build_rpu_config(NS, case)
+    torch.manual_seed(0)
+    k, n, m, t_count = 512, 512, 512, 4
+    layer = AnalogLinear(k, n, bias=False, rpu_config=rpu).to(device="cuda", dtype=torch.bfloat16)
+    x = (torch.randn(m, k, device="cuda") * torch.linspace(0.5, 2.0, m, device="cuda")[:, None]).bfloat16()
+    with F.operator_settings(engine=engine):
+        layer.eval()
+        clean = layer(x).float()
+        layer.train()
+        noisy1 = layer(x).float()
+        noisy2 = layer(x).float()
+    assert device_error() == (0, 0)
+    w, xs = layer.weight.detach().float().cpu(), x.float().cpu()
+    var = torch.zeros(m)
+    for t in range(t_count):
+        wmax = w[:, 128 * t:128 * (t + 1)].abs().max()
+        ir = xs[:, 128 * t:128 * (t + 1)].abs().amax(1)
+        var += (wmax * 0.1 / math.sqrt(t_count) * ir) ** 2
+    z1 = (noisy1 - clean).cpu() / var.sqrt()[:, None]
+    z2 = (noisy2 - clean).cpu() / var.sqrt()[:, None]
+    assert abs(z1.mean().item()) < 0.02
+    assert abs(z1.std().item() - 1.0) < 0.03
+    assert (z1.std(dim=1) - 1.0).abs().max().item() < 0.2          # every row has its own scale
+    kurt = (z1 ** 4).mean().item() / (z1 ** 2).mean().item() ** 2
+    assert abs(kurt - 3.0) < 0.15
+    assert abs((z1[:, 1:] * z1[:, :-1]).mean().item()) < 0.02       # neighbours
+    assert abs((z1 * z2).mean().item()) < 0.02                      # calls
