@@ -35,6 +35,8 @@ SHAPES = [
     ("bf16_dynamic_adc_noise", dict(in_shape=(128, 256), out_features=768, max_input_size=128, out_bound=10.0)),
     ("bf16_dynamic_adc_noise", dict(in_shape=(128, 256), out_features=1024, max_input_size=128, out_bound=10.0,
                                     out_noise=0.0, noise_type="None")),
+    # an all-zero input row: input range 0, DAC and ADC steps clamped to the smallest normal number
+    ("bf16_dynamic_adc_noise", dict(in_shape=(256, 512), out_features=256, max_input_size=256, zero_row=3)),
     # heavy ADC clamping: most rows of the staged gradient blocks have many blocked entries
     ("bf16_dynamic_adc_noise", dict(in_shape=(384, 512), out_features=392, max_input_size=128, out_bound=0.3)),
     ("bf16_static_adc", dict(in_shape=(200, 512), out_features=264, max_input_size=256, ir_init_value=2.0,
