@@ -70,3 +70,34 @@ def test_few_rows_path_is_not_taken_under_autograd():
     launches = {k: v[0] for k, v in _lib.profile_read(True).items() if v[0]}
     assert launches.get("fwd_gemm") == 1 and launches.get("dgrad_gemm") == 1
     assert x.grad is not None and torch.isfinite(x.grad.float()).all()
+
+
+@pytest.mark.parametrize("rows", [1, 64])
+def test_forward_can_be_captured_in_a_cuda_graph(rows):
+    """Inference loops replay the layer from a CUDA graph: nothing in the forward may synchronise,
+    allocate outside PyTorch's allocator or depend on host state that changes between replays.
+    rows = 1 takes the few-rows kernels, rows = 64 the DAC / weight pre-pass / tcgen05 kernels."""
+    from aihwkit_lightning_b200.nn import AnalogLinear
+
+    case = dict(C.DEFAULTS)
+    case.update(dtype="bf16", ir_dynamic=True, out_bound=10.0, out_res=254.0, max_input_size=256)
+    rpu = C.build_rpu_config(NS, case)
+    torch.manual_seed(0)
+    layer = AnalogLinear(512, 256, bias=True, rpu_config=rpu).to(device="cuda", dtype=torch.bfloat16).eval()
+    static_x = torch.randn(rows, 512, device="cuda").bfloat16()
+    with torch.no_grad():
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                layer(static_x)                       # warm-up outside the capture
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_out = layer(static_x)
+        for seed in (1, 2):
+            new_x = torch.randn(rows, 512, device="cuda", generator=torch.Generator("cuda").manual_seed(seed)).bfloat16()
+            static_x.copy_(new_x)
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(static_out, layer(new_x))
