@@ -18,7 +18,8 @@ SOURCES = [
     "reduce_kernels.cu",
     "prepass_kernels.cu",
     "gemm_simt.cu",
-    "gemm_tcgen05.cu",
+    "gemm_tcgen05_fwd.cu",
+    "gemm_tcgen05_bwd.cu",
     "gemm_smallm.cu",
     "backward_kernels.cu",
     "conv_kernels.cu",

@@ -1,0 +1,810 @@
+// Backward GEMMs of the analog linear path on the Blackwell tensor cores (sm_100a):
+//   C[i, lo_t + j] = sum_l (g * keep_t)(i,l) * B(l, lo_t + j)
+// dgrad (C = grad_x, A = g, B = w_mod) and wgrad (C = grad_w, A = g^T, B = xq) in one template.
+// TMA brings the operands into shared memory (the ones that are contiguous along the output
+// dimension as MN-major tiles), groups of four warps apply the ADC clamp mask of the analog tile
+// to the staged gradient tile, tcgen05.mma accumulates in tensor memory, four warps drain it.
+// Large problems run on CTA pairs (256 x 256 blocks, cta_group::2, six stages), small ones on
+// single CTAs (128 x 256 blocks, four stages).
+#include "tcgen05_common.cuh"
+
+namespace al {
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// backward (dgrad / wgrad)
+// ---------------------------------------------------------------------------------------------
+struct BwdTcParams {
+  int32_t I;           // rows of C (M for dgrad, N for wgrad)
+  int32_t L;           // reduction length (N for dgrad, M for wgrad)
+  int32_t K;           // row stride of C
+  int32_t M;           // rows of the mask
+  int32_t T;           // analog tiles that carry their own mask (1 when there is no mask)
+  int32_t tile_w;      // width of a tile (K when there is no mask)
+  int32_t num_ib, num_jb, lsteps;
+  const uint32_t* keep_mask;
+  int32_t mask_words;
+  void* c_out;
+};
+
+// A heavily clamped 128-byte row of a staged A tile: rewrite its 16-byte chunks under the
+// expanded keep mask (bit j = keep element j).
+__device__ __forceinline__ void rewrite_row_masked(uint32_t row_addr, int sw, uint64_t keep) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint32_t kb = (uint32_t)(keep >> (8 * c)) & 0xffu;
+    if (kb == 0xffu) continue;
+    const uint32_t addr = row_addr + (uint32_t)((c ^ sw) << 4);
+    uint32_t v[4];
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr) : "memory");
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t two = (kb >> (2 * j)) & 3u;
+      v[j] &= (two & 1u) * 0x0000ffffu + (two >> 1) * 0xffff0000u;
+    }
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                 "r"(v[3]) : "memory");
+  }
+}
+
+template <bool WGRAD>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+              const BwdTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* stage_base = align_1024(smem_raw);
+  Barriers* bars = reinterpret_cast<Barriers*>(stage_base + B_STAGES * B_STAGE_BYTES);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool masked = p.keep_mask != nullptr;
+  const int num_work = p.num_ib * p.T * p.num_jb;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < B_STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->ready[s], B_XFORM_THREADS / 32);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], B_EPI_WARPS);
+    }
+    mbar_init(&bars->mma_done, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc(&bars->tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer ------------------------------------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const int ib = w / (p.T * p.num_jb);
+        const int rem = w % (p.T * p.num_jb);
+        const int t = rem / p.num_jb, jb = rem % p.num_jb;
+        const int j0 = t * p.tile_w + jb * B_BN;
+        for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+          const int s = it % B_STAGES;
+          const uint32_t ph = (it / B_STAGES) & 1u;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag)) {
+            raise_error(kErrProducer, abort_flag);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = stage_base + s * B_STAGE_BYTES;
+          uint8_t* sb = sa + B_A_BYTES;
+          const int l0 = ls * BK;
+          mbar_expect_tx(&bars->full[s], B_STAGE_BYTES);
+          if (WGRAD) {
+            // A = g^T: two MN-major boxes [64 rows of m] x [64 n]
+            tma_load_2d(sa, &map_a, &bars->full[s], ib * BM, l0);
+            tma_load_2d(sa + B_BOX_BYTES, &map_a, &bars->full[s], ib * BM + 64, l0);
+          } else {
+            // A = g: K-major [128 rows of m] x [64 n]
+            tma_load_2d(sa, &map_a, &bars->full[s], l0, ib * BM);
+          }
+#pragma unroll
+          for (int c = 0; c < B_BN / 64; ++c)
+            tma_load_2d(sb + c * B_BOX_BYTES, &map_b, &bars->full[s], j0 + c * 64, l0);
+        }
+      }
+      const uint32_t n_back = it < (uint32_t)B_STAGES ? it : (uint32_t)B_STAGES;
+      for (uint32_t j = it - n_back; j < it; ++j) {
+        const int s = j % B_STAGES;
+        const uint32_t ph = (j / B_STAGES) & 1u;
+        uint64_t t0 = globaltimer_ns();
+        while (!mbar_try(&bars->full[s], ph)) {
+          if (globaltimer_ns() - t0 > kTimeoutNs) {
+            raise_error(kErrDrain, abort_flag);
+            break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer --------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, B_BN, WGRAD ? 1 : 0, 1);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++acc_it) {
+        const int b = acc_it & 1u;
+        const uint32_t aph = (acc_it >> 1) & 1u;
+        if (!mbar_wait(&bars->acc_empty[b], aph ^ 1u, abort_flag)) {
+          raise_error(kErrMma, abort_flag);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * B_BN);
+        for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+          const int s = it % B_STAGES;
+          const uint32_t ph = (it / B_STAGES) & 1u;
+          // the transform warps vouch for a stage on `ready` before its copy has landed when
+          // the stage has nothing to zero, so both barriers gate the MMA
+          if (!mbar_wait(&bars->full[s], ph, abort_flag) ||
+              (masked && !mbar_wait(&bars->ready[s], ph, abort_flag))) {
+            raise_error(kErrMma, abort_flag);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stage_base + s * B_STAGE_BYTES);
+          const uint32_t sb = sa + B_A_BYTES;
+          const uint64_t da = WGRAD ? desc_mn_major(sa, B_BOX_BYTES) : desc_k_major(sa);
+          const uint64_t db = desc_mn_major(sb, B_BOX_BYTES);
+          // one MMA consumes 16 k: 32 bytes along a K-major row, 16 rows (2048 bytes) of an MN-major box
+          constexpr uint64_t a_step = WGRAD ? (2048u >> 4) : (32u >> 4);
+          constexpr uint64_t b_step = 2048u >> 4;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4)
+            umma_bf16(d_tmem, da + a_step * k4, db + b_step * k4, idesc, (ls | k4) != 0 ? 1u : 0u);
+          umma_commit(&bars->empty[s]);
+        }
+        if (ok) umma_commit(&bars->acc_full[b]);
+      }
+      umma_commit(&bars->mma_done);
+      uint64_t t0 = globaltimer_ns();
+      while (!mbar_try(&bars->mma_done, 0)) {
+        if (globaltimer_ns() - t0 > kTimeoutNs) {
+          raise_error(kErrDrain, abort_flag);
+          break;
+        }
+      }
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ---- epilogue: TMEM -> bf16 -> global ------------------------------------------------
+    const int quad = warp & 3;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++acc_it) {
+      const int ib = w / (p.T * p.num_jb);
+      const int rem = w % (p.T * p.num_jb);
+      const int t = rem / p.num_jb, jb = rem % p.num_jb;
+      const int j0 = t * p.tile_w + jb * B_BN;
+      const int j_end = min((t + 1) * p.tile_w, p.K);
+      const int i = ib * BM + quad * 32 + lane;
+      const int b = acc_it & 1u;
+      const uint32_t aph = (acc_it >> 1) & 1u;
+      if (!mbar_wait(&bars->acc_full[b], aph, abort_flag)) {
+        if (lane == 0) raise_error(kErrEpilogue, abort_flag);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint16_t* dst_row = reinterpret_cast<uint16_t*>(p.c_out) + (int64_t)i * p.K;
+#pragma unroll 1
+      for (int c = 0; c < B_BN / 32; ++c) {
+        const int jc = j0 + c * 32;
+        if (jc >= j_end) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(tmem_base + lane_base + (uint32_t)(b * B_BN + c * 32), r);
+        tmem_wait_ld();
+        if (i < p.I) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (jc + v * 8 < j_end) {
+              uint4 pk = make_uint4(
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1])),
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3])),
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5])),
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7])));
+              *reinterpret_cast<uint4*>(dst_row + jc + v * 8) = pk;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty[b]);
+    }
+  } else if (warp >= 8 && masked && (int)blockIdx.x < num_work) {
+    // ---- mask transform: zero the gradient entries the tile's ADC clamp blocked ---------
+    // B_XFORM_GROUPS groups of 128 threads take the stage-iterations round robin, so that
+    // the fix-up of consecutive stages overlaps.  Within a group thread r owns one 128-byte
+    // row of the staged A tile and the two mask words that cover it.
+    const int grp = (warp - 8) >> 2;
+    const int r = threadIdx.x - (8 + 4 * grp) * 32;  // 0..127
+    const int row_in_box = WGRAD ? (r & 63) : r;
+    const int box = WGRAD ? (r >> 6) : 0;
+    const int total = ((num_work - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * p.lsteps;
+    // Mask words are [T][word][M].  The fetch stream walks (work item, l-step) with a cursor
+    // instead of dividing per turn, and its loads are unconditional: indices past an edge
+    // are clamped to the last valid row / word.  What a clamped word may zero lies in rows or
+    // columns that the TMA copy filled with zeros anyway, and a load that nothing selects on
+    // does not stall the warp at the point of issue.
+    const int m_last = p.M - 1, w_last = p.mask_words - 1;
+    int f_w = (int)blockIdx.x + (grp / p.lsteps) * (int)gridDim.x, f_ls = grp % p.lsteps;
+    const uint32_t* f_lo = p.keep_mask;  // dgrad: word 0 of (t, row); wgrad: row 0 of (t, word)
+    const uint32_t* f_hi = p.keep_mask;
+    auto seek_item = [&]() {
+      if (f_w >= num_work) return;  // past the end: keep pointing at valid memory
+      const int ib = f_w / (p.T * p.num_jb);
+      const int t = (f_w % (p.T * p.num_jb)) / p.num_jb;
+      const uint32_t* tile = p.keep_mask + (int64_t)t * p.mask_words * p.M;
+      if (WGRAD) {
+        const int w0 = (ib * BM + box * 64) >> 5;
+        f_lo = tile + (int64_t)min(w0, w_last) * p.M;
+        f_hi = tile + (int64_t)min(w0 + 1, w_last) * p.M;
+      } else {
+        f_lo = tile + min(ib * BM + r, m_last);
+        f_hi = f_lo;
+      }
+    };
+    seek_item();
+    auto fetch = [&](uint32_t* lo, uint32_t* hi) {
+      if (WGRAD) {
+        const int m = min(f_ls * BK + row_in_box, m_last);
+        *lo = f_lo[m];
+        *hi = f_hi[m];
+      } else {
+        *lo = f_lo[(int64_t)min(2 * f_ls, w_last) * p.M];
+        *hi = f_hi[(int64_t)min(2 * f_ls + 1, w_last) * p.M];
+      }
+      f_ls += B_XFORM_GROUPS;
+      if (f_ls >= p.lsteps) {
+        do {
+          f_ls -= p.lsteps;
+          f_w += (int)gridDim.x;
+        } while (f_ls >= p.lsteps);
+        seek_item();
+      }
+    };
+    constexpr int kScanLimit = 6;  // blocked entries per row up to which single stores beat a rewrite
+    uint8_t* const row_base = stage_base + box * B_BOX_BYTES + row_in_box * 128;
+    const int sw = r & 7;  // 128-byte swizzle: 16-byte chunk index is XORed with row % 8
+    // one stage-iteration of this thread's row; false = the wait gave up
+    auto process = [&](int it, uint32_t lo, uint32_t hi) -> bool {
+      const int s = it % B_STAGES;
+      const uint32_t ph = ((uint32_t)it / B_STAGES) & 1u;
+      uint64_t zeros = ~((uint64_t)lo | ((uint64_t)hi << 32));
+      // A parity wait tells phases apart only one phase deep, and a warp that had nothing to
+      // zero on the stage's previous use never looked at `full` then: first wait until that
+      // previous use has been consumed (normally long past), which puts `full` and `ready`
+      // of this stage in the phase of this use.
+      bool okw = true;
+      if (lane == 0) {
+        okw = mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag);
+        if (!okw) raise_error(kErrTransform, abort_flag);
+      }
+      if (!__shfl_sync(0xffffffffu, okw, 0)) return false;
+      if (!__any_sync(0xffffffffu, zeros != 0ull)) {
+        // Nothing to zero in this warp's rows: it vouches for the stage before the copy has
+        // landed, which takes this hand-off off the TMA -> MMA critical path, and it
+        // publishes no data, so the arrival is a relaxed one.
+        if (lane == 0) mbar_arrive_relaxed(&bars->ready[s]);
+        return true;
+      }
+      if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
+        raise_error(kErrTransform, abort_flag);
+        return false;
+      }
+      if (zeros != 0ull) {
+        const uint32_t row_addr = smem_u32(row_base + s * B_STAGE_BYTES);
+        if (__popcll(zeros) <= kScanLimit) {
+          // one 2-byte store of zero per blocked element (typically one or two per row)
+          while (zeros != 0ull) {
+            const int pos = __ffsll((long long)zeros) - 1;  // n - n0 of the blocked element
+            zeros &= zeros - 1ull;
+            const uint32_t addr = row_addr + (uint32_t)((((pos >> 3) ^ sw) << 4) + ((pos & 7) << 1));
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)0) : "memory");
+          }
+        } else {
+          rewrite_row_masked(row_addr, sw, ~zeros);
+        }
+        fence_proxy_async_smem();
+      }
+      // one arrival per warp: 128 arrivals on one mbarrier would serialise in shared memory
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->ready[s]);
+      return true;
+    };
+    // The mask words run kAhead turns ahead of their use in a ring of registers (the loop is
+    // unrolled by the ring size so that every slot is a fixed register): a turn never waits
+    // for a load it issued itself.
+    constexpr int kRing = 4, kAhead = 3;
+    uint32_t lo[kRing], hi[kRing];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) fetch(&lo[u], &hi[u]);
+    bool ok = true;
+    for (int base = grp; base < total && ok; base += kRing * B_XFORM_GROUPS) {
+#pragma unroll
+      for (int u = 0; u < kRing; ++u) {
+        const int it = base + u * B_XFORM_GROUPS;
+        if (it < total && ok) {
+          fetch(&lo[(u + kAhead) % kRing], &hi[(u + kAhead) % kRing]);
+          ok = process(it, lo[u], hi[u]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward (dgrad / wgrad) on CTA pairs
+// ---------------------------------------------------------------------------------------------
+// Same GEMM as bwd_tc_kernel with one tcgen05.mma.cta_group::2 of 256 x 256 x 16 per k-step.
+// CTA `rank` of the pair owns rows [256 ib + 128 rank, +128) of C: it stages those rows of A and
+// columns [128 rank, +128) of the B block, holds its half of the accumulator in its own tensor
+// memory and writes its rows of C.  Each CTA therefore stages 32 KiB per 64-deep k-step instead of
+// 48 KiB, which buys two more pipeline stages and takes a third off the L2 -> shared-memory
+// traffic per flop.
+//
+// Barriers.  `empty`, `acc_full`: one copy per CTA, signalled in both by the leader's multicast
+// commit.  `acc_empty`, `ready`, `mma_done`: used in the leader (rank 0) only; the other CTA
+// arrives on them through the cluster address.  `full`: without a mask the leader's barrier
+// collects the bytes of both CTAs' copies and gates the MMA; with a mask each CTA's copies
+// complete on its own barrier, its transform warps fix the A tile up and then vouch for the
+// stage on the leader's `ready`, which gates the MMA.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    if (mbar_try_cluster(bar, parity)) return true;
+    if ((spin & 31u) == 31u) {
+      if (*abort_flag) return false;
+      uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kTimeoutNs) return false;
+    }
+  }
+}
+
+template <bool WGRAD>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kBwdThreads, 1)
+bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const BwdTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* stage_base = align_1024(smem_raw);
+  Barriers* bars = reinterpret_cast<Barriers*>(stage_base + P_STAGES * P_STAGE_BYTES);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const bool masked = p.keep_mask != nullptr;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int num_work = p.num_ib * p.T * p.num_jb;  // num_ib counts 256-row blocks here
+  const int row_off = (int)rank * BM;               // this CTA's rows inside the pair's block
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->ready[s], 2 * (B_XFORM_THREADS / 32));
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], 2 * B_EPI_WARPS);
+    }
+    mbar_init(&bars->mma_done, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc_pair(&bars->tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer (both CTAs) --------------------------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = pair; w < num_work && ok; w += n_pairs) {
+        const int ib = w / (p.T * p.num_jb);
+        const int rem = w % (p.T * p.num_jb);
+        const int t = rem / p.num_jb, jb = rem % p.num_jb;
+        const int i0 = ib * (2 * BM) + row_off;
+        const int j0 = t * p.tile_w + jb * P_BN + (int)rank * P_BN_CTA;
+        for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+          const int s = it % P_STAGES;
+          const uint32_t ph = (it / P_STAGES) & 1u;
+          if (!mbar_wait_cluster(&bars->empty[s], ph ^ 1u, abort_flag)) {
+            raise_error(kErrProducer, abort_flag);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = stage_base + s * P_STAGE_BYTES;
+          uint8_t* sb = sa + P_A_BYTES;
+          const int l0 = ls * BK;
+          uint32_t bar;
+          if (masked) {
+            mbar_expect_tx(&bars->full[s], P_STAGE_BYTES);
+            bar = smem_u32(&bars->full[s]);
+          } else {
+            if (leader) mbar_expect_tx(&bars->full[s], 2 * P_STAGE_BYTES);
+            bar = mapa_u32(smem_u32(&bars->full[s]), 0);
+          }
+          if (WGRAD) {
+            tma_load_2d_pair(sa, &map_a, bar, i0, l0);
+            tma_load_2d_pair(sa + B_BOX_BYTES, &map_a, bar, i0 + 64, l0);
+          } else {
+            tma_load_2d_pair(sa, &map_a, bar, l0, i0);
+          }
+#pragma unroll
+          for (int c = 0; c < P_BN_CTA / 64; ++c)
+            tma_load_2d_pair(sb + c * B_BOX_BYTES, &map_b, bar, j0 + c * 64, l0);
+        }
+      }
+      // drain: copies that complete on this CTA's own barrier must have landed before it exits;
+      // copies that complete on the leader's barrier are covered by the leader's drain and the
+      // cluster barrier at the end
+      if (masked || leader) {
+        const uint32_t n_back = it < (uint32_t)P_STAGES ? it : (uint32_t)P_STAGES;
+        for (uint32_t j = it - n_back; j < it; ++j) {
+          const int s = j % P_STAGES;
+          const uint32_t ph = (j / P_STAGES) & 1u;
+          uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_cluster(&bars->full[s], ph)) {
+            if (globaltimer_ns() - t0 > kTimeoutNs) {
+              raise_error(kErrDrain, abort_flag);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer (leader only) --------------------------------------------------------
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc(2 * BM, P_BN, WGRAD ? 1 : 0, 1);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int w = pair; w < num_work && ok; w += n_pairs, ++acc_it) {
+        const int b = acc_it & 1u;
+        const uint32_t aph = (acc_it >> 1) & 1u;
+        if (!mbar_wait_cluster(&bars->acc_empty[b], aph ^ 1u, abort_flag)) {
+          raise_error(kErrMma, abort_flag);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * P_BN);
+        for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+          const int s = it % P_STAGES;
+          const uint32_t ph = (it / P_STAGES) & 1u;
+          if (!mbar_wait_cluster(masked ? &bars->ready[s] : &bars->full[s], ph, abort_flag)) {
+            raise_error(kErrMma, abort_flag);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stage_base + s * P_STAGE_BYTES);
+          const uint32_t sb = sa + P_A_BYTES;
+          const uint64_t da = WGRAD ? desc_mn_major(sa, B_BOX_BYTES) : desc_k_major(sa);
+          const uint64_t db = desc_mn_major(sb, B_BOX_BYTES);
+          constexpr uint64_t a_step = WGRAD ? (2048u >> 4) : (32u >> 4);
+          constexpr uint64_t b_step = 2048u >> 4;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4)
+            umma_bf16_pair(d_tmem, da + a_step * k4, db + b_step * k4, idesc, (ls | k4) != 0 ? 1u : 0u);
+          umma_commit_pair(&bars->empty[s], 3);  // frees the stage in both CTAs
+        }
+        if (ok) umma_commit_pair(&bars->acc_full[b], 3);
+      }
+      umma_commit_pair(&bars->mma_done, 1);
+      uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_cluster(&bars->mma_done, 0)) {
+        if (globaltimer_ns() - t0 > kTimeoutNs) {
+          raise_error(kErrDrain, abort_flag);
+          break;
+        }
+      }
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ---- epilogue (both CTAs): own half of the accumulator -> bf16 -> own rows of C --------
+    const int quad = warp & 3;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int w = pair; w < num_work && ok; w += n_pairs, ++acc_it) {
+      const int ib = w / (p.T * p.num_jb);
+      const int rem = w % (p.T * p.num_jb);
+      const int t = rem / p.num_jb, jb = rem % p.num_jb;
+      const int j0 = t * p.tile_w + jb * P_BN;
+      const int j_end = min((t + 1) * p.tile_w, p.K);
+      const int i = ib * (2 * BM) + row_off + quad * 32 + lane;
+      const int b = acc_it & 1u;
+      const uint32_t aph = (acc_it >> 1) & 1u;
+      if (!mbar_wait_cluster(&bars->acc_full[b], aph, abort_flag)) {
+        if (lane == 0) raise_error(kErrEpilogue, abort_flag);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint16_t* dst_row = reinterpret_cast<uint16_t*>(p.c_out) + (int64_t)i * p.K;
+#pragma unroll 1
+      for (int c = 0; c < P_BN / 32; ++c) {
+        const int jc = j0 + c * 32;
+        if (jc >= j_end) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(tmem_base + lane_base + (uint32_t)(b * P_BN + c * 32), r);
+        tmem_wait_ld();
+        if (i < p.I) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (jc + v * 8 < j_end) {
+              uint4 pk = make_uint4(
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1])),
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3])),
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5])),
+                  pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7])));
+              *reinterpret_cast<uint4*>(dst_row + jc + v * 8) = pk;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->acc_empty[b]), 0));
+    }
+  } else if (warp >= 8 && masked && pair < num_work) {
+    // ---- mask transform (both CTAs, own A tile): see bwd_tc_kernel -------------------------
+    const int grp = (warp - 8) >> 2;
+    const int r = threadIdx.x - (8 + 4 * grp) * 32;  // 0..127
+    const int row_in_box = WGRAD ? (r & 63) : r;
+    const int box = WGRAD ? (r >> 6) : 0;
+    const int total = ((num_work - pair + n_pairs - 1) / n_pairs) * p.lsteps;
+    const int m_last = p.M - 1, w_last = p.mask_words - 1;
+    int f_w = pair + (grp / p.lsteps) * n_pairs, f_ls = grp % p.lsteps;
+    const uint32_t* f_lo = p.keep_mask;
+    const uint32_t* f_hi = p.keep_mask;
+    auto seek_item = [&]() {
+      if (f_w >= num_work) return;
+      const int ib = f_w / (p.T * p.num_jb);
+      const int t = (f_w % (p.T * p.num_jb)) / p.num_jb;
+      const int i0 = ib * (2 * BM) + row_off;
+      const uint32_t* tile = p.keep_mask + (int64_t)t * p.mask_words * p.M;
+      if (WGRAD) {
+        const int w0 = (i0 + box * 64) >> 5;
+        f_lo = tile + (int64_t)min(w0, w_last) * p.M;
+        f_hi = tile + (int64_t)min(w0 + 1, w_last) * p.M;
+      } else {
+        f_lo = tile + min(i0 + r, m_last);
+        f_hi = f_lo;
+      }
+    };
+    seek_item();
+    auto fetch = [&](uint32_t* lo, uint32_t* hi) {
+      if (WGRAD) {
+        const int m = min(f_ls * BK + row_in_box, m_last);
+        *lo = f_lo[m];
+        *hi = f_hi[m];
+      } else {
+        *lo = f_lo[(int64_t)min(2 * f_ls, w_last) * p.M];
+        *hi = f_hi[(int64_t)min(2 * f_ls + 1, w_last) * p.M];
+      }
+      f_ls += B_XFORM_GROUPS;
+      if (f_ls >= p.lsteps) {
+        do {
+          f_ls -= p.lsteps;
+          f_w += n_pairs;
+        } while (f_ls >= p.lsteps);
+        seek_item();
+      }
+    };
+    constexpr int kScanLimit = 6;
+    uint8_t* const row_base = stage_base + box * B_BOX_BYTES + row_in_box * 128;
+    const int sw = r & 7;
+    auto process = [&](int it, uint32_t lo, uint32_t hi) -> bool {
+      const int s = it % P_STAGES;
+      const uint32_t ph = ((uint32_t)it / P_STAGES) & 1u;
+      // the MMA waits on `ready` alone, so every warp waits for its CTA's copy before it vouches
+      if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
+        raise_error(kErrTransform, abort_flag);
+        return false;
+      }
+      uint64_t zeros = ~((uint64_t)lo | ((uint64_t)hi << 32));
+      if (zeros != 0ull) {
+        const uint32_t row_addr = smem_u32(row_base + s * P_STAGE_BYTES);
+        if (__popcll(zeros) <= kScanLimit) {
+          while (zeros != 0ull) {
+            const int pos = __ffsll((long long)zeros) - 1;
+            zeros &= zeros - 1ull;
+            const uint32_t addr = row_addr + (uint32_t)((((pos >> 3) ^ sw) << 4) + ((pos & 7) << 1));
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)0) : "memory");
+          }
+        } else {
+          rewrite_row_masked(row_addr, sw, ~zeros);
+        }
+        fence_proxy_async_smem();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->ready[s]), 0));
+      return true;
+    };
+    constexpr int kRing = 4, kAhead = 3;
+    uint32_t lo[kRing], hi[kRing];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) fetch(&lo[u], &hi[u]);
+    bool ok = true;
+    for (int base = grp; base < total && ok; base += kRing * B_XFORM_GROUPS) {
+#pragma unroll
+      for (int u = 0; u < kRing; ++u) {
+        const int it = base + u * B_XFORM_GROUPS;
+        if (it < total && ok) {
+          fetch(&lo[(u + kAhead) % kRing], &hi[(u + kAhead) % kRing]);
+          ok = process(it, lo[u], hi[u]);
+        }
+      }
+    }
+  }
+
+  // nothing of this CTA's shared or tensor memory may go while the peer can still signal or
+  // read it: both CTAs meet before the pair's tensor memory is released
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
+}
+
+}  // namespace
+
+bool tc_backward_supported(const AlDesc& d, const TileTable& tt) { return tc_shape_ok(d, tt); }
+
+// How many 2-CTA clusters of the pair kernel the device runs at once (0: cannot run them).
+static int max_pairs(bool wgrad) {
+  static int cached[2] = {-1, -1};
+  int& n = cached[wgrad ? 1 : 0];
+  if (n >= 0) return n;
+  n = 0;
+  if ((wgrad ? ensure_smem(bwd_tc_pair_kernel<true>, P_SMEM) : ensure_smem(bwd_tc_pair_kernel<false>, P_SMEM)) != AL_OK)
+    return n;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * sm_count());
+  cfg.blockDim = dim3(kBwdThreads);
+  cfg.dynamicSmemBytes = P_SMEM;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  cudaError_t e = wgrad ? cudaOccupancyMaxActiveClusters(&clusters, bwd_tc_pair_kernel<true>, &cfg)
+                        : cudaOccupancyMaxActiveClusters(&clusters, bwd_tc_pair_kernel<false>, &cfg);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return n;
+  }
+  n = clusters;
+  return n;
+}
+static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint32_t* keep_mask,
+                         int mask_words, int M, int K, int N, const TileTable& tt, int pairing, void* c_out,
+                         cudaStream_t s) {
+  int w = 0;
+  if (!uniform_tiles(tt, &w) || !aligned16(g) || !aligned16(b_op) || !aligned16(c_out)) {
+    set_error("bwd_tc: operands must be 16-byte aligned with equally wide tiles");
+    return AL_ERR_UNSUPPORTED;
+  }
+  BwdTcParams p;
+  p.I = wgrad ? N : M;
+  p.L = wgrad ? M : N;
+  p.K = K;
+  p.M = M;
+  p.T = tt.T;
+  p.tile_w = w;
+  p.num_ib = (p.I + BM - 1) / BM;
+  p.num_jb = (w + B_BN - 1) / B_BN;
+  p.lsteps = (p.L + BK - 1) / BK;
+  p.keep_mask = keep_mask;
+  p.mask_words = mask_words;
+  p.c_out = c_out;
+  int rc = wgrad ? ensure_smem(bwd_tc_kernel<true>, B_SMEM) : ensure_smem(bwd_tc_kernel<false>, B_SMEM);
+  if (rc) return rc;
+  CUtensorMap map_a, map_b;
+  {
+    // g [M,N]: dims innermost first {N, M}
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+    uint64_t strides[1] = {(uint64_t)N * 2};
+    uint32_t box_k[2] = {BK, BM};   // dgrad: 64 n (reduction) x 128 m
+    uint32_t box_mn[2] = {64, BK};  // wgrad: 64 n (MMA-M) x 64 m (reduction)
+    rc = make_map(&map_a, g, 2, dims, strides, wgrad ? box_mn : box_k);
+    if (rc) return rc;
+  }
+  {
+    // B operand [L, K] row-major (w_mod [N,K] for dgrad, xq [M,K] for wgrad): {K, L}
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)p.L};
+    uint64_t strides[1] = {(uint64_t)K * 2};
+    uint32_t box[2] = {64, BK};
+    rc = make_map(&map_b, b_op, 2, dims, strides, box);
+    if (rc) return rc;
+  }
+  // CTA pairs (256-row blocks) when they fill the machine; single CTAs for smaller problems
+  const int pair_work = ((p.I + 2 * BM - 1) / (2 * BM)) * p.T * p.num_jb;
+  const int pairs = max_pairs(wgrad);
+  if (pairs > 0 && pairing >= 0 && (pair_work >= pairs || pairing > 0)) {
+    p.num_ib = (p.I + 2 * BM - 1) / (2 * BM);
+    rc = wgrad ? ensure_smem(bwd_tc_pair_kernel<true>, P_SMEM) : ensure_smem(bwd_tc_pair_kernel<false>, P_SMEM);
+    if (rc) return rc;
+    const int grid = 2 * (pair_work < pairs ? pair_work : pairs);
+    if (wgrad)
+      bwd_tc_pair_kernel<true><<<grid, kBwdThreads, P_SMEM, s>>>(map_a, map_b, p);
+    else
+      bwd_tc_pair_kernel<false><<<grid, kBwdThreads, P_SMEM, s>>>(map_a, map_b, p);
+    return check_launch(wgrad ? "wgrad_tc_pair" : "dgrad_tc_pair");
+  }
+  int work = p.num_ib * p.T * p.num_jb;
+  int grid = work < sm_count() ? work : sm_count();
+  if (wgrad)
+    bwd_tc_kernel<true><<<grid, kBwdThreads, B_SMEM, s>>>(map_a, map_b, p);
+  else
+    bwd_tc_kernel<false><<<grid, kBwdThreads, B_SMEM, s>>>(map_a, map_b, p);
+  return check_launch(wgrad ? "wgrad_tc" : "dgrad_tc");
+}
+
+int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask, int mask_words,
+                    int M, int K, int N, const TileTable& tt, int pairing, void* grad_x, cudaStream_t s) {
+  ProfScope prof(AL_K_DGRAD_GEMM, s);
+  return launch_bwd_tc(false, g, w_mod, keep_mask, mask_words, M, K, N, tt, pairing, grad_x, s);
+}
+
+int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, int mask_words,
+                    int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s) {
+  ProfScope prof(AL_K_WGRAD_GEMM, s);
+  return launch_bwd_tc(true, g, xq, keep_mask, mask_words, M, K, N, tt, pairing, grad_w, s);
+}
+
+int tc_read_device_error(cudaStream_t s, uint32_t* code) {
+  cudaError_t e = cudaStreamSynchronize(s);
+  uint32_t fwd_code = 0;
+  *code = 0;
+  if (e == cudaSuccess) e = take_error_word(code);
+  if (e == cudaSuccess) e = tc_fwd_take_error_word(&fwd_code);
+  if (e != cudaSuccess) {
+    set_error("al_read_device_error: %s", cudaGetErrorString(e));
+    return AL_ERR_CUDA;
+  }
+  *code |= fwd_code;
+  if (*code != 0) {
+    set_error("a device-side wait of the tcgen05 kernels gave up (role mask 0x%x)", *code);
+    return AL_ERR_DEVICE_TIMEOUT;
+  }
+  return AL_OK;
+}
+
+}  // namespace al

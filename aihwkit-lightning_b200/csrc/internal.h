@@ -129,7 +129,7 @@ int launch_fwd_smallm(int round_dt, const void* xq, const void* w, int K, const 
                       const FwdEpilogueParams& ep, void* w_amax, float* tile_max, float* scratch, void* out,
                       cudaStream_t s);
 
-// ---- tcgen05 GEMMs (gemm_tcgen05.cu) ------------------------------------------------------
+// ---- tcgen05 GEMMs (gemm_tcgen05_fwd.cu, gemm_tcgen05_bwd.cu) -----------------------------
 bool tc_forward_supported(const AlDesc& d, const TileTable& tt);
 // pairing: 0 = CTA pairs when they fill the machine, 1 = always pairs, -1 = never
 int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const TileTable& tt,
@@ -141,5 +141,7 @@ int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask,
 int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, int mask_words,
                     int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s);
 int tc_read_device_error(cudaStream_t s, uint32_t* code);
+// the forward translation unit's own error word (read and cleared); the stream must be idle
+cudaError_t tc_fwd_take_error_word(uint32_t* code);
 
 }  // namespace al
