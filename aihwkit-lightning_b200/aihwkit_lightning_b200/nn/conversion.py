@@ -1,71 +1,123 @@
-"""Swap ``nn.Linear`` / ``nn.Conv1d`` / ``nn.Conv2d`` / ``nn.Conv3d`` for their analog counterparts and back.
+"""Swap torch layers for their analog counterparts and back.
 
-Covers what the benchmark models need of the reference's ``convert_to_analog`` /
-``convert_to_digital`` (`nn/conversion.py:71-295`): same arguments for the Linear/ConvNd
-entries of the conversion map, recursion over children, ``exclude_modules`` by name suffix.
+Same arguments, traversal and results as the reference's ``convert_to_analog`` /
+``convert_to_digital`` (`nn/conversion.py:71-295`): the module itself is converted when its class
+is in the map, then its children -- a child that has children of its own is descended into
+(after its own conversion, which is how ``nn.Sequential`` and the recurrent modules are
+handled), a leaf is converted through ``from_digital`` -- ``exclude_modules`` holds full dotted
+names, every converted layer gets its own deep copy of the config passed through
+``specific_rpu_config_fun``, and a root that is not analog itself is wrapped in
+``AnalogWrapper`` when ``ensure_analog_root`` is set.
 """
 from copy import deepcopy
-from typing import Dict, List, Optional, Type
+from typing import Callable, Dict, List, Optional, Set, Type
 
-from torch.nn import Conv1d, Conv2d, Conv3d, Linear, Module
+from ..exceptions import ArgumentError
+from torch.nn import GRU, LSTM, RNN, Conv1d, Conv2d, Conv3d, Linear, Module, Sequential
 
-from .modules import AnalogConv1d, AnalogConv2d, AnalogConv3d, AnalogLayerBase, AnalogLinear
+from .modules import (
+    AnalogConv1d,
+    AnalogConv2d,
+    AnalogConv3d,
+    AnalogLayerBase,
+    AnalogLinear,
+    AnalogRNN,
+    AnalogSequential,
+    AnalogWrapper,
+)
 
-_DEFAULT_CONVERSION_MAP: Dict[Type, Type] = {Linear: AnalogLinear, Conv1d: AnalogConv1d, Conv2d: AnalogConv2d,
-                                             Conv3d: AnalogConv3d}
-_DEFAULT_DIGITAL_CONVERSION_SET = {AnalogLinear, AnalogConv1d, AnalogConv2d, AnalogConv3d}
+_DEFAULT_CONVERSION_MAP: Dict[Type, Type] = {
+    Linear: AnalogLinear,
+    Conv1d: AnalogConv1d,
+    Conv2d: AnalogConv2d,
+    Conv3d: AnalogConv3d,
+    Sequential: AnalogSequential,
+    LSTM: AnalogRNN,
+    GRU: AnalogRNN,
+    RNN: AnalogRNN,
+}
+_DEFAULT_DIGITAL_CONVERSION_SET = {*_DEFAULT_CONVERSION_MAP.values()}
+
+
+def specific_rpu_config_id(module_name: str, module: Module, rpu_config):
+    """Default ``specific_rpu_config_fun``: every layer keeps the generic config."""
+    # pylint: disable=unused-argument
+    return rpu_config
 
 
 def convert_to_analog(module: Module, rpu_config, conversion_map: Optional[Dict] = None,
-                      specific_rpu_config_fun=None, module_name: str = "", ensure_analog_root: bool = True,
-                      exclude_modules: Optional[List[str]] = None, inplace: bool = False,
-                      verbose: bool = False) -> Module:
-    """Return ``module`` with every convertible layer replaced through ``from_digital``."""
-    del ensure_analog_root
-    if not inplace:
-        module = deepcopy(module)
-    conversion_map = conversion_map or _DEFAULT_CONVERSION_MAP
+                      specific_rpu_config_fun: Optional[Callable] = None, module_name: str = "",
+                      ensure_analog_root: bool = True, exclude_modules: Optional[List[str]] = None,
+                      inplace: bool = False, verbose: bool = False) -> Module:
+    """Return ``module`` with every layer of ``conversion_map`` replaced through ``from_digital``."""
     exclude_modules = exclude_modules or []
-
-    def excluded(name: str) -> bool:
-        return any(name == pat or name.endswith("." + pat) or name.endswith(pat) for pat in exclude_modules)
-
-    def convert(mod: Module, name: str) -> Module:
-        if type(mod) in conversion_map and not excluded(name):  # pylint: disable=unidiomatic-typecheck
-            cfg = rpu_config
-            if specific_rpu_config_fun is not None:
-                cfg = specific_rpu_config_fun(name, mod, rpu_config)
-            if verbose:
-                print(f"converted {name or '<root>'} to {conversion_map[type(mod)].__name__}")
-            return conversion_map[type(mod)].from_digital(mod, deepcopy(cfg))
-        for child_name, child in list(mod.named_children()):
-            full = f"{name}.{child_name}" if name else child_name
-            new_child = convert(child, full)
-            if new_child is not child:
-                setattr(mod, child_name, new_child)
-        return mod
-
-    return convert(module, module_name)
-
-
-def convert_to_digital(module: Module, conversion_set=None, module_name: str = "",
-                       inplace: bool = False) -> Module:
-    """Inverse of :func:`convert_to_analog`."""
     if not inplace:
         module = deepcopy(module)
-    conversion_set = conversion_set or _DEFAULT_DIGITAL_CONVERSION_SET
+    if conversion_map is None:
+        conversion_map = _DEFAULT_CONVERSION_MAP
+    if not isinstance(conversion_map, dict):
+        raise ArgumentError("Conversion map should be a dictionary")
+    config_fun = specific_rpu_config_fun or specific_rpu_config_id
 
-    def convert(mod: Module) -> Module:
-        if type(mod) in conversion_set:  # pylint: disable=unidiomatic-typecheck
-            return type(mod).to_digital(mod)
-        for child_name, child in list(mod.named_children()):
-            new_child = convert(child)
-            if new_child is not child:
-                setattr(mod, child_name, new_child)
-        return mod
+    def make(mod: Module, name: str) -> Module:
+        target = conversion_map[type(mod)]
+        if verbose:
+            print(f"Converted '{name}' to '{target.__name__}'.")
+        return target.from_digital(mod, config_fun(name, mod, deepcopy(rpu_config)))
 
-    del module_name
-    return convert(module)
+    converted = module
+    if type(module) in conversion_map and module_name not in exclude_modules:
+        converted = make(module, module_name)
+        if inplace:
+            conversion_map[type(module)].move_to_meta(module)  # frees the digital copy at once
+
+    replacements = {}
+    for name, child in converted.named_children():
+        full_name = f"{module_name}.{name}" if module_name else name
+        if full_name in exclude_modules:
+            continue
+        if next(child.named_children(), None) is not None:
+            replacements[name] = convert_to_analog(child, rpu_config, conversion_map, config_fun, full_name, True,
+                                                   exclude_modules, True, verbose)
+        elif type(child) in conversion_map:
+            replacements[name] = make(child, full_name)
+    for name, new_child in replacements.items():
+        converted._modules[name] = new_child  # pylint: disable=protected-access
+
+    if ensure_analog_root and not module_name and not isinstance(converted, AnalogLayerBase):
+        return AnalogWrapper(converted)
+    return converted
 
 
-__all__ = ["convert_to_analog", "convert_to_digital", "AnalogLayerBase"]
+def convert_to_digital(module: Module, conversion_set: Optional[Set] = None, module_name: str = "",
+                       inplace: bool = False) -> Module:
+    """Inverse of :func:`convert_to_analog`: every analog layer of ``conversion_set`` (and any
+    ``AnalogWrapper``) becomes its torch counterpart through ``to_digital``."""
+    if not inplace:
+        module = deepcopy(module)
+    if conversion_set is None:
+        conversion_set = _DEFAULT_DIGITAL_CONVERSION_SET
+    if not isinstance(conversion_set, set):
+        raise ArgumentError("Conversion set should be a set")
+
+    def unmake(mod: Module) -> Module:
+        if not hasattr(type(mod), "to_digital"):
+            raise ArgumentError(
+                None, "The conversion set should only contain analog layers that support `to_digital` conversion.")
+        return type(mod).to_digital(mod)
+
+    if type(module) in conversion_set or isinstance(module, AnalogWrapper):
+        module = unmake(module)
+    replacements = {}
+    for name, child in module.named_children():
+        full_name = f"{module_name}.{name}" if module_name else name
+        if next(child.named_children(), None) is not None:
+            replacements[name] = convert_to_digital(child, conversion_set, full_name, inplace=True)
+        elif type(child) in conversion_set:
+            replacements[name] = unmake(child)
+    for name, new_child in replacements.items():
+        module._modules[name] = new_child  # pylint: disable=protected-access
+    return module
+
+
+__all__ = ["convert_to_analog", "convert_to_digital", "specific_rpu_config_id", "AnalogLayerBase"]

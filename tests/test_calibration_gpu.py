@@ -24,7 +24,8 @@ def test_calibrated_ranges_match_reference(model_name, kind, kwargs):
     model = convert_to_analog(CC.build_model(model_name), rpu).cuda().eval()
     batches = [b.cuda() for b in CC.make_batches(model_name)]
     calibrate_input_ranges(model, InputRangeCalibrationType(kind), iter([((b,), {}) for b in batches]), **kwargs)
-    layers = {name: mod for name, mod in model.named_modules() if isinstance(mod, AnalogLayerBase)}
+    assert isinstance(model, AnalogLayerBase)
+    layers = dict(model.named_analog_layers())
     assert set(layers) == set(want)
     for name, layer in layers.items():
         cfg = layer.rpu_config
