@@ -401,6 +401,89 @@ dac_batched_kernel(const uint16_t* __restrict__ x, int M, int K, int T, int ir_m
   }
 }
 
+// Persistent form of weight_fused_kernel for bf16 tiles of 256 * Q elements: a resident grid of
+// warps walks the (channel, tile) segments with the vectors of its next segment already in flight
+// while it reduces, perturbs and stores the current one, so a warp always has a load outstanding
+// and the grid needs no block turnover.  Tile maxima: one atomic per warp at the very end.
+template <int Q>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+weight_fused_stream_kernel(const uint16_t* __restrict__ w, int N, int K, int T, uint16_t* __restrict__ w_amax,
+                           float* __restrict__ tile_max, int noise_type, float std_dev, const NoiseKeys nk,
+                           uint16_t* __restrict__ w_mod) {
+  constexpr int kTileW = 256 * Q;
+  const int lane = threadIdx.x & 31;
+  const unsigned n_warps = gridDim.x * kWarpsPerBlock;
+  const unsigned segs = (unsigned)N * (unsigned)T;
+  unsigned seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  // the grid is sized so that n_warps is a multiple of T: a warp always meets the same tile
+  const int t = (int)(seg % (unsigned)T);
+  float run_max = 0.0f;
+  uint4 cur[Q], nxt[Q];
+  auto load = [&](unsigned sg, uint4* dst) {
+    const int64_t base = (int64_t)(sg / (unsigned)T) * K + (int64_t)t * kTileW;
+#pragma unroll
+    for (int j = 0; j < Q; ++j)
+      dst[j] = sg < segs ? __ldg(reinterpret_cast<const uint4*>(w + base + (j * 32 + lane) * 8)) : make_uint4(0u, 0u, 0u, 0u);
+  };
+  load(seg, cur);
+  for (; seg < segs; seg += n_warps) {
+    load(seg + n_warps, nxt);
+    const int n = (int)(seg / (unsigned)T);
+    const float row_max = vecs_abs_max(cur, Q);
+    run_max = fmaxf(run_max, row_max);
+    if (lane == 0) w_amax[(int64_t)t * N + n] = f32_to_bf16_bits(row_max);
+    if (noise_type != AL_NOISE_NONE) {
+      const __nv_bfloat162 amp2 = __float2bfloat162_rn(rnd<kBF16>(fmul(std_dev, row_max)));
+#pragma unroll
+      for (int j = 0; j < Q; ++j) {
+        const int64_t e0 = (int64_t)n * K + (int64_t)t * kTileW + (j * 32 + lane) * 8;
+        float z[8];
+        normal8_keyed(nk, (uint64_t)e0 >> 3, z);
+        uint32_t wv[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __nv_bfloat162 z2 = __floats2bfloat162_rn(z[2 * e], z[2 * e + 1]);
+          wv[e] = as_u32(__hadd2_rn(as_bf162(wv[e]), __hmul2_rn(amp2, z2)));
+        }
+        *reinterpret_cast<uint4*>(w_mod + e0) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < Q; ++j) cur[j] = nxt[j];
+  }
+  if (lane == 0) {
+    unsigned int* slot = reinterpret_cast<unsigned int*>(tile_max) + t;
+    const unsigned int bits = __float_as_uint(run_max);
+    if (bits > *reinterpret_cast<volatile unsigned int*>(slot)) atomicMax(slot, bits);
+  }
+}
+
+// A resident grid (what the occupancy query says fits, times the SM count) whose warp count is a
+// multiple of T.  Returns -1 when there is none, else the launch status.
+template <int Q>
+int launch_weight_stream(const void* w, int N, int K, int T, void* w_amax, float* tile_max, int noise_type,
+                         float std_dev, const NoiseKeys& nk, void* w_mod, cudaStream_t s) {
+  static int resident = 0;  // blocks of this instantiation the device holds at once
+  if (resident == 0) {
+    int sms = 0, dev = 0, per_sm = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, weight_fused_stream_kernel<Q>, kWarpsPerBlock * 32, 0) !=
+            cudaSuccess || per_sm <= 0)
+      per_sm = 2;
+    resident = sms * per_sm;
+  }
+  const int64_t segs = (int64_t)N * T;
+  int64_t blocks = resident;
+  if (blocks * kWarpsPerBlock > segs) blocks = segs / kWarpsPerBlock;
+  while (blocks > 0 && (blocks * kWarpsPerBlock) % T != 0) --blocks;
+  if (blocks <= 0) return -1;
+  weight_fused_stream_kernel<Q><<<(unsigned)blocks, kWarpsPerBlock * 32, 0, s>>>(
+      reinterpret_cast<const uint16_t*>(w), N, K, T, reinterpret_cast<uint16_t*>(w_amax), tile_max, noise_type, std_dev,
+      nk, reinterpret_cast<uint16_t*>(w_mod));
+  return check_launch("weight_fused_stream");
+}
+
 // Q for a tiling the batched kernels take (0: use the general kernels)
 int batched_q(const TileTable& tt, int K) {
   const int w = tt.hi(0);
@@ -472,6 +555,18 @@ int launch_weight_fused(int dtype, const void* w, int N, int K, const TileTable&
   if (e != cudaSuccess) {
     set_error("weight_fused: memset: %s", cudaGetErrorString(e));
     return AL_ERR_CUDA;
+  }
+  const int q = batched_q(tt, K);
+  if (dtype == AL_BF16 && q > 0 && q <= 4 && aligned && w_noise == nullptr && aligned16(w_amax) &&
+      (noise_type == AL_NOISE_NONE || w_mod != nullptr)) {
+    const NoiseKeys nk = make_noise_keys(seed, offset, 0u);
+    int rc = -1;
+    switch (q) {
+      case 1: rc = launch_weight_stream<1>(w, N, K, tt.T, w_amax, tile_max, noise_type, std_dev, nk, w_mod, s); break;
+      case 2: rc = launch_weight_stream<2>(w, N, K, tt.T, w_amax, tile_max, noise_type, std_dev, nk, w_mod, s); break;
+      default: rc = launch_weight_stream<4>(w, N, K, tt.T, w_amax, tile_max, noise_type, std_dev, nk, w_mod, s); break;
+    }
+    if (rc >= 0) return rc;  // < 0: no grid with a multiple of T warps, take the general kernel
   }
   if (dtype == AL_F32)
     weight_fused_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, noise_type, std_dev, w_noise, seed, offset, w_mod, aligned);
