@@ -395,9 +395,18 @@ int64_t al_smallm_scratch_floats(int32_t M, int32_t N, int32_t T) {
   return smallm_scratch_floats(N, T);
 }
 
+namespace {
+// reductions of the bias / range / clip gradients, rounded up to 16 bytes; the partial sums of
+// a split CUDA-core weight gradient follow
+int64_t backward_reduce_floats(int32_t M, int32_t N, int32_t T) {
+  const int64_t n = 256 * (int64_t)N + 3 * (int64_t)T * M + 16 + 2 * (int64_t)T + 16;
+  return (n + 3) / 4 * 4;
+}
+}  // namespace
+
 int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T) {
-  (void)K;
-  return 256 * (int64_t)N + 3 * (int64_t)T * M + 16 + 2 * (int64_t)T + 16;
+  if (M <= 0 || K <= 0 || N <= 0 || T <= 0) return 0;
+  return backward_reduce_floats(M, N, T) + al::wgrad_simt_partial_floats(M, K, N, T);
 }
 
 int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
@@ -463,7 +472,11 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
       return AL_ERR_BAD_ARGUMENT;
     }
     rc = tc ? launch_wgrad_tc(a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt, pairing, a->grad_w, s)
-            : launch_wgrad_simt(d.dtype, a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt, a->grad_w, s);
+            : launch_wgrad_simt(d.dtype, a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt,
+                                a->reduce_scratch ? a->reduce_scratch +
+                                                        backward_reduce_floats(d.M, d.N, d.T)
+                                                  : nullptr,
+                                a->grad_w, s);
     if (rc) return rc;
   }
   if (d.clip_type == AL_CLIP_LEARNABLE_PER_CHANNEL && (a->grad_w || a->grad_weight_clip)) {

@@ -1,9 +1,13 @@
 // CUDA-core GEMMs of the analog linear path.  They serve the fp32 layers (whose 1e-5 parity
 // bound rules out single-pass tensor-core arithmetic) and every shape the TMA-fed tcgen05
-// kernels cannot take (tile boundaries that are not 16-byte aligned).  One 64x64 output block
-// per CTA, 4x4 outputs per thread, fp32 accumulation; the forward kernel runs the per-tile
-// output stage (noise, ADC, clamp, cross-tile sum) in registers at the end of every analog
-// tile, the backward kernels apply the ADC clamp mask of the tile to the gradient operand.
+// kernels cannot take (tile boundaries that are not 16-byte aligned).  One output block of 4096
+// elements per CTA -- 64x64, or 128x32 / 256x16 (and their transposes) for the layers with few
+// output channels that convolutions produce, so that no lane multiplies padding -- 4x4 outputs
+// per thread, fp32 accumulation; the forward kernel runs the per-tile output stage (noise, ADC,
+// clamp, cross-tile sum) in registers at the end of every analog tile, the backward kernels
+// apply the ADC clamp mask of the tile to the gradient operand.  The weight gradient reduces
+// over the rows of the batch: when the output has too few blocks to fill the GPU that reduction
+// is split over CTAs, each writing a partial sum that a second kernel adds up in a fixed order.
 #include "analog_math.cuh"
 #include "internal.h"
 
@@ -11,25 +15,29 @@ namespace al {
 
 namespace {
 
-constexpr int BM = 64, BN = 64, BK = 16;
+constexpr int BK = 16;
+constexpr int kBlockElems = 4096;  // outputs per CTA: 256 threads x (4 x 4)
 constexpr int kThreads = 256;
 
-// Stages a [64 x 16] operand block into shared memory as floats, sm[l][i].
+// Stages a [ROWS x 16] operand block into shared memory as floats, sm[l][i].
 // L_CONTIG: the reduction index l is the contiguous one in memory, else the block-row index i.
-template <int DT, bool L_CONTIG>
+template <int DT, bool L_CONTIG, int ROWS>
 __device__ __forceinline__ void stage_block(const void* __restrict__ p, int64_t stride_i,
                                             int64_t stride_l, int i0, int i_end, int l0, int l_end,
-                                            float (*sm)[BM + 1], int tid) {
+                                            float (*sm)[ROWS + 1], int tid) {
+  constexpr int kIters = (ROWS * BK + kThreads - 1) / kThreads;
 #pragma unroll
-  for (int r = 0; r < (BM * BK) / kThreads; ++r) {
+  for (int r = 0; r < kIters; ++r) {
+    const int e = tid + r * kThreads;
     int i, l;
     if (L_CONTIG) {
-      l = tid % BK;
-      i = tid / BK + r * (kThreads / BK);
+      l = e % BK;
+      i = e / BK;
     } else {
-      i = tid % BM;
-      l = tid / BM + r * (kThreads / BM);
+      i = e % ROWS;
+      l = e / ROWS;
     }
+    if (ROWS * BK % kThreads != 0 && e >= ROWS * BK) break;
     float v = 0.0f;
     if (i0 + i < i_end && l0 + l < l_end)
       v = Elem<DT>::load(p, (int64_t)(i0 + i) * stride_i + (int64_t)(l0 + l) * stride_l);
@@ -37,15 +45,18 @@ __device__ __forceinline__ void stage_block(const void* __restrict__ p, int64_t 
   }
 }
 
-__device__ __forceinline__ void mac_block(const float (*As)[BM + 1], const float (*Bs)[BN + 1],
+// thread (ty, tx) owns rows ty*4 .. +3 and columns tx, tx + TBN/4, tx + 2 TBN/4, tx + 3 TBN/4
+template <int TBM, int TBN>
+__device__ __forceinline__ void mac_block(const float (*As)[TBM + 1], const float (*Bs)[TBN + 1],
                                           int ty, int tx, float acc[4][4]) {
+  constexpr int TX = TBN / 4;
 #pragma unroll
   for (int l = 0; l < BK; ++l) {
     float a[4], b[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) a[i] = As[l][ty * 4 + i];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) b[j] = Bs[l][tx + 16 * j];
+    for (int j = 0; j < 4; ++j) b[j] = Bs[l][tx + TX * j];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -54,13 +65,16 @@ __device__ __forceinline__ void mac_block(const float (*As)[BM + 1], const float
 }
 
 // out[m, n] = sum_t stage_t( xq[m, tile t] . w_mod[n, tile t] ) + bias[n]
-template <int DT, int RD>
+// BN in {16, 32, 64}: a block narrower than 64 is only launched when it covers all of N, so that
+// every 32-bit word of the keep mask has one writer.
+template <int DT, int RD, int BN>
 __global__ void __launch_bounds__(kThreads)
 fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int K, TileTable tt,
                 FwdEpilogueParams ep, void* __restrict__ out) {
+  constexpr int BM = kBlockElems / BN, TX = BN / 4;
   __shared__ float As[BK][BM + 1];
   __shared__ float Bs[BK][BN + 1];
-  const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16, lane = tid & 31;
+  const int tid = threadIdx.x, tx = tid % TX, ty = tid / TX, lane = tid & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int M = ep.M, N = ep.N;
 
@@ -82,10 +96,10 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
       for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
     const int lo = tt.lo(t), hi = tt.hi(t);
     for (int k0 = lo; k0 < hi; k0 += BK) {
-      stage_block<DT, true>(xq, K, 1, m0, M, k0, hi, As, tid);
-      stage_block<DT, true>(w_mod, K, 1, n0, N, k0, hi, Bs, tid);
+      stage_block<DT, true, BM>(xq, K, 1, m0, M, k0, hi, As, tid);
+      stage_block<DT, true, BN>(w_mod, K, 1, n0, N, k0, hi, Bs, tid);
       __syncthreads();
-      mac_block(As, Bs, ty, tx, acc);
+      mac_block<BM, BN>(As, Bs, ty, tx, acc);
       __syncthreads();
     }
     // per-tile output stage
@@ -93,7 +107,7 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
     float s_col_noise[4], s_col_bound[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      int n = n0 + tx + 16 * j;
+      int n = n0 + tx + TX * j;
       float cmax = (n < N && ep.w_amax && (ep.noise_pc || ep.bound_pc))
                        ? Elem<DT>::load(ep.w_amax, (int64_t)t * N + n)
                        : 0.0f;
@@ -111,7 +125,7 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
       uint32_t bal[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        int n = n0 + tx + 16 * j;
+        int n = n0 + tx + TX * j;
         bool keep = false;
         if (m < M && n < N) {
           float xi = 0.0f;
@@ -125,13 +139,20 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
         }
         bal[j] = __ballot_sync(0xffffffffu, keep);
       }
-      if (ep.keep_mask != nullptr && (lane == 0 || lane == 16) && m < M) {
-        int sh = lane == 0 ? 0 : 16;
-        uint32_t w0 = ((bal[0] >> sh) & 0xffffu) | (((bal[1] >> sh) & 0xffffu) << 16);
-        uint32_t w1 = ((bal[2] >> sh) & 0xffffu) | (((bal[3] >> sh) & 0xffffu) << 16);
+      // the TX lanes of this row hold, in ballot j, the bits of columns n0 + TX j .. + TX - 1
+      if (ep.keep_mask != nullptr && tx == 0 && m < M) {
+        const int sh = lane & ~(TX - 1);
+        constexpr uint32_t kBits = TX == 32 ? 0xffffffffu : ((1u << TX) - 1u);
+        uint32_t part[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) part[j] = (bal[j] >> sh) & kBits;
         int64_t base = ((int64_t)t * ep.mask_words + n0 / 32) * M + m;
-        if (n0 / 32 < ep.mask_words) ep.keep_mask[base] = w0;
-        if (n0 / 32 + 1 < ep.mask_words) ep.keep_mask[base + M] = w1;
+        if (BN == 64) {
+          if (n0 / 32 < ep.mask_words) ep.keep_mask[base] = part[0] | (part[1] << 16);
+          if (n0 / 32 + 1 < ep.mask_words) ep.keep_mask[base + M] = part[2] | (part[3] << 16);
+        } else {
+          ep.keep_mask[base] = part[0] | (part[1] << TX) | (part[2] << (2 * TX)) | (part[3] << (3 * TX));
+        }
       }
     }
   }
@@ -140,7 +161,7 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
     int m = m0 + ty * 4 + i;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      int n = n0 + tx + 16 * j;
+      int n = n0 + tx + TX * j;
       if (m < M && n < N) {
         float v = sum[i][j];
         if (ep.bias) v = fadd(rnd<RD>(v), Elem<DT>::load(ep.bias, n));
@@ -153,38 +174,44 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
 // Backward GEMMs.  C[i, lo_t + j] = sum_l A(i,l) * keep_t(i,l) * B(lo_t + j, l), where
 //   dgrad: i = m, l = n, A = g [M,N] (l contiguous), B = w_mod (j contiguous), C = grad_x
 //   wgrad: i = n, l = m, A = g^T     (i contiguous), B = xq    (j contiguous), C = grad_w
-template <int DT, bool WGRAD>
+// blockIdx.z = t * splits + s: split s reduces l over [s * chunk, (s + 1) * chunk) and, when
+// splits > 1, stores its fp32 partial block to partial[s][i][column] instead of C.
+template <int DT, bool WGRAD, int TBM, int TBN>
 __global__ void __launch_bounds__(kThreads)
 bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
                 const uint32_t* __restrict__ keep_mask, int mask_words, int M, int K, int N,
-                TileTable tt, void* __restrict__ c_out) {
-  __shared__ float As[BK][BM + 1];
-  __shared__ float Bs[BK][BN + 1];
-  const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
-  const int t = blockIdx.z;
+                TileTable tt, int splits, int chunk, float* __restrict__ partial, void* __restrict__ c_out) {
+  static_assert(TBM * TBN == kBlockElems, "4x4 outputs per thread");
+  constexpr int TX = TBN / 4;
+  __shared__ float As[BK][TBM + 1];
+  __shared__ float Bs[BK][TBN + 1];
+  const int tid = threadIdx.x, tx = tid % TX, ty = tid / TX;
+  const int t = blockIdx.z / splits, split = blockIdx.z - t * splits;
   const int lo = tt.lo(t), hi = tt.hi(t);
-  const int j0 = lo + blockIdx.x * BN;
+  const int j0 = lo + blockIdx.x * TBN;
   if (j0 >= hi) return;
-  const int i0 = blockIdx.y * BM;
+  const int i0 = blockIdx.y * TBM;
   const int I = WGRAD ? N : M;  // rows of C
   const int L = WGRAD ? M : N;  // reduction length
+  const int l_begin = split * chunk;
+  const int l_end = l_begin + chunk < L ? l_begin + chunk : L;
   float acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
 
-  for (int l0 = 0; l0 < L; l0 += BK) {
-    if (WGRAD) stage_block<DT, false>(g, 1, N, i0, I, l0, L, As, tid);
-    else stage_block<DT, true>(g, N, 1, i0, I, l0, L, As, tid);
-    stage_block<DT, false>(b_op, 1, K, j0, hi, l0, L, Bs, tid);
+  for (int l0 = l_begin; l0 < l_end; l0 += BK) {
+    if (WGRAD) stage_block<DT, false, TBM>(g, 1, N, i0, I, l0, l_end, As, tid);
+    else stage_block<DT, true, TBM>(g, N, 1, i0, I, l0, l_end, As, tid);
+    stage_block<DT, false, TBN>(b_op, 1, K, j0, hi, l0, l_end, Bs, tid);
     __syncthreads();
     if (keep_mask != nullptr) {
       // zero the gradient entries the ADC clamp of this tile blocked
-      for (int e = tid; e < BM * BK; e += kThreads) {
-        int i = e % BM, l = e / BM;
+      for (int e = tid; e < TBM * BK; e += kThreads) {
+        int i = e % TBM, l = e / TBM;
         int gi = i0 + i, gl = l0 + l;
-        if (gi < I && gl < L) {
+        if (gi < I && gl < l_end) {
           int m = WGRAD ? gl : gi, n = WGRAD ? gi : gl;
           uint32_t word = keep_mask[((int64_t)t * mask_words + (n >> 5)) * M + m];
           if (((word >> (n & 31)) & 1u) == 0u) As[l][i] = 0.0f;
@@ -192,7 +219,7 @@ bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
       }
       __syncthreads();
     }
-    mac_block(As, Bs, ty, tx, acc);
+    mac_block<TBM, TBN>(As, Bs, ty, tx, acc);
     __syncthreads();
   }
 #pragma unroll
@@ -200,10 +227,24 @@ bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
     int gi = i0 + ty * 4 + i;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      int gj = j0 + tx + 16 * j;
-      if (gi < I && gj < hi) Elem<DT>::store(c_out, (int64_t)gi * K + gj, acc[i][j]);
+      int gj = j0 + tx + TX * j;
+      if (gi < I && gj < hi) {
+        if (splits > 1) partial[((int64_t)split * I + gi) * K + gj] = acc[i][j];
+        else Elem<DT>::store(c_out, (int64_t)gi * K + gj, acc[i][j]);
+      }
     }
   }
+}
+
+// c[e] = sum_s partial[s][e], added in the order of s
+template <int DT>
+__global__ void __launch_bounds__(256)
+sum_partials_kernel(const float* __restrict__ partial, int splits, int64_t count, void* __restrict__ c_out) {
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= count) return;
+  float v = partial[e];
+  for (int s = 1; s < splits; ++s) v = fadd(v, partial[(int64_t)s * count + e]);
+  Elem<DT>::store(c_out, e, v);
 }
 
 inline int max_tile_width(const TileTable& tt) {
@@ -212,18 +253,59 @@ inline int max_tile_width(const TileTable& tt) {
   return w;
 }
 
+template <int BN>
+void fwd_simt_launch(int dtype, int round_dt, const void* xq, const void* w_mod, int K, const TileTable& tt,
+                     const FwdEpilogueParams& ep, void* out, cudaStream_t s) {
+  constexpr int BM = kBlockElems / BN;
+  dim3 grid((ep.N + BN - 1) / BN, (ep.M + BM - 1) / BM);
+  if (dtype == AL_F32)
+    fwd_simt_kernel<kF32, kF32, BN><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out);
+  else if (round_dt == AL_BF16)
+    fwd_simt_kernel<kBF16, kBF16, BN><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out);
+  else
+    fwd_simt_kernel<kBF16, kF32, BN><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out);
+}
+
+template <int TBM, int TBN>
+void wgrad_simt_launch(int dtype, const void* g, const void* xq, const uint32_t* keep_mask, int mask_words, int M,
+                       int K, int N, const TileTable& tt, int splits, int chunk, float* partial, void* grad_w,
+                       cudaStream_t s) {
+  dim3 grid((max_tile_width(tt) + TBN - 1) / TBN, (N + TBM - 1) / TBM, tt.T * splits);
+  if (dtype == AL_F32)
+    bwd_simt_kernel<kF32, true, TBM, TBN><<<grid, kThreads, 0, s>>>(g, xq, keep_mask, mask_words, M, K, N, tt, splits,
+                                                                    chunk, partial, grad_w);
+  else
+    bwd_simt_kernel<kBF16, true, TBM, TBN><<<grid, kThreads, 0, s>>>(g, xq, keep_mask, mask_words, M, K, N, tt,
+                                                                     splits, chunk, partial, grad_w);
+}
+
+// Number of CTAs the reduction over the batch rows is split over: enough to put two waves of
+// blocks on a 148-SM part, at least 512 rows each.  A function of the sizes alone, so that the
+// caller can size the partial-sum buffer without the tile table.
+int wgrad_splits(int M, int K, int N, int T) {
+  const int tbm = N <= 16 ? 16 : N <= 32 ? 32 : 64;
+  const int tbn = kBlockElems / tbm;
+  const int width = (K + T - 1) / T;
+  const int64_t blocks = (int64_t)((width + tbn - 1) / tbn) * ((N + tbm - 1) / tbm) * T;
+  int64_t want = (296 + blocks - 1) / blocks;
+  const int64_t most = (M + 511) / 512;
+  if (want > most) want = most;
+  return want < 1 ? 1 : (int)want;
+}
+
 }  // namespace
+
+int64_t wgrad_simt_partial_floats(int M, int K, int N, int T) {
+  const int splits = wgrad_splits(M, K, N, T);
+  return splits > 1 ? (int64_t)splits * N * K : 0;
+}
 
 int launch_fwd_simt(int dtype, int round_dt, const void* xq, const void* w_mod, int K,
                     const TileTable& tt, const FwdEpilogueParams& ep, void* out, cudaStream_t s) {
   ProfScope prof(AL_K_FWD_GEMM, s);
-  dim3 grid((ep.N + BN - 1) / BN, (ep.M + BM - 1) / BM);
-  if (dtype == AL_F32)
-    fwd_simt_kernel<kF32, kF32><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out);
-  else if (round_dt == AL_BF16)
-    fwd_simt_kernel<kBF16, kBF16><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out);
-  else
-    fwd_simt_kernel<kBF16, kF32><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out);
+  if (ep.N <= 16) fwd_simt_launch<16>(dtype, round_dt, xq, w_mod, K, tt, ep, out, s);
+  else if (ep.N <= 32) fwd_simt_launch<32>(dtype, round_dt, xq, w_mod, K, tt, ep, out, s);
+  else fwd_simt_launch<64>(dtype, round_dt, xq, w_mod, K, tt, ep, out, s);
   return check_launch("fwd_simt");
 }
 
@@ -231,24 +313,37 @@ int launch_dgrad_simt(int dtype, const void* g, const void* w_mod, const uint32_
                       int mask_words, int M, int K, int N, const TileTable& tt, void* grad_x,
                       cudaStream_t s) {
   ProfScope prof(AL_K_DGRAD_GEMM, s);
-  dim3 grid((max_tile_width(tt) + BN - 1) / BN, (M + BM - 1) / BM, tt.T);
+  dim3 grid((max_tile_width(tt) + 63) / 64, (M + 63) / 64, tt.T);
   if (dtype == AL_F32)
-    bwd_simt_kernel<kF32, false><<<grid, kThreads, 0, s>>>(g, w_mod, keep_mask, mask_words, M, K, N, tt, grad_x);
+    bwd_simt_kernel<kF32, false, 64, 64><<<grid, kThreads, 0, s>>>(g, w_mod, keep_mask, mask_words, M, K, N, tt, 1, N,
+                                                                  nullptr, grad_x);
   else
-    bwd_simt_kernel<kBF16, false><<<grid, kThreads, 0, s>>>(g, w_mod, keep_mask, mask_words, M, K, N, tt, grad_x);
+    bwd_simt_kernel<kBF16, false, 64, 64><<<grid, kThreads, 0, s>>>(g, w_mod, keep_mask, mask_words, M, K, N, tt, 1, N,
+                                                                   nullptr, grad_x);
   return check_launch("dgrad_simt");
 }
 
 int launch_wgrad_simt(int dtype, const void* g, const void* xq, const uint32_t* keep_mask,
-                      int mask_words, int M, int K, int N, const TileTable& tt, void* grad_w,
+                      int mask_words, int M, int K, int N, const TileTable& tt, float* partial, void* grad_w,
                       cudaStream_t s) {
-  ProfScope prof(AL_K_WGRAD_GEMM, s);
-  dim3 grid((max_tile_width(tt) + BN - 1) / BN, (N + BM - 1) / BM, tt.T);
-  if (dtype == AL_F32)
-    bwd_simt_kernel<kF32, true><<<grid, kThreads, 0, s>>>(g, xq, keep_mask, mask_words, M, K, N, tt, grad_w);
-  else
-    bwd_simt_kernel<kBF16, true><<<grid, kThreads, 0, s>>>(g, xq, keep_mask, mask_words, M, K, N, tt, grad_w);
-  return check_launch("wgrad_simt");
+  const int splits = wgrad_splits(M, K, N, tt.T);
+  ProfScope prof(AL_K_WGRAD_GEMM, s, splits > 1 ? 2 : 1);
+  if (splits > 1 && partial == nullptr) {
+    set_error("wgrad_simt: the partial-sum buffer is missing");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  const int per = (M + splits - 1) / splits;
+  const int chunk = (per + BK - 1) / BK * BK;
+  if (N <= 16) wgrad_simt_launch<16, 256>(dtype, g, xq, keep_mask, mask_words, M, K, N, tt, splits, chunk, partial, grad_w, s);
+  else if (N <= 32) wgrad_simt_launch<32, 128>(dtype, g, xq, keep_mask, mask_words, M, K, N, tt, splits, chunk, partial, grad_w, s);
+  else wgrad_simt_launch<64, 64>(dtype, g, xq, keep_mask, mask_words, M, K, N, tt, splits, chunk, partial, grad_w, s);
+  int rc = check_launch("wgrad_simt");
+  if (rc || splits == 1) return rc;
+  const int64_t count = (int64_t)N * K;
+  const unsigned blocks = (unsigned)((count + 255) / 256);
+  if (dtype == AL_F32) sum_partials_kernel<kF32><<<blocks, 256, 0, s>>>(partial, splits, count, grad_w);
+  else sum_partials_kernel<kBF16><<<blocks, 256, 0, s>>>(partial, splits, count, grad_w);
+  return check_launch("wgrad_sum_partials");
 }
 
 }  // namespace al

@@ -105,9 +105,12 @@ int launch_fwd_simt(int dtype, int round_dt, const void* xq, const void* w_mod, 
 int launch_dgrad_simt(int dtype, const void* g, const void* w_mod, const uint32_t* keep_mask,
                       int mask_words, int M, int K, int N, const TileTable& tt, void* grad_x,
                       cudaStream_t s);
-// grad_w[:, tile] = (g * keep_t)^T @ xq[:, tile]
+// grad_w[:, tile] = (g * keep_t)^T @ xq[:, tile].  `partial` holds wgrad_simt_partial_floats()
+// floats (fp32 partial sums of the reduction over the rows when it is split over CTAs; may be
+// null when that count is zero).
+int64_t wgrad_simt_partial_floats(int M, int K, int N, int T);
 int launch_wgrad_simt(int dtype, const void* g, const void* xq, const uint32_t* keep_mask,
-                      int mask_words, int M, int K, int N, const TileTable& tt, void* grad_w,
+                      int mask_words, int M, int K, int N, const TileTable& tt, float* partial, void* grad_w,
                       cudaStream_t s);
 
 // ---- backward element-wise parts (backward_kernels.cu) ------------------------------------
