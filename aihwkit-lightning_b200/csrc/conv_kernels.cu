@@ -65,6 +65,172 @@ fold2d_kernel(const void* __restrict__ gp, ConvGeom g, void* __restrict__ gx) {
   }
 }
 
+// ---- staged forms ------------------------------------------------------------------------------
+// The patch matrix is [B * Ho * Wo, C * kh * kw]: the patches of one output row (b, oh) form one
+// contiguous run of Wo * C*kh*kw elements.  A CTA of unfold2d_rows_kernel stages the kh input
+// rows that output row reads (for a chunk of channels, zero padding included) in shared memory
+// with coalesced loads and writes its part of the run with coalesced stores; where a patch
+// element comes from is a table lookup (lut[e], e = position inside the chunk of the patch)
+// plus ow * sw.
+constexpr int kStageBytes = 40 * 1024;
+
+template <int DT>
+__global__ void __launch_bounds__(256)
+unfold2d_rows_kernel(const void* __restrict__ x, ConvGeom g, int c_chunk, int span, void* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int kk = g.kh * g.kw, ckk = g.C * kk;
+  // blockIdx.x = output row * chunks + chunk: CTAs that run together read and write neighbouring memory
+  const int chunks = (g.C + c_chunk - 1) / c_chunk;
+  const int out_row = blockIdx.x / chunks;
+  const int c0 = (blockIdx.x - out_row * chunks) * c_chunk;
+  const int cn = g.C - c0 < c_chunk ? g.C - c0 : c_chunk;
+  const int len = cn * kk;       // patch elements of this chunk
+  const int rows = cn * g.kh;    // staged input rows
+  float* tile = reinterpret_cast<float*>(smem_raw);             // [rows][span]
+  int* lut = reinterpret_cast<int*>(tile + c_chunk * g.kh * span);  // [len]
+  const int b = out_row / g.Ho, oh = out_row - b * g.Ho;
+  int* row_src = lut + c_chunk * kk;                                  // [rows]: offset of the input row, -1 = padding
+  for (int e = threadIdx.x; e < len; e += blockDim.x) lut[e] = (e / g.kw) * span + (e % g.kw) * g.dw;
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+    const int c = c0 + r / g.kh, i = r % g.kh;
+    const int h = oh * g.sh - g.ph + i * g.dh;
+    row_src[r] = (h >= 0 && h < g.H) ? (c * g.H + h) * g.W : -1;
+  }
+  __syncthreads();
+  // element idx = r * span + col of the staged rows; (r, col) advance without a division, and
+  // kBatch loads are in flight per thread before the first one is stored
+  constexpr int kBatch = 4;
+  const int64_t image = (int64_t)b * g.C * g.H * g.W;
+  const int step_r = (int)blockDim.x / span, step_col = (int)blockDim.x - step_r * span;
+  int r = (int)threadIdx.x / span, col = (int)threadIdx.x - r * span;
+  for (int first = threadIdx.x; first < rows * span; first += blockDim.x * kBatch) {
+    float v[kBatch];
+    int rr = r, cc = col;
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      v[u] = 0.0f;
+      if (rr < rows) {
+        const int src = row_src[rr], w = cc - g.pw;
+        if (src >= 0 && w >= 0 && w < g.W) v[u] = Elem<DT>::load(x, image + src + w);
+      }
+      rr += step_r;
+      cc += step_col;
+      if (cc >= span) { cc -= span; ++rr; }
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      if (r < rows) tile[r * span + col] = v[u];
+      r += step_r;
+      col += step_col;
+      if (col >= span) { col -= span; ++r; }
+    }
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  const int64_t base = ((int64_t)out_row * g.Wo) * ckk + (int64_t)c0 * kk;
+  for (int ow = warp; ow < g.Wo; ow += n_warps) {
+    const int shift = ow * g.sw;
+    const int64_t row = base + (int64_t)ow * ckk;
+    for (int e = lane; e < len; e += 32) Elem<DT>::store(out, row + e, tile[lut[e] + shift]);
+  }
+}
+
+// The adjoint.  A CTA owns a band of kFoldRows input rows of one image for a chunk of channels,
+// stages every patch row (b, oh) that touches the band -- contiguous runs again -- and each
+// thread then sums, for its (channel, h, w), the up to kh * kw staged values in the order
+// (i, j), the order of the unstaged kernel.
+constexpr int kFoldRows = 4;
+
+// UNIT: both strides are 1, which takes the integer divisions out of the inner loop.
+template <int DT, bool UNIT>
+__global__ void __launch_bounds__(256)
+fold2d_band_kernel(const void* __restrict__ gp, ConvGeom g, int c_chunk, int n_oh_max, void* __restrict__ gx) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* tile = reinterpret_cast<float*>(smem_raw);  // [n_oh][Wo][pitch]
+  const int kk = g.kh * g.kw, ckk = g.C * kk;
+  const int chunks = (g.C + c_chunk - 1) / c_chunk;
+  const int band = blockIdx.x / chunks;  // blockIdx.x = band * chunks + chunk
+  const int c0 = (blockIdx.x - band * chunks) * c_chunk;
+  const int cn = g.C - c0 < c_chunk ? g.C - c0 : c_chunk;
+  const int len = cn * kk;
+  const int pitch = (c_chunk * kk) | 1;  // odd: threads with consecutive w read distinct banks
+  const int bands = (g.H + kFoldRows - 1) / kFoldRows;
+  const int b = band / bands, h0 = (band - b * bands) * kFoldRows;
+  const int h1 = h0 + kFoldRows < g.H ? h0 + kFoldRows : g.H;
+  // output rows that read input rows h0 .. h1 - 1
+  int oh_lo = h0 + g.ph - (g.kh - 1) * g.dh;
+  oh_lo = oh_lo <= 0 ? 0 : (oh_lo + g.sh - 1) / g.sh;
+  int oh_hi = (h1 - 1 + g.ph) / g.sh;
+  if (oh_hi > g.Ho - 1) oh_hi = g.Ho - 1;
+  const int n_oh = oh_hi - oh_lo + 1 < n_oh_max ? oh_hi - oh_lo + 1 : n_oh_max;  // <= n_oh_max by construction
+  // runs of `len` contiguous elements, one per patch row; kBatch loads in flight per thread
+  constexpr int kBatch = 8;
+  const int64_t src0 = ((int64_t)(b * g.Ho + oh_lo) * g.Wo) * ckk + (int64_t)c0 * kk;
+  const int total = n_oh > 0 ? n_oh * g.Wo * len : 0;
+  const int step_r = (int)blockDim.x / len, step_e = (int)blockDim.x - step_r * len;
+  int r = (int)threadIdx.x / len, e = (int)threadIdx.x - r * len;  // (row, element) advance without a division
+  for (int first = threadIdx.x; first < total; first += blockDim.x * kBatch) {
+    float v[kBatch];
+    int dst[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      dst[u] = -1;
+      if (first + u * (int)blockDim.x < total) {
+        dst[u] = r * pitch + e;
+        v[u] = Elem<DT>::load(gp, src0 + (int64_t)r * ckk + e);
+      }
+      r += step_r;
+      e += step_e;
+      if (e >= len) { e -= len; ++r; }
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u)
+      if (dst[u] >= 0) tile[dst[u]] = v[u];
+  }
+  __syncthreads();
+  const int per_c = (h1 - h0) * g.W;
+  for (int idx = threadIdx.x; idx < cn * per_c; idx += blockDim.x) {
+    const int cl = idx / per_c, rem = idx - cl * per_c;
+    const int h = h0 + rem / g.W, w = rem % g.W;
+    float acc = 0.0f;
+    for (int i = 0; i < g.kh; ++i) {
+      const int hh = h + g.ph - i * g.dh;
+      if (hh < 0 || (!UNIT && hh % g.sh != 0)) continue;
+      const int oh = UNIT ? hh : hh / g.sh;
+      if (oh > oh_hi) continue;
+      const float* row = tile + (oh - oh_lo) * g.Wo * pitch + (cl * g.kh + i) * g.kw;
+      for (int j = 0; j < g.kw; ++j) {
+        const int ww = w + g.pw - j * g.dw;
+        if (ww < 0 || (!UNIT && ww % g.sw != 0)) continue;
+        const int ow = UNIT ? ww : ww / g.sw;
+        if (ow >= g.Wo) continue;
+        acc += row[ow * pitch + j];
+      }
+    }
+    Elem<DT>::store(gx, (((int64_t)b * g.C + c0 + cl) * g.H + h) * g.W + w, acc);
+  }
+}
+
+// channels per CTA (0: does not fit, use the unstaged kernel): the most that fit the staging
+// budget, then evened out over the resulting number of chunks
+int even_chunk(int C, int most) {
+  if (most < 1) return 0;
+  if (most >= C) return C;
+  const int chunks = (C + most - 1) / most;
+  return (C + chunks - 1) / chunks;
+}
+int unfold_chunk(const ConvGeom& g, int span) {
+  if ((int64_t)g.C * g.H * g.W >= 2147483647) return 0;  // row offsets inside one image are ints
+  return even_chunk(g.C, kStageBytes / (g.kh * span * 4 + g.kh * g.kw * 4 + g.kh * 4));
+}
+int fold_max_rows(const ConvGeom& g) { return (kFoldRows - 1 + (g.kh - 1) * g.dh) / g.sh + 1; }
+int fold_chunk(const ConvGeom& g) {
+  const int64_t rows = (int64_t)fold_max_rows(g) * g.Wo;
+  int c = g.C;
+  while (c > 0 && rows * ((c * g.kh * g.kw) | 1) * 4 > kStageBytes) --c;
+  return even_chunk(g.C, c);
+}
+
 int make_geom(int B, int C, int H, int W, int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
               ConvGeom* g) {
   if (B < 1 || C < 1 || H < 1 || W < 1 || kh < 1 || kw < 1 || sh < 1 || sw < 1 || ph < 0 || pw < 0 || dh < 1 ||
@@ -107,6 +273,15 @@ int al_unfold2d(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t H, i
   if (rc) return rc;
   ProfScope prof(AL_K_UNFOLD, (cudaStream_t)stream);
   const int64_t total = (int64_t)B * g.Ho * g.Wo * C * kh * kw;
+  const int span = (g.Wo - 1) * sw + (kw - 1) * dw + 1;
+  const int chunk = unfold_chunk(g, span);
+  if (chunk >= 1 && (int64_t)B * g.Ho * ((C + chunk - 1) / chunk) < 2147483647) {
+    const unsigned grid = (unsigned)((int64_t)B * g.Ho * ((C + chunk - 1) / chunk));
+    const size_t smem = (size_t)chunk * (kh * span + kh * kw + kh) * 4;
+    if (dtype == AL_F32) unfold2d_rows_kernel<kF32><<<grid, 256, smem, (cudaStream_t)stream>>>(x, g, chunk, span, out);
+    else unfold2d_rows_kernel<kBF16><<<grid, 256, smem, (cudaStream_t)stream>>>(x, g, chunk, span, out);
+    return check_launch("unfold2d_rows");
+  }
   if (dtype == AL_F32) unfold2d_kernel<kF32><<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(x, g, out);
   else unfold2d_kernel<kBF16><<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(x, g, out);
   return check_launch("unfold2d");
@@ -124,6 +299,20 @@ int al_fold2d(int32_t dtype, const void* grad_patches, int32_t B, int32_t C, int
   if (rc) return rc;
   ProfScope prof(AL_K_FOLD, (cudaStream_t)stream);
   const int64_t total = (int64_t)B * C * H * W;
+  const int chunk = fold_chunk(g);
+  const int64_t bands = (int64_t)B * ((H + kFoldRows - 1) / kFoldRows);
+  if (chunk >= 1 && bands * ((C + chunk - 1) / chunk) < 2147483647) {
+    const int n_oh = fold_max_rows(g);
+    const unsigned grid = (unsigned)(bands * ((C + chunk - 1) / chunk));
+    const size_t smem = (size_t)n_oh * g.Wo * ((chunk * kh * kw) | 1) * 4;
+    const bool unit = sh == 1 && sw == 1;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == AL_F32 && unit) fold2d_band_kernel<kF32, true><<<grid, 256, smem, st>>>(grad_patches, g, chunk, n_oh, grad_x);
+    else if (dtype == AL_F32) fold2d_band_kernel<kF32, false><<<grid, 256, smem, st>>>(grad_patches, g, chunk, n_oh, grad_x);
+    else if (unit) fold2d_band_kernel<kBF16, true><<<grid, 256, smem, st>>>(grad_patches, g, chunk, n_oh, grad_x);
+    else fold2d_band_kernel<kBF16, false><<<grid, 256, smem, st>>>(grad_patches, g, chunk, n_oh, grad_x);
+    return check_launch("fold2d_band");
+  }
   if (dtype == AL_F32) fold2d_kernel<kF32><<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(grad_patches, g, grad_x);
   else fold2d_kernel<kBF16><<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(grad_patches, g, grad_x);
   return check_launch("fold2d");

@@ -145,6 +145,13 @@ def test_internal_generator_noise_moments():
     dict(c=3, h=32, w=32, k=(3, 3), s=(1, 1), p=(1, 1), d=(1, 1)),
     dict(c=16, h=9, w=11, k=(3, 2), s=(2, 1), p=(0, 2), d=(1, 2)),
     dict(c=5, h=7, w=7, k=(1, 1), s=(2, 2), p=(0, 0), d=(1, 1)),
+    # channels split over several CTAs (the staged rows of all 96 do not fit), ragged last band
+    dict(c=96, h=30, w=34, k=(3, 3), s=(1, 1), p=(1, 1), d=(1, 1)),
+    dict(c=40, h=21, w=50, k=(5, 3), s=(2, 3), p=(2, 0), d=(2, 1)),
+    # a stride larger than the kernel: input rows no patch reads get a zero gradient
+    dict(c=2, h=13, w=12, k=(2, 2), s=(5, 4), p=(0, 1), d=(1, 1)),
+    # rows too long to stage: the unstaged kernels
+    dict(c=1, h=3, w=12000, k=(3, 3), s=(1, 1), p=(1, 1), d=(1, 1)),
 ])
 def test_unfold2d_and_its_adjoint_match_torch(dtype, geom):
     """The patch-extraction kernel is a pure copy (bit-equal to F.unfold + transpose); its
