@@ -211,6 +211,116 @@ fold2d_band_kernel(const void* __restrict__ gp, ConvGeom g, int c_chunk, int n_o
   }
 }
 
+// Unit-stride fp32 form of the band kernel, built to spend few instructions per byte (the form
+// above is bound by instruction issue, not by memory).  The staged block is zero-padded --
+// patch rows above / below the image and patch columns left / right of it hold zeros -- so the
+// sum of an output needs no validity tests: kh * kw loads at offsets that a table in shared
+// memory lists once per CTA.  Patch runs are loaded as 16-byte vectors; the slot walk carries
+// (row, column, vector) along without divisions.  Lanes map to (channel mod 4, w): with a pitch
+// (floats per staged slot) that is an odd multiple of 4 and an odd kh * kw the 32 lanes of a warp
+// then read 32 distinct banks.
+// Requires: C-chunk a multiple of 4 channels, 16-byte aligned runs (checked by the host).
+__global__ void __launch_bounds__(256)
+fold2d_band_unit_kernel(const float* __restrict__ gp, ConvGeom g, int c_chunk, int pitch, float* __restrict__ gx) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int kk = g.kh * g.kw, ckk = g.C * kk;
+  const int chunks = (g.C + c_chunk - 1) / c_chunk;
+  const int band = blockIdx.x / chunks;
+  const int c0 = (blockIdx.x - band * chunks) * c_chunk;
+  const int cn = g.C - c0 < c_chunk ? g.C - c0 : c_chunk;   // a multiple of 4
+  const int len4 = cn * kk / 4;                            // 16-byte vectors per patch run
+  const int bands = (g.H + kFoldRows - 1) / kFoldRows;
+  const int b = band / bands, h0 = (band - b * bands) * kFoldRows;
+  const int h1 = h0 + kFoldRows < g.H ? h0 + kFoldRows : g.H;
+  // staged slots: patch rows oh_min .. oh_min + rows - 1, patch columns ow_min .. ow_min + cols - 1
+  const int rows = kFoldRows + (g.kh - 1) * g.dh, cols = g.W + (g.kw - 1) * g.dw;
+  const int oh_min = h0 + g.ph - (g.kh - 1) * g.dh, ow_min = g.pw - (g.kw - 1) * g.dw;
+  float* tile = reinterpret_cast<float*>(smem_raw);             // [rows][cols][pitch]
+  int* tap = reinterpret_cast<int*>(tile + rows * cols * pitch);  // [kk]
+  // tap (i, j) of output (h, w), channel cl sits at slot (h - h0 + (kh-1-i) dh, w + (kw-1-j) dw), element cl*kk + i*kw + j
+  for (int t = threadIdx.x; t < kk; t += blockDim.x) {
+    const int i = t / g.kw, j = t - i * g.kw;
+    tap[t] = (((g.kh - 1 - i) * g.dh) * cols + (g.kw - 1 - j) * g.dw) * pitch + t;
+  }
+  const int total = rows * cols * len4;
+  const int step_slot = (int)blockDim.x / len4, step_q = (int)blockDim.x - step_slot * len4;
+  int slot = (int)threadIdx.x / len4, q = (int)threadIdx.x - slot * len4;
+  int row = slot / cols, col = slot - row * cols;
+  const int64_t image_rows = (int64_t)b * g.Ho;
+  constexpr int kBatch = 4;
+  for (int first = threadIdx.x; first < total; first += blockDim.x * kBatch) {
+    float4 v[kBatch];
+    int dst[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      dst[u] = -1;
+      v[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (row < rows) {
+        dst[u] = (row * cols + col) * pitch + 4 * q;
+        const int oh = oh_min + row, ow = ow_min + col;
+        if (oh >= 0 && oh < g.Ho && ow >= 0 && ow < g.Wo)
+          v[u] = __ldg(reinterpret_cast<const float4*>(gp + ((image_rows + oh) * g.Wo + ow) * ckk + (int64_t)c0 * kk) + q);
+      }
+      q += step_q;
+      col += step_slot;
+      if (q >= len4) { q -= len4; ++col; }
+      while (col >= cols) { col -= cols; ++row; }
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u)
+      if (dst[u] >= 0) *reinterpret_cast<float4*>(tile + dst[u]) = v[u];
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  const int cl_lane = lane & 3, w_lane = lane >> 2;
+  const int w_groups = (g.W + 7) >> 3, c_groups = cn >> 2;
+  const int band_rows = h1 - h0;
+  // items: (channel group, row of the band, group of 8 columns), the last fastest
+  const int items = c_groups * band_rows * w_groups;
+  int item = warp;
+  int wg = item % w_groups, rest = item / w_groups;
+  int hr = rest % band_rows, cg = rest / band_rows;
+  const int adv_wg = n_warps % w_groups, adv_rest = n_warps / w_groups;
+  for (; item < items; item += n_warps) {
+    const int cl = cg * 4 + cl_lane, w = wg * 8 + w_lane;
+    if (w < g.W) {
+      const float* base = tile + (hr * cols + w) * pitch + cl * kk;
+      float acc = 0.0f;
+      for (int t = 0; t < kk; ++t) acc += base[tap[t]];
+      gx[(((int64_t)b * g.C + c0 + cl) * g.H + h0 + hr) * g.W + w] = acc;
+    }
+    wg += adv_wg;
+    int carry = adv_rest;
+    if (wg >= w_groups) { wg -= w_groups; ++carry; }
+    hr += carry;
+    while (hr >= band_rows) { hr -= band_rows; ++cg; }
+  }
+}
+
+constexpr size_t kFoldUnitMaxSmem = 100 * 1024;
+
+// floats per staged slot of the unit-stride kernel: the run, padded to an odd multiple of 4
+int fold_unit_pitch(int chunk, int kk) {
+  const int run = chunk * kk;  // a multiple of 4
+  return (run / 4) % 2 == 1 ? run : run + 4;
+}
+size_t fold_unit_smem(const ConvGeom& g, int chunk) {
+  const size_t slots = (size_t)(kFoldRows + (g.kh - 1) * g.dh) * (g.W + (g.kw - 1) * g.dw);
+  return (slots * fold_unit_pitch(chunk, g.kh * g.kw) + g.kh * g.kw) * 4;
+}
+// channel chunk for the unit-stride kernel: a multiple of 4 whose padded block fits, 0 if none
+int fold_unit_chunk(const ConvGeom& g) {
+  if (g.sh != 1 || g.sw != 1 || g.C % 4 != 0) return 0;
+  int c = g.C;
+  while (c >= 4 && fold_unit_smem(g, c) > 48 * 1024) c -= 4;
+  // wide images: four channels may still fit the opt-in shared memory (two CTAs per SM)
+  if (c < 4 && fold_unit_smem(g, 4) <= kFoldUnitMaxSmem) c = 4;
+  if (c < 4) return 0;
+  const int chunks = (g.C + c - 1) / c;
+  const int even = ((g.C + chunks - 1) / chunks + 3) / 4 * 4;
+  return even <= c ? even : c;
+}
+
 // channels per CTA (0: does not fit, use the unstaged kernel): the most that fit the staging
 // budget, then evened out over the resulting number of chunks
 int even_chunk(int C, int most) {
@@ -247,6 +357,8 @@ int make_geom(int B, int C, int H, int W, int kh, int kw, int sh, int sw, int ph
   *g = ConvGeom{B, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, Ho, Wo};
   return AL_OK;
 }
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 unsigned blocks_for(int64_t total) {
   int64_t b = (total + 255) / 256;
@@ -299,8 +411,22 @@ int al_fold2d(int32_t dtype, const void* grad_patches, int32_t B, int32_t C, int
   if (rc) return rc;
   ProfScope prof(AL_K_FOLD, (cudaStream_t)stream);
   const int64_t total = (int64_t)B * C * H * W;
-  const int chunk = fold_chunk(g);
   const int64_t bands = (int64_t)B * ((H + kFoldRows - 1) / kFoldRows);
+  const int unit_chunk = dtype == AL_F32 && aligned16(grad_patches) ? fold_unit_chunk(g) : 0;
+  if (unit_chunk >= 4 && bands * ((C + unit_chunk - 1) / unit_chunk) < 2147483647) {
+    const unsigned grid = (unsigned)(bands * ((C + unit_chunk - 1) / unit_chunk));
+    static const cudaError_t attr = cudaFuncSetAttribute(fold2d_band_unit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                        (int)kFoldUnitMaxSmem);
+    if (attr != cudaSuccess) {
+      set_error("fold2d: shared-memory opt-in failed: %s", cudaGetErrorString(attr));
+      return AL_ERR_CUDA;
+    }
+    fold2d_band_unit_kernel<<<grid, 256, fold_unit_smem(g, unit_chunk), (cudaStream_t)stream>>>(
+        reinterpret_cast<const float*>(grad_patches), g, unit_chunk, fold_unit_pitch(unit_chunk, kh * kw),
+        reinterpret_cast<float*>(grad_x));
+    return check_launch("fold2d_band_unit");
+  }
+  const int chunk = fold_chunk(g);
   if (chunk >= 1 && bands * ((C + chunk - 1) / chunk) < 2147483647) {
     const int n_oh = fold_max_rows(g);
     const unsigned grid = (unsigned)(bands * ((C + chunk - 1) / chunk));

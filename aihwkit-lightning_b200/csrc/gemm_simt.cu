@@ -17,6 +17,7 @@ namespace {
 
 constexpr int BK = 16;
 constexpr int kBlockElems = 4096;  // outputs per CTA: 256 threads x (4 x 4)
+constexpr int kPad = 4;             // row padding of the staged blocks: rows stay 16-byte aligned
 constexpr int kThreads = 256;
 
 // Stages a [ROWS x 16] operand block into shared memory as floats, sm[l][i].
@@ -24,7 +25,7 @@ constexpr int kThreads = 256;
 template <int DT, bool L_CONTIG, int ROWS>
 __device__ __forceinline__ void stage_block(const void* __restrict__ p, int64_t stride_i,
                                             int64_t stride_l, int i0, int i_end, int l0, int l_end,
-                                            float (*sm)[ROWS + 1], int tid) {
+                                            float (*sm)[ROWS + kPad], int tid) {
   constexpr int kIters = (ROWS * BK + kThreads - 1) / kThreads;
 #pragma unroll
   for (int r = 0; r < kIters; ++r) {
@@ -45,18 +46,16 @@ __device__ __forceinline__ void stage_block(const void* __restrict__ p, int64_t 
   }
 }
 
-// thread (ty, tx) owns rows ty*4 .. +3 and columns tx, tx + TBN/4, tx + 2 TBN/4, tx + 3 TBN/4
+// thread (ty, tx) owns rows ty*4 .. +3 and columns tx*4 .. +3: one 16-byte shared-memory load
+// per operand and reduction step feeds 16 multiply-adds
 template <int TBM, int TBN>
-__device__ __forceinline__ void mac_block(const float (*As)[TBM + 1], const float (*Bs)[TBN + 1],
+__device__ __forceinline__ void mac_block(const float (*As)[TBM + kPad], const float (*Bs)[TBN + kPad],
                                           int ty, int tx, float acc[4][4]) {
-  constexpr int TX = TBN / 4;
 #pragma unroll
   for (int l = 0; l < BK; ++l) {
-    float a[4], b[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) a[i] = As[l][ty * 4 + i];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) b[j] = Bs[l][tx + TX * j];
+    const float4 av = *reinterpret_cast<const float4*>(&As[l][ty * 4]);
+    const float4 bv = *reinterpret_cast<const float4*>(&Bs[l][tx * 4]);
+    const float a[4] = {av.x, av.y, av.z, av.w}, b[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -72,8 +71,8 @@ __global__ void __launch_bounds__(kThreads)
 fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int K, TileTable tt,
                 FwdEpilogueParams ep, void* __restrict__ out) {
   constexpr int BM = kBlockElems / BN, TX = BN / 4;
-  __shared__ float As[BK][BM + 1];
-  __shared__ float Bs[BK][BN + 1];
+  __shared__ __align__(16) float As[BK][BM + kPad];
+  __shared__ __align__(16) float Bs[BK][BN + kPad];
   const int tid = threadIdx.x, tx = tid % TX, ty = tid / TX, lane = tid & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int M = ep.M, N = ep.N;
@@ -107,7 +106,7 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
     float s_col_noise[4], s_col_bound[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      int n = n0 + tx + TX * j;
+      int n = n0 + tx * 4 + j;
       float cmax = (n < N && ep.w_amax && (ep.noise_pc || ep.bound_pc))
                        ? Elem<DT>::load(ep.w_amax, (int64_t)t * N + n)
                        : 0.0f;
@@ -122,14 +121,21 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
         if (ep.ir_mode == AL_IR_DYNAMIC) ir = Elem<DT>::load(ep.ir_rows, (int64_t)t * M + m);
         else if (ep.ir_mode == AL_IR_STATIC) ir = Elem<DT>::load(ep.ir_rows, t);
       }
-      uint32_t bal[4];
+      uint32_t nibble = 0u;
+      // the thread's four columns are one group of four of the noise stream when N is a multiple
+      // of 4: one generator call instead of four, same values
+      const bool quad = ep.has_noise && ep.out_noise == nullptr && (N & 3) == 0 && m < M && n0 + tx * 4 < N;
+      float z4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      if (quad) normal4(ep.seed, ep.offset, 1u, (((uint64_t)t * M + m) * N + n0 + tx * 4) >> 2, z4);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        int n = n0 + tx + TX * j;
+        int n = n0 + tx * 4 + j;
         bool keep = false;
         if (m < M && n < N) {
           float xi = 0.0f;
-          if (ep.has_noise) {
+          if (quad) {
+            xi = rnd<RD>(z4[j]);
+          } else if (ep.has_noise) {
             uint64_t idx = ((uint64_t)t * M + m) * N + n;
             xi = ep.out_noise ? Elem<DT>::load(ep.out_noise, (int64_t)idx)
                               : rnd<RD>(normal1(ep.seed, ep.offset, 1u, idx));
@@ -137,22 +143,18 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
           float o = tile_epilogue<RD>(acc[i][j], ir, s_col_noise[j], s_col_bound[j], xi, cfg, &keep);
           sum[i][j] = t == 0 ? fadd(0.0f, o) : rnd<RD>(fadd(sum[i][j], o));
         }
-        bal[j] = __ballot_sync(0xffffffffu, keep);
+        nibble |= (keep ? 1u : 0u) << j;
+        // keeps the sixteen output stages of a thread from being interleaved (registers: 80 instead of 210+)
+        __syncwarp();
       }
-      // the TX lanes of this row hold, in ballot j, the bits of columns n0 + TX j .. + TX - 1
-      if (ep.keep_mask != nullptr && tx == 0 && m < M) {
-        const int sh = lane & ~(TX - 1);
-        constexpr uint32_t kBits = TX == 32 ? 0xffffffffu : ((1u << TX) - 1u);
-        uint32_t part[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) part[j] = (bal[j] >> sh) & kBits;
-        int64_t base = ((int64_t)t * ep.mask_words + n0 / 32) * M + m;
-        if (BN == 64) {
-          if (n0 / 32 < ep.mask_words) ep.keep_mask[base] = part[0] | (part[1] << 16);
-          if (n0 / 32 + 1 < ep.mask_words) ep.keep_mask[base + M] = part[2] | (part[3] << 16);
-        } else {
-          ep.keep_mask[base] = part[0] | (part[1] << TX) | (part[2] << (2 * TX)) | (part[3] << (3 * TX));
-        }
+      if (ep.keep_mask != nullptr) {
+        // the kGroup lanes of this row that share a 32-bit mask word OR their nibbles together
+        constexpr int kGroup = TX < 8 ? TX : 8;
+        const uint32_t gmask = ((1u << kGroup) - 1u) << (lane & ~(kGroup - 1));
+        const uint32_t word = __reduce_or_sync(gmask, nibble << (4 * (tx & 7)));
+        const int wi = n0 / 32 + (tx >> 3);
+        if ((tx & (kGroup - 1)) == 0 && m < M && wi < ep.mask_words)
+          ep.keep_mask[((int64_t)t * ep.mask_words + wi) * M + m] = word;
       }
     }
   }
@@ -161,7 +163,7 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
     int m = m0 + ty * 4 + i;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      int n = n0 + tx + TX * j;
+      int n = n0 + tx * 4 + j;
       if (m < M && n < N) {
         float v = sum[i][j];
         if (ep.bias) v = fadd(rnd<RD>(v), Elem<DT>::load(ep.bias, n));
@@ -183,8 +185,8 @@ bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
                 TileTable tt, int splits, int chunk, float* __restrict__ partial, void* __restrict__ c_out) {
   static_assert(TBM * TBN == kBlockElems, "4x4 outputs per thread");
   constexpr int TX = TBN / 4;
-  __shared__ float As[BK][TBM + 1];
-  __shared__ float Bs[BK][TBN + 1];
+  __shared__ __align__(16) float As[BK][TBM + kPad];
+  __shared__ __align__(16) float Bs[BK][TBN + kPad];
   const int tid = threadIdx.x, tx = tid % TX, ty = tid / TX;
   const int t = blockIdx.z / splits, split = blockIdx.z - t * splits;
   const int lo = tt.lo(t), hi = tt.hi(t);
@@ -227,7 +229,7 @@ bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
     int gi = i0 + ty * 4 + i;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      int gj = j0 + tx + TX * j;
+      int gj = j0 + tx * 4 + j;
       if (gi < I && gj < hi) {
         if (splits > 1) partial[((int64_t)split * I + gi) * K + gj] = acc[i][j];
         else Elem<DT>::store(c_out, (int64_t)gi * K + gj, acc[i][j]);

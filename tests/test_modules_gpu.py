@@ -148,6 +148,11 @@ def test_internal_generator_noise_moments():
     # channels split over several CTAs (the staged rows of all 96 do not fit), ragged last band
     dict(c=96, h=30, w=34, k=(3, 3), s=(1, 1), p=(1, 1), d=(1, 1)),
     dict(c=40, h=21, w=50, k=(5, 3), s=(2, 3), p=(2, 0), d=(2, 1)),
+    # unit stride with dilation and more padding than the kernel reaches over; even kernel area
+    dict(c=8, h=12, w=20, k=(3, 3), s=(1, 1), p=(2, 2), d=(2, 2)),
+    dict(c=12, h=10, w=9, k=(2, 2), s=(1, 1), p=(3, 2), d=(1, 1)),
+    # wide rows: the staged band needs the opt-in shared-memory size
+    dict(c=4, h=9, w=100, k=(3, 3), s=(1, 1), p=(1, 1), d=(1, 1)),
     # a stride larger than the kernel: input rows no patch reads get a zero gradient
     dict(c=2, h=13, w=12, k=(2, 2), s=(5, 4), p=(0, 1), d=(1, 1)),
     # rows too long to stage: the unstaged kernels
