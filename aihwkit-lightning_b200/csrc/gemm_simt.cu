@@ -20,29 +20,39 @@ constexpr int kBlockElems = 4096;  // outputs per CTA: 256 threads x (4 x 4)
 constexpr int kPad = 4;             // row padding of the staged blocks: rows stay 16-byte aligned
 constexpr int kThreads = 256;
 
-// Stages a [ROWS x 16] operand block into shared memory as floats, sm[l][i].
+// A [ROWS x 16] operand block travels global -> registers (block_fetch) -> shared memory as
+// floats, sm[l][i] (block_commit): the fetch of block k+1 is issued before the multiply-adds of
+// block k, so that its latency hides behind them.
 // L_CONTIG: the reduction index l is the contiguous one in memory, else the block-row index i.
+template <int ROWS>
+struct BlockRegs {
+  static constexpr int kIters = (ROWS * BK + kThreads - 1) / kThreads;
+  float v[kIters];
+};
+
 template <int DT, bool L_CONTIG, int ROWS>
-__device__ __forceinline__ void stage_block(const void* __restrict__ p, int64_t stride_i,
-                                            int64_t stride_l, int i0, int i_end, int l0, int l_end,
-                                            float (*sm)[ROWS + kPad], int tid) {
-  constexpr int kIters = (ROWS * BK + kThreads - 1) / kThreads;
+__device__ __forceinline__ void block_fetch(const void* __restrict__ p, int64_t stride_i, int64_t stride_l, int i0,
+                                            int i_end, int l0, int l_end, int tid, BlockRegs<ROWS>& regs) {
 #pragma unroll
-  for (int r = 0; r < kIters; ++r) {
+  for (int r = 0; r < BlockRegs<ROWS>::kIters; ++r) {
     const int e = tid + r * kThreads;
-    int i, l;
-    if (L_CONTIG) {
-      l = e % BK;
-      i = e / BK;
-    } else {
-      i = e % ROWS;
-      l = e / ROWS;
-    }
-    if (ROWS * BK % kThreads != 0 && e >= ROWS * BK) break;
+    const int i = L_CONTIG ? e / BK : e % ROWS;
+    const int l = L_CONTIG ? e % BK : e / ROWS;
     float v = 0.0f;
-    if (i0 + i < i_end && l0 + l < l_end)
+    if ((ROWS * BK % kThreads == 0 || e < ROWS * BK) && i0 + i < i_end && l0 + l < l_end)
       v = Elem<DT>::load(p, (int64_t)(i0 + i) * stride_i + (int64_t)(l0 + l) * stride_l);
-    sm[l][i] = v;
+    regs.v[r] = v;
+  }
+}
+
+template <bool L_CONTIG, int ROWS>
+__device__ __forceinline__ void block_commit(const BlockRegs<ROWS>& regs, float (*sm)[ROWS + kPad], int tid) {
+#pragma unroll
+  for (int r = 0; r < BlockRegs<ROWS>::kIters; ++r) {
+    const int e = tid + r * kThreads;
+    const int i = L_CONTIG ? e / BK : e % ROWS;
+    const int l = L_CONTIG ? e % BK : e / ROWS;
+    if (ROWS * BK % kThreads == 0 || e < ROWS * BK) sm[l][i] = regs.v[r];
   }
 }
 
@@ -94,10 +104,18 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
     const int lo = tt.lo(t), hi = tt.hi(t);
+    BlockRegs<BM> ra;
+    BlockRegs<BN> rb;
+    block_fetch<DT, true, BM>(xq, K, 1, m0, M, lo, hi, tid, ra);
+    block_fetch<DT, true, BN>(w_mod, K, 1, n0, N, lo, hi, tid, rb);
     for (int k0 = lo; k0 < hi; k0 += BK) {
-      stage_block<DT, true, BM>(xq, K, 1, m0, M, k0, hi, As, tid);
-      stage_block<DT, true, BN>(w_mod, K, 1, n0, N, k0, hi, Bs, tid);
+      block_commit<true, BM>(ra, As, tid);
+      block_commit<true, BN>(rb, Bs, tid);
       __syncthreads();
+      if (k0 + BK < hi) {
+        block_fetch<DT, true, BM>(xq, K, 1, m0, M, k0 + BK, hi, tid, ra);
+        block_fetch<DT, true, BN>(w_mod, K, 1, n0, N, k0 + BK, hi, tid, rb);
+      }
       mac_block<BM, BN>(As, Bs, ty, tx, acc);
       __syncthreads();
     }
@@ -203,11 +221,19 @@ bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
 
+  BlockRegs<TBM> ra;
+  BlockRegs<TBN> rb;
+  auto fetch = [&](int l0) {
+    if (WGRAD) block_fetch<DT, false, TBM>(g, 1, N, i0, I, l0, l_end, tid, ra);
+    else block_fetch<DT, true, TBM>(g, N, 1, i0, I, l0, l_end, tid, ra);
+    block_fetch<DT, false, TBN>(b_op, 1, K, j0, hi, l0, l_end, tid, rb);
+  };
+  if (l_begin < l_end) fetch(l_begin);
   for (int l0 = l_begin; l0 < l_end; l0 += BK) {
-    if (WGRAD) stage_block<DT, false, TBM>(g, 1, N, i0, I, l0, l_end, As, tid);
-    else stage_block<DT, true, TBM>(g, N, 1, i0, I, l0, l_end, As, tid);
-    stage_block<DT, false, TBN>(b_op, 1, K, j0, hi, l0, l_end, Bs, tid);
+    block_commit<!WGRAD, TBM>(ra, As, tid);
+    block_commit<false, TBN>(rb, Bs, tid);
     __syncthreads();
+    if (l0 + BK < l_end) fetch(l0 + BK);
     if (keep_mask != nullptr) {
       // zero the gradient entries the ADC clamp of this tile blocked
       for (int e = tid; e < TBM * BK; e += kThreads) {
