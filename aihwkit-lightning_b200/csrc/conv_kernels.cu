@@ -415,13 +415,16 @@ int al_fold2d(int32_t dtype, const void* grad_patches, int32_t B, int32_t C, int
   const int unit_chunk = dtype == AL_F32 && aligned16(grad_patches) ? fold_unit_chunk(g) : 0;
   if (unit_chunk >= 4 && bands * ((C + unit_chunk - 1) / unit_chunk) < 2147483647) {
     const unsigned grid = (unsigned)(bands * ((C + unit_chunk - 1) / unit_chunk));
-    static const cudaError_t attr = cudaFuncSetAttribute(fold2d_band_unit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                        (int)kFoldUnitMaxSmem);
-    if (attr != cudaSuccess) {
-      set_error("fold2d: shared-memory opt-in failed: %s", cudaGetErrorString(attr));
-      return AL_ERR_CUDA;
+    const size_t smem = fold_unit_smem(g, unit_chunk);
+    if (smem > 48 * 1024) {  // per device and cheap: no caching
+      const cudaError_t attr = cudaFuncSetAttribute(fold2d_band_unit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    (int)kFoldUnitMaxSmem);
+      if (attr != cudaSuccess) {
+        set_error("fold2d: shared-memory opt-in failed: %s", cudaGetErrorString(attr));
+        return AL_ERR_CUDA;
+      }
     }
-    fold2d_band_unit_kernel<<<grid, 256, fold_unit_smem(g, unit_chunk), (cudaStream_t)stream>>>(
+    fold2d_band_unit_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(
         reinterpret_cast<const float*>(grad_patches), g, unit_chunk, fold_unit_pitch(unit_chunk, kh * kw),
         reinterpret_cast<float*>(grad_x));
     return check_launch("fold2d_band_unit");
