@@ -2,7 +2,8 @@
 
 Public surface (same names as the reference package):
 
-* ``aihwkit_lightning_b200.nn``        ``AnalogLinear``, ``AnalogConv1d/2d/3d``, ``convert_to_analog``
+* ``aihwkit_lightning_b200.nn``        ``AnalogLinear``, ``AnalogConv1d/2d/3d``, ``AnalogRNN`` and its cells,
+                                       ``AnalogSequential``, ``AnalogWrapper``, ``convert_to_analog`` / ``convert_to_digital``
 * ``aihwkit_lightning_b200.simulator`` ``TorchInferenceRPUConfig`` and its parameter classes / enums
 * ``aihwkit_lightning_b200.optim``     ``AnalogOptimizer``
 * ``aihwkit_lightning_b200.inference`` ``calibrate_input_ranges``, ``InputRangeCalibrationType``
