@@ -122,12 +122,22 @@ def check(status: int) -> None:
     raise KernelError(status, detail)
 
 
+_TILE_ENDS: dict = {}
+
+
 def tile_ends_array(in_sizes):
-    ends, acc = [], 0
-    for size in in_sizes:
-        acc += int(size)
-        ends.append(acc)
-    return (c_int32 * len(ends))(*ends)
+    """``int32[T]`` of the tiles' upper ends; the (read-only) arrays are kept per tiling."""
+    key = tuple(in_sizes)
+    arr = _TILE_ENDS.get(key)
+    if arr is None:
+        ends, acc = [], 0
+        for size in key:
+            acc += int(size)
+            ends.append(acc)
+        if len(_TILE_ENDS) > 4096:
+            _TILE_ENDS.clear()
+        arr = _TILE_ENDS[key] = (c_int32 * len(ends))(*ends)
+    return arr
 
 
 def profile_read(reset: bool = True) -> dict:

@@ -72,8 +72,33 @@ def _ptr(t: Optional[Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)  # pylint: disable=protected-access
+
+
 def _stream(device) -> int:
+    """Handle of the current CUDA stream of ``device`` (the raw getter skips building a Stream object)."""
+    if _raw_stream is not None:
+        return _raw_stream(device.index if device.index is not None else torch.cuda.current_device())
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class _OnDevice:
+    """``with torch.cuda.device(dev)`` that costs nothing when ``dev`` is already current."""
+
+    __slots__ = ("guard",)
+
+    def __init__(self, device):
+        index = device.index
+        self.guard = None if index is None or index == torch.cuda.current_device() else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+        return False
 
 
 def _next_seed(device):
@@ -85,7 +110,30 @@ def _next_seed(device):
     return seed & 0xFFFFFFFFFFFFFFFF, offset
 
 
+_DESC_CACHE: dict = {}
+
+
 def make_desc(rpu_config, m: int, k: int, n: int, t: int, dtype, training: bool) -> "_lib.AlDesc":
+    """Flattened configuration of one call.  Descriptors are cached by VALUE of every field that
+    goes into them (the configuration objects are mutable), and handed out as copies."""
+    fwd, mod, clip = rpu_config.forward, rpu_config.modifier, rpu_config.clip
+    irp = rpu_config.pre_post.input_range
+    key = (m, k, n, t, dtype, training, irp.enable, irp.fast_mode, irp.dynamic, irp.init_from_data,
+           irp.init_std_alpha, irp.decay, irp.input_min_percentage, irp.act_range_momentum, fwd.inp_res,
+           fwd.out_res, fwd.out_bound, fwd.out_noise, fwd.out_noise_per_channel, mod.noise_type,
+           mod.quantization_type, mod.std_dev, mod.res, clip.type, settings.no_rounding,
+           settings.reference_rounding, settings.engine)
+    cached = _DESC_CACHE.get(key)
+    if cached is not None:
+        return _lib.AlDesc.from_buffer_copy(cached)
+    if len(_DESC_CACHE) > 4096:
+        _DESC_CACHE.clear()
+    d = _build_desc(rpu_config, m, k, n, t, dtype, training)
+    _DESC_CACHE[key] = _lib.AlDesc.from_buffer_copy(d)
+    return d
+
+
+def _build_desc(rpu_config, m: int, k: int, n: int, t: int, dtype, training: bool) -> "_lib.AlDesc":
     fwd, mod, clip = rpu_config.forward, rpu_config.modifier, rpu_config.clip
     irp = rpu_config.pre_post.input_range
     if dtype not in _DTYPE:
@@ -122,6 +170,15 @@ def make_desc(rpu_config, m: int, k: int, n: int, t: int, dtype, training: bool)
     return d
 
 
+class _NoGradCtx:
+    """Stands in for the autograd context when a call records nothing for a backward pass."""
+
+    needs_input_grad = (False,) * 12
+
+    def save_for_backward(self, *_):
+        return None
+
+
 class AnalogLinearFunction(torch.autograd.Function):
     """out = analog_linear(x, weight, bias) with the noisy / quantised tile model."""
 
@@ -129,52 +186,96 @@ class AnalogLinearFunction(torch.autograd.Function):
     def forward(ctx, inp, weight, bias, input_range, input_range_update_idx, in_sizes, training,
                 rpu_config, x_min=None, x_max=None, learnable_weight_clip=None,
                 grad_enabled=True):  # type: ignore[override]
-        lib = _lib.load()
-        if not inp.is_cuda or not weight.is_cuda:
-            raise ValueError(
-                "analog layers of this package run on CUDA tensors only (no CPU fallback): "
-                f"input on {inp.device}, weight on {weight.device}"
-            )
-        if inp.dtype != weight.dtype:
-            raise RuntimeError(f"input dtype {inp.dtype} and weight dtype {weight.dtype} differ")
-        n, k = weight.shape
-        if inp.shape[-1] != k:
-            raise RuntimeError(f"input has {inp.shape[-1]} features, the layer expects {k}")
-        x2d = inp.reshape(-1, k).contiguous()
-        m = x2d.shape[0]
-        w = weight.contiguous()
-        t = len(in_sizes)
-        dev, dtype = inp.device, inp.dtype
-        # needs_input_grad mirrors requires_grad of the inputs even under torch.no_grad(); the
-        # caller's grad mode arrives as an argument (inside forward it is always off)
-        needs_grad = grad_enabled and (any(ctx.needs_input_grad[:4]) or ctx.needs_input_grad[10])
-        desc = make_desc(rpu_config, m, k, n, t, dtype, training)
-        desc.save_for_backward = int(needs_grad)
-        ends = _lib.tile_ends_array(in_sizes)
-        static = desc.ir_mode in (_lib.AL_IR_STATIC, _lib.AL_IR_FAST)  # one stored range per tile
-        if static:
-            assert input_range is not None, "Input range must be provided"
-            assert input_range_update_idx is not None, "Input range update index must be provided"
-        if m == 0:
-            ctx.empty = True
-            return inp.new_zeros(*inp.shape[:-1], n) + (bias if bias is not None else 0)
-        ctx.empty = False
+        return _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx, in_sizes, training,
+                               rpu_config, x_min, x_max, learnable_weight_clip, grad_enabled)
 
-        with torch.cuda.device(dev):
-            out = torch.empty(m, n, device=dev, dtype=dtype)
-            args = _lib.AlForwardArgs()
-            args.x, args.w, args.bias, args.out = _ptr(x2d), _ptr(w), _ptr(bias), _ptr(out)
-            args.tile_ends = ends
-            ir_data = iridx_data = None
-            if static:
-                ir_data = input_range.data if input_range.is_contiguous() else input_range.data.contiguous()
-                iridx_data = input_range_update_idx
-                args.input_range, args.input_range_update_idx = _ptr(ir_data), _ptr(iridx_data)
-                if desc.ir_mode == _lib.AL_IR_FAST:
-                    assert x_min is not None and x_max is not None, "x_min and x_max must be provided"
-                    args.x_min, args.x_max = _ptr(x_min), _ptr(x_max)
-            xq = x2d
-            ir_rows = None
+    @staticmethod
+    def backward(ctx, grad_out):  # type: ignore[override]
+        return _analog_backward(ctx, grad_out)
+
+
+def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx, in_sizes, training,
+                    rpu_config, x_min, x_max, learnable_weight_clip, grad_enabled):
+    """One forward call of the library; ``ctx`` receives what the backward pass needs."""
+    lib = _lib.load()
+    if not inp.is_cuda or not weight.is_cuda:
+        raise ValueError(
+            "analog layers of this package run on CUDA tensors only (no CPU fallback): "
+            f"input on {inp.device}, weight on {weight.device}"
+        )
+    if inp.dtype != weight.dtype:
+        raise RuntimeError(f"input dtype {inp.dtype} and weight dtype {weight.dtype} differ")
+    n, k = weight.shape
+    if inp.shape[-1] != k:
+        raise RuntimeError(f"input has {inp.shape[-1]} features, the layer expects {k}")
+    x2d = inp.reshape(-1, k).contiguous()
+    m = x2d.shape[0]
+    w = weight.contiguous()
+    t = len(in_sizes)
+    dev, dtype = inp.device, inp.dtype
+    # needs_input_grad mirrors requires_grad of the inputs even under torch.no_grad(); the
+    # caller's grad mode arrives as an argument (inside forward it is always off)
+    needs_grad = grad_enabled and (any(ctx.needs_input_grad[:4]) or ctx.needs_input_grad[10])
+    desc = make_desc(rpu_config, m, k, n, t, dtype, training)
+    desc.save_for_backward = int(needs_grad)
+    ends = _lib.tile_ends_array(in_sizes)
+    static = desc.ir_mode in (_lib.AL_IR_STATIC, _lib.AL_IR_FAST)  # one stored range per tile
+    if static:
+        assert input_range is not None, "Input range must be provided"
+        assert input_range_update_idx is not None, "Input range update index must be provided"
+    if m == 0:
+        ctx.empty = True
+        return inp.new_zeros(*inp.shape[:-1], n) + (bias if bias is not None else 0)
+    ctx.empty = False
+
+    with _OnDevice(dev):
+        out = torch.empty(m, n, device=dev, dtype=dtype)
+        args = _lib.AlForwardArgs()
+        args.x, args.w, args.bias, args.out = _ptr(x2d), _ptr(w), _ptr(bias), _ptr(out)
+        args.tile_ends = ends
+        ir_data = iridx_data = None
+        if static:
+            ir_data = input_range.data if input_range.is_contiguous() else input_range.data.contiguous()
+            iridx_data = input_range_update_idx
+            args.input_range, args.input_range_update_idx = _ptr(ir_data), _ptr(iridx_data)
+            if desc.ir_mode == _lib.AL_IR_FAST:
+                assert x_min is not None and x_max is not None, "x_min and x_max must be provided"
+                args.x_min, args.x_max = _ptr(x_min), _ptr(x_max)
+        learn_clip = desc.clip_type == _CLIP[WeightClipType.LEARNABLE_PER_CHANNEL]
+        lwc = None
+        if learn_clip:
+            assert learnable_weight_clip is not None, "learnable_weight_clip should not be None"
+            assert tuple(learnable_weight_clip.shape) == (t, n), f"learnable_weight_clip.shape must be ({t}, {n})"
+            lwc = learnable_weight_clip.detach().to(dtype).contiguous()
+            args.learnable_weight_clip = _ptr(lwc)
+        modifies = desc.quant_type != 0 or (training and desc.noise_type != 0) or learn_clip
+        need_std = static and training and desc.init_from_data > 0
+        few_rows = m <= 16 and not needs_grad and dtype == torch.bfloat16 and settings.capture is None
+        xq = x2d
+        ir_rows = w_amax = w_tile_max = keep_mask = None
+        w_mod = w
+        if not needs_grad and settings.capture is None:
+            # nothing of the workspace outlives the call: one allocation, carved by offset
+            es = x2d.element_size()
+            plan = [("w_amax", t * n * es), ("w_tile_max", 2 * t * 4)]
+            if desc.ir_mode != _lib.AL_IR_OFF:
+                plan += [("xq", m * k * es), ("ir_rows", (t if static else t * m) * es)]
+            if modifies:
+                plan.append(("w_mod", n * k * es))
+            if need_std:
+                plan.append(("std_scratch", lib.al_std_scratch_floats(m, t) * 4))
+            if few_rows:
+                plan.append(("smallm_scratch", lib.al_smallm_scratch_floats(m, n, t) * 4))
+            total = 0
+            for _, nbytes in plan:
+                total += (nbytes + 255) & ~255
+            arena = torch.empty(total, device=dev, dtype=torch.uint8)
+            cursor = arena.data_ptr()
+            args.xq, args.w_mod = _ptr(x2d), _ptr(w)
+            for field, nbytes in plan:
+                setattr(args, field, cursor)
+                cursor += (nbytes + 255) & ~255
+        else:
             if desc.ir_mode != _lib.AL_IR_OFF:
                 xq = torch.empty_like(x2d)
                 ir_rows = torch.empty((t, m) if not static else (t,), device=dev, dtype=dtype)
@@ -182,103 +283,94 @@ class AnalogLinearFunction(torch.autograd.Function):
             w_amax = torch.empty(t, n, device=dev, dtype=dtype)
             w_tile_max = torch.empty(2 * t, device=dev, dtype=torch.float32)
             args.w_amax, args.w_tile_max = _ptr(w_amax), _ptr(w_tile_max)
-            learn_clip = desc.clip_type == _CLIP[WeightClipType.LEARNABLE_PER_CHANNEL]
-            lwc = None
-            if learn_clip:
-                assert learnable_weight_clip is not None, "learnable_weight_clip should not be None"
-                assert tuple(learnable_weight_clip.shape) == (t, n), f"learnable_weight_clip.shape must be ({t}, {n})"
-                lwc = learnable_weight_clip.detach().to(dtype).contiguous()
-                args.learnable_weight_clip = _ptr(lwc)
-            modifies = desc.quant_type != 0 or (training and desc.noise_type != 0) or learn_clip
             w_mod = torch.empty_like(w) if modifies else w
             args.w_mod = _ptr(w_mod)
-            keep_mask = None
             if desc.out_bound > 0 and needs_grad:
                 keep_mask = torch.empty(t, (n + 31) // 32, m, device=dev, dtype=torch.int32)
             args.keep_mask = _ptr(keep_mask)
             std_scratch = None
-            if static and training and desc.init_from_data > 0:
+            if need_std:
                 std_scratch = torch.empty(lib.al_std_scratch_floats(m, t), device=dev, dtype=torch.float32)
             args.std_scratch = _ptr(std_scratch)
             smallm_scratch = None
-            if m <= 16 and not needs_grad and dtype == torch.bfloat16 and settings.capture is None:
+            if few_rows:
                 smallm_scratch = torch.empty(lib.al_smallm_scratch_floats(m, n, t), device=dev, dtype=torch.float32)
             args.smallm_scratch = _ptr(smallm_scratch)
-            w_noise, out_noise = settings.w_noise, settings.out_noise
-            if w_noise is not None:
-                w_noise = w_noise.to(device=dev, dtype=dtype).contiguous()
-                assert w_noise.shape == w.shape, "replayed weight noise must be [N,K]"
-            if out_noise is not None:
-                out_noise = out_noise.to(device=dev, dtype=dtype).contiguous()
-                assert out_noise.numel() == t * m * n, "replayed output noise must be [T,M,N]"
-            args.w_noise, args.out_noise = _ptr(w_noise), _ptr(out_noise)
-            codes = None
-            if settings.capture is not None and settings.capture_codes and desc.ir_mode != _lib.AL_IR_OFF:
-                codes = torch.empty_like(x2d)
-            args.codes = _ptr(codes)
-            if training and (desc.noise_type != 0 or desc.out_noise > 0):
-                args.seed, args.offset = _next_seed(dev)
-            _lib.check(lib.al_forward(desc, args, _stream(dev)))
-            if static and ir_data is not input_range.data:
-                input_range.data.copy_(ir_data)
+        w_noise, out_noise = settings.w_noise, settings.out_noise
+        if w_noise is not None:
+            w_noise = w_noise.to(device=dev, dtype=dtype).contiguous()
+            assert w_noise.shape == w.shape, "replayed weight noise must be [N,K]"
+        if out_noise is not None:
+            out_noise = out_noise.to(device=dev, dtype=dtype).contiguous()
+            assert out_noise.numel() == t * m * n, "replayed output noise must be [T,M,N]"
+        args.w_noise, args.out_noise = _ptr(w_noise), _ptr(out_noise)
+        codes = None
+        if settings.capture is not None and settings.capture_codes and desc.ir_mode != _lib.AL_IR_OFF:
+            codes = torch.empty_like(x2d)
+        args.codes = _ptr(codes)
+        if training and (desc.noise_type != 0 or desc.out_noise > 0):
+            args.seed, args.offset = _next_seed(dev)
+        _lib.check(lib.al_forward(desc, args, _stream(dev)))
+        if static and ir_data is not input_range.data:
+            input_range.data.copy_(ir_data)
 
-        if settings.capture is not None:
-            settings.capture.update(
-                codes=codes, xq=xq, ir_rows=ir_rows, w_amax=w_amax, w_tile_max=w_tile_max[:t],
-                w_mod=w_mod, keep_mask=keep_mask,
-                uses_tcgen05=bool(lib.al_uses_tcgen05(desc, ends)),
-            )
-        ctx.desc, ctx.in_sizes = desc, list(in_sizes)
-        ctx.shape = tuple(inp.shape)
-        ctx.has_bias = bias is not None
-        ctx.ir_needs_grad = static and input_range is not None and input_range.requires_grad
-        ctx.learn_clip = learn_clip
-        if needs_grad:
-            ctx.save_for_backward(x2d if static else None, xq, w_mod, ir_rows, keep_mask,
-                                  w if learn_clip else None, lwc)
-        return out.view(*inp.shape[:-1], n)
+    if settings.capture is not None:
+        settings.capture.update(
+            codes=codes, xq=xq, ir_rows=ir_rows, w_amax=w_amax, w_tile_max=w_tile_max[:t],
+            w_mod=w_mod, keep_mask=keep_mask,
+            uses_tcgen05=bool(lib.al_uses_tcgen05(desc, ends)),
+        )
+    ctx.desc, ctx.in_sizes = desc, list(in_sizes)
+    ctx.shape = tuple(inp.shape)
+    ctx.has_bias = bias is not None
+    ctx.ir_needs_grad = static and input_range is not None and input_range.requires_grad
+    ctx.learn_clip = learn_clip
+    if needs_grad:
+        ctx.save_for_backward(x2d if static else None, xq, w_mod, ir_rows, keep_mask,
+                              w if learn_clip else None, lwc)
+    return out.view(*inp.shape[:-1], n)
 
-    @staticmethod
-    def backward(ctx, grad_out):  # type: ignore[override]
-        if ctx.empty:
-            return (None,) * 12
-        lib = _lib.load()
-        x2d, xq, w_mod, ir_rows, keep_mask, w_saved, lwc = ctx.saved_tensors
-        desc = ctx.desc
-        m, k, n, t = desc.M, desc.K, desc.N, desc.T
-        dev, dtype = grad_out.device, xq.dtype
-        g = grad_out.reshape(m, n).to(dtype).contiguous()
-        need_x, need_w, need_b, need_ir = ctx.needs_input_grad[:4]
-        need_b = need_b and ctx.has_bias
-        need_ir = need_ir and ctx.ir_needs_grad
-        need_clip = ctx.learn_clip and (ctx.needs_input_grad[10] or need_w)
-        need_w = need_w or need_clip
-        with torch.cuda.device(dev):
-            args = _lib.AlBackwardArgs()
-            ends = _lib.tile_ends_array(ctx.in_sizes)
-            args.tile_ends = ends
-            args.grad_out, args.x, args.xq, args.w_mod = _ptr(g), _ptr(x2d), _ptr(xq), _ptr(w_mod)
-            args.ir_rows, args.keep_mask = _ptr(ir_rows), _ptr(keep_mask)
-            grad_x = torch.empty(m, k, device=dev, dtype=dtype) if (need_x or need_ir) else None
-            grad_w = torch.empty(n, k, device=dev, dtype=dtype) if need_w else None
-            grad_b = torch.empty(n, device=dev, dtype=dtype) if need_b else None
-            grad_ir = torch.empty(t, device=dev, dtype=dtype) if need_ir else None
-            scratch = torch.empty(lib.al_backward_scratch_floats(m, k, n, t), device=dev, dtype=torch.float32)
-            args.grad_x, args.grad_w, args.grad_bias = _ptr(grad_x), _ptr(grad_w), _ptr(grad_b)
-            args.grad_input_range, args.reduce_scratch = _ptr(grad_ir), _ptr(scratch)
-            grad_clip = None
-            if need_clip:
-                grad_clip = torch.empty(t, n, device=dev, dtype=dtype)
-                args.w, args.learnable_weight_clip = _ptr(w_saved), _ptr(lwc)
-                args.grad_weight_clip = _ptr(grad_clip)
-            _lib.check(lib.al_backward(desc, args, _stream(dev)))
-        if grad_x is not None:
-            grad_x = grad_x.view(ctx.shape) if need_x else None
-        if not ctx.needs_input_grad[1]:
-            grad_w = None
-        if not ctx.needs_input_grad[10]:
-            grad_clip = None
-        return grad_x, grad_w, grad_b, grad_ir, None, None, None, None, None, None, grad_clip, None
+def _analog_backward(ctx, grad_out):
+    """The matching backward call: gradients of input, weight, bias, input range and weight ranges."""
+    if ctx.empty:
+        return (None,) * 12
+    lib = _lib.load()
+    x2d, xq, w_mod, ir_rows, keep_mask, w_saved, lwc = ctx.saved_tensors
+    desc = ctx.desc
+    m, k, n, t = desc.M, desc.K, desc.N, desc.T
+    dev, dtype = grad_out.device, xq.dtype
+    g = grad_out.reshape(m, n).to(dtype).contiguous()
+    need_x, need_w, need_b, need_ir = ctx.needs_input_grad[:4]
+    need_b = need_b and ctx.has_bias
+    need_ir = need_ir and ctx.ir_needs_grad
+    need_clip = ctx.learn_clip and (ctx.needs_input_grad[10] or need_w)
+    need_w = need_w or need_clip
+    with _OnDevice(dev):
+        args = _lib.AlBackwardArgs()
+        ends = _lib.tile_ends_array(ctx.in_sizes)
+        args.tile_ends = ends
+        args.grad_out, args.x, args.xq, args.w_mod = _ptr(g), _ptr(x2d), _ptr(xq), _ptr(w_mod)
+        args.ir_rows, args.keep_mask = _ptr(ir_rows), _ptr(keep_mask)
+        grad_x = torch.empty(m, k, device=dev, dtype=dtype) if (need_x or need_ir) else None
+        grad_w = torch.empty(n, k, device=dev, dtype=dtype) if need_w else None
+        grad_b = torch.empty(n, device=dev, dtype=dtype) if need_b else None
+        grad_ir = torch.empty(t, device=dev, dtype=dtype) if need_ir else None
+        scratch = torch.empty(lib.al_backward_scratch_floats(m, k, n, t), device=dev, dtype=torch.float32)
+        args.grad_x, args.grad_w, args.grad_bias = _ptr(grad_x), _ptr(grad_w), _ptr(grad_b)
+        args.grad_input_range, args.reduce_scratch = _ptr(grad_ir), _ptr(scratch)
+        grad_clip = None
+        if need_clip:
+            grad_clip = torch.empty(t, n, device=dev, dtype=dtype)
+            args.w, args.learnable_weight_clip = _ptr(w_saved), _ptr(lwc)
+            args.grad_weight_clip = _ptr(grad_clip)
+        _lib.check(lib.al_backward(desc, args, _stream(dev)))
+    if grad_x is not None:
+        grad_x = grad_x.view(ctx.shape) if need_x else None
+    if not ctx.needs_input_grad[1]:
+        grad_w = None
+    if not ctx.needs_input_grad[10]:
+        grad_clip = None
+    return grad_x, grad_w, grad_b, grad_ir, None, None, None, None, None, None, grad_clip, None
 
 
 def analog_linear(inp: Tensor, weight: Tensor, bias: Optional[Tensor], input_range: Optional[Tensor],
@@ -286,6 +378,14 @@ def analog_linear(inp: Tensor, weight: Tensor, bias: Optional[Tensor], input_ran
                   rpu_config, x_min: Optional[Tensor] = None, x_max: Optional[Tensor] = None,
                   learnable_weight_clip: Optional[Tensor] = None) -> Tensor:
     """Functional form used by ``AnalogLinear`` and ``AnalogConv2d``."""
+    grad = torch.is_grad_enabled()
+    if not grad or not (inp.requires_grad or weight.requires_grad
+                        or (bias is not None and bias.requires_grad)
+                        or (input_range is not None and input_range.requires_grad)
+                        or (learnable_weight_clip is not None and learnable_weight_clip.requires_grad)):
+        # nothing to differentiate: skip the autograd machinery altogether
+        return _analog_forward(_NoGradCtx(), inp, weight, bias, input_range, input_range_update_idx, in_sizes,
+                               training, rpu_config, x_min, x_max, learnable_weight_clip, False)
     return AnalogLinearFunction.apply(inp, weight, bias, input_range, input_range_update_idx,
                                       in_sizes, training, rpu_config, x_min, x_max, learnable_weight_clip,
                                       torch.is_grad_enabled())
@@ -300,7 +400,7 @@ def sliced_abs_max(in_sizes: List[int], weights: Tensor) -> Tensor:
         raise ValueError("sliced_abs_max runs on CUDA tensors only")
     w = weights.detach().contiguous()
     out = torch.empty(len(in_sizes), w.shape[0], device=w.device, dtype=w.dtype)
-    with torch.cuda.device(w.device):
+    with _OnDevice(w.device):
         _lib.check(lib.al_abs_max_tiles(_DTYPE[w.dtype], w.data_ptr(), w.shape[0], w.shape[1],
                                         _lib.tile_ends_array(in_sizes), len(in_sizes), out.data_ptr(),
                                         _stream(w.device)))
@@ -315,7 +415,7 @@ def sliced_std(in_sizes: List[int], values: Tensor) -> Tensor:
     t = len(in_sizes)
     out = torch.empty(t, device=v.device, dtype=torch.float32)
     scratch = torch.empty(lib.al_std_scratch_floats(v.shape[0], t), device=v.device, dtype=torch.float32)
-    with torch.cuda.device(v.device):
+    with _OnDevice(v.device):
         _lib.check(lib.al_std_tiles(_DTYPE[v.dtype], v.data_ptr(), v.shape[0], v.shape[1],
                                     _lib.tile_ends_array(in_sizes), t, out.data_ptr(), scratch.data_ptr(),
                                     _stream(v.device)))
@@ -337,7 +437,7 @@ def clip_weights_(weight: Tensor, clip_type: WeightClipType, sigma: float) -> No
     rows = w.shape[0]
     cols = w.numel() // rows
     scratch = torch.empty(2 * rows + 8, device=w.device, dtype=torch.float32)
-    with torch.cuda.device(w.device):
+    with _OnDevice(w.device):
         _lib.check(lib.al_clip_weights(_DTYPE[w.dtype], w.data_ptr(), rows, cols, _CLIP[clip_type],
                                        float(sigma), scratch.data_ptr(), _stream(w.device)))
 
@@ -361,7 +461,7 @@ class Unfold2dFunction(torch.autograd.Function):
         wo = (w + 2 * pw - dw * (kw - 1) - 1) // sw + 1
         out = torch.empty(b, max(ho, 0) * max(wo, 0), c * kh * kw, device=x.device, dtype=x.dtype)
         geom = (b, c, h, w, kh, kw, sh, sw, ph, pw, dh, dw)
-        with torch.cuda.device(x.device):
+        with _OnDevice(x.device):
             _lib.check(lib.al_unfold2d(_DTYPE[x.dtype], xc.data_ptr(), *geom, out.data_ptr(), _stream(x.device)))
         ctx.geom, ctx.dtype_code = geom, _DTYPE[x.dtype]
         return out
@@ -372,7 +472,7 @@ class Unfold2dFunction(torch.autograd.Function):
         gp = grad_patches.contiguous()
         b, c, h, w = ctx.geom[:4]
         gx = torch.empty(b, c, h, w, device=gp.device, dtype=gp.dtype)
-        with torch.cuda.device(gp.device):
+        with _OnDevice(gp.device):
             _lib.check(lib.al_fold2d(ctx.dtype_code, gp.data_ptr(), *ctx.geom, gx.data_ptr(), _stream(gp.device)))
         return gx, None, None, None, None
 
