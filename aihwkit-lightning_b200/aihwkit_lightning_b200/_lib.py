@@ -80,6 +80,7 @@ SYMBOLS = {
     "al_fold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
     "al_read_device_error": (c_int32, [c_void_p, POINTER(c_uint32)]),
     "al_uses_tcgen05": (c_int32, [POINTER(AlDesc), POINTER(c_int32)]),
+    "al_reserve_sms": (c_int32, [c_int32]),
     "al_profile_enable": (c_int32, [c_int32]),
     "al_profile_read": (c_int32, [POINTER(AlProfileEntry), c_int32]),
     "al_kernel_class_name": (c_char_p, [c_int32]),

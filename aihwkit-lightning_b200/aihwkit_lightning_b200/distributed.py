@@ -112,3 +112,62 @@ def all_reduce_gradients(params: Sequence[torch.nn.Parameter], group: Optional[d
     buckets = GradientBuckets(params, bucket_bytes=bucket_bytes, group=group)
     buckets.reduce_all_async()
     buckets.finish()
+
+
+class EagerGradientSync:
+    """Sums gradients over the replicas while the backward pass is still running.
+
+    ``attach(params)`` registers a post-accumulate hook on every parameter: as soon as autograd
+    has stored a gradient, its all-reduce (in place, on ``param.grad``) is issued on a side stream.
+    Installed as ``nn.functional.settings.after_wgrad`` the instance is also told the moment an
+    analog layer's weight-gradient kernels are enqueued -- before its input-gradient kernels --
+    and the exchange of that gradient then waits only for that point, so it runs beside the
+    input-gradient kernels.  ``finish()`` makes the compute stream wait for all exchanges and
+    averages; call it before the optimizer step.
+    """
+
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, average: bool = True):
+        self.group = group
+        self.average = average
+        self.side: Optional[torch.cuda.Stream] = None
+        self._ready: dict = {}  # data_ptr of a weight gradient -> event recorded when it was enqueued
+        self._pending: List[Tuple[torch.Tensor, "dist.Work"]] = []
+
+    def attach(self, params: Iterable[torch.nn.Parameter]) -> "EagerGradientSync":
+        for p in params:
+            if p.requires_grad:
+                p.register_post_accumulate_grad_hook(self._reduce)
+        return self
+
+    def __call__(self, grad: torch.Tensor) -> None:
+        """``after_wgrad`` hook: remember when this gradient was complete on the compute stream
+        (only its address is kept: a second reference would make autograd copy the tensor)."""
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(grad.device))
+        if len(self._ready) > 64:
+            self._ready.clear()
+        self._ready[grad.data_ptr()] = ready
+
+    def _reduce(self, param: torch.nn.Parameter) -> None:
+        grad = param.grad
+        if grad is None or not grad.is_cuda:
+            return
+        if self.side is None:
+            self.side = torch.cuda.Stream(grad.device)
+        # the early event is only valid if autograd kept the very tensor the layer produced
+        ready = self._ready.pop(grad.data_ptr(), None)
+        if ready is None:
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(grad.device))
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ready)
+            work = dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        self._pending.append((grad, work))
+
+    def finish(self) -> None:
+        world = dist.get_world_size(self.group)
+        for grad, work in self._pending:
+            work.wait()  # the current (compute) stream waits for the exchange
+            if self.average:
+                grad.div_(world)
+        self._pending.clear()

@@ -47,6 +47,11 @@ class _Settings:
     w_noise: Optional[Tensor] = None  # shared-noise parity mode: [N,K] standard normals
     out_noise: Optional[Tensor] = None  # [T,M,N] standard normals
     capture: Optional[dict] = None  # when a dict: filled with the intermediates of each call
+    # callable(weight_grad) run inside backward as soon as the weight-gradient kernels are enqueued and
+    # before the input-gradient ones (data-parallel training starts the gradient exchange there)
+    after_wgrad = None
+    # with ``after_wgrad``: SMs the input-gradient GEMM leaves unoccupied for the exchange kernel
+    comm_sms = 0
 
 
 settings = _Settings()
@@ -363,7 +368,27 @@ def _analog_backward(ctx, grad_out):
             grad_clip = torch.empty(t, n, device=dev, dtype=dtype)
             args.w, args.learnable_weight_clip = _ptr(w_saved), _ptr(lwc)
             args.grad_weight_clip = _ptr(grad_clip)
-        _lib.check(lib.al_backward(desc, args, _stream(dev)))
+        hook = settings.after_wgrad
+        if hook is not None and grad_w is not None and grad_x is not None:
+            # weight-side gradients first: their exchange between replicas can then run while the
+            # input gradient is still being computed
+            args.grad_x = args.grad_input_range = None
+            _lib.check(lib.al_backward(desc, args, _stream(dev)))
+            hook(grad_w)
+            args.grad_x, args.grad_input_range = _ptr(grad_x), _ptr(grad_ir)
+            args.grad_w = args.grad_bias = args.grad_weight_clip = None
+            if settings.comm_sms > 0:
+                lib.al_reserve_sms(int(settings.comm_sms))
+                try:
+                    _lib.check(lib.al_backward(desc, args, _stream(dev)))
+                finally:
+                    lib.al_reserve_sms(0)
+            else:
+                _lib.check(lib.al_backward(desc, args, _stream(dev)))
+        else:
+            _lib.check(lib.al_backward(desc, args, _stream(dev)))
+            if hook is not None and grad_w is not None:
+                hook(grad_w)
     if grad_x is not None:
         grad_x = grad_x.view(ctx.shape) if need_x else None
     if not ctx.needs_input_grad[1]:

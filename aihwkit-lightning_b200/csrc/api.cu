@@ -142,6 +142,14 @@ static bool pick_tc(const AlDesc& d, const TileTable& tt, bool backward) {
 
 }  // namespace al
 
+namespace {
+thread_local int g_reserved_sms = 0;
+}  // namespace
+
+namespace al {
+int comm_reserved_sms() { return g_reserved_sms; }
+}  // namespace al
+
 using namespace al;
 
 extern "C" {
@@ -582,6 +590,12 @@ ProfScope::~ProfScope() {
 }  // namespace al
 
 extern "C" {
+
+int al_reserve_sms(int32_t n) {
+  const int before = g_reserved_sms;
+  g_reserved_sms = n < 0 ? 0 : n;
+  return before;
+}
 
 int al_profile_enable(int on) {
   std::lock_guard<std::mutex> lock(g_prof_mu);

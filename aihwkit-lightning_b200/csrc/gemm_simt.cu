@@ -221,6 +221,9 @@ bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
 
+  // threads whose 4x4 outputs all lie outside C (a 256-wide block on a 144-wide tile leaves whole
+  // warps without work) skip the multiply-adds; they still help staging the operands
+  const bool owns_output = i0 + ty * 4 < I && j0 + tx * 4 < hi;
   BlockRegs<TBM> ra;
   BlockRegs<TBN> rb;
   auto fetch = [&](int l0) {
@@ -247,7 +250,7 @@ bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
       }
       __syncthreads();
     }
-    mac_block<TBM, TBN>(As, Bs, ty, tx, acc);
+    if (owns_output) mac_block<TBM, TBN>(As, Bs, ty, tx, acc);
     __syncthreads();
   }
 #pragma unroll

@@ -756,7 +756,9 @@ static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint
   }
   // CTA pairs (256-row blocks) when they fill the machine; single CTAs for smaller problems
   const int pair_work = ((p.I + 2 * BM - 1) / (2 * BM)) * p.T * p.num_jb;
-  const int pairs = max_pairs(wgrad);
+  int pairs = max_pairs(wgrad);
+  const int keep_free = comm_reserved_sms();
+  if (pairs > 1 && keep_free > 0) pairs = pairs - (keep_free + 1) / 2 > 1 ? pairs - (keep_free + 1) / 2 : 1;
   if (pairs > 0 && pairing >= 0 && (pair_work >= pairs || pairing > 0)) {
     p.num_ib = (p.I + 2 * BM - 1) / (2 * BM);
     rc = wgrad ? ensure_smem(bwd_tc_pair_kernel<true>, P_SMEM) : ensure_smem(bwd_tc_pair_kernel<false>, P_SMEM);
@@ -769,7 +771,8 @@ static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint
     return check_launch(wgrad ? "wgrad_tc_pair" : "dgrad_tc_pair");
   }
   int work = p.num_ib * p.T * p.num_jb;
-  int grid = work < sm_count() ? work : sm_count();
+  const int sms = sm_count() - keep_free > 1 ? sm_count() - keep_free : 1;
+  int grid = work < sms ? work : sms;
   if (wgrad)
     bwd_tc_kernel<true><<<grid, kBwdThreads, B_SMEM, s>>>(map_a, map_b, p);
   else

@@ -64,6 +64,10 @@ struct ProfScope {
 };
 int check_launch(const char* what);
 
+// SMs the calling thread asked the backward GEMMs to leave unoccupied (al_reserve_sms), so that a
+// communication kernel enqueued beside them finds room to run.
+int comm_reserved_sms();
+
 // ---- reductions (reduce_kernels.cu) -------------------------------------------------------
 int launch_abs_max_tiles(int dtype, const void* a, int rows, int K, const TileTable& tt,
                          void* out, cudaStream_t s);

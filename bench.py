@@ -215,7 +215,7 @@ def main():
     import torch.distributed as dist
 
     from aihwkit_lightning_b200 import _lib
-    from aihwkit_lightning_b200.distributed import GradientBuckets, rank_seed
+    from aihwkit_lightning_b200.distributed import EagerGradientSync, GradientBuckets, rank_seed
     from aihwkit_lightning_b200.nn import AnalogLinear
     from aihwkit_lightning_b200.nn import functional as F
     from aihwkit_lightning_b200.simulator import configs as cfg
@@ -236,7 +236,19 @@ def main():
     layer = AnalogLinear(K, N, bias=False, rpu_config=make_rpu_config(cfg)).to(device=dev, dtype=torch.bfloat16)
     layer.train()
     torch.cuda.manual_seed(rank_seed(0, rank))  # independent analog noise per replica
-    buckets = GradientBuckets(layer.parameters()) if world > 1 else None
+    # The only exchange step of data-parallel training: the weight gradient is summed over ranks.
+    # "eager" (BENCH_GRAD_SYNC=eager): the layer hands its weight gradient over as soon as it is enqueued, the
+    # all-reduce runs beside the input-gradient kernels and is complete when the step ends.
+    # "deferred" (default): the all-reduce of step i runs beside step i+1.
+    eager = os.environ.get("BENCH_GRAD_SYNC", "deferred") == "eager"
+    buckets = GradientBuckets(layer.parameters()) if world > 1 and not eager else None
+    sync = EagerGradientSync().attach(layer.parameters()) if world > 1 and eager else None
+    if sync is not None:
+        from aihwkit_lightning_b200.nn import functional as analog_functional
+        analog_functional.settings.after_wgrad = sync
+        # dgrad of this layer has 512 blocks of 256x256: 64 CTA pairs take them in exactly 8 rounds
+        # and leave 20 of the 148 SMs to the all-reduce kernel that runs beside it
+        analog_functional.settings.comm_sms = int(os.environ.get("BENCH_COMM_SMS", "20"))
     x_dev = x_host.to(dev).requires_grad_(True)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev)
@@ -246,8 +258,9 @@ def main():
         x_dev.grad = None
         out = layer(x_dev)
         out.backward(g)
+        if sync is not None:
+            sync.finish()
         if buckets is not None:
-            # the only exchange step of data-parallel training: sum the weight gradient over ranks
             buckets.finish()  # previous step's all-reduce (overlapped with this step's kernels)
             buckets.reduce_all_async()
 
@@ -284,6 +297,8 @@ def main():
         loss = (out * g).sum(dtype=torch.float32)
         loss.backward()
         consumed[slot].record(stream)
+        if sync is not None:
+            sync.finish()
         if buckets is not None:
             buckets.reduce_all_async()
             buckets.finish()
@@ -367,6 +382,11 @@ def main():
         d_launches, d_timed, d_ms = prof[dominant]
         achieved = gemm_flop[dominant] / (d_ms / max(d_timed, 1) * 1e-3) / 1e12 if d_ms > 0 else 0.0
         rec = base_record(args, world)
+        if world > 1:
+            rec["config"]["grad_sync"] = (
+                "NCCL all-reduce of the weight gradient, started inside backward after the weight-gradient kernels, "
+                "complete at step end" if eager else
+                "NCCL all-reduce of the weight gradient of step i overlapped with step i+1")
         rec.update({
             "value": value,
             "ms_per_step": ms_per_step,

@@ -243,6 +243,14 @@ typedef struct AlProfileEntry {
   int64_t timed;      /* scopes that were timed with events                                 */
   double total_ms;    /* summed event time of the timed scopes                              */
 } AlProfileEntry;
+/* Data-parallel training overlaps the exchange of a layer's weight gradient with the computation
+ * of its input gradient (the reference leaves that to DeepSpeed / DDP around
+ * `TorchLinear.linear`'s autograd, P/torch_linear.py:116-314).  The backward GEMMs are persistent
+ * kernels that occupy every SM, so a communication kernel enqueued beside them would only start
+ * when they end: after al_reserve_sms(n) the backward GEMMs launched by the calling thread leave
+ * n SMs unoccupied (n = 0 restores the default).  Returns the previous value. */
+int al_reserve_sms(int32_t n);
+
 int al_profile_enable(int on);
 int al_profile_read(AlProfileEntry* out, int reset);
 const char* al_kernel_class_name(int kernel_class);

@@ -252,3 +252,37 @@ def test_conv1d_conversion_and_checkpoint_use_pytorch_weight_shape():
     assert isinstance(convert_to_analog(torch.nn.Conv3d(1, 2, 3), rpu), AnalogConv3d)
     with pytest.raises(ValueError):
         AnalogConv1d(3, 4, 3, dilation=2, rpu_config=rpu)
+
+
+
+def test_after_wgrad_hook_gets_the_weight_gradient_before_the_input_gradient_is_enqueued():
+    """Data-parallel training starts its gradient exchange from this hook: it must see the final
+    weight gradient tensor, and splitting backward around it must not change any result."""
+    from aihwkit_lightning_b200.nn import AnalogLinear
+    from aihwkit_lightning_b200.nn import functional as F
+    from aihwkit_lightning_b200.simulator.configs import TorchInferenceRPUConfig
+
+    rpu = TorchInferenceRPUConfig()
+    rpu.mapping.max_input_size = 64
+    rpu.forward.inp_res = 254
+    rpu.forward.out_res = 254
+    rpu.forward.out_bound = 10.0
+    rpu.pre_post.input_range.enable = True
+    rpu.pre_post.input_range.dynamic = False
+    rpu.pre_post.input_range.init_from_data = 0
+    rpu.pre_post.input_range.init_value = 2.0
+    torch.manual_seed(0)
+    layer = AnalogLinear(128, 96, bias=True, rpu_config=rpu).cuda().train()
+    x = torch.randn(40, 128, device="cuda", requires_grad=True)
+    g = torch.randn(40, 96, device="cuda")
+    layer(x).backward(g)
+    want = [t.detach().clone() for t in (x.grad, layer.weight.grad, layer.bias.grad, layer.input_range.grad)]
+    layer.zero_grad(set_to_none=True)
+    x.grad = None
+    seen = []  # addresses only: holding the tensor would make autograd store a copy instead of it
+    with F.operator_settings(after_wgrad=lambda grad: seen.append((grad.data_ptr(), tuple(grad.shape)))):
+        layer(x).backward(g)
+    assert seen == [(layer.weight.grad.data_ptr(), (96, 128))]
+    for got, ref in zip((x.grad, layer.weight.grad, layer.bias.grad, layer.input_range.grad), want):
+        assert torch.equal(got, ref)
+
