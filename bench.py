@@ -237,18 +237,20 @@ def main():
     layer.train()
     torch.cuda.manual_seed(rank_seed(0, rank))  # independent analog noise per replica
     # The only exchange step of data-parallel training: the weight gradient is summed over ranks.
-    # "eager" (BENCH_GRAD_SYNC=eager): the layer hands its weight gradient over as soon as it is enqueued, the
-    # all-reduce runs beside the input-gradient kernels and is complete when the step ends.
-    # "deferred" (default): the all-reduce of step i runs beside step i+1.
-    eager = os.environ.get("BENCH_GRAD_SYNC", "deferred") == "eager"
+    # "eager" (default): the all-reduce of the weight gradient is issued from a hook inside backward and
+    # is complete when the step ends, as an optimizer step would need it.
+    # "deferred" (BENCH_GRAD_SYNC=deferred): the all-reduce of step i runs beside step i+1 (a step then
+    # ends with a gradient that is one step old; measured 4 % faster on 2 GPUs, not the default).
+    eager = os.environ.get("BENCH_GRAD_SYNC", "eager") != "deferred"
     buckets = GradientBuckets(layer.parameters()) if world > 1 and not eager else None
     sync = EagerGradientSync().attach(layer.parameters()) if world > 1 and eager else None
     if sync is not None:
         from aihwkit_lightning_b200.nn import functional as analog_functional
         analog_functional.settings.after_wgrad = sync
-        # dgrad of this layer has 512 blocks of 256x256: 64 CTA pairs take them in exactly 8 rounds
-        # and leave 20 of the 148 SMs to the all-reduce kernel that runs beside it
-        analog_functional.settings.comm_sms = int(os.environ.get("BENCH_COMM_SMS", "20"))
+        # SMs the input-gradient GEMM leaves to the all-reduce kernel beside it.  Measured on 2 GPUs:
+        # with 20 SMs free (64 CTA pairs = 8 full rounds of the 512 output blocks) the GEMM takes 39 us
+        # longer and the exposed all-reduce 45 us less -- no net gain, so the default is 0.
+        analog_functional.settings.comm_sms = int(os.environ.get("BENCH_COMM_SMS", "0"))
     x_dev = x_host.to(dev).requires_grad_(True)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev)
