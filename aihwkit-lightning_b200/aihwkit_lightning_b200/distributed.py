@@ -150,7 +150,10 @@ class EagerGradientSync:
 
     def _reduce(self, param: torch.nn.Parameter) -> None:
         grad = param.grad
-        if grad is None or not grad.is_cuda:
+        if grad is None:
+            return
+        if not grad.is_cuda:  # host tensors (gloo): no streams to order, the exchange itself is asynchronous
+            self._pending.append((grad, dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=self.group, async_op=True)))
             return
         if self.side is None:
             self.side = torch.cuda.Stream(grad.device)

@@ -9,7 +9,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from aihwkit_lightning_b200.distributed import GradientBuckets, all_reduce_gradients, rank_seed, shard_rows
+from aihwkit_lightning_b200.distributed import (
+    EagerGradientSync, GradientBuckets, all_reduce_gradients, rank_seed, shard_rows)
 
 
 def test_shard_rows_partition():
@@ -88,3 +89,39 @@ def test_bucketed_all_reduce_two_gloo_ranks(tmp_path):
             assert y is None
         else:
             assert torch.equal(x, y)  # replicas hold bit-identical averaged gradients
+
+
+def _eager_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)  # identical replicas
+        model = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 3))
+        model[2].bias.requires_grad_(False)
+        sync = EagerGradientSync().attach(model.parameters())
+        x = torch.randn(4, 6, generator=torch.Generator().manual_seed(10 + rank))  # per-rank batch
+        # the hook fires from inside backward, once per parameter that received a gradient
+        model(x).square().sum().backward()
+        assert len(sync._pending) == 3  # pylint: disable=protected-access
+        local = model(x).square().sum()
+        want = torch.autograd.grad(local, [p for p in model.parameters() if p.requires_grad])
+        sync.finish()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, [g.clone() for g in want])
+        trainable = [p for p in model.parameters() if p.requires_grad]
+        for i, p in enumerate(trainable):
+            mean = sum(g[i] for g in gathered) / world
+            assert torch.allclose(p.grad, mean, rtol=1e-6, atol=1e-7), i
+        assert model[2].bias.grad is None
+        torch.save([p.grad for p in trainable], os.path.join(out_dir, f"e{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_eager_gradient_sync_two_gloo_ranks(tmp_path):
+    world = 2
+    mp.spawn(_eager_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for x, y in zip(torch.load(tmp_path / "e0.pt"), torch.load(tmp_path / "e1.pt")):
+        assert torch.equal(x, y)
+
