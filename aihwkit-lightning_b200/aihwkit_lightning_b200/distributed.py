@@ -132,6 +132,7 @@ class EagerGradientSync:
         self.side: Optional[torch.cuda.Stream] = None
         self._ready: dict = {}  # data_ptr of a weight gradient -> event recorded when it was enqueued
         self._pending: List[Tuple[torch.Tensor, "dist.Work"]] = []
+        self._keep: list = []
 
     def attach(self, params: Iterable[torch.nn.Parameter]) -> "EagerGradientSync":
         for p in params:
@@ -139,13 +140,17 @@ class EagerGradientSync:
                 p.register_post_accumulate_grad_hook(self._reduce)
         return self
 
-    def __call__(self, grad: torch.Tensor) -> None:
-        """``after_wgrad`` hook: remember when this gradient was complete on the compute stream
-        (only its address is kept: a second reference would make autograd copy the tensor)."""
-        ready = torch.cuda.Event()
-        ready.record(torch.cuda.current_stream(grad.device))
+    def __call__(self, grad: torch.Tensor, progress=None) -> None:
+        """``after_wgrad`` hook: remember when this gradient was complete on the compute stream, or,
+        in chunked mode, the flags that say which of its rows are (only the gradient's address is
+        kept: a second reference would make autograd copy the tensor)."""
         if len(self._ready) > 64:
             self._ready.clear()
+        if progress is not None:
+            self._ready[grad.data_ptr()] = progress
+            return
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(grad.device))
         self._ready[grad.data_ptr()] = ready
 
     def _reduce(self, param: torch.nn.Parameter) -> None:
@@ -159,6 +164,9 @@ class EagerGradientSync:
             self.side = torch.cuda.Stream(grad.device)
         # the early event is only valid if autograd kept the very tensor the layer produced
         ready = self._ready.pop(grad.data_ptr(), None)
+        if ready is not None and hasattr(ready, "flags"):
+            self._reduce_chunks(grad, ready)
+            return
         if ready is None:
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream(grad.device))
@@ -167,6 +175,26 @@ class EagerGradientSync:
             work = dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
         self._pending.append((grad, work))
 
+    def _reduce_chunks(self, grad: torch.Tensor, progress) -> None:
+        """One all-reduce per chunk of rows, each held back on the side stream until the
+        weight-gradient kernel has raised the chunk's flag."""
+        from . import _lib  # pylint: disable=import-outside-toplevel
+
+        lib = _lib.load()
+        rows, total = progress.rows, grad.shape[0]
+        self.side.wait_event(progress.zeroed)  # never look at flags of an earlier use of that memory
+        base = progress.flags.data_ptr()
+        for c in range(progress.flags.numel()):
+            lo, hi = c * rows, min(total, (c + 1) * rows)
+            if lo >= hi:
+                break
+            _lib.check(lib.al_stream_wait_value32(self.side.cuda_stream, base + 4 * c, 1))
+            part = grad[lo:hi]
+            with torch.cuda.stream(self.side):
+                work = dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            self._pending.append((part, work))
+        self._keep.append(progress)  # the flags must outlive the waits
+
     def finish(self) -> None:
         world = dist.get_world_size(self.group)
         for grad, work in self._pending:
@@ -174,3 +202,4 @@ class EagerGradientSync:
             if self.average:
                 grad.div_(world)
         self._pending.clear()
+        self._keep.clear()

@@ -67,6 +67,8 @@ int check_launch(const char* what);
 // SMs the calling thread asked the backward GEMMs to leave unoccupied (al_reserve_sms), so that a
 // communication kernel enqueued beside them finds room to run.
 int comm_reserved_sms();
+// rows of grad_w per chunk of the weight gradient's progress reporting (multiple of 256)
+int wgrad_chunk_rows(int N, int chunks);
 
 // ---- reductions (reduce_kernels.cu) -------------------------------------------------------
 int launch_abs_max_tiles(int dtype, const void* a, int rows, int K, const TileTable& tt,
@@ -145,8 +147,10 @@ bool tc_backward_supported(const AlDesc& d, const TileTable& tt);
 // pairing: 0 = CTA pairs when they fill the machine, 1 = always pairs, -1 = never
 int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask, int mask_words,
                     int M, int K, int N, const TileTable& tt, int pairing, void* grad_x, cudaStream_t s);
+// chunk_count / chunk_flag / chunks: progress reporting (AlBackwardArgs.wgrad_flags), null / 0 for none
 int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, int mask_words,
-                    int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s);
+                    int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s,
+                    uint32_t* chunk_count = nullptr, uint32_t* chunk_flag = nullptr, int chunks = 0);
 int tc_read_device_error(cudaStream_t s, uint32_t* code);
 // the forward translation unit's own error word (read and cleared); the stream must be idle
 cudaError_t tc_fwd_take_error_word(uint32_t* code);

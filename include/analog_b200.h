@@ -154,7 +154,22 @@ typedef struct AlBackwardArgs {
   const void* w;             /* [N,K] dtype weights of the forward                          */
   const void* learnable_weight_clip; /* [T,N] dtype                                         */
   void* grad_weight_clip;    /* [T,N] dtype                                                 */
+  /* Progress of the weight gradient, for data-parallel callers that start the exchange of its
+   * first rows while the kernel still computes the last (the reference leaves gradient exchange
+   * to DDP / DeepSpeed around autograd, P/torch_linear.py:116-314).  wgrad_chunks in 1..32 splits
+   * the rows of grad_w into chunks of al_wgrad_chunk_rows(N, chunks) rows; wgrad_flags[c]
+   * (zeroed by the caller, on the stream, before the call) becomes 1 as soon as every row of
+   * chunk c is in memory -- at the latest when the whole gradient is.  al_stream_wait_value32
+   * makes another stream wait for such a flag.  Null / 0: no reporting. */
+  uint32_t* wgrad_flags;
+  int32_t wgrad_chunks;
 } AlBackwardArgs;
+
+/* Rows per chunk of the progress reporting above (a multiple of the GEMM's 256-row blocks). */
+int32_t al_wgrad_chunk_rows(int32_t N, int32_t chunks);
+/* Stream `stream` waits until the 32-bit word at device address `addr` is >= value
+ * (cuStreamWaitValue32): nothing enqueued on it afterwards starts before. */
+int al_stream_wait_value32(void* stream, const uint32_t* addr, uint32_t value);
 
 /* Per-tile, per-row abs-max: out[t, r] = max_k |a[r, k]|, k in tile t.  a is [rows, K] dtype,
  * out [T, rows] dtype.  Replaces `sliced_abs_max` (P/torch_utils/torch_abs_max.py:17-39), the

@@ -227,3 +227,48 @@ def test_output_noise_without_adc_is_one_gaussian_per_output(engine):
     assert abs(kurt - 3.0) < 0.15
     assert abs((z1[:, 1:] * z1[:, :-1]).mean().item()) < 0.02       # neighbours
     assert abs((z1 * z2).mean().item()) < 0.02                      # calls
+
+
+def test_weight_gradient_reports_its_rows_chunk_by_chunk():
+    """Chunked mode of the backward (data-parallel overlap): input gradient first, then the
+    weight-gradient kernel raises one flag per chunk of rows.  Results are those of the plain
+    backward, every flag ends up raised, and a stream can be made to wait for a flag."""
+    from aihwkit_lightning_b200 import _lib
+    from aihwkit_lightning_b200.nn import AnalogLinear
+    from aihwkit_lightning_b200.nn import functional as F
+    from aihwkit_lightning_b200.simulator.configs import TorchInferenceRPUConfig
+
+    rpu = TorchInferenceRPUConfig()
+    rpu.mapping.max_input_size = 512
+    rpu.forward.inp_res = 254
+    rpu.forward.out_res = 254
+    rpu.forward.out_bound = 10.0
+    rpu.pre_post.input_range.enable = True
+    rpu.pre_post.input_range.dynamic = True
+    torch.manual_seed(0)
+    layer = AnalogLinear(1024, 1280, bias=True, rpu_config=rpu).to(device="cuda", dtype=torch.bfloat16).train()
+    x = torch.randn(2048, 1024, device="cuda").bfloat16().requires_grad_(True)
+    g = torch.randn(2048, 1280, device="cuda").bfloat16()
+    for engine in ("tcgen05_pair", "tcgen05_single", "simt"):
+        with F.operator_settings(engine=engine):
+            layer.zero_grad(set_to_none=True)
+            x.grad = None
+            layer(x).backward(g)
+            want = [t.detach().clone() for t in (x.grad, layer.weight.grad, layer.bias.grad)]
+            seen = []
+            layer.zero_grad(set_to_none=True)
+            x.grad = None
+            with F.operator_settings(after_wgrad=lambda grad, progress=None: seen.append(progress), wgrad_chunks=3,
+                                     comm_sms=16):
+                layer(x).backward(g)
+        for got, ref in zip((x.grad, layer.weight.grad, layer.bias.grad), want):
+            assert torch.equal(got, ref), engine
+        progress = seen[0]
+        assert progress.rows == 512 and progress.flags.tolist() == [1, 1, 1]      # 1280 rows: 512 + 512 + 256
+        side = torch.cuda.Stream()
+        side.wait_event(progress.zeroed)
+        lib = _lib.load()
+        _lib.check(lib.al_stream_wait_value32(side.cuda_stream, progress.flags.data_ptr() + 8, 1))
+        done = torch.cuda.Event()
+        done.record(side)
+        done.synchronize()
