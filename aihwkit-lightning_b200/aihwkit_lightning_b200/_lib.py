@@ -52,9 +52,8 @@ class AlBackwardArgs(Structure):
         ("grad_out", c_void_p), ("x", c_void_p), ("xq", c_void_p), ("w_mod", c_void_p),
         ("ir_rows", c_void_p), ("keep_mask", c_void_p), ("tile_ends", POINTER(c_int32)),
         ("grad_x", c_void_p), ("grad_w", c_void_p), ("grad_bias", c_void_p),
-        ("grad_input_range", c_void_p), ("reduce_scratch", c_void_p),
+        ("grad_input_range", c_void_p), ("reduce_scratch", c_void_p), ("reduce_scratch_floats", c_int64),
         ("w", c_void_p), ("learnable_weight_clip", c_void_p), ("grad_weight_clip", c_void_p),
-        ("wgrad_flags", c_void_p), ("wgrad_chunks", c_int32),
     ]
 
 
@@ -82,8 +81,7 @@ SYMBOLS = {
     "al_read_device_error": (c_int32, [c_void_p, POINTER(c_uint32)]),
     "al_uses_tcgen05": (c_int32, [POINTER(AlDesc), POINTER(c_int32)]),
     "al_reserve_sms": (c_int32, [c_int32]),
-    "al_wgrad_chunk_rows": (c_int32, [c_int32, c_int32]),
-    "al_stream_wait_value32": (c_int32, [c_void_p, c_void_p, c_uint32]),
+    "al_wgrad_split_plan": (c_int32, [c_int32, c_int32, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
     "al_profile_enable": (c_int32, [c_int32]),
     "al_profile_read": (c_int32, [POINTER(AlProfileEntry), c_int32]),
     "al_kernel_class_name": (c_char_p, [c_int32]),

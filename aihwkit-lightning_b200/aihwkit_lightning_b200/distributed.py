@@ -117,22 +117,30 @@ def all_reduce_gradients(params: Sequence[torch.nn.Parameter], group: Optional[d
 class EagerGradientSync:
     """Sums gradients over the replicas while the backward pass is still running.
 
-    ``attach(params)`` registers a post-accumulate hook on every parameter: as soon as autograd
-    has stored a gradient, its all-reduce (in place, on ``param.grad``) is issued on a side stream.
-    Installed as ``nn.functional.settings.after_wgrad`` the instance is also told the moment an
-    analog layer's weight-gradient kernels are enqueued -- before its input-gradient kernels --
-    and the exchange of that gradient then waits only for that point, so it runs beside the
-    input-gradient kernels.  ``finish()`` makes the compute stream wait for all exchanges and
-    averages; call it before the optimizer step.
+    ``attach(params)`` registers a post-accumulate hook on every parameter.  A large gradient
+    (at least ``small_numel`` elements: the weight matrices) is all-reduced in place on a side
+    stream the moment autograd has stored it, so the exchange of layer L runs beside the backward
+    kernels of layers L-1 .. 0.  Small gradients (norm weights, biases, learned input ranges) are
+    copied into one flat buffer and exchanged by a single call in ``finish()``: a collective per
+    tiny tensor costs more in launch latency than its bytes.  Installed as
+    ``nn.functional.settings.after_wgrad`` the instance is also told the moment an analog layer's
+    weight-gradient kernels are enqueued -- before its input-gradient kernels -- and the exchange
+    of that gradient then waits only for that point.  ``finish()`` makes the compute stream wait
+    for all exchanges and averages; call it before the optimizer step.
     """
 
-    def __init__(self, group: Optional[dist.ProcessGroup] = None, average: bool = True):
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, average: bool = True,
+                 small_numel: int = 1 << 16):
         self.group = group
         self.average = average
+        self.small_numel = small_numel
         self.side: Optional[torch.cuda.Stream] = None
-        self._ready: dict = {}  # data_ptr of a weight gradient -> event recorded when it was enqueued
+        # (address, shape) of a weight gradient -> event recorded when its kernels were enqueued;
+        # entries live for one backward pass only (``finish`` drops what autograd never claimed)
+        self._ready: dict = {}
         self._pending: List[Tuple[torch.Tensor, "dist.Work"]] = []
-        self._keep: list = []
+        self._small: List[torch.Tensor] = []
+        self._flat: Optional[torch.Tensor] = None
 
     def attach(self, params: Iterable[torch.nn.Parameter]) -> "EagerGradientSync":
         for p in params:
@@ -140,33 +148,30 @@ class EagerGradientSync:
                 p.register_post_accumulate_grad_hook(self._reduce)
         return self
 
-    def __call__(self, grad: torch.Tensor, progress=None) -> None:
-        """``after_wgrad`` hook: remember when this gradient was complete on the compute stream, or,
-        in chunked mode, the flags that say which of its rows are (only the gradient's address is
-        kept: a second reference would make autograd copy the tensor)."""
-        if len(self._ready) > 64:
-            self._ready.clear()
-        if progress is not None:
-            self._ready[grad.data_ptr()] = progress
-            return
+    def __call__(self, grad: torch.Tensor) -> None:
+        """``after_wgrad`` hook: remember when this gradient was complete on the compute stream (only
+        the gradient's address and shape are kept: a second reference would make autograd copy the
+        tensor)."""
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream(grad.device))
-        self._ready[grad.data_ptr()] = ready
+        self._ready[(grad.data_ptr(), tuple(grad.shape))] = ready
 
     def _reduce(self, param: torch.nn.Parameter) -> None:
         grad = param.grad
         if grad is None:
+            return
+        if grad.numel() < self.small_numel:
+            self._small.append(grad)
             return
         if not grad.is_cuda:  # host tensors (gloo): no streams to order, the exchange itself is asynchronous
             self._pending.append((grad, dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=self.group, async_op=True)))
             return
         if self.side is None:
             self.side = torch.cuda.Stream(grad.device)
-        # the early event is only valid if autograd kept the very tensor the layer produced
-        ready = self._ready.pop(grad.data_ptr(), None)
-        if ready is not None and hasattr(ready, "flags"):
-            self._reduce_chunks(grad, ready)
-            return
+        # The early event is valid only if autograd kept the very tensor the layer produced (same
+        # address and shape).  When it accumulated into an older ``.grad`` or copied the gradient,
+        # the exchange waits for the compute stream as it stands now.
+        ready = self._ready.pop((grad.data_ptr(), tuple(grad.shape)), None)
         if ready is None:
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream(grad.device))
@@ -175,31 +180,31 @@ class EagerGradientSync:
             work = dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
         self._pending.append((grad, work))
 
-    def _reduce_chunks(self, grad: torch.Tensor, progress) -> None:
-        """One all-reduce per chunk of rows, each held back on the side stream until the
-        weight-gradient kernel has raised the chunk's flag."""
-        from . import _lib  # pylint: disable=import-outside-toplevel
-
-        lib = _lib.load()
-        rows, total = progress.rows, grad.shape[0]
-        self.side.wait_event(progress.zeroed)  # never look at flags of an earlier use of that memory
-        base = progress.flags.data_ptr()
-        for c in range(progress.flags.numel()):
-            lo, hi = c * rows, min(total, (c + 1) * rows)
-            if lo >= hi:
-                break
-            _lib.check(lib.al_stream_wait_value32(self.side.cuda_stream, base + 4 * c, 1))
-            part = grad[lo:hi]
-            with torch.cuda.stream(self.side):
-                work = dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
-            self._pending.append((part, work))
-        self._keep.append(progress)  # the flags must outlive the waits
+    def _reduce_small(self) -> None:
+        if not self._small:
+            return
+        groups: dict = {}
+        for g in self._small:
+            groups.setdefault((g.dtype, g.device), []).append(g)
+        for grads in groups.values():
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
+            if self.average:
+                flat.div_(dist.get_world_size(self.group))
+            offset = 0
+            for g in grads:
+                n = g.numel()
+                g.copy_(flat[offset:offset + n].reshape(g.shape))
+                offset += n
+        self._small.clear()
 
     def finish(self) -> None:
         world = dist.get_world_size(self.group)
+        self._reduce_small()
         for grad, work in self._pending:
             work.wait()  # the current (compute) stream waits for the exchange
             if self.average:
                 grad.div_(world)
         self._pending.clear()
-        self._keep.clear()
+        # an event autograd never claimed belongs to a tensor that is gone; its address may come back
+        self._ready.clear()

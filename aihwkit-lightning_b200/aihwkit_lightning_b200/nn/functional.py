@@ -52,9 +52,6 @@ class _Settings:
     after_wgrad = None
     # with ``after_wgrad``: SMs the GEMM that runs beside the exchange leaves unoccupied for it
     comm_sms = 0
-    # with ``after_wgrad``: > 1 makes the weight-gradient kernel report its rows in that many chunks;
-    # the hook then also receives a ``WgradProgress``
-    wgrad_chunks = 0
 
 
 settings = _Settings()
@@ -176,17 +173,6 @@ def _build_desc(rpu_config, m: int, k: int, n: int, t: int, dtype, training: boo
     d.engine = _ENGINE[settings.engine]
     d.save_for_backward = 0
     return d
-
-
-class WgradProgress:
-    """Handed to ``settings.after_wgrad`` in chunked mode: ``flags[c]`` (int32, device) turns 1 when
-    rows ``[c * rows, (c + 1) * rows)`` of the weight gradient are in memory; ``zeroed`` is an event
-    recorded after the flags were cleared and before the kernel that sets them was enqueued."""
-
-    __slots__ = ("flags", "zeroed", "rows")
-
-    def __init__(self, flags: Tensor, zeroed, rows: int):
-        self.flags, self.zeroed, self.rows = flags, zeroed, rows
 
 
 class _NoGradCtx:
@@ -377,32 +363,14 @@ def _analog_backward(ctx, grad_out):
         scratch = torch.empty(lib.al_backward_scratch_floats(m, k, n, t), device=dev, dtype=torch.float32)
         args.grad_x, args.grad_w, args.grad_bias = _ptr(grad_x), _ptr(grad_w), _ptr(grad_b)
         args.grad_input_range, args.reduce_scratch = _ptr(grad_ir), _ptr(scratch)
+        args.reduce_scratch_floats = scratch.numel()
         grad_clip = None
         if need_clip:
             grad_clip = torch.empty(t, n, device=dev, dtype=dtype)
             args.w, args.learnable_weight_clip = _ptr(w_saved), _ptr(lwc)
             args.grad_weight_clip = _ptr(grad_clip)
         hook = settings.after_wgrad
-        chunks = int(settings.wgrad_chunks)
-        if hook is not None and grad_w is not None and grad_x is not None and chunks > 1:
-            # input gradient first; the weight-gradient kernel then reports its rows chunk by chunk
-            # (flags in device memory), so that the exchange of the first rows between replicas
-            # runs while the kernel still computes the last
-            args.grad_w = args.grad_bias = args.grad_weight_clip = None
-            _lib.check(lib.al_backward(desc, args, _stream(dev)))
-            flags = torch.zeros(chunks, device=dev, dtype=torch.int32)
-            zeroed = torch.cuda.Event()
-            zeroed.record(torch.cuda.current_stream(dev))
-            args.grad_x = args.grad_input_range = None
-            args.grad_w, args.grad_bias, args.grad_weight_clip = _ptr(grad_w), _ptr(grad_b), _ptr(grad_clip)
-            args.wgrad_flags, args.wgrad_chunks = _ptr(flags), chunks
-            lib.al_reserve_sms(int(settings.comm_sms))
-            try:
-                _lib.check(lib.al_backward(desc, args, _stream(dev)))
-            finally:
-                lib.al_reserve_sms(0)
-            hook(grad_w, WgradProgress(flags, zeroed, int(lib.al_wgrad_chunk_rows(n, chunks))))
-        elif hook is not None and grad_w is not None and grad_x is not None:
+        if hook is not None and grad_w is not None and grad_x is not None:
             # weight-side gradients first: their exchange between replicas can then run while the
             # input gradient is still being computed
             args.grad_x = args.grad_input_range = None

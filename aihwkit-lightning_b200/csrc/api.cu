@@ -413,46 +413,20 @@ int64_t backward_reduce_floats(int32_t M, int32_t N, int32_t T) {
 }
 }  // namespace
 
-constexpr int kMaxWgradChunks = 32;  // progress counters sit between the reductions and the partial sums
-
-// all flags to 1: the weight gradient is complete whichever kernel produced it
-__global__ void set_flags_kernel(uint32_t* flags, int n) {
-  if ((int)threadIdx.x < n) atomicExch(&flags[threadIdx.x], 1u);
-}
-
 int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T) {
   if (M <= 0 || K <= 0 || N <= 0 || T <= 0) return 0;
-  return backward_reduce_floats(M, N, T) + kMaxWgradChunks + al::wgrad_simt_partial_floats(M, K, N, T);
+  return backward_reduce_floats(M, N, T) + al::wgrad_simt_partial_floats(M, K, N, T);
 }
 
-int32_t al_wgrad_chunk_rows(int32_t N, int32_t chunks) {
-  if (N <= 0 || chunks <= 0) return 0;
-  return al::wgrad_chunk_rows(N, chunks > kMaxWgradChunks ? kMaxWgradChunks : chunks);
-}
-
-int al_stream_wait_value32(void* stream, const uint32_t* addr, uint32_t value) {
-  typedef CUresult (*WaitFn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
-  static WaitFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<WaitFn>(ptr);
-    else
-      cudaGetLastError();
+int al_wgrad_split_plan(int32_t M, int32_t K, int32_t N, int32_t T, int32_t* splits, int32_t* rows_per_split) {
+  if (M <= 0 || K <= 0 || N <= 0 || T <= 0 || !splits || !rows_per_split) {
+    set_error("al_wgrad_split_plan: non-positive size or null output");
+    return AL_ERR_BAD_ARGUMENT;
   }
-  if (!fn || !addr) {
-    set_error("al_stream_wait_value32: %s", fn ? "null address" : "cuStreamWaitValue32 is not available from the driver");
-    return fn ? AL_ERR_BAD_ARGUMENT : AL_ERR_CUDA;
-  }
-  const CUresult r = fn((CUstream)stream, (CUdeviceptr)reinterpret_cast<uintptr_t>(addr), value, CU_STREAM_WAIT_VALUE_GEQ);
-  if (r != CUDA_SUCCESS) {
-    set_error("cuStreamWaitValue32 failed with CUresult %d", (int)r);
-    return AL_ERR_CUDA;
-  }
+  int s = 1, c = 0;
+  al::wgrad_simt_plan(M, K, N, T, &s, &c);
+  *splits = s;
+  *rows_per_split = c;
   return AL_OK;
 }
 
@@ -471,6 +445,11 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   if (!a->grad_out) {
     set_error("al_backward: grad_out missing");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  if (a->reduce_scratch && a->reduce_scratch_floats < al_backward_scratch_floats(d.M, d.K, d.N, d.T)) {
+    set_error("al_backward: reduce_scratch holds %lld floats, al_backward_scratch_floats asks for %lld",
+              (long long)a->reduce_scratch_floats, (long long)al_backward_scratch_floats(d.M, d.K, d.N, d.T));
     return AL_ERR_BAD_ARGUMENT;
   }
   const uint32_t* mask = dv.has_bound ? a->keep_mask : nullptr;
@@ -518,21 +497,14 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
       set_error("al_backward: xq missing");
       return AL_ERR_BAD_ARGUMENT;
     }
-    // rows of grad_w reported chunk by chunk while the tcgen05 pair kernel still runs; a later
-    // pass over grad_w (learned weight ranges) rules that out, the flags then only rise at the end
-    const bool report_chunks = a->wgrad_flags && a->wgrad_chunks > 0 && a->reduce_scratch &&
-                               d.clip_type != AL_CLIP_LEARNABLE_PER_CHANNEL;
-    uint32_t* counts = report_chunks
-                           ? reinterpret_cast<uint32_t*>(a->reduce_scratch + backward_reduce_floats(d.M, d.N, d.T))
-                           : nullptr;
-    const int chunks = a->wgrad_chunks < kMaxWgradChunks ? a->wgrad_chunks : kMaxWgradChunks;
-    rc = tc ? launch_wgrad_tc(a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt, pairing, a->grad_w, s, counts,
-                              report_chunks ? a->wgrad_flags : nullptr, report_chunks ? chunks : 0)
-            : launch_wgrad_simt(d.dtype, a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt,
-                                a->reduce_scratch ? a->reduce_scratch + backward_reduce_floats(d.M, d.N, d.T) +
-                                                        kMaxWgradChunks
-                                                  : nullptr,
-                                a->grad_w, s);
+    // the partial sums of a split CUDA-core weight gradient sit behind the reductions; what is
+    // left of the caller's buffer there is the capacity the launch may use
+    const int64_t fixed = backward_reduce_floats(d.M, d.N, d.T);
+    float* partial = a->reduce_scratch ? a->reduce_scratch + fixed : nullptr;
+    const int64_t partial_capacity = a->reduce_scratch ? a->reduce_scratch_floats - fixed : 0;
+    rc = tc ? launch_wgrad_tc(a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt, pairing, a->grad_w, s)
+            : launch_wgrad_simt(d.dtype, a->grad_out, a->xq, mask, mask_words, d.M, d.K, d.N, gt, d.T, partial,
+                                partial_capacity, a->grad_w, s);
     if (rc) return rc;
   }
   if (d.clip_type == AL_CLIP_LEARNABLE_PER_CHANNEL && (a->grad_w || a->grad_weight_clip)) {
@@ -551,13 +523,6 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
     const double n_states_d = d.mod_res > 0 ? (d.mod_res > 1.0 / d.mod_res ? d.mod_res : 1.0 / d.mod_res) : 1.0;
     rc = launch_learn_clip_backward(d.dtype, a->w, a->learnable_weight_clip, flags, d.N, d.K, tt, discretize,
                                     dv.n_states, n_states_d / 2.0, d.no_rounding, a->grad_w, a->grad_weight_clip, s);
-    if (rc) return rc;
-  }
-  if (a->grad_w && a->wgrad_flags && a->wgrad_chunks > 0) {
-    // whatever produced grad_w and however far the in-kernel reporting got: it is complete here
-    const int chunks = a->wgrad_chunks < kMaxWgradChunks ? a->wgrad_chunks : kMaxWgradChunks;
-    set_flags_kernel<<<1, kMaxWgradChunks, 0, s>>>(a->wgrad_flags, chunks);
-    rc = check_launch("wgrad_flags");
     if (rc) return rc;
   }
   if (a->grad_bias) {

@@ -84,7 +84,7 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
   __shared__ __align__(16) float As[BK][BM + kPad];
   __shared__ __align__(16) float Bs[BK][BN + kPad];
   const int tid = threadIdx.x, tx = tid % TX, ty = tid / TX, lane = tid & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;  // row blocks on x: no 65535 limit
   const int M = ep.M, N = ep.N;
 
   TileEpilogueCfg cfg;
@@ -208,9 +208,10 @@ bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
   const int tid = threadIdx.x, tx = tid % TX, ty = tid / TX;
   const int t = blockIdx.z / splits, split = blockIdx.z - t * splits;
   const int lo = tt.lo(t), hi = tt.hi(t);
-  const int j0 = lo + blockIdx.x * TBN;
+  // the row blocks of C sit on gridDim.x (up to 2^31 - 1 of them), the column blocks on y
+  const int j0 = lo + blockIdx.y * TBN;
   if (j0 >= hi) return;
-  const int i0 = blockIdx.y * TBM;
+  const int i0 = blockIdx.x * TBM;
   const int I = WGRAD ? N : M;  // rows of C
   const int L = WGRAD ? M : N;  // reduction length
   const int l_begin = split * chunk;
@@ -288,7 +289,7 @@ template <int BN>
 void fwd_simt_launch(int dtype, int round_dt, const void* xq, const void* w_mod, int K, const TileTable& tt,
                      const FwdEpilogueParams& ep, void* out, cudaStream_t s) {
   constexpr int BM = kBlockElems / BN;
-  dim3 grid((ep.N + BN - 1) / BN, (ep.M + BM - 1) / BM);
+  dim3 grid((ep.M + BM - 1) / BM, (ep.N + BN - 1) / BN);
   if (dtype == AL_F32)
     fwd_simt_kernel<kF32, kF32, BN><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out);
   else if (round_dt == AL_BF16)
@@ -301,7 +302,7 @@ template <int TBM, int TBN>
 void wgrad_simt_launch(int dtype, const void* g, const void* xq, const uint32_t* keep_mask, int mask_words, int M,
                        int K, int N, const TileTable& tt, int splits, int chunk, float* partial, void* grad_w,
                        cudaStream_t s) {
-  dim3 grid((max_tile_width(tt) + TBN - 1) / TBN, (N + TBM - 1) / TBM, tt.T * splits);
+  dim3 grid((N + TBM - 1) / TBM, (max_tile_width(tt) + TBN - 1) / TBN, tt.T * splits);
   if (dtype == AL_F32)
     bwd_simt_kernel<kF32, true, TBM, TBN><<<grid, kThreads, 0, s>>>(g, xq, keep_mask, mask_words, M, K, N, tt, splits,
                                                                     chunk, partial, grad_w);
@@ -311,8 +312,9 @@ void wgrad_simt_launch(int dtype, const void* g, const void* xq, const uint32_t*
 }
 
 // Number of CTAs the reduction over the batch rows is split over: enough to put two waves of
-// blocks on a 148-SM part, at least 512 rows each.  A function of the sizes alone, so that the
-// caller can size the partial-sum buffer without the tile table.
+// blocks on a 148-SM part, at least 512 rows each.  A function of the LAYER's sizes alone (T is
+// the layer's tile count, whatever tile table the GEMM itself runs with), so that the sizing of
+// the partial-sum buffer and the launch cannot disagree.
 int wgrad_splits(int M, int K, int N, int T) {
   const int tbm = N <= 16 ? 16 : N <= 32 ? 32 : 64;
   const int tbn = kBlockElems / tbm;
@@ -326,8 +328,18 @@ int wgrad_splits(int M, int K, int N, int T) {
 
 }  // namespace
 
-int64_t wgrad_simt_partial_floats(int M, int K, int N, int T) {
-  const int splits = wgrad_splits(M, K, N, T);
+void wgrad_simt_plan(int M, int K, int N, int layer_T, int* splits, int* chunk_rows) {
+  const int s = wgrad_splits(M, K, N, layer_T);
+  const int per = (M + s - 1) / s;
+  const int chunk = (per + BK - 1) / BK * BK;
+  // rounding the chunk up to whole k-steps can leave trailing splits without rows: drop them
+  *splits = (M + chunk - 1) / chunk;
+  *chunk_rows = chunk;
+}
+
+int64_t wgrad_simt_partial_floats(int M, int K, int N, int layer_T) {
+  int splits, chunk;
+  wgrad_simt_plan(M, K, N, layer_T, &splits, &chunk);
   return splits > 1 ? (int64_t)splits * N * K : 0;
 }
 
@@ -344,7 +356,7 @@ int launch_dgrad_simt(int dtype, const void* g, const void* w_mod, const uint32_
                       int mask_words, int M, int K, int N, const TileTable& tt, void* grad_x,
                       cudaStream_t s) {
   ProfScope prof(AL_K_DGRAD_GEMM, s);
-  dim3 grid((max_tile_width(tt) + 63) / 64, (M + 63) / 64, tt.T);
+  dim3 grid((M + 63) / 64, (max_tile_width(tt) + 63) / 64, tt.T);
   if (dtype == AL_F32)
     bwd_simt_kernel<kF32, false, 64, 64><<<grid, kThreads, 0, s>>>(g, w_mod, keep_mask, mask_words, M, K, N, tt, 1, N,
                                                                   nullptr, grad_x);
@@ -355,16 +367,18 @@ int launch_dgrad_simt(int dtype, const void* g, const void* w_mod, const uint32_
 }
 
 int launch_wgrad_simt(int dtype, const void* g, const void* xq, const uint32_t* keep_mask,
-                      int mask_words, int M, int K, int N, const TileTable& tt, float* partial, void* grad_w,
-                      cudaStream_t s) {
-  const int splits = wgrad_splits(M, K, N, tt.T);
+                      int mask_words, int M, int K, int N, const TileTable& tt, int layer_T, float* partial,
+                      int64_t partial_capacity, void* grad_w, cudaStream_t s) {
+  // the split count comes from the layer's tile count -- the argument the caller sized `partial`
+  // with -- never from `tt`, which is the one-tile table when there is no clamp mask
+  int splits, chunk;
+  wgrad_simt_plan(M, K, N, layer_T, &splits, &chunk);
   ProfScope prof(AL_K_WGRAD_GEMM, s, splits > 1 ? 2 : 1);
-  if (splits > 1 && partial == nullptr) {
-    set_error("wgrad_simt: the partial-sum buffer is missing");
+  if (splits > 1 && (partial == nullptr || (int64_t)splits * N * K > partial_capacity)) {
+    set_error("wgrad_simt: the partial-sum buffer holds %lld floats, %d splits x %d x %d need %lld",
+              (long long)(partial ? partial_capacity : 0), splits, N, K, (long long)splits * N * K);
     return AL_ERR_BAD_ARGUMENT;
   }
-  const int per = (M + splits - 1) / splits;
-  const int chunk = (per + BK - 1) / BK * BK;
   if (N <= 16) wgrad_simt_launch<16, 256>(dtype, g, xq, keep_mask, mask_words, M, K, N, tt, splits, chunk, partial, grad_w, s);
   else if (N <= 32) wgrad_simt_launch<32, 128>(dtype, g, xq, keep_mask, mask_words, M, K, N, tt, splits, chunk, partial, grad_w, s);
   else wgrad_simt_launch<64, 64>(dtype, g, xq, keep_mask, mask_words, M, K, N, tt, splits, chunk, partial, grad_w, s);

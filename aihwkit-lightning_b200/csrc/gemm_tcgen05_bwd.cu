@@ -26,10 +26,6 @@ struct BwdTcParams {
   const uint32_t* keep_mask;
   int32_t mask_words;
   void* c_out;
-  // progress reporting of the pair kernel (null: none): chunk c = row blocks [c * ib_per_chunk, ...)
-  uint32_t* chunk_count;  // [chunks] warps that have stored their part of an item of the chunk
-  uint32_t* chunk_flag;   // [chunks] set to 1 by the warp that completes the chunk
-  int32_t ib_per_chunk;
 };
 
 // A heavily clamped 128-byte row of a staged A tile: rewrite its 16-byte chunks under the
@@ -581,21 +577,7 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive_cluster(mapa_u32(smem_u32(&bars->acc_empty[b]), 0));
-        if (p.chunk_flag != nullptr) {
-          // this warp's rows of the item are stored; the last of the 8 warps x items of a chunk
-          // to say so (fence, then count) has every other warp's stores ordered before its own flag
-          const int c = ib / p.ib_per_chunk;
-          const int ibs = min(p.ib_per_chunk, p.num_ib - c * p.ib_per_chunk);
-          const uint32_t expected = 8u * (uint32_t)(ibs * p.T * p.num_jb);
-          __threadfence();
-          if (atomicAdd(&p.chunk_count[c], 1u) + 1u == expected) {
-            __threadfence();
-            atomicExch(&p.chunk_flag[c], 1u);
-          }
-        }
-      }
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->acc_empty[b]), 0));
     }
   } else if (warp >= 8 && masked && pair < num_work) {
     // ---- mask transform (both CTAs, own A tile): see bwd_tc_kernel -------------------------
@@ -731,15 +713,9 @@ static int max_pairs(bool wgrad) {
   n = clusters;
   return n;
 }
-struct ChunkReport {
-  uint32_t* count = nullptr;  // zeroed here
-  uint32_t* flag = nullptr;   // zeroed by the caller
-  int chunks = 0;
-};
-
 static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint32_t* keep_mask,
                          int mask_words, int M, int K, int N, const TileTable& tt, int pairing, void* c_out,
-                         cudaStream_t s, const ChunkReport& report = ChunkReport()) {
+                         cudaStream_t s) {
   int w = 0;
   if (!uniform_tiles(tt, &w) || !aligned16(g) || !aligned16(b_op) || !aligned16(c_out)) {
     set_error("bwd_tc: operands must be 16-byte aligned with equally wide tiles");
@@ -780,9 +756,6 @@ static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint
   }
   // CTA pairs (256-row blocks) when they fill the machine; single CTAs for smaller problems
   const int pair_work = ((p.I + 2 * BM - 1) / (2 * BM)) * p.T * p.num_jb;
-  p.chunk_count = nullptr;
-  p.chunk_flag = nullptr;
-  p.ib_per_chunk = 1;
   int pairs = max_pairs(wgrad);
   const int keep_free = comm_reserved_sms();
   if (pairs > 1 && keep_free > 0) pairs = pairs - (keep_free + 1) / 2 > 1 ? pairs - (keep_free + 1) / 2 : 1;
@@ -790,15 +763,6 @@ static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint
     p.num_ib = (p.I + 2 * BM - 1) / (2 * BM);
     rc = wgrad ? ensure_smem(bwd_tc_pair_kernel<true>, P_SMEM) : ensure_smem(bwd_tc_pair_kernel<false>, P_SMEM);
     if (rc) return rc;
-    if (report.chunks > 0 && report.flag != nullptr && report.count != nullptr) {
-      if (cudaMemsetAsync(report.count, 0, sizeof(uint32_t) * report.chunks, s) != cudaSuccess) {
-        set_error("bwd_tc: memset of the progress counters failed");
-        return AL_ERR_CUDA;
-      }
-      p.chunk_count = report.count;
-      p.chunk_flag = report.flag;
-      p.ib_per_chunk = wgrad_chunk_rows(p.I, report.chunks) / (2 * BM);
-    }
     const int grid = 2 * (pair_work < pairs ? pair_work : pairs);
     if (wgrad)
       bwd_tc_pair_kernel<true><<<grid, kBwdThreads, P_SMEM, s>>>(map_a, map_b, p);
@@ -823,20 +787,9 @@ int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask,
 }
 
 int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, int mask_words,
-                    int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s,
-                    uint32_t* chunk_count, uint32_t* chunk_flag, int chunks) {
+                    int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s) {
   ProfScope prof(AL_K_WGRAD_GEMM, s);
-  ChunkReport report;
-  report.count = chunk_count;
-  report.flag = chunk_flag;
-  report.chunks = chunks;
-  return launch_bwd_tc(true, g, xq, keep_mask, mask_words, M, K, N, tt, pairing, grad_w, s, report);
-}
-
-int wgrad_chunk_rows(int N, int chunks) {
-  const int blocks = (N + 2 * BM - 1) / (2 * BM);
-  const int per = (blocks + chunks - 1) / chunks;
-  return (per < 1 ? 1 : per) * 2 * BM;
+  return launch_bwd_tc(true, g, xq, keep_mask, mask_words, M, K, N, tt, pairing, grad_w, s);
 }
 
 int tc_read_device_error(cudaStream_t s, uint32_t* code) {

@@ -67,8 +67,6 @@ int check_launch(const char* what);
 // SMs the calling thread asked the backward GEMMs to leave unoccupied (al_reserve_sms), so that a
 // communication kernel enqueued beside them finds room to run.
 int comm_reserved_sms();
-// rows of grad_w per chunk of the weight gradient's progress reporting (multiple of 256)
-int wgrad_chunk_rows(int N, int chunks);
 
 // ---- reductions (reduce_kernels.cu) -------------------------------------------------------
 int launch_abs_max_tiles(int dtype, const void* a, int rows, int K, const TileTable& tt,
@@ -114,10 +112,15 @@ int launch_dgrad_simt(int dtype, const void* g, const void* w_mod, const uint32_
 // grad_w[:, tile] = (g * keep_t)^T @ xq[:, tile].  `partial` holds wgrad_simt_partial_floats()
 // floats (fp32 partial sums of the reduction over the rows when it is split over CTAs; may be
 // null when that count is zero).
-int64_t wgrad_simt_partial_floats(int M, int K, int N, int T);
+// Both take the LAYER's tile count (`layer_T`), not the tile table of the launch: the launch runs
+// with a one-tile table when there is no clamp mask, and the split count must be the one the
+// buffer was sized with.  `partial_capacity` is what the caller's buffer holds, in floats; a launch
+// that would need more is refused on the host.
+void wgrad_simt_plan(int M, int K, int N, int layer_T, int* splits, int* chunk_rows);
+int64_t wgrad_simt_partial_floats(int M, int K, int N, int layer_T);
 int launch_wgrad_simt(int dtype, const void* g, const void* xq, const uint32_t* keep_mask,
-                      int mask_words, int M, int K, int N, const TileTable& tt, float* partial, void* grad_w,
-                      cudaStream_t s);
+                      int mask_words, int M, int K, int N, const TileTable& tt, int layer_T, float* partial,
+                      int64_t partial_capacity, void* grad_w, cudaStream_t s);
 
 // ---- backward element-wise parts (backward_kernels.cu) ------------------------------------
 int launch_bias_grad(int dtype, const void* g, int M, int N, void* grad_bias, float* scratch,
@@ -147,10 +150,8 @@ bool tc_backward_supported(const AlDesc& d, const TileTable& tt);
 // pairing: 0 = CTA pairs when they fill the machine, 1 = always pairs, -1 = never
 int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask, int mask_words,
                     int M, int K, int N, const TileTable& tt, int pairing, void* grad_x, cudaStream_t s);
-// chunk_count / chunk_flag / chunks: progress reporting (AlBackwardArgs.wgrad_flags), null / 0 for none
 int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, int mask_words,
-                    int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s,
-                    uint32_t* chunk_count = nullptr, uint32_t* chunk_flag = nullptr, int chunks = 0);
+                    int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s);
 int tc_read_device_error(cudaStream_t s, uint32_t* code);
 // the forward translation unit's own error word (read and cleared); the stream must be idle
 cudaError_t tc_fwd_take_error_word(uint32_t* code);

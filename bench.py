@@ -251,9 +251,6 @@ def main():
         # with 20 SMs free (64 CTA pairs = 8 full rounds of the 512 output blocks) the GEMM takes 39 us
         # longer and the exposed all-reduce 45 us less -- no net gain, so the default is 0.
         analog_functional.settings.comm_sms = int(os.environ.get("BENCH_COMM_SMS", "0"))
-        # > 1: the weight-gradient kernel reports its rows in that many chunks and the all-reduce of a
-        # chunk starts as soon as its flag is up, beside the rest of the kernel
-        analog_functional.settings.wgrad_chunks = int(os.environ.get("BENCH_WGRAD_CHUNKS", "0"))
     x_dev = x_host.to(dev).requires_grad_(True)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev)

@@ -149,27 +149,14 @@ typedef struct AlBackwardArgs {
   void* grad_bias;           /* [N] dtype, nullable                                         */
   void* grad_input_range;    /* [T] dtype, nullable (static mode, learn_input_range)       */
   float* reduce_scratch;     /* >= al_backward_scratch_floats(M,K,N,T) floats               */
+  int64_t reduce_scratch_floats; /* floats the caller's reduce_scratch holds; a call that would need
+                                 more than that is refused before anything is launched     */
   /* clip type LEARNABLE_PER_CHANNEL (`quant_utils.py:125-151`): grad_w becomes the gradient of
    * the unclipped weights and grad_weight_clip that of the learned ranges; null otherwise */
   const void* w;             /* [N,K] dtype weights of the forward                          */
   const void* learnable_weight_clip; /* [T,N] dtype                                         */
   void* grad_weight_clip;    /* [T,N] dtype                                                 */
-  /* Progress of the weight gradient, for data-parallel callers that start the exchange of its
-   * first rows while the kernel still computes the last (the reference leaves gradient exchange
-   * to DDP / DeepSpeed around autograd, P/torch_linear.py:116-314).  wgrad_chunks in 1..32 splits
-   * the rows of grad_w into chunks of al_wgrad_chunk_rows(N, chunks) rows; wgrad_flags[c]
-   * (zeroed by the caller, on the stream, before the call) becomes 1 as soon as every row of
-   * chunk c is in memory -- at the latest when the whole gradient is.  al_stream_wait_value32
-   * makes another stream wait for such a flag.  Null / 0: no reporting. */
-  uint32_t* wgrad_flags;
-  int32_t wgrad_chunks;
 } AlBackwardArgs;
-
-/* Rows per chunk of the progress reporting above (a multiple of the GEMM's 256-row blocks). */
-int32_t al_wgrad_chunk_rows(int32_t N, int32_t chunks);
-/* Stream `stream` waits until the 32-bit word at device address `addr` is >= value
- * (cuStreamWaitValue32): nothing enqueued on it afterwards starts before. */
-int al_stream_wait_value32(void* stream, const uint32_t* addr, uint32_t value);
 
 /* Per-tile, per-row abs-max: out[t, r] = max_k |a[r, k]|, k in tile t.  a is [rows, K] dtype,
  * out [T, rows] dtype.  Replaces `sliced_abs_max` (P/torch_utils/torch_abs_max.py:17-39), the
@@ -213,6 +200,11 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* args, void* stream);
  * (triton_linear.py:695-764). */
 int al_backward(const AlDesc* desc, const AlBackwardArgs* args, void* stream);
 int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T);
+/* How the CUDA-core weight gradient (fp32 layers, unaligned tilings) cuts its reduction over the M
+ * rows of the batch: `splits` CTAs per output block, `rows_per_split` rows each; with more than one
+ * split, splits * N * K floats of reduce_scratch (behind the reductions) hold the partial sums.  A
+ * function of the layer's sizes alone: the same whether or not the call carries a clamp mask. */
+int al_wgrad_split_plan(int32_t M, int32_t K, int32_t N, int32_t T, int32_t* splits, int32_t* rows_per_split);
 /* floats of AlForwardArgs.smallm_scratch; 0 when the problem has more than 16 rows */
 int64_t al_smallm_scratch_floats(int32_t M, int32_t N, int32_t T);
 

@@ -1,0 +1,82 @@
+"""Forward + backward of the analog operator at the real layer shapes of the ResNet-32 configuration
+(batch 256, ``max_input_size=256``, no ADC): the patch matrices of the stage-2 and stage-3
+convolutions have few output channels and very many rows, which is where the CUDA-core weight
+gradient splits its reduction over CTAs and keeps partial sums in the caller's scratch.  The
+scratch is handed over with guard words behind it that must be intact afterwards, and the
+gradients are compared with fp32 matrix products over the operands the forward saved."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+GUARD = 1 << 18  # floats behind the scratch (1 MiB)
+
+
+@pytest.mark.parametrize("m,k,n,max_in", [
+    (65536, 288, 32, 256),   # stage 2: T = 2 (2 x 144); the shape whose split counts once disagreed
+    (65536, 144, 32, 256),   # stage 2, first convolution
+    (16384, 576, 64, 256),   # stage 3: T = 3 (3 x 192)
+    (16384, 288, 64, 256),
+    (262144, 144, 16, 256),  # stage 1
+])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_weight_gradient_partials_stay_inside_the_scratch(m, k, n, max_in, dtype):
+    from aihwkit_lightning_b200 import _lib
+    from aihwkit_lightning_b200.nn import functional as F
+    from aihwkit_lightning_b200.nn.modules.base import split_sizes
+    from aihwkit_lightning_b200.simulator.configs import TorchInferenceRPUConfig
+
+    lib = _lib.load()
+    rpu = TorchInferenceRPUConfig()
+    rpu.mapping.max_input_size = max_in
+    rpu.forward.inp_res = 254
+    rpu.forward.out_noise = 0.0
+    rpu.pre_post.input_range.enable = True
+    rpu.pre_post.input_range.dynamic = True
+    in_sizes = split_sizes(k, max_in)
+    t = len(in_sizes)
+    ends = _lib.tile_ends_array(in_sizes)
+    gen = torch.Generator(device="cuda").manual_seed(m + k + n)
+    x = torch.randn(m, k, device="cuda", generator=gen).to(dtype)
+    w = (torch.rand(n, k, device="cuda", generator=gen) * 0.2 - 0.1).to(dtype)
+    g = torch.randn(m, n, device="cuda", generator=gen).to(dtype)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    desc = F.make_desc(rpu, m, k, n, t, dtype, True)
+    desc.save_for_backward = 1
+    fa = _lib.AlForwardArgs()
+    out = torch.empty(m, n, device="cuda", dtype=dtype)
+    xq = torch.empty_like(x)
+    ir_rows = torch.empty(t, m, device="cuda", dtype=dtype)
+    w_amax = torch.empty(t, n, device="cuda", dtype=dtype)
+    w_tile_max = torch.empty(2 * t, device="cuda", dtype=torch.float32)
+    fa.x, fa.w, fa.out, fa.tile_ends = x.data_ptr(), w.data_ptr(), out.data_ptr(), ends
+    fa.xq, fa.ir_rows, fa.w_amax, fa.w_tile_max, fa.w_mod = (xq.data_ptr(), ir_rows.data_ptr(), w_amax.data_ptr(),
+                                                            w_tile_max.data_ptr(), w.data_ptr())
+    _lib.check(lib.al_forward(desc, fa, stream))
+
+    need = lib.al_backward_scratch_floats(m, k, n, t)
+    splits, rows = ctypes.c_int32(), ctypes.c_int32()
+    _lib.check(lib.al_wgrad_split_plan(m, k, n, t, ctypes.byref(splits), ctypes.byref(rows)))
+    if dtype == torch.float32:
+        assert splits.value > 1  # these shapes are the ones that split
+    arena = torch.full((need + GUARD,), float("nan"), device="cuda", dtype=torch.float32)
+    arena[need:] = 12345.0
+    ba = _lib.AlBackwardArgs()
+    grad_x = torch.empty(m, k, device="cuda", dtype=dtype)
+    grad_w = torch.empty(n, k, device="cuda", dtype=dtype)
+    ba.grad_out, ba.xq, ba.w_mod, ba.ir_rows, ba.tile_ends = g.data_ptr(), xq.data_ptr(), w.data_ptr(), ir_rows.data_ptr(), ends
+    ba.grad_x, ba.grad_w = grad_x.data_ptr(), grad_w.data_ptr()
+    ba.reduce_scratch, ba.reduce_scratch_floats = arena.data_ptr(), need
+    _lib.check(lib.al_backward(desc, ba, stream))
+    torch.cuda.synchronize()
+
+    assert bool((arena[need:] == 12345.0).all()), "the backward wrote behind its scratch buffer"
+    want_w = g.float().t() @ xq.float()
+    want_x = g.float() @ w.float()
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert ((grad_w.float() - want_w).norm() / want_w.norm()).item() <= tol
+    assert ((grad_x.float() - want_x).norm() / want_x.norm()).item() <= tol
+    assert ((out.float() - xq.float() @ w.float().t()).norm() / out.float().norm()).item() <= tol

@@ -99,11 +99,11 @@ def _eager_worker(rank, world, port, out_dir):
         torch.manual_seed(0)  # identical replicas
         model = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 3))
         model[2].bias.requires_grad_(False)
-        sync = EagerGradientSync().attach(model.parameters())
+        sync = EagerGradientSync(small_numel=8).attach(model.parameters())  # the biases go the flat way
         x = torch.randn(4, 6, generator=torch.Generator().manual_seed(10 + rank))  # per-rank batch
         # the hook fires from inside backward, once per parameter that received a gradient
         model(x).square().sum().backward()
-        assert len(sync._pending) == 3  # pylint: disable=protected-access
+        assert len(sync._pending) == 2 and len(sync._small) == 1  # pylint: disable=protected-access
         local = model(x).square().sum()
         want = torch.autograd.grad(local, [p for p in model.parameters() if p.requires_grad])
         sync.finish()

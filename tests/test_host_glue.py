@@ -33,3 +33,75 @@ def test_tile_ends_are_cumulative_and_shared_per_tiling():
     assert list(a) == [3, 6, 8]
     assert _lib.tile_ends_array((3, 3, 2)) is a
     assert list(_lib.tile_ends_array([5])) == [5]
+
+
+# ---- split plan of the CUDA-core weight gradient: sizing and launch share one source of truth -----
+
+RESNET32_LAYERS = [  # (M = batch 256 x output positions, K = C_in * 9, N = C_out, T at max_input_size 256)
+    (262144, 27, 16, 1), (262144, 144, 16, 1),
+    (65536, 144, 32, 1), (65536, 288, 32, 2), (65536, 16, 32, 1),
+    (16384, 288, 64, 2), (16384, 576, 64, 3), (16384, 32, 64, 1),
+    (256, 64, 10, 1),
+]
+
+
+def _plan(lib, m, k, n, t):
+    import ctypes
+    splits, rows = ctypes.c_int32(), ctypes.c_int32()
+    assert lib.al_wgrad_split_plan(m, k, n, t, ctypes.byref(splits), ctypes.byref(rows)) == 0
+    return splits.value, rows.value
+
+
+def test_wgrad_split_plan_fits_the_scratch_it_is_sized_with():
+    """The partial sums of a split weight gradient must fit what ``al_backward_scratch_floats``
+    promises for the same layer, whatever tile table the launch itself runs with (a call without
+    a clamp mask runs one GEMM over the whole K range: the plan may not depend on that)."""
+    import os
+    import random
+
+    import pytest
+
+    if not os.path.exists(_lib.LIB_PATH):
+        pytest.skip("library not built")
+    lib = _lib.load()
+    rng = random.Random(0)
+    shapes = list(RESNET32_LAYERS)
+    for _ in range(400):
+        k = rng.choice([3, 27, 64, 144, 288, 576, 1000, 1024, 4096])
+        shapes.append((rng.choice([1, 17, 512, 2048, 16384, 65536, 262144, 300001]), k,
+                       rng.choice([1, 10, 16, 32, 33, 64, 100, 1024]), rng.choice([1, 2, 3, 7, min(k, 16)])))
+    for m, k, n, t in shapes:
+        splits, rows = _plan(lib, m, k, n, t)
+        assert splits >= 1 and rows % 16 == 0
+        assert splits * rows >= m                      # the splits cover every row
+        assert splits == 1 or (splits - 1) * rows < m  # and none of them starts beyond the last
+        fixed = lib.al_backward_scratch_floats(m, k, n, t) - (splits * n * k if splits > 1 else 0)
+        # the fixed part (bias / range / clip reductions) does not depend on K
+        assert fixed == lib.al_backward_scratch_floats(m, 1, n, t) - (
+            _plan(lib, m, 1, n, t)[0] * n if _plan(lib, m, 1, n, t)[0] > 1 else 0)
+        assert fixed > 0
+
+
+def test_backward_refuses_a_scratch_buffer_that_is_too_small():
+    """Capacity travels with the pointer: a call whose scratch holds fewer floats than
+    ``al_backward_scratch_floats`` asks for is refused on the host, before any launch."""
+    import ctypes
+    import os
+
+    import pytest
+
+    if not os.path.exists(_lib.LIB_PATH):
+        pytest.skip("library not built")
+    lib = _lib.load()
+    m, k, n, t = 65536, 288, 32, 2
+    desc = _lib.AlDesc()
+    desc.M, desc.K, desc.N, desc.T = m, k, n, t
+    desc.dtype = _lib.AL_F32
+    desc.inp_res, desc.out_res, desc.out_bound = -1.0, -1.0, -1.0
+    args = _lib.AlBackwardArgs()
+    args.tile_ends = (ctypes.c_int32 * 2)(144, 288)
+    args.grad_out = 256  # never dereferenced: the call must fail before any launch
+    args.reduce_scratch = 256
+    args.reduce_scratch_floats = lib.al_backward_scratch_floats(m, k, n, t) - 1
+    assert lib.al_backward(desc, args, None) == _lib.AL_ERR_BAD_ARGUMENT
+    assert b"reduce_scratch holds" in lib.al_last_error()

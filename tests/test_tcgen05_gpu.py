@@ -229,11 +229,10 @@ def test_output_noise_without_adc_is_one_gaussian_per_output(engine):
     assert abs((z1 * z2).mean().item()) < 0.02                      # calls
 
 
-def test_weight_gradient_reports_its_rows_chunk_by_chunk():
-    """Chunked mode of the backward (data-parallel overlap): input gradient first, then the
-    weight-gradient kernel raises one flag per chunk of rows.  Results are those of the plain
-    backward, every flag ends up raised, and a stream can be made to wait for a flag."""
-    from aihwkit_lightning_b200 import _lib
+def test_weight_gradients_first_when_a_hook_asks_for_them():
+    """Data-parallel overlap: with an ``after_wgrad`` hook the backward enqueues the weight-side
+    kernels first, calls the hook with the weight gradient, then computes the input gradient
+    (optionally leaving SMs free for the exchange).  Results are those of the plain backward."""
     from aihwkit_lightning_b200.nn import AnalogLinear
     from aihwkit_lightning_b200.nn import functional as F
     from aihwkit_lightning_b200.simulator.configs import TorchInferenceRPUConfig
@@ -258,17 +257,8 @@ def test_weight_gradient_reports_its_rows_chunk_by_chunk():
             seen = []
             layer.zero_grad(set_to_none=True)
             x.grad = None
-            with F.operator_settings(after_wgrad=lambda grad, progress=None: seen.append(progress), wgrad_chunks=3,
-                                     comm_sms=16):
+            with F.operator_settings(after_wgrad=lambda grad: seen.append(tuple(grad.shape)), comm_sms=16):
                 layer(x).backward(g)
         for got, ref in zip((x.grad, layer.weight.grad, layer.bias.grad), want):
             assert torch.equal(got, ref), engine
-        progress = seen[0]
-        assert progress.rows == 512 and progress.flags.tolist() == [1, 1, 1]      # 1280 rows: 512 + 512 + 256
-        side = torch.cuda.Stream()
-        side.wait_event(progress.zeroed)
-        lib = _lib.load()
-        _lib.check(lib.al_stream_wait_value32(side.cuda_stream, progress.flags.data_ptr() + 8, 1))
-        done = torch.cuda.Event()
-        done.record(side)
-        done.synchronize()
+        assert seen == [(1280, 1024)]
