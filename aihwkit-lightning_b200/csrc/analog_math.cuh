@@ -192,6 +192,27 @@ AL_HD float frint_add(float x) {
   return fabsf(x) < 4194304.0f ? r : frint(x);
 }
 
+// ---- the tensor-core forward's ADC in bf16 arithmetic, one lane, on values held in floats ------
+// One bf16 operation = the exact result rounded to bf16 once (what mul / fma.rn.bf16x2 do per lane).
+AL_HD float bf16_mul(float a, float b) { return round_bf16(fmul(a, b)); }  // 16-bit product: exact in fp32
+AL_HD float bf16_add(float a, float b) { return round_bf16((float)((double)a + (double)b)); }
+AL_HD float bf16_fma(float a, float b, float c) { return round_bf16((float)((double)a * (double)b + (double)c)); }
+// code of adc_bf16x2 (device_fast.cuh): Markstein division from y = RN_bf16(1 / stepc), then
+// (|q| + 128) - 128 with the sign of o put back.
+AL_HD float adc_code_bf16(float o, float stepc, float y) {
+  const float q0 = bf16_mul(o, y);
+  const float r = bf16_fma(-stepc, q0, o);
+  const float q = bf16_fma(r, y, q0);
+  const float t = bf16_add(bf16_add(fabsf(q), 128.0f), -128.0f);
+  return u2f(f2u(t) | (f2u(o) & 0x80000000u));  // the step is positive: the code has the sign of o
+}
+// Whether every ADC code beyond +-127 ends on the clamp: 128 * step > bound for every bound, with
+// step = RN_bf16(2 bound / states) >= (2 bound / states)(1 - 2^-8), holds for states < 255.
+AL_HD bool adc_codes_fit_a_byte(float out_res, bool has_bound) {
+  const float states = out_res > 1.0f ? out_res : (out_res > 0.0f ? 1.0f / out_res : 0.0f);
+  return has_bound && states > 0.0f && states < 255.0f;
+}
+
 // Quantiser constants of one (row, tile) segment, hoisted out of the element loop.
 struct QuantSeg {
   float bound;   // clamp range (input range for the DAC)

@@ -86,6 +86,68 @@ __device__ __forceinline__ void normal8_keyed(const NoiseKeys& nk, uint64_t grou
   box_muller16(c2, &z[4], &z[5]);
   box_muller16(c3, &z[6], &z[7]);
 }
+// The four 32-bit words behind normal8_keyed(nk, group8, .): word i feeds elements 2i and 2i + 1.
+__device__ __forceinline__ void philox7_keyed(const NoiseKeys& nk, uint64_t group8, uint32_t w[4]) {
+  uint32_t c0 = (uint32_t)group8, c1 = (uint32_t)(group8 >> 32), c2 = nk.c2, c3 = nk.c3;
+#pragma unroll
+  for (int r = 0; r < 7; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ nk.k[2 * r];
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ nk.k[2 * r + 1];
+    c0 = n0; c1 = (uint32_t)p1; c2 = n2; c3 = (uint32_t)p0;
+  }
+  w[0] = c0; w[1] = c1; w[2] = c2; w[3] = c3;
+}
+// Two normals of box_muller16(ab, ..) already multiplied by a scale s and packed as bf16x2 (element
+// 0 in the low half): `neg_c` = -2 ln(2) s^2 goes under the square root, so the scale costs no
+// instruction of its own and the product is rounded to bf16 once.
+__device__ __forceinline__ __nv_bfloat162 box_muller16_scaled(uint32_t ab, float neg_c) {
+  const float f1 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7610));
+  const float f2 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7632));
+  const float u1 = fmaf(f1, -1.52587890625e-05f, 129.0f);
+  float lg, r, s, c;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(u1));
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(neg_c * lg));
+  const float phi = fmaf(f2, 9.587379924285257e-05f, -804.24771931898713f);
+  asm("sin.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(phi));
+  asm("cos.approx.ftz.f32 %0, %1;" : "=f"(c) : "f"(phi));
+  return __floats2bfloat162_rn(r * c, r * s);
+}
+#if defined(AL_EXP_HFMA_NOISE)
+__device__ __forceinline__ __nv_bfloat162 box_muller16_fma(uint32_t ab, float neg_c, __nv_bfloat162 acc) {
+  const float f1 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7610));
+  const float f2 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7632));
+  const float u1 = fmaf(f1, -1.52587890625e-05f, 129.0f);
+  float lg, r, s, c;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(u1));
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(neg_c * lg));
+  const float phi = fmaf(f2, 9.587379924285257e-05f, -804.24771931898713f);
+  asm("sin.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(phi));
+  asm("cos.approx.ftz.f32 %0, %1;" : "=f"(c) : "f"(phi));
+  return __hfma2(__floats2bfloat162_rn(c, s), __floats2bfloat162_rn(r, r), acc);
+}
+#endif
+constexpr float kNegTwoLn2 = -1.3862943611198906f;
+
+// ADC quantisation of a bf16x2 pair, all in packed bf16 arithmetic.
+//   code = rint(RN_bf16(o / stepc)),  result = RN_bf16(code * step)
+// Division: q0 = RN(o y), r = fma(-stepc, q0, o), q = fma(r, y, q0) with y = RN_bf16(1 / stepc) is
+// the correctly rounded bf16 quotient for every pair of 8-bit significands (checked exhaustively
+// on the host).  Rounding to an integer: (|q| + 128) - 128 with the sign of o put back -- sums in
+// [128, 256) have a spacing of 1 in bf16 and round half to even like rint.  Exact for |q| < 128;
+// a larger |q| yields some value >= 128, which is all the caller needs when every code beyond
+// +-127 ends on the clamp (see adc_codes_fit_a_byte).
+__device__ __forceinline__ __nv_bfloat162 adc_bf16x2(__nv_bfloat162 o, __nv_bfloat162 y, __nv_bfloat162 neg_stepc,
+                                                     __nv_bfloat162 step, __nv_bfloat162 c128, __nv_bfloat162 cneg128) {
+  const __nv_bfloat162 q0 = __hmul2_rn(o, y);
+  const __nv_bfloat162 r = __hfma2(neg_stepc, q0, o);
+  const __nv_bfloat162 q = __hfma2(r, y, q0);
+  const __nv_bfloat162 t = __hadd2_rn(__hadd2_rn(__habs2(q), c128), cneg128);
+  const uint32_t code = as_u32(t) | (as_u32(o) & 0x80008000u);  // the step is positive: sign of o
+  return __hmul2_rn(as_bf162(code), step);
+}
+
 // Eight normals for elements [8*group8, 8*group8 + 8) of stream `stream` of call (seed, offset).
 __device__ __forceinline__ void normal8_fast(uint64_t seed, uint64_t offset, uint32_t stream, uint64_t group8,
                                              float z[8]) {

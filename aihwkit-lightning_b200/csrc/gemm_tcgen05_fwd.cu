@@ -244,8 +244,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         if (kMergedNoise) {
           noise_var = t == 0 ? sc * sc : fmaf(sc, sc, noise_var);
           noise_now = t == T - 1;
-          sc = sqrtf(noise_var);
+        } else {
+          noise_var = sc * sc;
         }
+        // fixed modes: the scale of the noise goes under the generator's square root
+        const float noise_neg_c = kNegTwoLn2 * noise_var;
         const float bound = rnd<RD>(fmul(rnd<RD>(fmul(ir, ep.out_bound)), t_max));
         const float step = has_adc ? quant_step<RD>(bound, ep.out_res) : 1.0f;
         const float stepc = step < kTiny ? kTiny : step;
@@ -265,6 +268,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const __nv_bfloat162 zero2 = __float2bfloat162_rn(0.0f);
         const uint64_t nstepc2 = f32x2_pack(-stepc, -stepc), rstep2 = f32x2_pack(rstep, rstep);
         const uint64_t magic2 = f32x2_pack(12582912.0f, 12582912.0f), nmagic2 = f32x2_pack(-12582912.0f, -12582912.0f);
+        // fixed modes: ADC in packed bf16 arithmetic (stepc and its reciprocal are bf16 values or round to them)
+        const __nv_bfloat162 y2 = __float2bfloat162_rn(rstep), nstepc2b = __float2bfloat162_rn(-stepc);
+        const __nv_bfloat162 c128 = __float2bfloat162_rn(128.0f), cneg128 = __float2bfloat162_rn(-128.0f);
         // this thread's row of the shared-memory running sum (PAIR): chunk c of 8 columns sits at
         // 16 * (c ^ (row & 7)), so the eight rows a quarter-warp reads hit distinct banks
         const int srow = quad * 32 + lane;
@@ -293,6 +299,41 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             }
           }
           tmem_wait_ld();
+          if constexpr (kFixed) {
+            // ---- output stage fixed at compile time: everything in packed bf16 arithmetic --------
+            if (t == 0) {
+#pragma unroll
+              for (int pr = 0; pr < 8; ++pr) sumr[pr] = 0u;  // +0.0 in both halves
+            }
+            uint32_t kept = 0;  // bit 2*pr (low half) and bit 16 + 2*pr + 1 (high half): element kept
+#pragma unroll
+            for (int g8 = 0; g8 < 2; ++g8) {
+              uint32_t bits[4];
+              if (noise_now) {
+                const int nq = nh + g8 * 8;
+                philox7_keyed(p.noise, row_group8 + (uint32_t)((nq < N ? nq : 0) >> 3), bits);
+              }
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const int pr = g8 * 4 + q4;  // element 2*pr in the low half, 2*pr+1 in the high half
+                __nv_bfloat162 o2 = __floats2bfloat162_rn(__uint_as_float(accr[2 * pr]), __uint_as_float(accr[2 * pr + 1]));
+#if defined(AL_EXP_HFMA_NOISE)
+                if (noise_now) o2 = box_muller16_fma(bits[q4], noise_neg_c, o2);
+#else
+                if (noise_now) o2 = __hadd2_rn(o2, box_muller16_scaled(bits[q4], noise_neg_c));
+#endif
+                if (has_adc) o2 = adc_bf16x2(o2, y2, nstepc2b, step2, c128, cneg128);
+                if (has_bound) {
+                  // kept <=> inside the clamp (false for NaN, like the reference's -bound <= o <= bound)
+                  kept |= __hle2_mask(__habs2(o2), bound2) & ((1u << (2 * pr)) | (1u << (17 + 2 * pr)));
+                  o2 = __hmin2_nan(__hmax2_nan(o2, nbound2), bound2);
+                }
+                sumr[pr] = as_u32(__hadd2_rn(as_bf162(sumr[pr]), o2));
+              }
+            }
+            if (!has_bound) kept = 0xffffffffu;
+            keep_bits |= ((kept | (kept >> 16)) & 0xffffu) << ((h & 1) * 16);
+          } else {
           float z[16];
           if (noise_now) {
 #pragma unroll
@@ -390,6 +431,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
               keep_bits |= (keep ? 1u : 0u) << ((h & 1) * 16 + j);
             }
           }
+          }  // !kFixed
           if (t < T - 1) {
             if (PAIR) {
 #pragma unroll
@@ -527,8 +569,10 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
     p.small_adc_codes = max_code < 274877906944.0 ? 1 : 0;  // 2^38
   }
   const bool per_channel = ep.w_amax != nullptr && (ep.noise_pc || ep.bound_pc);
+  // the compile-time output stages quantise in packed bf16 arithmetic, which needs every ADC code
+  // beyond +-127 to end on the clamp (up to 254 states: the 8-bit converter and below)
   const bool fixed = round_dt == AL_BF16 && !per_channel && ep.out_noise == nullptr && !ep.no_rounding &&
-                     p.small_adc_codes;
+                     p.small_adc_codes && (!ep.has_adc || adc_codes_fit_a_byte(ep.out_res, ep.has_bound != 0));
   const int mode = fixed ? ((ep.has_noise ? 1 : 0) | (ep.has_adc ? 2 : 0) | (ep.has_bound ? 4 : 0)) : -1;
   // CTA pairs (256 x 256 blocks, packed bf16 output stage only) when there is a block per pair
   // of SMs; single CTAs (128 x 128) otherwise.

@@ -147,6 +147,29 @@ long long km_check_fast_ops(long long n, unsigned long long seed) {
   return bad;
 }
 
+// The tensor-core forward's ADC in bf16 arithmetic (adc_code_bf16) against the reference chain
+// rint(RN_bf16(o / max(step, tiny))): every bf16 step significand at a few exponents, every bf16 o
+// with |o / step| below about 300.  Codes up to +-127 must be equal bit for bit (sign of zero
+// included); where the reference's code is beyond, the fast form must be beyond +-127 as well.
+long long km_check_adc_bf16() {
+  long long bad = 0;
+  const int exps[5] = {-20, -3, 0, 1, 9};
+  for (int e = 0; e < 5; ++e)
+    for (uint32_t sig = 0; sig < 128; ++sig) {
+      const float step = u2f(((uint32_t)(127 + exps[e]) << 23) | (sig << 16));
+      const float stepc = step < kTiny ? kTiny : step;
+      const float y = round_bf16(frcp(stepc));
+      for (uint32_t ob = 0; ob < 65536; ++ob) {
+        const float o = bf16_bits_to_f32((uint16_t)ob);
+        if (!(fabsf(o) <= 300.0f * step)) continue;  // also skips NaN and infinities
+        const float want = quant_code<kBF16>(o, step, false);
+        const float got = adc_code_bf16(o, stepc, y);
+        if (fabsf(want) < 128.0f ? f2u(got) != f2u(want) : !(fabsf(got) >= 128.0f)) ++bad;
+      }
+    }
+  return bad;
+}
+
 // n standard normals of stream `stream` of call (seed, offset), element indices [0, n)
 void km_normals(unsigned long long seed, unsigned long long offset, unsigned stream, long long n, float* out) {
   for (long long i = 0; i < n; ++i) out[i] = normal1(seed, offset, stream, (uint64_t)i);

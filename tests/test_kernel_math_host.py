@@ -127,6 +127,14 @@ def test_fast_division_rint_and_rounding_are_exact(km):
     assert km.km_check_fast_ops(ctypes.c_longlong(20_000_000), ctypes.c_ulonglong(12345)) == 0
 
 
+def test_packed_bf16_adc_is_exact(km):
+    """The tensor-core forward divides, rounds to an integer and multiplies back in packed bf16
+    arithmetic; over every step significand and every bf16 input the codes up to +-127 equal the
+    reference chain bit for bit, and larger ones stay beyond +-127 (where the clamp takes over)."""
+    km.km_check_adc_bf16.restype = ctypes.c_longlong
+    assert km.km_check_adc_bf16() == 0
+
+
 def test_generator_moments(km):
     n = 1 << 18
     out = torch.empty(n)
