@@ -198,13 +198,13 @@ AL_HD float bf16_mul(float a, float b) { return round_bf16(fmul(a, b)); }  // 16
 AL_HD float bf16_add(float a, float b) { return round_bf16((float)((double)a + (double)b)); }
 AL_HD float bf16_fma(float a, float b, float c) { return round_bf16((float)((double)a * (double)b + (double)c)); }
 // code of adc_bf16x2 (device_fast.cuh): Markstein division from y = RN_bf16(1 / stepc), then
-// (|q| + 128) - 128 with the sign of o put back.
+// (q + s) - s with s = 128 carrying the sign of o.
 AL_HD float adc_code_bf16(float o, float stepc, float y) {
   const float q0 = bf16_mul(o, y);
   const float r = bf16_fma(-stepc, q0, o);
   const float q = bf16_fma(r, y, q0);
-  const float t = bf16_add(bf16_add(fabsf(q), 128.0f), -128.0f);
-  return u2f(f2u(t) | (f2u(o) & 0x80000000u));  // the step is positive: the code has the sign of o
+  const float s128 = u2f((f2u(o) & 0x80000000u) | 0x43000000u);
+  return bf16_add(bf16_add(q, s128), -s128);
 }
 // Whether every ADC code beyond +-127 ends on the clamp: 128 * step > bound for every bound, with
 // step = RN_bf16(2 bound / states) >= (2 bound / states)(1 - 2^-8), holds for states < 255.

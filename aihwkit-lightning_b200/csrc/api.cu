@@ -555,6 +555,17 @@ int al_clip_weights(int32_t dtype, void* w, int32_t rows, int32_t cols, int32_t 
   return launch_clip_weights(dtype, w, rows, cols, clip_type, sigma, scratch, (cudaStream_t)stream);
 }
 
+int al_set_device_wait_limit_ns(uint64_t ns) { return tc_set_wait_limit(ns == 0 ? 2000000000ull : ns); }
+
+int al_debug_withhold_forward_signal(int32_t on) {
+  cudaError_t e = tc_fwd_set_withhold_acc_signal(on != 0 ? 1u : 0u);
+  if (e != cudaSuccess) {
+    set_error("al_debug_withhold_forward_signal: %s", cudaGetErrorString(e));
+    return AL_ERR_CUDA;
+  }
+  return AL_OK;
+}
+
 int al_read_device_error(void* stream, uint32_t* out_code) {
   if (!out_code) return AL_ERR_BAD_ARGUMENT;
   return tc_read_device_error((cudaStream_t)stream, out_code);

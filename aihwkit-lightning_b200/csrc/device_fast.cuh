@@ -99,22 +99,9 @@ __device__ __forceinline__ void philox7_keyed(const NoiseKeys& nk, uint64_t grou
   }
   w[0] = c0; w[1] = c1; w[2] = c2; w[3] = c3;
 }
-// Two normals of box_muller16(ab, ..) already multiplied by a scale s and packed as bf16x2 (element
-// 0 in the low half): `neg_c` = -2 ln(2) s^2 goes under the square root, so the scale costs no
-// instruction of its own and the product is rounded to bf16 once.
-__device__ __forceinline__ __nv_bfloat162 box_muller16_scaled(uint32_t ab, float neg_c) {
-  const float f1 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7610));
-  const float f2 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7632));
-  const float u1 = fmaf(f1, -1.52587890625e-05f, 129.0f);
-  float lg, r, s, c;
-  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(u1));
-  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(neg_c * lg));
-  const float phi = fmaf(f2, 9.587379924285257e-05f, -804.24771931898713f);
-  asm("sin.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(phi));
-  asm("cos.approx.ftz.f32 %0, %1;" : "=f"(c) : "f"(phi));
-  return __floats2bfloat162_rn(r * c, r * s);
-}
-#if defined(AL_EXP_HFMA_NOISE)
+// acc + s * (z0, z1) for the two normals of box_muller16(ab, ..) and a scale s, in packed bf16:
+// `neg_c` = -2 ln(2) s^2 goes under the square root, so the radius comes out scaled; the unit vector
+// (cos, sin) and the radius are rounded to bf16 and meet the accumulator in one fused multiply-add.
 __device__ __forceinline__ __nv_bfloat162 box_muller16_fma(uint32_t ab, float neg_c, __nv_bfloat162 acc) {
   const float f1 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7610));
   const float f2 = __uint_as_float(__byte_perm(ab, 0x4b000000u, 0x7632));
@@ -127,25 +114,25 @@ __device__ __forceinline__ __nv_bfloat162 box_muller16_fma(uint32_t ab, float ne
   asm("cos.approx.ftz.f32 %0, %1;" : "=f"(c) : "f"(phi));
   return __hfma2(__floats2bfloat162_rn(c, s), __floats2bfloat162_rn(r, r), acc);
 }
-#endif
 constexpr float kNegTwoLn2 = -1.3862943611198906f;
 
 // ADC quantisation of a bf16x2 pair, all in packed bf16 arithmetic.
 //   code = rint(RN_bf16(o / stepc)),  result = RN_bf16(code * step)
 // Division: q0 = RN(o y), r = fma(-stepc, q0, o), q = fma(r, y, q0) with y = RN_bf16(1 / stepc) is
 // the correctly rounded bf16 quotient for every pair of 8-bit significands (checked exhaustively
-// on the host).  Rounding to an integer: (|q| + 128) - 128 with the sign of o put back -- sums in
-// [128, 256) have a spacing of 1 in bf16 and round half to even like rint.  Exact for |q| < 128;
-// a larger |q| yields some value >= 128, which is all the caller needs when every code beyond
-// +-127 ends on the clamp (see adc_codes_fit_a_byte).
+// on the host).  Rounding to an integer: (q + s) - s with s = 128 carrying the sign of o -- sums
+// with a magnitude in [128, 256) have a spacing of 1 in bf16 and round half to even like rint.
+// Exact for |q| < 128 (a zero code comes out as +0 whatever the sign of o); a larger |q| yields
+// some value of magnitude >= 128, which is all the caller needs when every code beyond +-127 ends
+// on the clamp (see adc_codes_fit_a_byte).
 __device__ __forceinline__ __nv_bfloat162 adc_bf16x2(__nv_bfloat162 o, __nv_bfloat162 y, __nv_bfloat162 neg_stepc,
-                                                     __nv_bfloat162 step, __nv_bfloat162 c128, __nv_bfloat162 cneg128) {
+                                                     __nv_bfloat162 step) {
   const __nv_bfloat162 q0 = __hmul2_rn(o, y);
   const __nv_bfloat162 r = __hfma2(neg_stepc, q0, o);
   const __nv_bfloat162 q = __hfma2(r, y, q0);
-  const __nv_bfloat162 t = __hadd2_rn(__hadd2_rn(__habs2(q), c128), cneg128);
-  const uint32_t code = as_u32(t) | (as_u32(o) & 0x80008000u);  // the step is positive: sign of o
-  return __hmul2_rn(as_bf162(code), step);
+  const __nv_bfloat162 s128 = as_bf162((as_u32(o) & 0x80008000u) | 0x43004300u);
+  const __nv_bfloat162 code = __hsub2_rn(__hadd2_rn(q, s128), s128);
+  return __hmul2_rn(code, step);
 }
 
 // Eight normals for elements [8*group8, 8*group8 + 8) of stream `stream` of call (seed, offset).

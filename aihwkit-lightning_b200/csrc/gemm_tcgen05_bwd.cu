@@ -125,7 +125,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const uint32_t ph = (j / B_STAGES) & 1u;
         uint64_t t0 = globaltimer_ns();
         while (!mbar_try(&bars->full[s], ph)) {
-          if (globaltimer_ns() - t0 > kTimeoutNs) {
+          if (globaltimer_ns() - t0 > wait_limit_ns()) {
             raise_error(kErrDrain, abort_flag);
             break;
           }
@@ -177,7 +177,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       umma_commit(&bars->mma_done);
       uint64_t t0 = globaltimer_ns();
       while (!mbar_try(&bars->mma_done, 0)) {
-        if (globaltimer_ns() - t0 > kTimeoutNs) {
+        if (globaltimer_ns() - t0 > wait_limit_ns()) {
           raise_error(kErrDrain, abort_flag);
           break;
         }
@@ -374,16 +374,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 // complete on its own barrier, its transform warps fix the A tile up and then vouch for the
 // stage on the leader's `ready`, which gates the MMA.
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  uint64_t t0 = 0;
-  for (uint32_t spin = 0;; ++spin) {
-    if (mbar_try_cluster(bar, parity)) return true;
-    if ((spin & 31u) == 31u) {
-      if (*abort_flag) return false;
-      uint64_t now = globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > kTimeoutNs) return false;
-    }
-  }
+  return mbar_wait(bar, parity, abort_flag);
 }
 
 template <bool WGRAD>
@@ -477,7 +468,7 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           const uint32_t ph = (j / P_STAGES) & 1u;
           uint64_t t0 = globaltimer_ns();
           while (!mbar_try_cluster(&bars->full[s], ph)) {
-            if (globaltimer_ns() - t0 > kTimeoutNs) {
+            if (globaltimer_ns() - t0 > wait_limit_ns()) {
               raise_error(kErrDrain, abort_flag);
               break;
             }
@@ -526,7 +517,7 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       umma_commit_pair(&bars->mma_done, 1);
       uint64_t t0 = globaltimer_ns();
       while (!mbar_try_cluster(&bars->mma_done, 0)) {
-        if (globaltimer_ns() - t0 > kTimeoutNs) {
+        if (globaltimer_ns() - t0 > wait_limit_ns()) {
           raise_error(kErrDrain, abort_flag);
           break;
         }
@@ -790,6 +781,16 @@ int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, in
                     int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s) {
   ProfScope prof(AL_K_WGRAD_GEMM, s);
   return launch_bwd_tc(true, g, xq, keep_mask, mask_words, M, K, N, tt, pairing, grad_w, s);
+}
+
+int tc_set_wait_limit(unsigned long long ns) {
+  cudaError_t e = set_wait_limit(ns);
+  if (e == cudaSuccess) e = tc_fwd_set_wait_limit(ns);
+  if (e != cudaSuccess) {
+    set_error("al_set_device_wait_limit_ns: %s", cudaGetErrorString(e));
+    return AL_ERR_CUDA;
+  }
+  return AL_OK;
 }
 
 int tc_read_device_error(cudaStream_t s, uint32_t* code) {

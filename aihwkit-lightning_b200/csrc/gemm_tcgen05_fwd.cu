@@ -104,7 +104,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
-            if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag)) {
+            if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag AL_POLL_ROLE(0))) {
               raise_error(kErrProducer, abort_flag);
               ok = false;
               break;
@@ -133,7 +133,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           const uint32_t ph = (j / kStages) & 1u;
           uint64_t t0 = globaltimer_ns();
           while (!mbar_try(&bars->full[s], ph)) {
-            if (globaltimer_ns() - t0 > kTimeoutNs) {
+            if (globaltimer_ns() - t0 > wait_limit_ns()) {
               raise_error(kErrDrain, abort_flag);
               break;
             }
@@ -147,11 +147,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       constexpr uint32_t idesc = make_idesc(kBlockRows, kBN, 0, 0);
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
+      const bool withhold = *(volatile uint32_t*)&g_tc_withhold_acc_signal != 0u;  // test aid, see its declaration
       for (int tile = worker; tile < num_tiles && ok; tile += n_workers) {
         for (int t = 0; t < T && ok; ++t, ++acc_it) {
           const int b = acc_it & 1u;
           const uint32_t aph = (acc_it >> 1) & 1u;
-          if (!mbar_wait(&bars->acc_empty[b], aph ^ 1u, abort_flag)) {
+          if (!mbar_wait(&bars->acc_empty[b], aph ^ 1u, abort_flag AL_POLL_ROLE(1))) {
             raise_error(kErrMma, abort_flag);
             ok = false;
             break;
@@ -161,7 +162,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
-            if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
+            if (!mbar_wait(&bars->full[s], ph, abort_flag AL_POLL_ROLE(2))) {
               raise_error(kErrMma, abort_flag);
               ok = false;
               break;
@@ -177,7 +178,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             if (PAIR) umma_commit_pair(&bars->empty[s], 3);  // frees the stage in both CTAs
             else umma_commit(&bars->empty[s]);
           }
-          if (ok) {
+          if (ok && !withhold) {
             if (PAIR) umma_commit_pair(&bars->acc_full[b], 3);
             else umma_commit(&bars->acc_full[b]);
           }
@@ -188,14 +189,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       else umma_commit(&bars->mma_done);
       uint64_t t0 = globaltimer_ns();
       while (!mbar_try(&bars->mma_done, 0)) {
-        if (globaltimer_ns() - t0 > kTimeoutNs) {
+        if (globaltimer_ns() - t0 > wait_limit_ns()) {
           raise_error(kErrDrain, abort_flag);
           break;
         }
       }
     }
   } else if (warp >= 4) {
-    // ---- epilogue: per-tile output stage, running sum in TMEM ---------------------------
+    // ---- epilogue: per-tile output stage and running sum ----------------------------------
     // 16 warps: warp & 3 selects the TMEM lane quadrant (rows), (warp - 4) >> 2 the kCols columns.
     constexpr int kCols = kBN / 4;
     const int quad = warp & 3;
@@ -253,7 +254,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const float step = has_adc ? quant_step<RD>(bound, ep.out_res) : 1.0f;
         const float stepc = step < kTiny ? kTiny : step;
         const float rstep = __frcp_rn(stepc);
-        if (!mbar_wait(&bars->acc_full[b], aph, abort_flag)) {
+        if (!mbar_wait(&bars->acc_full[b], aph, abort_flag AL_POLL_ROLE(3))) {
           if (lane == 0) raise_error(kErrEpilogue, abort_flag);
           ok = false;
           break;
@@ -270,12 +271,18 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const uint64_t magic2 = f32x2_pack(12582912.0f, 12582912.0f), nmagic2 = f32x2_pack(-12582912.0f, -12582912.0f);
         // fixed modes: ADC in packed bf16 arithmetic (stepc and its reciprocal are bf16 values or round to them)
         const __nv_bfloat162 y2 = __float2bfloat162_rn(rstep), nstepc2b = __float2bfloat162_rn(-stepc);
-        const __nv_bfloat162 c128 = __float2bfloat162_rn(128.0f), cneg128 = __float2bfloat162_rn(-128.0f);
         // this thread's row of the shared-memory running sum (PAIR): chunk c of 8 columns sits at
         // 16 * (c ^ (row & 7)), so the eight rows a quarter-warp reads hit distinct banks
         const int srow = quad * 32 + lane;
         const uint32_t sum_row = smem_u32(sum_base) + (uint32_t)srow * (uint32_t)(kBN * 2);
-#pragma unroll 1
+        // word (t, first column of this warp / 32, row m) of the clamp mask; the next word of the row is M further
+        uint32_t* const mask_p = ep.keep_mask != nullptr
+                                     ? ep.keep_mask + ((int64_t)t * ep.mask_words + (n_first >> 5)) * M + (row_ok ? m : 0)
+                                     : nullptr;
+        // the compile-time output stages unroll the walk over this warp's columns: every offset below
+        // becomes an immediate
+        constexpr int kUnrollH = kFixed ? kCols / 16 : 1;
+#pragma unroll kUnrollH
         for (int h = 0; h < kCols / 16; ++h) {
           const int cc = col0 + h * 16;
           const int nh = n_first + h * 16;
@@ -317,16 +324,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
               for (int q4 = 0; q4 < 4; ++q4) {
                 const int pr = g8 * 4 + q4;  // element 2*pr in the low half, 2*pr+1 in the high half
                 __nv_bfloat162 o2 = __floats2bfloat162_rn(__uint_as_float(accr[2 * pr]), __uint_as_float(accr[2 * pr + 1]));
-#if defined(AL_EXP_HFMA_NOISE)
                 if (noise_now) o2 = box_muller16_fma(bits[q4], noise_neg_c, o2);
-#else
-                if (noise_now) o2 = __hadd2_rn(o2, box_muller16_scaled(bits[q4], noise_neg_c));
-#endif
-                if (has_adc) o2 = adc_bf16x2(o2, y2, nstepc2b, step2, c128, cneg128);
+                if (has_adc) o2 = adc_bf16x2(o2, y2, nstepc2b, step2);
                 if (has_bound) {
-                  // kept <=> inside the clamp (false for NaN, like the reference's -bound <= o <= bound)
-                  kept |= __hle2_mask(__habs2(o2), bound2) & ((1u << (2 * pr)) | (1u << (17 + 2 * pr)));
-                  o2 = __hmin2_nan(__hmax2_nan(o2, nbound2), bound2);
+                  // kept <=> the clamp leaves the value unchanged (false for NaN, like the reference's
+                  // -bound <= o <= bound)
+                  const __nv_bfloat162 c2 = __hmin2_nan(__hmax2_nan(o2, nbound2), bound2);
+                  kept |= __heq2_mask(c2, o2) & ((1u << (2 * pr)) | (1u << (17 + 2 * pr)));
+                  o2 = c2;
                 }
                 sumr[pr] = as_u32(__hadd2_rn(as_bf162(sumr[pr]), o2));
               }
@@ -477,8 +482,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
               }
             }
           }
-          if ((h & 1) && ep.keep_mask != nullptr && row_ok && (n0 >> 5) < ep.mask_words)
-            ep.keep_mask[((int64_t)t * ep.mask_words + (n0 >> 5)) * M + m] = keep_bits;  // lanes = consecutive rows
+          if ((h & 1) && mask_p != nullptr && row_ok && (n0 >> 5) < ep.mask_words)
+            mask_p[(int64_t)(h >> 1) * M] = keep_bits;  // lanes = consecutive rows
         }
         tmem_wait_st();
         tc_fence_before();
@@ -527,14 +532,14 @@ static FwdKernel pick_fwd_kernel(int mode, int round_dt) {
 }
 
 // how many CTA pairs of the forward kernel the device runs at once (0: it cannot)
-static int max_fwd_pairs(FwdKernel kernel) {
+static int max_fwd_pairs(FwdKernel kernel, int smem) {
   static FwdKernel seen[24];
   static int count[24];
   static int n_seen = 0;
   for (int i = 0; i < n_seen; ++i)
     if (seen[i] == kernel) return count[i];
   int clusters = 0;
-  PairLaunch pl(2 * sm_count(), kFwdThreads, FP_SMEM, nullptr);
+  PairLaunch pl(2 * sm_count(), kFwdThreads, smem, nullptr);
   if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &pl.cfg) != cudaSuccess) {
     cudaGetLastError();
     clusters = 0;
@@ -583,11 +588,12 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
   const int pair_tiles = ((ep.M + 2 * BM - 1) / (2 * BM)) * ((ep.N + 2 * F_BN - 1) / (2 * F_BN));
   FwdKernel kernel = nullptr;
   int rc = AL_OK, pairs = 0;
+  const int pair_smem = FP_SMEM;
   if (pair_ok) {
     kernel = pick_fwd_kernel<true>(mode, round_dt);
-    rc = ensure_smem(kernel, FP_SMEM);
+    rc = ensure_smem(kernel, pair_smem);
     if (rc) return rc;
-    pairs = max_fwd_pairs(kernel);
+    pairs = max_fwd_pairs(kernel, pair_smem);
   }
   const bool pair = pairs > 0 && (pair_tiles >= pairs || pairing > 0);
   if (!pair) {
@@ -614,7 +620,7 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
     if (rc) return rc;
   }
   if (pair) {
-    PairLaunch pl(2 * (pair_tiles < pairs ? pair_tiles : pairs), kFwdThreads, FP_SMEM, s);
+    PairLaunch pl(2 * (pair_tiles < pairs ? pair_tiles : pairs), kFwdThreads, pair_smem, s);
     cudaError_t e = cudaLaunchKernelEx(&pl.cfg, kernel, map_a, map_b, p);
     if (e != cudaSuccess) {
       set_error("fwd_tc (pairs): %s", cudaGetErrorString(e));
@@ -629,5 +635,15 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
 }
 
 cudaError_t tc_fwd_take_error_word(uint32_t* code) { return take_error_word(code); }
+#if defined(AL_EXP_COUNT_POLLS)
+extern "C" int al_exp_poll_counts(unsigned long long* out, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, g_poll_counts, sizeof(unsigned long long) * 16);
+  if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(g_poll_counts, z, sizeof(z)); }
+  return 0;
+}
+#endif
+cudaError_t tc_fwd_set_wait_limit(unsigned long long ns) { return set_wait_limit(ns); }
+cudaError_t tc_fwd_set_withhold_acc_signal(uint32_t on) { return set_withhold_acc_signal(on); }
 
 }  // namespace al

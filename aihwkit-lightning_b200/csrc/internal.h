@@ -153,6 +153,11 @@ int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask,
 int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, int mask_words,
                     int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s);
 int tc_read_device_error(cudaStream_t s, uint32_t* code);
+// limit of the device-side waits of all tcgen05 kernels (both translation units)
+int tc_set_wait_limit(unsigned long long ns);
+cudaError_t tc_fwd_set_wait_limit(unsigned long long ns);
+// test aid: the forward kernel's MMA issuer withholds its "accumulator full" signal
+cudaError_t tc_fwd_set_withhold_acc_signal(uint32_t on);
 // the forward translation unit's own error word (read and cleared); the stream must be idle
 cudaError_t tc_fwd_take_error_word(uint32_t* code);
 

@@ -21,11 +21,25 @@ namespace al {
 namespace {
 
 __device__ uint32_t g_tc_error_word = 0;
+// Wall-clock limit of every device-side wait, in nanoseconds.  A variable (not a constant) so that
+// a test can make the waits run out (al_set_device_wait_limit_ns): a wait that gives up raises
+// the error word and the CTA leaves in an orderly way.  Read on the slow path of a wait only.
+__device__ unsigned long long g_tc_wait_limit_ns = 2000000000ull;
+// Test aid: non-zero makes the forward kernel's MMA issuer withhold the "accumulator full" signal,
+// so that the output-stage warps' wait for it runs out (nothing traps or spins without bound: the
+// wait gives up after the limit above, the other roles see the abort flag and the kernel returns).
+__device__ uint32_t g_tc_withhold_acc_signal = 0;
 
 constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle span
 constexpr int kThreads = 384;          // 12 warps
-constexpr uint64_t kTimeoutNs = 2000000000ull;
+constexpr uint64_t kDefaultWaitLimitNs = 2000000000ull;
+// A waiting thread is parked by the barrier unit for up to this long per attempt and wakes when
+// the barrier's state changes: a thread that polls in a tight loop takes issue slots from the
+// warps of its scheduler that have work to do, and the producer and the MMA issuer wait nearly
+// all the time.  (Measured: sleeping a fixed time between polls instead is slower -- the wake-up
+// then lags the event -- and plain polling slower still.)
+constexpr uint32_t kSuspendHintNs = 20000u;
 
 // forward kernel
 constexpr int F_BN = 128;
@@ -93,23 +107,41 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ uint64_t wait_limit_ns() { return *(volatile unsigned long long*)&g_tc_wait_limit_ns; }
+#if defined(AL_EXP_COUNT_POLLS)
+__device__ unsigned long long g_poll_counts[16];
+#define AL_POLL_ROLE(r) , r
+#define AL_POLL_COUNT(r) atomicAdd(&g_poll_counts[r], 1ull)
+#else
+#define AL_POLL_ROLE(r)
+#define AL_POLL_COUNT(r)
+#endif
 // Bounded wait.  Returns false when the wait gave up (time limit, or another role aborted).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag
+#if defined(AL_EXP_COUNT_POLLS)
+                                          , int role = 15
+#endif
+) {
+#if defined(AL_EXP_COUNT_POLLS)
+  const long long c0 = clock64();
+  struct Acc { long long c0; int role; __device__ ~Acc() { if ((threadIdx.x & 31) == 0) { atomicAdd(&g_poll_counts[8 + role], (unsigned long long)(clock64() - c0)); atomicAdd(&g_poll_counts[4 + role], 1ull); } } } acc_{c0, role};
+#endif
   uint64_t t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
     if (mbar_try(bar, parity)) return true;
-    if ((spin & 31u) == 31u) {
+    AL_POLL_COUNT(role);
+    if ((spin & 3u) == 3u) {
       if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kTimeoutNs) return false;
+      else if (now - t0 > wait_limit_ns()) return false;
     }
   }
 }
@@ -188,10 +220,10 @@ __device__ __forceinline__ bool mbar_try_cluster(uint64_t* bar, uint32_t parity)
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
@@ -472,6 +504,15 @@ bool tc_shape_ok(const AlDesc& d, const TileTable& tt) {
   if (!uniform_tiles(tt, &w)) return false;
   if (w % 8 != 0 || d.K % 8 != 0 || d.N % 8 != 0) return false;
   return true;
+}
+
+// Sets this translation unit's limit of the device-side waits.
+cudaError_t set_wait_limit(unsigned long long ns) {
+  return cudaMemcpyToSymbol(g_tc_wait_limit_ns, &ns, sizeof(ns));
+}
+
+cudaError_t set_withhold_acc_signal(uint32_t on) {
+  return cudaMemcpyToSymbol(g_tc_withhold_acc_signal, &on, sizeof(on));
 }
 
 // Takes (reads and clears) this translation unit's device error word.  The stream must be idle.

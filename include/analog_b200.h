@@ -230,6 +230,17 @@ int al_fold2d(int32_t dtype, const void* grad_patches, int32_t B, int32_t C, int
  * clears it; synchronises `stream`.  0 = no error. */
 int al_read_device_error(void* stream, uint32_t* out_code);
 
+/* Every wait inside the tcgen05 kernels (on an mbarrier: a TMA copy, an MMA commit, a peer CTA) is
+ * bounded by a wall-clock limit, 2 s by default; a wait that runs out sets the error word above,
+ * the CTA drains its copies in flight, frees its tensor memory and returns -- the context stays
+ * usable.  al_set_device_wait_limit_ns changes the limit for kernels launched afterwards on the
+ * current device (0 restores the default).  al_debug_withhold_forward_signal(1) is a test aid:
+ * the forward kernel then withholds the signal its output-stage warps wait for, so that their
+ * wait runs out after the limit and the path above can be exercised; (0) restores normal
+ * operation.  Neither has a counterpart in the reference. */
+int al_set_device_wait_limit_ns(uint64_t ns);
+int al_debug_withhold_forward_signal(int32_t on);
+
 /* 1 if the given problem would run on the tcgen05/TMA kernels under AL_ENGINE_AUTO. */
 int al_uses_tcgen05(const AlDesc* desc, const int32_t* tile_ends_host);
 

@@ -149,8 +149,8 @@ long long km_check_fast_ops(long long n, unsigned long long seed) {
 
 // The tensor-core forward's ADC in bf16 arithmetic (adc_code_bf16) against the reference chain
 // rint(RN_bf16(o / max(step, tiny))): every bf16 step significand at a few exponents, every bf16 o
-// with |o / step| below about 300.  Codes up to +-127 must be equal bit for bit (sign of zero
-// included); where the reference's code is beyond, the fast form must be beyond +-127 as well.
+// with |o / step| below about 300.  Codes up to +-127 must be equal (a zero code may differ in
+// its sign); where the reference's code is beyond, the fast form must be beyond +-127 as well.
 long long km_check_adc_bf16() {
   long long bad = 0;
   const int exps[5] = {-20, -3, 0, 1, 9};
@@ -164,7 +164,7 @@ long long km_check_adc_bf16() {
         if (!(fabsf(o) <= 300.0f * step)) continue;  // also skips NaN and infinities
         const float want = quant_code<kBF16>(o, step, false);
         const float got = adc_code_bf16(o, stepc, y);
-        if (fabsf(want) < 128.0f ? f2u(got) != f2u(want) : !(fabsf(got) >= 128.0f)) ++bad;
+        if (fabsf(want) < 128.0f ? !(got == want) : !(fabsf(got) >= 128.0f)) ++bad;
       }
     }
   return bad;

@@ -130,7 +130,7 @@ def test_fast_division_rint_and_rounding_are_exact(km):
 def test_packed_bf16_adc_is_exact(km):
     """The tensor-core forward divides, rounds to an integer and multiplies back in packed bf16
     arithmetic; over every step significand and every bf16 input the codes up to +-127 equal the
-    reference chain bit for bit, and larger ones stay beyond +-127 (where the clamp takes over)."""
+    reference chain (a zero code may come out as +0 where the reference has -0), and larger ones stay beyond +-127 (where the clamp takes over)."""
     km.km_check_adc_bf16.restype = ctypes.c_longlong
     assert km.km_check_adc_bf16() == 0
 

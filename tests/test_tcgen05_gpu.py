@@ -262,3 +262,47 @@ def test_weight_gradients_first_when_a_hook_asks_for_them():
         for got, ref in zip((x.grad, layer.weight.grad, layer.bias.grad), want):
             assert torch.equal(got, ref), engine
         assert seen == [(1280, 1024)]
+
+
+@pytest.mark.parametrize("engine", ["tcgen05_single", "tcgen05_pair"])
+def test_a_wait_that_runs_out_raises_the_error_word_and_the_context_stays_usable(engine):
+    """Failure path of the bounded device-side waits.  With the wait limit at 2 ms and the forward
+    kernel told to withhold the signal its output-stage warps wait for, that wait runs out: the
+    warps raise the error word, every other role of the kernel sees the abort flag (or runs out
+    itself), copies in flight are drained, tensor memory is freed and the kernel returns.  The host
+    reads ``AL_ERR_DEVICE_TIMEOUT``; afterwards the same call works again and gives the same result
+    as before.  Nothing traps, faults or waits without bound in this test."""
+    from aihwkit_lightning_b200 import _lib
+    from aihwkit_lightning_b200.nn import AnalogLinear
+    from aihwkit_lightning_b200.nn import functional as F
+    from aihwkit_lightning_b200.simulator.configs import TorchInferenceRPUConfig
+
+    lib = _lib.load()
+    rpu = TorchInferenceRPUConfig()
+    rpu.mapping.max_input_size = 256
+    rpu.forward.inp_res = 254
+    rpu.forward.out_res = 254
+    rpu.forward.out_bound = 10.0
+    rpu.pre_post.input_range.enable = True
+    rpu.pre_post.input_range.dynamic = True
+    torch.manual_seed(0)
+    layer = AnalogLinear(512, 512, bias=False, rpu_config=rpu).to(device="cuda", dtype=torch.bfloat16).eval()
+    x = torch.randn(512, 512, device="cuda").bfloat16()
+    with F.operator_settings(engine=engine), torch.no_grad():
+        before = layer(x).clone()
+        assert device_error() == (0, 0)
+        torch.cuda.synchronize()
+        _lib.check(lib.al_set_device_wait_limit_ns(2_000_000))
+        _lib.check(lib.al_debug_withhold_forward_signal(1))
+        try:
+            layer(x)
+            status, code = device_error()
+        finally:
+            _lib.check(lib.al_debug_withhold_forward_signal(0))
+            _lib.check(lib.al_set_device_wait_limit_ns(0))
+        assert status == _lib.AL_ERR_DEVICE_TIMEOUT
+        assert code & 4, f"the output-stage warps must have given up (role mask {code:#x})"
+        after = layer(x)
+        torch.cuda.synchronize()
+        assert device_error() == (0, 0)
+        assert torch.equal(after, before)
