@@ -1,26 +1,37 @@
-"""Benchmark of the analog linear hot path (forward + backward of one analog layer).
+"""Benchmark of the analog linear hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config c2|c1|c3|c4|c5]
 
-Workload (N=1): the configuration the headline metric is quoted on -- ``AnalogLinear``
-4096 -> 4096 in bf16, 8192 tokens ~N(0,1), ``max_input_size=512`` (8 analog tiles), dynamic
-per-token input ranges with an 8-bit DAC, 8-bit ADC with ``out_bound=10``, ``out_noise=0.04``,
-weight noise 0.02 relative to the per-channel abs-max, training mode, forward + backward.
-A "step" is one forward + backward over one batch of synthetic tokens; the metric is
-algorithmic TFLOP/s = 6*M*K*N / time.
+Default workload (``--config c2``, N=1): the configuration the headline metric is quoted on --
+``AnalogLinear`` 4096 -> 4096 in bf16, 8192 tokens ~N(0,1), ``max_input_size=512`` (8 analog
+tiles), dynamic per-token input ranges with an 8-bit DAC, 8-bit ADC with ``out_bound=10``,
+``out_noise=0.04``, weight noise 0.02 relative to the per-channel abs-max, training mode,
+forward + backward.  A "step" is one forward + backward over one batch of synthetic tokens; the
+metric is algorithmic TFLOP/s = 6*M*K*N / time.
 
 * ``value``: inputs resident in HBM, CUDA-event timing over exactly K steps (max over ranks).
 * ``e2e``: the same step through the public ``AnalogLinear`` call with the batch in pinned
   host memory: every step uploads its batch (double-buffered on a copy stream, so the upload
   of the next batch overlaps the current step) and copies its loss back to pinned host memory,
-  where the host reads it one step later; all inside the timed region.
+  where the host reads it one step later; all inside the timed region.  The upload is 67 MB per
+  0.8 ms step, so this number is bound by the host link, not by the kernels.
 * ``roofline``: the dominant kernel, timed live with CUDA events by the library's launch
-  accounting, against the measured bf16 tensor peak.
+  accounting, against the measured burst bf16 tensor peak (the timed region lasts milliseconds).
 * ``cpu_baseline`` / ``--impl reference``: the CPU restatement of the reference's torch path
   (``oracle/analog_oracle.py::linear_autograd``) timed on the host cores on a bounded sample
   of the workload (fewer rows, same K, N and tiling).
-* N > 1 (torchrun): every rank runs the layer on its own batch (weak scaling) and the weight
-  gradient is all-reduced over NCCL, as in data-parallel training.
+* ``gpu_torch_baseline`` (N=1): the same restatement of the reference's torch path run on CUDA
+  tensors of the full workload (cuBLAS per-tile GEMMs + eager element-wise kernels), timed after
+  the library's own measurement: what the reference's torch backend costs on the same GPU.
+* ``c3``: one full data-parallel training step of the Phi-3-mini-shaped decoder (32 layers,
+  d=3072, MLP 8192, vocab 32064, every Linear analog, sequence 2048 x micro-batch 4 per GPU, AdamW),
+  timed after the headline: tokens/s, analog TFLOP/s and the exposed part of the gradient exchange.
+* N > 1 (torchrun): every rank runs on its own batch (weak scaling) and the weight gradients
+  are all-reduced over NCCL, as in data-parallel training.
+
+``--config c1 | c4 | c5`` measure the other benchmark configurations with the same line format
+(c1: the fp32 1024 x 1024 layer; c4: a ResNet-32 training step; c5: the inference shape sweep);
+``--config c3`` prints the decoder step as a line of its own.
 """
 import argparse
 import json
@@ -38,18 +49,21 @@ M, K, N, MAX_IN = 8192, 4096, 4096, 512
 CPU_SAMPLE_ROWS = 1024
 FLOP_PER_STEP = 6.0 * M * K * N
 L2_FLUSH_BYTES = 256 << 20
+# DRAM bytes (read + write) of one forward-GEMM launch on the headline workload, from the ncu
+# capture summarised in profiles/fwd_tc_kernel_c2.md
 FWD_KERNEL_DRAM_BYTES = 120.1e6 + 76.4e6
 
 
-def make_rpu_config(ns):
+def make_rpu_config(ns, max_in=MAX_IN, adc=True, out_noise=0.04, dynamic=True):
     rpu = ns.TorchInferenceRPUConfig()
-    rpu.mapping.max_input_size = MAX_IN
+    rpu.mapping.max_input_size = max_in
     rpu.forward.inp_res = 254.0
-    rpu.forward.out_res = 254.0
-    rpu.forward.out_bound = 10.0
-    rpu.forward.out_noise = 0.04
+    if adc:
+        rpu.forward.out_res = 254.0
+        rpu.forward.out_bound = 10.0
+    rpu.forward.out_noise = out_noise
     rpu.pre_post.input_range.enable = True
-    rpu.pre_post.input_range.dynamic = True
+    rpu.pre_post.input_range.dynamic = dynamic
     rpu.modifier.noise_type = ns.WeightNoiseInjectionType.ADD_NORMAL_PER_CHANNEL
     rpu.modifier.std_dev = 0.02
     return rpu
@@ -114,6 +128,9 @@ class ClockSampler:
                     samples=len(sm), reasons=sorted(reasons))
 
 
+# ---------------------------------------------------------------------------------------------
+# reference arm / baselines (the only places that execute oracle/)
+# ---------------------------------------------------------------------------------------------
 def cpu_reference_run(steps: int, warmup: int, rows: int):
     """Time the CPU restatement of the reference's torch path (autograd flavour) on ``rows``
     rows of the workload with all host threads."""
@@ -155,6 +172,41 @@ def cpu_reference_run(steps: int, warmup: int, rows: int):
                        f"{sec * 1e3:.0f} ms/step", ms_per_step=sec * 1e3)
 
 
+def gpu_torch_baseline(dev, steps=5, warmup=2):
+    """The reference's torch path (its op sequence under autograd, restated in
+    ``oracle/analog_oracle.py::linear_autograd``) on CUDA tensors of the full headline workload:
+    per-tile cuBLAS GEMMs and eager element-wise kernels on the same GPU."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import analog_oracle as O
+    from aihwkit_lightning_b200.simulator import configs as cfg
+
+    rpu = make_rpu_config(cfg)
+    gen = torch.Generator().manual_seed(0)
+    x = torch.randn(M, K, generator=gen).bfloat16().to(dev).requires_grad_(True)
+    torch.manual_seed(0)
+    w = torch.nn.Linear(K, N, bias=False).weight.detach().bfloat16().to(dev).requires_grad_(True)
+    g = torch.randn(M, N, generator=gen).bfloat16().to(dev)
+    in_sizes = O.split_sizes(K, MAX_IN)
+    stream = torch.cuda.current_stream(dev)
+    events = []
+    for it in range(warmup + steps):
+        x.grad = None
+        w.grad = None
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(stream)
+        O.linear_autograd(x, w, None, None, None, in_sizes, True, rpu).backward(g)
+        e.record(stream)
+        if it >= warmup:
+            events.append((s, e))
+    torch.cuda.synchronize(dev)
+    ms = sum(s.elapsed_time(e) for s, e in events) / len(events)
+    del x, w, g
+    torch.cuda.empty_cache()
+    return dict(ms_per_step=ms, value=FLOP_PER_STEP / (ms * 1e-3) / 1e12, unit="TFLOP/s",
+                what="reference torch op sequence (oracle restatement) on CUDA tensors, bf16, same workload, "
+                     f"{len(events)} timed steps")
+
+
 def base_record(args, n_gpus):
     return {
         "metric": "analog-layer fwd+bwd TFLOP/s",
@@ -172,6 +224,8 @@ def base_record(args, n_gpus):
                         "dynamic input range, 8-bit DAC, 8-bit ADC out_bound=10, out_noise=0.04, "
                         "weight noise 0.02 per-channel, training fwd+bwd",
             "l2": "inputs larger than L2 (x 67 MB + w 34 MB + g 67 MB per step) and a 256 MB flush write between steps",
+            "e2e": "bound by the host link: every step uploads its 67 MB batch from pinned host memory "
+                   "(double-buffered) and reads its loss back",
             "parallelism": f"dp{n_gpus}",
         },
     }
@@ -193,38 +247,242 @@ def run_reference(args, rank, world):
     print(json.dumps(rec), flush=True)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
-    ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+# ---------------------------------------------------------------------------------------------
+# shared helpers of the GPU arms
+# ---------------------------------------------------------------------------------------------
+class Ctx:
+    """Rank, device and process group of one bench process."""
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    def __init__(self):
+        import torch.distributed as dist
 
-    if args.impl == "reference":
-        run_reference(args, rank, world)
-        return
+        self.dist = dist
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.stream = torch.cuda.current_stream(self.dev)
 
-    import torch.distributed as dist
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier(device_ids=[self.local_rank])
+        torch.cuda.synchronize(self.dev)
+
+    def max_over_ranks(self, value: float) -> float:
+        t = torch.tensor([value], device=self.dev, dtype=torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+def timed_steps(ctx, fn, steps, between=None):
+    """CUDA-event time (ms) of exactly `steps` calls of fn on the current stream; what `between`
+    does before each call (the L2 flush) is not timed."""
+    events = []
+    for _ in range(steps):
+        if between is not None:
+            between()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(ctx.stream)
+        fn()
+        e.record(ctx.stream)
+        events.append((s, e))
+    torch.cuda.synchronize(ctx.dev)
+    return sum(s.elapsed_time(e) for s, e in events)
+
+
+def kernel_table(prof):
+    out = {}
+    for name, (launches, timed_scopes, total) in prof.items():
+        if launches:
+            out[name] = dict(launches=launches, ms_total=round(total, 4), ms_avg=round(total / max(timed_scopes, 1), 5))
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# config 3: Phi-3-mini-shaped decoder, one data-parallel training step
+# ---------------------------------------------------------------------------------------------
+def build_decoder(dev, layers=32, d=3072, heads=32, mlp=8192, vocab=32064):
+    from torch import nn
+    from torch.nn import functional as TF
+
+    class RMSNorm(nn.Module):
+        def __init__(self, dim, eps=1e-5):
+            super().__init__()
+            self.weight = nn.Parameter(torch.ones(dim))
+            self.eps = eps
+
+        def forward(self, x):
+            return TF.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.norm1, self.norm2 = RMSNorm(d), RMSNorm(d)
+            self.qkv_proj = nn.Linear(d, 3 * d, bias=False)
+            self.o_proj = nn.Linear(d, d, bias=False)
+            self.gate_up_proj = nn.Linear(d, 2 * mlp, bias=False)
+            self.down_proj = nn.Linear(mlp, d, bias=False)
+
+        def forward(self, x, cos, sin):
+            b, s, _ = x.shape
+            hd = d // heads
+            q, k, v = self.qkv_proj(self.norm1(x)).view(b, s, 3, heads, hd).permute(2, 0, 3, 1, 4)
+
+            def rope(t):
+                t1, t2 = t[..., : hd // 2], t[..., hd // 2:]
+                return t * cos + torch.cat([-t2, t1], -1) * sin
+
+            att = TF.scaled_dot_product_attention(rope(q), rope(k), v, is_causal=True)
+            x = x + self.o_proj(att.transpose(1, 2).reshape(b, s, d))
+            gate, up = self.gate_up_proj(self.norm2(x)).chunk(2, dim=-1)
+            return x + self.down_proj(TF.silu(gate) * up)
+
+    class Decoder(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embed = nn.Embedding(vocab, d)
+            self.layers = nn.ModuleList([Layer() for _ in range(layers)])
+            self.norm = RMSNorm(d)
+            self.lm_head = nn.Linear(d, vocab, bias=False)
+            self.hd = d // heads
+
+        def forward(self, ids):
+            s = ids.shape[1]
+            pos = torch.arange(s, device=ids.device, dtype=torch.float32)
+            inv = 1.0 / (10000 ** (torch.arange(0, self.hd, 2, device=ids.device, dtype=torch.float32) / self.hd))
+            ang = pos[:, None] * inv[None, :]
+            cos = torch.cat([ang.cos(), ang.cos()], -1).to(self.embed.weight.dtype)
+            sin = torch.cat([ang.sin(), ang.sin()], -1).to(self.embed.weight.dtype)
+            x = self.embed(ids)
+            for layer in self.layers:
+                x = layer(x, cos, sin)
+            return self.lm_head(self.norm(x))
+
+    with torch.device(dev):
+        model = Decoder().to(torch.bfloat16)
+    return model
+
+
+def run_c3(args, ctx, layers=32, steps=3, warmup=2, seq=2048, micro_batch=4):
+    """One full data-parallel training step of the decoder: forward, loss, backward with the
+    gradient exchange started from inside it, AdamW step.  Returns the fields of the ``c3`` block."""
+    from torch.nn import functional as TF
 
     from aihwkit_lightning_b200 import _lib
-    from aihwkit_lightning_b200.distributed import EagerGradientSync, GradientBuckets, rank_seed
+    from aihwkit_lightning_b200.distributed import EagerGradientSync, rank_seed
+    from aihwkit_lightning_b200.nn import AnalogLinear, convert_to_analog
+    from aihwkit_lightning_b200.nn import functional as F
+    from aihwkit_lightning_b200.optim import AnalogOptimizer
+    from aihwkit_lightning_b200.simulator import configs as cfg
+
+    dev, rank, world = ctx.dev, ctx.rank, ctx.world
+    lib = _lib.load()
+    vocab = 32064
+    torch.manual_seed(0)  # identical replicas
+    model = build_decoder(dev, layers=layers, vocab=vocab)
+    rpu = make_rpu_config(cfg, adc=False)  # 8-bit DAC, out_noise 0.04, weight noise 0.02, no ADC
+    model = convert_to_analog(model, rpu).train()
+    analog = [m for m in model.modules() if isinstance(m, AnalogLinear)]
+    tokens = seq * micro_batch
+    flop = sum(6.0 * tokens * m.in_features * m.out_features for m in analog)
+    torch.cuda.manual_seed(rank_seed(0, rank))  # independent analog noise per replica
+    opt = AnalogOptimizer(torch.optim.AdamW, model.analog_layers, model.parameters(), lr=1e-5, fused=True)
+    sync = None
+    if world > 1:
+        sync = EagerGradientSync().attach(model.parameters())
+        F.settings.after_wgrad = sync
+    gen = torch.Generator().manual_seed(1000 + rank)
+    ids_host = torch.randint(0, vocab, (micro_batch, seq), generator=gen).pin_memory()
+    labels_host = torch.randint(0, vocab, (micro_batch, seq), generator=gen).pin_memory()
+    exposed = []
+    losses = []
+
+    def step():
+        ids = ids_host.to(dev, non_blocking=True)
+        labels = labels_host.to(dev, non_blocking=True)
+        opt.zero_grad(set_to_none=True)
+        logits = model(ids)
+        loss = TF.cross_entropy(logits.float().view(-1, vocab), labels.view(-1))
+        loss.backward()
+        if sync is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(ctx.stream)
+            sync.finish()  # the compute stream waits here for what is left of the exchange
+            e1.record(ctx.stream)
+            exposed.append((e0, e1))
+        opt.step()
+        losses.append(loss.detach())
+
+    for _ in range(warmup):
+        step()
+    ctx.barrier()
+    exposed.clear()
+    losses.clear()
+    _lib.profile_read(reset=True)
+    lib.al_profile_enable(1)
+    ms_total = timed_steps(ctx, step, steps)
+    ctx.barrier()
+    lib.al_profile_enable(0)
+    prof = _lib.profile_read(reset=True)
+    ms_step = ctx.max_over_ranks(ms_total) / steps
+    exposed_ms = sum(a.elapsed_time(b) for a, b in exposed) / max(len(exposed), 1) if exposed else 0.0
+    exposed_ms = ctx.max_over_ranks(exposed_ms)
+    # replicas must hold the same parameters after the steps: compare a checksum over all ranks
+    checksum = torch.stack([p.detach().double().sum() for p in list(model.parameters())[:16]]).sum().reshape(1)
+    lo, hi = checksum.clone(), checksum.clone()
+    if world > 1:
+        ctx.dist.all_reduce(lo, op=ctx.dist.ReduceOp.MIN)
+        ctx.dist.all_reduce(hi, op=ctx.dist.ReduceOp.MAX)
+    grad_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
+    analog_ms = sum(v[2] for v in prof.values()) / steps
+    out = {
+        "workload": f"Phi-3-mini-shaped decoder, {layers} layers, d=3072, 32 heads, MLP 8192, vocab {vocab}, "
+                    f"{len(analog)} analog linears (max_input_size=512, dynamic input range, 8-bit DAC, out_noise 0.04, "
+                    f"weight noise 0.02), seq {seq} x micro-batch {micro_batch} per GPU, bf16, AdamW, random init, "
+                    "uniform synthetic token ids",
+        "n_gpus": world,
+        "steps": steps,
+        "warmup": warmup,
+        "ms_per_step": ms_step,
+        "tokens_per_s": tokens * world / (ms_step * 1e-3),
+        "analog_tflops": flop * world / (ms_step * 1e-3) / 1e12,
+        "analog_flop_per_gpu_step": flop,
+        "analog_kernel_ms_per_step": analog_ms,
+        "exposed_exchange_ms": exposed_ms,
+        "exchange": None if world == 1 else
+        f"NCCL all-reduce of {grad_bytes / 1e9:.2f} GB of gradients per step, one call per weight matrix issued "
+        "from inside backward on a side stream, small gradients in one flat call at the end",
+        "loss": float(losses[-1].item()),
+        "replicas_identical": bool((lo == hi).all().item()),
+        "gpu_launches": sum(v[0] for v in prof.values()),
+        "kernels": kernel_table(prof),
+    }
+    F.settings.after_wgrad = None
+    del model, opt, analog
+    torch.cuda.empty_cache()
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# config 2 (headline): one analog layer, forward + backward
+# ---------------------------------------------------------------------------------------------
+def run_c2(args, ctx):
+    from aihwkit_lightning_b200 import _lib
+    from aihwkit_lightning_b200.distributed import EagerGradientSync, rank_seed
     from aihwkit_lightning_b200.nn import AnalogLinear
     from aihwkit_lightning_b200.nn import functional as F
     from aihwkit_lightning_b200.simulator import configs as cfg
 
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    dev, rank, world, stream = ctx.dev, ctx.rank, ctx.world, ctx.stream
     lib = _lib.load()
     F.settings.engine = args.engine
 
@@ -237,23 +495,17 @@ def main():
     layer.train()
     torch.cuda.manual_seed(rank_seed(0, rank))  # independent analog noise per replica
     # The only exchange step of data-parallel training: the weight gradient is summed over ranks.
-    # "eager" (default): the all-reduce of the weight gradient is issued from a hook inside backward and
-    # is complete when the step ends, as an optimizer step would need it.
-    # "deferred" (BENCH_GRAD_SYNC=deferred): the all-reduce of step i runs beside step i+1 (a step then
-    # ends with a gradient that is one step old; measured 4 % faster on 2 GPUs, not the default).
-    eager = os.environ.get("BENCH_GRAD_SYNC", "eager") != "deferred"
-    buckets = GradientBuckets(layer.parameters()) if world > 1 and not eager else None
-    sync = EagerGradientSync().attach(layer.parameters()) if world > 1 and eager else None
-    if sync is not None:
-        from aihwkit_lightning_b200.nn import functional as analog_functional
-        analog_functional.settings.after_wgrad = sync
-        # SMs the input-gradient GEMM leaves to the all-reduce kernel beside it.  Measured on 2 GPUs:
-        # with 20 SMs free (64 CTA pairs = 8 full rounds of the 512 output blocks) the GEMM takes 39 us
-        # longer and the exposed all-reduce 45 us less -- no net gain, so the default is 0.
-        analog_functional.settings.comm_sms = int(os.environ.get("BENCH_COMM_SMS", "0"))
+    # Its all-reduce is issued from a hook inside backward, right after the weight-gradient kernel
+    # and before the input-gradient kernel, and is complete when the step ends, as an optimizer
+    # step would need it.
+    sync = None
+    if world > 1:
+        sync = EagerGradientSync().attach(layer.parameters())
+        F.settings.after_wgrad = sync
+        # SMs the input-gradient GEMM leaves to the all-reduce kernel that runs beside it
+        F.settings.comm_sms = int(os.environ.get("BENCH_COMM_SMS", "0"))
     x_dev = x_host.to(dev).requires_grad_(True)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
-    stream = torch.cuda.current_stream(dev)
 
     def step_resident():
         layer.weight.grad = None
@@ -262,13 +514,6 @@ def main():
         out.backward(g)
         if sync is not None:
             sync.finish()
-        if buckets is not None:
-            buckets.finish()  # previous step's all-reduce (overlapped with this step's kernels)
-            buckets.reduce_all_async()
-
-    def drain():
-        if buckets is not None:
-            buckets.finish()
 
     # end to end: the batch lives in pinned host memory; the upload of batch i+1 is enqueued on
     # a copy stream before step i runs (double buffering), every step reads its loss back.
@@ -301,9 +546,6 @@ def main():
         consumed[slot].record(stream)
         if sync is not None:
             sync.finish()
-        if buckets is not None:
-            buckets.reduce_all_async()
-            buckets.finish()
         # device -> host read of this step's loss: copied to pinned memory on the compute stream
         # and picked up by the host one step later, so the host can already enqueue the next step
         loss_host[slot].copy_(loss.detach().reshape(1), non_blocking=True)
@@ -313,49 +555,21 @@ def main():
             state["losses"].append(float(loss_host[slot ^ 1][0]))
         state["i"] = i + 1
 
-    def timed(fn, steps, between=None):
-        """CUDA-event time of exactly `steps` calls; the L2 flush between steps is excluded."""
-        total = 0.0
-        events = []
-        for _ in range(steps):
-            if between is not None:
-                between()
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record(stream)
-            fn()
-            e.record(stream)
-            events.append((s, e))
-        drain()
-        torch.cuda.synchronize(dev)
-        for s, e in events:
-            total += s.elapsed_time(e)
-        return total
-
-    def barrier():
-        if world > 1:
-            dist.barrier(device_ids=[local_rank])
-        torch.cuda.synchronize(dev)
-
     # ---- device-resident timing ----------------------------------------------------------
     for _ in range(args.warmup):
         step_resident()
-    drain()
-    barrier()
+    ctx.barrier()
     _lib.profile_read(reset=True)
     lib.al_profile_enable(1)
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(ctx.local_rank)
     if rank == 0:
         sampler.start()
-    ms_total = timed(step_resident, args.steps, between=lambda: flush.fill_(1))
-    barrier()
+    ms_total = timed_steps(ctx, step_resident, args.steps, between=lambda: flush.fill_(1))
+    ctx.barrier()
     lib.al_profile_enable(0)
     prof = _lib.profile_read(reset=True)
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total = float(t.item())
-    ms_per_step = ms_total / args.steps
+    ms_per_step = ctx.max_over_ranks(ms_total) / args.steps
     value = FLOP_PER_STEP * world / (ms_per_step * 1e-3) / 1e12
 
     # ---- end to end through the public API, batch in pinned host memory -------------------
@@ -363,61 +577,330 @@ def main():
         consumed[slot].record(stream)
     for _ in range(3):
         step_e2e()
-    barrier()
-    e2e_ms = timed(step_e2e, args.steps)
-    barrier()
-    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms_per_step = float(t.item()) / args.steps
+    ctx.barrier()
+    e2e_ms = timed_steps(ctx, step_e2e, args.steps)
+    ctx.barrier()
+    e2e_ms_per_step = ctx.max_over_ranks(e2e_ms) / args.steps
     e2e_value = FLOP_PER_STEP * world / (e2e_ms_per_step * 1e-3) / 1e12
 
-    if rank == 0:
-        peaks = load_peaks()
-        gemm_flop = {"fwd_gemm": 2.0 * M * K * N, "dgrad_gemm": 2.0 * M * K * N, "wgrad_gemm": 2.0 * M * K * N}
-        kernels = {}
-        for name, (launches, timed_scopes, total) in prof.items():
-            if launches:
-                kernels[name] = dict(launches=launches, ms_total=round(total, 4),
-                                     ms_avg=round(total / max(timed_scopes, 1), 5))
-        dominant = max(gemm_flop, key=lambda k: prof[k][2])
-        d_launches, d_timed, d_ms = prof[dominant]
-        achieved = gemm_flop[dominant] / (d_ms / max(d_timed, 1) * 1e-3) / 1e12 if d_ms > 0 else 0.0
-        rec = base_record(args, world)
-        if world > 1:
-            rec["config"]["grad_sync"] = (
-                "NCCL all-reduce of the weight gradient, started inside backward after the weight-gradient kernels, "
-                "complete at step end" if eager else
-                "NCCL all-reduce of the weight gradient of step i overlapped with step i+1")
-        rec.update({
-            "value": value,
-            "ms_per_step": ms_per_step,
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms_per_step,
-                    "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
-                    "d2h_bytes_per_step": 4},
-            "gpu_launches": sum(v[0] for v in prof.values()),
-            "pct_of_bf16_peak": {"burst": 100 * value / world / peaks["bf16"],
-                                 "sustained": 100 * value / world / peaks["bf16_sustained"]},
-            "roofline": {"kernel": dominant, "bound": "tensor", "achieved": achieved,
-                         "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["bf16_sustained"],
-                         "peak_source": f"{peaks['source']} (sustained; burst {peaks['bf16']})",
-                         # DRAM bytes (read + write) of one fwd_tc_kernel launch on this workload,
-                         # from the ncu capture summarised in profiles/fwd_tc_kernel_c2.md
-                         "traffic": FWD_KERNEL_DRAM_BYTES if dominant == "fwd_gemm" else None},
-            "kernels": kernels,
-            "engine": {"requested": args.engine,
-                       "tcgen05": bool(lib.al_uses_tcgen05(
-                           F.make_desc(layer.rpu_config, M, K, N, len(layer.in_sizes), torch.bfloat16, True),
-                           _lib.tile_ends_array(layer.in_sizes)))},
-            "clocks": clocks,
-        })
-        if not args.no_cpu_baseline and world == 1:
-            res = cpu_reference_run(steps=3, warmup=1, rows=CPU_SAMPLE_ROWS)
-            rec["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(rec), flush=True)
+    uses_tc = bool(lib.al_uses_tcgen05(
+        F.make_desc(layer.rpu_config, M, K, N, len(layer.in_sizes), torch.bfloat16, True),
+        _lib.tile_ends_array(layer.in_sizes)))
+    F.settings.after_wgrad = None
+    h2d_bytes = x_host.numel() * x_host.element_size()
+    del layer, slots, x_dev, flush, x_host
+    torch.cuda.empty_cache()
+
+    peaks = load_peaks()
+    gemm_flop = {"fwd_gemm": 2.0 * M * K * N, "dgrad_gemm": 2.0 * M * K * N, "wgrad_gemm": 2.0 * M * K * N}
+    dominant = max(gemm_flop, key=lambda k: prof[k][2])
+    _, d_timed, d_ms = prof[dominant]
+    achieved = gemm_flop[dominant] / (d_ms / max(d_timed, 1) * 1e-3) / 1e12 if d_ms > 0 else 0.0
+    rec = base_record(args, world)
     if world > 1:
-        dist.destroy_process_group()
+        rec["config"]["grad_sync"] = ("NCCL all-reduce of the weight gradient, started inside backward after the "
+                                      "weight-gradient kernel, complete at step end")
+    rec.update({
+        "value": value,
+        "ms_per_step": ms_per_step,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms_per_step,
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4},
+        "gpu_launches": sum(v[0] for v in prof.values()),
+        "pct_of_bf16_peak": {"burst": 100 * value / world / peaks["bf16"],
+                             "sustained": 100 * value / world / peaks["bf16_sustained"]},
+        "roofline": {"kernel": dominant, "bound": "tensor", "achieved": achieved,
+                     "peak": peaks["bf16"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["bf16"],
+                     "frac_sustained": achieved / peaks["bf16_sustained"],
+                     "peak_source": f"{peaks['source']} (burst; sustained {peaks['bf16_sustained']})",
+                     "traffic": FWD_KERNEL_DRAM_BYTES if dominant == "fwd_gemm" else None},
+        "kernels": kernel_table(prof),
+        "engine": {"requested": args.engine, "tcgen05": uses_tc},
+        "clocks": clocks,
+    })
+    return rec
+
+
+# ---------------------------------------------------------------------------------------------
+# the other configurations (lines of their own; kept under profiles/)
+# ---------------------------------------------------------------------------------------------
+def run_c1(args, ctx):
+    """Config 1: AnalogLinear 1024 -> 1024 fp32, 512 rows, 2 tiles, learned static input range 3.0,
+    inp_res 254, out_noise 0.04, weight noise 0.02 (per channel), no ADC; forward + backward."""
+    from aihwkit_lightning_b200 import _lib
+    from aihwkit_lightning_b200.nn import AnalogLinear
+    from aihwkit_lightning_b200.simulator import configs as cfg
+
+    dev = ctx.dev
+    lib = _lib.load()
+    m, k, n = 512, 1024, 1024
+    rpu = make_rpu_config(cfg, max_in=512, adc=False, dynamic=False)
+    rpu.pre_post.input_range.learn_input_range = True
+    rpu.pre_post.input_range.init_value = 3.0
+    rpu.pre_post.input_range.init_from_data = 0
+    torch.manual_seed(0)
+    layer = AnalogLinear(k, n, bias=True, rpu_config=rpu).to(dev).train()
+    with torch.no_grad():
+        layer.weight.uniform_(-1 / 32, 1 / 32)
+    x = torch.randn(m, k, device=dev, requires_grad=True)
+    g = torch.randn(m, n, device=dev)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+
+    def step():
+        layer.zero_grad(set_to_none=True)
+        x.grad = None
+        layer(x).backward(g)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ctx.barrier()
+    _lib.profile_read(reset=True)
+    lib.al_profile_enable(1)
+    sampler = ClockSampler(ctx.local_rank)
+    sampler.start()
+    ms = timed_steps(ctx, step, args.steps, between=lambda: flush.fill_(1)) / args.steps
+    lib.al_profile_enable(0)
+    prof = _lib.profile_read(reset=True)
+    clocks = sampler.stop()
+    flop = 6.0 * m * k * n
+    peaks = load_peaks()
+    gemm_ms = sum(prof[c][2] for c in ("fwd_gemm", "dgrad_gemm", "wgrad_gemm")) / args.steps
+    rec = base_record(args, 1)
+    rec.update({
+        "dtype": "f32",
+        "config": {"workload": "config 1: AnalogLinear 1024->1024 fp32, 512 rows ~N(0,1), weights ~U(-1/32,1/32), "
+                               "max_input_size=512 (2 tiles), inp_res=254, learned static input range 3.0, out_noise 0.04, "
+                               "weight noise 0.02 per-channel, no ADC, training fwd+bwd",
+                   "l2": "256 MB flush write between steps", "parallelism": "dp1"},
+        "value": flop / (ms * 1e-3) / 1e12, "ms_per_step": ms,
+        "gpu_launches": sum(v[0] for v in prof.values()),
+        "roofline": {"kernel": "fwd+dgrad+wgrad GEMMs", "bound": "tensor", "achieved": flop / (gemm_ms * 1e-3) / 1e12,
+                     "peak": peaks["bf16"], "unit": "TFLOP/s", "frac": flop / (gemm_ms * 1e-3) / 1e12 / peaks["bf16"],
+                     "note": "3.2 GFLOP per step: the step is bound by launch latency, not by a pipe", "traffic": None},
+        "kernels": kernel_table(prof), "clocks": clocks,
+    })
+    return rec
+
+
+def run_c4(args, ctx):
+    """Config 4: ResNet-32 (CIFAR shape) with AnalogConv2d / AnalogLinear, batch 256 per GPU, fp32,
+    max_input_size=256, 8-bit DAC, out_noise 0.02; one SGD training step."""
+    from torch import nn
+    from torch.nn import functional as TF
+
+    from aihwkit_lightning_b200 import _lib
+    from aihwkit_lightning_b200.nn import AnalogConv2d, AnalogLinear, convert_to_analog
+    from aihwkit_lightning_b200.optim import AnalogOptimizer
+    from aihwkit_lightning_b200.simulator import configs as cfg
+
+    dev = ctx.dev
+    lib = _lib.load()
+
+    class Block(nn.Module):
+        def __init__(self, cin, cout, stride):
+            super().__init__()
+            self.conv1 = nn.Conv2d(cin, cout, 3, stride=stride, padding=1, bias=False)
+            self.bn1 = nn.BatchNorm2d(cout)
+            self.conv2 = nn.Conv2d(cout, cout, 3, padding=1, bias=False)
+            self.bn2 = nn.BatchNorm2d(cout)
+            self.short = nn.Conv2d(cin, cout, 1, stride=stride, bias=False) if (stride != 1 or cin != cout) else None
+
+        def forward(self, x):
+            y = TF.relu(self.bn1(self.conv1(x)))
+            y = self.bn2(self.conv2(y))
+            return TF.relu(y + (x if self.short is None else self.short(x)))
+
+    class ResNet32(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.conv = nn.Conv2d(3, 16, 3, padding=1, bias=False)
+            self.bn = nn.BatchNorm2d(16)
+            blocks, cin = [], 16
+            for cout, stride in ((16, 1), (32, 2), (64, 2)):
+                for i in range(5):
+                    blocks.append(Block(cin, cout, stride if i == 0 else 1))
+                    cin = cout
+            self.blocks = nn.Sequential(*blocks)
+            self.fc = nn.Linear(64, 10)
+
+        def forward(self, x):
+            return self.fc(self.blocks(TF.relu(self.bn(self.conv(x)))).mean((2, 3)))
+
+    batch = 256
+    rpu = make_rpu_config(cfg, max_in=256, adc=False, out_noise=0.02)
+    torch.manual_seed(0)
+    model = convert_to_analog(ResNet32(), rpu).to(dev).train()
+    layers = [m for m in model.modules() if isinstance(m, (AnalogConv2d, AnalogLinear))]
+    opt = AnalogOptimizer(torch.optim.SGD, model.analog_layers, model.parameters(), lr=0.05, momentum=0.9)
+    gen = torch.Generator().manual_seed(ctx.rank)
+    x_host = torch.randn(batch, 3, 32, 32, generator=gen).pin_memory()
+    y_host = torch.randint(0, 10, (batch,), generator=gen).pin_memory()
+    # algorithmic bytes of the analog layers: input activation, output activation and weights of every
+    # layer, each once per pass (forward, input gradient, weight gradient); shapes from a forward hook
+    act_bytes = [0.0]
+
+    def count(mod, inp, out):
+        act_bytes[0] += 4.0 * (inp[0].numel() + out.numel() + mod.weight.numel())
+
+    hooks = [m.register_forward_hook(count) for m in layers]
+    with torch.no_grad():
+        model(x_host.to(dev))
+    for h in hooks:
+        h.remove()
+    alg_bytes = 3.0 * act_bytes[0]
+
+    def step():
+        x = x_host.to(dev, non_blocking=True)
+        y = y_host.to(dev, non_blocking=True)
+        opt.zero_grad(set_to_none=True)
+        loss = TF.cross_entropy(model(x), y)
+        loss.backward()
+        opt.step()
+        return loss
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ctx.barrier()
+    _lib.profile_read(reset=True)
+    lib.al_profile_enable(1)
+    sampler = ClockSampler(ctx.local_rank)
+    sampler.start()
+    t0 = time.perf_counter()
+    ms = timed_steps(ctx, step, args.steps) / args.steps
+    wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    lib.al_profile_enable(0)
+    prof = _lib.profile_read(reset=True)
+    clocks = sampler.stop()
+    lib_ms = sum(v[2] for v in prof.values()) / args.steps
+    peaks = load_peaks()
+    rec = base_record(args, 1)
+    rec.update({
+        "metric": "ResNet-32 training images/s", "unit": "images/s", "dtype": "f32",
+        "config": {"workload": f"config 4: ResNet-32 (CIFAR shape), AnalogConv2d/AnalogLinear ({len(layers)} analog layers), "
+                               "batch 256 of 32x32x3 ~N(0,1), uniform labels, max_input_size=256, 8-bit DAC, out_noise 0.02, "
+                               "weight noise 0.02, fp32, SGD step", "parallelism": "dp1"},
+        "value": batch / (ms * 1e-3), "ms_per_step": ms, "host_ms_per_step": wall_ms,
+        "library_kernel_ms_per_step": lib_ms,
+        "gpu_launches": sum(v[0] for v in prof.values()),
+        "e2e": {"value": batch / (ms * 1e-3), "unit": "images/s",
+                "h2d_bytes_per_step": x_host.numel() * 4 + y_host.numel() * 8, "d2h_bytes_per_step": 0},
+        "roofline": {"kernel": "all library kernels of a step", "bound": "hbm",
+                     "achieved": alg_bytes / (lib_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": alg_bytes / (lib_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
+                     "note": "algorithmic bytes = activations in + out + weights of every analog layer, three passes"},
+        "kernels": kernel_table(prof), "clocks": clocks,
+    })
+    return rec
+
+
+def run_c5(args, ctx):
+    """Config 5: inference sweep, noise off: M in {1,16,256,4096,16384} x K=N in {2048,4096,8192,16384},
+    max_input_size in {256,512,1024}, 8-bit DAC/ADC, bf16, forward only."""
+    from aihwkit_lightning_b200 import _lib
+    from aihwkit_lightning_b200.nn import AnalogLinear
+    from aihwkit_lightning_b200.simulator import configs as cfg
+
+    dev = ctx.dev
+    peaks = load_peaks()
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    points = []
+    total_flop = total_ms = 0.0
+    _lib.profile_read(reset=True)
+    for kn in (2048, 4096, 8192, 16384):
+        for max_in in (256, 512, 1024):
+            rpu = make_rpu_config(cfg, max_in=max_in, out_noise=0.0)
+            rpu.modifier.noise_type = cfg.WeightNoiseInjectionType.NONE
+            torch.manual_seed(0)
+            layer = AnalogLinear(kn, kn, bias=False, rpu_config=rpu).to(device=dev, dtype=torch.bfloat16).eval()
+            with torch.no_grad():
+                layer.weight.normal_(0, 0.02)
+            for m in (1, 16, 256, 4096, 16384):
+                x = torch.randn(m, kn, device=dev).bfloat16()
+                reps = 3 if m * kn * kn > 1e12 else 10
+                with torch.no_grad():
+                    for _ in range(3):
+                        layer(x)
+                    ms = timed_steps(ctx, lambda: layer(x), reps, between=lambda: flush.fill_(1)) / reps  # noqa: B023
+                flop = 2.0 * m * kn * kn
+                nbytes = 2.0 * (kn * kn + m * kn + m * kn)
+                tensor_bound = m >= 256
+                ach = flop / (ms * 1e-3) / 1e12 if tensor_bound else nbytes / (ms * 1e-3) / 1e9
+                peak = peaks["bf16"] if tensor_bound else peaks["hbm_gbs"]
+                points.append(dict(M=m, K=kn, N=kn, max_input_size=max_in, ms=round(ms, 5),
+                                   tflops=round(flop / (ms * 1e-3) / 1e12, 3), bound="tensor" if tensor_bound else "hbm",
+                                   achieved=round(ach, 2), frac=round(ach / peak, 4)))
+                total_flop += flop
+                total_ms += ms
+                del x
+            del layer
+            torch.cuda.empty_cache()
+    prof = _lib.profile_read(reset=True)
+    rec = base_record(args, 1)
+    best = max((p for p in points if p["bound"] == "tensor"), key=lambda p: p["frac"])
+    rec.update({
+        "metric": "analog-layer forward TFLOP/s (inference sweep)",
+        "config": {"workload": "config 5: eval forward, noise off, M in {1,16,256,4096,16384} x K=N in {2048,4096,8192,16384} x "
+                               "max_input_size in {256,512,1024}, 8-bit DAC + ADC out_bound=10, dynamic input range, bf16, "
+                               "weights ~N(0,0.02); value = total FLOP / total time over the 60 points",
+                   "l2": "256 MB flush write between calls", "parallelism": "dp1"},
+        "value": total_flop / (total_ms * 1e-3) / 1e12, "ms_per_step": total_ms,
+        "gpu_launches": sum(v[0] for v in prof.values()),
+        "roofline": {"kernel": f"best tensor-bound point M={best['M']} K=N={best['K']} max_input_size={best['max_input_size']}",
+                     "bound": "tensor", "achieved": best["achieved"], "peak": peaks["bf16"], "unit": "TFLOP/s",
+                     "frac": best["frac"], "traffic": None},
+        "points": points,
+    })
+    return rec
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05"])
+    ap.add_argument("--config", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gpu-baseline", action="store_true")
+    ap.add_argument("--no-c3", action="store_true", help="headline line only, without the decoder step")
+    ap.add_argument("--c3-layers", type=int, default=32)
+    ap.add_argument("--c3-steps", type=int, default=3)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    if args.impl == "reference":
+        run_reference(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")))
+        return
+
+    ctx = Ctx()
+    try:
+        if args.config == "c2":
+            rec = run_c2(args, ctx)
+            if not args.no_c3:
+                rec["c3"] = run_c3(args, ctx, layers=args.c3_layers, steps=args.c3_steps)
+            if ctx.rank == 0 and ctx.world == 1:
+                if not args.no_gpu_baseline:
+                    base = gpu_torch_baseline(ctx.dev)
+                    base["ratio_to_value"] = rec["value"] / base["value"]
+                    rec["gpu_torch_baseline"] = base
+                if not args.no_cpu_baseline:
+                    res = cpu_reference_run(steps=3, warmup=1, rows=CPU_SAMPLE_ROWS)
+                    rec["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        elif args.config == "c3":
+            c3 = run_c3(args, ctx, layers=args.c3_layers, steps=args.c3_steps)
+            rec = base_record(args, ctx.world)
+            rec.update({"metric": "decoder training tokens/s", "unit": "tokens/s", "value": c3["tokens_per_s"],
+                        "ms_per_step": c3["ms_per_step"], "steps": c3["steps"], "warmup": c3["warmup"],
+                        "gpu_launches": c3["gpu_launches"],
+                        "config": {"workload": c3["workload"], "parallelism": f"dp{ctx.world}"}, "c3": c3})
+        else:
+            assert ctx.world == 1, "configs 1, 4 and 5 are single-GPU lines"
+            rec = {"c1": run_c1, "c4": run_c4, "c5": run_c5}[args.config](args, ctx)
+        if ctx.rank == 0:
+            print(json.dumps(rec), flush=True)
+    finally:
+        ctx.close()
 
 
 if __name__ == "__main__":
