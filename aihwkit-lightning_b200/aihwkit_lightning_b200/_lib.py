@@ -42,7 +42,7 @@ class AlForwardArgs(Structure):
         ("tile_ends", POINTER(c_int32)),
         ("out", c_void_p), ("xq", c_void_p), ("ir_rows", c_void_p), ("w_amax", c_void_p),
         ("w_tile_max", c_void_p), ("w_mod", c_void_p), ("keep_mask", c_void_p),
-        ("std_scratch", c_void_p), ("smallm_scratch", c_void_p), ("w_noise", c_void_p), ("out_noise", c_void_p),
+        ("std_scratch", c_void_p), ("std_override", c_void_p), ("smallm_scratch", c_void_p), ("w_noise", c_void_p), ("out_noise", c_void_p),
         ("codes", c_void_p), ("seed", c_uint64), ("offset", c_uint64),
     ]
 

@@ -33,6 +33,20 @@ def rank_seed(seed: int, rank: int) -> int:
     return (seed * 1_000_003 + 7919 * (rank + 1)) & 0x7FFFFFFFFFFFFFFF
 
 
+def mean_over_replicas(values: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """Mean of a small statistics tensor over all replicas (in place, returned for chaining).
+
+    Installed as ``nn.functional.settings.sync_tile_std`` it makes the init-from-data phase of a
+    learned input range use the per-tile standard deviation averaged over the replicas, so that
+    every replica applies the same update.  The reference updates from the local batch
+    (`nn/modules/torch_utils/torch_linear.py:338-352`) and its DeepSpeed example patches around the
+    resulting divergence (`examples/deepspeed_and_huggingface/README.md:60-106`)."""
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(values, op=dist.ReduceOp.SUM, group=group)
+        values.div_(dist.get_world_size(group))
+    return values
+
+
 class GradientBuckets:
     """Flat-bucket gradient all-reduce for a fixed list of parameters.
 

@@ -52,6 +52,10 @@ class _Settings:
     after_wgrad = None
     # with ``after_wgrad``: SMs the GEMM that runs beside the exchange leaves unoccupied for it
     comm_sms = 0
+    # callable(std [T] float32 tensor) -> tensor: data-parallel training averages the per-tile standard
+    # deviations of the init-from-data phase over the replicas here (``distributed.mean_over_replicas``),
+    # so that every replica keeps the same input ranges
+    sync_tile_std = None
 
 
 settings = _Settings()
@@ -301,6 +305,10 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
             if few_rows:
                 smallm_scratch = torch.empty(lib.al_smallm_scratch_floats(m, n, t), device=dev, dtype=torch.float32)
             args.smallm_scratch = _ptr(smallm_scratch)
+        std_shared = None
+        if need_std and desc.ir_mode == _lib.AL_IR_STATIC and settings.sync_tile_std is not None:
+            std_shared = settings.sync_tile_std(sliced_std(in_sizes, x2d)).to(torch.float32).contiguous()
+            args.std_override = _ptr(std_shared)
         w_noise, out_noise = settings.w_noise, settings.out_noise
         if w_noise is not None:
             w_noise = w_noise.to(device=dev, dtype=dtype).contiguous()

@@ -62,7 +62,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError(f"nvcc failed on {src}")
     with open(os.path.join(OUT_DIR, "ptxas.log"), "w") as fh:
         fh.write("\n".join(log))
-    link = [nvcc, "-shared", "-o", OUT, *objs, "-lcudart"]
+    link = [nvcc, "-shared", "-o", OUT, *objs, "-lcudart", "-ldl"]
     res = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout)

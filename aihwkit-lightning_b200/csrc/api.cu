@@ -7,10 +7,19 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "analog_math.cuh"
 #include "internal.h"
 
 namespace al {
+
+// NVTX range around an entry point: a timeline profiler shows which kernels belong to which call
+// (the header-only NVTX loader does nothing unless a tool is attached).
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+};
 
 static thread_local char g_last_error[512] = "";
 
@@ -220,6 +229,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     set_error("al_forward: null descriptor");
     return AL_ERR_BAD_ARGUMENT;
   }
+  NvtxRange range("al_forward");
   const AlDesc& d = *desc;
   Derived dv;
   int rc = derive(d, &dv);
@@ -259,14 +269,18 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     }
     int do_update = d.training && d.init_from_data > 0;
     if (do_update) {
-      if (!a->std_scratch) {
-        set_error("init_from_data > 0 needs std_scratch");
-        return AL_ERR_BAD_ARGUMENT;
+      const float* std_in = a->std_override;  // given: the caller's (replica-averaged) statistics
+      if (!std_in) {
+        if (!a->std_scratch) {
+          set_error("init_from_data > 0 needs std_scratch");
+          return AL_ERR_BAD_ARGUMENT;
+        }
+        float* std_out = a->std_scratch + 2 * (int64_t)d.M * d.T;
+        rc = launch_std_tiles(d.dtype, a->x, d.M, d.K, tt, std_out, a->std_scratch, s);
+        if (rc) return rc;
+        std_in = std_out;
       }
-      float* std_out = a->std_scratch + 2 * (int64_t)d.M * d.T;
-      rc = launch_std_tiles(d.dtype, a->x, d.M, d.K, tt, std_out, a->std_scratch, s);
-      if (rc) return rc;
-      rc = launch_ir_update(d.dtype, a->input_range, a->input_range_update_idx, std_out, d.T,
+      rc = launch_ir_update(d.dtype, a->input_range, a->input_range_update_idx, std_in, d.T,
                             d.init_from_data, dv.init_std_alpha, 1, a->ir_rows, s);
     } else {
       rc = launch_ir_update(d.dtype, a->input_range, a->input_range_update_idx, nullptr, d.T, 0,
@@ -435,6 +449,7 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
     set_error("al_backward: null descriptor");
     return AL_ERR_BAD_ARGUMENT;
   }
+  NvtxRange range("al_backward");
   const AlDesc& d = *desc;
   Derived dv;
   int rc = derive(d, &dv);

@@ -124,6 +124,12 @@ typedef struct AlForwardArgs {
                                  nullable if out_bound <= 0                                 */
   float* std_scratch;        /* >= al_std_scratch_floats(M, T) floats, static mode with
                                  init_from_data > 0 in training; nullable otherwise        */
+  const float* std_override; /* [T] float, nullable: per-tile standard deviations to use for the
+                                 init-from-data update of a static input range instead of
+                                 computing them from x -- data-parallel callers pass the mean
+                                 of al_std_tiles over all replicas so that every replica
+                                 updates its ranges identically (the reference updates from
+                                 the local batch, P/torch_utils/torch_linear.py:338-352)   */
   float* smallm_scratch;     /* >= al_smallm_scratch_floats(M, N, T) floats, nullable: lets a
                                  call with M <= 16 rows that modifies no weights and prepares
                                  no backward stream the weights once (abs-max and tile

@@ -10,7 +10,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from aihwkit_lightning_b200.distributed import (
-    EagerGradientSync, GradientBuckets, all_reduce_gradients, rank_seed, shard_rows)
+    EagerGradientSync, GradientBuckets, all_reduce_gradients, mean_over_replicas, rank_seed, shard_rows)
 
 
 def test_shard_rows_partition():
@@ -125,3 +125,38 @@ def test_eager_gradient_sync_two_gloo_ranks(tmp_path):
     for x, y in zip(torch.load(tmp_path / "e0.pt"), torch.load(tmp_path / "e1.pt")):
         assert torch.equal(x, y)
 
+
+
+def _ir_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # the init-from-data update of a learned input range (`torch_linear.py:338-352`) with the per-tile
+        # standard deviation shared between the replicas: ir <- (ir * idx + alpha * std) / (idx + 1)
+        gen = torch.Generator().manual_seed(50 + rank)  # every replica sees its own batch
+        ir, idx, alpha = torch.full((3,), 3.0), torch.zeros(3), 3.0
+        local_ir = ir.clone()
+        for _ in range(4):
+            x = torch.randn(64, 48, generator=gen) * (1.0 + rank)
+            std = torch.stack([x[:, 16 * t:16 * (t + 1)].std() for t in range(3)])
+            local_ir = (local_ir * idx + alpha * std) / (idx + 1)
+            shared = mean_over_replicas(std.clone())
+            ir = (ir * idx + alpha * shared) / (idx + 1)
+            idx = idx + 1
+        torch.save((ir, local_ir), os.path.join(out_dir, f"ir{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_shared_tile_statistics_keep_input_ranges_identical(tmp_path):
+    world = 2
+    mp.spawn(_ir_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    (a, a_local), (b, b_local) = torch.load(tmp_path / "ir0.pt"), torch.load(tmp_path / "ir1.pt")
+    assert torch.equal(a, b)                    # replicas agree bit for bit
+    assert not torch.allclose(a_local, b_local)  # the purely local updates would have diverged
+
+
+def test_mean_over_replicas_is_the_identity_without_a_group():
+    v = torch.tensor([1.0, 2.0])
+    assert mean_over_replicas(v) is v and v.tolist() == [1.0, 2.0]

@@ -96,9 +96,12 @@ def test_config2_training_step_at_full_size():
 
 
 SWEEP = [
-    # (M, K=N, max_input_size): points of the inference shape sweep (noise off, exact compare)
-    (1, 2048, 256), (16, 4096, 512), (256, 4096, 1024), (4096, 2048, 512), (4096, 4096, 256),
-    (16, 8192, 1024), (256, 16384, 512),
+    # (M, K=N, max_input_size): points of the inference shape sweep (noise off, exact compare):
+    # every M at K = N = 4096 and 8192, the corners of the other sizes and tilings
+    (1, 2048, 256), (4096, 2048, 512), (4096, 4096, 256), (256, 4096, 1024),
+    (1, 4096, 512), (16, 4096, 512), (256, 4096, 512), (4096, 4096, 512), (16384, 4096, 512),
+    (1, 8192, 512), (16, 8192, 1024), (256, 8192, 512), (4096, 8192, 512), (16384, 8192, 256),
+    (256, 16384, 512), (16384, 16384, 1024),
 ]
 
 

@@ -286,3 +286,34 @@ def test_after_wgrad_hook_gets_the_weight_gradient_before_the_input_gradient_is_
     for got, ref in zip((x.grad, layer.weight.grad, layer.bias.grad, layer.input_range.grad), want):
         assert torch.equal(got, ref)
 
+
+
+def test_shared_tile_statistics_override_the_local_ones():
+    """Data-parallel init-from-data: with ``settings.sync_tile_std`` installed the range update uses
+    the statistics that callable returns (the replica mean in training) instead of the local ones."""
+    from aihwkit_lightning_b200.nn import AnalogLinear
+    from aihwkit_lightning_b200.nn import functional as F
+    from aihwkit_lightning_b200.simulator.configs import TorchInferenceRPUConfig
+
+    rpu = TorchInferenceRPUConfig()
+    rpu.mapping.max_input_size = 32
+    rpu.forward.inp_res = 254
+    rpu.pre_post.input_range.enable = True
+    rpu.pre_post.input_range.init_from_data = 10
+    rpu.pre_post.input_range.init_value = 3.0
+    torch.manual_seed(0)
+    layer = AnalogLinear(64, 16, rpu_config=rpu).cuda().train()
+    x = torch.randn(128, 64, device="cuda")
+    seen = []
+
+    def doubled(std):
+        seen.append(std.clone())
+        return std * 2.0
+
+    with F.operator_settings(sync_tile_std=doubled):
+        layer(x)
+    local = torch.stack([x[:, :32].std(), x[:, 32:].std()])
+    assert torch.allclose(seen[0], local, rtol=1e-5)
+    alpha = rpu.pre_post.input_range.init_std_alpha
+    assert torch.allclose(layer.input_range.detach(), alpha * 2.0 * local, rtol=1e-5)  # idx 0: ir <- alpha * std
+    assert layer.input_range_update_idx.tolist() == [1.0, 1.0]

@@ -29,7 +29,12 @@ def check_close(name, got, want, dtype, case):
     got, want = got.detach().cpu(), want.cpu()
     assert got.shape == want.shape, f"{name}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
     if dtype == torch.float32:
-        ok = torch.isclose(got, want, rtol=FP32_TOL, atol=FP32_TOL)
+        # 1e-5 relative: element by element against the larger of the element and the tensor's scale (a sum
+        # over hundreds of rows carries summation-order noise of the size of its terms, not of its value)
+        scale = max(1.0, want.abs().max().item())
+        ok = torch.isclose(got, want, rtol=FP32_TOL, atol=FP32_TOL * scale)
+        if case["out_res"] <= 0:
+            assert rel_fro(got, want) <= FP32_TOL, f"{name}: rel fro {rel_fro(got, want):.3e}"
         if case["out_res"] > 0 and not bool(ok.all()):
             # allow counted one-level ADC flips (and what they drag along in the gradients)
             assert (~ok).float().mean().item() <= ADC_FLIP_FRACTION, f"{name}: too many mismatches"
@@ -99,6 +104,12 @@ SIZED = [
     ("bf16_dynamic_adc_noise", dict(in_shape=(256, 1024), out_features=512, max_input_size=256)),
     ("bf16_static_noise", dict(in_shape=(128, 768), out_features=256, max_input_size=256, ir_init_value=2.0)),
     ("ragged_tiles", dict(in_shape=(33, 1000), out_features=130, max_input_size=300)),
+    # benchmark configuration 1 at its own size: 512 x 1024 -> 1024 fp32, two tiles of 512, learned static range
+    # 3.0, inp_res 254, out_noise 0.04, weight noise 0.02 relative to the tile maximum / to each channel's abs-max
+    ("static_train_noise", dict(in_shape=(512, 1024), out_features=1024, max_input_size=512, ir_init_value=3.0,
+                                config1=True)),
+    ("static_train_noise_pc", dict(in_shape=(512, 1024), out_features=1024, max_input_size=512, ir_init_value=3.0,
+                                   out_noise_per_channel=False, config1=True)),
 ]
 
 
@@ -107,7 +118,7 @@ def test_against_oracle_at_medium_size(base, over):
     """Sizes the CPU oracle finishes in seconds; inputs seeded on the CPU and copied over."""
     case = dict(C.CASES_BY_NAME[base])
     case.update(over)
-    case["weight_scale"] = 0.05
+    case["weight_scale"] = 1 / 32 if case.pop("config1", False) else 0.05  # config 1: weights ~U(-1/32, 1/32)
     data = C.make_inputs(case)
     rec, grads = oracle_run(case, data, w_noise=data["w_noise"][-1], out_noise=data["out_noise"][-1])
     layer, x, out = run_product_layer(case, data, engine="simt")

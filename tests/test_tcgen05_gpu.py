@@ -187,8 +187,9 @@ def test_order_independent_problem_is_bit_exact(variant):
         assert torch.equal(layer.weight.grad.cpu(), grads["grad_w"]), f"{engine}: grad_w differs"
 
 
+@pytest.mark.parametrize("k,tile", [(512, 128), (3072, 512), (8192, 512)], ids=["T4", "T6", "T16"])
 @pytest.mark.parametrize("engine", ["tcgen05_single", "tcgen05_pair"])
-def test_output_noise_without_adc_is_one_gaussian_per_output(engine):
+def test_output_noise_without_adc_is_one_gaussian_per_output(engine, k, tile):
     """No ADC and no clamp: the tile terms s_t * xi_t of an output are drawn as one Gaussian of the
     summed variance.  Mean, variance (per row: it depends on the row's input ranges), Gaussian shape
     and independence across neighbouring outputs and across calls."""
@@ -199,10 +200,11 @@ def test_output_noise_without_adc_is_one_gaussian_per_output(engine):
     from util import NS
 
     case = dict(C.DEFAULTS)
-    case.update(ir_dynamic=True, out_noise=0.1, max_input_size=128, inp_res=254.0)
+    # T4: a small layer; T6 / T16: the tilings of the decoder configuration (K = 3072 and 8192 in tiles of 512)
+    case.update(ir_dynamic=True, out_noise=0.1, max_input_size=tile, inp_res=254.0)
     rpu = C.build_rpu_config(NS, case)
     torch.manual_seed(0)
-    k, n, m, t_count = 512, 512, 512, 4
+    n, m, t_count = 512, 512, k // tile
     layer = AnalogLinear(k, n, bias=False, rpu_config=rpu).to(device="cuda", dtype=torch.bfloat16)
     x = (torch.randn(m, k, device="cuda") * torch.linspace(0.5, 2.0, m, device="cuda")[:, None]).bfloat16()
     with F.operator_settings(engine=engine):
@@ -215,8 +217,8 @@ def test_output_noise_without_adc_is_one_gaussian_per_output(engine):
     w, xs = layer.weight.detach().float().cpu(), x.float().cpu()
     var = torch.zeros(m)
     for t in range(t_count):
-        wmax = w[:, 128 * t:128 * (t + 1)].abs().max()
-        ir = xs[:, 128 * t:128 * (t + 1)].abs().amax(1)
+        wmax = w[:, tile * t:tile * (t + 1)].abs().max()
+        ir = xs[:, tile * t:tile * (t + 1)].abs().amax(1)
         var += (wmax * 0.1 / math.sqrt(t_count) * ir) ** 2
     z1 = (noisy1 - clean).cpu() / var.sqrt()[:, None]
     z2 = (noisy2 - clean).cpu() / var.sqrt()[:, None]
