@@ -42,7 +42,8 @@ class AlForwardArgs(Structure):
         ("tile_ends", POINTER(c_int32)),
         ("out", c_void_p), ("xq", c_void_p), ("ir_rows", c_void_p), ("w_amax", c_void_p),
         ("w_tile_max", c_void_p), ("w_mod", c_void_p), ("keep_mask", c_void_p),
-        ("std_scratch", c_void_p), ("std_override", c_void_p), ("smallm_scratch", c_void_p), ("w_noise", c_void_p), ("out_noise", c_void_p),
+        ("std_scratch", c_void_p), ("std_override", c_void_p), ("smallm_scratch", c_void_p),
+        ("codes16", c_void_p), ("w_planes", c_void_p), ("w_noise", c_void_p), ("out_noise", c_void_p),
         ("codes", c_void_p), ("seed", c_uint64), ("offset", c_uint64),
     ]
 
@@ -53,6 +54,7 @@ class AlBackwardArgs(Structure):
         ("ir_rows", c_void_p), ("keep_mask", c_void_p), ("tile_ends", POINTER(c_int32)),
         ("grad_x", c_void_p), ("grad_w", c_void_p), ("grad_bias", c_void_p),
         ("grad_input_range", c_void_p), ("reduce_scratch", c_void_p), ("reduce_scratch_floats", c_int64),
+        ("codes16", c_void_p), ("w_planes", c_void_p), ("g_planes", c_void_p), ("g_planes_elems", c_int64),
         ("w", c_void_p), ("learnable_weight_clip", c_void_p), ("grad_weight_clip", c_void_p),
     ]
 
@@ -75,6 +77,7 @@ SYMBOLS = {
     "al_backward": (c_int32, [POINTER(AlDesc), POINTER(AlBackwardArgs), c_void_p]),
     "al_backward_scratch_floats": (c_int64, [c_int32, c_int32, c_int32, c_int32]),
     "al_smallm_scratch_floats": (c_int64, [c_int32, c_int32, c_int32]),
+    "al_backward_plane_elems": (c_int64, [POINTER(AlDesc), POINTER(c_int32)]),
     "al_clip_weights": (c_int32, [c_int32, c_void_p, c_int32, c_int32, c_int32, c_float, c_void_p, c_void_p]),
     "al_unfold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
     "al_fold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),

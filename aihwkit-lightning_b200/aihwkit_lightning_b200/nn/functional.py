@@ -263,6 +263,9 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
         xq = x2d
         ir_rows = w_amax = w_tile_max = keep_mask = None
         w_mod = w
+        # fp32 layer on the tensor cores: the GEMMs read the DAC codes and the weights as bf16 planes
+        planes = dtype == torch.float32 and bool(lib.al_uses_tcgen05(desc, ends))
+        codes16 = w_planes = None
         if not needs_grad and settings.capture is None:
             # nothing of the workspace outlives the call: one allocation, carved by offset
             es = x2d.element_size()
@@ -275,6 +278,8 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
                 plan.append(("std_scratch", lib.al_std_scratch_floats(m, t) * 4))
             if few_rows:
                 plan.append(("smallm_scratch", lib.al_smallm_scratch_floats(m, n, t) * 4))
+            if planes:
+                plan += [("codes16", m * k * 2), ("w_planes", 3 * n * k * 2)]
             total = 0
             for _, nbytes in plan:
                 total += (nbytes + 255) & ~255
@@ -305,6 +310,10 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
             if few_rows:
                 smallm_scratch = torch.empty(lib.al_smallm_scratch_floats(m, n, t), device=dev, dtype=torch.float32)
             args.smallm_scratch = _ptr(smallm_scratch)
+            if planes:
+                codes16 = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
+                w_planes = torch.empty(3, n, k, device=dev, dtype=torch.bfloat16)
+                args.codes16, args.w_planes = _ptr(codes16), _ptr(w_planes)
         std_shared = None
         if need_std and desc.ir_mode == _lib.AL_IR_STATIC and settings.sync_tile_std is not None:
             std_shared = settings.sync_tile_std(sliced_std(in_sizes, x2d)).to(torch.float32).contiguous()
@@ -333,14 +342,15 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
             w_mod=w_mod, keep_mask=keep_mask,
             uses_tcgen05=bool(lib.al_uses_tcgen05(desc, ends)),
         )
-    ctx.desc, ctx.in_sizes = desc, list(in_sizes)
+    ctx.desc, ctx.in_sizes, ctx.dtype = desc, list(in_sizes), dtype
     ctx.shape = tuple(inp.shape)
     ctx.has_bias = bias is not None
     ctx.ir_needs_grad = static and input_range is not None and input_range.requires_grad
     ctx.learn_clip = learn_clip
     if needs_grad:
-        ctx.save_for_backward(x2d if static else None, xq, w_mod, ir_rows, keep_mask,
-                              w if learn_clip else None, lwc)
+        # with bf16 planes the backward GEMMs read those: the fp32 copies need not be kept
+        ctx.save_for_backward(x2d if static else None, None if planes else xq, None if planes else w_mod, ir_rows,
+                              keep_mask, w if learn_clip else None, lwc, codes16, w_planes)
     return out.view(*inp.shape[:-1], n)
 
 def _analog_backward(ctx, grad_out):
@@ -348,10 +358,10 @@ def _analog_backward(ctx, grad_out):
     if ctx.empty:
         return (None,) * 12
     lib = _lib.load()
-    x2d, xq, w_mod, ir_rows, keep_mask, w_saved, lwc = ctx.saved_tensors
+    x2d, xq, w_mod, ir_rows, keep_mask, w_saved, lwc, codes16, w_planes = ctx.saved_tensors
     desc = ctx.desc
     m, k, n, t = desc.M, desc.K, desc.N, desc.T
-    dev, dtype = grad_out.device, xq.dtype
+    dev, dtype = grad_out.device, ctx.dtype
     g = grad_out.reshape(m, n).to(dtype).contiguous()
     need_x, need_w, need_b, need_ir = ctx.needs_input_grad[:4]
     need_b = need_b and ctx.has_bias
@@ -372,6 +382,11 @@ def _analog_backward(ctx, grad_out):
         args.grad_x, args.grad_w, args.grad_bias = _ptr(grad_x), _ptr(grad_w), _ptr(grad_b)
         args.grad_input_range, args.reduce_scratch = _ptr(grad_ir), _ptr(scratch)
         args.reduce_scratch_floats = scratch.numel()
+        g_planes = None
+        if codes16 is not None:
+            g_planes = torch.empty(lib.al_backward_plane_elems(desc, ends), device=dev, dtype=torch.bfloat16)
+            args.codes16, args.w_planes, args.g_planes = _ptr(codes16), _ptr(w_planes), _ptr(g_planes)
+            args.g_planes_elems = g_planes.numel()
         grad_clip = None
         if need_clip:
             grad_clip = torch.empty(t, n, device=dev, dtype=dtype)

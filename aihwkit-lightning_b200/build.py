@@ -17,6 +17,7 @@ SOURCES = [
     "api.cu",
     "reduce_kernels.cu",
     "prepass_kernels.cu",
+    "split_kernels.cu",
     "gemm_simt.cu",
     "gemm_tcgen05_fwd.cu",
     "gemm_tcgen05_bwd.cu",

@@ -150,6 +150,15 @@ static bool pick_tc(const AlDesc& d, const TileTable& tt, bool backward) {
   return backward ? tc_backward_supported(d, tt) : tc_forward_supported(d, tt);
 }
 
+// fp32 layers: tensor cores (bf16 planes) when the configuration allows it and, under AUTO, when
+// the layer is large enough for 128-wide blocks and the extra operand pre-passes to pay; layers
+// with few output channels (convolutions) stay on the CUDA cores, they are bound by memory
+static bool pick_tc_f32(const AlDesc& d, const TileTable& tt) {
+  if (d.engine == AL_ENGINE_SIMT || !tc_f32_supported(d, tt)) return false;
+  if (d.engine >= AL_ENGINE_TCGEN05) return true;
+  return d.M >= 128 && d.N >= 128 && d.K >= 128 && (double)d.M * d.N * d.K >= 134217728.0;
+}
+
 }  // namespace al
 
 namespace {
@@ -221,7 +230,17 @@ int al_uses_tcgen05(const AlDesc* desc, const int32_t* tile_ends_host) {
   if (!desc) return 0;
   TileTable tt;
   if (make_tile_table(tile_ends_host, desc->T, desc->K, &tt)) return 0;
-  return pick_tc(*desc, tt, false) ? 1 : 0;
+  return (pick_tc(*desc, tt, false) || pick_tc_f32(*desc, tt)) ? 1 : 0;
+}
+
+int64_t al_backward_plane_elems(const AlDesc* desc, const int32_t* tile_ends_host) {
+  if (!desc) return 0;
+  TileTable tt;
+  if (make_tile_table(tile_ends_host, desc->T, desc->K, &tt) || !pick_tc_f32(*desc, tt)) return 0;
+  const int64_t plane = (int64_t)desc->M * desc->N;
+  const int64_t sets_d = desc->out_bound > 0 ? desc->T : 1;                    // masked: one set per tile
+  const int64_t sets_w = desc->ir_mode == AL_IR_DYNAMIC ? desc->T : 0;          // per-row DAC steps folded in
+  return 3 * plane * (sets_d + sets_w);
 }
 
 int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
@@ -290,6 +309,14 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     ir_static = a->ir_rows;
   }
 
+  // fp32 layer on the tensor cores: needs the bf16 workspaces
+  const bool tc_f32 = pick_tc_f32(d, tt) && a->codes16 != nullptr && a->w_planes != nullptr;
+  if (d.dtype == AL_F32 && d.engine >= AL_ENGINE_TCGEN05 && !tc_f32) {
+    set_error("tcgen05 engine requested for an fp32 layer that does not qualify (DAC on, rounding on, aligned tiles, "
+              "codes16 and w_planes given)");
+    return AL_ERR_UNSUPPORTED;
+  }
+
   // 2. DAC: x -> xq (+ per-row ranges in dynamic mode)
   const void* xq = a->x;
   if (d.ir_mode != AL_IR_OFF) {
@@ -298,7 +325,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
       return AL_ERR_BAD_ARGUMENT;
     }
     rc = launch_dac(d.dtype, a->x, d.M, d.K, tt, d.ir_mode == AL_IR_FAST ? AL_IR_STATIC : d.ir_mode, ir_static, dv.has_dac ? dv.inp_res : -1.0f,
-                    d.no_rounding, a->xq, a->ir_rows, a->codes, s);
+                    d.no_rounding, a->xq, a->ir_rows, a->codes, s, tc_f32 ? a->codes16 : nullptr);
     if (rc) return rc;
     xq = a->xq;
   }
@@ -403,6 +430,11 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
   ep.noise_coef = dv.noise_coef; ep.out_bound = dv.out_bound; ep.out_res = dv.out_res;
   ep.seed = a->seed; ep.offset = a->offset;
 
+  if (tc_f32) {
+    rc = launch_split3(static_cast<const float*>(w_mod), (int64_t)d.N * d.K, a->w_planes, s);
+    if (rc) return rc;
+    return launch_fwd_tc_f32(a->codes16, a->w_planes, d.K, tt, ep, dv.inp_res, a->out, s);
+  }
   if (d.engine >= AL_ENGINE_TCGEN05 && !tc_forward_supported(d, tt)) {
     set_error("tcgen05 engine requested but the problem does not qualify (bf16, 16-byte aligned tiles)");
     return AL_ERR_UNSUPPORTED;
@@ -479,19 +511,36 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
   one.ends[0] = d.K;
   const TileTable& gt = mask ? tt : one;
   const int pairing = d.engine == AL_ENGINE_TCGEN05_PAIR ? 1 : d.engine == AL_ENGINE_TCGEN05_SINGLE ? -1 : 0;
-  if (d.engine >= AL_ENGINE_TCGEN05 && !tc_backward_supported(d, tt)) {
+  // fp32 layer whose forward ran on the tensor cores: bf16 planes of the upstream gradient
+  const bool tc_f32 = pick_tc_f32(d, tt) && a->codes16 != nullptr && a->w_planes != nullptr && a->g_planes != nullptr;
+  const int sets_d = mask ? d.T : 1;
+  const int64_t plane_elems = 3 * (int64_t)d.M * d.N;
+  if (tc_f32 && a->g_planes_elems < al_backward_plane_elems(desc, a->tile_ends)) {
+    set_error("al_backward: g_planes holds %lld elements, al_backward_plane_elems asks for %lld",
+              (long long)a->g_planes_elems, (long long)al_backward_plane_elems(desc, a->tile_ends));
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  if (d.engine >= AL_ENGINE_TCGEN05 && !tc_f32 && !tc_backward_supported(d, tt)) {
     set_error("tcgen05 engine requested but the problem does not qualify");
     return AL_ERR_UNSUPPORTED;
   }
-  bool tc = pick_tc(d, tt, true);
+  bool tc = !tc_f32 && pick_tc(d, tt, true);
+  if (tc_f32 && (a->grad_x || a->grad_w)) {
+    // planes of g (masked per tile when the ADC clamped), shared by the input gradient and -- with
+    // one input range per tile -- by the weight gradient
+    rc = launch_split3_grad(static_cast<const float*>(a->grad_out), d.M, d.N, mask, mask_words, nullptr, 0, 0.0f,
+                            sets_d, a->g_planes, s);
+    if (rc) return rc;
+  }
 
   if (a->grad_x) {
-    if (!a->w_mod) {
+    if (!a->w_mod && !tc_f32) {
       set_error("al_backward: w_mod missing");
       return AL_ERR_BAD_ARGUMENT;
     }
-    rc = tc ? launch_dgrad_tc(a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, pairing, a->grad_x, s)
-            : launch_dgrad_simt(d.dtype, a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, a->grad_x, s);
+    rc = tc_f32 ? launch_dgrad_tc_f32(a->g_planes, sets_d, a->w_planes, d.M, d.K, d.N, tt, pairing, a->grad_x, s)
+         : tc   ? launch_dgrad_tc(a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, pairing, a->grad_x, s)
+                : launch_dgrad_simt(d.dtype, a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, a->grad_x, s);
     if (rc) return rc;
     if (d.ir_mode == AL_IR_STATIC || d.ir_mode == AL_IR_FAST) {
       if (!a->x || !a->ir_rows || !a->reduce_scratch) {
@@ -507,7 +556,20 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
     set_error("al_backward: grad_input_range needs grad_x");
     return AL_ERR_BAD_ARGUMENT;
   }
-  if (a->grad_w) {
+  if (a->grad_w && tc_f32) {
+    if (d.ir_mode == AL_IR_DYNAMIC) {
+      // per-row DAC steps: a second set of planes, one per tile, with the step (and the mask) folded in
+      uint16_t* planes_w = static_cast<uint16_t*>(a->g_planes) + plane_elems * sets_d;
+      rc = launch_split3_grad(static_cast<const float*>(a->grad_out), d.M, d.N, mask, mask_words,
+                              static_cast<const float*>(a->ir_rows), 1, dv.inp_res, d.T, planes_w, s);
+      if (rc) return rc;
+      rc = launch_wgrad_tc_f32(planes_w, d.T, a->codes16, d.M, d.K, d.N, tt, nullptr, 0.0f, pairing, a->grad_w, s);
+    } else {
+      rc = launch_wgrad_tc_f32(a->g_planes, sets_d, a->codes16, d.M, d.K, d.N, tt,
+                               static_cast<const float*>(a->ir_rows), dv.inp_res, pairing, a->grad_w, s);
+    }
+    if (rc) return rc;
+  } else if (a->grad_w) {
     if (!a->xq) {
       set_error("al_backward: xq missing");
       return AL_ERR_BAD_ARGUMENT;

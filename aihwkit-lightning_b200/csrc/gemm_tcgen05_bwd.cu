@@ -26,7 +26,54 @@ struct BwdTcParams {
   const uint32_t* keep_mask;
   int32_t mask_words;
   void* c_out;
+  // fp32 layers: the operands arrive as bf16 planes (third dimension of the tensor maps) and an
+  // output block accumulates `products` plane products, product q = A plane pa[q] x B plane pb[q];
+  // bf16 layers: one product of plane 0.  A has a_planes_per_tile planes per analog tile when the
+  // caller prepared it per tile (clamp mask / DAC step folded in), 0 when all tiles share it.
+  int32_t products;
+  uint8_t pa[8], pb[8];
+  int32_t a_planes_per_tile;
+  int32_t f32_out;          // C is fp32 (else bf16)
+  const float* c_scale_ir;  // [T] input ranges: C[:, tile t] is multiplied by the DAC step of tile t (null: no scaling)
+  float inp_res;
 };
+
+// r += the 32 columns of the cross-term accumulator at taddr (fp32, round to nearest)
+__device__ __forceinline__ void add_cross_terms(uint32_t taddr, uint32_t r[32]) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t x[16];
+    tmem_ld16(taddr + (uint32_t)(half * 16), x);
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      r[half * 16 + j] = __float_as_uint(__fadd_rn(__uint_as_float(r[half * 16 + j]), __uint_as_float(x[j])));
+  }
+}
+
+// 32 accumulator columns of one row -> C (bf16 or fp32), columns jc .. jc + 31 clipped at j_end
+__device__ __forceinline__ void store_c_row(const BwdTcParams& p, int64_t row, int jc, int j_end, const uint32_t r[32],
+                                            float scale) {
+  if (p.f32_out) {
+    float* dst = reinterpret_cast<float*>(p.c_out) + row * p.K + jc;
+#pragma unroll
+    for (int v = 0; v < 8; ++v)
+      if (jc + v * 4 < j_end)
+        *reinterpret_cast<float4*>(dst + v * 4) =
+            make_float4(__uint_as_float(r[v * 4]) * scale, __uint_as_float(r[v * 4 + 1]) * scale,
+                        __uint_as_float(r[v * 4 + 2]) * scale, __uint_as_float(r[v * 4 + 3]) * scale);
+  } else {
+    uint16_t* dst = reinterpret_cast<uint16_t*>(p.c_out) + row * p.K + jc;
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+      if (jc + v * 8 < j_end)
+        *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(
+            pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1])),
+            pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3])),
+            pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5])),
+            pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7])));
+  }
+}
 
 // A heavily clamped 128-byte row of a staged A tile: rewrite its 16-byte chunks under the
 // expanded keep mask (bit j = keep element j).
@@ -60,6 +107,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool masked = p.keep_mask != nullptr;
+  const bool split_acc = p.products > 1;
   const int num_work = p.num_ib * p.T * p.num_jb;
 
   if (threadIdx.x == 0) {
@@ -94,29 +142,32 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const int rem = w % (p.T * p.num_jb);
         const int t = rem / p.num_jb, jb = rem % p.num_jb;
         const int j0 = t * p.tile_w + jb * B_BN;
-        for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
-          const int s = it % B_STAGES;
-          const uint32_t ph = (it / B_STAGES) & 1u;
-          if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag)) {
-            raise_error(kErrProducer, abort_flag);
-            ok = false;
-            break;
-          }
-          uint8_t* sa = stage_base + s * B_STAGE_BYTES;
-          uint8_t* sb = sa + B_A_BYTES;
-          const int l0 = ls * BK;
-          mbar_expect_tx(&bars->full[s], B_STAGE_BYTES);
-          if (WGRAD) {
-            // A = g^T: two MN-major boxes [64 rows of m] x [64 n]
-            tma_load_2d(sa, &map_a, &bars->full[s], ib * BM, l0);
-            tma_load_2d(sa + B_BOX_BYTES, &map_a, &bars->full[s], ib * BM + 64, l0);
-          } else {
-            // A = g: K-major [128 rows of m] x [64 n]
-            tma_load_2d(sa, &map_a, &bars->full[s], l0, ib * BM);
-          }
+        for (int q = 0; q < p.products && ok; ++q) {
+          const int plane_a = p.pa[q] + t * p.a_planes_per_tile, plane_b = p.pb[q];
+          for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+            const int s = it % B_STAGES;
+            const uint32_t ph = (it / B_STAGES) & 1u;
+            if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag)) {
+              raise_error(kErrProducer, abort_flag);
+              ok = false;
+              break;
+            }
+            uint8_t* sa = stage_base + s * B_STAGE_BYTES;
+            uint8_t* sb = sa + B_A_BYTES;
+            const int l0 = ls * BK;
+            mbar_expect_tx(&bars->full[s], B_STAGE_BYTES);
+            if (WGRAD) {
+              // A = g^T: two MN-major boxes [64 rows of m] x [64 n]
+              tma_load_3d(sa, &map_a, &bars->full[s], ib * BM, l0, plane_a);
+              tma_load_3d(sa + B_BOX_BYTES, &map_a, &bars->full[s], ib * BM + 64, l0, plane_a);
+            } else {
+              // A = g: K-major [128 rows of m] x [64 n]
+              tma_load_3d(sa, &map_a, &bars->full[s], l0, ib * BM, plane_a);
+            }
 #pragma unroll
-          for (int c = 0; c < B_BN / 64; ++c)
-            tma_load_2d(sb + c * B_BOX_BYTES, &map_b, &bars->full[s], j0 + c * 64, l0);
+            for (int c = 0; c < B_BN / 64; ++c)
+              tma_load_3d(sb + c * B_BOX_BYTES, &map_b, &bars->full[s], j0 + c * 64, l0, plane_b);
+          }
         }
       }
       const uint32_t n_back = it < (uint32_t)B_STAGES ? it : (uint32_t)B_STAGES;
@@ -139,16 +190,22 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++acc_it) {
-        const int b = acc_it & 1u;
-        const uint32_t aph = (acc_it >> 1) & 1u;
+        // plane products: the leading product accumulates in buffer 0 and the (much smaller) cross terms
+        // in buffer 1 -- the tensor core truncates when it adds into an accumulator, and the truncation is
+        // relative to the accumulator's size -- so an item holds both buffers and there is no overlap
+        const int b = split_acc ? 0 : (int)(acc_it & 1u);
+        const uint32_t aph = split_acc ? (acc_it & 1u) : ((acc_it >> 1) & 1u);
         if (!mbar_wait(&bars->acc_empty[b], aph ^ 1u, abort_flag)) {
           raise_error(kErrMma, abort_flag);
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(b * B_BN);
-        for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+        const int steps = p.lsteps * p.products;  // every plane product runs over the whole reduction
+        for (int ls = 0; ls < steps; ++ls, ++it) {
+          const bool cross = split_acc && ls >= p.lsteps;
+          const uint32_t d_tmem = tmem_base + (uint32_t)((cross ? 1 : b) * B_BN);
+          const bool first = ls == 0 || (split_acc && ls == p.lsteps);
           const int s = it % B_STAGES;
           const uint32_t ph = (it / B_STAGES) & 1u;
           // the transform warps vouch for a stage on `ready` before its copy has landed when
@@ -169,7 +226,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           constexpr uint64_t b_step = 2048u >> 4;
 #pragma unroll
           for (int k4 = 0; k4 < BK / 16; ++k4)
-            umma_bf16(d_tmem, da + a_step * k4, db + b_step * k4, idesc, (ls | k4) != 0 ? 1u : 0u);
+            umma_bf16(d_tmem, da + a_step * k4, db + b_step * k4, idesc, (first && k4 == 0) ? 0u : 1u);
           umma_commit(&bars->empty[s]);
         }
         if (ok) umma_commit(&bars->acc_full[b]);
@@ -196,15 +253,15 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       const int j0 = t * p.tile_w + jb * B_BN;
       const int j_end = min((t + 1) * p.tile_w, p.K);
       const int i = ib * BM + quad * 32 + lane;
-      const int b = acc_it & 1u;
-      const uint32_t aph = (acc_it >> 1) & 1u;
+      const int b = split_acc ? 0 : (int)(acc_it & 1u);
+      const uint32_t aph = split_acc ? (acc_it & 1u) : ((acc_it >> 1) & 1u);
       if (!mbar_wait(&bars->acc_full[b], aph, abort_flag)) {
         if (lane == 0) raise_error(kErrEpilogue, abort_flag);
         ok = false;
         break;
       }
       tc_fence_after();
-      uint16_t* dst_row = reinterpret_cast<uint16_t*>(p.c_out) + (int64_t)i * p.K;
+      const float c_scale = p.c_scale_ir != nullptr ? quant_step<kF32>(p.c_scale_ir[t], p.inp_res) : 1.0f;
 #pragma unroll 1
       for (int c = 0; c < B_BN / 32; ++c) {
         const int jc = j0 + c * 32;
@@ -212,19 +269,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         uint32_t r[32];
         tmem_ld32(tmem_base + lane_base + (uint32_t)(b * B_BN + c * 32), r);
         tmem_wait_ld();
-        if (i < p.I) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            if (jc + v * 8 < j_end) {
-              uint4 pk = make_uint4(
-                  pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1])),
-                  pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3])),
-                  pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5])),
-                  pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7])));
-              *reinterpret_cast<uint4*>(dst_row + jc + v * 8) = pk;
-            }
-          }
-        }
+        if (split_acc) add_cross_terms(tmem_base + lane_base + (uint32_t)(B_BN + c * 32), r);
+        if (i < p.I) store_c_row(p, i, jc, j_end, r, c_scale);
       }
       tc_fence_before();
       __syncwarp();
@@ -390,6 +436,7 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const bool masked = p.keep_mask != nullptr;
+  const bool split_acc = p.products > 1;  // see bwd_tc_kernel
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int num_work = p.num_ib * p.T * p.num_jb;  // num_ib counts 256-row blocks here
   const int row_off = (int)rank * BM;               // this CTA's rows inside the pair's block
@@ -428,34 +475,37 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int t = rem / p.num_jb, jb = rem % p.num_jb;
         const int i0 = ib * (2 * BM) + row_off;
         const int j0 = t * p.tile_w + jb * P_BN + (int)rank * P_BN_CTA;
-        for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
-          const int s = it % P_STAGES;
-          const uint32_t ph = (it / P_STAGES) & 1u;
-          if (!mbar_wait_cluster(&bars->empty[s], ph ^ 1u, abort_flag)) {
-            raise_error(kErrProducer, abort_flag);
-            ok = false;
-            break;
-          }
-          uint8_t* sa = stage_base + s * P_STAGE_BYTES;
-          uint8_t* sb = sa + P_A_BYTES;
-          const int l0 = ls * BK;
-          uint32_t bar;
-          if (masked) {
-            mbar_expect_tx(&bars->full[s], P_STAGE_BYTES);
-            bar = smem_u32(&bars->full[s]);
-          } else {
-            if (leader) mbar_expect_tx(&bars->full[s], 2 * P_STAGE_BYTES);
-            bar = mapa_u32(smem_u32(&bars->full[s]), 0);
-          }
-          if (WGRAD) {
-            tma_load_2d_pair(sa, &map_a, bar, i0, l0);
-            tma_load_2d_pair(sa + B_BOX_BYTES, &map_a, bar, i0 + 64, l0);
-          } else {
-            tma_load_2d_pair(sa, &map_a, bar, l0, i0);
-          }
+        for (int q = 0; q < p.products && ok; ++q) {
+          const int plane_a = p.pa[q] + t * p.a_planes_per_tile, plane_b = p.pb[q];
+          for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+            const int s = it % P_STAGES;
+            const uint32_t ph = (it / P_STAGES) & 1u;
+            if (!mbar_wait_cluster(&bars->empty[s], ph ^ 1u, abort_flag)) {
+              raise_error(kErrProducer, abort_flag);
+              ok = false;
+              break;
+            }
+            uint8_t* sa = stage_base + s * P_STAGE_BYTES;
+            uint8_t* sb = sa + P_A_BYTES;
+            const int l0 = ls * BK;
+            uint32_t bar;
+            if (masked) {
+              mbar_expect_tx(&bars->full[s], P_STAGE_BYTES);
+              bar = smem_u32(&bars->full[s]);
+            } else {
+              if (leader) mbar_expect_tx(&bars->full[s], 2 * P_STAGE_BYTES);
+              bar = mapa_u32(smem_u32(&bars->full[s]), 0);
+            }
+            if (WGRAD) {
+              tma_load_3d_pair(sa, &map_a, bar, i0, l0, plane_a);
+              tma_load_3d_pair(sa + B_BOX_BYTES, &map_a, bar, i0 + 64, l0, plane_a);
+            } else {
+              tma_load_3d_pair(sa, &map_a, bar, l0, i0, plane_a);
+            }
 #pragma unroll
-          for (int c = 0; c < P_BN_CTA / 64; ++c)
-            tma_load_2d_pair(sb + c * B_BOX_BYTES, &map_b, bar, j0 + c * 64, l0);
+            for (int c = 0; c < P_BN_CTA / 64; ++c)
+              tma_load_3d_pair(sb + c * B_BOX_BYTES, &map_b, bar, j0 + c * 64, l0, plane_b);
+          }
         }
       }
       // drain: copies that complete on this CTA's own barrier must have landed before it exits;
@@ -483,16 +533,19 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
       for (int w = pair; w < num_work && ok; w += n_pairs, ++acc_it) {
-        const int b = acc_it & 1u;
-        const uint32_t aph = (acc_it >> 1) & 1u;
+        const int b = split_acc ? 0 : (int)(acc_it & 1u);
+        const uint32_t aph = split_acc ? (acc_it & 1u) : ((acc_it >> 1) & 1u);
         if (!mbar_wait_cluster(&bars->acc_empty[b], aph ^ 1u, abort_flag)) {
           raise_error(kErrMma, abort_flag);
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(b * P_BN);
-        for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+        const int steps = p.lsteps * p.products;
+        for (int ls = 0; ls < steps; ++ls, ++it) {
+          const bool cross = split_acc && ls >= p.lsteps;
+          const uint32_t d_tmem = tmem_base + (uint32_t)((cross ? 1 : b) * P_BN);
+          const bool first = ls == 0 || (split_acc && ls == p.lsteps);
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1u;
           if (!mbar_wait_cluster(masked ? &bars->ready[s] : &bars->full[s], ph, abort_flag)) {
@@ -509,7 +562,7 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           constexpr uint64_t b_step = 2048u >> 4;
 #pragma unroll
           for (int k4 = 0; k4 < BK / 16; ++k4)
-            umma_bf16_pair(d_tmem, da + a_step * k4, db + b_step * k4, idesc, (ls | k4) != 0 ? 1u : 0u);
+            umma_bf16_pair(d_tmem, da + a_step * k4, db + b_step * k4, idesc, (first && k4 == 0) ? 0u : 1u);
           umma_commit_pair(&bars->empty[s], 3);  // frees the stage in both CTAs
         }
         if (ok) umma_commit_pair(&bars->acc_full[b], 3);
@@ -536,15 +589,15 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       const int j0 = t * p.tile_w + jb * P_BN;
       const int j_end = min((t + 1) * p.tile_w, p.K);
       const int i = ib * (2 * BM) + row_off + quad * 32 + lane;
-      const int b = acc_it & 1u;
-      const uint32_t aph = (acc_it >> 1) & 1u;
+      const int b = split_acc ? 0 : (int)(acc_it & 1u);
+      const uint32_t aph = split_acc ? (acc_it & 1u) : ((acc_it >> 1) & 1u);
       if (!mbar_wait_cluster(&bars->acc_full[b], aph, abort_flag)) {
         if (lane == 0) raise_error(kErrEpilogue, abort_flag);
         ok = false;
         break;
       }
       tc_fence_after();
-      uint16_t* dst_row = reinterpret_cast<uint16_t*>(p.c_out) + (int64_t)i * p.K;
+      const float c_scale = p.c_scale_ir != nullptr ? quant_step<kF32>(p.c_scale_ir[t], p.inp_res) : 1.0f;
 #pragma unroll 1
       for (int c = 0; c < P_BN / 32; ++c) {
         const int jc = j0 + c * 32;
@@ -552,19 +605,8 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         uint32_t r[32];
         tmem_ld32(tmem_base + lane_base + (uint32_t)(b * P_BN + c * 32), r);
         tmem_wait_ld();
-        if (i < p.I) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            if (jc + v * 8 < j_end) {
-              uint4 pk = make_uint4(
-                  pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1])),
-                  pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3])),
-                  pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5])),
-                  pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7])));
-              *reinterpret_cast<uint4*>(dst_row + jc + v * 8) = pk;
-            }
-          }
-        }
+        if (split_acc) add_cross_terms(tmem_base + lane_base + (uint32_t)(P_BN + c * 32), r);
+        if (i < p.I) store_c_row(p, i, jc, j_end, r, c_scale);
       }
       tc_fence_before();
       __syncwarp();
@@ -704,13 +746,29 @@ static int max_pairs(bool wgrad) {
   n = clusters;
   return n;
 }
+// Plane layout of the operands of an fp32 layer (see BwdTcParams); all-zero = bf16 operands.
+struct PlaneSpec {
+  int products = 1;
+  uint8_t pa[8] = {0}, pb[8] = {0};
+  int a_planes = 1;           // planes in the A tensor (all tiles)
+  int b_planes = 1;
+  int a_planes_per_tile = 0;
+  int f32_out = 0;
+  const float* c_scale_ir = nullptr;
+  float inp_res = 0.0f;
+};
+
 static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint32_t* keep_mask,
                          int mask_words, int M, int K, int N, const TileTable& tt, int pairing, void* c_out,
-                         cudaStream_t s) {
+                         cudaStream_t s, const PlaneSpec& spec = PlaneSpec()) {
   int w = 0;
   if (!uniform_tiles(tt, &w) || !aligned16(g) || !aligned16(b_op) || !aligned16(c_out)) {
     set_error("bwd_tc: operands must be 16-byte aligned with equally wide tiles");
     return AL_ERR_UNSUPPORTED;
+  }
+  if (spec.products > 1 && keep_mask != nullptr) {
+    set_error("bwd_tc: plane products take their clamp mask folded into the A planes");
+    return AL_ERR_BAD_ARGUMENT;
   }
   BwdTcParams p;
   p.I = wgrad ? N : M;
@@ -725,24 +783,33 @@ static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint
   p.keep_mask = keep_mask;
   p.mask_words = mask_words;
   p.c_out = c_out;
+  p.products = spec.products;
+  for (int q = 0; q < 8; ++q) {
+    p.pa[q] = spec.pa[q];
+    p.pb[q] = spec.pb[q];
+  }
+  p.a_planes_per_tile = spec.a_planes_per_tile;
+  p.f32_out = spec.f32_out;
+  p.c_scale_ir = spec.c_scale_ir;
+  p.inp_res = spec.inp_res;
   int rc = wgrad ? ensure_smem(bwd_tc_kernel<true>, B_SMEM) : ensure_smem(bwd_tc_kernel<false>, B_SMEM);
   if (rc) return rc;
   CUtensorMap map_a, map_b;
   {
-    // g [M,N]: dims innermost first {N, M}
-    uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
-    uint64_t strides[1] = {(uint64_t)N * 2};
-    uint32_t box_k[2] = {BK, BM};   // dgrad: 64 n (reduction) x 128 m
-    uint32_t box_mn[2] = {64, BK};  // wgrad: 64 n (MMA-M) x 64 m (reduction)
-    rc = make_map(&map_a, g, 2, dims, strides, wgrad ? box_mn : box_k);
+    // g [planes][M,N]: dims innermost first {N, M, planes}
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)spec.a_planes};
+    uint64_t strides[2] = {(uint64_t)N * 2, (uint64_t)M * N * 2};
+    uint32_t box_k[3] = {BK, BM, 1};   // dgrad: 64 n (reduction) x 128 m
+    uint32_t box_mn[3] = {64, BK, 1};  // wgrad: 64 n (MMA-M) x 64 m (reduction)
+    rc = make_map(&map_a, g, 3, dims, strides, wgrad ? box_mn : box_k);
     if (rc) return rc;
   }
   {
-    // B operand [L, K] row-major (w_mod [N,K] for dgrad, xq [M,K] for wgrad): {K, L}
-    uint64_t dims[2] = {(uint64_t)K, (uint64_t)p.L};
-    uint64_t strides[1] = {(uint64_t)K * 2};
-    uint32_t box[2] = {64, BK};
-    rc = make_map(&map_b, b_op, 2, dims, strides, box);
+    // B operand [planes][L, K] row-major (w_mod [N,K] for dgrad, xq [M,K] for wgrad): {K, L, planes}
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)p.L, (uint64_t)spec.b_planes};
+    uint64_t strides[2] = {(uint64_t)K * 2, (uint64_t)p.L * K * 2};
+    uint32_t box[3] = {64, BK, 1};
+    rc = make_map(&map_b, b_op, 3, dims, strides, box);
     if (rc) return rc;
   }
   // CTA pairs (256-row blocks) when they fill the machine; single CTAs for smaller problems
@@ -781,6 +848,48 @@ int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, in
                     int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s) {
   ProfScope prof(AL_K_WGRAD_GEMM, s);
   return launch_bwd_tc(true, g, xq, keep_mask, mask_words, M, K, N, tt, pairing, grad_w, s);
+}
+
+// fp32 layers.  g_planes: [sets][3][M][N] bf16 planes of the (masked) upstream gradient, sets = T when
+// they were prepared per analog tile and 1 otherwise; w_planes [3][N][K]; codes16 [M,K] bf16 codes.
+int launch_dgrad_tc_f32(const void* g_planes, int sets, const void* w_planes, int M, int K, int N, const TileTable& tt,
+                        int pairing, void* grad_x, cudaStream_t s) {
+  ProfScope prof(AL_K_DGRAD_GEMM, s);
+  PlaneSpec spec;
+  spec.products = 6;  // every plane product that weighs at least 2^-16 of the leading one
+  const uint8_t pa[6] = {0, 0, 1, 0, 1, 2}, pb[6] = {0, 1, 0, 2, 1, 0};
+  for (int q = 0; q < 6; ++q) {
+    spec.pa[q] = pa[q];
+    spec.pb[q] = pb[q];
+  }
+  spec.a_planes = 3 * sets;
+  spec.b_planes = 3;
+  spec.a_planes_per_tile = sets > 1 ? 3 : 0;
+  spec.f32_out = 1;
+  TileTable one;
+  one.T = 1;
+  one.ends[0] = K;
+  return launch_bwd_tc(false, g_planes, w_planes, nullptr, 0, M, K, N, sets > 1 ? tt : one, pairing, grad_x, s, spec);
+}
+
+// scale_ir: [T] static input ranges whose DAC step multiplies the tile's columns of grad_w (null when
+// the step is already folded into per-tile planes)
+int launch_wgrad_tc_f32(const void* g_planes, int sets, const void* codes16, int M, int K, int N, const TileTable& tt,
+                        const float* scale_ir, float inp_res, int pairing, void* grad_w, cudaStream_t s) {
+  ProfScope prof(AL_K_WGRAD_GEMM, s);
+  PlaneSpec spec;
+  spec.products = 3;  // the codes are exact in one plane
+  for (int q = 0; q < 3; ++q) {
+    spec.pa[q] = (uint8_t)q;
+    spec.pb[q] = 0;
+  }
+  spec.a_planes = 3 * sets;
+  spec.b_planes = 1;
+  spec.a_planes_per_tile = sets > 1 ? 3 : 0;
+  spec.f32_out = 1;
+  spec.c_scale_ir = scale_ir;
+  spec.inp_res = inp_res;
+  return launch_bwd_tc(true, g_planes, codes16, nullptr, 0, M, K, N, tt, pairing, grad_w, s, spec);
 }
 
 int tc_set_wait_limit(unsigned long long ns) {

@@ -22,6 +22,8 @@ struct FwdTcParams {
   int32_t tile_w;      // width of every analog tile (all equal on this path)
   int32_t ksteps;      // ceil(tile_w / 64)
   int32_t num_mb, num_nb;
+  int32_t planes_b;    // bf16 planes of the weights (3 for an fp32 layer, else 1): accumulated per analog tile
+  float inp_res;       // fp32 layers: the A operand holds integer DAC codes, the accumulator is scaled by the DAC step
   FwdEpilogueParams ep;
   NoiseKeys noise;     // output-noise stream of this call, prepared on the host
   void* out;
@@ -42,7 +44,12 @@ struct FwdTcParams {
 // `full` collects both CTAs' copies in the leader, `empty` and `acc_full` are signalled in both
 // CTAs by the leader's multicast commits, `acc_empty` collects both CTAs' epilogue warps in the
 // leader.
-template <int RD, int MODE, bool PAIR>
+//
+// IO: element type of the layer's tensors (input ranges, bias, replayed noise, per-channel scales,
+// outputs).  IO = fp32: the A operand holds the DAC codes as bf16 integers and the weights come as
+// three bf16 planes (fourth dimension of their tensor map) that are accumulated one after the other;
+// the output stage multiplies the accumulator by the DAC step of its (row, tile) first.
+template <int RD, int MODE, bool PAIR, int IO = kBF16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
               const FwdTcParams p) {
@@ -101,7 +108,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       for (int tile = worker; tile < num_tiles && ok; tile += n_workers) {
         const int mb = tile / p.num_nb, nb = tile % p.num_nb;
         for (int t = 0; t < T && ok; ++t) {
-          for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
+          const int steps = p.ksteps * p.planes_b;
+          for (int st = 0; st < steps; ++st, ++it) {
+            const int ks = st % p.ksteps, plane = st / p.ksteps;
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
             if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag AL_POLL_ROLE(0))) {
@@ -119,7 +128,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             } else {
               mbar_expect_tx(&bars->full[s], kStageBytes);
               tma_load_3d(sa, &map_a, &bars->full[s], ks * BK, t, mb * BM);
-              tma_load_3d(sa + F_A_BYTES, &map_b, &bars->full[s], ks * BK, t, nb * F_BN);
+              if (IO == kF32) tma_load_4d(sa + F_A_BYTES, &map_b, &bars->full[s], ks * BK, t, nb * F_BN, plane);
+              else tma_load_3d(sa + F_A_BYTES, &map_b, &bars->full[s], ks * BK, t, nb * F_BN);
             }
           }
         }
@@ -159,7 +169,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(b * kBN);
-          for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
+          const int steps = p.ksteps * p.planes_b;
+          for (int ks = 0; ks < steps; ++ks, ++it) {
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
             if (!mbar_wait(&bars->full[s], ph, abort_flag AL_POLL_ROLE(2))) {
@@ -236,10 +247,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         // accumulator, so that the load latency and the division overlap the tile's MMAs
         float ir = 0.0f;
         if (row_ok) {
-          if (ep.ir_mode == AL_IR_DYNAMIC) ir = Elem<kBF16>::load(ep.ir_rows, (int64_t)t * M + m);
-          else if (ep.ir_mode == AL_IR_STATIC) ir = Elem<kBF16>::load(ep.ir_rows, t);
+          if (ep.ir_mode == AL_IR_DYNAMIC) ir = Elem<IO>::load(ep.ir_rows, (int64_t)t * M + m);
+          else if (ep.ir_mode == AL_IR_STATIC) ir = Elem<IO>::load(ep.ir_rows, t);
         }
         const float t_max = ep.w_tile_max ? ep.w_tile_max[t] : 0.0f;
+        // fp32 layers: accumulator = sum of code * weight; the DAC step turns it into the tile's product
+        const float dac_step = IO == kF32 ? quant_step<kF32>(ir, p.inp_res) : 1.0f;
         float sc = rnd<RD>(fmul(t_max, rnd<RD>(fmul(ep.noise_coef, ir))));
         bool noise_now = has_noise;
         if (kMergedNoise) {
@@ -306,6 +319,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             }
           }
           tmem_wait_ld();
+          if (IO == kF32) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) accr[j] = __float_as_uint(fmul(__uint_as_float(accr[j]), dac_step));
+          }
           if constexpr (kFixed) {
             // ---- output stage fixed at compile time: everything in packed bf16 arithmetic --------
             if (t == 0) {
@@ -346,12 +363,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
               const int nq = nh + g8 * 8;
               if (replay) {
                 const uint64_t idx = ((uint64_t)t * M + (row_ok ? m : 0)) * N + (nq < N ? nq : 0);
-                const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(ep.out_noise) + idx);
-                const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+                if (IO == kF32) {
+                  const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(ep.out_noise) + idx);
+                  const float4 lo4 = src[0], hi4 = src[1];
+                  z[g8 * 8 + 0] = lo4.x; z[g8 * 8 + 1] = lo4.y; z[g8 * 8 + 2] = lo4.z; z[g8 * 8 + 3] = lo4.w;
+                  z[g8 * 8 + 4] = hi4.x; z[g8 * 8 + 5] = hi4.y; z[g8 * 8 + 6] = hi4.z; z[g8 * 8 + 7] = hi4.w;
+                } else {
+                  const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(ep.out_noise) + idx);
+                  const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  z[g8 * 8 + 2 * q] = __uint_as_float(rw[q] << 16);
-                  z[g8 * 8 + 2 * q + 1] = __uint_as_float(rw[q] & 0xffff0000u);
+                  for (int q = 0; q < 4; ++q) {
+                    z[g8 * 8 + 2 * q] = __uint_as_float(rw[q] << 16);
+                    z[g8 * 8 + 2 * q + 1] = __uint_as_float(rw[q] & 0xffff0000u);
+                  }
                 }
               } else {
                 normal8_keyed(p.noise, row_group8 + (uint32_t)((nq < N ? nq : 0) >> 3), &z[g8 * 8]);
@@ -427,7 +451,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int n = nh + j;
-              const float cmax = n < N ? Elem<kBF16>::load(ep.w_amax, (int64_t)t * N + n) : 0.0f;
+              const float cmax = n < N ? Elem<IO>::load(ep.w_amax, (int64_t)t * N + n) : 0.0f;
               bool keep;
               const float o = tile_epilogue<RD>(__uint_as_float(accr[j]), ir, ep.noise_pc ? cmax : t_max,
                                                 ep.bound_pc ? cmax : t_max, has_noise ? rnd<RD>(z[j]) : 0.0f,
@@ -449,6 +473,21 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
               tmem_st8(tmem_base + lane_base + (uint32_t)(2 * F_BN + (cc >> 1)), sumr);
             } else {
               tmem_st16(tmem_base + lane_base + (uint32_t)(2 * F_BN + cc), sumr);
+            }
+          } else if (row_ok && IO == kF32) {
+            // final (fp32 layer): bias, store 16 floats of this row
+            float* dst = reinterpret_cast<float*>(p.out) + (int64_t)m * N + nh;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (nh + v * 4 < N) {
+                float f[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  f[e] = __uint_as_float(sumr[v * 4 + e]);
+                  if (ep.bias) f[e] = fadd(f[e], Elem<kF32>::load(ep.bias, nh + v * 4 + e));
+                }
+                *reinterpret_cast<float4*>(dst + v * 4) = make_float4(f[0], f[1], f[2], f[3]);
+              }
             }
           } else if (row_ok) {
             // final: bias, convert, store 16 bf16 = 32 bytes of this row
@@ -567,6 +606,8 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
   p.ep = ep;
   p.noise = make_noise_keys(ep.seed, ep.offset, 1u);
   p.out = out;
+  p.planes_b = 1;
+  p.inp_res = 0.0f;
   {
     // |o| <= tile_w * ir * wmax * (1 + noise) and step = 2 * out_bound * ir * wmax / states
     double states = ep.out_res > 1.0f ? ep.out_res : (ep.out_res > 0.0f ? 1.0 / ep.out_res : 1.0);
@@ -632,6 +673,60 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
   int grid = tiles < sm_count() ? tiles : sm_count();
   kernel<<<grid, kFwdThreads, F_SMEM, s>>>(map_a, map_b, p);
   return check_launch("fwd_tc");
+}
+
+// fp32 with the DAC on and integer codes of at most 9 bits (exact in bf16), tiles as for bf16
+bool tc_f32_supported(const AlDesc& d, const TileTable& tt) {
+  if (d.dtype != AL_F32 || !tc_tiling_ok(d, tt)) return false;
+  if (d.ir_mode == AL_IR_OFF || !(d.inp_res > 0) || d.no_rounding) return false;
+  const double states = d.inp_res > 1.0 ? d.inp_res : 1.0 / d.inp_res;
+  return states <= 510.0;
+}
+
+// Forward of an fp32 layer on the tensor cores: A = DAC codes as bf16 [M,K], B = three bf16 planes of the
+// modified weights [3][N][K]; single CTAs (128 x 128 blocks, fp32 running sum in tensor memory), every
+// output-stage switch read at run time.
+int launch_fwd_tc_f32(const void* codes16, const void* w_planes, int K, const TileTable& tt,
+                      const FwdEpilogueParams& ep, float inp_res, void* out, cudaStream_t s) {
+  ProfScope prof(AL_K_FWD_GEMM, s);
+  int w = 0;
+  if (!uniform_tiles(tt, &w) || !aligned16(codes16) || !aligned16(w_planes) || !aligned16(out)) {
+    set_error("fwd_tc_f32: operands must be 16-byte aligned with equally wide tiles");
+    return AL_ERR_UNSUPPORTED;
+  }
+  FwdTcParams p;
+  p.tile_w = w;
+  p.ksteps = (w + BK - 1) / BK;
+  p.num_mb = (ep.M + BM - 1) / BM;
+  p.num_nb = (ep.N + F_BN - 1) / F_BN;
+  p.ep = ep;
+  p.noise = make_noise_keys(ep.seed, ep.offset, 1u);
+  p.out = out;
+  p.planes_b = 3;
+  p.inp_res = inp_res;
+  p.small_adc_codes = 0;  // fp32 accumulators: guarded rint
+  auto kernel = fwd_tc_kernel<kF32, -1, false, kF32>;
+  int rc = ensure_smem(kernel, F_SMEM);
+  if (rc) return rc;
+  CUtensorMap map_a, map_b;
+  {
+    uint64_t dims[3] = {(uint64_t)w, (uint64_t)tt.T, (uint64_t)ep.M};
+    uint64_t strides[2] = {(uint64_t)w * 2, (uint64_t)K * 2};
+    uint32_t box[3] = {BK, 1, BM};
+    rc = make_map(&map_a, codes16, 3, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)w, (uint64_t)tt.T, (uint64_t)ep.N, 3};
+    uint64_t strides[3] = {(uint64_t)w * 2, (uint64_t)K * 2, (uint64_t)ep.N * K * 2};
+    uint32_t box[4] = {BK, 1, F_BN, 1};
+    rc = make_map(&map_b, w_planes, 4, dims, strides, box);
+    if (rc) return rc;
+  }
+  const int tiles = p.num_mb * p.num_nb;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kernel<<<grid, kFwdThreads, F_SMEM, s>>>(map_a, map_b, p);
+  return check_launch("fwd_tc_f32");
 }
 
 cudaError_t tc_fwd_take_error_word(uint32_t* code) { return take_error_word(code); }

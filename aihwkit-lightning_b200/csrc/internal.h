@@ -88,9 +88,19 @@ int launch_clip_weights(int dtype, void* w, int rows, int cols, int clip_type, f
                         float* scratch, cudaStream_t s);
 
 // ---- operand pre-passes (prepass_kernels.cu) ----------------------------------------------
+// codes16 (fp32 layers only, nullable): the integer DAC codes as bf16 [M,K], the A operand of the
+// tensor-core GEMMs of an fp32 layer
 int launch_dac(int dtype, const void* x, int M, int K, const TileTable& tt, int ir_mode,
                const void* ir_static, float inp_res, int no_rounding, void* xq, void* ir_rows,
-               void* codes, cudaStream_t s);
+               void* codes, cudaStream_t s, void* codes16 = nullptr);
+
+// ---- bf16 planes of fp32 operands (split_kernels.cu) ----------------------------------------
+// planes [3][count] bf16 with planes[0] + planes[1] + planes[2] = src (count % 4 == 0)
+int launch_split3(const float* src, int64_t count, void* planes, cudaStream_t s);
+// planes [sets][3][M][N] of g * keep_t * step(row, tile t): keep_mask null = nothing masked (sets may
+// then be 1), ir null = no scaling; ir_per_row: ir is [T,M] (dynamic ranges), else [T]
+int launch_split3_grad(const float* g, int M, int N, const uint32_t* keep_mask, int mask_words, const float* ir,
+                       int ir_per_row, float inp_res, int sets, void* planes, cudaStream_t s);
 int launch_weight_modify(int dtype, const void* w, int N, int K, const TileTable& tt,
                          const void* w_amax, const float* tile_max, const int32_t* flags,
                          int quant_type, float n_states, float max_state, int noise_type,
@@ -152,6 +162,14 @@ int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask,
                     int M, int K, int N, const TileTable& tt, int pairing, void* grad_x, cudaStream_t s);
 int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, int mask_words,
                     int M, int K, int N, const TileTable& tt, int pairing, void* grad_w, cudaStream_t s);
+// fp32 layers on the tensor cores: operands as bf16 planes (split_kernels.cu)
+bool tc_f32_supported(const AlDesc& d, const TileTable& tt);
+int launch_fwd_tc_f32(const void* codes16, const void* w_planes, int K, const TileTable& tt,
+                      const FwdEpilogueParams& ep, float inp_res, void* out, cudaStream_t s);
+int launch_dgrad_tc_f32(const void* g_planes, int sets, const void* w_planes, int M, int K, int N, const TileTable& tt,
+                        int pairing, void* grad_x, cudaStream_t s);
+int launch_wgrad_tc_f32(const void* g_planes, int sets, const void* codes16, int M, int K, int N, const TileTable& tt,
+                        const float* scale_ir, float inp_res, int pairing, void* grad_w, cudaStream_t s);
 int tc_read_device_error(cudaStream_t s, uint32_t* code);
 // limit of the device-side waits of all tcgen05 kernels (both translation units)
 int tc_set_wait_limit(unsigned long long ns);

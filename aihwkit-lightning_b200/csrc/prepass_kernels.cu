@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 dac_kernel(const void* __restrict__ x, int M, int K, TileTable tt, int ir_mode,
            const void* __restrict__ ir_static, float inp_res, int no_rounding,
            void* __restrict__ xq, void* __restrict__ ir_rows, void* __restrict__ codes,
-           int aligned_base, int small_codes) {
+           uint16_t* __restrict__ codes16, int aligned_base, int small_codes) {
   constexpr int VN = Pack<DT>::N;
   constexpr int ES = 16 / VN;
   const unsigned seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);  // rows * T < 2^31 (checked by the host)
@@ -135,6 +135,7 @@ dac_kernel(const void* __restrict__ x, int M, int K, TileTable tt, int ir_mode,
     float c;
     Elem<DT>::store(xq, start + i, dac_apply<DT>(q, Elem<DT>::load(x, start + i), &c));
     if (codes) Elem<DT>::store(codes, start + i, c);
+    if (codes16) codes16[start + i] = f32_to_bf16_bits(c);  // small integers: exact
   }
   const char* src = reinterpret_cast<const char*>(x) + (start + p.head) * ES;
   char* dst = reinterpret_cast<char*>(xq) + (start + p.head) * ES;
@@ -165,15 +166,22 @@ dac_kernel(const void* __restrict__ x, int M, int K, TileTable tt, int ir_mode,
     }
   } else {
     for (int v = lane; v < p.nvec; v += 32) {
-      float a[VN];
+      float a[VN], c[VN];
       Pack<DT>::load(src + (int64_t)v * 16, a);
 #pragma unroll
-      for (int i = 0; i < VN; ++i) a[i] = dac_apply<DT>(q, a[i], nullptr);
+      for (int i = 0; i < VN; ++i) a[i] = dac_apply<DT>(q, a[i], &c[i]);
       Pack<DT>::store(dst + (int64_t)v * 16, a);
+      if (codes16 != nullptr) {
+#pragma unroll
+        for (int i = 0; i < VN; ++i) codes16[start + p.head + (int64_t)v * VN + i] = f32_to_bf16_bits(c[i]);
+      }
     }
   }
-  for (int i = p.done + lane; i < len; i += 32)
-    Elem<DT>::store(xq, start + i, dac_apply<DT>(q, Elem<DT>::load(x, start + i), nullptr));
+  for (int i = p.done + lane; i < len; i += 32) {
+    float c;
+    Elem<DT>::store(xq, start + i, dac_apply<DT>(q, Elem<DT>::load(x, start + i), &c));
+    if (codes16) codes16[start + i] = f32_to_bf16_bits(c);
+  }
 }
 
 // w_mod[n, tile] = noise(discretise(w[n, tile]))
@@ -498,7 +506,7 @@ int batched_q(const TileTable& tt, int K) {
 
 int launch_dac(int dtype, const void* x, int M, int K, const TileTable& tt, int ir_mode,
                const void* ir_static, float inp_res, int no_rounding, void* xq, void* ir_rows,
-               void* codes, cudaStream_t s) {
+               void* codes, cudaStream_t s, void* codes16) {
   ProfScope prof(AL_K_DAC, s);
   int64_t segs = (int64_t)M * tt.T;
   int aligned = aligned16(x) && aligned16(xq);
@@ -523,9 +531,9 @@ int launch_dac(int dtype, const void* x, int M, int K, const TileTable& tt, int 
     return check_launch("dac_batched");
   }
   if (dtype == AL_F32)
-    dac_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(x, M, K, tt, ir_mode, ir_static, inp_res, no_rounding, xq, ir_rows, codes, aligned, small_codes);
+    dac_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(x, M, K, tt, ir_mode, ir_static, inp_res, no_rounding, xq, ir_rows, codes, static_cast<uint16_t*>(codes16), aligned, small_codes);
   else
-    dac_kernel<kBF16><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(x, M, K, tt, ir_mode, ir_static, inp_res, no_rounding, xq, ir_rows, codes, aligned, small_codes);
+    dac_kernel<kBF16><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(x, M, K, tt, ir_mode, ir_static, inp_res, no_rounding, xq, ir_rows, codes, nullptr, aligned, small_codes);
   return check_launch("dac");
 }
 

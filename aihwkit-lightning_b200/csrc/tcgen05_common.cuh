@@ -170,6 +170,13 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 // tensor memory
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
@@ -497,14 +504,14 @@ struct PairLaunch {
   }
 };
 
-// bf16, all analog tiles equally wide, every row pitch and tile offset a multiple of 16 bytes
-bool tc_shape_ok(const AlDesc& d, const TileTable& tt) {
+// all analog tiles equally wide, every row pitch and tile offset of the bf16 operands a multiple of 16 bytes
+bool tc_tiling_ok(const AlDesc& d, const TileTable& tt) {
   int w = 0;
-  if (d.dtype != AL_BF16) return false;
   if (!uniform_tiles(tt, &w)) return false;
   if (w % 8 != 0 || d.K % 8 != 0 || d.N % 8 != 0) return false;
   return true;
 }
+bool tc_shape_ok(const AlDesc& d, const TileTable& tt) { return d.dtype == AL_BF16 && tc_tiling_ok(d, tt); }
 
 // Sets this translation unit's limit of the device-side waits.
 cudaError_t set_wait_limit(unsigned long long ns) {

@@ -134,6 +134,10 @@ typedef struct AlForwardArgs {
                                  call with M <= 16 rows that modifies no weights and prepares
                                  no backward stream the weights once (abs-max and tile
                                  products from the same read)                               */
+  /* fp32 layers on the tensor cores (al_uses_tcgen05): workspace for the bf16 operands of the GEMMs,
+   * both nullable (the layer then runs on the CUDA cores) */
+  void* codes16;             /* [M,K] bf16: the integer DAC codes                           */
+  void* w_planes;            /* [3,N,K] bf16: three planes whose sum is w_mod               */
   /* shared-noise parity mode: standard normals to use instead of the internal generator */
   const void* w_noise;       /* [N,K] dtype, nullable                                       */
   const void* out_noise;     /* [T,M,N] dtype, nullable                                     */
@@ -157,6 +161,13 @@ typedef struct AlBackwardArgs {
   float* reduce_scratch;     /* >= al_backward_scratch_floats(M,K,N,T) floats               */
   int64_t reduce_scratch_floats; /* floats the caller's reduce_scratch holds; a call that would need
                                  more than that is refused before anything is launched     */
+  /* fp32 layers on the tensor cores: codes16 and w_planes as written by the forward, g_planes a
+   * workspace of g_planes_elems >= al_backward_plane_elems(desc) bf16 elements; all null / 0 when
+   * the forward ran on the CUDA cores */
+  const void* codes16;
+  const void* w_planes;
+  void* g_planes;
+  int64_t g_planes_elems;
   /* clip type LEARNABLE_PER_CHANNEL (`quant_utils.py:125-151`): grad_w becomes the gradient of
    * the unclipped weights and grad_weight_clip that of the learned ranges; null otherwise */
   const void* w;             /* [N,K] dtype weights of the forward                          */
@@ -211,6 +222,10 @@ int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T);
  * split, splits * N * K floats of reduce_scratch (behind the reductions) hold the partial sums.  A
  * function of the layer's sizes alone: the same whether or not the call carries a clamp mask. */
 int al_wgrad_split_plan(int32_t M, int32_t K, int32_t N, int32_t T, int32_t* splits, int32_t* rows_per_split);
+/* bf16 elements of AlBackwardArgs.g_planes for an fp32 layer on the tensor cores: the upstream
+ * gradient as three bf16 planes, per analog tile when the ADC clamp mask or a per-row DAC step has
+ * to be folded in.  tile_ends_host as in the forward.  0 when the layer runs on the CUDA cores. */
+int64_t al_backward_plane_elems(const AlDesc* desc, const int32_t* tile_ends_host);
 /* floats of AlForwardArgs.smallm_scratch; 0 when the problem has more than 16 rows */
 int64_t al_smallm_scratch_floats(int32_t M, int32_t N, int32_t T);
 

@@ -200,8 +200,11 @@ def test_output_noise_without_adc_is_one_gaussian_per_output(engine, k, tile):
     from util import NS
 
     case = dict(C.DEFAULTS)
-    # T4: a small layer; T6 / T16: the tilings of the decoder configuration (K = 3072 and 8192 in tiles of 512)
-    case.update(ir_dynamic=True, out_noise=0.1, max_input_size=tile, inp_res=254.0)
+    # T4: a small layer; T6 / T16: the tilings of the decoder configuration (K = 3072 and 8192 in tiles of 512).
+    # The wide layers have small weights (1 / sqrt(K)): their noise level is raised so that the noise stays
+    # well above the bf16 rounding step of the outputs, which would otherwise show up in the statistics.
+    out_noise = 0.1 if k == 512 else 1.0
+    case.update(ir_dynamic=True, out_noise=out_noise, max_input_size=tile, inp_res=254.0)
     rpu = C.build_rpu_config(NS, case)
     torch.manual_seed(0)
     n, m, t_count = 512, 512, k // tile
@@ -219,7 +222,7 @@ def test_output_noise_without_adc_is_one_gaussian_per_output(engine, k, tile):
     for t in range(t_count):
         wmax = w[:, tile * t:tile * (t + 1)].abs().max()
         ir = xs[:, tile * t:tile * (t + 1)].abs().amax(1)
-        var += (wmax * 0.1 / math.sqrt(t_count) * ir) ** 2
+        var += (wmax * out_noise / math.sqrt(t_count) * ir) ** 2
     z1 = (noisy1 - clean).cpu() / var.sqrt()[:, None]
     z2 = (noisy2 - clean).cpu() / var.sqrt()[:, None]
     assert abs(z1.mean().item()) < 0.02
