@@ -78,6 +78,7 @@ SYMBOLS = {
     "al_backward_scratch_floats": (c_int64, [c_int32, c_int32, c_int32, c_int32]),
     "al_smallm_scratch_floats": (c_int64, [c_int32, c_int32, c_int32]),
     "al_backward_plane_elems": (c_int64, [POINTER(AlDesc), POINTER(c_int32)]),
+    "al_f32_planes": (c_int32, []),
     "al_clip_weights": (c_int32, [c_int32, c_void_p, c_int32, c_int32, c_int32, c_float, c_void_p, c_void_p]),
     "al_unfold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
     "al_fold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),

@@ -279,7 +279,7 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
             if few_rows:
                 plan.append(("smallm_scratch", lib.al_smallm_scratch_floats(m, n, t) * 4))
             if planes:
-                plan += [("codes16", m * k * 2), ("w_planes", 3 * n * k * 2)]
+                plan += [("codes16", m * k * 2), ("w_planes", lib.al_f32_planes() * n * k * 2)]
             total = 0
             for _, nbytes in plan:
                 total += (nbytes + 255) & ~255
@@ -312,7 +312,7 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
             args.smallm_scratch = _ptr(smallm_scratch)
             if planes:
                 codes16 = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
-                w_planes = torch.empty(3, n, k, device=dev, dtype=torch.bfloat16)
+                w_planes = torch.empty(lib.al_f32_planes(), n, k, device=dev, dtype=torch.bfloat16)
                 args.codes16, args.w_planes = _ptr(codes16), _ptr(w_planes)
         std_shared = None
         if need_std and desc.ir_mode == _lib.AL_IR_STATIC and settings.sync_tile_std is not None:

@@ -226,6 +226,8 @@ int al_std_tiles(int32_t dtype, const void* a, int32_t rows, int32_t K,
   return launch_std_tiles(dtype, a, rows, K, tt, out, scratch, (cudaStream_t)stream);
 }
 
+int32_t al_f32_planes(void) { return kPlanes; }
+
 int al_uses_tcgen05(const AlDesc* desc, const int32_t* tile_ends_host) {
   if (!desc) return 0;
   TileTable tt;
@@ -240,7 +242,7 @@ int64_t al_backward_plane_elems(const AlDesc* desc, const int32_t* tile_ends_hos
   const int64_t plane = (int64_t)desc->M * desc->N;
   const int64_t sets_d = desc->out_bound > 0 ? desc->T : 1;                    // masked: one set per tile
   const int64_t sets_w = desc->ir_mode == AL_IR_DYNAMIC ? desc->T : 0;          // per-row DAC steps folded in
-  return 3 * plane * (sets_d + sets_w);
+  return kPlanes * plane * (sets_d + sets_w);
 }
 
 int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
@@ -431,7 +433,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
   ep.seed = a->seed; ep.offset = a->offset;
 
   if (tc_f32) {
-    rc = launch_split3(static_cast<const float*>(w_mod), (int64_t)d.N * d.K, a->w_planes, s);
+    rc = launch_split_planes(static_cast<const float*>(w_mod), (int64_t)d.N * d.K, a->w_planes, s);
     if (rc) return rc;
     return launch_fwd_tc_f32(a->codes16, a->w_planes, d.K, tt, ep, dv.inp_res, a->out, s);
   }
@@ -514,7 +516,7 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
   // fp32 layer whose forward ran on the tensor cores: bf16 planes of the upstream gradient
   const bool tc_f32 = pick_tc_f32(d, tt) && a->codes16 != nullptr && a->w_planes != nullptr && a->g_planes != nullptr;
   const int sets_d = mask ? d.T : 1;
-  const int64_t plane_elems = 3 * (int64_t)d.M * d.N;
+  const int64_t plane_elems = kPlanes * (int64_t)d.M * d.N;
   if (tc_f32 && a->g_planes_elems < al_backward_plane_elems(desc, a->tile_ends)) {
     set_error("al_backward: g_planes holds %lld elements, al_backward_plane_elems asks for %lld",
               (long long)a->g_planes_elems, (long long)al_backward_plane_elems(desc, a->tile_ends));
@@ -528,7 +530,7 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
   if (tc_f32 && (a->grad_x || a->grad_w)) {
     // planes of g (masked per tile when the ADC clamped), shared by the input gradient and -- with
     // one input range per tile -- by the weight gradient
-    rc = launch_split3_grad(static_cast<const float*>(a->grad_out), d.M, d.N, mask, mask_words, nullptr, 0, 0.0f,
+    rc = launch_split_planes_grad(static_cast<const float*>(a->grad_out), d.M, d.N, mask, mask_words, nullptr, 0, 0.0f,
                             sets_d, a->g_planes, s);
     if (rc) return rc;
   }
@@ -560,7 +562,7 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
     if (d.ir_mode == AL_IR_DYNAMIC) {
       // per-row DAC steps: a second set of planes, one per tile, with the step (and the mask) folded in
       uint16_t* planes_w = static_cast<uint16_t*>(a->g_planes) + plane_elems * sets_d;
-      rc = launch_split3_grad(static_cast<const float*>(a->grad_out), d.M, d.N, mask, mask_words,
+      rc = launch_split_planes_grad(static_cast<const float*>(a->grad_out), d.M, d.N, mask, mask_words,
                               static_cast<const float*>(a->ir_rows), 1, dv.inp_res, d.T, planes_w, s);
       if (rc) return rc;
       rc = launch_wgrad_tc_f32(planes_w, d.T, a->codes16, d.M, d.K, d.N, tt, nullptr, 0.0f, pairing, a->grad_w, s);

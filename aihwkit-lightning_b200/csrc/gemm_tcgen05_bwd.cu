@@ -850,21 +850,25 @@ int launch_wgrad_tc(const void* g, const void* xq, const uint32_t* keep_mask, in
   return launch_bwd_tc(true, g, xq, keep_mask, mask_words, M, K, N, tt, pairing, grad_w, s);
 }
 
-// fp32 layers.  g_planes: [sets][3][M][N] bf16 planes of the (masked) upstream gradient, sets = T when
-// they were prepared per analog tile and 1 otherwise; w_planes [3][N][K]; codes16 [M,K] bf16 codes.
+// fp32 layers.  g_planes: [sets][kPlanes][M][N] bf16 planes of the (masked) upstream gradient, sets = T
+// when they were prepared per analog tile and 1 otherwise; w_planes [kPlanes][N][K]; codes16 [M,K] bf16 codes.
 int launch_dgrad_tc_f32(const void* g_planes, int sets, const void* w_planes, int M, int K, int N, const TileTable& tt,
                         int pairing, void* grad_x, cudaStream_t s) {
   ProfScope prof(AL_K_DGRAD_GEMM, s);
   PlaneSpec spec;
-  spec.products = 6;  // every plane product that weighs at least 2^-16 of the leading one
-  const uint8_t pa[6] = {0, 0, 1, 0, 1, 2}, pb[6] = {0, 1, 0, 2, 1, 0};
-  for (int q = 0; q < 6; ++q) {
+  // Both operands are fp32 here.  The products of the two leading planes of each -- g0 w0, g0 w1, g1 w0 --
+  // leave a relative error of about 3e-6 (what the third planes and g1 w1 would add is below 2^-17 of the
+  // result), inside the 1e-5 bar of fp32 layers at half the work of the six products down to 2^-16.
+  spec.products = 3;
+  const uint8_t pa[3] = {0, 0, 1}, pb[3] = {0, 1, 0};
+  for (int q = 0; q < 3; ++q) {
     spec.pa[q] = pa[q];
     spec.pb[q] = pb[q];
   }
-  spec.a_planes = 3 * sets;
-  spec.b_planes = 3;
-  spec.a_planes_per_tile = sets > 1 ? 3 : 0;
+  static_assert(kPlanes >= 2, "the three products below read two planes of each operand");
+  spec.a_planes = kPlanes * sets;
+  spec.b_planes = kPlanes;
+  spec.a_planes_per_tile = sets > 1 ? kPlanes : 0;
   spec.f32_out = 1;
   TileTable one;
   one.T = 1;
@@ -878,14 +882,14 @@ int launch_wgrad_tc_f32(const void* g_planes, int sets, const void* codes16, int
                         const float* scale_ir, float inp_res, int pairing, void* grad_w, cudaStream_t s) {
   ProfScope prof(AL_K_WGRAD_GEMM, s);
   PlaneSpec spec;
-  spec.products = 3;  // the codes are exact in one plane
-  for (int q = 0; q < 3; ++q) {
+  spec.products = kPlanes;  // the codes are exact in one plane
+  for (int q = 0; q < kPlanes; ++q) {
     spec.pa[q] = (uint8_t)q;
     spec.pb[q] = 0;
   }
-  spec.a_planes = 3 * sets;
+  spec.a_planes = kPlanes * sets;
   spec.b_planes = 1;
-  spec.a_planes_per_tile = sets > 1 ? 3 : 0;
+  spec.a_planes_per_tile = sets > 1 ? kPlanes : 0;
   spec.f32_out = 1;
   spec.c_scale_ir = scale_ir;
   spec.inp_res = inp_res;

@@ -22,7 +22,7 @@ struct FwdTcParams {
   int32_t tile_w;      // width of every analog tile (all equal on this path)
   int32_t ksteps;      // ceil(tile_w / 64)
   int32_t num_mb, num_nb;
-  int32_t planes_b;    // bf16 planes of the weights (3 for an fp32 layer, else 1): accumulated per analog tile
+  int32_t planes_b;    // bf16 planes of the weights (kPlanes for an fp32 layer, else 1): accumulated per analog tile
   float inp_res;       // fp32 layers: the A operand holds integer DAC codes, the accumulator is scaled by the DAC step
   FwdEpilogueParams ep;
   NoiseKeys noise;     // output-noise stream of this call, prepared on the host
@@ -47,7 +47,7 @@ struct FwdTcParams {
 //
 // IO: element type of the layer's tensors (input ranges, bias, replayed noise, per-channel scales,
 // outputs).  IO = fp32: the A operand holds the DAC codes as bf16 integers and the weights come as
-// three bf16 planes (fourth dimension of their tensor map) that are accumulated one after the other;
+// bf16 planes (fourth dimension of their tensor map) that are accumulated one after the other;
 // the output stage multiplies the accumulator by the DAC step of its (row, tile) first.
 template <int RD, int MODE, bool PAIR, int IO = kBF16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
@@ -683,8 +683,8 @@ bool tc_f32_supported(const AlDesc& d, const TileTable& tt) {
   return states <= 510.0;
 }
 
-// Forward of an fp32 layer on the tensor cores: A = DAC codes as bf16 [M,K], B = three bf16 planes of the
-// modified weights [3][N][K]; single CTAs (128 x 128 blocks, fp32 running sum in tensor memory), every
+// Forward of an fp32 layer on the tensor cores: A = DAC codes as bf16 [M,K], B = the bf16 planes of the
+// modified weights [kPlanes][N][K]; single CTAs (128 x 128 blocks, fp32 running sum in tensor memory), every
 // output-stage switch read at run time.
 int launch_fwd_tc_f32(const void* codes16, const void* w_planes, int K, const TileTable& tt,
                       const FwdEpilogueParams& ep, float inp_res, void* out, cudaStream_t s) {
@@ -702,7 +702,7 @@ int launch_fwd_tc_f32(const void* codes16, const void* w_planes, int K, const Ti
   p.ep = ep;
   p.noise = make_noise_keys(ep.seed, ep.offset, 1u);
   p.out = out;
-  p.planes_b = 3;
+  p.planes_b = kPlanes;
   p.inp_res = inp_res;
   p.small_adc_codes = 0;  // fp32 accumulators: guarded rint
   auto kernel = fwd_tc_kernel<kF32, -1, false, kF32>;
@@ -717,7 +717,7 @@ int launch_fwd_tc_f32(const void* codes16, const void* w_planes, int K, const Ti
     if (rc) return rc;
   }
   {
-    uint64_t dims[4] = {(uint64_t)w, (uint64_t)tt.T, (uint64_t)ep.N, 3};
+    uint64_t dims[4] = {(uint64_t)w, (uint64_t)tt.T, (uint64_t)ep.N, (uint64_t)kPlanes};
     uint64_t strides[3] = {(uint64_t)w * 2, (uint64_t)K * 2, (uint64_t)ep.N * K * 2};
     uint32_t box[4] = {BK, 1, F_BN, 1};
     rc = make_map(&map_b, w_planes, 4, dims, strides, box);

@@ -95,11 +95,16 @@ int launch_dac(int dtype, const void* x, int M, int K, const TileTable& tt, int 
                void* codes, cudaStream_t s, void* codes16 = nullptr);
 
 // ---- bf16 planes of fp32 operands (split_kernels.cu) ----------------------------------------
-// planes [3][count] bf16 with planes[0] + planes[1] + planes[2] = src (count % 4 == 0)
-int launch_split3(const float* src, int64_t count, void* planes, cudaStream_t s);
-// planes [sets][3][M][N] of g * keep_t * step(row, tile t): keep_mask null = nothing masked (sets may
-// then be 1), ir null = no scaling; ir_per_row: ir is [T,M] (dynamic ranges), else [T]
-int launch_split3_grad(const float* g, int M, int N, const uint32_t* keep_mask, int mask_words, const float* ir,
+// An fp32 operand v travels to the tensor cores as kPlanes bf16 planes p0 = RN(v), p1 = RN(v - p0), ...
+// Two planes carry 16 significant bits: the value is off by at most 2^-18 (2.2e-6 rms), which keeps a
+// GEMM inside the 1e-5 relative bar of fp32 layers at two (one exact operand) or three (both split)
+// plane products.
+constexpr int kPlanes = 2;
+// planes [kPlanes][count] bf16 (count % 4 == 0)
+int launch_split_planes(const float* src, int64_t count, void* planes, cudaStream_t s);
+// planes [sets][kPlanes][M][N] of g * keep_t * step(row, tile t): keep_mask null = nothing masked (sets
+// may then be 1), ir null = no scaling; ir_per_row: ir is [T,M] (dynamic ranges), else [T]
+int launch_split_planes_grad(const float* g, int M, int N, const uint32_t* keep_mask, int mask_words, const float* ir,
                        int ir_per_row, float inp_res, int sets, void* planes, cudaStream_t s);
 int launch_weight_modify(int dtype, const void* w, int N, int K, const TileTable& tt,
                          const void* w_amax, const float* tile_max, const int32_t* flags,

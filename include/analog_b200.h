@@ -137,7 +137,8 @@ typedef struct AlForwardArgs {
   /* fp32 layers on the tensor cores (al_uses_tcgen05): workspace for the bf16 operands of the GEMMs,
    * both nullable (the layer then runs on the CUDA cores) */
   void* codes16;             /* [M,K] bf16: the integer DAC codes                           */
-  void* w_planes;            /* [3,N,K] bf16: three planes whose sum is w_mod               */
+  void* w_planes;            /* [al_f32_planes(),N,K] bf16: planes whose sum approximates
+                                 w_mod to 2^-18 relative                                    */
   /* shared-noise parity mode: standard normals to use instead of the internal generator */
   const void* w_noise;       /* [N,K] dtype, nullable                                       */
   const void* out_noise;     /* [T,M,N] dtype, nullable                                     */
@@ -223,9 +224,11 @@ int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T);
  * function of the layer's sizes alone: the same whether or not the call carries a clamp mask. */
 int al_wgrad_split_plan(int32_t M, int32_t K, int32_t N, int32_t T, int32_t* splits, int32_t* rows_per_split);
 /* bf16 elements of AlBackwardArgs.g_planes for an fp32 layer on the tensor cores: the upstream
- * gradient as three bf16 planes, per analog tile when the ADC clamp mask or a per-row DAC step has
+ * gradient as bf16 planes, per analog tile when the ADC clamp mask or a per-row DAC step has
  * to be folded in.  tile_ends_host as in the forward.  0 when the layer runs on the CUDA cores. */
 int64_t al_backward_plane_elems(const AlDesc* desc, const int32_t* tile_ends_host);
+/* Number of bf16 planes an fp32 operand is split into for the tensor cores (first dimension of w_planes). */
+int32_t al_f32_planes(void);
 /* floats of AlForwardArgs.smallm_scratch; 0 when the problem has more than 16 rows */
 int64_t al_smallm_scratch_floats(int32_t M, int32_t N, int32_t T);
 
