@@ -60,6 +60,7 @@ class AlBackwardArgs(Structure):
 
 
 AL_K_COUNT = 14
+AL_PEER_SIGNAL_SLOT = 192
 AL_STD_STATIC_MAX_SEGMENTS = 262144
 
 
@@ -87,6 +88,9 @@ SYMBOLS = {
     "al_debug_withhold_forward_signal": (c_int32, [c_int32]),
     "al_uses_tcgen05": (c_int32, [POINTER(AlDesc), POINTER(c_int32)]),
     "al_reserve_sms": (c_int32, [c_int32]),
+    "al_peer_allreduce": (c_int32, [c_int32, c_int32, c_int32, POINTER(c_uint64), POINTER(c_uint64), c_uint64, c_int64,
+                                    c_int64, c_uint32, c_float, c_int32, c_void_p]),
+    "al_peer_read_error": (c_int32, [POINTER(c_uint32)]),
     "al_wgrad_split_plan": (c_int32, [c_int32, c_int32, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
     "al_profile_enable": (c_int32, [c_int32]),
     "al_profile_read": (c_int32, [POINTER(AlProfileEntry), c_int32]),

@@ -222,3 +222,108 @@ class EagerGradientSync:
         self._pending.clear()
         # an event autograd never claimed belongs to a tensor that is gone; its address may come back
         self._ready.clear()
+
+
+class PeerGradientSync(EagerGradientSync):
+    """``EagerGradientSync`` whose large gradients are summed by the library's own peer-memory kernel
+    (``al_peer_allreduce``) instead of a library collective.
+
+    The weight gradients of the analog layers live in one buffer per dtype that every replica has
+    mapped (PyTorch symmetric memory: NVLink peer mappings and, where the switch offers it, a
+    multicast address).  Installed as ``settings.grad_w_alloc`` the instance makes the backward write
+    each weight gradient straight into its place in that buffer; the moment the layer's
+    weight-gradient kernels are enqueued, a kernel of ``n_ctas`` CTAs on the side stream signals the
+    peers, reduces this rank's slice of the gradient over all replicas (through the switch with
+    ``multimem`` when ``use_multicast``), writes it to every replica and waits for the peers' slices --
+    beside the input-gradient GEMM, which leaves ``comm_sms`` SMs free for it.  Everything else (small
+    gradients, gradients autograd did not leave in the buffer) goes the way of the base class.
+    """
+
+    def __init__(self, params: Iterable[torch.nn.Parameter], group: Optional[dist.ProcessGroup] = None,
+                 average: bool = True, small_numel: int = 1 << 16, n_ctas: int = 16, use_multicast: bool = True):
+        super().__init__(group=group, average=average, small_numel=small_numel)
+        import torch.distributed._symmetric_memory as symm_mem  # pylint: disable=import-outside-toplevel
+
+        from . import _lib  # pylint: disable=import-outside-toplevel
+
+        self._lib = _lib
+        self._peer_pending: list = []
+        self.n_ctas = n_ctas
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self._params = [p for p in params if p.requires_grad]
+        self._slot: dict = {}    # weight address -> (parameter, pool, element offset)
+        self._pools: dict = {}   # dtype -> pool
+        group_obj = group if group is not None else dist.group.WORLD
+        by_dtype: dict = {}
+        for p in self._params:
+            if p.is_cuda and p.numel() >= small_numel and p.dtype in (torch.bfloat16, torch.float32) \
+                    and p.numel() % 8 == 0 and p.dim() == 2:
+                by_dtype.setdefault(p.dtype, []).append(p)
+        for dtype, plist in by_dtype.items():
+            total = sum((p.numel() + 127) // 128 * 128 for p in plist)
+            flat = symm_mem.empty(total, dtype=dtype, device=plist[0].device)
+            handle = symm_mem.rendezvous(flat, group_obj)
+            need = 4 * (_lib.AL_PEER_SIGNAL_SLOT + 9)
+            if handle.signal_pad_size < need:
+                raise RuntimeError(f"signal pads of {handle.signal_pad_size} bytes, {need} needed")
+            import ctypes  # pylint: disable=import-outside-toplevel
+            pool = dict(
+                flat=flat, handle=handle, calls=0,
+                bufs=(ctypes.c_uint64 * self.world)(*[int(a) for a in handle.buffer_ptrs]),
+                pads=(ctypes.c_uint64 * self.world)(*[int(a) for a in handle.signal_pad_ptrs]),
+                mc=int(handle.multicast_ptr) if (use_multicast and handle.has_multicast_support) else 0)
+            self._pools[dtype] = pool
+            offset = 0
+            for p in plist:
+                self._slot[p.data_ptr()] = (p, pool, offset)
+                offset += (p.numel() + 127) // 128 * 128
+        self.attach(self._params)
+
+    def grad_buffer(self, weight_address: int, shape, dtype):
+        """``settings.grad_w_alloc``: the place of this weight's gradient in the shared buffer, as a fresh
+        view (autograd keeps a gradient it alone refers to, and copies one that is referred to twice)."""
+        slot = self._slot.get(weight_address)
+        if slot is None:
+            return None
+        param, pool, offset = slot
+        if param.grad is not None or pool["flat"].dtype != dtype or tuple(param.shape) != tuple(shape):
+            return None  # accumulation into an older gradient: let autograd handle it
+        return pool["flat"][offset:offset + param.numel()].view(param.shape)
+
+    def _reduce(self, param: torch.nn.Parameter) -> None:
+        grad = param.grad
+        slot = self._slot.get(param.data_ptr()) if grad is not None else None
+        if slot is not None:
+            _, pool, offset = slot
+            flat = pool["flat"]
+            if grad.data_ptr() == flat.data_ptr() + offset * flat.element_size() and grad.is_contiguous():
+                self._peer_reduce(grad, pool, offset)
+                return
+        super()._reduce(param)
+
+    def _peer_reduce(self, grad: torch.Tensor, pool: dict, offset: int) -> None:
+        lib = self._lib.load()
+        if self.side is None:
+            self.side = torch.cuda.Stream(grad.device)
+        ready = self._ready.pop((grad.data_ptr(), tuple(grad.shape)), None)
+        if ready is None:
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(grad.device))
+        self.side.wait_event(ready)
+        flat = pool["flat"]
+        dtype_code = self._lib.AL_BF16 if flat.dtype == torch.bfloat16 else self._lib.AL_F32
+        scale = 1.0 / self.world if self.average else 1.0
+        self._lib.check(lib.al_peer_allreduce(dtype_code, self.world, self.rank, pool["bufs"], pool["pads"], pool["mc"],
+                                              offset * flat.element_size(), grad.numel(), pool["calls"], scale,
+                                              self.n_ctas, self.side.cuda_stream))
+        pool["calls"] += 1
+        done = torch.cuda.Event()
+        done.record(self.side)
+        self._peer_pending.append(done)
+
+    def finish(self) -> None:
+        for done in self._peer_pending:
+            torch.cuda.current_stream().wait_event(done)
+        self._peer_pending = []
+        super().finish()

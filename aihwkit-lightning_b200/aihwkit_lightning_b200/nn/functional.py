@@ -52,6 +52,10 @@ class _Settings:
     after_wgrad = None
     # with ``after_wgrad``: SMs the GEMM that runs beside the exchange leaves unoccupied for it
     comm_sms = 0
+    # callable(weight_address, shape, dtype) -> Tensor or None: where the backward writes a layer's weight
+    # gradient (``distributed.PeerGradientSync`` hands out views of a buffer that all replicas have mapped,
+    # so that the exchange kernel can reduce it in place); None: a fresh tensor
+    grad_w_alloc = None
     # callable(std [T] float32 tensor) -> tensor: data-parallel training averages the per-tile standard
     # deviations of the init-from-data phase over the replicas here (``distributed.mean_over_replicas``),
     # so that every replica keeps the same input ranges
@@ -343,6 +347,7 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
             uses_tcgen05=bool(lib.al_uses_tcgen05(desc, ends)),
         )
     ctx.desc, ctx.in_sizes, ctx.dtype = desc, list(in_sizes), dtype
+    ctx.weight_address = weight.data_ptr()
     ctx.shape = tuple(inp.shape)
     ctx.has_bias = bias is not None
     ctx.ir_needs_grad = static and input_range is not None and input_range.requires_grad
@@ -375,7 +380,12 @@ def _analog_backward(ctx, grad_out):
         args.grad_out, args.x, args.xq, args.w_mod = _ptr(g), _ptr(x2d), _ptr(xq), _ptr(w_mod)
         args.ir_rows, args.keep_mask = _ptr(ir_rows), _ptr(keep_mask)
         grad_x = torch.empty(m, k, device=dev, dtype=dtype) if (need_x or need_ir) else None
-        grad_w = torch.empty(n, k, device=dev, dtype=dtype) if need_w else None
+        grad_w = None
+        if need_w:
+            if settings.grad_w_alloc is not None and ctx.needs_input_grad[1] and not need_clip:
+                grad_w = settings.grad_w_alloc(ctx.weight_address, (n, k), dtype)
+            if grad_w is None:
+                grad_w = torch.empty(n, k, device=dev, dtype=dtype)
         grad_b = torch.empty(n, device=dev, dtype=dtype) if need_b else None
         grad_ir = torch.empty(t, device=dev, dtype=dtype) if need_ir else None
         scratch = torch.empty(lib.al_backward_scratch_floats(m, k, n, t), device=dev, dtype=torch.float32)

@@ -24,6 +24,7 @@ SOURCES = [
     "gemm_smallm.cu",
     "backward_kernels.cu",
     "conv_kernels.cu",
+    "peer_kernels.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -283,6 +283,52 @@ class Ctx:
             self.dist.destroy_process_group()
 
 
+def make_gradient_sync(ctx, params, n_ctas=None):
+    """Gradient exchange of the data-parallel arms: the library's peer-memory kernel
+    (``PeerGradientSync``) when the replicas can map one another's memory, NCCL all-reduce otherwise or
+    when BENCH_EXCHANGE=nccl.  Returns (sync, description)."""
+    from aihwkit_lightning_b200.distributed import EagerGradientSync, PeerGradientSync
+    from aihwkit_lightning_b200.nn import functional as F
+
+    params = list(params)
+    sync, how = None, None
+    n_ctas = int(os.environ.get("BENCH_COMM_CTAS", "16")) if n_ctas is None else n_ctas
+    if os.environ.get("BENCH_EXCHANGE", "peer") == "peer":
+        try:
+            sync = PeerGradientSync(params, n_ctas=n_ctas,
+                                    use_multicast=os.environ.get("BENCH_MULTICAST", "0") == "1")
+            F.settings.grad_w_alloc = sync.grad_buffer
+            multicast = any(pool["mc"] for pool in sync._pools.values())  # pylint: disable=protected-access
+            how = (f"library kernel over peer memory ({n_ctas} CTAs beside the input-gradient GEMM, "
+                   f"{'switch reduction (multimem)' if multicast else 'peer loads and stores'}); "
+                   "small gradients in one NCCL call")
+        except Exception as exc:  # pylint: disable=broad-except
+            if ctx.rank == 0:
+                print(f"peer-memory exchange unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
+            sync = None
+    if sync is None:
+        sync = EagerGradientSync().attach(params)
+        how = "NCCL all-reduce per weight matrix on a side stream, small gradients in one flat call"
+    # every rank must have taken the same route
+    flag = torch.tensor([1.0 if isinstance(sync, PeerGradientSync) else 0.0], device=ctx.dev)
+    lo = flag.clone()
+    ctx.dist.all_reduce(lo, op=ctx.dist.ReduceOp.MIN)
+    if lo.item() != flag.item():
+        F.settings.grad_w_alloc = None
+        sync = EagerGradientSync().attach(params)
+        how = "NCCL all-reduce per weight matrix on a side stream (peer mapping failed on a rank)"
+    F.settings.after_wgrad = sync
+    return sync, how
+
+
+def release_gradient_sync():
+    from aihwkit_lightning_b200.nn import functional as F
+
+    F.settings.after_wgrad = None
+    F.settings.grad_w_alloc = None
+    F.settings.comm_sms = 0
+
+
 def timed_steps(ctx, fn, steps, between=None):
     """CUDA-event time (ms) of exactly `steps` calls of fn on the current stream; what `between`
     does before each call (the L2 flush) is not timed."""
@@ -378,7 +424,7 @@ def run_c3(args, ctx, layers=32, steps=3, warmup=2, seq=2048, micro_batch=4):
     from torch.nn import functional as TF
 
     from aihwkit_lightning_b200 import _lib
-    from aihwkit_lightning_b200.distributed import EagerGradientSync, rank_seed
+    from aihwkit_lightning_b200.distributed import rank_seed
     from aihwkit_lightning_b200.nn import AnalogLinear, convert_to_analog
     from aihwkit_lightning_b200.nn import functional as F
     from aihwkit_lightning_b200.optim import AnalogOptimizer
@@ -396,10 +442,9 @@ def run_c3(args, ctx, layers=32, steps=3, warmup=2, seq=2048, micro_batch=4):
     flop = sum(6.0 * tokens * m.in_features * m.out_features for m in analog)
     torch.cuda.manual_seed(rank_seed(0, rank))  # independent analog noise per replica
     opt = AnalogOptimizer(torch.optim.AdamW, model.analog_layers, model.parameters(), lr=1e-5, fused=True)
-    sync = None
+    sync, how = None, None
     if world > 1:
-        sync = EagerGradientSync().attach(model.parameters())
-        F.settings.after_wgrad = sync
+        sync, how = make_gradient_sync(ctx, model.parameters())
     gen = torch.Generator().manual_seed(1000 + rank)
     ids_host = torch.randint(0, vocab, (micro_batch, seq), generator=gen).pin_memory()
     labels_host = torch.randint(0, vocab, (micro_batch, seq), generator=gen).pin_memory()
@@ -459,15 +504,14 @@ def run_c3(args, ctx, layers=32, steps=3, warmup=2, seq=2048, micro_batch=4):
         "analog_kernel_ms_per_step": analog_ms,
         "exposed_exchange_ms": exposed_ms,
         "exchange": None if world == 1 else
-        f"NCCL all-reduce of {grad_bytes / 1e9:.2f} GB of gradients per step, one call per weight matrix issued "
-        "from inside backward on a side stream, small gradients in one flat call at the end",
+        f"{grad_bytes / 1e9:.2f} GB of gradients per step, each weight matrix exchanged from inside backward: {how}",
         "loss": float(losses[-1].item()),
         "replicas_identical": bool((lo == hi).all().item()),
         "gpu_launches": sum(v[0] for v in prof.values()),
         "kernels": kernel_table(prof),
     }
-    F.settings.after_wgrad = None
-    del model, opt, analog
+    release_gradient_sync()
+    del model, opt, analog, sync
     torch.cuda.empty_cache()
     return out
 
@@ -477,7 +521,7 @@ def run_c3(args, ctx, layers=32, steps=3, warmup=2, seq=2048, micro_batch=4):
 # ---------------------------------------------------------------------------------------------
 def run_c2(args, ctx):
     from aihwkit_lightning_b200 import _lib
-    from aihwkit_lightning_b200.distributed import EagerGradientSync, rank_seed
+    from aihwkit_lightning_b200.distributed import PeerGradientSync, rank_seed
     from aihwkit_lightning_b200.nn import AnalogLinear
     from aihwkit_lightning_b200.nn import functional as F
     from aihwkit_lightning_b200.simulator import configs as cfg
@@ -498,12 +542,12 @@ def run_c2(args, ctx):
     # Its all-reduce is issued from a hook inside backward, right after the weight-gradient kernel
     # and before the input-gradient kernel, and is complete when the step ends, as an optimizer
     # step would need it.
-    sync = None
+    sync, how = None, None
     if world > 1:
-        sync = EagerGradientSync().attach(layer.parameters())
-        F.settings.after_wgrad = sync
-        # SMs the input-gradient GEMM leaves to the all-reduce kernel that runs beside it
-        F.settings.comm_sms = int(os.environ.get("BENCH_COMM_SMS", "0"))
+        sync, how = make_gradient_sync(ctx, layer.parameters())
+        # SMs the input-gradient GEMM leaves to the exchange kernel that runs beside it
+        default_sms = "16" if isinstance(sync, PeerGradientSync) else "0"
+        F.settings.comm_sms = int(os.environ.get("BENCH_COMM_SMS", default_sms))
     x_dev = x_host.to(dev).requires_grad_(True)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
@@ -586,9 +630,10 @@ def run_c2(args, ctx):
     uses_tc = bool(lib.al_uses_tcgen05(
         F.make_desc(layer.rpu_config, M, K, N, len(layer.in_sizes), torch.bfloat16, True),
         _lib.tile_ends_array(layer.in_sizes)))
-    F.settings.after_wgrad = None
+    comm_sms = F.settings.comm_sms
+    release_gradient_sync()
     h2d_bytes = x_host.numel() * x_host.element_size()
-    del layer, slots, x_dev, flush, x_host
+    del layer, slots, x_dev, flush, x_host, sync
     torch.cuda.empty_cache()
 
     peaks = load_peaks()
@@ -598,8 +643,9 @@ def run_c2(args, ctx):
     achieved = gemm_flop[dominant] / (d_ms / max(d_timed, 1) * 1e-3) / 1e12 if d_ms > 0 else 0.0
     rec = base_record(args, world)
     if world > 1:
-        rec["config"]["grad_sync"] = ("NCCL all-reduce of the weight gradient, started inside backward after the "
-                                      "weight-gradient kernel, complete at step end")
+        rec["config"]["grad_sync"] = (f"weight gradient (34 MB) summed over the replicas inside backward, after the "
+                                      f"weight-gradient kernel and beside the input-gradient GEMM ({comm_sms} SMs left to "
+                                      f"it), complete at step end: {how}")
     rec.update({
         "value": value,
         "ms_per_step": ms_per_step,

@@ -293,6 +293,31 @@ typedef struct AlProfileEntry {
  * n SMs unoccupied (n = 0 restores the default).  Returns the previous value. */
 int al_reserve_sms(int32_t n);
 
+/* Sum of a gradient buffer over the replicas of data-parallel training, over peer memory (NVLink /
+ * NVSwitch), as one small kernel that runs beside the backward GEMMs.  The reference leaves gradient
+ * exchange to DDP / DeepSpeed around its autograd (P/torch_utils/torch_linear.py:116-314 has no
+ * exchange of its own); this entry point is what a data-parallel caller of this library uses
+ * instead of a library all-reduce.
+ *   buffer_ptrs[r], signal_pad_ptrs[r] (HOST arrays of `world` device addresses): rank r's copy of the
+ *   exchanged buffer and its signal pad, as mapped into this process (symmetric memory: same size and
+ *   layout on every rank; pads zero-initialised, at least 4 * (AL_PEER_SIGNAL_SLOT + 9) bytes, the
+ *   32-bit words from AL_PEER_SIGNAL_SLOT on belong to this library);
+ *   multicast_ptr: multicast address of the buffer (switch reduction, multimem) or 0 for plain peer
+ *   loads and stores;  byte_offset / count: the part of the buffer to reduce (16-byte aligned, count a
+ *   multiple of 8 bf16 / 4 fp32 elements);  call_index: 0, 1, 2, ... -- every rank passes the same
+ *   number for the same exchange and a larger one for each later exchange on these pads;
+ *   scale: factor applied to the sum (1 / world for the mean).
+ * Every rank launches it on its own GPU; the kernels of the ranks signal and wait for one another
+ * through the pads (waits bounded at 4 s: al_peer_read_error).  On return of the kernel the part of
+ * the buffer holds the same bits on every rank.  Exchanges that share pads must not overlap. */
+#define AL_PEER_SIGNAL_SLOT 192
+int al_peer_allreduce(int32_t dtype, int32_t world, int32_t rank, const uint64_t* buffer_ptrs,
+                      const uint64_t* signal_pad_ptrs, uint64_t multicast_ptr, int64_t byte_offset, int64_t count,
+                      uint32_t call_index, float scale, int32_t n_ctas, void* stream);
+/* Reads and clears the error word of al_peer_allreduce (a wait for a peer ran out): AL_ERR_DEVICE_TIMEOUT
+ * if set.  The streams that ran the exchange must be idle. */
+int al_peer_read_error(uint32_t* out_code);
+
 int al_profile_enable(int on);
 int al_profile_read(AlProfileEntry* out, int reset);
 const char* al_kernel_class_name(int kernel_class);
