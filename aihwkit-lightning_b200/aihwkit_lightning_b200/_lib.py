@@ -44,7 +44,7 @@ class AlForwardArgs(Structure):
         ("w_tile_max", c_void_p), ("w_mod", c_void_p), ("keep_mask", c_void_p),
         ("std_scratch", c_void_p), ("std_override", c_void_p), ("smallm_scratch", c_void_p),
         ("codes16", c_void_p), ("w_planes", c_void_p), ("w_noise", c_void_p), ("out_noise", c_void_p),
-        ("codes", c_void_p), ("seed", c_uint64), ("offset", c_uint64),
+        ("codes", c_void_p), ("seed", c_uint64), ("offset", c_uint64), ("x_prequantised", c_int32),
     ]
 
 
@@ -83,6 +83,8 @@ SYMBOLS = {
     "al_clip_weights": (c_int32, [c_int32, c_void_p, c_int32, c_int32, c_int32, c_float, c_void_p, c_void_p]),
     "al_unfold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
     "al_fold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
+    "al_unfold2d_dac": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [POINTER(c_int32), c_int32, c_double, c_void_p,
+                                                                       c_void_p, c_void_p]),
     "al_read_device_error": (c_int32, [c_void_p, POINTER(c_uint32)]),
     "al_set_device_wait_limit_ns": (c_int32, [c_uint64]),
     "al_debug_withhold_forward_signal": (c_int32, [c_int32]),

@@ -186,7 +186,7 @@ def _build_desc(rpu_config, m: int, k: int, n: int, t: int, dtype, training: boo
 class _NoGradCtx:
     """Stands in for the autograd context when a call records nothing for a backward pass."""
 
-    needs_input_grad = (False,) * 12
+    needs_input_grad = (False,) * 13
 
     def save_for_backward(self, *_):
         return None
@@ -208,8 +208,10 @@ class AnalogLinearFunction(torch.autograd.Function):
 
 
 def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx, in_sizes, training,
-                    rpu_config, x_min, x_max, learnable_weight_clip, grad_enabled):
-    """One forward call of the library; ``ctx`` receives what the backward pass needs."""
+                    rpu_config, x_min, x_max, learnable_weight_clip, grad_enabled, prequant=None):
+    """One forward call of the library; ``ctx`` receives what the backward pass needs.
+    ``prequant``: (xq [M,K], ir_rows [T,M]) when the DAC already ran (convolutions: fused into the patch
+    extraction); ``inp`` is then ``xq`` itself."""
     lib = _lib.load()
     if not inp.is_cuda or not weight.is_cuda:
         raise ValueError(
@@ -221,7 +223,7 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
     n, k = weight.shape
     if inp.shape[-1] != k:
         raise RuntimeError(f"input has {inp.shape[-1]} features, the layer expects {k}")
-    x2d = inp.reshape(-1, k).contiguous()
+    x2d = inp.reshape(-1, k).contiguous() if prequant is None else prequant[0]
     m = x2d.shape[0]
     w = weight.contiguous()
     t = len(in_sizes)
@@ -245,6 +247,8 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
         out = torch.empty(m, n, device=dev, dtype=dtype)
         args = _lib.AlForwardArgs()
         args.x, args.w, args.bias, args.out = _ptr(x2d), _ptr(w), _ptr(bias), _ptr(out)
+        if prequant is not None:
+            args.x, args.x_prequantised = None, 1
         args.tile_ends = ends
         ir_data = iridx_data = None
         if static:
@@ -274,7 +278,7 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
             # nothing of the workspace outlives the call: one allocation, carved by offset
             es = x2d.element_size()
             plan = [("w_amax", t * n * es), ("w_tile_max", 2 * t * 4)]
-            if desc.ir_mode != _lib.AL_IR_OFF:
+            if desc.ir_mode != _lib.AL_IR_OFF and prequant is None:
                 plan += [("xq", m * k * es), ("ir_rows", (t if static else t * m) * es)]
             if modifies:
                 plan.append(("w_mod", n * k * es))
@@ -293,8 +297,12 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
             for field, nbytes in plan:
                 setattr(args, field, cursor)
                 cursor += (nbytes + 255) & ~255
+            if prequant is not None:
+                args.xq, args.ir_rows = _ptr(prequant[0]), _ptr(prequant[1])
         else:
-            if desc.ir_mode != _lib.AL_IR_OFF:
+            if prequant is not None:
+                xq, ir_rows = prequant
+            elif desc.ir_mode != _lib.AL_IR_OFF:
                 xq = torch.empty_like(x2d)
                 ir_rows = torch.empty((t, m) if not static else (t,), device=dev, dtype=dtype)
             args.xq, args.ir_rows = _ptr(xq), _ptr(ir_rows)
@@ -348,7 +356,7 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
         )
     ctx.desc, ctx.in_sizes, ctx.dtype = desc, list(in_sizes), dtype
     ctx.weight_address = weight.data_ptr()
-    ctx.shape = tuple(inp.shape)
+    ctx.shape = tuple(inp.shape) if prequant is None else (m, k)
     ctx.has_bias = bias is not None
     ctx.ir_needs_grad = static and input_range is not None and input_range.requires_grad
     ctx.learn_clip = learn_clip
@@ -356,7 +364,8 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
         # with bf16 planes the backward GEMMs read those: the fp32 copies need not be kept
         ctx.save_for_backward(x2d if static else None, None if planes else xq, None if planes else w_mod, ir_rows,
                               keep_mask, w if learn_clip else None, lwc, codes16, w_planes)
-    return out.view(*inp.shape[:-1], n)
+    return out.view(*inp.shape[:-1], n) if prequant is None else out
+
 
 def _analog_backward(ctx, grad_out):
     """The matching backward call: gradients of input, weight, bias, input range and weight ranges."""
@@ -534,6 +543,81 @@ class Unfold2dFunction(torch.autograd.Function):
         with _OnDevice(gp.device):
             _lib.check(lib.al_fold2d(ctx.dtype_code, gp.data_ptr(), *ctx.geom, gx.data_ptr(), _stream(gp.device)))
         return gx, None, None, None, None
+
+
+class AnalogConv2dFunction(torch.autograd.Function):
+    """Analog convolution with a dynamic input range as ONE operator: the patch extraction quantises on
+    the way (``al_unfold2d_dac``), the tiled GEMM consumes the quantised patches, and the backward folds
+    the patch gradients back into the image.  Same values as ``unfold2d`` followed by ``analog_linear``;
+    the unquantised patch matrix is never written.  Returns ``[B * Ho * Wo, out_channels]``."""
+
+    @staticmethod
+    def forward(ctx, inp, weight, bias, input_range, input_range_update_idx, in_sizes, training, rpu_config,
+                x_min, x_max, learnable_weight_clip, grad_enabled, geometry):  # type: ignore[override]
+        lib = _lib.load()
+        xc = inp.contiguous()
+        b, c, h, w = xc.shape
+        (kh, kw), (dh, dw), (ph, pw), (sh, sw) = geometry
+        ho = (h + 2 * ph - dh * (kh - 1) - 1) // sh + 1
+        wo = (w + 2 * pw - dw * (kw - 1) - 1) // sw + 1
+        rows, t = b * ho * wo, len(in_sizes)
+        geom = (b, c, h, w, kh, kw, sh, sw, ph, pw, dh, dw)
+        with _OnDevice(xc.device):
+            xq = torch.empty(rows, c * kh * kw, device=xc.device, dtype=xc.dtype)
+            ir_rows = torch.empty(t, rows, device=xc.device, dtype=xc.dtype)
+            status = lib.al_unfold2d_dac(_DTYPE[xc.dtype], xc.data_ptr(), *geom, _lib.tile_ends_array(in_sizes), t,
+                                         float(rpu_config.forward.inp_res), xq.data_ptr(), ir_rows.data_ptr(),
+                                         _stream(xc.device))
+        if status == _lib.AL_ERR_UNSUPPORTED:
+            raise _PatchTooLarge()
+        _lib.check(status)
+        ctx.geom, ctx.dtype_code = geom, _DTYPE[xc.dtype]
+        return _analog_forward(ctx, xq, weight, bias, input_range, input_range_update_idx, in_sizes, training,
+                               rpu_config, x_min, x_max, learnable_weight_clip, grad_enabled, prequant=(xq, ir_rows))
+
+    @staticmethod
+    def backward(ctx, grad_out):  # type: ignore[override]
+        grads = _analog_backward(ctx, grad_out)
+        grad_img = None
+        if grads[0] is not None:
+            lib = _lib.load()
+            gp = grads[0]
+            b, c, h, w = ctx.geom[:4]
+            grad_img = torch.empty(b, c, h, w, device=gp.device, dtype=gp.dtype)
+            with _OnDevice(gp.device):
+                _lib.check(lib.al_fold2d(ctx.dtype_code, gp.data_ptr(), *ctx.geom, grad_img.data_ptr(), _stream(gp.device)))
+        return (grad_img,) + tuple(grads[1:]) + (None,)
+
+
+class _PatchTooLarge(Exception):
+    """The fused patch extraction cannot stage a whole patch: the caller takes the two-step route."""
+
+
+def analog_conv2d_rows(inp: Tensor, weight2d: Tensor, bias, input_range, input_range_update_idx, in_sizes, training,
+                       rpu_config, x_min, x_max, learnable_weight_clip, kernel_size, dilation, padding, stride):
+    """``[B, C, H, W] -> [B * Ho * Wo, out_channels]`` (or ``[Ho * Wo, out]`` for a 3-D input): patches through the
+    analog linear operator.  Dynamic input ranges with the DAC on take the fused operator."""
+    irp = rpu_config.pre_post.input_range
+    fused = (inp.dim() == 4 and inp.is_cuda and irp.enable and irp.dynamic and not irp.fast_mode
+             and rpu_config.forward.inp_res > 0 and not settings.no_rounding and settings.capture is None
+             and inp.dtype in _DTYPE and inp.shape[0] > 0)
+    if fused:
+        grad = torch.is_grad_enabled()
+        geometry = (tuple(kernel_size), tuple(dilation), tuple(padding), tuple(stride))
+        try:
+            if not grad or not (inp.requires_grad or weight2d.requires_grad or (bias is not None and bias.requires_grad)):
+                ctx = _NoGradCtx()
+                return AnalogConv2dFunction.forward(ctx, inp, weight2d, bias, input_range, input_range_update_idx,
+                                                    in_sizes, training, rpu_config, x_min, x_max, learnable_weight_clip,
+                                                    False, geometry)
+            return AnalogConv2dFunction.apply(inp, weight2d, bias, input_range, input_range_update_idx, in_sizes,
+                                              training, rpu_config, x_min, x_max, learnable_weight_clip, grad, geometry)
+        except _PatchTooLarge:
+            pass
+    patches = unfold2d(inp, kernel_size, dilation, padding, stride)
+    out = analog_linear(patches, weight2d, bias, input_range, input_range_update_idx, in_sizes, training, rpu_config,
+                        x_min, x_max, learnable_weight_clip)
+    return out.reshape(-1, out.shape[-1])
 
 
 def unfold2d(x: Tensor, kernel_size, dilation, padding, stride) -> Tensor:

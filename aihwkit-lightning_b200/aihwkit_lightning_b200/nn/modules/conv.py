@@ -94,16 +94,16 @@ class _AnalogConvNd(AnalogLayerBase, _ConvNd):
         self._check_forward_config()
         im_shape = inp.shape
         assert isinstance(self.padding, tuple), "Padding must be a tuple"
-        patches = F.unfold2d(inp, self.kernel_size, self.dilation, self.padding, self.stride)
-        out = F.analog_linear(patches, self.weight.view(self.out_channels, -1), self.bias,
-                              self.input_range, self.input_range_update_idx, self.in_sizes,
-                              self.training, self.rpu_config, self.x_min, self.x_max,
-                              self.learnable_weight_clip)
-        out = out.transpose(-1, -2).contiguous()
+        out = F.analog_conv2d_rows(inp, self.weight.view(self.out_channels, -1), self.bias,
+                                   self.input_range, self.input_range_update_idx, self.in_sizes,
+                                   self.training, self.rpu_config, self.x_min, self.x_max,
+                                   self.learnable_weight_clip, self.kernel_size, self.dilation, self.padding,
+                                   self.stride)
         out_size = (im_shape[-2] + 2 * self.padding[0] - self.dilation[0] * (self.kernel_size[0] - 1) - 1
                     ) // self.stride[0] + 1
         if len(im_shape) == 3:
-            return out.view(self.out_channels, out_size, -1)
+            return out.transpose(-1, -2).contiguous().view(self.out_channels, out_size, -1)
+        out = out.view(im_shape[0], -1, self.out_channels).transpose(-1, -2).contiguous()
         return out.view(im_shape[0], self.out_channels, out_size, -1)
 
     def _save_to_state_dict(self, destination, prefix, keep_vars):

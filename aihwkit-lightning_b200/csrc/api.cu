@@ -259,7 +259,12 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
   rc = make_tile_table(a->tile_ends, d.T, d.K, &tt);
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  if (!a->x || !a->w || !a->out) {
+  const bool prequantised = a->x_prequantised != 0;
+  if (prequantised && (d.ir_mode != AL_IR_DYNAMIC || !(d.inp_res > 0) || !a->xq || !a->ir_rows)) {
+    set_error("al_forward: x_prequantised needs a dynamic input range with the DAC on, xq and ir_rows");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  if ((!a->x && !prequantised) || !a->w || !a->out) {
     set_error("al_forward: x, w and out must be given");
     return AL_ERR_BAD_ARGUMENT;
   }
@@ -312,7 +317,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
   }
 
   // fp32 layer on the tensor cores: needs the bf16 workspaces
-  const bool tc_f32 = pick_tc_f32(d, tt) && a->codes16 != nullptr && a->w_planes != nullptr;
+  const bool tc_f32 = pick_tc_f32(d, tt) && a->codes16 != nullptr && a->w_planes != nullptr && !a->x_prequantised;
   if (d.dtype == AL_F32 && d.engine >= AL_ENGINE_TCGEN05 && !tc_f32) {
     set_error("tcgen05 engine requested for an fp32 layer that does not qualify (DAC on, rounding on, aligned tiles, "
               "codes16 and w_planes given)");
@@ -321,7 +326,9 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
 
   // 2. DAC: x -> xq (+ per-row ranges in dynamic mode)
   const void* xq = a->x;
-  if (d.ir_mode != AL_IR_OFF) {
+  if (prequantised) {
+    xq = a->xq;
+  } else if (d.ir_mode != AL_IR_OFF) {
     if (!a->xq || (d.ir_mode == AL_IR_DYNAMIC && !a->ir_rows)) {
       set_error("al_forward: xq / ir_rows workspace missing");
       return AL_ERR_BAD_ARGUMENT;

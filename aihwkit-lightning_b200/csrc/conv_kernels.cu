@@ -3,6 +3,8 @@
 // torch.nn.functional.unfold followed by the transpose the reference applies), fold2d is its
 // adjoint for the backward pass (a gather per input pixel: fixed summation order, no atomics).
 // Both are pure data movement and HBM bound.
+#include <string.h>
+
 #include "analog_math.cuh"
 #include "internal.h"
 
@@ -74,9 +76,20 @@ fold2d_kernel(const void* __restrict__ gp, ConvGeom g, void* __restrict__ gx) {
 // plus ow * sw.
 constexpr int kStageBytes = 40 * 1024;
 
-template <int DT>
+// DAC fused into the patch extraction (dynamic per-patch input ranges): a warp writes one patch, so it
+// has all elements of every analog tile of the patch in the staged rows in front of it -- abs-max of
+// each tile by a warp reduction, then the quantised values straight to the GEMM's input matrix.  The
+// fp32 patch matrix is never written.  Needs the whole patch in one channel chunk.
+struct UnfoldDac {
+  TileTable tt;
+  float inp_res;
+  void* ir_rows;  // [T, B*Ho*Wo] dtype: the ranges, as the DAC pre-pass would write them
+};
+
+template <int DT, bool DAC>
 __global__ void __launch_bounds__(256)
-unfold2d_rows_kernel(const void* __restrict__ x, ConvGeom g, int c_chunk, int span, void* __restrict__ out) {
+unfold2d_rows_kernel(const void* __restrict__ x, ConvGeom g, int c_chunk, int span, void* __restrict__ out,
+                     const UnfoldDac dac) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int kk = g.kh * g.kw, ckk = g.C * kk;
   // blockIdx.x = output row * chunks + chunk: CTAs that run together read and write neighbouring memory
@@ -131,7 +144,22 @@ unfold2d_rows_kernel(const void* __restrict__ x, ConvGeom g, int c_chunk, int sp
   for (int ow = warp; ow < g.Wo; ow += n_warps) {
     const int shift = ow * g.sw;
     const int64_t row = base + (int64_t)ow * ckk;
-    for (int e = lane; e < len; e += 32) Elem<DT>::store(out, row + e, tile[lut[e] + shift]);
+    if (DAC) {
+      const int64_t m = (int64_t)out_row * g.Wo + ow, rows_total = (int64_t)g.B * g.Ho * g.Wo;
+      for (int t = 0; t < dac.tt.T; ++t) {
+        const int lo = dac.tt.lo(t), hi = dac.tt.hi(t);
+        float amax = 0.0f;
+        for (int e = lo + lane; e < hi; e += 32) amax = fmaxf(amax, fabsf(tile[lut[e] + shift]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (lane == 0) Elem<DT>::store(dac.ir_rows, (int64_t)t * rows_total + m, amax);
+        const QuantSeg q = dac_prepare<DT>(amax, dac.inp_res, false, false);
+        for (int e = lo + lane; e < hi; e += 32)
+          Elem<DT>::store(out, row + e, dac_apply<DT>(q, tile[lut[e] + shift], nullptr));
+      }
+    } else {
+      for (int e = lane; e < len; e += 32) Elem<DT>::store(out, row + e, tile[lut[e] + shift]);
+    }
   }
 }
 
@@ -390,13 +418,57 @@ int al_unfold2d(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t H, i
   if (chunk >= 1 && (int64_t)B * g.Ho * ((C + chunk - 1) / chunk) < 2147483647) {
     const unsigned grid = (unsigned)((int64_t)B * g.Ho * ((C + chunk - 1) / chunk));
     const size_t smem = (size_t)chunk * (kh * span + kh * kw + kh) * 4;
-    if (dtype == AL_F32) unfold2d_rows_kernel<kF32><<<grid, 256, smem, (cudaStream_t)stream>>>(x, g, chunk, span, out);
-    else unfold2d_rows_kernel<kBF16><<<grid, 256, smem, (cudaStream_t)stream>>>(x, g, chunk, span, out);
+    if (dtype == AL_F32) unfold2d_rows_kernel<kF32, false><<<grid, 256, smem, (cudaStream_t)stream>>>(x, g, chunk, span, out, UnfoldDac());
+    else unfold2d_rows_kernel<kBF16, false><<<grid, 256, smem, (cudaStream_t)stream>>>(x, g, chunk, span, out, UnfoldDac());
     return check_launch("unfold2d_rows");
   }
   if (dtype == AL_F32) unfold2d_kernel<kF32><<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(x, g, out);
   else unfold2d_kernel<kBF16><<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(x, g, out);
   return check_launch("unfold2d");
+}
+
+int al_unfold2d_dac(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh, int32_t kw,
+                    int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw,
+                    const int32_t* tile_ends_host, int32_t T, double inp_res, void* xq, void* ir_rows, void* stream) {
+  if ((dtype != AL_F32 && dtype != AL_BF16) || !x || !xq || !ir_rows || !tile_ends_host) {
+    set_error("al_unfold2d_dac: bad dtype or null pointer");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  ConvGeom g;
+  int rc = make_geom(B, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, &g);
+  if (rc) return rc;
+  const int ckk = C * kh * kw;
+  if (T < 1 || T > kMaxTiles || !(inp_res > 0) || tile_ends_host[T - 1] != ckk) {
+    set_error("al_unfold2d_dac: tile table (T=%d, last end %d, patch length %d) or inp_res", T,
+              T >= 1 && T <= kMaxTiles ? tile_ends_host[T - 1] : -1, ckk);
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  const int span = (g.Wo - 1) * sw + (kw - 1) * dw + 1;
+  const int chunk = unfold_chunk(g, span);
+  if (chunk < C || (int64_t)B * g.Ho >= 2147483647 || (int64_t)B * g.Ho * g.Wo * T >= 2147483647) {
+    set_error("al_unfold2d_dac: the patch does not fit one staged block (use al_unfold2d and the DAC of al_forward)");
+    return AL_ERR_UNSUPPORTED;
+  }
+  UnfoldDac host;
+  memset(&host, 0, sizeof(host));
+  host.tt.T = T;
+  int prev = 0;
+  for (int t = 0; t < T; ++t) {
+    if (tile_ends_host[t] <= prev) {
+      set_error("al_unfold2d_dac: tile ends must be strictly increasing");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    host.tt.ends[t] = prev = tile_ends_host[t];
+  }
+  host.inp_res = (float)inp_res;
+  host.ir_rows = ir_rows;
+  cudaStream_t st = (cudaStream_t)stream;
+  ProfScope prof(AL_K_UNFOLD, st);
+  const unsigned grid = (unsigned)((int64_t)B * g.Ho);
+  const size_t smem = (size_t)chunk * (kh * span + kh * kw + kh) * 4;
+  if (dtype == AL_F32) unfold2d_rows_kernel<kF32, true><<<grid, 256, smem, st>>>(x, g, chunk, span, xq, host);
+  else unfold2d_rows_kernel<kBF16, true><<<grid, 256, smem, st>>>(x, g, chunk, span, xq, host);
+  return check_launch("unfold2d_dac");
 }
 
 int al_fold2d(int32_t dtype, const void* grad_patches, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh,

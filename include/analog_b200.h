@@ -145,6 +145,9 @@ typedef struct AlForwardArgs {
   /* optional debug output */
   void* codes;               /* [M,K] dtype integer DAC codes, nullable                     */
   uint64_t seed, offset;     /* counter-based generator: (seed, call counter)              */
+  int32_t x_prequantised;    /* 1: xq and ir_rows already hold the DAC's output (al_unfold2d_dac);
+                                 x may then be null and the DAC stage is skipped (dynamic
+                                 input ranges only)                                          */
 } AlForwardArgs;
 
 typedef struct AlBackwardArgs {
@@ -246,6 +249,15 @@ int al_clip_weights(int32_t dtype, void* w, int32_t rows, int32_t cols, int32_t 
  * expression): grad_x[b,c,h,w] = sum of grad_patches over every patch position that read x[b,c,h,w]. */
 int al_unfold2d(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh, int32_t kw,
                 int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw, void* out, void* stream);
+/* al_unfold2d with the DAC of a dynamic input range fused in: writes the quantised patches xq
+ * [B*Ho*Wo, C*kh*kw] and the per-(tile, patch) ranges ir_rows [T, B*Ho*Wo] that al_forward would
+ * otherwise compute from the patch matrix (P/conv.py:312-322 followed by P/torch_utils/torch_linear.py:
+ * 156, 182-192); the unquantised patch matrix is never written.  al_forward then runs with
+ * AlForwardArgs.x_prequantised = 1.  AL_ERR_UNSUPPORTED when a patch does not fit one staged block:
+ * use al_unfold2d then. */
+int al_unfold2d_dac(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh, int32_t kw,
+                    int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw,
+                    const int32_t* tile_ends_host, int32_t T, double inp_res, void* xq, void* ir_rows, void* stream);
 int al_fold2d(int32_t dtype, const void* grad_patches, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh,
               int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw, void* grad_x,
               void* stream);
