@@ -113,7 +113,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             const int ks = st % p.ksteps, plane = st / p.ksteps;
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
-            if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag AL_POLL_ROLE(0))) {
+            if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag)) {
               raise_error(kErrProducer, abort_flag);
               ok = false;
               break;
@@ -162,7 +162,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         for (int t = 0; t < T && ok; ++t, ++acc_it) {
           const int b = acc_it & 1u;
           const uint32_t aph = (acc_it >> 1) & 1u;
-          if (!mbar_wait(&bars->acc_empty[b], aph ^ 1u, abort_flag AL_POLL_ROLE(1))) {
+          if (!mbar_wait(&bars->acc_empty[b], aph ^ 1u, abort_flag)) {
             raise_error(kErrMma, abort_flag);
             ok = false;
             break;
@@ -173,7 +173,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           for (int ks = 0; ks < steps; ++ks, ++it) {
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
-            if (!mbar_wait(&bars->full[s], ph, abort_flag AL_POLL_ROLE(2))) {
+            if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
               raise_error(kErrMma, abort_flag);
               ok = false;
               break;
@@ -267,7 +267,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const float step = has_adc ? quant_step<RD>(bound, ep.out_res) : 1.0f;
         const float stepc = step < kTiny ? kTiny : step;
         const float rstep = __frcp_rn(stepc);
-        if (!mbar_wait(&bars->acc_full[b], aph, abort_flag AL_POLL_ROLE(3))) {
+        if (!mbar_wait(&bars->acc_full[b], aph, abort_flag)) {
           if (lane == 0) raise_error(kErrEpilogue, abort_flag);
           ok = false;
           break;
@@ -730,14 +730,6 @@ int launch_fwd_tc_f32(const void* codes16, const void* w_planes, int K, const Ti
 }
 
 cudaError_t tc_fwd_take_error_word(uint32_t* code) { return take_error_word(code); }
-#if defined(AL_EXP_COUNT_POLLS)
-extern "C" int al_exp_poll_counts(unsigned long long* out, int reset) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, g_poll_counts, sizeof(unsigned long long) * 16);
-  if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(g_poll_counts, z, sizeof(z)); }
-  return 0;
-}
-#endif
 cudaError_t tc_fwd_set_wait_limit(unsigned long long ns) { return set_wait_limit(ns); }
 cudaError_t tc_fwd_set_withhold_acc_signal(uint32_t on) { return set_withhold_acc_signal(on); }
 

@@ -115,28 +115,11 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 __device__ __forceinline__ uint64_t wait_limit_ns() { return *(volatile unsigned long long*)&g_tc_wait_limit_ns; }
-#if defined(AL_EXP_COUNT_POLLS)
-__device__ unsigned long long g_poll_counts[16];
-#define AL_POLL_ROLE(r) , r
-#define AL_POLL_COUNT(r) atomicAdd(&g_poll_counts[r], 1ull)
-#else
-#define AL_POLL_ROLE(r)
-#define AL_POLL_COUNT(r)
-#endif
 // Bounded wait.  Returns false when the wait gave up (time limit, or another role aborted).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag
-#if defined(AL_EXP_COUNT_POLLS)
-                                          , int role = 15
-#endif
-) {
-#if defined(AL_EXP_COUNT_POLLS)
-  const long long c0 = clock64();
-  struct Acc { long long c0; int role; __device__ ~Acc() { if ((threadIdx.x & 31) == 0) { atomicAdd(&g_poll_counts[8 + role], (unsigned long long)(clock64() - c0)); atomicAdd(&g_poll_counts[4 + role], 1ull); } } } acc_{c0, role};
-#endif
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
   uint64_t t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
     if (mbar_try(bar, parity)) return true;
-    AL_POLL_COUNT(role);
     if ((spin & 3u) == 3u) {
       if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();

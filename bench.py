@@ -26,8 +26,9 @@ metric is algorithmic TFLOP/s = 6*M*K*N / time.
 * ``c3``: one full data-parallel training step of the Phi-3-mini-shaped decoder (32 layers,
   d=3072, MLP 8192, vocab 32064, every Linear analog, sequence 2048 x micro-batch 4 per GPU, AdamW),
   timed after the headline: tokens/s, analog TFLOP/s and the exposed part of the gradient exchange.
-* N > 1 (torchrun): every rank runs on its own batch (weak scaling) and the weight gradients
-  are all-reduced over NCCL, as in data-parallel training.
+* N > 1 (torchrun): every rank runs on its own batch (weak scaling) and the weight gradients are
+  summed over the replicas as in data-parallel training, by the library's own exchange kernel over
+  peer memory (``BENCH_EXCHANGE=nccl``: by NCCL all-reduce calls instead).
 
 ``--config c1 | c4 | c5`` measure the other benchmark configurations with the same line format
 (c1: the fp32 1024 x 1024 layer; c4: a ResNet-32 training step; c5: the inference shape sweep);
@@ -51,7 +52,7 @@ FLOP_PER_STEP = 6.0 * M * K * N
 L2_FLUSH_BYTES = 256 << 20
 # DRAM bytes (read + write) of one forward-GEMM launch on the headline workload, from the ncu
 # capture summarised in profiles/fwd_tc_kernel_c2.md
-FWD_KERNEL_DRAM_BYTES = 120.1e6 + 76.4e6
+FWD_KERNEL_DRAM_BYTES = 119.6e6 + 77.4e6
 
 
 def make_rpu_config(ns, max_in=MAX_IN, adc=True, out_noise=0.04, dynamic=True):
@@ -679,7 +680,7 @@ def run_c1(args, ctx):
 
     dev = ctx.dev
     lib = _lib.load()
-    m, k, n = 512, 1024, 1024
+    m, k, n = args.c1_rows, args.c1_size, args.c1_size  # other sizes: the same layer where the GEMMs bound the step
     rpu = make_rpu_config(cfg, max_in=512, adc=False, dynamic=False)
     rpu.pre_post.input_range.learn_input_range = True
     rpu.pre_post.input_range.init_value = 3.0
@@ -714,15 +715,16 @@ def run_c1(args, ctx):
     rec = base_record(args, 1)
     rec.update({
         "dtype": "f32",
-        "config": {"workload": "config 1: AnalogLinear 1024->1024 fp32, 512 rows ~N(0,1), weights ~U(-1/32,1/32), "
-                               "max_input_size=512 (2 tiles), inp_res=254, learned static input range 3.0, out_noise 0.04, "
+        "config": {"workload": f"config 1: AnalogLinear {k}->{n} fp32, {m} rows ~N(0,1), weights ~U(-1/32,1/32), "
+                               f"max_input_size=512 ({k // 512} tiles), inp_res=254, learned static input range 3.0, out_noise 0.04, "
                                "weight noise 0.02 per-channel, no ADC, training fwd+bwd",
                    "l2": "256 MB flush write between steps", "parallelism": "dp1"},
         "value": flop / (ms * 1e-3) / 1e12, "ms_per_step": ms,
         "gpu_launches": sum(v[0] for v in prof.values()),
         "roofline": {"kernel": "fwd+dgrad+wgrad GEMMs", "bound": "tensor", "achieved": flop / (gemm_ms * 1e-3) / 1e12,
                      "peak": peaks["bf16"], "unit": "TFLOP/s", "frac": flop / (gemm_ms * 1e-3) / 1e12 / peaks["bf16"],
-                     "note": "3.2 GFLOP per step: the step is bound by launch latency, not by a pipe", "traffic": None},
+                     "note": f"{flop / 1e9:.1f} GFLOP per step; at the configuration's own size the step is bound by launch "
+                             "latency, not by a pipe", "traffic": None},
         "kernels": kernel_table(prof), "clocks": clocks,
     })
     return rec
@@ -910,6 +912,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-baseline", action="store_true")
     ap.add_argument("--no-c3", action="store_true", help="headline line only, without the decoder step")
+    ap.add_argument("--c1-size", type=int, default=1024, help="in = out features of the fp32 layer of --config c1")
+    ap.add_argument("--c1-rows", type=int, default=512, help="input rows of the fp32 layer of --config c1")
     ap.add_argument("--c3-layers", type=int, default=32)
     ap.add_argument("--c3-steps", type=int, default=3)
     args = ap.parse_args()
