@@ -95,6 +95,7 @@ SYMBOLS = {
     "al_peer_read_error": (c_int32, [POINTER(c_uint32)]),
     "al_wgrad_split_plan": (c_int32, [c_int32, c_int32, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
     "al_profile_enable": (c_int32, [c_int32]),
+    "al_profile_select": (c_int32, [c_uint32]),
     "al_profile_read": (c_int32, [POINTER(AlProfileEntry), c_int32]),
     "al_kernel_class_name": (c_char_p, [c_int32]),
     "al_status_str": (c_char_p, [c_int32]),

@@ -671,6 +671,7 @@ struct EventPair {
 };
 std::mutex g_prof_mu;
 bool g_prof_on = false;
+uint32_t g_prof_classes = 0xffffffffu;
 AlProfileEntry g_prof[AL_K_COUNT];
 std::vector<EventPair*> g_pending, g_free;
 }  // namespace
@@ -679,7 +680,7 @@ ProfScope::ProfScope(int kernel_class, cudaStream_t s, int launches)
     : cls(kernel_class), stream(s), slot(nullptr) {
   std::lock_guard<std::mutex> lock(g_prof_mu);
   g_prof[cls].launches += launches;
-  if (!g_prof_on) return;
+  if (!g_prof_on || !((g_prof_classes >> cls) & 1u)) return;
   EventPair* ep = nullptr;
   if (!g_free.empty()) {
     ep = g_free.back();
@@ -717,6 +718,12 @@ int al_reserve_sms(int32_t n) {
 int al_profile_enable(int on) {
   std::lock_guard<std::mutex> lock(g_prof_mu);
   g_prof_on = on != 0;
+  return AL_OK;
+}
+
+int al_profile_select(uint32_t class_mask) {
+  std::lock_guard<std::mutex> lock(g_prof_mu);
+  g_prof_classes = class_mask;
   return AL_OK;
 }
 

@@ -331,6 +331,10 @@ int al_peer_allreduce(int32_t dtype, int32_t world, int32_t rank, const uint64_t
 int al_peer_read_error(uint32_t* out_code);
 
 int al_profile_enable(int on);
+/* Which kernel classes are bracketed by events while profiling is on: bit c = class c (default: all).
+ * Launches are counted for every class either way.  An event pair costs about a microsecond of stream
+ * time, so a caller that times a whole step and one kernel inside it selects that kernel only. */
+int al_profile_select(uint32_t class_mask);
 int al_profile_read(AlProfileEntry* out, int reset);
 const char* al_kernel_class_name(int kernel_class);
 
