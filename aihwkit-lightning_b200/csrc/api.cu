@@ -324,11 +324,25 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     return AL_ERR_UNSUPPORTED;
   }
 
+  // A handful of rows, nothing to modify in the weights, no backward to prepare: the layer is
+  // bound by streaming W once; one kernel takes abs-max and tile products from the same read and
+  // quantises its slice of the inputs itself.
+  const bool smallm = a->smallm_scratch && d.dtype == AL_BF16 && d.engine == AL_ENGINE_AUTO && !dv.has_noise &&
+                      dv.weight_quant == AL_QUANT_NONE && dv.weight_noise == AL_NOISE_NONE &&
+                      d.clip_type != AL_CLIP_LEARNABLE_PER_CHANNEL && !d.save_for_backward && a->w_amax &&
+                      a->w_tile_max && smallm_forward_supported(d.M, d.K, d.N, tt) && ((uintptr_t)a->w % 16) == 0;
+  // Every block of 64 output channels quantises the rows again, so the in-kernel DAC pays while
+  // rows x channels is small (measured on B200: up to 13 % off a single-row call at every size, 3-8 %
+  // off 16 rows up to 4096 channels, slower beyond that, where the stand-alone pass is used).
+  const bool smallm_dac = smallm && !prequantised && d.ir_mode != AL_IR_OFF && a->codes == nullptr &&
+                          ((uintptr_t)a->x % 16) == 0 && (d.ir_mode != AL_IR_DYNAMIC || a->ir_rows != nullptr) &&
+                          (int64_t)d.M * d.N <= 65536;
+
   // 2. DAC: x -> xq (+ per-row ranges in dynamic mode)
   const void* xq = a->x;
   if (prequantised) {
     xq = a->xq;
-  } else if (d.ir_mode != AL_IR_OFF) {
+  } else if (d.ir_mode != AL_IR_OFF && !smallm_dac) {
     if (!a->xq || (d.ir_mode == AL_IR_DYNAMIC && !a->ir_rows)) {
       set_error("al_forward: xq / ir_rows workspace missing");
       return AL_ERR_BAD_ARGUMENT;
@@ -339,12 +353,8 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     xq = a->xq;
   }
 
-  // 2b. a handful of rows, nothing to modify in the weights, no backward to prepare: the layer is
-  // bound by streaming W once; one kernel takes abs-max and tile products from the same read
-  if (a->smallm_scratch && d.dtype == AL_BF16 && d.engine == AL_ENGINE_AUTO && !dv.has_noise &&
-      dv.weight_quant == AL_QUANT_NONE && dv.weight_noise == AL_NOISE_NONE &&
-      d.clip_type != AL_CLIP_LEARNABLE_PER_CHANNEL && !d.save_for_backward && a->w_amax && a->w_tile_max &&
-      smallm_forward_supported(d.M, d.K, d.N, tt) && ((uintptr_t)xq % 16) == 0 && ((uintptr_t)a->w % 16) == 0) {
+  // 2b. the few-rows forward
+  if (smallm && ((uintptr_t)xq % 16) == 0) {
     FwdEpilogueParams ep;
     memset(&ep, 0, sizeof(ep));
     ep.M = d.M; ep.N = d.N; ep.T = d.T;
@@ -355,7 +365,8 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     ep.bound_pc = dv.bound_pc; ep.noise_pc = dv.noise_pc; ep.no_rounding = d.no_rounding;
     ep.noise_coef = dv.noise_coef; ep.out_bound = dv.out_bound; ep.out_res = dv.out_res;
     return launch_fwd_smallm(dv.round_dt, xq, a->w, d.K, tt, ep, a->w_amax, (float*)a->w_tile_max,
-                             a->smallm_scratch, a->out, s);
+                             a->smallm_scratch, a->out, s, smallm_dac ? 1 : 0, ir_static,
+                             dv.has_dac ? dv.inp_res : -1.0f, d.no_rounding);
   }
 
   // 3. weight statistics and modifier

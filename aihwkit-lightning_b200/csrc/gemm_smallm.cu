@@ -7,6 +7,11 @@
 // needs the tile maximum over ALL channels, which is known only when the whole tile has been
 // streamed, so it runs in a second, tiny kernel over the [T, 16, N] fp32 partial results.
 //
+// The DAC runs inside the same kernel: every CTA stages the 16 x tile_w slice of the raw inputs it
+// multiplies with, takes the per-row range of the slice (dynamic input range) and quantises it in
+// shared memory with the arithmetic of the stand-alone DAC pass, so a call of this path has no
+// input pre-pass and no quantised copy of the inputs in HBM.
+//
 // Preconditions (checked by the caller): bf16, equally wide tiles with 16-byte aligned starts,
 // no weight modifier active in this call (the GEMM reads `w` itself) and no output noise.
 #include <cuda_bf16.h>
@@ -37,12 +42,23 @@ __device__ __forceinline__ void mma_16x8x16(float c[4], uint32_t a0, uint32_t a1
 // k-chunks) fall on distinct banks
 __host__ __device__ inline int x_pitch(int tile_w) { return ((tile_w + 63) / 64) * 64 + 32; }
 
+// What the in-kernel DAC needs (dac.on == 0: the inputs arrive quantised).
+struct SmallmDac {
+  int on;
+  int ir_mode;               // AL_IR_DYNAMIC or AL_IR_STATIC
+  const uint16_t* ir_static;  // [T] ranges of a static input range
+  float inp_res;
+  int no_rounding;
+  int small_codes;    // |code| stays far below 2^22: the add-based rint applies
+  uint16_t* ir_rows;  // [T][M]: the dynamic ranges, written by the first column of CTAs
+};
+
 // grid: (ceil(N / 64), T).  acc [T][16][N] fp32, w_amax [T][N] bf16, tile_max [T] (float bits,
 // zeroed by the caller).
 __global__ void __launch_bounds__(kWarps * 32)
 smallm_partial_kernel(const uint16_t* __restrict__ xq, int M, int K, const uint16_t* __restrict__ w, int N,
                       int tile_w, float* __restrict__ acc, uint16_t* __restrict__ w_amax,
-                      float* __restrict__ tile_max) {
+                      float* __restrict__ tile_max, const SmallmDac dac) {
   extern __shared__ __align__(16) uint16_t x_s[];  // [16][pitch]
   const int t = blockIdx.y;
   const int lo = t * tile_w;
@@ -68,7 +84,7 @@ smallm_partial_kernel(const uint16_t* __restrict__ xq, int M, int K, const uint1
     }
   };
   load_batch(0);
-  // stage the tile's slice of the (already DAC-quantised) inputs; rows >= M and the padding are zero
+  // stage the tile's slice of the inputs; rows >= M and the padding are zero
   for (int idx = threadIdx.x; idx < kRows * vec_per_row; idx += blockDim.x) {
     const int m = idx / vec_per_row, v = idx - m * vec_per_row;
     uint4 val = make_uint4(0u, 0u, 0u, 0u);
@@ -76,6 +92,71 @@ smallm_partial_kernel(const uint16_t* __restrict__ xq, int M, int K, const uint1
     *reinterpret_cast<uint4*>(x_s + m * pitch + v * 8) = val;
   }
   __syncthreads();
+  if (dac.on) {
+    // DAC of the staged slice by all threads, one 16-byte vector at a time: range of every (row,
+    // tile) segment first, then the element-wise chain of the stand-alone pass (dac_prepare /
+    // dac_apply; its packed bf16 form when rounding is on and the codes are small)
+    __shared__ unsigned int row_bits[kRows];
+    __shared__ QuantSeg row_q[kRows];
+    const int vecs = tile_w / 8, total = M * vecs;
+    if (dac.ir_mode == AL_IR_DYNAMIC) {
+      if (threadIdx.x < kRows) row_bits[threadIdx.x] = 0u;
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+        const int m = idx / vecs, v = idx - m * vecs;
+        const uint4 raw = *reinterpret_cast<const uint4*>(x_s + m * pitch + v * 8);
+        __nv_bfloat162 a2 = __hmax2(__habs2(as_bf162(raw.x)), __habs2(as_bf162(raw.y)));
+        a2 = __hmax2(a2, __hmax2(__habs2(as_bf162(raw.z)), __habs2(as_bf162(raw.w))));
+        // non-negative floats order like their bit patterns
+        atomicMax(&row_bits[m], __float_as_uint(fmaxf(__low2float(a2), __high2float(a2))));
+      }
+      __syncthreads();
+    }
+    if (threadIdx.x < M) {
+      float ir;
+      bool clampit = false;
+      if (dac.ir_mode == AL_IR_DYNAMIC) {
+        ir = __uint_as_float(row_bits[threadIdx.x]);
+        if (blockIdx.x == 0) dac.ir_rows[(int64_t)t * M + threadIdx.x] = f32_to_bf16_bits(ir);
+      } else {
+        ir = bf16_bits_to_f32(dac.ir_static[t]);
+        clampit = true;
+      }
+      row_q[threadIdx.x] = dac_prepare<kBF16>(ir, dac.inp_res, clampit, dac.no_rounding != 0);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+      const int m = idx / vecs, v = idx - m * vecs;
+      const QuantSeg q = row_q[m];
+      uint4* slot = reinterpret_cast<uint4*>(x_s + m * pitch + v * 8);
+      const uint4 raw = *slot;
+      uint32_t wd[4] = {raw.x, raw.y, raw.z, raw.w};
+      if (q.quantise && !q.no_rounding && dac.small_codes) {
+        const __nv_bfloat162 b2 = __float2bfloat162_rn(q.bound), nb2 = __float2bfloat162_rn(-q.bound);
+        const __nv_bfloat162 step2 = __float2bfloat162_rn(q.step);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 x2 = as_bf162(wd[i]);
+          if (q.clampit) x2 = __hmin2_nan(__hmax2_nan(x2, nb2), b2);
+          const __nv_bfloat162 q2 = __floats2bfloat162_rn(fdiv_rcp(__low2float(x2), q.stepc, q.rstep),
+                                                          fdiv_rcp(__high2float(x2), q.stepc, q.rstep));
+          const float c_lo = rint_small(__low2float(q2)), c_hi = rint_small(__high2float(q2));
+          const uint32_t c2 = (__float_as_uint(c_lo) >> 16) | (__float_as_uint(c_hi) & 0xffff0000u);
+          wd[i] = as_u32(__hmul2_rn(as_bf162(c2), step2));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float code;
+          const uint32_t lo16 = f32_to_bf16_bits(dac_apply<kBF16>(q, bf16_bits_to_f32((uint16_t)(wd[i] & 0xffffu)), &code));
+          const uint32_t hi16 = f32_to_bf16_bits(dac_apply<kBF16>(q, bf16_bits_to_f32((uint16_t)(wd[i] >> 16)), &code));
+          wd[i] = lo16 | (hi16 << 16);
+        }
+      }
+      *slot = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+    }
+    __syncthreads();
+  }
   if (!active) return;
 
   const uint16_t* xa = x_s + g * pitch;
@@ -159,7 +240,7 @@ bool smallm_forward_supported(int M, int K, int N, const TileTable& tt) {
 
 int launch_fwd_smallm(int round_dt, const void* xq, const void* w, int K, const TileTable& tt,
                       const FwdEpilogueParams& ep, void* w_amax, float* tile_max, float* scratch, void* out,
-                      cudaStream_t s) {
+                      cudaStream_t s, int dac_in_kernel, const void* ir_static, float inp_res, int no_rounding) {
   ProfScope prof(AL_K_FWD_GEMM, s, 2);
   const int tile_w = tt.hi(0);
   const int smem = kRows * x_pitch(tile_w) * 2;
@@ -170,9 +251,20 @@ int launch_fwd_smallm(int round_dt, const void* xq, const void* w, int K, const 
     return AL_ERR_CUDA;
   }
   dim3 grid((ep.N + kWarps * kChanPerWarp - 1) / (kWarps * kChanPerWarp), tt.T);
+  SmallmDac dac;
+  dac.on = dac_in_kernel;
+  dac.ir_mode = ep.ir_mode;
+  dac.ir_static = reinterpret_cast<const uint16_t*>(ir_static);
+  dac.inp_res = inp_res;
+  dac.no_rounding = no_rounding;
+  {
+    const float states = inp_res > 0.0f ? (inp_res > 1.0f ? inp_res : 1.0f / inp_res) : 0.0f;
+    dac.small_codes = states < 4.0e6f;
+  }
+  dac.ir_rows = reinterpret_cast<uint16_t*>(const_cast<void*>(ep.ir_rows));
   smallm_partial_kernel<<<grid, kWarps * 32, smem, s>>>(
       reinterpret_cast<const uint16_t*>(xq), ep.M, K, reinterpret_cast<const uint16_t*>(w), ep.N, tile_w, scratch,
-      reinterpret_cast<uint16_t*>(w_amax), tile_max);
+      reinterpret_cast<uint16_t*>(w_amax), tile_max, dac);
   int rc = check_launch("smallm_partial");
   if (rc) return rc;
   FwdEpilogueParams e2 = ep;

@@ -154,7 +154,7 @@ int64_t smallm_scratch_floats(int N, int T);
 bool smallm_forward_supported(int M, int K, int N, const TileTable& tt);
 int launch_fwd_smallm(int round_dt, const void* xq, const void* w, int K, const TileTable& tt,
                       const FwdEpilogueParams& ep, void* w_amax, float* tile_max, float* scratch, void* out,
-                      cudaStream_t s);
+                      cudaStream_t s, int dac_in_kernel, const void* ir_static, float inp_res, int no_rounding);
 
 // ---- tcgen05 GEMMs (gemm_tcgen05_fwd.cu, gemm_tcgen05_bwd.cu) -----------------------------
 bool tc_forward_supported(const AlDesc& d, const TileTable& tt);
