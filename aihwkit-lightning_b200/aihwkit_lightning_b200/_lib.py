@@ -45,6 +45,7 @@ class AlForwardArgs(Structure):
         ("std_scratch", c_void_p), ("std_override", c_void_p), ("smallm_scratch", c_void_p),
         ("codes16", c_void_p), ("w_planes", c_void_p), ("w_noise", c_void_p), ("out_noise", c_void_p),
         ("codes", c_void_p), ("seed", c_uint64), ("offset", c_uint64), ("x_prequantised", c_int32),
+        ("offset_base", c_void_p),
     ]
 
 

@@ -60,9 +60,46 @@ class _Settings:
     # deviations of the init-from-data phase over the replicas here (``distributed.mean_over_replicas``),
     # so that every replica keeps the same input ranges
     sync_tile_std = None
+    # a ``GraphNoise``: the calls draw their noise counters from it instead of torch's generator, so
+    # that a training step can be captured in a CUDA graph and still see fresh noise on every replay
+    graph_noise = None
 
 
 settings = _Settings()
+
+
+class GraphNoise:
+    """Noise counters for analog calls that are captured in a CUDA graph.
+
+    A captured call replays with the arguments it was captured with, so a call counter passed by
+    value would repeat the same noise on every replay.  With ``settings.graph_noise`` set, every call
+    gets a distinct host-side offset (fixed at capture) plus the address of one counter in device
+    memory that the noise kernels add to it; ``advance()`` (capturable itself, so it can be the first
+    node of the graph) moves that counter on by 2**32 and with it every call's noise.
+
+        noise = F.GraphNoise(device)
+        F.settings.graph_noise = noise
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            noise.advance()
+            loss = model(x).sum(); loss.backward(); optimizer.step()
+        graph.replay()  # fresh noise each time
+    """
+
+    def __init__(self, device):
+        device = torch.device(device)
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        self.counter = torch.zeros(1, dtype=torch.int64, device=device)
+        self.seed = torch.cuda.default_generators[index].initial_seed() & 0xFFFFFFFFFFFFFFFF
+        self.calls = 0
+
+    def advance(self) -> None:
+        self.counter.add_(1 << 32)
+
+    def next(self):
+        offset = self.calls
+        self.calls += 4
+        return self.seed, offset
 
 
 @contextmanager
@@ -343,7 +380,11 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
             codes = torch.empty_like(x2d)
         args.codes = _ptr(codes)
         if training and (desc.noise_type != 0 or desc.out_noise > 0):
-            args.seed, args.offset = _next_seed(dev)
+            if settings.graph_noise is not None:
+                args.seed, args.offset = settings.graph_noise.next()
+                args.offset_base = settings.graph_noise.counter.data_ptr()
+            else:
+                args.seed, args.offset = _next_seed(dev)
         _lib.check(lib.al_forward(desc, args, _stream(dev)))
         if static and ir_data is not input_range.data:
             input_range.data.copy_(ir_data)

@@ -332,8 +332,8 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
                       d.clip_type != AL_CLIP_LEARNABLE_PER_CHANNEL && !d.save_for_backward && a->w_amax &&
                       a->w_tile_max && smallm_forward_supported(d.M, d.K, d.N, tt) && ((uintptr_t)a->w % 16) == 0;
   // Every block of 64 output channels quantises the rows again, so the in-kernel DAC pays while
-  // rows x channels is small (measured on B200: up to 13 % off a single-row call at every size, 3-8 %
-  // off 16 rows up to 4096 channels, slower beyond that, where the stand-alone pass is used).
+  // rows x channels is small (measured on B200: 3-13 % off a single-row call at every size, about even at
+  // 16 rows x 4096 channels, slower beyond that, where the stand-alone pass is used).
   const bool smallm_dac = smallm && !prequantised && d.ir_mode != AL_IR_OFF && a->codes == nullptr &&
                           ((uintptr_t)a->x % 16) == 0 && (d.ir_mode != AL_IR_DYNAMIC || a->ir_rows != nullptr) &&
                           (int64_t)d.M * d.N <= 65536;
@@ -394,7 +394,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     if (rc) return rc;
     rc = launch_weight_modify(d.dtype, a->w, d.N, d.K, tt, a->w_amax, tile_max, flags, quant, dv.n_states,
                               dv.max_state, dv.weight_noise, dv.std_dev, a->w_noise, a->seed, a->offset,
-                              d.no_rounding, a->w_mod, s);
+                              d.no_rounding, a->w_mod, s, a->offset_base);
     if (rc) return rc;
     w_mod = a->w_mod;
   } else if (needs_wmax(dv)) {
@@ -412,7 +412,8 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     if (dv.weight_quant == AL_QUANT_NONE && dv.weight_noise != AL_NOISE_ADD_NORMAL) {
       // every scale the modifier needs is the segment's own abs-max: one sweep over w
       rc = launch_weight_fused(d.dtype, a->w, d.N, d.K, tt, a->w_amax, tile_max, dv.weight_noise,
-                               dv.std_dev, a->w_noise, a->seed, a->offset, modifies ? a->w_mod : nullptr, s);
+                               dv.std_dev, a->w_noise, a->seed, a->offset, modifies ? a->w_mod : nullptr, s,
+                               a->offset_base);
       if (rc) return rc;
     } else {
       rc = launch_abs_max_tiles(d.dtype, a->w, d.N, d.K, tt, a->w_amax, s);
@@ -422,7 +423,8 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
       if (modifies) {
         rc = launch_weight_modify(d.dtype, a->w, d.N, d.K, tt, a->w_amax, tile_max, flags,
                                   dv.weight_quant, dv.n_states, dv.max_state, dv.weight_noise,
-                                  dv.std_dev, a->w_noise, a->seed, a->offset, d.no_rounding, a->w_mod, s);
+                                  dv.std_dev, a->w_noise, a->seed, a->offset, d.no_rounding, a->w_mod, s,
+                                  a->offset_base);
         if (rc) return rc;
       }
     }
@@ -449,6 +451,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
   ep.bound_pc = dv.bound_pc; ep.noise_pc = dv.noise_pc; ep.no_rounding = d.no_rounding;
   ep.noise_coef = dv.noise_coef; ep.out_bound = dv.out_bound; ep.out_res = dv.out_res;
   ep.seed = a->seed; ep.offset = a->offset;
+  ep.offset_base = a->offset_base;
 
   if (tc_f32) {
     rc = launch_split_planes(static_cast<const float*>(w_mod), (int64_t)d.N * d.K, a->w_planes, s);

@@ -59,9 +59,18 @@ __device__ __forceinline__ Philox4 philox4x32_wide(uint32_t c0, uint32_t c1, uin
 struct NoiseKeys {
   uint32_t k[14];  // k[2r] = seed.lo + r * 0x9E3779B9, k[2r+1] = seed.hi + r * 0xBB67AE85
   uint32_t c2, c3;
+  // A call counter in device memory (null: none) that is added to `offset` when the kernel starts, so
+  // that a captured CUDA graph draws fresh noise on every replay: see noise_counter().
+  const uint64_t* offset_base;
+  uint64_t offset;
+  uint32_t mix;  // what the stream contributes to c3
 };
-__host__ __device__ inline NoiseKeys make_noise_keys(uint64_t seed, uint64_t offset, uint32_t stream) {
+__host__ __device__ inline NoiseKeys make_noise_keys(uint64_t seed, uint64_t offset, uint32_t stream,
+                                                     const uint64_t* offset_base = nullptr) {
   NoiseKeys nk;
+  nk.offset_base = offset_base;
+  nk.offset = offset;
+  nk.mix = (stream * 0x85EBCA6Bu) ^ 0x5bd1e995u;
   for (int r = 0; r < 7; ++r) {
     nk.k[2 * r] = (uint32_t)seed + (uint32_t)r * 0x9E3779B9u;
     nk.k[2 * r + 1] = (uint32_t)(seed >> 32) + (uint32_t)r * 0xBB67AE85u;
@@ -70,9 +79,23 @@ __host__ __device__ inline NoiseKeys make_noise_keys(uint64_t seed, uint64_t off
   nk.c3 = (uint32_t)(offset >> 32) ^ (stream * 0x85EBCA6Bu) ^ 0x5bd1e995u;
   return nk;
 }
+// The two counter words the call contributes: the host's values, or (offset + *offset_base) when
+// the caller keeps a counter on the device.  Read once per thread; the keys stay in the constant bank.
+struct NoiseCounter {
+  uint32_t c2, c3;
+};
+__device__ __forceinline__ NoiseCounter noise_counter(const NoiseKeys& nk) {
+  NoiseCounter c = {nk.c2, nk.c3};
+  if (nk.offset_base != nullptr) {
+    const uint64_t off = nk.offset + *nk.offset_base;
+    c.c2 = (uint32_t)off;
+    c.c3 = (uint32_t)(off >> 32) ^ nk.mix;
+  }
+  return c;
+}
 // same values as normal8_fast(seed, offset, stream, group8, z)
-__device__ __forceinline__ void normal8_keyed(const NoiseKeys& nk, uint64_t group8, float z[8]) {
-  uint32_t c0 = (uint32_t)group8, c1 = (uint32_t)(group8 >> 32), c2 = nk.c2, c3 = nk.c3;
+__device__ __forceinline__ void normal8_keyed(const NoiseKeys& nk, const NoiseCounter& ctr, uint64_t group8, float z[8]) {
+  uint32_t c0 = (uint32_t)group8, c1 = (uint32_t)(group8 >> 32), c2 = ctr.c2, c3 = ctr.c3;
 #pragma unroll
   for (int r = 0; r < 7; ++r) {
     const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
@@ -87,8 +110,8 @@ __device__ __forceinline__ void normal8_keyed(const NoiseKeys& nk, uint64_t grou
   box_muller16(c3, &z[6], &z[7]);
 }
 // The four 32-bit words behind normal8_keyed(nk, group8, .): word i feeds elements 2i and 2i + 1.
-__device__ __forceinline__ void philox7_keyed(const NoiseKeys& nk, uint64_t group8, uint32_t w[4]) {
-  uint32_t c0 = (uint32_t)group8, c1 = (uint32_t)(group8 >> 32), c2 = nk.c2, c3 = nk.c3;
+__device__ __forceinline__ void philox7_keyed(const NoiseKeys& nk, const NoiseCounter& ctr, uint64_t group8, uint32_t w[4]) {
+  uint32_t c0 = (uint32_t)group8, c1 = (uint32_t)(group8 >> 32), c2 = ctr.c2, c3 = ctr.c3;
 #pragma unroll
   for (int r = 0; r < 7; ++r) {
     const uint64_t p0 = (uint64_t)0xD2511F53u * c0;

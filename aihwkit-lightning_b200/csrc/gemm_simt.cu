@@ -96,6 +96,7 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
   cfg.out_bound = ep.out_bound;
   cfg.out_res = ep.out_res;
 
+  const uint64_t noise_offset = ep.offset + (ep.offset_base != nullptr ? *ep.offset_base : 0ull);
   float sum[4][4] = {};
   for (int t = 0; t < tt.T; ++t) {
     float acc[4][4];
@@ -144,7 +145,7 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
       // of 4: one generator call instead of four, same values
       const bool quad = ep.has_noise && ep.out_noise == nullptr && (N & 3) == 0 && m < M && n0 + tx * 4 < N;
       float z4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      if (quad) normal4(ep.seed, ep.offset, 1u, (((uint64_t)t * M + m) * N + n0 + tx * 4) >> 2, z4);
+      if (quad) normal4(ep.seed, noise_offset, 1u, (((uint64_t)t * M + m) * N + n0 + tx * 4) >> 2, z4);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         int n = n0 + tx * 4 + j;
@@ -156,7 +157,7 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
           } else if (ep.has_noise) {
             uint64_t idx = ((uint64_t)t * M + m) * N + n;
             xi = ep.out_noise ? Elem<DT>::load(ep.out_noise, (int64_t)idx)
-                              : rnd<RD>(normal1(ep.seed, ep.offset, 1u, idx));
+                              : rnd<RD>(normal1(ep.seed, noise_offset, 1u, idx));
           }
           float o = tile_epilogue<RD>(acc[i][j], ir, s_col_noise[j], s_col_bound[j], xi, cfg, &keep);
           sum[i][j] = t == 0 ? fadd(0.0f, o) : rnd<RD>(fadd(sum[i][j], o));

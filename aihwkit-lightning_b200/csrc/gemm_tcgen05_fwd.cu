@@ -220,6 +220,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     const bool has_bound = kFixed ? (MODE & 4) != 0 : ep.has_bound != 0;
     const bool replay = kFixed ? false : ep.out_noise != nullptr;
     const bool no_round = kFixed ? false : ep.no_rounding != 0;
+    const NoiseCounter noise_ctr = noise_counter(p.noise);
     const bool small_codes = kFixed ? true : p.small_adc_codes != 0;
     const bool per_channel = kFixed ? false : (ep.w_amax != nullptr && (ep.noise_pc || ep.bound_pc));
     // Output noise with nothing non-linear between the tiles (no ADC, no clamp): the T independent
@@ -335,7 +336,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
               uint32_t bits[4];
               if (noise_now) {
                 const int nq = nh + g8 * 8;
-                philox7_keyed(p.noise, row_group8 + (uint32_t)((nq < N ? nq : 0) >> 3), bits);
+                philox7_keyed(p.noise, noise_ctr, row_group8 + (uint32_t)((nq < N ? nq : 0) >> 3), bits);
               }
 #pragma unroll
               for (int q4 = 0; q4 < 4; ++q4) {
@@ -378,7 +379,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                   }
                 }
               } else {
-                normal8_keyed(p.noise, row_group8 + (uint32_t)((nq < N ? nq : 0) >> 3), &z[g8 * 8]);
+                normal8_keyed(p.noise, noise_ctr, row_group8 + (uint32_t)((nq < N ? nq : 0) >> 3), &z[g8 * 8]);
               }
             }
           }
@@ -604,7 +605,7 @@ int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const 
   p.num_mb = (ep.M + BM - 1) / BM;
   p.num_nb = (ep.N + F_BN - 1) / F_BN;
   p.ep = ep;
-  p.noise = make_noise_keys(ep.seed, ep.offset, 1u);
+  p.noise = make_noise_keys(ep.seed, ep.offset, 1u, ep.offset_base);
   p.out = out;
   p.planes_b = 1;
   p.inp_res = 0.0f;
@@ -700,7 +701,7 @@ int launch_fwd_tc_f32(const void* codes16, const void* w_planes, int K, const Ti
   p.num_mb = (ep.M + BM - 1) / BM;
   p.num_nb = (ep.N + F_BN - 1) / F_BN;
   p.ep = ep;
-  p.noise = make_noise_keys(ep.seed, ep.offset, 1u);
+  p.noise = make_noise_keys(ep.seed, ep.offset, 1u, ep.offset_base);
   p.out = out;
   p.planes_b = kPlanes;
   p.inp_res = inp_res;

@@ -44,6 +44,7 @@ struct FwdEpilogueParams {
   int32_t has_noise, has_bound, has_adc, bound_pc, noise_pc, no_rounding;
   float noise_coef, out_bound, out_res;
   uint64_t seed, offset;
+  const uint64_t* offset_base;  // call counter on the device, added to offset by the kernels (null: none)
 };
 
 // Internal weight-quantiser mode next to AlQuantType: the learned per-channel range used as a
@@ -110,12 +111,13 @@ int launch_weight_modify(int dtype, const void* w, int N, int K, const TileTable
                          const void* w_amax, const float* tile_max, const int32_t* flags,
                          int quant_type, float n_states, float max_state, int noise_type,
                          float std_dev, const void* w_noise, uint64_t seed, uint64_t offset,
-                         int no_rounding, void* w_mod, cudaStream_t s);
+                         int no_rounding, void* w_mod, cudaStream_t s, const uint64_t* offset_base = nullptr);
 
 // abs-max + tile max + (per-channel-scaled) noise in one sweep; w_mod may be null when noise is off
 int launch_weight_fused(int dtype, const void* w, int N, int K, const TileTable& tt, void* w_amax,
                         float* tile_max, int noise_type, float std_dev, const void* w_noise,
-                        uint64_t seed, uint64_t offset, void* w_mod, cudaStream_t s);
+                        uint64_t seed, uint64_t offset, void* w_mod, cudaStream_t s,
+                        const uint64_t* offset_base = nullptr);
 
 // ---- SIMT GEMMs (gemm_simt.cu) ------------------------------------------------------------
 int launch_fwd_simt(int dtype, int round_dt, const void* xq, const void* w_mod, int K,

@@ -192,9 +192,11 @@ weight_modify_kernel(const void* __restrict__ w, int N, int K, TileTable tt,
                      const int32_t* __restrict__ flags, int quant_type, float n_states,
                      float max_state, int noise_type, float std_dev,
                      const void* __restrict__ w_noise, uint64_t seed, uint64_t offset,
-                     int no_rounding, void* __restrict__ w_mod, int aligned_base) {
+                     int no_rounding, void* __restrict__ w_mod, int aligned_base,
+                     const uint64_t* __restrict__ offset_base) {
   constexpr int VN = Pack<DT>::N;
   constexpr int ES = 16 / VN;
+  if (offset_base != nullptr) offset += *offset_base;  // the caller's call counter on the device
   const unsigned seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);  // rows * T < 2^31 (checked by the host)
   int lane = threadIdx.x & 31;
   if (seg >= (unsigned)N * (unsigned)tt.T) return;
@@ -257,9 +259,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 weight_fused_kernel(const void* __restrict__ w, int N, int K, TileTable tt, void* __restrict__ w_amax,
                     float* __restrict__ tile_max, int noise_type, float std_dev,
                     const void* __restrict__ w_noise, uint64_t seed, uint64_t offset,
-                    void* __restrict__ w_mod, int aligned_base) {
+                    void* __restrict__ w_mod, int aligned_base, const uint64_t* __restrict__ offset_base) {
   constexpr int VN = Pack<DT>::N;
   constexpr int ES = 16 / VN;
+  if (offset_base != nullptr) offset += *offset_base;  // the caller's call counter on the device
   const unsigned seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);  // rows * T < 2^31 (checked by the host)
   int lane = threadIdx.x & 31;
   if (seg >= (unsigned)N * (unsigned)tt.T) return;
@@ -422,6 +425,7 @@ weight_fused_stream_kernel(const uint16_t* __restrict__ w, int N, int K, int T, 
   const int lane = threadIdx.x & 31;
   const unsigned n_warps = gridDim.x * kWarpsPerBlock;
   const unsigned segs = (unsigned)N * (unsigned)T;
+  const NoiseCounter ctr = noise_counter(nk);
   unsigned seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   // the grid is sized so that n_warps is a multiple of T: a warp always meets the same tile
   const int t = (int)(seg % (unsigned)T);
@@ -446,7 +450,7 @@ weight_fused_stream_kernel(const uint16_t* __restrict__ w, int N, int K, int T, 
       for (int j = 0; j < Q; ++j) {
         const int64_t e0 = (int64_t)n * K + (int64_t)t * kTileW + (j * 32 + lane) * 8;
         float z[8];
-        normal8_keyed(nk, (uint64_t)e0 >> 3, z);
+        normal8_keyed(nk, ctr, (uint64_t)e0 >> 3, z);
         uint32_t wv[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -541,20 +545,20 @@ int launch_weight_modify(int dtype, const void* w, int N, int K, const TileTable
                          const void* w_amax, const float* tile_max, const int32_t* flags,
                          int quant_type, float n_states, float max_state, int noise_type,
                          float std_dev, const void* w_noise, uint64_t seed, uint64_t offset,
-                         int no_rounding, void* w_mod, cudaStream_t s) {
+                         int no_rounding, void* w_mod, cudaStream_t s, const uint64_t* offset_base) {
   ProfScope prof(AL_K_WEIGHT_MODIFY, s);
   int64_t segs = (int64_t)N * tt.T;
   int aligned = aligned16(w) && aligned16(w_mod) && (w_noise == nullptr || aligned16(w_noise));
   if (dtype == AL_F32)
-    weight_modify_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, flags, quant_type, n_states, max_state, noise_type, std_dev, w_noise, seed, offset, no_rounding, w_mod, aligned);
+    weight_modify_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, flags, quant_type, n_states, max_state, noise_type, std_dev, w_noise, seed, offset, no_rounding, w_mod, aligned, offset_base);
   else
-    weight_modify_kernel<kBF16><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, flags, quant_type, n_states, max_state, noise_type, std_dev, w_noise, seed, offset, no_rounding, w_mod, aligned);
+    weight_modify_kernel<kBF16><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, flags, quant_type, n_states, max_state, noise_type, std_dev, w_noise, seed, offset, no_rounding, w_mod, aligned, offset_base);
   return check_launch("weight_modify");
 }
 
 int launch_weight_fused(int dtype, const void* w, int N, int K, const TileTable& tt, void* w_amax,
                         float* tile_max, int noise_type, float std_dev, const void* w_noise,
-                        uint64_t seed, uint64_t offset, void* w_mod, cudaStream_t s) {
+                        uint64_t seed, uint64_t offset, void* w_mod, cudaStream_t s, const uint64_t* offset_base) {
   ProfScope prof(AL_K_WEIGHT_MODIFY, s);
   int64_t segs = (int64_t)N * tt.T;
   int aligned = aligned16(w) && (w_mod == nullptr || aligned16(w_mod)) && (w_noise == nullptr || aligned16(w_noise));
@@ -567,7 +571,7 @@ int launch_weight_fused(int dtype, const void* w, int N, int K, const TileTable&
   const int q = batched_q(tt, K);
   if (dtype == AL_BF16 && q > 0 && q <= 4 && aligned && w_noise == nullptr && aligned16(w_amax) &&
       (noise_type == AL_NOISE_NONE || w_mod != nullptr)) {
-    const NoiseKeys nk = make_noise_keys(seed, offset, 0u);
+    const NoiseKeys nk = make_noise_keys(seed, offset, 0u, offset_base);
     int rc = -1;
     switch (q) {
       case 1: rc = launch_weight_stream<1>(w, N, K, tt.T, w_amax, tile_max, noise_type, std_dev, nk, w_mod, s); break;
@@ -577,9 +581,9 @@ int launch_weight_fused(int dtype, const void* w, int N, int K, const TileTable&
     if (rc >= 0) return rc;  // < 0: no grid with a multiple of T warps, take the general kernel
   }
   if (dtype == AL_F32)
-    weight_fused_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, noise_type, std_dev, w_noise, seed, offset, w_mod, aligned);
+    weight_fused_kernel<kF32><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, noise_type, std_dev, w_noise, seed, offset, w_mod, aligned, offset_base);
   else
-    weight_fused_kernel<kBF16><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, noise_type, std_dev, w_noise, seed, offset, w_mod, aligned);
+    weight_fused_kernel<kBF16><<<seg_blocks(segs), kWarpsPerBlock * 32, 0, s>>>(w, N, K, tt, w_amax, tile_max, noise_type, std_dev, w_noise, seed, offset, w_mod, aligned, offset_base);
   return check_launch("weight_fused");
 }
 

@@ -148,6 +148,10 @@ typedef struct AlForwardArgs {
   int32_t x_prequantised;    /* 1: xq and ir_rows already hold the DAC's output (al_unfold2d_dac);
                                  x may then be null and the DAC stage is skipped (dynamic
                                  input ranges only)                                          */
+  const uint64_t* offset_base; /* nullable: one counter in DEVICE memory that every noise kernel of the
+                                 call adds to `offset` when it starts.  A caller that captures its
+                                 calls in a CUDA graph (where `offset` is frozen) advances this
+                                 counter between replays and so draws fresh noise every time      */
 } AlForwardArgs;
 
 typedef struct AlBackwardArgs {
