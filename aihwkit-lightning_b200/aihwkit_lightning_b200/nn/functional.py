@@ -52,6 +52,9 @@ class _Settings:
     after_wgrad = None
     # with ``after_wgrad``: SMs the GEMM that runs beside the exchange leaves unoccupied for it
     comm_sms = 0
+    # with ``after_wgrad``: SMs the weight-gradient GEMM leaves unoccupied as well (for the exchanges of
+    # the layers before it that are still in flight when it starts)
+    comm_sms_wgrad = 0
     # callable(weight_address, shape, dtype) -> Tensor or None: where the backward writes a layer's weight
     # gradient (``distributed.PeerGradientSync`` hands out views of a buffer that all replicas have mapped,
     # so that the exchange kernel can reduce it in place); None: a fresh tensor
@@ -457,7 +460,14 @@ def _analog_backward(ctx, grad_out):
             # weight-side gradients first: their exchange between replicas can then run while the
             # input gradient is still being computed
             args.grad_x = args.grad_input_range = None
-            _lib.check(lib.al_backward(desc, args, _stream(dev)))
+            if settings.comm_sms_wgrad > 0:
+                lib.al_reserve_sms(int(settings.comm_sms_wgrad))
+                try:
+                    _lib.check(lib.al_backward(desc, args, _stream(dev)))
+                finally:
+                    lib.al_reserve_sms(0)
+            else:
+                _lib.check(lib.al_backward(desc, args, _stream(dev)))
             hook(grad_w)
             args.grad_x, args.grad_input_range = _ptr(grad_x), _ptr(grad_ir)
             args.grad_w = args.grad_bias = args.grad_weight_clip = None

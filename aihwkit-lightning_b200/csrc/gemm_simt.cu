@@ -26,13 +26,74 @@ constexpr int kThreads = 256;
 // L_CONTIG: the reduction index l is the contiguous one in memory, else the block-row index i.
 template <int ROWS>
 struct BlockRegs {
-  static constexpr int kIters = (ROWS * BK + kThreads - 1) / kThreads;
-  float v[kIters];
+  static constexpr int kIters = (ROWS * BK + kThreads - 1) / kThreads;            // one element per turn
+  static constexpr int kVecIters = (ROWS * BK / 4 + kThreads - 1) / kThreads;    // four elements per turn
+  static constexpr int kRegs = kIters > 4 * kVecIters ? kIters : 4 * kVecIters;
+  float v[kRegs];
 };
 
-template <int DT, bool L_CONTIG, int ROWS>
+// four consecutive elements starting at element idx (idx a multiple of 4, base 16-byte aligned)
+template <int DT>
+__device__ __forceinline__ void load4(const void* __restrict__ p, int64_t idx, float out[4]) {
+  if (DT == kF32) {
+    const float4 f = *reinterpret_cast<const float4*>(static_cast<const float*>(p) + idx);
+    out[0] = f.x; out[1] = f.y; out[2] = f.z; out[3] = f.w;
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(p) + idx);
+    out[0] = __uint_as_float(u.x << 16); out[1] = __uint_as_float(u.x & 0xffff0000u);
+    out[2] = __uint_as_float(u.y << 16); out[3] = __uint_as_float(u.y & 0xffff0000u);
+  }
+}
+template <int DT>
+__device__ __forceinline__ void store4(void* __restrict__ p, int64_t idx, const float v[4]) {
+  if (DT == kF32) {
+    *reinterpret_cast<float4*>(static_cast<float*>(p) + idx) = make_float4(v[0], v[1], v[2], v[3]);
+  } else {
+    *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p) + idx) =
+        make_uint2((uint32_t)f32_to_bf16_bits(v[0]) | ((uint32_t)f32_to_bf16_bits(v[1]) << 16),
+                   (uint32_t)f32_to_bf16_bits(v[2]) | ((uint32_t)f32_to_bf16_bits(v[3]) << 16));
+  }
+}
+
+// VEC: the operand's contiguous dimension can be read four elements at a time (the launcher checked
+// the alignment of its base, row stride and tile starts); edges fall back to single elements.
+template <int DT, bool L_CONTIG, int ROWS, bool VEC>
 __device__ __forceinline__ void block_fetch(const void* __restrict__ p, int64_t stride_i, int64_t stride_l, int i0,
                                             int i_end, int l0, int l_end, int tid, BlockRegs<ROWS>& regs) {
+  if (VEC) {
+    constexpr int kUnits = ROWS * BK / 4;
+#pragma unroll
+    for (int r = 0; r < BlockRegs<ROWS>::kVecIters; ++r) {
+      const int u = tid + r * kThreads;
+      const int i = L_CONTIG ? u / (BK / 4) : (u % (ROWS / 4)) * 4;
+      const int l = L_CONTIG ? (u % (BK / 4)) * 4 : u / (ROWS / 4);
+      float* v = &regs.v[4 * r];
+      v[0] = v[1] = v[2] = v[3] = 0.0f;
+      if (kUnits % kThreads != 0 && u >= kUnits) continue;
+      if (L_CONTIG) {
+        if (i0 + i >= i_end) continue;
+        const int64_t base = (int64_t)(i0 + i) * stride_i + (l0 + l);
+        if (l0 + l + 3 < l_end) {
+          load4<DT>(p, base, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (l0 + l + j < l_end) v[j] = Elem<DT>::load(p, base + j);
+        }
+      } else {
+        if (l0 + l >= l_end) continue;
+        const int64_t base = (int64_t)(l0 + l) * stride_l + (i0 + i);
+        if (i0 + i + 3 < i_end) {
+          load4<DT>(p, base, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (i0 + i + j < i_end) v[j] = Elem<DT>::load(p, base + j);
+        }
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int r = 0; r < BlockRegs<ROWS>::kIters; ++r) {
     const int e = tid + r * kThreads;
@@ -45,8 +106,26 @@ __device__ __forceinline__ void block_fetch(const void* __restrict__ p, int64_t 
   }
 }
 
-template <bool L_CONTIG, int ROWS>
+template <bool L_CONTIG, int ROWS, bool VEC>
 __device__ __forceinline__ void block_commit(const BlockRegs<ROWS>& regs, float (*sm)[ROWS + kPad], int tid) {
+  if (VEC) {
+    constexpr int kUnits = ROWS * BK / 4;
+#pragma unroll
+    for (int r = 0; r < BlockRegs<ROWS>::kVecIters; ++r) {
+      const int u = tid + r * kThreads;
+      if (kUnits % kThreads != 0 && u >= kUnits) continue;
+      const int i = L_CONTIG ? u / (BK / 4) : (u % (ROWS / 4)) * 4;
+      const int l = L_CONTIG ? (u % (BK / 4)) * 4 : u / (ROWS / 4);
+      const float* v = &regs.v[4 * r];
+      if (L_CONTIG) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sm[l + j][i] = v[j];
+      } else {
+        *reinterpret_cast<float4*>(&sm[l][i]) = make_float4(v[0], v[1], v[2], v[3]);
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int r = 0; r < BlockRegs<ROWS>::kIters; ++r) {
     const int e = tid + r * kThreads;
@@ -76,10 +155,10 @@ __device__ __forceinline__ void mac_block(const float (*As)[TBM + kPad], const f
 // out[m, n] = sum_t stage_t( xq[m, tile t] . w_mod[n, tile t] ) + bias[n]
 // BN in {16, 32, 64}: a block narrower than 64 is only launched when it covers all of N, so that
 // every 32-bit word of the keep mask has one writer.
-template <int DT, int RD, int BN>
+template <int DT, int RD, int BN, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int K, TileTable tt,
-                FwdEpilogueParams ep, void* __restrict__ out) {
+                FwdEpilogueParams ep, void* __restrict__ out, int vec_out) {
   constexpr int BM = kBlockElems / BN, TX = BN / 4;
   __shared__ __align__(16) float As[BK][BM + kPad];
   __shared__ __align__(16) float Bs[BK][BN + kPad];
@@ -107,15 +186,15 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
     const int lo = tt.lo(t), hi = tt.hi(t);
     BlockRegs<BM> ra;
     BlockRegs<BN> rb;
-    block_fetch<DT, true, BM>(xq, K, 1, m0, M, lo, hi, tid, ra);
-    block_fetch<DT, true, BN>(w_mod, K, 1, n0, N, lo, hi, tid, rb);
+    block_fetch<DT, true, BM, VEC>(xq, K, 1, m0, M, lo, hi, tid, ra);
+    block_fetch<DT, true, BN, VEC>(w_mod, K, 1, n0, N, lo, hi, tid, rb);
     for (int k0 = lo; k0 < hi; k0 += BK) {
-      block_commit<true, BM>(ra, As, tid);
-      block_commit<true, BN>(rb, Bs, tid);
+      block_commit<true, BM, VEC>(ra, As, tid);
+      block_commit<true, BN, VEC>(rb, Bs, tid);
       __syncthreads();
       if (k0 + BK < hi) {
-        block_fetch<DT, true, BM>(xq, K, 1, m0, M, k0 + BK, hi, tid, ra);
-        block_fetch<DT, true, BN>(w_mod, K, 1, n0, N, k0 + BK, hi, tid, rb);
+        block_fetch<DT, true, BM, VEC>(xq, K, 1, m0, M, k0 + BK, hi, tid, ra);
+        block_fetch<DT, true, BN, VEC>(w_mod, K, 1, n0, N, k0 + BK, hi, tid, rb);
       }
       mac_block<BM, BN>(As, Bs, ty, tx, acc);
       __syncthreads();
@@ -180,14 +259,20 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+    float v[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       int n = n0 + tx * 4 + j;
-      if (m < M && n < N) {
-        float v = sum[i][j];
-        if (ep.bias) v = fadd(rnd<RD>(v), Elem<DT>::load(ep.bias, n));
-        Elem<DT>::store(out, (int64_t)m * N + n, v);
-      }
+      v[j] = sum[i][j];
+      if (ep.bias && n < N) v[j] = fadd(rnd<RD>(v[j]), Elem<DT>::load(ep.bias, n));
+    }
+    if (vec_out && n0 + tx * 4 + 3 < N) {
+      store4<DT>(out, (int64_t)m * N + n0 + tx * 4, v);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (n0 + tx * 4 + j < N) Elem<DT>::store(out, (int64_t)m * N + n0 + tx * 4 + j, v[j]);
     }
   }
 }
@@ -197,7 +282,7 @@ fwd_simt_kernel(const void* __restrict__ xq, const void* __restrict__ w_mod, int
 //   wgrad: i = n, l = m, A = g^T     (i contiguous), B = xq    (j contiguous), C = grad_w
 // blockIdx.z = t * splits + s: split s reduces l over [s * chunk, (s + 1) * chunk) and, when
 // splits > 1, stores its fp32 partial block to partial[s][i][column] instead of C.
-template <int DT, bool WGRAD, int TBM, int TBN>
+template <int DT, bool WGRAD, int TBM, int TBN, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
                 const uint32_t* __restrict__ keep_mask, int mask_words, int M, int K, int N,
@@ -229,14 +314,14 @@ bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
   BlockRegs<TBM> ra;
   BlockRegs<TBN> rb;
   auto fetch = [&](int l0) {
-    if (WGRAD) block_fetch<DT, false, TBM>(g, 1, N, i0, I, l0, l_end, tid, ra);
-    else block_fetch<DT, true, TBM>(g, N, 1, i0, I, l0, l_end, tid, ra);
-    block_fetch<DT, false, TBN>(b_op, 1, K, j0, hi, l0, l_end, tid, rb);
+    if (WGRAD) block_fetch<DT, false, TBM, VEC>(g, 1, N, i0, I, l0, l_end, tid, ra);
+    else block_fetch<DT, true, TBM, VEC>(g, N, 1, i0, I, l0, l_end, tid, ra);
+    block_fetch<DT, false, TBN, VEC>(b_op, 1, K, j0, hi, l0, l_end, tid, rb);
   };
   if (l_begin < l_end) fetch(l_begin);
   for (int l0 = l_begin; l0 < l_end; l0 += BK) {
-    block_commit<!WGRAD, TBM>(ra, As, tid);
-    block_commit<false, TBN>(rb, Bs, tid);
+    block_commit<!WGRAD, TBM, VEC>(ra, As, tid);
+    block_commit<false, TBN, VEC>(rb, Bs, tid);
     __syncthreads();
     if (l0 + BK < l_end) fetch(l0 + BK);
     if (keep_mask != nullptr) {
@@ -258,10 +343,17 @@ bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     int gi = i0 + ty * 4 + i;
+    if (gi >= I) continue;
+    const int gj0 = j0 + tx * 4;
+    if (VEC && gj0 + 3 < hi) {
+      if (splits > 1) store4<kF32>(partial, ((int64_t)split * I + gi) * K + gj0, acc[i]);
+      else store4<DT>(c_out, (int64_t)gi * K + gj0, acc[i]);
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      int gj = j0 + tx * 4 + j;
-      if (gi < I && gj < hi) {
+      int gj = gj0 + j;
+      if (gj < hi) {
         if (splits > 1) partial[((int64_t)split * I + gi) * K + gj] = acc[i][j];
         else Elem<DT>::store(c_out, (int64_t)gi * K + gj, acc[i][j]);
       }
@@ -280,6 +372,19 @@ sum_partials_kernel(const float* __restrict__ partial, int splits, int64_t count
   Elem<DT>::store(c_out, e, v);
 }
 
+// Can rows of a [.., K] matrix be read four elements at a time from every tile start?
+inline bool vec4_rows(const void* p, int dtype, int K, const TileTable& tt) {
+  const uintptr_t align = dtype == AL_F32 ? 16 : 8;
+  if (p == nullptr || reinterpret_cast<uintptr_t>(p) % align != 0 || K % 4 != 0) return false;
+  for (int t = 0; t < tt.T; ++t)
+    if (tt.lo(t) % 4 != 0) return false;
+  return true;
+}
+inline bool vec4_plain(const void* p, int dtype, int cols) {
+  const uintptr_t align = dtype == AL_F32 ? 16 : 8;
+  return p != nullptr && reinterpret_cast<uintptr_t>(p) % align == 0 && cols % 4 == 0;
+}
+
 inline int max_tile_width(const TileTable& tt) {
   int w = 0;
   for (int t = 0; t < tt.T; ++t) w = tt.hi(t) - tt.lo(t) > w ? tt.hi(t) - tt.lo(t) : w;
@@ -291,12 +396,17 @@ void fwd_simt_launch(int dtype, int round_dt, const void* xq, const void* w_mod,
                      const FwdEpilogueParams& ep, void* out, cudaStream_t s) {
   constexpr int BM = kBlockElems / BN;
   dim3 grid((ep.M + BM - 1) / BM, (ep.N + BN - 1) / BN);
-  if (dtype == AL_F32)
-    fwd_simt_kernel<kF32, kF32, BN><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out);
-  else if (round_dt == AL_BF16)
-    fwd_simt_kernel<kBF16, kBF16, BN><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out);
-  else
-    fwd_simt_kernel<kBF16, kF32, BN><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out);
+  const int vec_k = vec4_rows(xq, dtype, K, tt) && vec4_rows(w_mod, dtype, K, tt);
+  const int vec_out = vec4_plain(out, dtype, ep.N);
+#define AL_FWD_SIMT(DT_, RD_)                                                                                   \
+  do {                                                                                                           \
+    if (vec_k) fwd_simt_kernel<DT_, RD_, BN, true><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out, vec_out); \
+    else fwd_simt_kernel<DT_, RD_, BN, false><<<grid, kThreads, 0, s>>>(xq, w_mod, K, tt, ep, out, vec_out);      \
+  } while (0)
+  if (dtype == AL_F32) AL_FWD_SIMT(kF32, kF32);
+  else if (round_dt == AL_BF16) AL_FWD_SIMT(kBF16, kBF16);
+  else AL_FWD_SIMT(kBF16, kF32);
+#undef AL_FWD_SIMT
 }
 
 template <int TBM, int TBN>
@@ -304,12 +414,22 @@ void wgrad_simt_launch(int dtype, const void* g, const void* xq, const uint32_t*
                        int K, int N, const TileTable& tt, int splits, int chunk, float* partial, void* grad_w,
                        cudaStream_t s) {
   dim3 grid((N + TBM - 1) / TBM, (max_tile_width(tt) + TBN - 1) / TBN, tt.T * splits);
-  if (dtype == AL_F32)
-    bwd_simt_kernel<kF32, true, TBM, TBN><<<grid, kThreads, 0, s>>>(g, xq, keep_mask, mask_words, M, K, N, tt, splits,
-                                                                    chunk, partial, grad_w);
-  else
-    bwd_simt_kernel<kBF16, true, TBM, TBN><<<grid, kThreads, 0, s>>>(g, xq, keep_mask, mask_words, M, K, N, tt,
-                                                                     splits, chunk, partial, grad_w);
+  // vec_k: rows of xq and of grad_w (or its fp32 partials) from every tile start; vec_n: rows of g
+  const int vec_k = vec4_rows(xq, dtype, K, tt) && vec4_rows(grad_w, dtype, K, tt) &&
+                    (splits == 1 || vec4_rows(partial, AL_F32, K, tt));
+  const int vec_n = vec4_plain(g, dtype, N);
+#define AL_WGRAD_SIMT(DT_, VEC_)                                                                              \
+  bwd_simt_kernel<DT_, true, TBM, TBN, VEC_><<<grid, kThreads, 0, s>>>(g, xq, keep_mask, mask_words, M, K, N, tt, \
+                                                                       splits, chunk, partial, grad_w)
+  const bool vec = vec_k && vec_n;
+  if (dtype == AL_F32) {
+    if (vec) AL_WGRAD_SIMT(kF32, true);
+    else AL_WGRAD_SIMT(kF32, false);
+  } else {
+    if (vec) AL_WGRAD_SIMT(kBF16, true);
+    else AL_WGRAD_SIMT(kBF16, false);
+  }
+#undef AL_WGRAD_SIMT
 }
 
 // Number of CTAs the reduction over the batch rows is split over: enough to put two waves of
@@ -358,12 +478,20 @@ int launch_dgrad_simt(int dtype, const void* g, const void* w_mod, const uint32_
                       cudaStream_t s) {
   ProfScope prof(AL_K_DGRAD_GEMM, s);
   dim3 grid((M + 63) / 64, (max_tile_width(tt) + 63) / 64, tt.T);
-  if (dtype == AL_F32)
-    bwd_simt_kernel<kF32, false, 64, 64><<<grid, kThreads, 0, s>>>(g, w_mod, keep_mask, mask_words, M, K, N, tt, 1, N,
-                                                                  nullptr, grad_x);
-  else
-    bwd_simt_kernel<kBF16, false, 64, 64><<<grid, kThreads, 0, s>>>(g, w_mod, keep_mask, mask_words, M, K, N, tt, 1, N,
-                                                                   nullptr, grad_x);
+  const int vec_k = vec4_rows(w_mod, dtype, K, tt) && vec4_rows(grad_x, dtype, K, tt);
+  const int vec_n = vec4_plain(g, dtype, N);
+#define AL_DGRAD_SIMT(DT_, VEC_)                                                                                \
+  bwd_simt_kernel<DT_, false, 64, 64, VEC_><<<grid, kThreads, 0, s>>>(g, w_mod, keep_mask, mask_words, M, K, N, tt, 1, \
+                                                                      N, nullptr, grad_x)
+  const bool vec = vec_k && vec_n;
+  if (dtype == AL_F32) {
+    if (vec) AL_DGRAD_SIMT(kF32, true);
+    else AL_DGRAD_SIMT(kF32, false);
+  } else {
+    if (vec) AL_DGRAD_SIMT(kBF16, true);
+    else AL_DGRAD_SIMT(kBF16, false);
+  }
+#undef AL_DGRAD_SIMT
   return check_launch("dgrad_simt");
 }
 

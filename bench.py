@@ -328,6 +328,7 @@ def release_gradient_sync():
     F.settings.after_wgrad = None
     F.settings.grad_w_alloc = None
     F.settings.comm_sms = 0
+    F.settings.comm_sms_wgrad = 0
 
 
 def timed_steps(ctx, fn, steps, between=None):
@@ -506,7 +507,7 @@ def run_c3(args, ctx, layers=32, steps=3, warmup=2, seq=2048, micro_batch=4):
     from torch.nn import functional as TF
 
     from aihwkit_lightning_b200 import _lib
-    from aihwkit_lightning_b200.distributed import rank_seed
+    from aihwkit_lightning_b200.distributed import PeerGradientSync, rank_seed
     from aihwkit_lightning_b200.nn import AnalogLinear, convert_to_analog
     from aihwkit_lightning_b200.nn import functional as F
     from aihwkit_lightning_b200.optim import AnalogOptimizer
@@ -528,6 +529,11 @@ def run_c3(args, ctx, layers=32, steps=3, warmup=2, seq=2048, micro_batch=4):
     sync, how = None, None
     if world > 1:
         sync, how = make_gradient_sync(ctx, model.parameters())
+        if isinstance(sync, PeerGradientSync):
+            # SMs the backward GEMMs leave to the exchange kernels that run beside them
+            F.settings.comm_sms = int(os.environ.get("BENCH_C3_COMM_SMS", "0"))
+            F.settings.comm_sms_wgrad = int(os.environ.get("BENCH_C3_COMM_SMS_WGRAD", "0"))
+            how += f"; backward GEMMs leave {F.settings.comm_sms} (input gradient) / {F.settings.comm_sms_wgrad} (weight gradient) SMs free"
     gen = torch.Generator().manual_seed(1000 + rank)
     ids_host = torch.randint(0, vocab, (micro_batch, seq), generator=gen).pin_memory()
     labels_host = torch.randint(0, vocab, (micro_batch, seq), generator=gen).pin_memory()
