@@ -340,6 +340,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
 
   // 2. DAC: x -> xq (+ per-row ranges in dynamic mode)
   const void* xq = a->x;
+  bool tile_max_zeroed = false;
   if (prequantised) {
     xq = a->xq;
   } else if (d.ir_mode != AL_IR_OFF && !smallm_dac) {
@@ -347,8 +348,14 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
       set_error("al_forward: xq / ir_rows workspace missing");
       return AL_ERR_BAD_ARGUMENT;
     }
+    // the fused weight pre-pass that follows accumulates tile maxima into w_tile_max: the DAC kernel
+    // clears those words on its way (no memset between the two kernels)
+    const bool fused_weights_next = !smallm && d.clip_type != AL_CLIP_LEARNABLE_PER_CHANNEL && needs_wmax(dv) &&
+                                    dv.weight_quant == AL_QUANT_NONE && dv.weight_noise != AL_NOISE_ADD_NORMAL &&
+                                    a->w_amax && a->w_tile_max;
     rc = launch_dac(d.dtype, a->x, d.M, d.K, tt, d.ir_mode == AL_IR_FAST ? AL_IR_STATIC : d.ir_mode, ir_static, dv.has_dac ? dv.inp_res : -1.0f,
-                    d.no_rounding, a->xq, a->ir_rows, a->codes, s, tc_f32 ? a->codes16 : nullptr);
+                    d.no_rounding, a->xq, a->ir_rows, a->codes, s, tc_f32 ? a->codes16 : nullptr,
+                    fused_weights_next ? a->w_tile_max : nullptr, 2 * d.T, &tile_max_zeroed);
     if (rc) return rc;
     xq = a->xq;
   }
@@ -413,7 +420,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
       // every scale the modifier needs is the segment's own abs-max: one sweep over w
       rc = launch_weight_fused(d.dtype, a->w, d.N, d.K, tt, a->w_amax, tile_max, dv.weight_noise,
                                dv.std_dev, a->w_noise, a->seed, a->offset, modifies ? a->w_mod : nullptr, s,
-                               a->offset_base);
+                               a->offset_base, tile_max_zeroed);
       if (rc) return rc;
     } else {
       rc = launch_abs_max_tiles(d.dtype, a->w, d.N, d.K, tt, a->w_amax, s);

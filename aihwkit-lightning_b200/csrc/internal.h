@@ -93,7 +93,8 @@ int launch_clip_weights(int dtype, void* w, int rows, int cols, int clip_type, f
 // tensor-core GEMMs of an fp32 layer
 int launch_dac(int dtype, const void* x, int M, int K, const TileTable& tt, int ir_mode,
                const void* ir_static, float inp_res, int no_rounding, void* xq, void* ir_rows,
-               void* codes, cudaStream_t s, void* codes16 = nullptr);
+               void* codes, cudaStream_t s, void* codes16 = nullptr,
+               void* zero_words = nullptr, int zero_count = 0, bool* zeroed = nullptr);
 
 // ---- bf16 planes of fp32 operands (split_kernels.cu) ----------------------------------------
 // An fp32 operand v travels to the tensor cores as kPlanes bf16 planes p0 = RN(v), p1 = RN(v - p0), ...
@@ -117,7 +118,7 @@ int launch_weight_modify(int dtype, const void* w, int N, int K, const TileTable
 int launch_weight_fused(int dtype, const void* w, int N, int K, const TileTable& tt, void* w_amax,
                         float* tile_max, int noise_type, float std_dev, const void* w_noise,
                         uint64_t seed, uint64_t offset, void* w_mod, cudaStream_t s,
-                        const uint64_t* offset_base = nullptr);
+                        const uint64_t* offset_base = nullptr, bool tile_max_zeroed = false);
 
 // ---- SIMT GEMMs (gemm_simt.cu) ------------------------------------------------------------
 int launch_fwd_simt(int dtype, int round_dt, const void* xq, const void* w_mod, int K,

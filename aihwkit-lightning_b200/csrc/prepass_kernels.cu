@@ -358,7 +358,10 @@ template <int Q>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 dac_batched_kernel(const uint16_t* __restrict__ x, int M, int K, int T, int ir_mode,
                    const uint16_t* __restrict__ ir_static, float inp_res, uint16_t* __restrict__ xq,
-                   uint16_t* __restrict__ ir_rows) {
+                   uint16_t* __restrict__ ir_rows, uint32_t* __restrict__ zero_words, int zero_count) {
+  // side job of the first block: clear the words the weight pre-pass that follows accumulates into
+  // (saves that pass a memset between the two kernels)
+  if (blockIdx.x == 0 && (int)threadIdx.x < zero_count) zero_words[threadIdx.x] = 0u;
   constexpr int kTiles = kBatchVecs / Q;  // tiles per warp
   constexpr int kTileW = 256 * Q;
   const int batches = (T + kTiles - 1) / kTiles;
@@ -510,8 +513,9 @@ int batched_q(const TileTable& tt, int K) {
 
 int launch_dac(int dtype, const void* x, int M, int K, const TileTable& tt, int ir_mode,
                const void* ir_static, float inp_res, int no_rounding, void* xq, void* ir_rows,
-               void* codes, cudaStream_t s, void* codes16) {
+               void* codes, cudaStream_t s, void* codes16, void* zero_words, int zero_count, bool* zeroed) {
   ProfScope prof(AL_K_DAC, s);
+  if (zeroed) *zeroed = false;
   int64_t segs = (int64_t)M * tt.T;
   int aligned = aligned16(x) && aligned16(xq);
   // |code| <= max(inp_res, 1/inp_res)/2 + 1: the guard-free rint needs that below 2^22
@@ -526,11 +530,14 @@ int launch_dac(int dtype, const void* x, int M, int K, const TileTable& tt, int 
     const uint16_t* irs = reinterpret_cast<const uint16_t*>(ir_static);
     uint16_t* xqs = reinterpret_cast<uint16_t*>(xq);
     uint16_t* irr = reinterpret_cast<uint16_t*>(ir_rows);
+    uint32_t* zw = reinterpret_cast<uint32_t*>(zero_words);
+    if (zw == nullptr || zero_count > kWarpsPerBlock * 32) zero_count = 0;
+    if (zeroed) *zeroed = zero_count > 0;
     switch (q) {
-      case 1: dac_batched_kernel<1><<<blocks, kWarpsPerBlock * 32, 0, s>>>(xs, M, K, tt.T, ir_mode, irs, inp_res, xqs, irr); break;
-      case 2: dac_batched_kernel<2><<<blocks, kWarpsPerBlock * 32, 0, s>>>(xs, M, K, tt.T, ir_mode, irs, inp_res, xqs, irr); break;
-      case 4: dac_batched_kernel<4><<<blocks, kWarpsPerBlock * 32, 0, s>>>(xs, M, K, tt.T, ir_mode, irs, inp_res, xqs, irr); break;
-      default: dac_batched_kernel<8><<<blocks, kWarpsPerBlock * 32, 0, s>>>(xs, M, K, tt.T, ir_mode, irs, inp_res, xqs, irr); break;
+      case 1: dac_batched_kernel<1><<<blocks, kWarpsPerBlock * 32, 0, s>>>(xs, M, K, tt.T, ir_mode, irs, inp_res, xqs, irr, zw, zero_count); break;
+      case 2: dac_batched_kernel<2><<<blocks, kWarpsPerBlock * 32, 0, s>>>(xs, M, K, tt.T, ir_mode, irs, inp_res, xqs, irr, zw, zero_count); break;
+      case 4: dac_batched_kernel<4><<<blocks, kWarpsPerBlock * 32, 0, s>>>(xs, M, K, tt.T, ir_mode, irs, inp_res, xqs, irr, zw, zero_count); break;
+      default: dac_batched_kernel<8><<<blocks, kWarpsPerBlock * 32, 0, s>>>(xs, M, K, tt.T, ir_mode, irs, inp_res, xqs, irr, zw, zero_count); break;
     }
     return check_launch("dac_batched");
   }
@@ -558,12 +565,14 @@ int launch_weight_modify(int dtype, const void* w, int N, int K, const TileTable
 
 int launch_weight_fused(int dtype, const void* w, int N, int K, const TileTable& tt, void* w_amax,
                         float* tile_max, int noise_type, float std_dev, const void* w_noise,
-                        uint64_t seed, uint64_t offset, void* w_mod, cudaStream_t s, const uint64_t* offset_base) {
+                        uint64_t seed, uint64_t offset, void* w_mod, cudaStream_t s, const uint64_t* offset_base,
+                        bool tile_max_zeroed) {
   ProfScope prof(AL_K_WEIGHT_MODIFY, s);
   int64_t segs = (int64_t)N * tt.T;
   int aligned = aligned16(w) && (w_mod == nullptr || aligned16(w_mod)) && (w_noise == nullptr || aligned16(w_noise));
-  // tile_max[T] floats followed by T int32 flags (zero: the discretiser is off on this path)
-  cudaError_t e = cudaMemsetAsync(tile_max, 0, 2 * sizeof(float) * tt.T, s);
+  // tile_max[T] floats followed by T int32 flags (zero: the discretiser is off on this path); cleared
+  // here unless the DAC kernel before this one already did it
+  cudaError_t e = tile_max_zeroed ? cudaSuccess : cudaMemsetAsync(tile_max, 0, 2 * sizeof(float) * tt.T, s);
   if (e != cudaSuccess) {
     set_error("weight_fused: memset: %s", cudaGetErrorString(e));
     return AL_ERR_CUDA;
