@@ -528,10 +528,12 @@ def run_c3(args, ctx, layers=32, steps=3, warmup=2, seq=2048, micro_batch=4):
                           capturable=world == 1)
     sync, how = None, None
     if world > 1:
-        sync, how = make_gradient_sync(ctx, model.parameters())
+        # 8 CTAs of exchange beside the backward, 8 SMs left to them by the input-gradient GEMMs: on 4 GPUs
+        # 288 ms per step against 293 with 16 CTAs and no SMs left free (0 / 8 / 16 SMs left by the
+        # weight-gradient GEMMs as well, and the switch-reduction form, measured within 2 ms of that)
+        sync, how = make_gradient_sync(ctx, model.parameters(), n_ctas=int(os.environ.get("BENCH_C3_COMM_CTAS", "8")))
         if isinstance(sync, PeerGradientSync):
-            # SMs the backward GEMMs leave to the exchange kernels that run beside them
-            F.settings.comm_sms = int(os.environ.get("BENCH_C3_COMM_SMS", "0"))
+            F.settings.comm_sms = int(os.environ.get("BENCH_C3_COMM_SMS", "8"))
             F.settings.comm_sms_wgrad = int(os.environ.get("BENCH_C3_COMM_SMS_WGRAD", "0"))
             how += f"; backward GEMMs leave {F.settings.comm_sms} (input gradient) / {F.settings.comm_sms_wgrad} (weight gradient) SMs free"
     gen = torch.Generator().manual_seed(1000 + rank)
