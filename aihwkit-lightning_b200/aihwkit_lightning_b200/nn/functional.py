@@ -405,8 +405,10 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
     ctx.ir_needs_grad = static and input_range is not None and input_range.requires_grad
     ctx.learn_clip = learn_clip
     if needs_grad:
-        # with bf16 planes the backward GEMMs read those: the fp32 copies need not be kept
-        ctx.save_for_backward(x2d if static else None, None if planes else xq, None if planes else w_mod, ir_rows,
+        # with bf16 planes the backward GEMMs read those: the fp32 copies need not be kept, except the (small)
+        # modified weights of a layer with fewer than 64 channels, whose input gradient runs on the CUDA cores
+        ctx.save_for_backward(x2d if static else None, None if planes else xq,
+                              None if (planes and n >= 64) else w_mod, ir_rows,
                               keep_mask, w if learn_clip else None, lwc, codes16, w_planes)
     return out.view(*inp.shape[:-1], n) if prequant is None else out
 

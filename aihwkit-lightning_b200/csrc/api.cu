@@ -156,7 +156,9 @@ static bool pick_tc(const AlDesc& d, const TileTable& tt, bool backward) {
 static bool pick_tc_f32(const AlDesc& d, const TileTable& tt) {
   if (d.engine == AL_ENGINE_SIMT || !tc_f32_supported(d, tt)) return false;
   if (d.engine >= AL_ENGINE_TCGEN05) return true;
-  return d.M >= 128 && d.N >= 128 && d.K >= 128 && (double)d.M * d.N * d.K >= 134217728.0;
+  // few output channels (convolutions): the 128-column blocks are mostly empty, but the forward and the
+  // weight gradient still run 1.5-3 times faster than on the CUDA cores once there are enough rows
+  return d.M >= 128 && d.N >= 16 && d.K >= 128 && (double)d.M * d.N * d.K >= 134217728.0;
 }
 
 }  // namespace al
@@ -568,7 +570,10 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
       set_error("al_backward: w_mod missing");
       return AL_ERR_BAD_ARGUMENT;
     }
-    rc = tc_f32 ? launch_dgrad_tc_f32(a->g_planes, sets_d, a->w_planes, d.M, d.K, d.N, tt, pairing, a->grad_x, s)
+    // an fp32 layer with fewer than 64 output channels: the input gradient reduces over those few channels
+    // only, which the CUDA-core kernel does faster (52 against 76 us at 65536 x 288 x 32); it needs w_mod
+    const bool dgrad_tc_f32 = tc_f32 && (d.N >= 64 || d.engine >= AL_ENGINE_TCGEN05 || !a->w_mod);
+    rc = dgrad_tc_f32 ? launch_dgrad_tc_f32(a->g_planes, sets_d, a->w_planes, d.M, d.K, d.N, tt, pairing, a->grad_x, s)
          : tc   ? launch_dgrad_tc(a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, pairing, a->grad_x, s)
                 : launch_dgrad_simt(d.dtype, a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, a->grad_x, s);
     if (rc) return rc;
@@ -587,16 +592,33 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
     return AL_ERR_BAD_ARGUMENT;
   }
   if (a->grad_w && tc_f32) {
+    // few output blocks (layers with few channels): the reduction over the batch rows is split over CTAs
+    // exactly as the CUDA-core kernel splits it, into the same caller-sized buffer
+    int w_splits = 1, w_chunk = 0;
+    wgrad_simt_plan(d.M, d.K, d.N, d.T, &w_splits, &w_chunk);
+    float* w_partial = nullptr;
+    if (w_splits > 1) {
+      const int64_t fixed = backward_reduce_floats(d.M, d.N, d.T);
+      w_partial = a->reduce_scratch ? a->reduce_scratch + fixed : nullptr;
+      const int64_t capacity = a->reduce_scratch ? a->reduce_scratch_floats - fixed : 0;
+      if (w_partial == nullptr || (int64_t)w_splits * d.N * d.K > capacity) {
+        set_error("al_backward: the partial-sum buffer holds %lld floats, %d splits x %d x %d need %lld",
+                  (long long)capacity, w_splits, d.N, d.K, (long long)w_splits * d.N * d.K);
+        return AL_ERR_BAD_ARGUMENT;
+      }
+    }
     if (d.ir_mode == AL_IR_DYNAMIC) {
       // per-row DAC steps: a second set of planes, one per tile, with the step (and the mask) folded in
       uint16_t* planes_w = static_cast<uint16_t*>(a->g_planes) + plane_elems * sets_d;
       rc = launch_split_planes_grad(static_cast<const float*>(a->grad_out), d.M, d.N, mask, mask_words,
                               static_cast<const float*>(a->ir_rows), 1, dv.inp_res, d.T, planes_w, s);
       if (rc) return rc;
-      rc = launch_wgrad_tc_f32(planes_w, d.T, a->codes16, d.M, d.K, d.N, tt, nullptr, 0.0f, pairing, a->grad_w, s);
+      rc = launch_wgrad_tc_f32(planes_w, d.T, a->codes16, d.M, d.K, d.N, tt, nullptr, 0.0f, pairing, a->grad_w, s,
+                               w_splits, w_partial);
     } else {
       rc = launch_wgrad_tc_f32(a->g_planes, sets_d, a->codes16, d.M, d.K, d.N, tt,
-                               static_cast<const float*>(a->ir_rows), dv.inp_res, pairing, a->grad_w, s);
+                               static_cast<const float*>(a->ir_rows), dv.inp_res, pairing, a->grad_w, s, w_splits,
+                               w_partial);
     }
     if (rc) return rc;
   } else if (a->grad_w) {

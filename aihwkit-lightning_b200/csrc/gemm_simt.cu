@@ -449,6 +449,13 @@ int wgrad_splits(int M, int K, int N, int T) {
 
 }  // namespace
 
+int launch_sum_partials(int dtype, const float* partial, int splits, int64_t count, void* c_out, cudaStream_t s) {
+  const unsigned blocks = (unsigned)((count + 255) / 256);
+  if (dtype == AL_F32) sum_partials_kernel<kF32><<<blocks, 256, 0, s>>>(partial, splits, count, c_out);
+  else sum_partials_kernel<kBF16><<<blocks, 256, 0, s>>>(partial, splits, count, c_out);
+  return check_launch("sum_partials");
+}
+
 void wgrad_simt_plan(int M, int K, int N, int layer_T, int* splits, int* chunk_rows) {
   const int s = wgrad_splits(M, K, N, layer_T);
   const int per = (M + s - 1) / s;

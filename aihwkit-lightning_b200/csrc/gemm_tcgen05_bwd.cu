@@ -36,6 +36,11 @@ struct BwdTcParams {
   int32_t f32_out;          // C is fp32 (else bf16)
   const float* c_scale_ir;  // [T] input ranges: C[:, tile t] is multiplied by the DAC step of tile t (null: no scaling)
   float inp_res;
+  // Reduction split over CTAs (single-CTA kernel, no mask): an output block is computed `splits` times,
+  // copy sp over the l-steps [sp * split_lsteps, (sp + 1) * split_lsteps), and stored as fp32 to
+  // partial[sp][I][K]; a second kernel adds the copies in the order of sp.  1: no split.
+  int32_t splits, split_lsteps;
+  float* partial;
 };
 
 // r += the 32 columns of the cross-term accumulator at taddr (fp32, round to nearest)
@@ -52,10 +57,10 @@ __device__ __forceinline__ void add_cross_terms(uint32_t taddr, uint32_t r[32]) 
 }
 
 // 32 accumulator columns of one row -> C (bf16 or fp32), columns jc .. jc + 31 clipped at j_end
-__device__ __forceinline__ void store_c_row(const BwdTcParams& p, int64_t row, int jc, int j_end, const uint32_t r[32],
-                                            float scale) {
-  if (p.f32_out) {
-    float* dst = reinterpret_cast<float*>(p.c_out) + row * p.K + jc;
+__device__ __forceinline__ void store_c_row(void* c_out, bool f32_out, int ld, int64_t row, int jc, int j_end,
+                                            const uint32_t r[32], float scale) {
+  if (f32_out) {
+    float* dst = reinterpret_cast<float*>(c_out) + row * ld + jc;
 #pragma unroll
     for (int v = 0; v < 8; ++v)
       if (jc + v * 4 < j_end)
@@ -63,7 +68,7 @@ __device__ __forceinline__ void store_c_row(const BwdTcParams& p, int64_t row, i
             make_float4(__uint_as_float(r[v * 4]) * scale, __uint_as_float(r[v * 4 + 1]) * scale,
                         __uint_as_float(r[v * 4 + 2]) * scale, __uint_as_float(r[v * 4 + 3]) * scale);
   } else {
-    uint16_t* dst = reinterpret_cast<uint16_t*>(p.c_out) + row * p.K + jc;
+    uint16_t* dst = reinterpret_cast<uint16_t*>(c_out) + row * ld + jc;
 #pragma unroll
     for (int v = 0; v < 4; ++v)
       if (jc + v * 8 < j_end)
@@ -108,7 +113,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool masked = p.keep_mask != nullptr;
   const bool split_acc = p.products > 1;
-  const int num_work = p.num_ib * p.T * p.num_jb;
+  const int per_split = p.num_ib * p.T * p.num_jb;
+  const int num_work = per_split * p.splits;  // item w: copy w / per_split of output block w % per_split
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < B_STAGES; ++s) {
@@ -138,13 +144,15 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       uint32_t it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-        const int ib = w / (p.T * p.num_jb);
-        const int rem = w % (p.T * p.num_jb);
+        const int sp = w / per_split, blk = w - sp * per_split;
+        const int ib = blk / (p.T * p.num_jb);
+        const int rem = blk % (p.T * p.num_jb);
         const int t = rem / p.num_jb, jb = rem % p.num_jb;
         const int j0 = t * p.tile_w + jb * B_BN;
+        const int ls0 = sp * p.split_lsteps, ls1 = min(ls0 + p.split_lsteps, p.lsteps);
         for (int q = 0; q < p.products && ok; ++q) {
           const int plane_a = p.pa[q] + t * p.a_planes_per_tile, plane_b = p.pb[q];
-          for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
+          for (int ls = ls0; ls < ls1; ++ls, ++it) {
             const int s = it % B_STAGES;
             const uint32_t ph = (it / B_STAGES) & 1u;
             if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag)) {
@@ -201,11 +209,13 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           break;
         }
         tc_fence_after();
-        const int steps = p.lsteps * p.products;  // every plane product runs over the whole reduction
+        const int sp = w / per_split;
+        const int nls = min((sp + 1) * p.split_lsteps, p.lsteps) - sp * p.split_lsteps;  // this copy's l-steps
+        const int steps = nls * p.products;  // every plane product runs over the whole range
         for (int ls = 0; ls < steps; ++ls, ++it) {
-          const bool cross = split_acc && ls >= p.lsteps;
+          const bool cross = split_acc && ls >= nls;
           const uint32_t d_tmem = tmem_base + (uint32_t)((cross ? 1 : b) * B_BN);
-          const bool first = ls == 0 || (split_acc && ls == p.lsteps);
+          const bool first = ls == 0 || (split_acc && ls == nls);
           const int s = it % B_STAGES;
           const uint32_t ph = (it / B_STAGES) & 1u;
           // the transform warps vouch for a stage on `ready` before its copy has landed when
@@ -247,12 +257,15 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     uint32_t acc_it = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++acc_it) {
-      const int ib = w / (p.T * p.num_jb);
-      const int rem = w % (p.T * p.num_jb);
+      const int sp = w / per_split, blk = w - sp * per_split;
+      const int ib = blk / (p.T * p.num_jb);
+      const int rem = blk % (p.T * p.num_jb);
       const int t = rem / p.num_jb, jb = rem % p.num_jb;
       const int j0 = t * p.tile_w + jb * B_BN;
       const int j_end = min((t + 1) * p.tile_w, p.K);
       const int i = ib * BM + quad * 32 + lane;
+      void* const c_dst = p.splits > 1 ? static_cast<void*>(p.partial + (int64_t)sp * p.I * p.K) : p.c_out;
+      const bool c_f32 = p.splits > 1 || p.f32_out != 0;
       const int b = split_acc ? 0 : (int)(acc_it & 1u);
       const uint32_t aph = split_acc ? (acc_it & 1u) : ((acc_it >> 1) & 1u);
       if (!mbar_wait(&bars->acc_full[b], aph, abort_flag)) {
@@ -270,7 +283,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         tmem_ld32(tmem_base + lane_base + (uint32_t)(b * B_BN + c * 32), r);
         tmem_wait_ld();
         if (split_acc) add_cross_terms(tmem_base + lane_base + (uint32_t)(B_BN + c * 32), r);
-        if (i < p.I) store_c_row(p, i, jc, j_end, r, c_scale);
+        if (i < p.I) store_c_row(c_dst, c_f32, p.K, i, jc, j_end, r, c_scale);
       }
       tc_fence_before();
       __syncwarp();
@@ -589,6 +602,8 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       const int j0 = t * p.tile_w + jb * P_BN;
       const int j_end = min((t + 1) * p.tile_w, p.K);
       const int i = ib * (2 * BM) + row_off + quad * 32 + lane;
+      void* const c_dst = p.c_out;
+      const bool c_f32 = p.f32_out != 0;
       const int b = split_acc ? 0 : (int)(acc_it & 1u);
       const uint32_t aph = split_acc ? (acc_it & 1u) : ((acc_it >> 1) & 1u);
       if (!mbar_wait_cluster(&bars->acc_full[b], aph, abort_flag)) {
@@ -606,7 +621,7 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         tmem_ld32(tmem_base + lane_base + (uint32_t)(b * P_BN + c * 32), r);
         tmem_wait_ld();
         if (split_acc) add_cross_terms(tmem_base + lane_base + (uint32_t)(P_BN + c * 32), r);
-        if (i < p.I) store_c_row(p, i, jc, j_end, r, c_scale);
+        if (i < p.I) store_c_row(c_dst, c_f32, p.K, i, jc, j_end, r, c_scale);
       }
       tc_fence_before();
       __syncwarp();
@@ -756,6 +771,10 @@ struct PlaneSpec {
   int f32_out = 0;
   const float* c_scale_ir = nullptr;
   float inp_res = 0.0f;
+  // weight gradient whose output has few blocks: the reduction over the batch rows is split over `splits`
+  // CTAs per block (fp32 copies in `partial`, added by a second kernel); see BwdTcParams
+  int splits = 1;
+  float* partial = nullptr;
 };
 
 static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint32_t* keep_mask,
@@ -792,6 +811,18 @@ static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint
   p.f32_out = spec.f32_out;
   p.c_scale_ir = spec.c_scale_ir;
   p.inp_res = spec.inp_res;
+  p.splits = 1;
+  p.split_lsteps = p.lsteps;
+  p.partial = nullptr;
+  if (spec.splits > 1) {
+    if (!wgrad || keep_mask != nullptr || spec.partial == nullptr) {
+      set_error("bwd_tc: a split reduction is for the weight gradient without a clamp mask and needs a partial-sum buffer");
+      return AL_ERR_BAD_ARGUMENT;
+    }
+    p.split_lsteps = (p.lsteps + spec.splits - 1) / spec.splits;
+    p.splits = (p.lsteps + p.split_lsteps - 1) / p.split_lsteps;  // no empty copy
+    p.partial = spec.partial;
+  }
   int rc = wgrad ? ensure_smem(bwd_tc_kernel<true>, B_SMEM) : ensure_smem(bwd_tc_kernel<false>, B_SMEM);
   if (rc) return rc;
   CUtensorMap map_a, map_b;
@@ -817,7 +848,7 @@ static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint
   int pairs = max_pairs(wgrad);
   const int keep_free = comm_reserved_sms();
   if (pairs > 1 && keep_free > 0) pairs = pairs - (keep_free + 1) / 2 > 1 ? pairs - (keep_free + 1) / 2 : 1;
-  if (pairs > 0 && pairing >= 0 && (pair_work >= pairs || pairing > 0)) {
+  if (p.splits == 1 && pairs > 0 && pairing >= 0 && (pair_work >= pairs || pairing > 0)) {
     p.num_ib = (p.I + 2 * BM - 1) / (2 * BM);
     rc = wgrad ? ensure_smem(bwd_tc_pair_kernel<true>, P_SMEM) : ensure_smem(bwd_tc_pair_kernel<false>, P_SMEM);
     if (rc) return rc;
@@ -828,14 +859,16 @@ static int launch_bwd_tc(bool wgrad, const void* g, const void* b_op, const uint
       bwd_tc_pair_kernel<false><<<grid, kBwdThreads, P_SMEM, s>>>(map_a, map_b, p);
     return check_launch(wgrad ? "wgrad_tc_pair" : "dgrad_tc_pair");
   }
-  int work = p.num_ib * p.T * p.num_jb;
+  int work = p.num_ib * p.T * p.num_jb * p.splits;
   const int sms = sm_count() - keep_free > 1 ? sm_count() - keep_free : 1;
   int grid = work < sms ? work : sms;
   if (wgrad)
     bwd_tc_kernel<true><<<grid, kBwdThreads, B_SMEM, s>>>(map_a, map_b, p);
   else
     bwd_tc_kernel<false><<<grid, kBwdThreads, B_SMEM, s>>>(map_a, map_b, p);
-  return check_launch(wgrad ? "wgrad_tc" : "dgrad_tc");
+  rc = check_launch(wgrad ? "wgrad_tc" : "dgrad_tc");
+  if (rc || p.splits == 1) return rc;
+  return launch_sum_partials(spec.f32_out ? AL_F32 : AL_BF16, p.partial, p.splits, (int64_t)p.I * K, c_out, s);
 }
 
 int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask, int mask_words,
@@ -879,7 +912,8 @@ int launch_dgrad_tc_f32(const void* g_planes, int sets, const void* w_planes, in
 // scale_ir: [T] static input ranges whose DAC step multiplies the tile's columns of grad_w (null when
 // the step is already folded into per-tile planes)
 int launch_wgrad_tc_f32(const void* g_planes, int sets, const void* codes16, int M, int K, int N, const TileTable& tt,
-                        const float* scale_ir, float inp_res, int pairing, void* grad_w, cudaStream_t s) {
+                        const float* scale_ir, float inp_res, int pairing, void* grad_w, cudaStream_t s, int splits,
+                        float* partial) {
   ProfScope prof(AL_K_WGRAD_GEMM, s);
   PlaneSpec spec;
   spec.products = kPlanes;  // the codes are exact in one plane
@@ -893,6 +927,8 @@ int launch_wgrad_tc_f32(const void* g_planes, int sets, const void* codes16, int
   spec.f32_out = 1;
   spec.c_scale_ir = scale_ir;
   spec.inp_res = inp_res;
+  spec.splits = splits;
+  spec.partial = partial;
   return launch_bwd_tc(true, g_planes, codes16, nullptr, 0, M, K, N, tt, pairing, grad_w, s, spec);
 }
 

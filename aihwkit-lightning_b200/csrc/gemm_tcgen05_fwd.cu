@@ -301,6 +301,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           const int cc = col0 + h * 16;
           const int nh = n_first + h * 16;
           const int n0 = n_first + (h >> 1) * 32;  // the 32 columns whose mask word this half belongs to
+          // layers with few output channels: column groups beyond the last channel hold nothing (uniform
+          // across the warp; a group is skipped as a whole, so that its mask word keeps its one writer)
+          if (!kFixed && n0 >= N) break;
           if ((h & 1) == 0) keep_bits = 0;
           uint32_t accr[16], sumr[16];
           tmem_ld16(tmem_base + lane_base + (uint32_t)(b * kBN + cc), accr);

@@ -121,6 +121,8 @@ int launch_weight_fused(int dtype, const void* w, int N, int K, const TileTable&
                         const uint64_t* offset_base = nullptr, bool tile_max_zeroed = false);
 
 // ---- SIMT GEMMs (gemm_simt.cu) ------------------------------------------------------------
+// c_out[e] = sum over s of partial[s][e], e < count, added in the order of s
+int launch_sum_partials(int dtype, const float* partial, int splits, int64_t count, void* c_out, cudaStream_t s);
 int launch_fwd_simt(int dtype, int round_dt, const void* xq, const void* w_mod, int K,
                     const TileTable& tt, const FwdEpilogueParams& ep, void* out, cudaStream_t s);
 // grad_x[:, tile] = (g * keep_t) @ w_mod[:, tile]
@@ -177,7 +179,8 @@ int launch_fwd_tc_f32(const void* codes16, const void* w_planes, int K, const Ti
 int launch_dgrad_tc_f32(const void* g_planes, int sets, const void* w_planes, int M, int K, int N, const TileTable& tt,
                         int pairing, void* grad_x, cudaStream_t s);
 int launch_wgrad_tc_f32(const void* g_planes, int sets, const void* codes16, int M, int K, int N, const TileTable& tt,
-                        const float* scale_ir, float inp_res, int pairing, void* grad_w, cudaStream_t s);
+                        const float* scale_ir, float inp_res, int pairing, void* grad_w, cudaStream_t s, int splits = 1,
+                        float* partial = nullptr);
 int tc_read_device_error(cudaStream_t s, uint32_t* code);
 // limit of the device-side waits of all tcgen05 kernels (both translation units)
 int tc_set_wait_limit(unsigned long long ns);
