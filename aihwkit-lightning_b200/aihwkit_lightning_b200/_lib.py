@@ -85,7 +85,7 @@ SYMBOLS = {
     "al_unfold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
     "al_fold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
     "al_unfold2d_dac": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [POINTER(c_int32), c_int32, c_double, c_void_p,
-                                                                       c_void_p, c_void_p]),
+                                                                       c_void_p, c_void_p, c_void_p]),
     "al_read_device_error": (c_int32, [c_void_p, POINTER(c_uint32)]),
     "al_set_device_wait_limit_ns": (c_int32, [c_uint64]),
     "al_debug_withhold_forward_signal": (c_int32, [c_int32]),

@@ -261,10 +261,17 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
     if inp.dtype != weight.dtype:
         raise RuntimeError(f"input dtype {inp.dtype} and weight dtype {weight.dtype} differ")
     n, k = weight.shape
-    if inp.shape[-1] != k:
-        raise RuntimeError(f"input has {inp.shape[-1]} features, the layer expects {k}")
-    x2d = inp.reshape(-1, k).contiguous() if prequant is None else prequant[0]
-    m = x2d.shape[0]
+    if prequant is None:
+        if inp.shape[-1] != k:
+            raise RuntimeError(f"input has {inp.shape[-1]} features, the layer expects {k}")
+        x2d = inp.reshape(-1, k).contiguous()
+        m = x2d.shape[0]
+        pre_codes = None
+    else:
+        # (xq or None, ir_rows, codes16 or None, rows, patch length): the DAC already ran (``al_unfold2d_dac``)
+        x2d, _, pre_codes, m, pre_k = prequant
+        if pre_k != k:
+            raise RuntimeError(f"patches have {pre_k} features, the layer expects {k}")
     w = weight.contiguous()
     t = len(in_sizes)
     dev, dtype = inp.device, inp.dtype
@@ -288,7 +295,7 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
         args = _lib.AlForwardArgs()
         args.x, args.w, args.bias, args.out = _ptr(x2d), _ptr(w), _ptr(bias), _ptr(out)
         if prequant is not None:
-            args.x, args.x_prequantised = None, 1
+            args.x, args.x_prequantised = None, (2 if pre_codes is not None else 1)
         args.tile_ends = ends
         ir_data = iridx_data = None
         if static:
@@ -316,7 +323,7 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
         codes16 = w_planes = None
         if not needs_grad and settings.capture is None:
             # nothing of the workspace outlives the call: one allocation, carved by offset
-            es = x2d.element_size()
+            es = w.element_size()
             plan = [("w_amax", t * n * es), ("w_tile_max", 2 * t * 4)]
             if desc.ir_mode != _lib.AL_IR_OFF and prequant is None:
                 plan += [("xq", m * k * es), ("ir_rows", (t if static else t * m) * es)]
@@ -327,7 +334,9 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
             if few_rows:
                 plan.append(("smallm_scratch", lib.al_smallm_scratch_floats(m, n, t) * 4))
             if planes:
-                plan += [("codes16", m * k * 2), ("w_planes", lib.al_f32_planes() * n * k * 2)]
+                plan.append(("w_planes", lib.al_f32_planes() * n * k * 2))
+                if pre_codes is None:
+                    plan.append(("codes16", m * k * 2))
             total = 0
             for _, nbytes in plan:
                 total += (nbytes + 255) & ~255
@@ -338,10 +347,10 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
                 setattr(args, field, cursor)
                 cursor += (nbytes + 255) & ~255
             if prequant is not None:
-                args.xq, args.ir_rows = _ptr(prequant[0]), _ptr(prequant[1])
+                args.xq, args.ir_rows, args.codes16 = _ptr(prequant[0]), _ptr(prequant[1]), _ptr(pre_codes)
         else:
             if prequant is not None:
-                xq, ir_rows = prequant
+                xq, ir_rows = prequant[0], prequant[1]
             elif desc.ir_mode != _lib.AL_IR_OFF:
                 xq = torch.empty_like(x2d)
                 ir_rows = torch.empty((t, m) if not static else (t,), device=dev, dtype=dtype)
@@ -363,7 +372,7 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
                 smallm_scratch = torch.empty(lib.al_smallm_scratch_floats(m, n, t), device=dev, dtype=torch.float32)
             args.smallm_scratch = _ptr(smallm_scratch)
             if planes:
-                codes16 = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
+                codes16 = pre_codes if pre_codes is not None else torch.empty(m, k, device=dev, dtype=torch.bfloat16)
                 w_planes = torch.empty(lib.al_f32_planes(), n, k, device=dev, dtype=torch.bfloat16)
                 args.codes16, args.w_planes = _ptr(codes16), _ptr(w_planes)
         std_shared = None
@@ -613,20 +622,28 @@ class AnalogConv2dFunction(torch.autograd.Function):
         (kh, kw), (dh, dw), (ph, pw), (sh, sw) = geometry
         ho = (h + 2 * ph - dh * (kh - 1) - 1) // sh + 1
         wo = (w + 2 * pw - dw * (kw - 1) - 1) // sw + 1
-        rows, t = b * ho * wo, len(in_sizes)
+        rows, t, k = b * ho * wo, len(in_sizes), c * kh * kw
         geom = (b, c, h, w, kh, kw, sh, sw, ph, pw, dh, dw)
+        ends = _lib.tile_ends_array(in_sizes)
         with _OnDevice(xc.device):
-            xq = torch.empty(rows, c * kh * kw, device=xc.device, dtype=xc.dtype)
+            # an fp32 layer whose GEMMs run on the tensor cores takes the DAC codes as bf16 (half the bytes
+            # of the quantised patch matrix, and its exact content: the GEMMs multiply codes, the step
+            # comes in afterwards)
+            desc = make_desc(rpu_config, rows, k, weight.shape[0], t, xc.dtype, training)
+            as_codes = xc.dtype == torch.float32 and bool(lib.al_uses_tcgen05(desc, ends))
+            xq = None if as_codes else torch.empty(rows, k, device=xc.device, dtype=xc.dtype)
+            codes16 = torch.empty(rows, k, device=xc.device, dtype=torch.bfloat16) if as_codes else None
             ir_rows = torch.empty(t, rows, device=xc.device, dtype=xc.dtype)
-            status = lib.al_unfold2d_dac(_DTYPE[xc.dtype], xc.data_ptr(), *geom, _lib.tile_ends_array(in_sizes), t,
-                                         float(rpu_config.forward.inp_res), xq.data_ptr(), ir_rows.data_ptr(),
+            status = lib.al_unfold2d_dac(_DTYPE[xc.dtype], xc.data_ptr(), *geom, ends, t,
+                                         float(rpu_config.forward.inp_res), _ptr(xq), ir_rows.data_ptr(), _ptr(codes16),
                                          _stream(xc.device))
         if status == _lib.AL_ERR_UNSUPPORTED:
             raise _PatchTooLarge()
         _lib.check(status)
         ctx.geom, ctx.dtype_code = geom, _DTYPE[xc.dtype]
-        return _analog_forward(ctx, xq, weight, bias, input_range, input_range_update_idx, in_sizes, training,
-                               rpu_config, x_min, x_max, learnable_weight_clip, grad_enabled, prequant=(xq, ir_rows))
+        return _analog_forward(ctx, xc, weight, bias, input_range, input_range_update_idx, in_sizes, training,
+                               rpu_config, x_min, x_max, learnable_weight_clip, grad_enabled,
+                               prequant=(xq, ir_rows, codes16, rows, k))
 
     @staticmethod
     def backward(ctx, grad_out):  # type: ignore[override]

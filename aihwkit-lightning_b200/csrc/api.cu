@@ -262,7 +262,9 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   const bool prequantised = a->x_prequantised != 0;
-  if (prequantised && (d.ir_mode != AL_IR_DYNAMIC || !(d.inp_res > 0) || !a->xq || !a->ir_rows)) {
+  const bool prequantised_codes = a->x_prequantised == 2;
+  if (prequantised && (d.ir_mode != AL_IR_DYNAMIC || !(d.inp_res > 0) || !a->ir_rows ||
+                       (prequantised_codes ? !a->codes16 : !a->xq))) {
     set_error("al_forward: x_prequantised needs a dynamic input range with the DAC on, xq and ir_rows");
     return AL_ERR_BAD_ARGUMENT;
   }
@@ -319,7 +321,11 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
   }
 
   // fp32 layer on the tensor cores: needs the bf16 workspaces
-  const bool tc_f32 = pick_tc_f32(d, tt) && a->codes16 != nullptr && a->w_planes != nullptr && !a->x_prequantised;
+  const bool tc_f32 = pick_tc_f32(d, tt) && a->codes16 != nullptr && a->w_planes != nullptr && a->x_prequantised != 1;
+  if (prequantised_codes && !tc_f32) {
+    set_error("al_forward: x_prequantised = 2 (bf16 codes) is for fp32 layers on the tensor cores (al_uses_tcgen05)");
+    return AL_ERR_UNSUPPORTED;
+  }
   if (d.dtype == AL_F32 && d.engine >= AL_ENGINE_TCGEN05 && !tc_f32) {
     set_error("tcgen05 engine requested for an fp32 layer that does not qualify (DAC on, rounding on, aligned tiles, "
               "codes16 and w_planes given)");
@@ -557,7 +563,10 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
     return AL_ERR_UNSUPPORTED;
   }
   bool tc = !tc_f32 && pick_tc(d, tt, true);
-  if (tc_f32 && (a->grad_x || a->grad_w)) {
+  // an fp32 layer with fewer than 64 output channels: the input gradient reduces over those few channels
+  // only, which the CUDA-core kernel does faster (52 against 76 us at 65536 x 288 x 32); it needs w_mod
+  const bool dgrad_tc_f32 = tc_f32 && (d.N >= 64 || d.engine >= AL_ENGINE_TCGEN05 || !a->w_mod);
+  if (tc_f32 && ((a->grad_x && dgrad_tc_f32) || (a->grad_w && d.ir_mode != AL_IR_DYNAMIC))) {
     // planes of g (masked per tile when the ADC clamped), shared by the input gradient and -- with
     // one input range per tile -- by the weight gradient
     rc = launch_split_planes_grad(static_cast<const float*>(a->grad_out), d.M, d.N, mask, mask_words, nullptr, 0, 0.0f,
@@ -570,9 +579,6 @@ int al_backward(const AlDesc* desc, const AlBackwardArgs* a, void* stream) {
       set_error("al_backward: w_mod missing");
       return AL_ERR_BAD_ARGUMENT;
     }
-    // an fp32 layer with fewer than 64 output channels: the input gradient reduces over those few channels
-    // only, which the CUDA-core kernel does faster (52 against 76 us at 65536 x 288 x 32); it needs w_mod
-    const bool dgrad_tc_f32 = tc_f32 && (d.N >= 64 || d.engine >= AL_ENGINE_TCGEN05 || !a->w_mod);
     rc = dgrad_tc_f32 ? launch_dgrad_tc_f32(a->g_planes, sets_d, a->w_planes, d.M, d.K, d.N, tt, pairing, a->grad_x, s)
          : tc   ? launch_dgrad_tc(a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, pairing, a->grad_x, s)
                 : launch_dgrad_simt(d.dtype, a->grad_out, a->w_mod, mask, mask_words, d.M, d.K, d.N, gt, a->grad_x, s);

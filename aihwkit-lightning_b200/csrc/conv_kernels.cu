@@ -83,7 +83,8 @@ constexpr int kStageBytes = 40 * 1024;
 struct UnfoldDac {
   TileTable tt;
   float inp_res;
-  void* ir_rows;  // [T, B*Ho*Wo] dtype: the ranges, as the DAC pre-pass would write them
+  void* ir_rows;      // [T, B*Ho*Wo] dtype: the ranges, as the DAC pre-pass would write them
+  uint16_t* codes16;  // nullable: the integer DAC codes as bf16 (operand of the tensor-core GEMMs of an fp32 layer)
 };
 
 template <int DT, bool DAC>
@@ -154,8 +155,12 @@ unfold2d_rows_kernel(const void* __restrict__ x, ConvGeom g, int c_chunk, int sp
         for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         if (lane == 0) Elem<DT>::store(dac.ir_rows, (int64_t)t * rows_total + m, amax);
         const QuantSeg q = dac_prepare<DT>(amax, dac.inp_res, false, false);
-        for (int e = lo + lane; e < hi; e += 32)
-          Elem<DT>::store(out, row + e, dac_apply<DT>(q, tile[lut[e] + shift], nullptr));
+        for (int e = lo + lane; e < hi; e += 32) {
+          float code;
+          const float v = dac_apply<DT>(q, tile[lut[e] + shift], &code);
+          if (out != nullptr) Elem<DT>::store(out, row + e, v);
+          if (dac.codes16 != nullptr) dac.codes16[row + e] = f32_to_bf16_bits(code);  // small integers: exact
+        }
       }
     } else {
       for (int e = lane; e < len; e += 32) Elem<DT>::store(out, row + e, tile[lut[e] + shift]);
@@ -429,8 +434,9 @@ int al_unfold2d(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t H, i
 
 int al_unfold2d_dac(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh, int32_t kw,
                     int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw,
-                    const int32_t* tile_ends_host, int32_t T, double inp_res, void* xq, void* ir_rows, void* stream) {
-  if ((dtype != AL_F32 && dtype != AL_BF16) || !x || !xq || !ir_rows || !tile_ends_host) {
+                    const int32_t* tile_ends_host, int32_t T, double inp_res, void* xq, void* ir_rows, void* codes16,
+                    void* stream) {
+  if ((dtype != AL_F32 && dtype != AL_BF16) || !x || (!xq && !codes16) || !ir_rows || !tile_ends_host) {
     set_error("al_unfold2d_dac: bad dtype or null pointer");
     return AL_ERR_BAD_ARGUMENT;
   }
@@ -462,6 +468,7 @@ int al_unfold2d_dac(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t 
   }
   host.inp_res = (float)inp_res;
   host.ir_rows = ir_rows;
+  host.codes16 = static_cast<uint16_t*>(codes16);
   cudaStream_t st = (cudaStream_t)stream;
   ProfScope prof(AL_K_UNFOLD, st);
   const unsigned grid = (unsigned)((int64_t)B * g.Ho);

@@ -147,7 +147,9 @@ typedef struct AlForwardArgs {
   uint64_t seed, offset;     /* counter-based generator: (seed, call counter)              */
   int32_t x_prequantised;    /* 1: xq and ir_rows already hold the DAC's output (al_unfold2d_dac);
                                  x may then be null and the DAC stage is skipped (dynamic
-                                 input ranges only)                                          */
+                                 input ranges only).  2: codes16 and ir_rows hold it (the codes
+                                 as bf16, for an fp32 layer that al_uses_tcgen05 reports on the
+                                 tensor cores); x and xq may be null                          */
   const uint64_t* offset_base; /* nullable: one counter in DEVICE memory that every noise kernel of the
                                  call adds to `offset` when it starts.  A caller that captures its
                                  calls in a CUDA graph (where `offset` is frozen) advances this
@@ -257,11 +259,13 @@ int al_unfold2d(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t H, i
  * [B*Ho*Wo, C*kh*kw] and the per-(tile, patch) ranges ir_rows [T, B*Ho*Wo] that al_forward would
  * otherwise compute from the patch matrix (P/conv.py:312-322 followed by P/torch_utils/torch_linear.py:
  * 156, 182-192); the unquantised patch matrix is never written.  al_forward then runs with
- * AlForwardArgs.x_prequantised = 1.  AL_ERR_UNSUPPORTED when a patch does not fit one staged block:
- * use al_unfold2d then. */
+ * AlForwardArgs.x_prequantised = 1.  codes16 (nullable): the integer DAC codes as bf16, same shape as
+ * xq, for fp32 layers whose GEMMs run on the tensor cores (x_prequantised = 2); xq may be null when
+ * codes16 is given.  AL_ERR_UNSUPPORTED when a patch does not fit one staged block: use al_unfold2d then. */
 int al_unfold2d_dac(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh, int32_t kw,
                     int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw,
-                    const int32_t* tile_ends_host, int32_t T, double inp_res, void* xq, void* ir_rows, void* stream);
+                    const int32_t* tile_ends_host, int32_t T, double inp_res, void* xq, void* ir_rows, void* codes16,
+                    void* stream);
 int al_fold2d(int32_t dtype, const void* grad_patches, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh,
               int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw, void* grad_x,
               void* stream);
