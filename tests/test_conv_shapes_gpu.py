@@ -80,3 +80,113 @@ def test_weight_gradient_partials_stay_inside_the_scratch(m, k, n, max_in, dtype
     assert ((grad_w.float() - want_w).norm() / want_w.norm()).item() <= tol
     assert ((grad_x.float() - want_x).norm() / want_x.norm()).item() <= tol
     assert ((out.float() - xq.float() @ w.float().t()).norm() / out.float().norm()).item() <= tol
+
+
+@pytest.mark.parametrize("m,k,n,max_in", [
+    (65536, 288, 32, 256),   # T = 2, input gradient on the CUDA cores (fewer than 64 channels)
+    (16384, 576, 64, 256),   # T = 3, all three GEMMs on the tensor cores
+    (262144, 144, 16, 256),  # one output block, 296 copies of it over the batch rows
+])
+def test_tensor_core_weight_gradient_split_stays_inside_the_scratch(m, k, n, max_in):
+    """The same layer shapes in fp32 with the bf16-plane workspaces given: forward and weight gradient run
+    on the tcgen05 kernels, and the weight gradient splits its reduction over CTAs into the caller's scratch."""
+    from aihwkit_lightning_b200 import _lib
+    from aihwkit_lightning_b200.nn import functional as F
+    from aihwkit_lightning_b200.nn.modules.base import split_sizes
+    from aihwkit_lightning_b200.simulator.configs import TorchInferenceRPUConfig
+
+    lib = _lib.load()
+    rpu = TorchInferenceRPUConfig()
+    rpu.mapping.max_input_size = max_in
+    rpu.forward.inp_res = 254
+    rpu.forward.out_noise = 0.0
+    rpu.pre_post.input_range.enable = True
+    rpu.pre_post.input_range.dynamic = True
+    in_sizes = split_sizes(k, max_in)
+    t = len(in_sizes)
+    ends = _lib.tile_ends_array(in_sizes)
+    dtype = torch.float32
+    gen = torch.Generator(device="cuda").manual_seed(m + k + n)
+    x = torch.randn(m, k, device="cuda", generator=gen)
+    w = torch.rand(n, k, device="cuda", generator=gen) * 0.2 - 0.1
+    g = torch.randn(m, n, device="cuda", generator=gen)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    desc = F.make_desc(rpu, m, k, n, t, dtype, True)
+    desc.save_for_backward = 1
+    assert lib.al_uses_tcgen05(desc, ends)
+    fa = _lib.AlForwardArgs()
+    out = torch.empty(m, n, device="cuda")
+    xq = torch.empty_like(x)
+    ir_rows = torch.empty(t, m, device="cuda")
+    w_amax = torch.empty(t, n, device="cuda")
+    w_tile_max = torch.empty(2 * t, device="cuda")
+    codes16 = torch.empty(m, k, device="cuda", dtype=torch.bfloat16)
+    w_planes = torch.empty(lib.al_f32_planes(), n, k, device="cuda", dtype=torch.bfloat16)
+    fa.x, fa.w, fa.out, fa.tile_ends = x.data_ptr(), w.data_ptr(), out.data_ptr(), ends
+    fa.xq, fa.ir_rows, fa.w_amax, fa.w_tile_max, fa.w_mod = (xq.data_ptr(), ir_rows.data_ptr(), w_amax.data_ptr(),
+                                                            w_tile_max.data_ptr(), w.data_ptr())
+    fa.codes16, fa.w_planes = codes16.data_ptr(), w_planes.data_ptr()
+    _lib.check(lib.al_forward(desc, fa, stream))
+
+    need = lib.al_backward_scratch_floats(m, k, n, t)
+    splits, rows = ctypes.c_int32(), ctypes.c_int32()
+    _lib.check(lib.al_wgrad_split_plan(m, k, n, t, ctypes.byref(splits), ctypes.byref(rows)))
+    assert splits.value > 1
+    arena = torch.full((need + GUARD,), float("nan"), device="cuda", dtype=torch.float32)
+    arena[need:] = 12345.0
+    g_planes = torch.empty(lib.al_backward_plane_elems(desc, ends), device="cuda", dtype=torch.bfloat16)
+    ba = _lib.AlBackwardArgs()
+    grad_x = torch.empty(m, k, device="cuda")
+    grad_w = torch.empty(n, k, device="cuda")
+    ba.grad_out, ba.xq, ba.w_mod, ba.ir_rows, ba.tile_ends = g.data_ptr(), xq.data_ptr(), w.data_ptr(), ir_rows.data_ptr(), ends
+    ba.codes16, ba.w_planes, ba.g_planes, ba.g_planes_elems = (codes16.data_ptr(), w_planes.data_ptr(), g_planes.data_ptr(),
+                                                              g_planes.numel())
+    ba.grad_x, ba.grad_w = grad_x.data_ptr(), grad_w.data_ptr()
+    ba.reduce_scratch, ba.reduce_scratch_floats = arena.data_ptr(), need
+    _lib.check(lib.al_backward(desc, ba, stream))
+    torch.cuda.synchronize()
+
+    assert bool((arena[need:] == 12345.0).all()), "the backward wrote behind its scratch buffer"
+    # the codes the GEMMs multiplied are the quantised inputs divided by their steps
+    want_w = g.t() @ xq
+    want_x = g @ w
+    assert ((grad_w - want_w).norm() / want_w.norm()).item() <= 1e-5
+    assert ((grad_x - want_x).norm() / want_x.norm()).item() <= 1e-5
+    assert ((out - xq @ w.t()).norm() / out.norm()).item() <= 1e-5
+
+    # a scratch buffer that is too small for the copies is refused on the host
+    ba.reduce_scratch_floats = need - 1
+    assert lib.al_backward(desc, ba, stream) == _lib.AL_ERR_BAD_ARGUMENT
+
+
+def test_conv2d_on_the_tensor_cores_matches_the_cuda_core_route():
+    """An fp32 convolution with enough patches runs its forward and weight gradient on the tcgen05
+    kernels (patch extraction writes bf16 codes); same results as the CUDA-core engine within 1e-5."""
+    from aihwkit_lightning_b200.nn import AnalogConv2d
+    from aihwkit_lightning_b200.nn import functional as F
+    from aihwkit_lightning_b200.simulator.configs import TorchInferenceRPUConfig
+
+    rpu = TorchInferenceRPUConfig()
+    rpu.mapping.max_input_size = 256
+    rpu.forward.inp_res = 254
+    rpu.forward.out_noise = 0.0
+    rpu.pre_post.input_range.enable = True
+    rpu.pre_post.input_range.dynamic = True
+    torch.manual_seed(0)
+    conv = AnalogConv2d(16, 32, 3, padding=1, bias=True, rpu_config=rpu).cuda().train()
+    x = torch.randn(64, 16, 32, 32, device="cuda")  # 65536 patches of 144
+    g = torch.randn(64, 32, 32, 32, device="cuda")
+    results = {}
+    for engine in ("auto", "simt"):
+        xin = x.clone().requires_grad_(True)
+        conv.zero_grad(set_to_none=True)
+        with F.operator_settings(engine=engine):
+            out = conv(xin)
+            out.backward(g)
+        results[engine] = (out.detach(), xin.grad, conv.weight.grad.clone(), conv.bias.grad.clone())
+    desc = F.make_desc(rpu, 65536, 144, 32, 1, torch.float32, True)
+    from aihwkit_lightning_b200 import _lib
+    assert _lib.load().al_uses_tcgen05(desc, _lib.tile_ends_array([144]))
+    for got, want in zip(results["auto"], results["simt"]):
+        assert ((got - want).norm() / want.norm()).item() <= 1e-5
