@@ -86,6 +86,10 @@ SYMBOLS = {
     "al_fold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
     "al_unfold2d_dac": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [POINTER(c_int32), c_int32, c_double, c_void_p,
                                                                        c_void_p, c_void_p, c_void_p]),
+    "al_swiglu_forward": (c_int32, [c_int32, c_void_p, c_int64, c_int32, c_void_p, c_void_p]),
+    "al_swiglu_backward": (c_int32, [c_int32, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_void_p]),
+    "al_rotary_qkv": (c_int32, [c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
+                                c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "al_read_device_error": (c_int32, [c_void_p, POINTER(c_uint32)]),
     "al_set_device_wait_limit_ns": (c_int32, [c_uint64]),
     "al_debug_withhold_forward_signal": (c_int32, [c_int32]),

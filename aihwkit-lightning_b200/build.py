@@ -25,6 +25,7 @@ SOURCES = [
     "backward_kernels.cu",
     "conv_kernels.cu",
     "peer_kernels.cu",
+    "decoder_glue_kernels.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -390,59 +390,10 @@ def build_decoder(dev, layers=32, d=3072, heads=32, mlp=8192, vocab=32064):
     from torch.nn import functional as TF
     from torch.nn.attention import SDPBackend, sdpa_kernel
 
+    from aihwkit_lightning_b200.nn.decoder_ops import rotary_qkv, swiglu
+
     # cuDNN's attention first (1.1 ms per layer forward + backward at these shapes against 2.0 ms)
     ATTENTION_BACKENDS = [SDPBackend.CUDNN_ATTENTION, SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION]
-
-    class Rotary(torch.autograd.Function):
-        """Rotary embedding of the q and k parts of a fused qkv activation [b, s, 3, heads, hd] -> (rotated
-        [b, s, 2, heads, hd], v [b, s, heads, hd]).  As a Function of its own the backward is the inverse
-        rotation of the gradient, written straight into the qkv gradient together with v's (no slice /
-        cat / stack / select gradients, each of which fills a qkv-sized tensor with zeros first)."""
-
-        @staticmethod
-        def forward(ctx, qkv, cos, sin):
-            half = qkv.shape[-1] // 2
-            qk = qkv[:, :, :2]
-            x1, x2 = qk[..., :half], qk[..., half:]
-            c, sn = cos[..., :half], sin[..., :half]
-            out = torch.empty(qk.shape, dtype=qkv.dtype, device=qkv.device)
-            torch.addcmul(x1 * c, x2, sn, value=-1, out=out[..., :half])
-            torch.addcmul(x2 * c, x1, sn, out=out[..., half:])
-            ctx.save_for_backward(cos, sin)
-            return out, qkv[:, :, 2].contiguous()
-
-        @staticmethod
-        def backward(ctx, g, gv):
-            cos, sin = ctx.saved_tensors
-            half = g.shape[-1] // 2
-            g1, g2 = g[..., :half], g[..., half:]
-            c, sn = cos[..., :half], sin[..., :half]
-            b, s, _, h, hd = g.shape
-            dqkv = torch.empty(b, s, 3, h, hd, dtype=g.dtype, device=g.device)
-            torch.addcmul(g1 * c, g2, sn, out=dqkv[:, :, :2, :, :half])
-            torch.addcmul(g2 * c, g1, sn, value=-1, out=dqkv[:, :, :2, :, half:])
-            dqkv[:, :, 2].copy_(gv)
-            return dqkv, None, None
-
-    class SwiGLU(torch.autograd.Function):
-        """silu(gate) * up of a fused [.., 2 mlp] activation; the backward writes both halves of the
-        gradient into one buffer."""
-
-        @staticmethod
-        def forward(ctx, gu):
-            gate, up = gu.chunk(2, dim=-1)
-            ctx.save_for_backward(gu)
-            return TF.silu(gate) * up
-
-        @staticmethod
-        def backward(ctx, g):
-            (gu,) = ctx.saved_tensors
-            gate, up = gu.chunk(2, dim=-1)
-            dgu = torch.empty_like(gu)
-            dgate, dup = dgu.chunk(2, dim=-1)
-            torch.mul(g, TF.silu(gate), out=dup)
-            torch.ops.aten.silu_backward.grad_input(g * up, gate, grad_input=dgate)
-            return dgu
 
     class RMSNorm(nn.Module):
         def __init__(self, dim, eps=1e-5):
@@ -465,14 +416,12 @@ def build_decoder(dev, layers=32, d=3072, heads=32, mlp=8192, vocab=32064):
         def forward(self, x, cos, sin):
             b, s, _ = x.shape
             hd = d // heads
-            qkv = self.qkv_proj(self.norm1(x)).view(b, s, 3, heads, hd)
-            qk, v = Rotary.apply(qkv, cos, sin)
-            q, k = qk.permute(2, 0, 3, 1, 4)
-            v = v.transpose(1, 2)
+            # rotary embedding of q and k and the split of the fused projection in one pass of the library
+            q, k, v = (t.transpose(1, 2) for t in rotary_qkv(self.qkv_proj(self.norm1(x)).view(b, s, 3, heads, hd), cos, sin))
             with sdpa_kernel(ATTENTION_BACKENDS, set_priority=True):
                 att = TF.scaled_dot_product_attention(q, k, v, is_causal=True)
             x = x + self.o_proj(att.transpose(1, 2).reshape(b, s, d))
-            return x + self.down_proj(SwiGLU.apply(self.gate_up_proj(self.norm2(x))))
+            return x + self.down_proj(swiglu(self.gate_up_proj(self.norm2(x))))
 
     class Decoder(nn.Module):
         def __init__(self):
@@ -488,9 +437,7 @@ def build_decoder(dev, layers=32, d=3072, heads=32, mlp=8192, vocab=32064):
             pos = torch.arange(s, device=ids.device, dtype=torch.float32)
             inv = 1.0 / (10000 ** (torch.arange(0, self.hd, 2, device=ids.device, dtype=torch.float32) / self.hd))
             ang = pos[:, None] * inv[None, :]
-            # [s, 1, 1, hd]: broadcasts over (q | k) and the heads of a [b, s, 2, heads, hd] tensor
-            cos = torch.cat([ang.cos(), ang.cos()], -1).to(self.embed.weight.dtype)[:, None, None, :]
-            sin = torch.cat([ang.sin(), ang.sin()], -1).to(self.embed.weight.dtype)[:, None, None, :]
+            cos, sin = ang.cos(), ang.sin()  # [s, hd / 2] float32 tables of the rotary embedding
             x = self.embed(ids)
             for layer in self.layers:
                 x = layer(x, cos, sin)

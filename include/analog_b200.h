@@ -270,6 +270,28 @@ int al_fold2d(int32_t dtype, const void* grad_patches, int32_t B, int32_t C, int
               int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw, void* grad_x,
               void* stream);
 
+/* Element-wise operators of a decoder layer that sit between its analog linear layers, one pass each
+ * (16-byte vectors, fp32 arithmetic, one rounding per result); the reference leaves them to PyTorch
+ * (HF Phi-3 `modeling_phi3.py`: `apply_rotary_pos_emb`, `Phi3MLP.forward`), where the strided views of the
+ * fused projections make them chains of slow element-wise kernels.
+ *   al_swiglu_forward:  out[m, d] = silu(gate_up[m, d]) * gate_up[m, width + d],  gate_up [rows, 2 width]
+ *   al_swiglu_backward: grad_gate_up [rows, 2 width] from gate_up and grad_out [rows, width]
+ *   al_rotary_qkv: the rotary embedding of q and k (rotation of the two halves of each head by the angle
+ *     of the row's position, position = row % seq_len, tables [seq_len, head_dim / 2] fp32) and a copy of
+ *     v, from three [rows, heads, head_dim] inputs with a common row stride (the thirds of a fused qkv
+ *     activation: in_k = in_q + heads * head_dim, row stride 3 * heads * head_dim) into three outputs with
+ *     their own row stride.  inverse != 0: the transposed rotation, which is the backward (inputs: the
+ *     three gradients, outputs: the thirds of the qkv gradient).
+ * dtype AL_F32 or AL_BF16; pointers and row strides 16-byte aligned; width and head_dim / 2 multiples of
+ * the vector length (4 fp32, 8 bf16). */
+int al_swiglu_forward(int32_t dtype, const void* gate_up, int64_t rows, int32_t width, void* out, void* stream);
+int al_swiglu_backward(int32_t dtype, const void* gate_up, const void* grad_out, int64_t rows, int32_t width,
+                       void* grad_gate_up, void* stream);
+int al_rotary_qkv(int32_t dtype, int32_t inverse, const void* in_q, const void* in_k, const void* in_v,
+                  int64_t in_row_stride, const float* cos_table, const float* sin_table, int64_t rows, int32_t seq_len,
+                  int32_t heads, int32_t head_dim, void* out_q, void* out_k, void* out_v, int64_t out_row_stride,
+                  void* stream);
+
 /* Device-side error word of the tcgen05 kernels (a bounded wait that gave up).  Reads and
  * clears it; synchronises `stream`.  0 = no error. */
 int al_read_device_error(void* stream, uint32_t* out_code);
