@@ -284,7 +284,7 @@ class Ctx:
             self.dist.destroy_process_group()
 
 
-def make_gradient_sync(ctx, params, n_ctas=None):
+def make_gradient_sync(ctx, params, n_ctas=None, multicast_from=None):
     """Gradient exchange of the data-parallel arms: the library's peer-memory kernel
     (``PeerGradientSync``) when the replicas can map one another's memory, NCCL all-reduce otherwise or
     when BENCH_EXCHANGE=nccl.  Returns (sync, description)."""
@@ -296,8 +296,12 @@ def make_gradient_sync(ctx, params, n_ctas=None):
     n_ctas = int(os.environ.get("BENCH_COMM_CTAS", "16")) if n_ctas is None else n_ctas
     if os.environ.get("BENCH_EXCHANGE", "peer") == "peer":
         try:
+            # multicast_from: replica count from which the reduction runs in the switch (multimem): a rank then
+            # moves 2/N of the buffer through its SMs instead of all of it
+            multicast_env = os.environ.get("BENCH_MULTICAST", "auto")
+            auto = multicast_from is not None and ctx.world >= multicast_from
             sync = PeerGradientSync(params, n_ctas=n_ctas,
-                                    use_multicast=os.environ.get("BENCH_MULTICAST", "0") == "1")
+                                    use_multicast=multicast_env == "1" or (multicast_env == "auto" and auto))
             F.settings.grad_w_alloc = sync.grad_buffer
             multicast = any(pool["mc"] for pool in sync._pools.values())  # pylint: disable=protected-access
             how = (f"library kernel over peer memory ({n_ctas} CTAs beside the input-gradient GEMM, "
@@ -478,7 +482,10 @@ def run_c3(args, ctx, layers=32, steps=3, warmup=2, seq=2048, micro_batch=4):
         # 8 CTAs of exchange beside the backward, 8 SMs left to them by the input-gradient GEMMs: on 4 GPUs
         # 288 ms per step against 293 with 16 CTAs and no SMs left free (0 / 8 / 16 SMs left by the
         # weight-gradient GEMMs as well, and the switch-reduction form, measured within 2 ms of that)
-        sync, how = make_gradient_sync(ctx, model.parameters(), n_ctas=int(os.environ.get("BENCH_C3_COMM_CTAS", "8")))
+        # (8 GPUs, 225 ms step: switch reduction on 8 CTAs 241.6 ms, plain loads on 16 CTAs 244.1, on 8 CTAs 257.2
+        # with 15.7 ms of the exchange exposed: from 4 replicas on the reduction runs in the switch)
+        sync, how = make_gradient_sync(ctx, model.parameters(), n_ctas=int(os.environ.get("BENCH_C3_COMM_CTAS", "8")),
+                                       multicast_from=4)
         if isinstance(sync, PeerGradientSync):
             F.settings.comm_sms = int(os.environ.get("BENCH_C3_COMM_SMS", "8"))
             F.settings.comm_sms_wgrad = int(os.environ.get("BENCH_C3_COMM_SMS_WGRAD", "0"))
