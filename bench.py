@@ -479,15 +479,16 @@ def run_c3(args, ctx, layers=32, steps=3, warmup=2, seq=2048, micro_batch=4):
                           capturable=world == 1)
     sync, how = None, None
     if world > 1:
-        # 8 CTAs of exchange beside the backward, 8 SMs left to them by the input-gradient GEMMs: on 4 GPUs
-        # 288 ms per step against 293 with 16 CTAs and no SMs left free (0 / 8 / 16 SMs left by the
-        # weight-gradient GEMMs as well, and the switch-reduction form, measured within 2 ms of that)
-        # (8 GPUs, 225 ms step: switch reduction on 8 CTAs 241.6 ms, plain loads on 16 CTAs 244.1, on 8 CTAs 257.2
-        # with 15.7 ms of the exchange exposed: from 4 replicas on the reduction runs in the switch)
-        sync, how = make_gradient_sync(ctx, model.parameters(), n_ctas=int(os.environ.get("BENCH_C3_COMM_CTAS", "8")),
+        # Measured with the 225 ms step.  2 GPUs: plain peer loads on 16 CTAs with 16 SMs left free by the
+        # input-gradient GEMMs 232.5 ms, on 8 CTAs / 8 SMs 245.2, switch reduction on 8 CTAs 243.3.  8 GPUs: switch
+        # reduction on 8 CTAs / 8 SMs 241.6 ms, plain loads on 16 CTAs 244.1, on 8 CTAs 257.2 (15.7 ms exposed).
+        # So: plain loads on 16 CTAs below 4 replicas, the reduction in the switch on 8 CTAs from 4 on.
+        few = world < 4
+        sync, how = make_gradient_sync(ctx, model.parameters(),
+                                       n_ctas=int(os.environ.get("BENCH_C3_COMM_CTAS", "16" if few else "8")),
                                        multicast_from=4)
         if isinstance(sync, PeerGradientSync):
-            F.settings.comm_sms = int(os.environ.get("BENCH_C3_COMM_SMS", "8"))
+            F.settings.comm_sms = int(os.environ.get("BENCH_C3_COMM_SMS", "16" if few else "8"))
             F.settings.comm_sms_wgrad = int(os.environ.get("BENCH_C3_COMM_SMS_WGRAD", "0"))
             how += f"; backward GEMMs leave {F.settings.comm_sms} (input gradient) / {F.settings.comm_sms_wgrad} (weight gradient) SMs free"
     gen = torch.Generator().manual_seed(1000 + rank)
