@@ -160,7 +160,9 @@ def test_tensor_core_weight_gradient_split_stays_inside_the_scratch(m, k, n, max
     assert lib.al_backward(desc, ba, stream) == _lib.AL_ERR_BAD_ARGUMENT
 
 
-def test_conv2d_on_the_tensor_cores_matches_the_cuda_core_route():
+@pytest.mark.parametrize("cin,cout,size,batch", [(16, 32, 32, 64), (32, 32, 16, 64)],
+                         ids=["one-tile-144", "two-tiles-288"])
+def test_conv2d_on_the_tensor_cores_matches_the_cuda_core_route(cin, cout, size, batch):
     """An fp32 convolution with enough patches runs its forward and weight gradient on the tcgen05
     kernels (patch extraction writes bf16 codes); same results as the CUDA-core engine within 1e-5."""
     from aihwkit_lightning_b200.nn import AnalogConv2d
@@ -174,9 +176,9 @@ def test_conv2d_on_the_tensor_cores_matches_the_cuda_core_route():
     rpu.pre_post.input_range.enable = True
     rpu.pre_post.input_range.dynamic = True
     torch.manual_seed(0)
-    conv = AnalogConv2d(16, 32, 3, padding=1, bias=True, rpu_config=rpu).cuda().train()
-    x = torch.randn(64, 16, 32, 32, device="cuda")  # 65536 patches of 144
-    g = torch.randn(64, 32, 32, 32, device="cuda")
+    conv = AnalogConv2d(cin, cout, 3, padding=1, bias=True, rpu_config=rpu).cuda().train()
+    x = torch.randn(batch, cin, size, size, device="cuda")  # batch * size^2 patches of 9 cin
+    g = torch.randn(batch, cout, size, size, device="cuda")
     results = {}
     for engine in ("auto", "simt"):
         xin = x.clone().requires_grad_(True)
@@ -185,8 +187,8 @@ def test_conv2d_on_the_tensor_cores_matches_the_cuda_core_route():
             out = conv(xin)
             out.backward(g)
         results[engine] = (out.detach(), xin.grad, conv.weight.grad.clone(), conv.bias.grad.clone())
-    desc = F.make_desc(rpu, 65536, 144, 32, 1, torch.float32, True)
     from aihwkit_lightning_b200 import _lib
-    assert _lib.load().al_uses_tcgen05(desc, _lib.tile_ends_array([144]))
+    desc = F.make_desc(rpu, batch * size * size, 9 * cin, cout, len(conv.in_sizes), torch.float32, True)
+    assert _lib.load().al_uses_tcgen05(desc, _lib.tile_ends_array(conv.in_sizes))
     for got, want in zip(results["auto"], results["simt"]):
         assert ((got - want).norm() / want.norm()).item() <= 1e-5
