@@ -41,13 +41,15 @@ def test_phi3_shaped_decoder_step_matches_oracle_model():
     loss = TF.cross_entropy(gpu(ids.cuda()).float().view(-1, 512), labels.cuda().view(-1))
     loss.backward()
 
-    assert abs(loss.item() - loss_ref.item()) <= 2e-2 * abs(loss_ref.item())
+    assert abs(loss.item() - loss_ref.item()) <= 1e-3 * abs(loss_ref.item())
     pairs = [(gpu.lm_head.weight.grad, ref.lm_head.weight.grad),
              (gpu.layers[1].down_proj.weight.grad, ref.layers[1].down_proj.weight.grad),
              (gpu.layers[0].qkv_proj.weight.grad, ref.layers[0].qkv_proj.weight.grad),
              (gpu.embed.weight.grad, ref.embed.weight.grad)]
     for got, want in pairs:
-        assert rel_fro(got, want) <= 8e-2  # bf16 end to end through two decoder layers
+        # bf16 end to end through two decoder layers: measured 1.6e-3 .. 3.4e-3, while the oracle model moves by
+        # 6e-3 .. 3e-2 when one per cent of its embedding entries change by one bf16 ulp
+        assert rel_fro(got, want) <= 1e-2
 
 
 @pytest.mark.parametrize("quantised", [False, True])
@@ -88,9 +90,18 @@ def test_resnet_shaped_step_matches_oracle_model(quantised):
         # then lands on the other side of a DAC rounding boundary downstream: the loss still
         # agrees closely, gradients only to within the quantisation noise they carry.
         assert abs(loss.item() - loss_ref.item()) <= 1e-3 * abs(loss_ref.item())
-        assert rel_fro(pairs[0][0], pairs[0][1]) <= 2e-2
-        for got, want in pairs[1:]:
-            assert rel_fro(got, want) <= 0.25
+        # The yardstick is the oracle model itself: its gradients for an input that differs by 1e-6 relative
+        # (far below anything the two implementations disagree on layer by layer).  The GPU model must stay
+        # within 1.5 times that distance of the oracle (measured: 0.8 times), and within the fixed caps.
+        torch.manual_seed(1)
+        nudged = Z.to_oracle(copy.deepcopy(base), rpu).train()
+        TF.cross_entropy(nudged(x * (1 + 1e-6 * torch.randn_like(x))), y).backward()
+        yard = [rel_fro(nudged.fc.weight.grad, ref.fc.weight.grad),
+                rel_fro(nudged.conv.conv.weight.grad, ref.conv.conv.weight.grad),
+                rel_fro(nudged.blocks[2].conv2.conv.weight.grad, ref.blocks[2].conv2.conv.weight.grad)]
+        caps = [2e-2, 0.25, 0.25]
+        for (got, want), own, cap in zip(pairs, yard, caps):
+            assert rel_fro(got, want) <= min(cap, 1.5 * max(own, 1e-3))
 
     # one optimizer step with the clipping hook runs and changes the weights
     layers = lambda: (m for m in gpu.modules() if isinstance(m, (AnalogConv2d, AnalogLinear)))  # noqa: E731
