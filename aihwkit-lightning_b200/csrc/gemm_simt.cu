@@ -361,15 +361,28 @@ bwd_simt_kernel(const void* __restrict__ g, const void* __restrict__ b_op,
   }
 }
 
-// c[e] = sum_s partial[s][e], added in the order of s
+// c[e] = sum_s partial[s][e] in a fixed order: a block of 32 x 8 threads takes 32 consecutive elements;
+// thread (i, g) adds the copies s = g, g + 8, ... of element i in that order, then the eight group sums
+// are added in the order of g.  (One thread per element walking all copies took 12 us for 296 copies of
+// a 16 x 144 gradient: a chain of 296 dependent loads on nine blocks.)
+constexpr int kSumGroups = 8;
 template <int DT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(32 * kSumGroups)
 sum_partials_kernel(const float* __restrict__ partial, int splits, int64_t count, void* __restrict__ c_out) {
-  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= count) return;
-  float v = partial[e];
-  for (int s = 1; s < splits; ++s) v = fadd(v, partial[(int64_t)s * count + e]);
-  Elem<DT>::store(c_out, e, v);
+  __shared__ float part[kSumGroups][32];
+  const int i = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int64_t e = (int64_t)blockIdx.x * 32 + i;
+  float v = 0.0f;
+  if (e < count)
+    for (int s = g; s < splits; s += kSumGroups) v = fadd(v, partial[(int64_t)s * count + e]);
+  part[g][i] = v;
+  __syncthreads();
+  if (g == 0 && e < count) {
+    float sum = part[0][i];
+#pragma unroll
+    for (int k = 1; k < kSumGroups; ++k) sum = fadd(sum, part[k][i]);
+    Elem<DT>::store(c_out, e, sum);
+  }
 }
 
 // Can rows of a [.., K] matrix be read four elements at a time from every tile start?
@@ -450,9 +463,9 @@ int wgrad_splits(int M, int K, int N, int T) {
 }  // namespace
 
 int launch_sum_partials(int dtype, const float* partial, int splits, int64_t count, void* c_out, cudaStream_t s) {
-  const unsigned blocks = (unsigned)((count + 255) / 256);
-  if (dtype == AL_F32) sum_partials_kernel<kF32><<<blocks, 256, 0, s>>>(partial, splits, count, c_out);
-  else sum_partials_kernel<kBF16><<<blocks, 256, 0, s>>>(partial, splits, count, c_out);
+  const unsigned blocks = (unsigned)((count + 31) / 32);
+  if (dtype == AL_F32) sum_partials_kernel<kF32><<<blocks, 32 * kSumGroups, 0, s>>>(partial, splits, count, c_out);
+  else sum_partials_kernel<kBF16><<<blocks, 32 * kSumGroups, 0, s>>>(partial, splits, count, c_out);
   return check_launch("sum_partials");
 }
 
@@ -520,11 +533,7 @@ int launch_wgrad_simt(int dtype, const void* g, const void* xq, const uint32_t* 
   else wgrad_simt_launch<64, 64>(dtype, g, xq, keep_mask, mask_words, M, K, N, tt, splits, chunk, partial, grad_w, s);
   int rc = check_launch("wgrad_simt");
   if (rc || splits == 1) return rc;
-  const int64_t count = (int64_t)N * K;
-  const unsigned blocks = (unsigned)((count + 255) / 256);
-  if (dtype == AL_F32) sum_partials_kernel<kF32><<<blocks, 256, 0, s>>>(partial, splits, count, grad_w);
-  else sum_partials_kernel<kBF16><<<blocks, 256, 0, s>>>(partial, splits, count, grad_w);
-  return check_launch("wgrad_sum_partials");
+  return launch_sum_partials(dtype, partial, splits, (int64_t)N * K, grad_w, s);
 }
 
 }  // namespace al
