@@ -16,6 +16,15 @@ struct ConvGeom {
   int B, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, Ho, Wo;
 };
 
+// n / d for 0 <= n, n * d < 2^32 as one multiplication: m = ceil(2^32 / d) from the host (0 stands for d = 1).
+// Index arithmetic with run-time divisors is most of what the staging kernels below would otherwise execute.
+inline uint32_t magic_of(int d) { return d == 1 ? 0u : (uint32_t)(0xFFFFFFFFull / (uint32_t)d + 1ull); }
+__device__ __forceinline__ int fast_div(int n, uint32_t m) { return m ? (int)__umulhi((uint32_t)n, m) : n; }
+struct StageDiv {
+  uint32_t kw, kh, span, per_row, pads;  // magic numbers of the divisors the staging uses
+  int n_pads;                            // padding columns of a slot (16-byte staging)
+};
+
 template <int DT>
 __global__ void __launch_bounds__(256)
 unfold2d_kernel(const void* __restrict__ x, ConvGeom g, void* __restrict__ out) {
@@ -87,36 +96,74 @@ struct UnfoldDac {
   uint16_t* codes16;  // nullable: the integer DAC codes as bf16 (operand of the tensor-core GEMMs of an fp32 layer)
 };
 
-template <int DT, bool DAC>
-__global__ void __launch_bounds__(256)
-unfold2d_rows_kernel(const void* __restrict__ x, ConvGeom g, int c_chunk, int span, void* __restrict__ out,
-                     const UnfoldDac dac) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int kk = g.kh * g.kw, ckk = g.C * kk;
-  // blockIdx.x = output row * chunks + chunk: CTAs that run together read and write neighbouring memory
-  const int chunks = (g.C + c_chunk - 1) / c_chunk;
-  const int out_row = blockIdx.x / chunks;
-  const int c0 = (blockIdx.x - out_row * chunks) * c_chunk;
-  const int cn = g.C - c0 < c_chunk ? g.C - c0 : c_chunk;
+// Stages, for the output row `out_row` = (b, oh) and the channels [c0, c0 + cn), the kh input rows each channel's
+// patches read (zero padding included) as tile[r * span + col], and fills lut[e] = where element e of a patch that
+// starts at column 0 sits in the staged rows.  All threads of the CTA call it; it ends with a barrier.
+// `by16`: a thread moves 16 bytes of an input row per load (the host checked that W is a multiple of the vector and
+// that the slot of a row, `span` floats, holds the whole padded row).
+template <int DT>
+__device__ __forceinline__ void stage_patch_rows(const void* __restrict__ x, const ConvGeom& g, int out_row, int c0,
+                                                 int cn, int span, float* tile, int* lut, int* row_src,
+                                                 const StageDiv& dv, bool by16 = false) {
+  const int kk = g.kh * g.kw;
   const int len = cn * kk;       // patch elements of this chunk
   const int rows = cn * g.kh;    // staged input rows
-  float* tile = reinterpret_cast<float*>(smem_raw);             // [rows][span]
-  int* lut = reinterpret_cast<int*>(tile + c_chunk * g.kh * span);  // [len]
   const int b = out_row / g.Ho, oh = out_row - b * g.Ho;
-  int* row_src = lut + c_chunk * kk;                                  // [rows]: offset of the input row, -1 = padding
-  for (int e = threadIdx.x; e < len; e += blockDim.x) lut[e] = (e / g.kw) * span + (e % g.kw) * g.dw;
+  for (int e = threadIdx.x; e < len; e += blockDim.x) {
+    const int row = fast_div(e, dv.kw);
+    lut[e] = row * span + (e - row * g.kw) * g.dw;
+  }
   for (int r = threadIdx.x; r < rows; r += blockDim.x) {
-    const int c = c0 + r / g.kh, i = r % g.kh;
+    const int cl = fast_div(r, dv.kh);
+    const int c = c0 + cl, i = r - cl * g.kh;
     const int h = oh * g.sh - g.ph + i * g.dh;
-    row_src[r] = (h >= 0 && h < g.H) ? (c * g.H + h) * g.W : -1;
+    row_src[r] = (h >= 0 && h < g.H) ? (c * g.H + h) * g.W : -1;  // offset of the input row, -1 = padding
   }
   __syncthreads();
+  const int64_t image = (int64_t)b * g.C * g.H * g.W;
+  if (by16) {
+    // the stores are single floats: with an odd slot length the lanes of a warp, 4 (8) floats apart along a row and
+    // one slot apart between rows, fall into different banks.  The padding columns are cleared afterwards.
+    constexpr int V = DT == kF32 ? 4 : 8;
+    const int per_row = g.W / V;
+    for (int it = threadIdx.x; it < rows * per_row; it += blockDim.x) {
+      const int r = fast_div(it, dv.per_row), at = (it - r * per_row) * V;
+      const int src = row_src[r];
+      float v[V];
+#pragma unroll
+      for (int u = 0; u < V; ++u) v[u] = 0.0f;
+      if (src >= 0) {
+        if (DT == kF32) {
+          const float4 raw = *reinterpret_cast<const float4*>(static_cast<const float*>(x) + image + src + at);
+          v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+        } else {
+          const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + image + src + at);
+          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            v[2 * u] = __uint_as_float(w[u] << 16);
+            v[2 * u + 1] = __uint_as_float(w[u] & 0xffff0000u);
+          }
+        }
+      }
+      float* dst = tile + r * span + g.pw + at;
+#pragma unroll
+      for (int u = 0; u < V; ++u) dst[u] = v[u];
+    }
+    const int right = g.pw + g.W;  // columns [pw, right) of a slot hold the image
+    const int pads = dv.n_pads;
+    for (int it = threadIdx.x; it < rows * pads; it += blockDim.x) {
+      const int r = fast_div(it, dv.pads), p = it - r * pads;
+      tile[r * span + (p < g.pw ? p : right + (p - g.pw))] = 0.0f;
+    }
+    __syncthreads();
+    return;
+  }
   // element idx = r * span + col of the staged rows; (r, col) advance without a division, and
   // kBatch loads are in flight per thread before the first one is stored
   constexpr int kBatch = 4;
-  const int64_t image = (int64_t)b * g.C * g.H * g.W;
-  const int step_r = (int)blockDim.x / span, step_col = (int)blockDim.x - step_r * span;
-  int r = (int)threadIdx.x / span, col = (int)threadIdx.x - r * span;
+  const int step_r = fast_div((int)blockDim.x, dv.span), step_col = (int)blockDim.x - step_r * span;
+  int r = fast_div((int)threadIdx.x, dv.span), col = (int)threadIdx.x - r * span;
   for (int first = threadIdx.x; first < rows * span; first += blockDim.x * kBatch) {
     float v[kBatch];
     int rr = r, cc = col;
@@ -140,6 +187,24 @@ unfold2d_rows_kernel(const void* __restrict__ x, ConvGeom g, int c_chunk, int sp
     }
   }
   __syncthreads();
+}
+
+template <int DT, bool DAC>
+__global__ void __launch_bounds__(256)
+unfold2d_rows_kernel(const void* __restrict__ x, ConvGeom g, int c_chunk, int span, const StageDiv dv,
+                     void* __restrict__ out, const UnfoldDac dac) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int kk = g.kh * g.kw, ckk = g.C * kk;
+  // blockIdx.x = output row * chunks + chunk: CTAs that run together read and write neighbouring memory
+  const int chunks = (g.C + c_chunk - 1) / c_chunk;
+  const int out_row = blockIdx.x / chunks;
+  const int c0 = (blockIdx.x - out_row * chunks) * c_chunk;
+  const int cn = g.C - c0 < c_chunk ? g.C - c0 : c_chunk;
+  const int len = cn * kk;
+  float* tile = reinterpret_cast<float*>(smem_raw);             // [rows][span]
+  int* lut = reinterpret_cast<int*>(tile + c_chunk * g.kh * span);  // [len]
+  int* row_src = lut + c_chunk * kk;                                  // [rows]
+  stage_patch_rows<DT>(x, g, out_row, c0, cn, span, tile, lut, row_src, dv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
   const int64_t base = ((int64_t)out_row * g.Wo) * ckk + (int64_t)c0 * kk;
   for (int ow = warp; ow < g.Wo; ow += n_warps) {
@@ -164,6 +229,136 @@ unfold2d_rows_kernel(const void* __restrict__ x, ConvGeom g, int c_chunk, int sp
       }
     } else {
       for (int e = lane; e < len; e += 32) Elem<DT>::store(out, row + e, tile[lut[e] + shift]);
+    }
+  }
+}
+
+// The same patch extraction + DAC for patches whose length and tile ends are multiples of 4 (every convolution of a
+// ResNet after the first): the CTA's output, the Wo patches of one output row, is one contiguous run, and a thread
+// owns groups of 4 consecutive elements of it -- a group never straddles a patch or an analog tile.  Pass 1 gathers a
+// group from the staged rows and folds its abs-max into the (patch, tile) maximum in shared memory; then one thread
+// per (patch, tile) derives the quantiser; pass 2 quantises the group and writes it with 8- or 16-byte stores.  HOLD
+// groups per thread stay in registers between the passes (HOLD = 0: any number of groups, gathered twice).  The slot
+// of a staged row is an odd number of floats, which keeps the gather (lanes 4 elements apart, so 4/kw rows apart)
+// at two to three lanes per bank.
+__device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+constexpr int kGroupHold = 5;
+
+template <int DT, int HOLD>
+__global__ void __launch_bounds__(256)
+unfold2d_dac4_kernel(const void* __restrict__ x, ConvGeom g, int span, const StageDiv dv, uint32_t gpp_magic, int by16,
+                     int quads, void* __restrict__ out, const UnfoldDac dac) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int kk = g.kh * g.kw, ckk = g.C * kk, T = dac.tt.T;
+  const int out_row = blockIdx.x;
+  const int gpp = ckk >> 2, n_groups = g.Wo * gpp;  // groups per patch, per CTA
+  const int staged = (g.C * g.kh * span + 3) & ~3;
+  float* tile = reinterpret_cast<float*>(smem_raw);   // [C * kh][span]
+  int* lut = reinterpret_cast<int*>(tile + staged);   // [ckk], 16-byte aligned
+  int* row_src = lut + ckk;                           // [C * kh]
+  uint32_t* amax_bits = reinterpret_cast<uint32_t*>(row_src + g.C * g.kh);  // [Wo * T]
+  float* seg_step = reinterpret_cast<float*>(amax_bits + g.Wo * T);         // [Wo * T]
+  float* seg_rstep = seg_step + g.Wo * T;                                   // [Wo * T]
+  unsigned char* grp_tile = reinterpret_cast<unsigned char*>(seg_rstep + g.Wo * T);  // [gpp]
+  for (int i = threadIdx.x; i < g.Wo * T; i += blockDim.x) amax_bits[i] = 0u;
+  for (int i = threadIdx.x; i < gpp; i += blockDim.x) {
+    int t = 0;
+    while (dac.tt.hi(t) <= i * 4) ++t;
+    grp_tile[i] = (unsigned char)t;
+  }
+  stage_patch_rows<DT>(x, g, out_row, 0, g.C, span, tile, lut, row_src, dv, by16 != 0);
+
+  auto gather = [&](int q, float (&v)[4], int& ow, int& e) {
+    ow = fast_div(q, gpp_magic);
+    e = (q - ow * gpp) << 2;
+    const int shift = ow * g.sw;
+    const int4 l = *reinterpret_cast<const int4*>(lut + e);
+    v[0] = tile[l.x + shift]; v[1] = tile[l.y + shift]; v[2] = tile[l.z + shift]; v[3] = tile[l.w + shift];
+  };
+  // every thread of the warp calls this (q >= n_groups: nothing to add).  `quads`: tiles are whole multiples of 16
+  // elements, so the 4 lanes of an aligned quad always share their (patch, tile) and one of them speaks for all.
+  auto fold_max = [&](bool valid, const float (&v)[4], int ow, int e) {
+    float m = valid ? fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))) : 0.0f;
+    if (quads) {
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+      if ((threadIdx.x & 3) != 0) valid = false;
+    }
+    // non-negative floats order like their bits
+    if (valid) atomicMax(&amax_bits[ow * T + grp_tile[e >> 2]], __float_as_uint(m));
+  };
+  const int64_t base = ((int64_t)out_row * g.Wo) * ckk;
+  // |v| <= the range of its tile, so |v / step| <= inp_res / 2 (or the quotient is NaN): rounding to an integer by
+  // adding and subtracting 1.5 * 2^23 needs no large-value case here
+  auto emit = [&](const float (&v)[4], int ow, int e) {
+    const int seg = ow * T + grp_tile[e >> 2];
+    const float step = seg_step[seg], stepc = step < kTiny ? kTiny : step, rstep = seg_rstep[seg];
+    float code[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      code[u] = fsub(fadd(rnd_int<DT>(fdiv_rcp(v[u], stepc, rstep)), 12582912.0f), 12582912.0f);
+    const int64_t at = base + (int64_t)ow * ckk + e;  // a multiple of 4
+    if (dac.codes16 != nullptr)  // small integers: exact in bf16
+      *reinterpret_cast<uint2*>(dac.codes16 + at) = make_uint2(cvt_bf16x2(code[0], code[1]), cvt_bf16x2(code[2], code[3]));
+    if (out != nullptr) {
+      float val[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) val[u] = rnd_int<DT>(fmul(code[u], step));
+      if (DT == kF32)
+        *reinterpret_cast<float4*>(static_cast<float*>(out) + at) = make_float4(val[0], val[1], val[2], val[3]);
+      else  // values already rounded to bf16
+        *reinterpret_cast<uint2*>(static_cast<uint16_t*>(out) + at) =
+            make_uint2(cvt_bf16x2(val[0], val[1]), cvt_bf16x2(val[2], val[3]));
+    }
+  };
+
+  float held[HOLD > 0 ? HOLD : 1][4];
+  if (HOLD > 0) {
+#pragma unroll
+    for (int h = 0; h < HOLD; ++h) {
+      const int q = threadIdx.x + h * 256;
+      int ow = 0, e = 0;
+      if (q < n_groups) gather(q, held[h], ow, e);
+      fold_max(q < n_groups, held[h], ow, e);
+    }
+  } else {
+    for (int q0 = 0; q0 < n_groups; q0 += 256) {
+      const int q = q0 + threadIdx.x;
+      int ow = 0, e = 0;
+      if (q < n_groups) gather(q, held[0], ow, e);
+      fold_max(q < n_groups, held[0], ow, e);
+    }
+  }
+  __syncthreads();
+  const int64_t rows_total = (int64_t)g.B * g.Ho * g.Wo;
+  for (int i = threadIdx.x; i < g.Wo * T; i += blockDim.x) {
+    const int t = i / g.Wo, ow = i - t * g.Wo;  // consecutive threads write consecutive ranges
+    const float amax = __uint_as_float(amax_bits[ow * T + t]);
+    Elem<DT>::store(dac.ir_rows, (int64_t)t * rows_total + (int64_t)out_row * g.Wo + ow, amax);
+    const QuantSeg q = dac_prepare<DT>(amax, dac.inp_res, false, false);
+    seg_step[ow * T + t] = q.step;
+    seg_rstep[ow * T + t] = q.rstep;
+  }
+  __syncthreads();
+  if (HOLD > 0) {
+#pragma unroll
+    for (int h = 0; h < HOLD; ++h) {
+      const int q = threadIdx.x + h * 256;
+      if (q < n_groups) {
+        const int ow = fast_div(q, gpp_magic);
+        emit(held[h], ow, (q - ow * gpp) << 2);
+      }
+    }
+  } else {
+    for (int q = threadIdx.x; q < n_groups; q += 256) {
+      int ow, e;
+      gather(q, held[0], ow, e);
+      emit(held[0], ow, e);
     }
   }
 }
@@ -374,6 +569,17 @@ int fold_chunk(const ConvGeom& g) {
   return even_chunk(g.C, c);
 }
 
+StageDiv make_stage_div(const ConvGeom& g, int span, int per_row, int n_pads) {
+  StageDiv dv;
+  dv.kw = magic_of(g.kw);
+  dv.kh = magic_of(g.kh);
+  dv.span = magic_of(span);
+  dv.per_row = magic_of(per_row > 0 ? per_row : 1);
+  dv.pads = magic_of(n_pads > 0 ? n_pads : 1);
+  dv.n_pads = n_pads;
+  return dv;
+}
+
 int make_geom(int B, int C, int H, int W, int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
               ConvGeom* g) {
   if (B < 1 || C < 1 || H < 1 || W < 1 || kh < 1 || kw < 1 || sh < 1 || sw < 1 || ph < 0 || pw < 0 || dh < 1 ||
@@ -423,8 +629,9 @@ int al_unfold2d(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t H, i
   if (chunk >= 1 && (int64_t)B * g.Ho * ((C + chunk - 1) / chunk) < 2147483647) {
     const unsigned grid = (unsigned)((int64_t)B * g.Ho * ((C + chunk - 1) / chunk));
     const size_t smem = (size_t)chunk * (kh * span + kh * kw + kh) * 4;
-    if (dtype == AL_F32) unfold2d_rows_kernel<kF32, false><<<grid, 256, smem, (cudaStream_t)stream>>>(x, g, chunk, span, out, UnfoldDac());
-    else unfold2d_rows_kernel<kBF16, false><<<grid, 256, smem, (cudaStream_t)stream>>>(x, g, chunk, span, out, UnfoldDac());
+    const StageDiv dv = make_stage_div(g, span, 1, 0);
+    if (dtype == AL_F32) unfold2d_rows_kernel<kF32, false><<<grid, 256, smem, (cudaStream_t)stream>>>(x, g, chunk, span, dv, out, UnfoldDac());
+    else unfold2d_rows_kernel<kBF16, false><<<grid, 256, smem, (cudaStream_t)stream>>>(x, g, chunk, span, dv, out, UnfoldDac());
     return check_launch("unfold2d_rows");
   }
   if (dtype == AL_F32) unfold2d_kernel<kF32><<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(x, g, out);
@@ -472,9 +679,36 @@ int al_unfold2d_dac(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t 
   cudaStream_t st = (cudaStream_t)stream;
   ProfScope prof(AL_K_UNFOLD, st);
   const unsigned grid = (unsigned)((int64_t)B * g.Ho);
+  // patches and analog tiles in whole groups of 4 elements: the kernel with vector stores
+  bool by4 = ckk % 4 == 0 && (!xq || aligned16(xq)) && (!codes16 || aligned16(codes16));
+  bool quads = true;  // tiles in whole multiples of 16 elements: four neighbouring lanes always share a tile
+  for (int t = 0; t < T; ++t) {
+    by4 = by4 && tile_ends_host[t] % 4 == 0;
+    quads = quads && tile_ends_host[t] % 16 == 0;
+  }
+  // 16-byte loads of the image rows need rows that start aligned and a slot that holds the whole padded row; the
+  // slot length is odd either way (bank spread of the stores and of the gather)
+  const int vec = dtype == AL_F32 ? 4 : 8;
+  const bool by16 = W % vec == 0 && aligned16(x);
+  const int pitch = (by16 && pw + W > span ? pw + W : span) | 1;
+  const size_t smem4 = ((size_t)((C * kh * pitch + 3) & ~3) + ckk + C * kh + 3 * (size_t)g.Wo * T) * 4 + ckk / 4;
+  if (by4 && smem4 <= 48 * 1024) {
+    const bool hold = (int64_t)g.Wo * (ckk / 4) <= kGroupHold * 256;
+    const StageDiv dv = make_stage_div(g, pitch, W / vec, by16 ? pw + (pitch - (pw + W)) : 0);
+    const uint32_t gm = magic_of(ckk / 4);
+    if (dtype == AL_F32) {
+      if (hold) unfold2d_dac4_kernel<kF32, kGroupHold><<<grid, 256, smem4, st>>>(x, g, pitch, dv, gm, by16, quads, xq, host);
+      else unfold2d_dac4_kernel<kF32, 0><<<grid, 256, smem4, st>>>(x, g, pitch, dv, gm, by16, quads, xq, host);
+    } else {
+      if (hold) unfold2d_dac4_kernel<kBF16, kGroupHold><<<grid, 256, smem4, st>>>(x, g, pitch, dv, gm, by16, quads, xq, host);
+      else unfold2d_dac4_kernel<kBF16, 0><<<grid, 256, smem4, st>>>(x, g, pitch, dv, gm, by16, quads, xq, host);
+    }
+    return check_launch("unfold2d_dac4");
+  }
   const size_t smem = (size_t)chunk * (kh * span + kh * kw + kh) * 4;
-  if (dtype == AL_F32) unfold2d_rows_kernel<kF32, true><<<grid, 256, smem, st>>>(x, g, chunk, span, xq, host);
-  else unfold2d_rows_kernel<kBF16, true><<<grid, 256, smem, st>>>(x, g, chunk, span, xq, host);
+  const StageDiv dv_rows = make_stage_div(g, span, 1, 0);
+  if (dtype == AL_F32) unfold2d_rows_kernel<kF32, true><<<grid, 256, smem, st>>>(x, g, chunk, span, dv_rows, xq, host);
+  else unfold2d_rows_kernel<kBF16, true><<<grid, 256, smem, st>>>(x, g, chunk, span, dv_rows, xq, host);
   return check_launch("unfold2d_dac");
 }
 

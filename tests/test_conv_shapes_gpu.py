@@ -192,3 +192,69 @@ def test_conv2d_on_the_tensor_cores_matches_the_cuda_core_route(cin, cout, size,
     assert _lib.load().al_uses_tcgen05(desc, _lib.tile_ends_array(conv.in_sizes))
     for got, want in zip(results["auto"], results["simt"]):
         assert ((got - want).norm() / want.norm()).item() <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("cin,size,stride,max_in,batch,pad", [
+    (16, 32, 1, 256, 3, 1),    # 144-element patches, one tile, 1152 groups of 4 per output row (kept in registers)
+    (32, 16, 1, 256, 3, 1),    # two tiles of 144
+    (64, 8, 1, 256, 5, 1),     # three tiles of 192
+    (32, 32, 2, 256, 2, 1),    # strided
+    (16, 64, 1, 256, 2, 1),    # 2304 groups per output row: gathered twice
+    (16, 32, 1, 100, 2, 1),    # tiles of 72: whole groups, but four neighbouring groups may straddle two tiles
+    (16, 30, 1, 256, 2, 1),    # image rows that are no multiple of 16 bytes: element-wise staging
+    (16, 32, 1, 256, 2, 0),    # no padding
+    (16, 32, 1, 256, 2, 2),    # two padding columns on either side
+    (12, 20, 1, 256, 2, 1),    # 108-element patches
+    (5, 20, 1, 256, 2, 1),     # 45-element patches: not a multiple of 4, the element-wise kernel
+], ids=["c16", "c32-two-tiles", "c64-three-tiles", "stride2", "wide", "tiles-of-72", "odd-row-length", "no-padding",
+        "padding-2", "patches-of-108", "ragged"])
+def test_patch_extraction_with_the_dac_fused_is_bit_exact(dtype, cin, size, stride, max_in, batch, pad):
+    """``al_unfold2d_dac`` writes the quantised patches, their integer codes as bf16 and the per-(tile, patch) ranges;
+    all three equal, bit for bit, what the patch-extraction kernel followed by the stand-alone DAC of the linear
+    layer produces (which the parity tests pin against the oracle)."""
+    from aihwkit_lightning_b200 import _lib
+    from aihwkit_lightning_b200.nn import AnalogLinear
+    from aihwkit_lightning_b200.nn import functional as F
+    from aihwkit_lightning_b200.simulator.configs import TorchInferenceRPUConfig
+
+    rpu = TorchInferenceRPUConfig()
+    rpu.mapping.max_input_size = max_in
+    rpu.forward.inp_res = 254
+    rpu.forward.out_noise = 0.0
+    rpu.pre_post.input_range.enable = True
+    rpu.pre_post.input_range.dynamic = True
+    torch.manual_seed(5)
+    x = (torch.randn(batch, cin, size, size, device="cuda") * 1.7).to(dtype)
+    x[0, :, :5, :9] = 0.0       # patches that are zero throughout: range 0, step clamped to tiny
+    x[1, 3, 7, 2] = 40.0        # an outlier that sets the range of the patches around it
+    k = cin * 9
+    patches = F.unfold2d(x, (3, 3), (1, 1), (pad, pad), (stride, stride)).reshape(-1, k)
+    layer = AnalogLinear(k, 8, bias=False, rpu_config=rpu).to(device="cuda", dtype=dtype).eval()
+    cap = {}
+    with torch.no_grad(), F.operator_settings(capture=cap, engine="simt"):
+        layer(patches)
+    rows, t = patches.shape[0], len(layer.in_sizes)
+    xq = torch.empty(rows, k, device="cuda", dtype=dtype)
+    codes16 = torch.empty(rows, k, device="cuda", dtype=torch.bfloat16)
+    ir_rows = torch.empty(t, rows, device="cuda", dtype=dtype)
+    lib = _lib.load()
+    geom = (batch, cin, size, size, 3, 3, stride, stride, pad, pad, 1, 1)
+    ends = _lib.tile_ends_array(layer.in_sizes)
+    stream = torch.cuda.current_stream().cuda_stream
+    code = 1 if dtype == torch.bfloat16 else 0
+    _lib.check(lib.al_unfold2d_dac(code, x.data_ptr(), *geom, ends, t, 254.0, xq.data_ptr(), ir_rows.data_ptr(),
+                                   codes16.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert torch.equal(ir_rows, cap["ir_rows"].reshape(t, rows))
+    assert torch.equal(xq, cap["xq"].reshape(rows, k))
+    assert torch.equal(codes16.float(), cap["codes"].reshape(rows, k).float())
+    # one output at a time gives the same bytes (the tensor-core route asks for the codes alone)
+    only_codes = torch.zeros_like(codes16)
+    _lib.check(lib.al_unfold2d_dac(code, x.data_ptr(), *geom, ends, t, 254.0, None, ir_rows.data_ptr(),
+                                   only_codes.data_ptr(), stream))
+    only_xq = torch.zeros_like(xq)
+    _lib.check(lib.al_unfold2d_dac(code, x.data_ptr(), *geom, ends, t, 254.0, only_xq.data_ptr(), ir_rows.data_ptr(),
+                                   None, stream))
+    torch.cuda.synchronize()
+    assert torch.equal(only_codes, codes16) and torch.equal(only_xq, xq)
