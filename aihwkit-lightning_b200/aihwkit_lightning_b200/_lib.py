@@ -84,6 +84,8 @@ SYMBOLS = {
     "al_clip_weights": (c_int32, [c_int32, c_void_p, c_int32, c_int32, c_int32, c_float, c_void_p, c_void_p]),
     "al_unfold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
     "al_fold2d": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [c_void_p, c_void_p]),
+    "al_conv2d_input_grad_supported": (c_int32, [c_int32] * 14),
+    "al_conv2d_input_grad": (c_int32, [c_int32, c_void_p, c_void_p] + [c_int32] * 13 + [c_void_p, c_void_p]),
     "al_unfold2d_dac": (c_int32, [c_int32, c_void_p] + [c_int32] * 12 + [POINTER(c_int32), c_int32, c_double, c_void_p,
                                                                        c_void_p, c_void_p, c_void_p]),
     "al_swiglu_forward": (c_int32, [c_int32, c_void_p, c_int64, c_int32, c_void_p, c_void_p]),

@@ -66,6 +66,9 @@ class _Settings:
     # a ``GraphNoise``: the calls draw their noise counters from it instead of torch's generator, so
     # that a training step can be captured in a CUDA graph and still see fresh noise on every replay
     graph_noise = None
+    # fp32 convolutions with fewer than 64 output channels and no ADC compute their input gradient straight
+    # from the output gradient (``al_conv2d_input_grad``) instead of a patch gradient that is folded afterwards
+    conv_direct_input_grad = True
 
 
 settings = _Settings()
@@ -422,8 +425,10 @@ def _analog_forward(ctx, inp, weight, bias, input_range, input_range_update_idx,
     return out.view(*inp.shape[:-1], n) if prequant is None else out
 
 
-def _analog_backward(ctx, grad_out):
-    """The matching backward call: gradients of input, weight, bias, input range and weight ranges."""
+def _analog_backward(ctx, grad_out, skip_input_grad=False):
+    """The matching backward call: gradients of input, weight, bias, input range and weight ranges.
+    ``skip_input_grad``: the caller computes the input gradient itself (a convolution that never forms the
+    patch gradient)."""
     if ctx.empty:
         return (None,) * 12
     lib = _lib.load()
@@ -433,6 +438,7 @@ def _analog_backward(ctx, grad_out):
     dev, dtype = grad_out.device, ctx.dtype
     g = grad_out.reshape(m, n).to(dtype).contiguous()
     need_x, need_w, need_b, need_ir = ctx.needs_input_grad[:4]
+    need_x = need_x and not skip_input_grad
     need_b = need_b and ctx.has_bias
     need_ir = need_ir and ctx.ir_needs_grad
     need_clip = ctx.learn_clip and (ctx.needs_input_grad[10] or need_w)
@@ -607,6 +613,33 @@ class Unfold2dFunction(torch.autograd.Function):
         return gx, None, None, None, None
 
 
+def _direct_input_grad_applies(ctx) -> bool:
+    """Whether the input gradient of this convolution comes straight from ``grad_out`` and the modified weights
+    (``al_conv2d_input_grad``) instead of the general route (patch gradient + fold).  Not with an ADC clamp
+    mask, strides, bf16, fewer than 4 or at least 64 output channels (from 64 on the patch gradient is a
+    tensor-core GEMM)."""
+    if ctx.empty or not ctx.needs_input_grad[0] or not settings.conv_direct_input_grad:
+        return False
+    w_mod, keep_mask = ctx.saved_tensors[2], ctx.saved_tensors[4]
+    if w_mod is None or keep_mask is not None or ctx.dtype != torch.float32 or ctx.desc.N >= 64:
+        return False
+    if ctx.ir_needs_grad:
+        return False
+    return bool(_lib.load().al_conv2d_input_grad_supported(ctx.dtype_code, ctx.desc.N, *ctx.geom))
+
+
+def _direct_input_grad(ctx, grad_out):
+    lib = _lib.load()
+    desc, w_mod = ctx.desc, ctx.saved_tensors[2]
+    b, c, h, w = ctx.geom[:4]
+    g = grad_out.reshape(desc.M, desc.N).to(ctx.dtype).contiguous()
+    grad_img = torch.empty(b, c, h, w, device=g.device, dtype=g.dtype)
+    with _OnDevice(g.device):
+        _lib.check(lib.al_conv2d_input_grad(ctx.dtype_code, g.data_ptr(), w_mod.data_ptr(), desc.N, *ctx.geom,
+                                            grad_img.data_ptr(), _stream(g.device)))
+    return grad_img
+
+
 class AnalogConv2dFunction(torch.autograd.Function):
     """Analog convolution with a dynamic input range as ONE operator: the patch extraction quantises on
     the way (``al_unfold2d_dac``), the tiled GEMM consumes the quantised patches, and the backward folds
@@ -647,8 +680,9 @@ class AnalogConv2dFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_out):  # type: ignore[override]
-        grads = _analog_backward(ctx, grad_out)
-        grad_img = None
+        direct = _direct_input_grad_applies(ctx)
+        grads = _analog_backward(ctx, grad_out, skip_input_grad=direct)  # weight-side gradients first
+        grad_img = _direct_input_grad(ctx, grad_out) if direct else None
         if grads[0] is not None:
             lib = _lib.load()
             gp = grads[0]

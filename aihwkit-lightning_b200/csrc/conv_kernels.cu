@@ -6,6 +6,7 @@
 #include <string.h>
 
 #include "analog_math.cuh"
+#include "device_fast.cuh"
 #include "internal.h"
 
 namespace al {
@@ -525,6 +526,140 @@ fold2d_band_unit_kernel(const float* __restrict__ gp, ConvGeom g, int c_chunk, i
   }
 }
 
+// ---- input gradient of a unit-stride convolution without the patch matrix --------------------------------------
+// grad_x[b, c, h, w] = sum over taps (i, j) and output channels n of grad_out[b, h + ph - i, w + pw - j, n] *
+// w[n, c, i, j]: the product grad_out @ w followed by the fold, computed in place.  For layers with few output
+// channels the patch gradient (kh * kw times the image) costs far more to write and read back than these
+// multiplications cost on the CUDA cores.  A CTA owns `R` image rows of one image and a chunk of input channels;
+// it stages the R + kh - 1 rows of grad_out it needs as gs[row][n][column] (zero outside the image, so the sums
+// need no validity tests) and the weights as ws[tap][n][channel].  A thread accumulates two pixels (rows hr and
+// hr + R / 2, same column) times CT channels in packed fp32 pairs: per (tap, n) two scalar loads of grad_out and CT / 4
+// 16-byte broadcast loads of weights feed CT packed multiply-adds.
+struct DirectPlan {
+  int R, c_chunk, ct, rp, tp, threads;
+  size_t smem;
+  uint32_t m_w, m_kk, m_ckk, m_per_row, m_n4;
+};
+
+template <int CT>
+__global__ void __launch_bounds__(256)
+conv2d_dgrad_direct_kernel(const float* __restrict__ go, const float* __restrict__ w, ConvGeom g, int N, DirectPlan pl,
+                           float* __restrict__ gx) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int kk = g.kh * g.kw, ckk = g.C * kk;
+  const int Wp = g.W + g.kw - 1, rows = pl.R + g.kh - 1, half = pl.R >> 1;
+  const int gs_floats = (rows * pl.rp + 3) & ~3;
+  float* gs = reinterpret_cast<float*>(smem_raw);  // [rows] x rp floats, a row = [N][Wp]
+  float* ws = gs + gs_floats;                      // [kk] x tp floats, a tap = [N][c_chunk]
+  const int bands = (g.H + pl.R - 1) / pl.R;
+  const int b = blockIdx.x / bands, h0 = (blockIdx.x - b * bands) * pl.R;
+  const int c0 = blockIdx.y * pl.c_chunk;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  for (int i = tid; i < gs_floats / 4; i += nthreads) reinterpret_cast<float4*>(gs)[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  const int run = pl.c_chunk * kk;  // weights of one output channel for this chunk: contiguous in w
+  for (int idx = tid; idx < N * run; idx += nthreads) {
+    const int n = fast_div(idx, pl.m_ckk), e = idx - n * run;
+    const int cl = fast_div(e, pl.m_kk), tap = e - cl * kk;
+    ws[tap * pl.tp + n * pl.c_chunk + cl] = w[(int64_t)n * ckk + (int64_t)c0 * kk + e];
+  }
+  __syncthreads();
+  const int oh_min = h0 + g.ph - (g.kh - 1), col0 = g.kw - 1 - g.pw;
+  const int n4 = N >> 2, per_row = g.Wo * n4;
+  for (int idx = tid; idx < rows * per_row; idx += nthreads) {
+    const int r = fast_div(idx, pl.m_per_row), rem = idx - r * per_row;
+    const int ow = fast_div(rem, pl.m_n4), q = rem - ow * n4;
+    const int oh = oh_min + r;
+    if (oh < 0 || oh >= g.Ho) continue;
+    const float4 v = *reinterpret_cast<const float4*>(go + (((int64_t)b * g.Ho + oh) * g.Wo + ow) * N + 4 * q);
+    float* d = gs + r * pl.rp + (4 * q) * Wp + col0 + ow;
+    d[0] = v.x; d[Wp] = v.y; d[2 * Wp] = v.z; d[3 * Wp] = v.w;
+  }
+  __syncthreads();
+  const int warp = tid >> 5, lane = tid & 31, n_warps = nthreads >> 5;
+  const int pixels = half * g.W, px_chunks = (pixels + 31) >> 5, c_groups = pl.c_chunk / CT;
+  for (int item = warp; item < px_chunks * c_groups; item += n_warps) {
+    const int cg = item / px_chunks, pc = item - cg * px_chunks;
+    const int p = pc * 32 + lane;
+    const bool valid = p < pixels;
+    const int hr = valid ? fast_div(p, pl.m_w) : 0, wc = valid ? p - hr * g.W : 0;
+    uint64_t a0[CT / 2], a1[CT / 2];
+#pragma unroll
+    for (int u = 0; u < CT / 2; ++u) a0[u] = a1[u] = 0ull;  // two +0.0f
+    for (int i = 0; i < g.kh; ++i) {
+      for (int j = 0; j < g.kw; ++j) {
+        const float* gt0 = gs + (hr + g.kh - 1 - i) * pl.rp + (wc + g.kw - 1 - j);
+        const float* gt1 = gt0 + half * pl.rp;
+        const float* wt = ws + (i * g.kw + j) * pl.tp + cg * CT;
+#pragma unroll 4
+        for (int n = 0; n < N; ++n) {
+          const float g0 = gt0[n * Wp], g1 = gt1[n * Wp];
+          const uint64_t g0p = f32x2_pack(g0, g0), g1p = f32x2_pack(g1, g1);
+#pragma unroll
+          for (int v4 = 0; v4 < CT / 4; ++v4) {
+            const ulonglong2 wv = *reinterpret_cast<const ulonglong2*>(wt + n * pl.c_chunk + 4 * v4);
+            a0[2 * v4] = f32x2_fma(wv.x, g0p, a0[2 * v4]);
+            a0[2 * v4 + 1] = f32x2_fma(wv.y, g0p, a0[2 * v4 + 1]);
+            a1[2 * v4] = f32x2_fma(wv.x, g1p, a1[2 * v4]);
+            a1[2 * v4 + 1] = f32x2_fma(wv.y, g1p, a1[2 * v4 + 1]);
+          }
+        }
+      }
+    }
+    if (!valid) continue;
+    const int h_a = h0 + hr, h_b = h_a + half;
+#pragma unroll
+    for (int u = 0; u < CT / 2; ++u) {
+      const int c = c0 + cg * CT + 2 * u;
+      float lo, hi;
+      if (h_a < g.H) {
+        f32x2_unpack(a0[u], &lo, &hi);
+        gx[(((int64_t)b * g.C + c) * g.H + h_a) * g.W + wc] = lo;
+        gx[(((int64_t)b * g.C + c + 1) * g.H + h_a) * g.W + wc] = hi;
+      }
+      if (h_b < g.H) {
+        f32x2_unpack(a1[u], &lo, &hi);
+        gx[(((int64_t)b * g.C + c) * g.H + h_b) * g.W + wc] = lo;
+        gx[(((int64_t)b * g.C + c + 1) * g.H + h_b) * g.W + wc] = hi;
+      }
+    }
+  }
+}
+
+constexpr size_t kDirectMaxSmem = 96 * 1024;
+
+// 0 = the direct kernel does not apply
+int plan_direct(int dtype, const ConvGeom& g, int N, DirectPlan* pl) {
+  if (dtype != AL_F32 || g.sh != 1 || g.sw != 1 || g.dh != 1 || g.dw != 1) return 0;
+  if (g.ph > g.kh - 1 || g.pw > g.kw - 1 || N < 4 || N % 4 != 0 || g.C % 4 != 0) return 0;
+  const int kk = g.kh * g.kw, Wp = g.W + g.kw - 1;
+  pl->ct = g.C % 8 == 0 ? 8 : 4;
+  // bands of 8 rows while that still gives every SM several CTAs, else 4
+  pl->R = (int64_t)g.B * ((g.H + 7) / 8) >= 6 * 148 ? 8 : 4;
+  // a warp spans 32 / W rows when the image is narrow: a row pitch of W (mod 32) keeps its lanes in distinct banks
+  int rp = N * Wp;
+  if (g.W < 32) rp += ((g.W - rp % 32) + 32) % 32;
+  pl->rp = rp;
+  const size_t gs_bytes = (size_t)(((pl->R + g.kh - 1) * rp + 3) & ~3) * 4;
+  int cc = g.C;
+  for (;;) {
+    pl->tp = N * cc + 4;
+    pl->smem = gs_bytes + (size_t)kk * pl->tp * 4;
+    if (pl->smem <= kDirectMaxSmem) break;
+    if (cc % 2 != 0 || (cc / 2) % pl->ct != 0) return 0;
+    cc /= 2;
+  }
+  pl->c_chunk = cc;
+  const int items = (((pl->R / 2) * g.W + 31) / 32) * (cc / pl->ct);
+  pl->threads = 32 * (items < 8 ? items : 8);
+  if ((int64_t)g.B * ((g.H + pl->R - 1) / pl->R) >= 2147483647 || g.C / cc > 65535) return 0;
+  pl->m_w = magic_of(g.W);
+  pl->m_kk = magic_of(kk);
+  pl->m_ckk = magic_of(cc * kk);
+  pl->m_per_row = magic_of(g.Wo * (N / 4));
+  pl->m_n4 = magic_of(N / 4);
+  return 1;
+}
+
 constexpr size_t kFoldUnitMaxSmem = 100 * 1024;
 
 // floats per staged slot of the unit-stride kernel: the run, padded to an odd multiple of 4
@@ -758,6 +893,52 @@ int al_fold2d(int32_t dtype, const void* grad_patches, int32_t B, int32_t C, int
   if (dtype == AL_F32) fold2d_kernel<kF32><<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(grad_patches, g, grad_x);
   else fold2d_kernel<kBF16><<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(grad_patches, g, grad_x);
   return check_launch("fold2d");
+}
+
+int al_conv2d_input_grad_supported(int32_t dtype, int32_t N, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh,
+                                   int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw) {
+  ConvGeom g;
+  DirectPlan pl;
+  if (make_geom(B, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, &g)) return 0;
+  return plan_direct(dtype, g, N, &pl);
+}
+
+int al_conv2d_input_grad(int32_t dtype, const void* grad_out, const void* w_mod, int32_t N, int32_t B, int32_t C,
+                         int32_t H, int32_t W, int32_t kh, int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw,
+                         int32_t dh, int32_t dw, void* grad_x, void* stream) {
+  if (!grad_out || !w_mod || !grad_x) {
+    set_error("al_conv2d_input_grad: null pointer");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  ConvGeom g;
+  int rc = make_geom(B, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, &g);
+  if (rc) return rc;
+  DirectPlan pl;
+  if (!plan_direct(dtype, g, N, &pl) || !aligned16(grad_out)) {
+    set_error("al_conv2d_input_grad: not a unit-stride fp32 convolution the direct kernel covers "
+              "(ask al_conv2d_input_grad_supported; use al_backward and al_fold2d)");
+    return AL_ERR_UNSUPPORTED;
+  }
+  ProfScope prof(AL_K_DGRAD_GEMM, (cudaStream_t)stream);
+  const dim3 grid((unsigned)((int64_t)B * ((H + pl.R - 1) / pl.R)), (unsigned)(C / pl.c_chunk));
+  const float* go = static_cast<const float*>(grad_out);
+  const float* wm = static_cast<const float*>(w_mod);
+  float* gx = static_cast<float*>(grad_x);
+  cudaError_t attr = cudaSuccess;
+  if (pl.ct == 8) {
+    if (pl.smem > 48 * 1024)
+      attr = cudaFuncSetAttribute(conv2d_dgrad_direct_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDirectMaxSmem);
+    if (attr == cudaSuccess) conv2d_dgrad_direct_kernel<8><<<grid, pl.threads, pl.smem, (cudaStream_t)stream>>>(go, wm, g, N, pl, gx);
+  } else {
+    if (pl.smem > 48 * 1024)
+      attr = cudaFuncSetAttribute(conv2d_dgrad_direct_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDirectMaxSmem);
+    if (attr == cudaSuccess) conv2d_dgrad_direct_kernel<4><<<grid, pl.threads, pl.smem, (cudaStream_t)stream>>>(go, wm, g, N, pl, gx);
+  }
+  if (attr != cudaSuccess) {
+    set_error("al_conv2d_input_grad: cudaFuncSetAttribute: %s", cudaGetErrorString(attr));
+    return AL_ERR_CUDA;
+  }
+  return check_launch("conv2d_dgrad_direct");
 }
 
 }  // extern "C"

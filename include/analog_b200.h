@@ -269,6 +269,19 @@ int al_unfold2d_dac(int32_t dtype, const void* x, int32_t B, int32_t C, int32_t 
 int al_fold2d(int32_t dtype, const void* grad_patches, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh,
               int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw, void* grad_x,
               void* stream);
+/* Input gradient of a convolution without the patch matrix: grad_x[b,c,h,w] = sum over taps (i, j) and output
+ * channels n of grad_out[b, h+ph-i, w+pw-j, n] * w_mod[n, (c*kh+i)*kw+j] -- the same values as the product
+ * grad_out @ w_mod of al_backward followed by al_fold2d (the autograd of P/conv.py:312-322 + P/torch_utils/
+ * torch_linear.py:253), summed in another order.  For layers with few output channels the patch gradient costs more
+ * to write and read back than these multiplications.  grad_out [B*Ho*Wo, N] and w_mod [N, C*kh*kw] (the modified
+ * weights the forward multiplied with) are fp32; only for layers without an ADC clamp mask (out_bound <= 0), unit
+ * stride, no dilation, padding smaller than the kernel, N and C multiples of 4: al_conv2d_input_grad_supported
+ * returns 1 for those, and al_conv2d_input_grad returns AL_ERR_UNSUPPORTED otherwise. */
+int al_conv2d_input_grad_supported(int32_t dtype, int32_t N, int32_t B, int32_t C, int32_t H, int32_t W, int32_t kh,
+                                   int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t dh, int32_t dw);
+int al_conv2d_input_grad(int32_t dtype, const void* grad_out, const void* w_mod, int32_t N, int32_t B, int32_t C,
+                         int32_t H, int32_t W, int32_t kh, int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw,
+                         int32_t dh, int32_t dw, void* grad_x, void* stream);
 
 /* Element-wise operators of a decoder layer that sit between its analog linear layers, one pass each
  * (16-byte vectors, fp32 arithmetic, one rounding per result); the reference leaves them to PyTorch

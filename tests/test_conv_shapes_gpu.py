@@ -258,3 +258,67 @@ def test_patch_extraction_with_the_dac_fused_is_bit_exact(dtype, cin, size, stri
                                    None, stream))
     torch.cuda.synchronize()
     assert torch.equal(only_codes, codes16) and torch.equal(only_xq, xq)
+
+
+@pytest.mark.parametrize("cin,cout,size,batch,ksize,pad", [
+    (16, 16, 32, 8, 3, 1),      # bands of 4 rows, 8 channels per thread
+    (16, 16, 32, 224, 3, 1),    # enough images for bands of 8 rows (the ResNet-32 stage-1 shape)
+    (32, 32, 16, 64, 3, 1),     # 16 columns: a warp spans two rows; weights beyond 48 KB of shared memory
+    (16, 32, 32, 4, 3, 1),
+    (8, 12, 20, 3, 3, 1),       # a row length that does not divide 32
+    (4, 4, 9, 2, 3, 0),         # no padding, a last band with a single row, 4 channels per thread
+    (8, 8, 12, 2, 5, 2),        # 5 x 5 taps
+    (64, 32, 8, 16, 3, 1),      # 64 input channels
+], ids=["c16", "c16-bands-of-8", "c32-w16", "n32", "w20", "h9-no-padding", "taps-5x5", "c64"])
+def test_direct_input_gradient_of_a_convolution_matches_the_patch_route(cin, cout, size, batch, ksize, pad):
+    """fp32 convolutions with fewer than 64 output channels and no ADC compute their input gradient straight from
+    the output gradient (``al_conv2d_input_grad``): same values as patch gradient + fold, and as the autograd of a
+    float64 convolution with the same weights."""
+    from aihwkit_lightning_b200.nn import AnalogConv2d
+    from aihwkit_lightning_b200.nn import functional as F
+    from aihwkit_lightning_b200.simulator.configs import TorchInferenceRPUConfig
+
+    rpu = TorchInferenceRPUConfig()
+    rpu.mapping.max_input_size = 256
+    rpu.forward.inp_res = 254
+    rpu.forward.out_noise = 0.0
+    rpu.pre_post.input_range.enable = True
+    rpu.pre_post.input_range.dynamic = True
+    torch.manual_seed(1)
+    conv = AnalogConv2d(cin, cout, ksize, padding=pad, bias=False, rpu_config=rpu).cuda().train()
+    x = torch.randn(batch, cin, size, size, device="cuda")
+    out_size = size + 2 * pad - ksize + 1
+    g = torch.randn(batch, cout, out_size, out_size, device="cuda")
+    lib = __import__("aihwkit_lightning_b200._lib", fromlist=["load"]).load()
+    assert lib.al_conv2d_input_grad_supported(0, cout, batch, cin, size, size, ksize, ksize, 1, 1, pad, pad, 1, 1)
+    grads = {}
+    for direct in (True, False):
+        xin = x.clone().requires_grad_(True)
+        conv.zero_grad(set_to_none=True)
+        with F.operator_settings(conv_direct_input_grad=direct):
+            conv(xin).backward(g)
+        grads[direct] = (xin.grad.clone(), conv.weight.grad.clone())
+    assert ((grads[True][0] - grads[False][0]).norm() / grads[False][0].norm()).item() <= 1e-5
+    assert torch.equal(grads[True][1], grads[False][1])   # the weight gradient does not depend on the route
+    x64 = x.double().requires_grad_(True)
+    w64 = conv.weight.detach().double().reshape(cout, cin, ksize, ksize)
+    torch.nn.functional.conv2d(x64, w64, padding=pad).backward(g.double())
+    assert ((grads[True][0].double() - x64.grad).norm() / x64.grad.norm()).item() <= 1e-5
+
+
+def test_direct_input_gradient_is_refused_for_what_it_does_not_cover():
+    from aihwkit_lightning_b200 import _lib
+    lib = _lib.load()
+    geom = (4, 16, 32, 32, 3, 3, 1, 1, 1, 1, 1, 1)
+    assert lib.al_conv2d_input_grad_supported(0, 16, *geom) == 1
+    assert lib.al_conv2d_input_grad_supported(1, 16, *geom) == 0                                   # bf16
+    assert lib.al_conv2d_input_grad_supported(0, 16, 4, 16, 32, 32, 3, 3, 2, 2, 1, 1, 1, 1) == 0    # strided
+    assert lib.al_conv2d_input_grad_supported(0, 16, 4, 16, 32, 32, 3, 3, 1, 1, 1, 1, 2, 2) == 0    # dilated
+    assert lib.al_conv2d_input_grad_supported(0, 10, *geom) == 0                                   # N not a multiple of 4
+    assert lib.al_conv2d_input_grad_supported(0, 16, 4, 3, 32, 32, 3, 3, 1, 1, 1, 1, 1, 1) == 0     # 3 input channels
+    g = torch.zeros(4 * 16 * 16, 16, device="cuda")
+    w = torch.zeros(16, 144, device="cuda")
+    gx = torch.zeros(4, 16, 32, 32, device="cuda")
+    status = lib.al_conv2d_input_grad(0, g.data_ptr(), w.data_ptr(), 16, 4, 16, 32, 32, 3, 3, 2, 2, 1, 1, 1, 1,
+                                      gx.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert status == _lib.AL_ERR_UNSUPPORTED
