@@ -532,22 +532,22 @@ fold2d_band_unit_kernel(const float* __restrict__ gp, ConvGeom g, int c_chunk, i
 // channels the patch gradient (kh * kw times the image) costs far more to write and read back than these
 // multiplications cost on the CUDA cores.  A CTA owns `R` image rows of one image and a chunk of input channels;
 // it stages the R + kh - 1 rows of grad_out it needs as gs[row][n][column] (zero outside the image, so the sums
-// need no validity tests) and the weights as ws[tap][n][channel].  A thread accumulates two pixels (rows hr and
-// hr + R / 2, same column) times CT channels in packed fp32 pairs: per (tap, n) two scalar loads of grad_out and CT / 4
-// 16-byte broadcast loads of weights feed CT packed multiply-adds.
+// need no validity tests) and the weights as ws[tap][n][channel].  A thread accumulates PX pixels (rows hr + k * R / PX,
+// same column) times CT channels in packed fp32 pairs: per (tap, n) PX scalar loads of grad_out and CT / 4 16-byte
+// broadcast loads of weights feed PX * CT / 2 packed multiply-adds.
 struct DirectPlan {
-  int R, c_chunk, ct, rp, tp, threads;
+  int R, px, c_chunk, ct, rp, tp, threads;
   size_t smem;
   uint32_t m_w, m_kk, m_ckk, m_per_row, m_n4;
 };
 
-template <int CT>
+template <int CT, int PX>
 __global__ void __launch_bounds__(256)
 conv2d_dgrad_direct_kernel(const float* __restrict__ go, const float* __restrict__ w, ConvGeom g, int N, DirectPlan pl,
                            float* __restrict__ gx) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int kk = g.kh * g.kw, ckk = g.C * kk;
-  const int Wp = g.W + g.kw - 1, rows = pl.R + g.kh - 1, half = pl.R >> 1;
+  const int Wp = g.W + g.kw - 1, rows = pl.R + g.kh - 1, part = pl.R / PX;
   const int gs_floats = (rows * pl.rp + 3) & ~3;
   float* gs = reinterpret_cast<float*>(smem_raw);  // [rows] x rp floats, a row = [N][Wp]
   float* ws = gs + gs_floats;                      // [kk] x tp floats, a tap = [N][c_chunk]
@@ -576,50 +576,53 @@ conv2d_dgrad_direct_kernel(const float* __restrict__ go, const float* __restrict
   }
   __syncthreads();
   const int warp = tid >> 5, lane = tid & 31, n_warps = nthreads >> 5;
-  const int pixels = half * g.W, px_chunks = (pixels + 31) >> 5, c_groups = pl.c_chunk / CT;
+  const int pixels = part * g.W, px_chunks = (pixels + 31) >> 5, c_groups = pl.c_chunk / CT;
   for (int item = warp; item < px_chunks * c_groups; item += n_warps) {
     const int cg = item / px_chunks, pc = item - cg * px_chunks;
     const int p = pc * 32 + lane;
     const bool valid = p < pixels;
     const int hr = valid ? fast_div(p, pl.m_w) : 0, wc = valid ? p - hr * g.W : 0;
-    uint64_t a0[CT / 2], a1[CT / 2];
+    uint64_t acc[PX][CT / 2];
 #pragma unroll
-    for (int u = 0; u < CT / 2; ++u) a0[u] = a1[u] = 0ull;  // two +0.0f
+    for (int k = 0; k < PX; ++k)
+#pragma unroll
+      for (int u = 0; u < CT / 2; ++u) acc[k][u] = 0ull;  // two +0.0f
     for (int i = 0; i < g.kh; ++i) {
       for (int j = 0; j < g.kw; ++j) {
-        const float* gt0 = gs + (hr + g.kh - 1 - i) * pl.rp + (wc + g.kw - 1 - j);
-        const float* gt1 = gt0 + half * pl.rp;
+        const float* gt = gs + (hr + g.kh - 1 - i) * pl.rp + (wc + g.kw - 1 - j);
         const float* wt = ws + (i * g.kw + j) * pl.tp + cg * CT;
 #pragma unroll 4
         for (int n = 0; n < N; ++n) {
-          const float g0 = gt0[n * Wp], g1 = gt1[n * Wp];
-          const uint64_t g0p = f32x2_pack(g0, g0), g1p = f32x2_pack(g1, g1);
+          uint64_t gp[PX];
+#pragma unroll
+          for (int k = 0; k < PX; ++k) {
+            const float gv = gt[k * part * pl.rp + n * Wp];
+            gp[k] = f32x2_pack(gv, gv);
+          }
 #pragma unroll
           for (int v4 = 0; v4 < CT / 4; ++v4) {
             const ulonglong2 wv = *reinterpret_cast<const ulonglong2*>(wt + n * pl.c_chunk + 4 * v4);
-            a0[2 * v4] = f32x2_fma(wv.x, g0p, a0[2 * v4]);
-            a0[2 * v4 + 1] = f32x2_fma(wv.y, g0p, a0[2 * v4 + 1]);
-            a1[2 * v4] = f32x2_fma(wv.x, g1p, a1[2 * v4]);
-            a1[2 * v4 + 1] = f32x2_fma(wv.y, g1p, a1[2 * v4 + 1]);
+#pragma unroll
+            for (int k = 0; k < PX; ++k) {
+              acc[k][2 * v4] = f32x2_fma(wv.x, gp[k], acc[k][2 * v4]);
+              acc[k][2 * v4 + 1] = f32x2_fma(wv.y, gp[k], acc[k][2 * v4 + 1]);
+            }
           }
         }
       }
     }
     if (!valid) continue;
-    const int h_a = h0 + hr, h_b = h_a + half;
 #pragma unroll
-    for (int u = 0; u < CT / 2; ++u) {
-      const int c = c0 + cg * CT + 2 * u;
-      float lo, hi;
-      if (h_a < g.H) {
-        f32x2_unpack(a0[u], &lo, &hi);
-        gx[(((int64_t)b * g.C + c) * g.H + h_a) * g.W + wc] = lo;
-        gx[(((int64_t)b * g.C + c + 1) * g.H + h_a) * g.W + wc] = hi;
-      }
-      if (h_b < g.H) {
-        f32x2_unpack(a1[u], &lo, &hi);
-        gx[(((int64_t)b * g.C + c) * g.H + h_b) * g.W + wc] = lo;
-        gx[(((int64_t)b * g.C + c + 1) * g.H + h_b) * g.W + wc] = hi;
+    for (int k = 0; k < PX; ++k) {
+      const int h = h0 + hr + k * part;
+      if (h >= g.H) continue;
+#pragma unroll
+      for (int u = 0; u < CT / 2; ++u) {
+        const int c = c0 + cg * CT + 2 * u;
+        float lo, hi;
+        f32x2_unpack(acc[k][u], &lo, &hi);
+        gx[(((int64_t)b * g.C + c) * g.H + h) * g.W + wc] = lo;
+        gx[(((int64_t)b * g.C + c + 1) * g.H + h) * g.W + wc] = hi;
       }
     }
   }
@@ -633,8 +636,9 @@ int plan_direct(int dtype, const ConvGeom& g, int N, DirectPlan* pl) {
   if (g.ph > g.kh - 1 || g.pw > g.kw - 1 || N < 4 || N % 4 != 0 || g.C % 4 != 0) return 0;
   const int kk = g.kh * g.kw, Wp = g.W + g.kw - 1;
   pl->ct = g.C % 8 == 0 ? 8 : 4;
-  // bands of 8 rows while that still gives every SM several CTAs, else 4
-  pl->R = (int64_t)g.B * ((g.H + 7) / 8) >= 6 * 148 ? 8 : 4;
+  // bands of 8 rows, four pixels per thread; images of fewer than 8 rows: bands of 4, two pixels
+  pl->R = g.H >= 8 ? 8 : 4;
+  pl->px = g.H >= 8 ? 4 : 2;
   // a warp spans 32 / W rows when the image is narrow: a row pitch of W (mod 32) keeps its lanes in distinct banks
   int rp = N * Wp;
   if (g.W < 32) rp += ((g.W - rp % 32) + 32) % 32;
@@ -649,7 +653,7 @@ int plan_direct(int dtype, const ConvGeom& g, int N, DirectPlan* pl) {
     cc /= 2;
   }
   pl->c_chunk = cc;
-  const int items = (((pl->R / 2) * g.W + 31) / 32) * (cc / pl->ct);
+  const int items = (((pl->R / pl->px) * g.W + 31) / 32) * (cc / pl->ct);
   pl->threads = 32 * (items < 8 ? items : 8);
   if ((int64_t)g.B * ((g.H + pl->R - 1) / pl->R) >= 2147483647 || g.C / cc > 65535) return 0;
   pl->m_w = magic_of(g.W);
@@ -925,15 +929,19 @@ int al_conv2d_input_grad(int32_t dtype, const void* grad_out, const void* w_mod,
   const float* wm = static_cast<const float*>(w_mod);
   float* gx = static_cast<float*>(grad_x);
   cudaError_t attr = cudaSuccess;
-  if (pl.ct == 8) {
-    if (pl.smem > 48 * 1024)
-      attr = cudaFuncSetAttribute(conv2d_dgrad_direct_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDirectMaxSmem);
-    if (attr == cudaSuccess) conv2d_dgrad_direct_kernel<8><<<grid, pl.threads, pl.smem, (cudaStream_t)stream>>>(go, wm, g, N, pl, gx);
-  } else {
-    if (pl.smem > 48 * 1024)
-      attr = cudaFuncSetAttribute(conv2d_dgrad_direct_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDirectMaxSmem);
-    if (attr == cudaSuccess) conv2d_dgrad_direct_kernel<4><<<grid, pl.threads, pl.smem, (cudaStream_t)stream>>>(go, wm, g, N, pl, gx);
-  }
+#define AL_LAUNCH_DIRECT(CT_, PX_)                                                                                   \
+  do {                                                                                                               \
+    if (pl.smem > 48 * 1024)                                                                                         \
+      attr = cudaFuncSetAttribute(conv2d_dgrad_direct_kernel<CT_, PX_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                  (int)kDirectMaxSmem);                                                              \
+    if (attr == cudaSuccess)                                                                                         \
+      conv2d_dgrad_direct_kernel<CT_, PX_><<<grid, pl.threads, pl.smem, (cudaStream_t)stream>>>(go, wm, g, N, pl, gx); \
+  } while (0)
+  if (pl.ct == 8 && pl.px == 4) AL_LAUNCH_DIRECT(8, 4);
+  else if (pl.ct == 8) AL_LAUNCH_DIRECT(8, 2);
+  else if (pl.px == 4) AL_LAUNCH_DIRECT(4, 4);
+  else AL_LAUNCH_DIRECT(4, 2);
+#undef AL_LAUNCH_DIRECT
   if (attr != cudaSuccess) {
     set_error("al_conv2d_input_grad: cudaFuncSetAttribute: %s", cudaGetErrorString(attr));
     return AL_ERR_CUDA;

@@ -261,15 +261,16 @@ def test_patch_extraction_with_the_dac_fused_is_bit_exact(dtype, cin, size, stri
 
 
 @pytest.mark.parametrize("cin,cout,size,batch,ksize,pad", [
-    (16, 16, 32, 8, 3, 1),      # bands of 4 rows, 8 channels per thread
-    (16, 16, 32, 224, 3, 1),    # enough images for bands of 8 rows (the ResNet-32 stage-1 shape)
+    (16, 16, 32, 8, 3, 1),      # bands of 8 rows, 4 pixels x 8 channels per thread
+    (16, 16, 32, 224, 3, 1),    # the ResNet-32 stage-1 shape
+    (8, 8, 6, 2, 3, 1),         # fewer than 8 rows: bands of 4, 2 pixels per thread
     (32, 32, 16, 64, 3, 1),     # 16 columns: a warp spans two rows; weights beyond 48 KB of shared memory
     (16, 32, 32, 4, 3, 1),
     (8, 12, 20, 3, 3, 1),       # a row length that does not divide 32
     (4, 4, 9, 2, 3, 0),         # no padding, a last band with a single row, 4 channels per thread
     (8, 8, 12, 2, 5, 2),        # 5 x 5 taps
     (64, 32, 8, 16, 3, 1),      # 64 input channels
-], ids=["c16", "c16-bands-of-8", "c32-w16", "n32", "w20", "h9-no-padding", "taps-5x5", "c64"])
+], ids=["c16", "c16-batch-224", "h6", "c32-w16", "n32", "w20", "h9-no-padding", "taps-5x5", "c64"])
 def test_direct_input_gradient_of_a_convolution_matches_the_patch_route(cin, cout, size, batch, ksize, pad):
     """fp32 convolutions with fewer than 64 output channels and no ADC compute their input gradient straight from
     the output gradient (``al_conv2d_input_grad``): same values as patch gradient + fold, and as the autograd of a
