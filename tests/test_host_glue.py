@@ -105,3 +105,22 @@ def test_backward_refuses_a_scratch_buffer_that_is_too_small():
     args.reduce_scratch_floats = lib.al_backward_scratch_floats(m, k, n, t) - 1
     assert lib.al_backward(desc, args, None) == _lib.AL_ERR_BAD_ARGUMENT
     assert b"reduce_scratch holds" in lib.al_last_error()
+
+
+def test_direct_convolution_input_gradient_says_which_layers_it_covers():
+    """``al_conv2d_input_grad_supported`` is host arithmetic (geometry, divisibility, shared-memory budget): the
+    unit-stride fp32 convolutions of ResNet-32 qualify, strided / dilated / bf16 layers and ragged channel counts
+    take the patch-gradient route."""
+    lib = _lib.load()
+    ok = lib.al_conv2d_input_grad_supported
+    for cin, cout, size in ((16, 16, 32), (32, 32, 16), (64, 64, 8), (16, 32, 32)):
+        assert ok(_lib.AL_F32, cout, 256, cin, size, size, 3, 3, 1, 1, 1, 1, 1, 1) == 1
+    assert ok(_lib.AL_BF16, 16, 256, 16, 32, 32, 3, 3, 1, 1, 1, 1, 1, 1) == 0
+    assert ok(_lib.AL_F32, 32, 256, 16, 32, 32, 3, 3, 2, 2, 1, 1, 1, 1) == 0      # strided
+    assert ok(_lib.AL_F32, 16, 256, 16, 32, 32, 3, 3, 1, 1, 2, 2, 2, 2) == 0      # dilated
+    assert ok(_lib.AL_F32, 16, 256, 16, 32, 32, 3, 3, 1, 1, 3, 3, 1, 1) == 0      # padding as large as the kernel
+    assert ok(_lib.AL_F32, 10, 256, 16, 32, 32, 3, 3, 1, 1, 1, 1, 1, 1) == 0      # output channels not a multiple of 4
+    assert ok(_lib.AL_F32, 16, 256, 3, 32, 32, 3, 3, 1, 1, 1, 1, 1, 1) == 0       # three input channels
+    assert ok(_lib.AL_F32, 16, 0, 16, 32, 32, 3, 3, 1, 1, 1, 1, 1, 1) == 0        # no image
+    # wide layers: the weights of a channel chunk must fit 96 KB of shared memory next to the staged rows
+    assert ok(_lib.AL_F32, 256, 8, 256, 14, 14, 3, 3, 1, 1, 1, 1, 1, 1) == 0
