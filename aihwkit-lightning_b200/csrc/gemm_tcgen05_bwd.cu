@@ -436,6 +436,35 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   return mbar_wait(bar, parity, abort_flag);
 }
 
+// Work list of the pair kernel.  Pair p takes items p, p + n_pairs, ...  When the blocks do not fill the last round
+// (rem = num_work mod n_pairs pairs busy, the others idle for a whole block) and 2 rem <= n_pairs, the last rem blocks
+// are cut into two halves of 128 columns each, so that the last round keeps 2 rem pairs busy for a shorter time:
+// items [0, n_full) are whole blocks, items [n_full, total) half blocks.  A half block still reads the whole A tile
+// per k-step, so it takes about three quarters of a block, not half: the cut is made only where the last round is
+// a large share of the launch (at most kSplitTailRounds full rounds before it).  Every role of the kernel walks
+// the same list.
+constexpr int kSplitTailRounds = 3;
+struct PairWork {
+  int n_full, total;
+};
+__device__ __forceinline__ PairWork pair_work_list(int num_work, int n_pairs) {
+  const int rem = num_work % n_pairs;
+  PairWork pw;
+  pw.n_full = (rem > 0 && 2 * rem <= n_pairs && num_work / n_pairs <= kSplitTailRounds) ? num_work - rem : num_work;
+  pw.total = pw.n_full + 2 * (num_work - pw.n_full);
+  return pw;
+}
+// item v -> block index; *half = -1 for a whole block, else which 128-column half of it
+__device__ __forceinline__ int pair_item(const PairWork& pw, int v, int* half) {
+  if (v < pw.n_full) {
+    *half = -1;
+    return v;
+  }
+  const int h = v - pw.n_full;
+  *half = h & 1;
+  return pw.n_full + (h >> 1);
+}
+
 template <bool WGRAD>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kBwdThreads, 1)
 bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -452,6 +481,7 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const bool split_acc = p.products > 1;  // see bwd_tc_kernel
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int num_work = p.num_ib * p.T * p.num_jb;  // num_ib counts 256-row blocks here
+  const PairWork pw = pair_work_list(num_work, n_pairs);
   const int row_off = (int)rank * BM;               // this CTA's rows inside the pair's block
 
   if (threadIdx.x == 0) {
@@ -482,12 +512,17 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       tma_prefetch_desc(&map_b);
       uint32_t it = 0;
       bool ok = true;
-      for (int w = pair; w < num_work && ok; w += n_pairs) {
+      for (int v = pair; v < pw.total && ok; v += n_pairs) {
+        int half;
+        const int w = pair_item(pw, v, &half);
         const int ib = w / (p.T * p.num_jb);
         const int rem = w % (p.T * p.num_jb);
         const int t = rem / p.num_jb, jb = rem % p.num_jb;
         const int i0 = ib * (2 * BM) + row_off;
-        const int j0 = t * p.tile_w + jb * P_BN + (int)rank * P_BN_CTA;
+        // this CTA's columns of B: 128 of the block's 256, or 64 of the half block's 128
+        const int b_boxes = half >= 0 ? P_BN_CTA / 128 : P_BN_CTA / 64;
+        const int j0 = t * p.tile_w + jb * P_BN + (half > 0 ? P_BN / 2 : 0) + (int)rank * b_boxes * 64;
+        const uint32_t stage_bytes = (uint32_t)(P_A_BYTES + b_boxes * B_BOX_BYTES);
         for (int q = 0; q < p.products && ok; ++q) {
           const int plane_a = p.pa[q] + t * p.a_planes_per_tile, plane_b = p.pb[q];
           for (int ls = 0; ls < p.lsteps; ++ls, ++it) {
@@ -503,10 +538,10 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             const int l0 = ls * BK;
             uint32_t bar;
             if (masked) {
-              mbar_expect_tx(&bars->full[s], P_STAGE_BYTES);
+              mbar_expect_tx(&bars->full[s], stage_bytes);
               bar = smem_u32(&bars->full[s]);
             } else {
-              if (leader) mbar_expect_tx(&bars->full[s], 2 * P_STAGE_BYTES);
+              if (leader) mbar_expect_tx(&bars->full[s], 2 * stage_bytes);
               bar = mapa_u32(smem_u32(&bars->full[s]), 0);
             }
             if (WGRAD) {
@@ -515,8 +550,7 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             } else {
               tma_load_3d_pair(sa, &map_a, bar, l0, i0, plane_a);
             }
-#pragma unroll
-            for (int c = 0; c < P_BN_CTA / 64; ++c)
+            for (int c = 0; c < b_boxes; ++c)
               tma_load_3d_pair(sb + c * B_BOX_BYTES, &map_b, bar, j0 + c * 64, l0, plane_b);
           }
         }
@@ -542,10 +576,12 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   } else if (warp == 1) {
     // ---- MMA issuer (leader only) --------------------------------------------------------
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = make_idesc(2 * BM, P_BN, WGRAD ? 1 : 0, 1);
+      constexpr uint32_t idesc_block = make_idesc(2 * BM, P_BN, WGRAD ? 1 : 0, 1);
+      constexpr uint32_t idesc_half = make_idesc(2 * BM, P_BN / 2, WGRAD ? 1 : 0, 1);
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
-      for (int w = pair; w < num_work && ok; w += n_pairs, ++acc_it) {
+      for (int v = pair; v < pw.total && ok; v += n_pairs, ++acc_it) {
+        const uint32_t idesc = v < pw.n_full ? idesc_block : idesc_half;
         const int b = split_acc ? 0 : (int)(acc_it & 1u);
         const uint32_t aph = split_acc ? (acc_it & 1u) : ((acc_it >> 1) & 1u);
         if (!mbar_wait_cluster(&bars->acc_empty[b], aph ^ 1u, abort_flag)) {
@@ -595,11 +631,14 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     uint32_t acc_it = 0;
     bool ok = true;
-    for (int w = pair; w < num_work && ok; w += n_pairs, ++acc_it) {
+    for (int v = pair; v < pw.total && ok; v += n_pairs, ++acc_it) {
+      int half;
+      const int w = pair_item(pw, v, &half);
       const int ib = w / (p.T * p.num_jb);
       const int rem = w % (p.T * p.num_jb);
       const int t = rem / p.num_jb, jb = rem % p.num_jb;
-      const int j0 = t * p.tile_w + jb * P_BN;
+      const int j0 = t * p.tile_w + jb * P_BN + (half > 0 ? P_BN / 2 : 0);
+      const int n_chunks = half >= 0 ? P_BN / 64 : P_BN / 32;  // chunks of 32 accumulator columns
       const int j_end = min((t + 1) * p.tile_w, p.K);
       const int i = ib * (2 * BM) + row_off + quad * 32 + lane;
       void* const c_dst = p.c_out;
@@ -614,7 +653,7 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       tc_fence_after();
       const float c_scale = p.c_scale_ir != nullptr ? quant_step<kF32>(p.c_scale_ir[t], p.inp_res) : 1.0f;
 #pragma unroll 1
-      for (int c = 0; c < P_BN / 32; ++c) {
+      for (int c = 0; c < n_chunks; ++c) {
         const int jc = j0 + c * 32;
         if (jc >= j_end) break;  // uniform across the warp
         uint32_t r[32];
@@ -627,21 +666,23 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->acc_empty[b]), 0));
     }
-  } else if (warp >= 8 && masked && pair < num_work) {
+  } else if (warp >= 8 && masked && pair < pw.total) {
     // ---- mask transform (both CTAs, own A tile): see bwd_tc_kernel -------------------------
     const int grp = (warp - 8) >> 2;
     const int r = threadIdx.x - (8 + 4 * grp) * 32;  // 0..127
     const int row_in_box = WGRAD ? (r & 63) : r;
     const int box = WGRAD ? (r >> 6) : 0;
-    const int total = ((num_work - pair + n_pairs - 1) / n_pairs) * p.lsteps;
+    const int total = ((pw.total - pair + n_pairs - 1) / n_pairs) * p.lsteps;
     const int m_last = p.M - 1, w_last = p.mask_words - 1;
-    int f_w = pair + (grp / p.lsteps) * n_pairs, f_ls = grp % p.lsteps;
+    int f_w = pair + (grp / p.lsteps) * n_pairs, f_ls = grp % p.lsteps;  // f_w: item of the work list
     const uint32_t* f_lo = p.keep_mask;
     const uint32_t* f_hi = p.keep_mask;
     auto seek_item = [&]() {
-      if (f_w >= num_work) return;
-      const int ib = f_w / (p.T * p.num_jb);
-      const int t = (f_w % (p.T * p.num_jb)) / p.num_jb;
+      if (f_w >= pw.total) return;
+      int half;
+      const int blk = pair_item(pw, f_w, &half);  // a half block has the A tile of its block
+      const int ib = blk / (p.T * p.num_jb);
+      const int t = (blk % (p.T * p.num_jb)) / p.num_jb;
       const int i0 = ib * (2 * BM) + row_off;
       const uint32_t* tile = p.keep_mask + (int64_t)t * p.mask_words * p.M;
       if (WGRAD) {

@@ -41,6 +41,11 @@ SHAPES = [
     ("bf16_dynamic_adc_noise", dict(in_shape=(384, 512), out_features=392, max_input_size=128, out_bound=0.3)),
     ("bf16_static_adc", dict(in_shape=(200, 512), out_features=264, max_input_size=256, ir_init_value=2.0,
                              out_bound=0.5)),
+    # 80 blocks of 256 x 256 for both backward GEMMs: on 74 CTA pairs the last 6 blocks run as 12 half blocks
+    # (masked operands)
+    ("bf16_dynamic_adc_noise", dict(in_shape=(2560, 2048), out_features=2560, max_input_size=512)),
+    # the same for the weight gradient without a clamp mask and with tiles that end inside a block (84 blocks)
+    ("bf16_static_noise", dict(in_shape=(384, 2304), out_features=1792, max_input_size=384, ir_init_value=2.0)),
 ]
 
 
