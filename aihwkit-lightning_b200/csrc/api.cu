@@ -7,6 +7,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
+
 #include <nvtx3/nvToolsExt.h>
 
 #include "analog_math.cuh"
@@ -172,6 +174,32 @@ int comm_reserved_sms() { return g_reserved_sms; }
 }  // namespace al
 
 using namespace al;
+
+// The weight pre-pass of a large layer runs beside the DAC pass of its input on a second stream (both stream
+// through HBM once and neither fills it alone): the caller's stream forks before the DAC launch and joins before
+// the GEMM.  One stream and two events per device and host thread, made on first use.
+namespace {
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  bool ready = false;
+};
+SideStream* side_stream() {
+  thread_local SideStream table[64];  // per host thread: two threads never share the fork / join events
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  SideStream& ss = table[dev];
+  if (!ss.ready) {
+    if (cudaStreamCreateWithFlags(&ss.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&ss.join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    ss.ready = true;
+  }
+  return &ss;
+}
+// both passes move at least this many elements: below that the fork and join cost more than they hide
+constexpr int64_t kOverlapMinElems = (int64_t)1 << 22;
+}  // namespace
 
 extern "C" {
 
@@ -349,6 +377,7 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
   // 2. DAC: x -> xq (+ per-row ranges in dynamic mode)
   const void* xq = a->x;
   bool tile_max_zeroed = false;
+  SideStream* side = nullptr;  // non-null: forked, the weight pre-pass goes there
   if (prequantised) {
     xq = a->xq;
   } else if (d.ir_mode != AL_IR_OFF && !smallm_dac) {
@@ -358,9 +387,17 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     }
     // the fused weight pre-pass that follows accumulates tile maxima into w_tile_max: the DAC kernel
     // clears those words on its way (no memset between the two kernels)
-    const bool fused_weights_next = !smallm && d.clip_type != AL_CLIP_LEARNABLE_PER_CHANNEL && needs_wmax(dv) &&
-                                    dv.weight_quant == AL_QUANT_NONE && dv.weight_noise != AL_NOISE_ADD_NORMAL &&
-                                    a->w_amax && a->w_tile_max;
+    bool fused_weights_next = !smallm && d.clip_type != AL_CLIP_LEARNABLE_PER_CHANNEL && needs_wmax(dv) &&
+                              dv.weight_quant == AL_QUANT_NONE && dv.weight_noise != AL_NOISE_ADD_NORMAL &&
+                              a->w_amax && a->w_tile_max;
+    if (fused_weights_next && (int64_t)d.M * d.K >= kOverlapMinElems && (int64_t)d.N * d.K >= kOverlapMinElems &&
+        a->w_mod && a->w_mod != a->w) {
+      side = side_stream();
+      if (side && cudaEventRecord(side->fork, s) == cudaSuccess && cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess)
+        fused_weights_next = false;  // the weight pass clears its own words: it no longer runs behind the DAC kernel
+      else
+        side = nullptr;
+    }
     rc = launch_dac(d.dtype, a->x, d.M, d.K, tt, d.ir_mode == AL_IR_FAST ? AL_IR_STATIC : d.ir_mode, ir_static, dv.has_dac ? dv.inp_res : -1.0f,
                     d.no_rounding, a->xq, a->ir_rows, a->codes, s, tc_f32 ? a->codes16 : nullptr,
                     fused_weights_next ? a->w_tile_max : nullptr, 2 * d.T, &tile_max_zeroed);
@@ -427,8 +464,17 @@ int al_forward(const AlDesc* desc, const AlForwardArgs* a, void* stream) {
     if (dv.weight_quant == AL_QUANT_NONE && dv.weight_noise != AL_NOISE_ADD_NORMAL) {
       // every scale the modifier needs is the segment's own abs-max: one sweep over w
       rc = launch_weight_fused(d.dtype, a->w, d.N, d.K, tt, a->w_amax, tile_max, dv.weight_noise,
-                               dv.std_dev, a->w_noise, a->seed, a->offset, modifies ? a->w_mod : nullptr, s,
-                               a->offset_base, tile_max_zeroed);
+                               dv.std_dev, a->w_noise, a->seed, a->offset, modifies ? a->w_mod : nullptr,
+                               side ? side->stream : s, a->offset_base, tile_max_zeroed);
+      if (side) {  // join, also after a failed launch: the caller's stream must not stay forked
+        const cudaError_t ej = cudaEventRecord(side->join, side->stream);
+        const cudaError_t ew = ej == cudaSuccess ? cudaStreamWaitEvent(s, side->join, 0) : ej;
+        if (ew != cudaSuccess && !rc) {
+          set_error("al_forward: joining the weight pre-pass: %s", cudaGetErrorString(ew));
+          rc = AL_ERR_CUDA;
+        }
+        side = nullptr;
+      }
       if (rc) return rc;
     } else {
       rc = launch_abs_max_tiles(d.dtype, a->w, d.N, d.K, tt, a->w_amax, s);
