@@ -5,6 +5,7 @@
 #include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -185,6 +186,12 @@ struct SideStream {
   bool ready = false;
 };
 SideStream* side_stream() {
+  // AL_B200_SERIAL_PREPASS=1 in the environment keeps both passes on the caller's stream (for A/B timing)
+  static const bool serial = [] {
+    const char* v = getenv("AL_B200_SERIAL_PREPASS");
+    return v != nullptr && v[0] == '1';
+  }();
+  if (serial) return nullptr;
   thread_local SideStream table[64];  // per host thread: two threads never share the fork / join events
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
