@@ -101,6 +101,7 @@ SYMBOLS = {
                                     c_int64, c_uint32, c_float, c_int32, c_void_p]),
     "al_peer_read_error": (c_int32, [POINTER(c_uint32)]),
     "al_wgrad_split_plan": (c_int32, [c_int32, c_int32, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
+    "al_pair_work_item": (c_int32, [c_int32, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32)]),
     "al_profile_enable": (c_int32, [c_int32]),
     "al_profile_select": (c_int32, [c_uint32]),
     "al_profile_read": (c_int32, [POINTER(AlProfileEntry), c_int32]),

@@ -555,6 +555,19 @@ int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T) {
   return backward_reduce_floats(M, N, T) + al::wgrad_simt_partial_floats(M, K, N, T);
 }
 
+int al_pair_work_item(int32_t num_blocks, int32_t n_pairs, int32_t item, int32_t* total, int32_t* block, int32_t* half) {
+  if (num_blocks < 1 || n_pairs < 1 || !total || !block || !half) {
+    set_error("al_pair_work_item: non-positive size or null output");
+    return AL_ERR_BAD_ARGUMENT;
+  }
+  int t = 0, b = -1, h = -1;
+  tc_pair_work_item(num_blocks, n_pairs, item, &t, &b, &h);
+  *total = t;
+  *block = b;
+  *half = h;
+  return AL_OK;
+}
+
 int al_wgrad_split_plan(int32_t M, int32_t K, int32_t N, int32_t T, int32_t* splits, int32_t* rows_per_split) {
   if (M <= 0 || K <= 0 || N <= 0 || T <= 0 || !splits || !rows_per_split) {
     set_error("al_wgrad_split_plan: non-positive size or null output");

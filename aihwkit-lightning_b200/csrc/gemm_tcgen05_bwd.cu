@@ -447,7 +447,7 @@ constexpr int kSplitTailRounds = 3;
 struct PairWork {
   int n_full, total;
 };
-__device__ __forceinline__ PairWork pair_work_list(int num_work, int n_pairs) {
+__host__ __device__ __forceinline__ PairWork pair_work_list(int num_work, int n_pairs) {
   const int rem = num_work % n_pairs;
   PairWork pw;
   pw.n_full = (rem > 0 && 2 * rem <= n_pairs && num_work / n_pairs <= kSplitTailRounds) ? num_work - rem : num_work;
@@ -455,7 +455,7 @@ __device__ __forceinline__ PairWork pair_work_list(int num_work, int n_pairs) {
   return pw;
 }
 // item v -> block index; *half = -1 for a whole block, else which 128-column half of it
-__device__ __forceinline__ int pair_item(const PairWork& pw, int v, int* half) {
+__host__ __device__ __forceinline__ int pair_item(const PairWork& pw, int v, int* half) {
   if (v < pw.n_full) {
     *half = -1;
     return v;
@@ -772,6 +772,15 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 }  // namespace
 
 bool tc_backward_supported(const AlDesc& d, const TileTable& tt) { return tc_shape_ok(d, tt); }
+
+// The pair kernel's work list on the host (the same two functions the kernel calls), for the tests.
+void tc_pair_work_item(int num_work, int n_pairs, int item, int* total, int* block, int* half) {
+  const PairWork pw = pair_work_list(num_work, n_pairs);
+  *total = pw.total;
+  *block = -1;
+  *half = -1;
+  if (item >= 0 && item < pw.total) *block = pair_item(pw, item, half);
+}
 
 // How many 2-CTA clusters of the pair kernel the device runs at once (0: cannot run them).
 static int max_pairs(bool wgrad) {

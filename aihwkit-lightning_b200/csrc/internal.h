@@ -167,6 +167,7 @@ bool tc_forward_supported(const AlDesc& d, const TileTable& tt);
 int launch_fwd_tc(int round_dt, const void* xq, const void* w_mod, int K, const TileTable& tt,
                   const FwdEpilogueParams& ep, int pairing, void* out, cudaStream_t s);
 bool tc_backward_supported(const AlDesc& d, const TileTable& tt);
+void tc_pair_work_item(int num_work, int n_pairs, int item, int* total, int* block, int* half);
 // pairing: 0 = CTA pairs when they fill the machine, 1 = always pairs, -1 = never
 int launch_dgrad_tc(const void* g, const void* w_mod, const uint32_t* keep_mask, int mask_words,
                     int M, int K, int N, const TileTable& tt, int pairing, void* grad_x, cudaStream_t s);

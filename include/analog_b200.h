@@ -232,6 +232,12 @@ int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T);
  * split, splits * N * K floats of reduce_scratch (behind the reductions) hold the partial sums.  A
  * function of the layer's sizes alone: the same whether or not the call carries a clamp mask. */
 int al_wgrad_split_plan(int32_t M, int32_t K, int32_t N, int32_t T, int32_t* splits, int32_t* rows_per_split);
+/* Work list of the backward GEMMs on CTA pairs: `num_blocks` output blocks of 256 x 256 walked by `n_pairs` pairs
+ * (pair p takes items p, p + n_pairs, ...).  When the last round would keep at most half of the pairs busy (and at
+ * most three full rounds precede it) its blocks are listed as two half blocks of 128 columns each.  Returns the
+ * length of the list in *total and, for 0 <= item < *total, the block of that item and which half of it (-1: the
+ * whole block); *block = -1 for an item outside the list.  Host arithmetic, the functions the kernel itself calls. */
+int al_pair_work_item(int32_t num_blocks, int32_t n_pairs, int32_t item, int32_t* total, int32_t* block, int32_t* half);
 /* bf16 elements of AlBackwardArgs.g_planes for an fp32 layer on the tensor cores: the upstream
  * gradient as bf16 planes, per analog tile when the ADC clamp mask or a per-row DAC step has
  * to be folded in.  tile_ends_host as in the forward.  0 when the layer runs on the CUDA cores. */

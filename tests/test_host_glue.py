@@ -124,3 +124,46 @@ def test_direct_convolution_input_gradient_says_which_layers_it_covers():
     assert ok(_lib.AL_F32, 16, 0, 16, 32, 32, 3, 3, 1, 1, 1, 1, 1, 1) == 0        # no image
     # wide layers: the weights of a channel chunk must fit 96 KB of shared memory next to the staged rows
     assert ok(_lib.AL_F32, 256, 8, 256, 14, 14, 3, 3, 1, 1, 1, 1, 1, 1) == 0
+
+
+def test_pair_kernel_work_list_covers_every_block_once():
+    """The backward GEMMs on CTA pairs walk a list of whole blocks followed, when the last round would be short, by
+    the halves of its blocks: every block appears once as a whole or once per half, no pair gets more than one half
+    block, and the list is only cut when it shortens the last round."""
+    import ctypes
+
+    lib = _lib.load()
+    total, block, half = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
+
+    def items(num_blocks, n_pairs):
+        assert lib.al_pair_work_item(num_blocks, n_pairs, 0, total, block, half) == _lib.AL_OK
+        out = []
+        for v in range(total.value):
+            assert lib.al_pair_work_item(num_blocks, n_pairs, v, total, block, half) == _lib.AL_OK
+            out.append((block.value, half.value))
+        assert lib.al_pair_work_item(num_blocks, n_pairs, total.value, total, block, half) == _lib.AL_OK
+        assert block.value == -1
+        return out
+
+    cut = 0
+    for n_pairs in (1, 2, 7, 66, 70, 74):
+        for num_blocks in list(range(1, 4 * n_pairs + 3)) + [256, 384, 432, 512, 768, 1024, 1152]:
+            work = items(num_blocks, n_pairs)
+            whole = [b for b, h in work if h < 0]
+            halves = [(b, h) for b, h in work if h >= 0]
+            assert whole == list(range(len(whole)))
+            assert sorted(halves) == [(b, h) for b in range(len(whole), num_blocks) for h in (0, 1)]
+            if halves:
+                cut += 1
+                rem = num_blocks % n_pairs
+                assert len(whole) % n_pairs == 0 and len(whole) // n_pairs <= 3
+                assert 0 < rem and 2 * rem <= n_pairs and len(halves) == 2 * rem
+                # items of one pair: v = p, p + n_pairs, ...; the half blocks sit in the last round, one per pair
+                assert all(v >= len(whole) for v, (b, h) in enumerate(work) if h >= 0)
+            else:
+                assert len(work) == num_blocks
+    assert cut > 0
+    # config 2's weight gradient: 256 blocks on 74 pairs -> 222 whole blocks and the last 34 as 68 halves
+    work = items(256, 74)
+    assert len(work) == 222 + 68 and work[221] == (221, -1) and work[222] == (222, 0) and work[-1] == (255, 1)
+    assert lib.al_pair_work_item(0, 74, 0, total, block, half) == _lib.AL_ERR_BAD_ARGUMENT
