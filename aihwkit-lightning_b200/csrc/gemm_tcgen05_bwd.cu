@@ -447,10 +447,11 @@ constexpr int kSplitTailRounds = 3;
 struct PairWork {
   int n_full, total;
 };
-__host__ __device__ __forceinline__ PairWork pair_work_list(int num_work, int n_pairs) {
+__host__ __device__ __forceinline__ PairWork pair_work_list(int num_work, int n_pairs, bool allow_halves = true) {
   const int rem = num_work % n_pairs;
   PairWork pw;
-  pw.n_full = (rem > 0 && 2 * rem <= n_pairs && num_work / n_pairs <= kSplitTailRounds) ? num_work - rem : num_work;
+  pw.n_full = (allow_halves && rem > 0 && 2 * rem <= n_pairs && num_work / n_pairs <= kSplitTailRounds) ? num_work - rem
+                                                                                                        : num_work;
   pw.total = pw.n_full + 2 * (num_work - pw.n_full);
   return pw;
 }
@@ -481,7 +482,9 @@ bwd_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const bool split_acc = p.products > 1;  // see bwd_tc_kernel
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int num_work = p.num_ib * p.T * p.num_jb;  // num_ib counts 256-row blocks here
-  const PairWork pw = pair_work_list(num_work, n_pairs);
+  // half blocks only for plain bf16 operands: with the plane products of an fp32 layer (two accumulators per block)
+  // the cut has not been measured, so those launches keep whole blocks
+  const PairWork pw = pair_work_list(num_work, n_pairs, p.products == 1);
   const int row_off = (int)rank * BM;               // this CTA's rows inside the pair's block
 
   if (threadIdx.x == 0) {

@@ -234,7 +234,8 @@ int64_t al_backward_scratch_floats(int32_t M, int32_t K, int32_t N, int32_t T);
 int al_wgrad_split_plan(int32_t M, int32_t K, int32_t N, int32_t T, int32_t* splits, int32_t* rows_per_split);
 /* Work list of the backward GEMMs on CTA pairs: `num_blocks` output blocks of 256 x 256 walked by `n_pairs` pairs
  * (pair p takes items p, p + n_pairs, ...).  When the last round would keep at most half of the pairs busy (and at
- * most three full rounds precede it) its blocks are listed as two half blocks of 128 columns each.  Returns the
+ * most three full rounds precede it) its blocks are listed as two half blocks of 128 columns each (bf16 layers; the
+ * plane products of fp32 layers always take whole blocks).  Returns the
  * length of the list in *total and, for 0 <= item < *total, the block of that item and which half of it (-1: the
  * whole block); *block = -1 for an item outside the list.  Host arithmetic, the functions the kernel itself calls. */
 int al_pair_work_item(int32_t num_blocks, int32_t n_pairs, int32_t item, int32_t* total, int32_t* block, int32_t* half);
